@@ -1,0 +1,166 @@
+/*
+ * twmarlin.h — C ABI of libtwmarlin: the TW-Marlin W4A16 Q4 GEMM family for
+ * NVIDIA B200 (sm_100a), compiled ahead of time.  No JIT, no CPU fallback.
+ *
+ * Data contract (identical to the reference engine's tensors):
+ *   packed : u8  [K/32][N][16]  byte i of a 16-byte block holds the nibble of
+ *            k = 32*g + 2*i in its low half and k = 32*g + 2*i + 1 in its high
+ *            half (crates/loader/src/gemma_moe_q4.rs:239-249,
+ *            crates/kernels/src/quantize.rs:1207-1217,1226).
+ *   scales : f16 [K/G][N]       one scale per G consecutive K of a column.
+ *            G = 32 is the reference's layout (quantize.rs:1221); G = 128
+ *            shares one scale between four consecutive 32-blocks.
+ *   weight : w[k][n] = f32(scales[k/G][n]) * (nibble(k,n) - 8).
+ *
+ * Conventions, as on the reference's Rust entry points
+ * (crates/kernels/src/quantize.rs:1301-1360): every pointer is a device
+ * pointer owned by the caller; calls only enqueue work on the given stream and
+ * never synchronise or allocate, so they are legal during stream capture; the
+ * status is returned, nothing aborts.  `stream` is a CUstream / cudaStream_t
+ * passed as void* (NULL = legacy default stream).
+ */
+#ifndef TWMARLIN_H
+#define TWMARLIN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum twm_status {
+    TWM_OK = 0,
+    TWM_EINVAL = -1,     /* bad shape, dtype, null pointer (the reference panics: quantize.rs:1311) */
+    TWM_EALIGN = -2,     /* packed not 16-byte aligned, a/c not aligned to their vector width */
+    TWM_EWORKSPACE = -3, /* split-K needs more workspace than was passed */
+    TWM_ELAUNCH = -4,    /* CUDA reported a launch error (DeviceError::Launch in the reference) */
+    TWM_EARCH = -5,      /* the device is not sm_100 */
+    TWM_ETIMEOUT = -6    /* a bounded device-side wait expired (reported by twm_device_error) */
+} twm_status;
+
+typedef enum twm_dtype { TWM_F32 = 0, TWM_F16 = 1 } twm_dtype;
+
+/* Kernel families twm_plan can choose. */
+enum {
+    TWM_KERNEL_AUTO = 0,
+    TWM_KERNEL_SIMT = 1, /* memory-bound streaming kernel, FP32 FMA, M <= 8 */
+    TWM_KERNEL_TC = 2    /* tcgen05 tensor-core kernel, fp16 operands, fp32 accumulate in TMEM */
+};
+
+/* Flags of twm_gemm_args.flags. */
+enum {
+    /* Launch with programmatic stream serialisation: the kernel may start
+     * streaming packed/scales while the kernel before it in the stream is still
+     * running, and waits for that kernel only before it reads `a`, the
+     * workspace or `c`.  Set it when the weights are constants (the decode
+     * loop); leave it clear when the preceding kernel writes packed/scales. */
+    TWM_FLAG_PDL = 1,
+    TWM_FLAG_ACCUMULATE = 2 /* c += result instead of c = result (residual add fused in the epilogue) */
+};
+
+/* One GEMM  C[M,N] = A[M,K] x dequant(packed, scales).
+ * Replaces gemm_tw_marlin_m1 (quantize.rs:1301-1360) for M = 1 with f32 A/C,
+ * gemm_tw_marlin_m1_from_buffer (quantize.rs:1731-1782; pass offset pointers)
+ * and gemm_tw_marlin_m1_indirect (quantize_indirect.rs:228-253; fill the
+ * *_offsets fields), and is the M > 1 TW-Marlin GEMM the reference lacks
+ * (its stand-in is gemm_q4_0, quantize.rs:1825-1858). */
+typedef struct twm_gemm_args {
+    int M, N, K;
+    int group_size;          /* 32 or 128; K % group_size == 0 */
+    int a_dtype, c_dtype;    /* twm_dtype */
+    const void* a;           /* [M, lda] row-major, lda >= K elements */
+    long lda;
+    const uint8_t* packed;   /* [K/32][N][16], 16-byte aligned */
+    const uint16_t* scales;  /* [K/G][N] fp16 bits */
+    void* c;                 /* [M, ldc] row-major; every element of [M,N] is written */
+    long ldc;
+    void* workspace;         /* split-K scratch from twm_workspace_bytes(); may be NULL when 0 bytes are needed.
+                                Zero it once after allocation; the kernels leave its counters at zero.
+                                One workspace serves one stream at a time. */
+    size_t workspace_bytes;
+    int splits_override;     /* 0 = heuristic */
+    int kernel_override;     /* TWM_KERNEL_* ; 0 = heuristic */
+    int flags;               /* TWM_FLAG_* */
+    /* Device-side expert indirection (quantize_indirect.rs:185-200).  When
+     * packed_offsets != NULL the kernel reads packed + packed_offsets[expert_idx]
+     * (bytes, multiple of 16) and scales + scales_offsets[expert_idx] (elements). */
+    const uint32_t* packed_offsets;
+    const uint32_t* scales_offsets;
+    int expert_idx;
+} twm_gemm_args;
+
+/* What the heuristic decided for a shape; pure host arithmetic. */
+typedef struct twm_plan_t {
+    int kernel;          /* TWM_KERNEL_SIMT or TWM_KERNEL_TC */
+    int n_tile;          /* columns per CTA */
+    int splits;          /* K slices; 1 = no workspace traffic */
+    int blocks_per_split;/* 32-blocks of K per slice (last slice may be shorter) */
+    int grid_x, grid_y;  /* n tiles, splits */
+    size_t workspace_bytes;
+} twm_plan_t;
+
+/* Replaces the adaptive split-K arithmetic of quantize.rs:1314-1325, re-derived
+ * for 148 SMs.  sm_count <= 0 means 148.  Deterministic: the same arguments
+ * always give the same plan, so a plan made before graph capture stays valid. */
+twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int splits_override,
+                    int kernel_override, twm_plan_t* out);
+
+/* Workspace twm_gemm_w4a16 needs for this shape with the heuristic's own split
+ * count on a 148-SM device (0 when it does not split).  With splits_override
+ * ask twm_plan for the exact figure. */
+size_t twm_workspace_bytes(int M, int N, int K, int group_size);
+
+/* Enqueue one GEMM.  See twm_gemm_args. */
+twm_status twm_gemm_w4a16(const twm_gemm_args* args, void* stream);
+
+/* Dequantise to a dense [K,N] row-major matrix, f32 (exact) or f16 (round to
+ * nearest even of the f32 product).  Replaces warp_dequantize_q4_0 /
+ * dequant_q4_to_f16 (quantize.rs:150-175, 534-618) on the TW-Marlin tensors. */
+twm_status twm_dequant(const uint8_t* packed, const uint16_t* scales, void* out, int out_dtype,
+                       int K, int N, int group_size, void* stream);
+
+/* Quantise + pack on the device.  w is f32, [K,N] row-major when w_is_nk == 0
+ * (quantize_f32_to_tw_marlin, quantize.rs:1171-1180) or [N,K] row-major when
+ * w_is_nk != 0 (cpu_quantize_tw_marlin, gemma_moe_q4.rs:218-254).  Same bytes
+ * as the reference's CPU quantiser for group_size 32. */
+twm_status twm_quantize_pack(const float* w, int w_is_nk, int K, int N, int group_size,
+                             uint8_t* packed, uint16_t* scales, void* stream);
+
+/* Concatenate `count` TW-Marlin matrices along N (fuse_tw_marlin_n,
+ * quantize.rs:1018-1063).  packed_srcs/scales_srcs/ns are HOST arrays of
+ * device pointers / widths; dst tensors hold sum(ns) columns. */
+twm_status twm_fuse_n(const uint8_t* const* packed_srcs, const uint16_t* const* scales_srcs,
+                      const int* ns, int count, int K, int group_size, uint8_t* packed_dst,
+                      uint16_t* scales_dst, void* stream);
+
+/* Column slice [n0, n0+n_len) of a TW-Marlin matrix (tensor-parallel column
+ * shard; the inverse of twm_fuse_n). */
+twm_status twm_slice_n(const uint8_t* packed_src, const uint16_t* scales_src, int K, int N,
+                       int group_size, int n0, int n_len, uint8_t* packed_dst,
+                       uint16_t* scales_dst, void* stream);
+
+/* Row slice [k0, k0+k_len) of a TW-Marlin matrix (tensor-parallel row shard);
+ * k0 and k_len are multiples of group_size.  The slice is contiguous, so this
+ * only returns the byte/element offsets. */
+twm_status twm_slice_k_offsets(int K, int N, int group_size, int k0, int k_len,
+                               size_t* packed_byte_offset, size_t* scales_elem_offset);
+
+const char* twm_status_string(twm_status s);
+
+/* Read and clear the device-side error word.  SYNCHRONISES the stream, so it
+ * is a diagnostic for after a step, not for inside a capture.  *word: bit 0 an
+ * mbarrier wait ran out, bit 1 a split-K wait, bit 2 a peer-flag wait.
+ * Returns TWM_ETIMEOUT when the word was non-zero. */
+twm_status twm_device_error(void* stream, unsigned int* word);
+
+/* Text of the last CUDA error this thread saw inside libtwmarlin ("" if none). */
+const char* twm_last_error(void);
+
+/* Library build tag, e.g. "twmarlin sm_100a". */
+const char* twm_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TWMARLIN_H */

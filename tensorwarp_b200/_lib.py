@@ -1,0 +1,92 @@
+"""ctypes view of the C ABI declared in ``include/twmarlin.h``.
+
+Loading fails loudly: there is no Python or CPU stand-in for any entry point.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG, "libtwmarlin.so")
+
+TWM_OK, TWM_EINVAL, TWM_EALIGN, TWM_EWORKSPACE, TWM_ELAUNCH, TWM_EARCH, TWM_ETIMEOUT = 0, -1, -2, -3, -4, -5, -6
+TWM_F32, TWM_F16 = 0, 1
+TWM_KERNEL_AUTO, TWM_KERNEL_SIMT, TWM_KERNEL_TC = 0, 1, 2
+TWM_FLAG_PDL, TWM_FLAG_ACCUMULATE = 1, 2
+
+
+class GemmArgs(C.Structure):
+    """``twm_gemm_args``."""
+    _fields_ = [
+        ("M", C.c_int), ("N", C.c_int), ("K", C.c_int),
+        ("group_size", C.c_int),
+        ("a_dtype", C.c_int), ("c_dtype", C.c_int),
+        ("a", C.c_void_p), ("lda", C.c_long),
+        ("packed", C.c_void_p), ("scales", C.c_void_p),
+        ("c", C.c_void_p), ("ldc", C.c_long),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("splits_override", C.c_int), ("kernel_override", C.c_int), ("flags", C.c_int),
+        ("packed_offsets", C.c_void_p), ("scales_offsets", C.c_void_p), ("expert_idx", C.c_int),
+    ]
+
+
+class Plan(C.Structure):
+    """``twm_plan_t``."""
+    _fields_ = [
+        ("kernel", C.c_int), ("n_tile", C.c_int), ("splits", C.c_int), ("blocks_per_split", C.c_int),
+        ("grid_x", C.c_int), ("grid_y", C.c_int), ("workspace_bytes", C.c_size_t),
+    ]
+
+
+# name -> (restype, argtypes); every symbol the header declares
+SIGNATURES = {
+    "twm_plan": (C.c_int, [C.c_int] * 7 + [C.POINTER(Plan)]),
+    "twm_workspace_bytes": (C.c_size_t, [C.c_int] * 4),
+    "twm_gemm_w4a16": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
+    "twm_dequant": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "twm_quantize_pack": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "twm_fuse_n": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.c_int, C.c_int,
+                             C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "twm_slice_n": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                              C.c_void_p, C.c_void_p]),
+    "twm_slice_k_offsets": (C.c_int, [C.c_int] * 5 + [C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
+    "twm_device_error": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint)]),
+    "twm_status_string": (C.c_char_p, [C.c_int]),
+    "twm_last_error": (C.c_char_p, []),
+    "twm_version": (C.c_char_p, []),
+}
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Load ``libtwmarlin.so`` (built by ``tensorwarp_b200.build``) and bind every entry point."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: run `python -m tensorwarp_b200.build` (needs nvcc). "
+                "There is no fallback path.")
+        handle = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)   # AttributeError if the symbol is not exported
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+class TwmError(RuntimeError):
+    """A non-zero ``twm_status``; mirrors ``DeviceError`` on the reference's side."""
+
+    def __init__(self, status: int, where: str):
+        self.status = status
+        l = lib()
+        detail = l.twm_last_error().decode() if status == TWM_ELAUNCH else ""
+        super().__init__(f"{where}: {l.twm_status_string(status).decode()}" + (f" [{detail}]" if detail else ""))
+
+
+def check(status: int, where: str) -> None:
+    if status != TWM_OK:
+        raise TwmError(status, where)

@@ -1,0 +1,352 @@
+// twmarlin.cu — the C ABI of libtwmarlin (see include/twmarlin.h) and the host
+// logic behind it: argument checks, the tile / split-K plan, launches.
+//
+// Host-side counterpart of the reference's launcher gemm_tw_marlin_m1
+// (crates/kernels/src/quantize.rs:1301-1360) and of its layout helpers
+// (quantize.rs:1018-1063, 1171-1180).  One translation unit: every kernel
+// header is included here so that no relocatable device code is needed.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "twm_common.cuh"
+#include "twm_gemv_simt.cuh"
+#include "twm_layout.cuh"
+
+namespace {
+
+thread_local char t_last_error[256] = "";
+
+void set_error(const char* where, cudaError_t e)
+{
+    snprintf(t_last_error, sizeof(t_last_error), "%s: %s", where, cudaGetErrorString(e));
+}
+
+constexpr int kMaxDevices = 64;
+constexpr int kDefaultSms = 148;
+constexpr int kMaxSplits = 64;
+constexpr size_t kCounterBytes = 16384;   // 4096 tile counters at the head of the workspace
+
+struct DeviceState {
+    bool ready = false;
+    twm_status status = TWM_OK;
+    int sm_count = kDefaultSms;
+};
+DeviceState g_dev[kMaxDevices];
+std::mutex g_dev_mutex;
+
+// Once per device: check the architecture and raise the dynamic shared memory
+// limit of every kernel that needs more than 48 KB.
+twm_status ensure_device(int* sm_count_out)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { set_error("cudaGetDevice", e); return TWM_ELAUNCH; }
+    if (dev < 0 || dev >= kMaxDevices) return TWM_EINVAL;
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    DeviceState& st = g_dev[dev];
+    if (!st.ready) {
+        int major = 0, sms = 0;
+        cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        st.sm_count = sms > 0 ? sms : kDefaultSms;
+        if (major != 10) {
+            snprintf(t_last_error, sizeof(t_last_error), "device %d is sm_%d*, libtwmarlin holds sm_100a code only", dev, major);
+            st.status = TWM_EARCH;
+        } else {
+            const int smem = (int)sizeof(twm::simt::Smem);
+            cudaError_t r = cudaSuccess;
+            auto raise = [&](const void* fn) {
+                if (r == cudaSuccess) r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            };
+            raise((const void*)twm::simt::gemv_kernel<1>);
+            raise((const void*)twm::simt::gemv_kernel<2>);
+            raise((const void*)twm::simt::gemv_kernel<4>);
+            raise((const void*)twm::simt::gemv_kernel<8>);
+            if (r != cudaSuccess) { set_error("cudaFuncSetAttribute", r); st.status = TWM_ELAUNCH; }
+        }
+        st.ready = true;
+    }
+    if (sm_count_out) *sm_count_out = st.sm_count;
+    return st.status;
+}
+
+bool shape_ok(int M, int N, int K, int G)
+{
+    return M >= 1 && N >= 1 && K >= 32 && (G == 32 || G == 128) && (K % G) == 0 && (K % 32) == 0 &&
+           (long long)((N + twm::simt::NT - 1) / twm::simt::NT) <= (long long)(kCounterBytes / 4);
+}
+
+// Choose the number of K slices for the streaming kernel.  Costs are counted in
+// units of one 32-block of one tile (2 KB of packed weights): a CTA pays a
+// fixed start-up (barrier init, activation staging, warp reduce) worth about
+// 16 such blocks, and a split tile pays the last-arriver's pass over the
+// partials.  `slots` = CTAs that can be resident at once.
+void choose_splits(int n_tiles, int nkb, int slots, int* splits, int* bps)
+{
+    double best = 1e30;
+    int best_s = 1, best_bps = nkb;
+    const int smax = std::min(kMaxSplits, nkb);
+    for (int s = 1; s <= smax; ++s) {
+        const int b = (nkb + s - 1) / s;
+        const int s_eff = (nkb + b - 1) / b;
+        if (s_eff != s) continue;   // same slicing as a smaller s
+        const long ctas = (long)n_tiles * s_eff;
+        const long waves = (ctas + slots - 1) / slots;
+        double cost = (double)waves * (b + 16.0);
+        if (s_eff > 1) cost += 10.0 + 0.25 * s_eff;
+        if (cost < best - 1e-9) { best = cost; best_s = s_eff; best_bps = b; }
+    }
+    *splits = best_s;
+    *bps = best_bps;
+}
+
+int mmax_for(int M) { return M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : 8)); }
+
+twm_status launch_simt(const twm::GemmParams& p, int mmax, dim3 grid, bool pdl, cudaStream_t stream)
+{
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(twm::simt::THREADS, 1, 1);
+    cfg.dynamicSmemBytes = sizeof(twm::simt::Smem);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cudaError_t e;
+    switch (mmax) {
+        case 1: e = cudaLaunchKernelEx(&cfg, twm::simt::gemv_kernel<1>, p); break;
+        case 2: e = cudaLaunchKernelEx(&cfg, twm::simt::gemv_kernel<2>, p); break;
+        case 4: e = cudaLaunchKernelEx(&cfg, twm::simt::gemv_kernel<4>, p); break;
+        default: e = cudaLaunchKernelEx(&cfg, twm::simt::gemv_kernel<8>, p); break;
+    }
+    if (e != cudaSuccess) { set_error("launch gemv_kernel", e); return TWM_ELAUNCH; }
+    return TWM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int splits_override,
+                    int kernel_override, twm_plan_t* out)
+{
+    if (!out || !shape_ok(M, N, K, group_size)) return TWM_EINVAL;
+    if (splits_override < 0 || splits_override > kMaxSplits) return TWM_EINVAL;
+    if (sm_count <= 0) sm_count = kDefaultSms;
+    const int nkb = K / 32;
+    int kernel = kernel_override;
+    if (kernel == TWM_KERNEL_AUTO) kernel = TWM_KERNEL_SIMT;
+    if (kernel != TWM_KERNEL_SIMT) return TWM_EINVAL;
+    const int rows = std::min(M, 8);                       // rows one launch carries
+    const int n_tiles = (N + twm::simt::NT - 1) / twm::simt::NT;
+    const int slots = sm_count * (mmax_for(rows) <= 4 ? 2 : 1);
+    int splits, bps;
+    if (splits_override > 0) {
+        bps = (nkb + splits_override - 1) / splits_override;
+        splits = (nkb + bps - 1) / bps;
+    } else {
+        choose_splits(n_tiles, nkb, slots, &splits, &bps);
+    }
+    out->kernel = kernel;
+    out->n_tile = twm::simt::NT;
+    out->splits = splits;
+    out->blocks_per_split = bps;
+    out->grid_x = n_tiles;
+    out->grid_y = splits;
+    out->workspace_bytes = splits > 1 ? kCounterBytes + (size_t)splits * rows * N * sizeof(float) : 0;
+    return TWM_OK;
+}
+
+size_t twm_workspace_bytes(int M, int N, int K, int group_size)
+{
+    twm_plan_t pl;
+    if (twm_plan(M, N, K, group_size, kDefaultSms, 0, 0, &pl) != TWM_OK) return 0;
+    return pl.workspace_bytes;
+}
+
+twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
+{
+    if (!a) return TWM_EINVAL;
+    if (!shape_ok(a->M, a->N, a->K, a->group_size)) return TWM_EINVAL;
+    if (!a->a || !a->packed || !a->scales || !a->c) return TWM_EINVAL;
+    if ((a->a_dtype != TWM_F32 && a->a_dtype != TWM_F16) || (a->c_dtype != TWM_F32 && a->c_dtype != TWM_F16))
+        return TWM_EINVAL;
+    if (a->lda < a->K || a->ldc < a->N) return TWM_EINVAL;
+    if ((a->packed_offsets == nullptr) != (a->scales_offsets == nullptr)) return TWM_EINVAL;
+    if (a->packed_offsets && a->expert_idx < 0) return TWM_EINVAL;
+    if (reinterpret_cast<uintptr_t>(a->packed) & 15) return TWM_EALIGN;
+    if (reinterpret_cast<uintptr_t>(a->scales) & 1) return TWM_EALIGN;
+    if (reinterpret_cast<uintptr_t>(a->a) & (a->a_dtype == TWM_F16 ? 1 : 3)) return TWM_EALIGN;
+    if (reinterpret_cast<uintptr_t>(a->c) & (a->c_dtype == TWM_F16 ? 1 : 3)) return TWM_EALIGN;
+
+    int sm_count = kDefaultSms;
+    twm_status st = ensure_device(&sm_count);
+    if (st != TWM_OK) return st;
+
+    twm_plan_t pl;
+    st = twm_plan(a->M, a->N, a->K, a->group_size, sm_count, a->splits_override, a->kernel_override, &pl);
+    if (st != TWM_OK) return st;
+    if (pl.workspace_bytes > 0) {
+        if (!a->workspace || a->workspace_bytes < pl.workspace_bytes) return TWM_EWORKSPACE;
+        if (reinterpret_cast<uintptr_t>(a->workspace) & 15) return TWM_EALIGN;
+    }
+
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const size_t a_elt = a->a_dtype == TWM_F16 ? 2 : 4;
+    const size_t c_elt = a->c_dtype == TWM_F16 ? 2 : 4;
+    for (int m0 = 0; m0 < a->M; m0 += 8) {
+        const int rows = std::min(8, a->M - m0);
+        twm::GemmParams p;
+        memset(&p, 0, sizeof(p));
+        p.M = rows; p.N = a->N; p.K = a->K; p.group = a->group_size; p.nkb = a->K / 32;
+        p.a_is_f16 = a->a_dtype == TWM_F16; p.c_is_f16 = a->c_dtype == TWM_F16;
+        p.a = (const char*)a->a + (size_t)m0 * a->lda * a_elt; p.lda = a->lda;
+        p.packed = a->packed; p.scales = a->scales;
+        p.c = (char*)a->c + (size_t)m0 * a->ldc * c_elt; p.ldc = a->ldc;
+        p.ws_counters = (unsigned int*)a->workspace;
+        p.ws_partials = a->workspace ? (float*)((char*)a->workspace + kCounterBytes) : nullptr;
+        p.splits = pl.splits; p.blocks_per_split = pl.blocks_per_split;
+        p.accumulate = (a->flags & TWM_FLAG_ACCUMULATE) ? 1 : 0;
+        p.packed_offsets = a->packed_offsets; p.scales_offsets = a->scales_offsets; p.expert_idx = a->expert_idx;
+        st = launch_simt(p, mmax_for(rows), dim3(pl.grid_x, pl.grid_y, 1), (a->flags & TWM_FLAG_PDL) != 0, stream);
+        if (st != TWM_OK) return st;
+    }
+    return TWM_OK;
+}
+
+twm_status twm_dequant(const uint8_t* packed, const uint16_t* scales, void* out, int out_dtype,
+                       int K, int N, int group_size, void* stream_)
+{
+    if (!packed || !scales || !out || !shape_ok(1, N, K, group_size)) return TWM_EINVAL;
+    if (out_dtype != TWM_F32 && out_dtype != TWM_F16) return TWM_EINVAL;
+    if (reinterpret_cast<uintptr_t>(packed) & 15) return TWM_EALIGN;
+    twm_status st = ensure_device(nullptr);
+    if (st != TWM_OK) return st;
+    dim3 grid((N + 127) / 128, K / 32, 1);
+    if (grid.y > 65535) return TWM_EINVAL;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (out_dtype == TWM_F16)
+        twm::layout::dequant_kernel<__half><<<grid, 128, 0, stream>>>(packed, scales, (__half*)out, K, N, group_size);
+    else
+        twm::layout::dequant_kernel<float><<<grid, 128, 0, stream>>>(packed, scales, (float*)out, K, N, group_size);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { set_error("launch dequant_kernel", e); return TWM_ELAUNCH; }
+    return TWM_OK;
+}
+
+twm_status twm_quantize_pack(const float* w, int w_is_nk, int K, int N, int group_size,
+                             uint8_t* packed, uint16_t* scales, void* stream_)
+{
+    if (!w || !packed || !scales || !shape_ok(1, N, K, group_size)) return TWM_EINVAL;
+    if (reinterpret_cast<uintptr_t>(packed) & 15) return TWM_EALIGN;
+    twm_status st = ensure_device(nullptr);
+    if (st != TWM_OK) return st;
+    dim3 grid((N + 127) / 128, K / group_size, 1);
+    if (grid.y > 65535) return TWM_EINVAL;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (group_size == 32)
+        twm::layout::quantize_pack_kernel<32><<<grid, 128, 0, stream>>>(w, w_is_nk, K, N, packed, scales);
+    else
+        twm::layout::quantize_pack_kernel<128><<<grid, 128, 0, stream>>>(w, w_is_nk, K, N, packed, scales);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { set_error("launch quantize_pack_kernel", e); return TWM_ELAUNCH; }
+    return TWM_OK;
+}
+
+twm_status twm_fuse_n(const uint8_t* const* packed_srcs, const uint16_t* const* scales_srcs,
+                      const int* ns, int count, int K, int group_size, uint8_t* packed_dst,
+                      uint16_t* scales_dst, void* stream_)
+{
+    if (!packed_srcs || !scales_srcs || !ns || count < 1 || !packed_dst || !scales_dst) return TWM_EINVAL;
+    if (K < 32 || (group_size != 32 && group_size != 128) || K % group_size) return TWM_EINVAL;
+    long total = 0;
+    for (int i = 0; i < count; ++i) {
+        if (ns[i] < 1 || !packed_srcs[i] || !scales_srcs[i]) return TWM_EINVAL;
+        total += ns[i];
+    }
+    cudaStream_t stream = (cudaStream_t)stream_;
+    long off = 0;
+    for (int i = 0; i < count; ++i) {
+        // one strided copy per source: K/32 rows of ns[i]*16 bytes, K/G rows of ns[i]*2 bytes
+        cudaError_t e = cudaMemcpy2DAsync(packed_dst + off * 16, (size_t)total * 16, packed_srcs[i],
+                                          (size_t)ns[i] * 16, (size_t)ns[i] * 16, K / 32,
+                                          cudaMemcpyDeviceToDevice, stream);
+        if (e == cudaSuccess)
+            e = cudaMemcpy2DAsync(scales_dst + off, (size_t)total * 2, scales_srcs[i], (size_t)ns[i] * 2,
+                                  (size_t)ns[i] * 2, K / group_size, cudaMemcpyDeviceToDevice, stream);
+        if (e != cudaSuccess) { set_error("twm_fuse_n copy", e); return TWM_ELAUNCH; }
+        off += ns[i];
+    }
+    return TWM_OK;
+}
+
+twm_status twm_slice_n(const uint8_t* packed_src, const uint16_t* scales_src, int K, int N,
+                       int group_size, int n0, int n_len, uint8_t* packed_dst,
+                       uint16_t* scales_dst, void* stream_)
+{
+    if (!packed_src || !scales_src || !packed_dst || !scales_dst) return TWM_EINVAL;
+    if (K < 32 || (group_size != 32 && group_size != 128) || K % group_size) return TWM_EINVAL;
+    if (n0 < 0 || n_len < 1 || n0 + n_len > N) return TWM_EINVAL;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    cudaError_t e = cudaMemcpy2DAsync(packed_dst, (size_t)n_len * 16, packed_src + (size_t)n0 * 16,
+                                      (size_t)N * 16, (size_t)n_len * 16, K / 32,
+                                      cudaMemcpyDeviceToDevice, stream);
+    if (e == cudaSuccess)
+        e = cudaMemcpy2DAsync(scales_dst, (size_t)n_len * 2, scales_src + n0, (size_t)N * 2,
+                              (size_t)n_len * 2, K / group_size, cudaMemcpyDeviceToDevice, stream);
+    if (e != cudaSuccess) { set_error("twm_slice_n copy", e); return TWM_ELAUNCH; }
+    return TWM_OK;
+}
+
+twm_status twm_slice_k_offsets(int K, int N, int group_size, int k0, int k_len,
+                               size_t* packed_byte_offset, size_t* scales_elem_offset)
+{
+    if (!packed_byte_offset || !scales_elem_offset) return TWM_EINVAL;
+    if ((group_size != 32 && group_size != 128) || K % group_size || N < 1) return TWM_EINVAL;
+    if (k0 < 0 || k_len < group_size || k0 % group_size || k_len % group_size || k0 + k_len > K) return TWM_EINVAL;
+    *packed_byte_offset = (size_t)(k0 / 32) * N * 16;
+    *scales_elem_offset = (size_t)(k0 / group_size) * N;
+    return TWM_OK;
+}
+
+twm_status twm_device_error(void* stream_, unsigned int* word)
+{
+    if (!word) return TWM_EINVAL;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    unsigned int zero = 0;
+    cudaError_t e = cudaMemcpyFromSymbolAsync(word, twm::g_error_word, sizeof(unsigned int), 0,
+                                              cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e == cudaSuccess && *word != 0)
+        e = cudaMemcpyToSymbolAsync(twm::g_error_word, &zero, sizeof(unsigned int), 0, cudaMemcpyHostToDevice, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) { set_error("twm_device_error", e); return TWM_ELAUNCH; }
+    return *word ? TWM_ETIMEOUT : TWM_OK;
+}
+
+const char* twm_status_string(twm_status s)
+{
+    switch (s) {
+        case TWM_OK: return "ok";
+        case TWM_EINVAL: return "invalid argument (shape, dtype, group size or null pointer)";
+        case TWM_EALIGN: return "pointer alignment (packed and workspace need 16 bytes)";
+        case TWM_EWORKSPACE: return "split-K workspace missing or too small (see twm_workspace_bytes)";
+        case TWM_ELAUNCH: return "CUDA launch or copy failed (see twm_last_error)";
+        case TWM_EARCH: return "device is not sm_100 (B200)";
+        case TWM_ETIMEOUT: return "a bounded device-side wait expired";
+    }
+    return "unknown status";
+}
+
+const char* twm_last_error(void) { return t_last_error; }
+
+const char* twm_version(void) { return "twmarlin 0.1 sm_100a"; }
+
+}  // extern "C"

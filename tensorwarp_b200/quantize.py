@@ -1,0 +1,258 @@
+"""Host-side mirror of the reference's TW-Marlin interface, over the C ABI.
+
+Function names, argument order and error behaviour follow the reference's
+``warp_kernels::quantize`` module (crates/kernels/src/quantize.rs) so that a
+test written against the reference reads the same here; tensors are torch CUDA
+tensors standing in for ``GpuTensor<T>``.  torch only supplies device memory
+and the current stream: every computation is a call into ``libtwmarlin.so``.
+
+  gemm_tw_marlin_m1             quantize.rs:1301-1360
+  gemm_tw_marlin_m1_from_buffer quantize.rs:1731-1782
+  gemm_tw_marlin_m1_indirect    quantize_indirect.rs:228-253
+  fuse_tw_marlin_n              quantize.rs:1018-1063
+  quantize_f32_to_tw_marlin     quantize.rs:1171-1180
+  cpu_quantize_tw_marlin        crates/loader/src/gemma_moe_q4.rs:218-254 (here: on the device)
+  TWMarlinWeights               quantize.rs:1067-1165
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import GemmArgs, Plan, TwmError, check
+
+BLOCK_SIZE = 32  # quantize.rs:25
+
+_DTYPES = {torch.float32: _lib.TWM_F32, torch.float16: _lib.TWM_F16}
+
+
+def _stream_ptr(stream: Optional[torch.cuda.Stream]) -> int:
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return s.cuda_stream
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if not t.is_cuda:
+            raise TwmError(_lib.TWM_EINVAL, "expected a CUDA tensor (there is no CPU path)")
+
+
+def plan(m: int, n: int, k: int, group_size: int = BLOCK_SIZE, sm_count: int = 0,
+         splits_override: int = 0, kernel_override: int = 0) -> Plan:
+    """The tile / split-K decision for a shape (pure host arithmetic; replaces
+    the heuristic of quantize.rs:1314-1325)."""
+    out = Plan()
+    check(_lib.lib().twm_plan(m, n, k, group_size, sm_count, splits_override, kernel_override, C.byref(out)),
+          "twm_plan")
+    return out
+
+
+def workspace_bytes(m: int, n: int, k: int, group_size: int = BLOCK_SIZE) -> int:
+    return int(_lib.lib().twm_workspace_bytes(m, n, k, group_size))
+
+
+class Workspace:
+    """Caller-owned split-K scratch.  Zeroed once here; the kernels hand its
+    counters back at zero, so it is reusable launch after launch on one stream."""
+
+    def __init__(self, nbytes: int, device: torch.device | str = "cuda"):
+        self.nbytes = max(int(nbytes), 16)
+        self.buf = torch.zeros(self.nbytes, dtype=torch.uint8, device=device)
+
+    @classmethod
+    def for_shapes(cls, shapes: Sequence[Tuple[int, int, int, int]], device="cuda") -> "Workspace":
+        """shapes: (M, N, K, group_size) of every GEMM that will share it."""
+        return cls(max([workspace_bytes(*s) for s in shapes] + [16]), device)
+
+    @property
+    def ptr(self) -> int:
+        return self.buf.data_ptr()
+
+
+def gemm_tw_marlin(a: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, c: torch.Tensor,
+                   m: int, n: int, k: int, *, group_size: int = BLOCK_SIZE,
+                   workspace: Optional[Workspace] = None, stream: Optional[torch.cuda.Stream] = None,
+                   flags: int = 0, splits_override: int = 0, kernel_override: int = 0,
+                   packed_offsets: Optional[torch.Tensor] = None,
+                   scales_offsets: Optional[torch.Tensor] = None, expert_idx: int = 0) -> None:
+    """C[m,n] = A[m,k] x dequant(packed, scales); A and C are f32 or f16, row-major.
+
+    The M > 1 form of ``gemm_tw_marlin_m1``; enqueue only, like the reference."""
+    _require_cuda(a, packed, scales, c)
+    if a.dtype not in _DTYPES or c.dtype not in _DTYPES:
+        raise TwmError(_lib.TWM_EINVAL, "gemm_tw_marlin: A and C must be float32 or float16")
+    if packed.dtype != torch.uint8 or scales.dtype not in (torch.float16, torch.uint16, torch.int16):
+        raise TwmError(_lib.TWM_EINVAL, "gemm_tw_marlin: packed must be uint8 and scales float16")
+    if a.numel() < m * k or c.numel() < m * n:
+        raise TwmError(_lib.TWM_EINVAL, "gemm_tw_marlin: A or C smaller than the stated shape")
+    if packed_offsets is None:
+        if packed.numel() < (k // 32) * n * 16 or scales.numel() < (k // group_size) * n:
+            raise TwmError(_lib.TWM_EINVAL, "gemm_tw_marlin: packed or scales smaller than the stated shape")
+    lda = a.stride(0) if a.dim() == 2 else k
+    ldc = c.stride(0) if c.dim() == 2 else n
+    args = GemmArgs(
+        M=m, N=n, K=k, group_size=group_size,
+        a_dtype=_DTYPES[a.dtype], c_dtype=_DTYPES[c.dtype],
+        a=a.data_ptr(), lda=lda, packed=packed.data_ptr(), scales=scales.data_ptr(),
+        c=c.data_ptr(), ldc=ldc,
+        workspace=workspace.ptr if workspace is not None else None,
+        workspace_bytes=workspace.nbytes if workspace is not None else 0,
+        splits_override=splits_override, kernel_override=kernel_override, flags=flags,
+        packed_offsets=packed_offsets.data_ptr() if packed_offsets is not None else None,
+        scales_offsets=scales_offsets.data_ptr() if scales_offsets is not None else None,
+        expert_idx=expert_idx,
+    )
+    check(_lib.lib().twm_gemm_w4a16(C.byref(args), _stream_ptr(stream)), "twm_gemm_w4a16")
+
+
+def gemm_tw_marlin_m1(a: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, c: torch.Tensor,
+                      n: int, k: int, **kw) -> None:
+    """Drop-in for ``gemm_tw_marlin_m1(cache, device, a, packed, scales, c, n, k)``
+    (quantize.rs:1301-1310).  The kernel cache and device arguments have no
+    counterpart: kernels are compiled ahead of time and the device is the
+    tensors' device."""
+    if k % BLOCK_SIZE != 0:
+        raise TwmError(_lib.TWM_EINVAL, "gemm_tw_marlin_m1: k % 32 != 0")   # the reference asserts (quantize.rs:1311)
+    gemm_tw_marlin(a, packed, scales, c, 1, n, k, **kw)
+
+
+def gemm_tw_marlin_m1_from_buffer(a, packed_buf: torch.Tensor, packed_offset: int, scales_buf: torch.Tensor,
+                                  scales_offset: int, c, n: int, k: int, **kw) -> None:
+    """``gemm_tw_marlin_m1`` on a sub-range of two big buffers (quantize.rs:1731-1741):
+    packed_offset in bytes, scales_offset in elements, both applied on the host."""
+    g = kw.get("group_size", BLOCK_SIZE)
+    pv = packed_buf.view(-1)[packed_offset:packed_offset + (k // 32) * n * 16]
+    sv = scales_buf.view(-1)[scales_offset:scales_offset + (k // g) * n]
+    gemm_tw_marlin_m1(a, pv, sv, c, n, k, **kw)
+
+
+def gemm_tw_marlin_m1_indirect(a, packed_buf, packed_offsets: torch.Tensor, scales_buf,
+                               scales_offsets: torch.Tensor, expert_idx: int, c, n: int, k: int, **kw) -> None:
+    """Expert-indexed form (quantize_indirect.rs:228-237): the kernel itself reads
+    ``packed_offsets[expert_idx]`` (bytes) and ``scales_offsets[expert_idx]`` (elements)."""
+    gemm_tw_marlin(a, packed_buf, scales_buf, c, 1, n, k, packed_offsets=packed_offsets,
+                   scales_offsets=scales_offsets, expert_idx=expert_idx, **kw)
+
+
+def quantize_f32_to_tw_marlin(weights: torch.Tensor, k: int, n: int, group_size: int = BLOCK_SIZE,
+                              *, w_is_nk: bool = False, stream=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """F32 weights -> (packed u8 [k/32, n, 16], scales f16 [k/group, n]).
+
+    ``weights`` is [K,N] row-major as for the reference's function of this name
+    (quantize.rs:1171-1177), or [N,K] with ``w_is_nk`` as ``cpu_quantize_tw_marlin``
+    takes it (gemma_moe_q4.rs:214)."""
+    _require_cuda(weights)
+    if weights.dtype != torch.float32 or weights.numel() != k * n or not weights.is_contiguous():
+        raise TwmError(_lib.TWM_EINVAL, "quantize_f32_to_tw_marlin: need contiguous float32 of k*n elements")
+    packed = torch.empty((k // 32, n, 16), dtype=torch.uint8, device=weights.device)
+    scales = torch.empty((k // group_size, n), dtype=torch.float16, device=weights.device)
+    check(_lib.lib().twm_quantize_pack(weights.data_ptr(), int(w_is_nk), k, n, group_size, packed.data_ptr(),
+                                       scales.data_ptr(), _stream_ptr(stream)), "twm_quantize_pack")
+    return packed, scales
+
+
+def cpu_quantize_tw_marlin(data_nk: torch.Tensor, k: int, n: int, group_size: int = BLOCK_SIZE):
+    """Same tensors as the reference's CPU quantiser of this name
+    (gemma_moe_q4.rs:218-254), produced on the device from [N,K] input."""
+    return quantize_f32_to_tw_marlin(data_nk, k, n, group_size, w_is_nk=True)
+
+
+def dequant_tw_marlin(packed: torch.Tensor, scales: torch.Tensor, k: int, n: int,
+                      group_size: int = BLOCK_SIZE, dtype: torch.dtype = torch.float32, *, stream=None) -> torch.Tensor:
+    """Dense [K,N] matrix w = f32(scale) * (nibble - 8); f32 is exact, f16 rounds
+    to nearest even (dequant_q4_to_f16, quantize.rs:580-618)."""
+    _require_cuda(packed, scales)
+    out = torch.empty((k, n), dtype=dtype, device=packed.device)
+    check(_lib.lib().twm_dequant(packed.data_ptr(), scales.data_ptr(), out.data_ptr(), _DTYPES[dtype], k, n,
+                                 group_size, _stream_ptr(stream)), "twm_dequant")
+    return out
+
+
+def fuse_tw_marlin_n(matrices: Sequence[Tuple[torch.Tensor, torch.Tensor]], k: int, ns: Sequence[int],
+                     group_size: int = BLOCK_SIZE, *, stream=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Concatenate along N, block row by block row (quantize.rs:1018-1063), on
+    the device instead of through the host."""
+    cnt = len(matrices)
+    if cnt == 0 or cnt != len(ns):
+        raise TwmError(_lib.TWM_EINVAL, "fuse_tw_marlin_n: matrices and ns differ in length")
+    for (p, s), n_i in zip(matrices, ns):
+        _require_cuda(p, s)
+        if p.numel() != (k // 32) * n_i * 16 or s.numel() != (k // group_size) * n_i:
+            raise TwmError(_lib.TWM_EINVAL, "fuse_tw_marlin_n: a matrix does not match k and its n")
+    total = int(sum(ns))
+    dev = matrices[0][0].device
+    packed = torch.empty((k // 32, total, 16), dtype=torch.uint8, device=dev)
+    scales = torch.empty((k // group_size, total), dtype=torch.float16, device=dev)
+    pp = (C.c_void_p * cnt)(*[p.data_ptr() for p, _ in matrices])
+    sp = (C.c_void_p * cnt)(*[s.data_ptr() for _, s in matrices])
+    nn = (C.c_int * cnt)(*[int(x) for x in ns])
+    check(_lib.lib().twm_fuse_n(pp, sp, nn, cnt, k, group_size, packed.data_ptr(), scales.data_ptr(),
+                                _stream_ptr(stream)), "twm_fuse_n")
+    return packed, scales
+
+
+def slice_tw_marlin_n(packed: torch.Tensor, scales: torch.Tensor, k: int, n: int, n0: int, n_len: int,
+                      group_size: int = BLOCK_SIZE, *, stream=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Columns [n0, n0+n_len) as their own TW-Marlin matrix (column shard)."""
+    _require_cuda(packed, scales)
+    p = torch.empty((k // 32, n_len, 16), dtype=torch.uint8, device=packed.device)
+    s = torch.empty((k // group_size, n_len), dtype=torch.float16, device=packed.device)
+    check(_lib.lib().twm_slice_n(packed.data_ptr(), scales.data_ptr(), k, n, group_size, n0, n_len, p.data_ptr(),
+                                 s.data_ptr(), _stream_ptr(stream)), "twm_slice_n")
+    return p, s
+
+
+def slice_tw_marlin_k(packed: torch.Tensor, scales: torch.Tensor, k: int, n: int, k0: int, k_len: int,
+                      group_size: int = BLOCK_SIZE) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Rows [k0, k0+k_len) (row shard): contiguous, so these are views."""
+    po, so = C.c_size_t(), C.c_size_t()
+    check(_lib.lib().twm_slice_k_offsets(k, n, group_size, k0, k_len, C.byref(po), C.byref(so)),
+          "twm_slice_k_offsets")
+    p = packed.view(-1)[po.value:po.value + (k_len // 32) * n * 16].view(k_len // 32, n, 16)
+    s = scales.view(-1)[so.value:so.value + (k_len // group_size) * n].view(k_len // group_size, n)
+    return p, s
+
+
+def device_error(stream=None) -> int:
+    """Read and clear the device-side error word (synchronises the stream)."""
+    w = C.c_uint(0)
+    st = _lib.lib().twm_device_error(_stream_ptr(stream), C.byref(w))
+    if st not in (_lib.TWM_OK, _lib.TWM_ETIMEOUT):
+        check(st, "twm_device_error")
+    return int(w.value)
+
+
+@dataclass
+class TWMarlinWeights:
+    """One transformer layer in TW-Marlin form (quantize.rs:1067-1086): norms,
+    seven projections as (packed, scales), optional q/k/v bias, optional fused
+    QKV and gate+up."""
+    hidden: int
+    kv_dim: int
+    ffn: int
+    group_size: int
+    attn_norm: torch.Tensor
+    ffn_norm: torch.Tensor
+    wq: Tuple[torch.Tensor, torch.Tensor]
+    wk: Tuple[torch.Tensor, torch.Tensor]
+    wv: Tuple[torch.Tensor, torch.Tensor]
+    wo: Tuple[torch.Tensor, torch.Tensor]
+    w_gate: Tuple[torch.Tensor, torch.Tensor]
+    w_up: Tuple[torch.Tensor, torch.Tensor]
+    w_down: Tuple[torch.Tensor, torch.Tensor]
+    bq: Optional[torch.Tensor] = None
+    bk: Optional[torch.Tensor] = None
+    bv: Optional[torch.Tensor] = None
+    wqkv: Optional[Tuple[torch.Tensor, torch.Tensor]] = field(default=None)
+    wgu: Optional[Tuple[torch.Tensor, torch.Tensor]] = field(default=None)
+
+    def fuse_projections(self) -> None:
+        """Build the fused QKV and gate+up matrices (quantize.rs:1138-1165)."""
+        g = self.group_size
+        self.wqkv = fuse_tw_marlin_n([self.wq, self.wk, self.wv], self.hidden,
+                                     [self.hidden, self.kv_dim, self.kv_dim], g)
+        self.wgu = fuse_tw_marlin_n([self.w_gate, self.w_up], self.hidden, [self.ffn, self.ffn], g)

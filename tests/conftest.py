@@ -1,0 +1,20 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a B200 (run with -m gpu)")
+
+
+@pytest.fixture(scope="session")
+def twm_lib():
+    """libtwmarlin.so, built on demand (nvcc cross-compiles without a GPU)."""
+    from tensorwarp_b200 import _lib, build
+    build()
+    return _lib.lib()

@@ -1,0 +1,298 @@
+"""GPU parity tests, through the C ABI: the sm_100a kernels against the CPU oracle and
+against the reference's own CUDA kernels (compiled unchanged into oracle/_ref)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from oracle import ref as oref
+from helpers import raw_rel_violations, rel_err_floored, seeded_activations, seeded_weights
+from tensorwarp_b200 import _lib
+from tensorwarp_b200 import quantize as q
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+# north-star tolerance: max relative error per output element, FP16 output
+TOL_F16 = 1e-2
+# f32 output: only summation order differs from the oracle
+TOL_F32 = 2e-4
+
+
+def _to_dev(x, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(x)).to(DEV)
+    return t if dtype is None else t.to(dtype)
+
+
+def _quantised(k, n, group, seed):
+    w = seeded_weights(k, n, seed)
+    packed, scales = oracle.quantize_pack(w, k, n, group)
+    return w, packed, scales
+
+
+def _run_gemm(a_np, packed, scales, m, n, k, group, a_dtype, c_dtype, ws=None, **kw):
+    a = _to_dev(a_np, a_dtype)
+    c = torch.full((m, n), float("nan"), dtype=c_dtype, device=DEV)     # poison: every element must be written
+    p = _to_dev(packed)
+    s = _to_dev(scales.view(np.float16))
+    if ws is None:
+        ws = q.Workspace(max(q.workspace_bytes(m, n, k, group), 16) + 64 * m * n * 4 + 16384)
+    q.gemm_tw_marlin(a, p, s, c, m, n, k, group_size=group, workspace=ws, **kw)
+    torch.cuda.synchronize()
+    assert q.device_error() == 0
+    # the kernels hand the tile counters back at zero
+    assert int(ws.buf[:16384].view(torch.int32).abs().sum().item()) == 0
+    return c.float().cpu().numpy()
+
+
+# ---------------------------------------------------------------- layout --
+
+@pytest.mark.parametrize("group", [32, 128])
+@pytest.mark.parametrize("k,n", [(128, 1), (128, 33), (256, 257), (896, 9728), (3584, 512)])
+def test_quantize_pack_bit_exact(k, n, group):
+    w = seeded_weights(k, n, 11)
+    w[: group, 0] = 0.0                        # an all-zero group
+    p_ref, s_ref = oracle.quantize_pack(w, k, n, group)
+    p, s = q.quantize_f32_to_tw_marlin(_to_dev(w), k, n, group)
+    assert np.array_equal(p.cpu().numpy(), p_ref)
+    assert np.array_equal(s.cpu().numpy().view(np.uint16), s_ref)
+    p2, s2 = q.cpu_quantize_tw_marlin(_to_dev(np.ascontiguousarray(w.T)), k, n, group)      # [N,K] input
+    assert np.array_equal(p2.cpu().numpy(), p_ref)
+    assert np.array_equal(s2.cpu().numpy().view(np.uint16), s_ref)
+
+
+def test_oracle_quantiser_equals_reference_kernel():
+    """The reference's warp_quantize_q4_0 (quantize.rs:103-146) on the columns of a matrix
+    gives the same nibbles, and an f32 scale whose f16 rounding is the oracle's scale."""
+    if not oref.available():
+        pytest.skip("oracle/_ref not built")
+    k, n = 512, 96
+    w = seeded_weights(k, n, 13)
+    cols = np.ascontiguousarray(w.T).reshape(-1)                     # column after column = [N,K]
+    x = _to_dev(cols)
+    out = torch.zeros(cols.size // 32 * 20, dtype=torch.uint8, device=DEV)
+    oref.quantize_q4_0(out.data_ptr(), x.data_ptr(), cols.size)
+    torch.cuda.synchronize()
+    blocks = out.cpu().numpy().reshape(n, k // 32, 20)
+    p_ref, s_ref = oracle.quantize_pack(w, k, n, 32)
+    assert np.array_equal(blocks[:, :, 4:], np.transpose(p_ref, (1, 0, 2)))
+    scale32 = blocks[:, :, :4].copy().view(np.float32).reshape(n, k // 32)
+    assert np.array_equal(oracle.f32_to_f16_bits(scale32), s_ref.T)
+    # and the reference's dequantise kernel on those blocks equals the oracle's f32-scale round trip
+    back = torch.zeros(cols.size, dtype=torch.float32, device=DEV)
+    oref.dequantize_q4_0(back.data_ptr(), out.data_ptr(), cols.size)
+    torch.cuda.synchronize()
+    assert np.array_equal(back.cpu().numpy(), oracle.q4_0_roundtrip(cols))
+
+
+@pytest.mark.parametrize("group", [32, 128])
+@pytest.mark.parametrize("k,n", [(128, 1), (256, 31), (384, 257), (3584, 640)])
+def test_dequant_bit_exact(k, n, group):
+    _, packed, scales = _quantised(k, n, group, 17)
+    p, s = _to_dev(packed), _to_dev(scales.view(np.float16))
+    d32 = q.dequant_tw_marlin(p, s, k, n, group, torch.float32).cpu().numpy()
+    assert np.array_equal(d32.view(np.uint32), oracle.dequant_f32(packed, scales, k, n, group).view(np.uint32))
+    d16 = q.dequant_tw_marlin(p, s, k, n, group, torch.float16).cpu().numpy()
+    assert np.array_equal(d16.view(np.uint16), oracle.dequant_f16_bits(packed, scales, k, n, group))
+
+
+def test_dequant_all_nibbles_and_odd_scales():
+    """Every nibble value 0..15 against negative, subnormal and large scales: the decode is
+    exact whatever produced the tensors."""
+    k, n = 32, 16
+    packed = np.zeros((1, n, 16), dtype=np.uint8)
+    for col in range(n):
+        packed[0, col, :] = [(col + i) % 16 | (((col + i + 5) % 16) << 4) for i in range(16)]
+    scales = np.array([[0x3C00, 0xBC00, 0x0001, 0x03FF, 0x7BFF, 0x0000, 0x8000, 0x1234,
+                        0x5555, 0x3555, 0x2E66, 0x4900, 0x0400, 0x8400, 0x6000, 0x3800]], dtype=np.uint16)
+    p, s = _to_dev(packed), _to_dev(scales.view(np.float16))
+    d32 = q.dequant_tw_marlin(p, s, k, n, 32, torch.float32).cpu().numpy()
+    assert np.array_equal(d32.view(np.uint32), oracle.dequant_f32(packed, scales, k, n, 32).view(np.uint32))
+
+
+@pytest.mark.parametrize("group", [32, 128])
+def test_fuse_and_slice(group):
+    k, ns = 256, [40, 8, 8]
+    mats = [oracle.quantize_pack(seeded_weights(k, n_i, 30 + i), k, n_i, group) for i, n_i in enumerate(ns)]
+    fp_ref, fs_ref = oracle.fuse_n(mats, k, group)
+    dev = [(_to_dev(p), _to_dev(s.view(np.float16))) for p, s in mats]
+    fp, fs = q.fuse_tw_marlin_n(dev, k, ns, group)
+    assert np.array_equal(fp.cpu().numpy(), fp_ref)
+    assert np.array_equal(fs.cpu().numpy().view(np.uint16), fs_ref)
+    # slicing is the inverse of fusing
+    off = 0
+    for (p, s), n_i in zip(mats, ns):
+        sp, ss = q.slice_tw_marlin_n(fp, fs, k, sum(ns), off, n_i, group)
+        assert np.array_equal(sp.cpu().numpy(), p) and np.array_equal(ss.cpu().numpy().view(np.uint16), s)
+        off += n_i
+    # a K slice is a contiguous run of block rows
+    kp, ks = q.slice_tw_marlin_k(fp, fs, k, sum(ns), 128, 128, group)
+    assert np.array_equal(kp.cpu().numpy(), fp_ref[4:8])
+    assert np.array_equal(ks.cpu().numpy().view(np.uint16), fs_ref[128 // group: 256 // group])
+
+
+# ------------------------------------------------------------------ GEMM --
+
+SMALL_SHAPES = [(32, 1), (32, 31), (128, 33), (160, 128), (256, 257), (512, 129), (1024, 1000), (2560, 136)]
+
+
+@pytest.mark.parametrize("k,n", SMALL_SHAPES)
+@pytest.mark.parametrize("splits", [0, 1, 2, 3, 7])
+def test_m1_f32_reference_mode(k, n, splits):
+    """f32 in / f32 out, G=32: the reference's own signature (quantize.rs:1301-1310)."""
+    _, packed, scales = _quantised(k, n, 32, 41)
+    a = seeded_activations(1, k, 0)
+    y = _run_gemm(a, packed, scales, 1, n, k, 32, torch.float32, torch.float32, splits_override=splits)
+    ref64 = oracle.w4a16_f64(a, packed, scales, 1, n, k, 32)
+    assert rel_err_floored(y, ref64) < TOL_F32
+    ko = oracle.m1_kernel_order(a[0], packed, scales, n, k, 32)
+    assert np.max(np.abs(y[0] - ko)) <= 1e-5 * max(1.0, float(np.max(np.abs(ko))))
+
+
+@pytest.mark.parametrize("group", [32, 128])
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 8])
+@pytest.mark.parametrize("k,n", [(128, 33), (384, 257), (1024, 512), (3584, 264)])
+def test_small_m_f16(m, k, n, group):
+    if k % group:
+        pytest.skip("K not a multiple of the group")
+    _, packed, scales = _quantised(k, n, group, 43)
+    a = seeded_activations(m, k, 0)
+    y = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float16)
+    ref64 = oracle.w4a16_f64(a, packed, scales, m, n, k, group)
+    assert rel_err_floored(y, ref64) < TOL_F16
+    # and bit-identical to rounding the f32-output run to f16 (one rounding, at the end)
+    y32 = _run_gemm(a, packed, scales, m, n, k, group, torch.float32, torch.float32)
+    assert np.array_equal(y32.astype(np.float16).astype(np.float32), y)
+
+
+@pytest.mark.parametrize("m", [9, 16, 19])
+def test_m_beyond_eight(m):
+    k, n, group = 512, 200, 128
+    _, packed, scales = _quantised(k, n, group, 47)
+    a = seeded_activations(m, k, 0)
+    y = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float16)
+    assert rel_err_floored(y, oracle.w4a16_f64(a, packed, scales, m, n, k, group)) < TOL_F16
+
+
+def test_config0_shape_vs_literal_cpu_path():
+    """configs[0]: M=1, K=896, N=9728, G=128, FP16 in/out, against the reference's CPU route
+    restated literally (dequantise the matrix, naive matmul, FP32 accumulate)."""
+    k, n, group = 896, 9728, 128
+    _, packed, scales = _quantised(k, n, group, 0)
+    a = seeded_activations(1, k, 0)
+    y = _run_gemm(a, packed, scales, 1, n, k, group, torch.float16, torch.float16)
+    lit = oracle.w4a16_literal(a, packed, scales, 1, n, k, group)
+    ref64 = oracle.w4a16_f64(a, packed, scales, 1, n, k, group)
+    assert rel_err_floored(y, ref64) < TOL_F16
+    assert rel_err_floored(lit, ref64) < TOL_F16
+    bad, worst = raw_rel_violations(y, ref64, TOL_F16)
+    rms = float(np.sqrt(np.mean(ref64 ** 2)))
+    # raw (unfloored) criterion: any violator must be a near-zero output
+    assert bad == 0 or worst < rms * 2.0 ** -5, (bad, worst, rms)
+
+
+@pytest.mark.parametrize("k,n", [(3584, 4608), (3584, 3584), (3584, 37888), (18944, 3584)])
+def test_config1_shapes(k, n):
+    """configs[1]: the four Qwen2-7B decode GEMMs at full size, M=1, G=128, FP16."""
+    group = 128
+    w = torch.randn((k, n), generator=torch.Generator(device=DEV).manual_seed(1000 + n % 7), device=DEV) * 0.02
+    p, s = q.quantize_f32_to_tw_marlin(w, k, n, group)
+    torch.cuda.synchronize()
+    packed, scales = p.cpu().numpy(), s.cpu().numpy().view(np.uint16)
+    a = seeded_activations(1, k, 0)
+    y = _run_gemm(a, packed, scales, 1, n, k, group, torch.float16, torch.float16, flags=_lib.TWM_FLAG_PDL)
+    ref64 = oracle.w4a16_f64(a, packed, scales, 1, n, k, group)
+    assert rel_err_floored(y, ref64) < TOL_F16
+    # size-independent property: linearity in the activations, C(2a) = 2 C(a) exactly (power of two)
+    y2 = _run_gemm(2.0 * a, packed, scales, 1, n, k, group, torch.float16, torch.float16)
+    normal = (np.abs(y) < 30000) & (np.abs(y) > 1e-3)      # away from f16 overflow and subnormals
+    assert np.array_equal(y2[normal], 2.0 * y[normal])
+
+
+def test_against_reference_cuda_kernel():
+    """The reference's warp_gemm_tw_marlin_m1(_direct) run on this GPU: the oracle's
+    kernel-order restatement reproduces the direct kernel bit for bit, the split-K kernel
+    (FP32 atomics, any order) within summation error, and the sm_100a kernel agrees with both."""
+    if not oref.available():
+        pytest.skip("oracle/_ref not built")
+    for (k, n, group) in [(896, 9728, 32), (3584, 4608, 128), (3584, 3584, 32), (2048, 300, 32)]:
+        _, packed, scales = _quantised(k, n, group, 51)
+        a = seeded_activations(1, k, 0)
+        s32 = scales if group == 32 else np.repeat(scales, 4, axis=0)      # G=128 shown to a G=32 kernel
+        ad, pd, sd = _to_dev(a), _to_dev(packed), _to_dev(np.ascontiguousarray(s32).view(np.float16))
+        c_direct = torch.zeros(n, dtype=torch.float32, device=DEV)
+        assert oref.gemm_tw_marlin_m1(c_direct.data_ptr(), ad.data_ptr(), pd.data_ptr(), sd.data_ptr(), n, k,
+                                      force_splits=1) == 1
+        c_auto = torch.zeros(n, dtype=torch.float32, device=DEV)
+        used = oref.gemm_tw_marlin_m1(c_auto.data_ptr(), ad.data_ptr(), pd.data_ptr(), sd.data_ptr(), n, k)
+        torch.cuda.synchronize()
+        assert used == oracle.splitk_plan_ref(n, k)[1]
+        ko = oracle.m1_kernel_order(a[0], packed, np.ascontiguousarray(s32), n, k, 32)
+        assert np.array_equal(c_direct.cpu().numpy().view(np.uint32), ko.view(np.uint32))
+        ref64 = oracle.w4a16_f64(a, packed, scales, 1, n, k, group)
+        assert rel_err_floored(c_auto.cpu().numpy()[None], ref64) < TOL_F32
+        y = _run_gemm(a, packed, scales, 1, n, k, group, torch.float32, torch.float32)
+        assert rel_err_floored(y, c_direct.cpu().numpy()[None].astype(np.float64)) < TOL_F32
+        y16 = _run_gemm(a, packed, scales, 1, n, k, group, torch.float16, torch.float16)
+        assert rel_err_floored(y16, c_direct.cpu().numpy()[None].astype(np.float64)) < TOL_F16
+
+
+def test_deterministic_and_split_invariant():
+    """Two runs are bit-identical (the reference's split-K is not: FP32 atomics), and the
+    result does not depend on which slice arrives last."""
+    k, n, group = 3584, 4608, 128
+    _, packed, scales = _quantised(k, n, group, 53)
+    a = seeded_activations(1, k, 0)
+    runs = [_run_gemm(a, packed, scales, 1, n, k, group, torch.float16, torch.float32) for _ in range(3)]
+    assert np.array_equal(runs[0], runs[1]) and np.array_equal(runs[0], runs[2])
+
+
+def test_indirect_and_from_buffer():
+    """Expert-indexed weights (quantize_indirect.rs:185-253) and host offsets (quantize.rs:1731-1782)."""
+    k, n, group, experts = 256, 136, 32, 3
+    mats = [_quantised(k, n, group, 60 + e)[1:] for e in range(experts)]
+    pbuf = np.concatenate([p.reshape(-1) for p, _ in mats])
+    sbuf = np.concatenate([s.reshape(-1) for _, s in mats])
+    poff = np.array([e * (k // 32) * n * 16 for e in range(experts)], dtype=np.uint32)
+    soff = np.array([e * (k // group) * n for e in range(experts)], dtype=np.uint32)
+    a = seeded_activations(1, k, 0)
+    ad, pd, sd = _to_dev(a, torch.float32), _to_dev(pbuf), _to_dev(sbuf.view(np.float16))
+    po, so = _to_dev(poff.view(np.int32)), _to_dev(soff.view(np.int32))
+    for e in range(experts):
+        ref64 = oracle.w4a16_f64(a, mats[e][0], mats[e][1], 1, n, k, group)
+        c = torch.full((n,), float("nan"), dtype=torch.float32, device=DEV)
+        q.gemm_tw_marlin_m1_indirect(ad, pd, po, sd, so, e, c, n, k, flags=_lib.TWM_FLAG_PDL)
+        c2 = torch.full((n,), float("nan"), dtype=torch.float32, device=DEV)
+        q.gemm_tw_marlin_m1_from_buffer(ad, pd, int(poff[e]), sd, int(soff[e]), c2, n, k)
+        torch.cuda.synchronize()
+        assert rel_err_floored(c.cpu().numpy()[None], ref64) < TOL_F32
+        assert np.array_equal(c.cpu().numpy(), c2.cpu().numpy())
+
+
+def test_accumulate_flag_and_strides():
+    k, n, m, group = 256, 200, 2, 32
+    _, packed, scales = _quantised(k, n, group, 70)
+    a = seeded_activations(m, k, 0)
+    a_wide = torch.zeros((m, k + 64), dtype=torch.float16, device=DEV)
+    a_wide[:, :k] = _to_dev(a, torch.float16)
+    c_wide = torch.ones((m, n + 8), dtype=torch.float32, device=DEV)
+    q.gemm_tw_marlin(a_wide[:, :k], _to_dev(packed), _to_dev(scales.view(np.float16)), c_wide[:, :n], m, n, k,
+                     group_size=group, flags=_lib.TWM_FLAG_ACCUMULATE)
+    torch.cuda.synchronize()
+    ref64 = oracle.w4a16_f64(a, packed, scales, m, n, k, group) + 1.0
+    assert rel_err_floored(c_wide[:, :n].cpu().numpy(), ref64) < TOL_F32
+    assert torch.all(c_wide[:, n:] == 1.0)        # the padding columns are not touched
+
+
+def test_errors_are_statuses():
+    k, n = 3584, 3584
+    a = torch.zeros(k, dtype=torch.float16, device=DEV)
+    p = torch.zeros((k // 32, n, 16), dtype=torch.uint8, device=DEV)
+    s = torch.zeros((k // 128, n), dtype=torch.float16, device=DEV)
+    c = torch.zeros(n, dtype=torch.float16, device=DEV)
+    with pytest.raises(_lib.TwmError) as e:
+        q.gemm_tw_marlin_m1(a, p, s, c, n, k, group_size=128, workspace=None)     # this shape splits
+    assert e.value.status == _lib.TWM_EWORKSPACE
+    with pytest.raises(_lib.TwmError) as e:
+        q.gemm_tw_marlin_m1(a, p, s, c, n, k - 16, group_size=128)
+    assert e.value.status == _lib.TWM_EINVAL
