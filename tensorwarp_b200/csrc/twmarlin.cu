@@ -14,6 +14,7 @@
 
 #include "twm_common.cuh"
 #include "twm_gemv_simt.cuh"
+#include "twm_gemm_tc.cuh"
 #include "twm_layout.cuh"
 
 namespace {
@@ -66,6 +67,15 @@ twm_status ensure_device(int* sm_count_out)
             raise((const void*)twm::simt::gemv_kernel<2>);
             raise((const void*)twm::simt::gemv_kernel<4>);
             raise((const void*)twm::simt::gemv_kernel<8>);
+            auto raise_tc = [&](const void* fn) {
+                if (r == cudaSuccess)
+                    r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(twm::tc::Smem));
+            };
+            raise_tc((const void*)twm::tc::gemm_kernel<16, 1>);
+            raise_tc((const void*)twm::tc::gemm_kernel<16, 2>);
+            raise_tc((const void*)twm::tc::gemm_kernel<16, 4>);
+            raise_tc((const void*)twm::tc::gemm_kernel<16, 8>);
+            raise_tc((const void*)twm::tc::gemm_kernel<16, 16>);
             if (r != cudaSuccess) { set_error("cudaFuncSetAttribute", r); st.status = TWM_ELAUNCH; }
         }
         st.ready = true;
@@ -85,13 +95,14 @@ bool shape_ok(int M, int N, int K, int G)
 // fixed start-up (barrier init, activation staging, warp reduce) worth about
 // 16 such blocks, and a split tile pays the last-arriver's pass over the
 // partials.  `slots` = CTAs that can be resident at once.
-void choose_splits(int n_tiles, int nkb, int slots, int* splits, int* bps)
+void choose_splits(int n_tiles, int nkb, int slots, int max_bps, int* splits, int* bps)
 {
     double best = 1e30;
     int best_s = 1, best_bps = nkb;
     const int smax = std::min(kMaxSplits, nkb);
     for (int s = 1; s <= smax; ++s) {
         const int b = (nkb + s - 1) / s;
+        if (b > max_bps && s < smax) continue;   // the kernel's per-slice staging capacity
         const int s_eff = (nkb + b - 1) / b;
         if (s_eff != s) continue;   // same slicing as a smaller s
         const long ctas = (long)n_tiles * s_eff;
@@ -105,6 +116,32 @@ void choose_splits(int n_tiles, int nkb, int slots, int* splits, int* bps)
 }
 
 int mmax_for(int M) { return M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : 8)); }
+int mv_for(int M) { return M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : (M <= 8 ? 8 : 16))); }
+
+twm_status launch_tc(const twm::GemmParams& p, int mv, dim3 grid, bool pdl, cudaStream_t stream)
+{
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(twm::tc::THREADS, 1, 1);
+    cfg.dynamicSmemBytes = sizeof(twm::tc::Smem);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cudaError_t e;
+    switch (mv) {
+        case 1: e = cudaLaunchKernelEx(&cfg, twm::tc::gemm_kernel<16, 1>, p); break;
+        case 2: e = cudaLaunchKernelEx(&cfg, twm::tc::gemm_kernel<16, 2>, p); break;
+        case 4: e = cudaLaunchKernelEx(&cfg, twm::tc::gemm_kernel<16, 4>, p); break;
+        case 8: e = cudaLaunchKernelEx(&cfg, twm::tc::gemm_kernel<16, 8>, p); break;
+        default: e = cudaLaunchKernelEx(&cfg, twm::tc::gemm_kernel<16, 16>, p); break;
+    }
+    if (e != cudaSuccess) { set_error("launch tc::gemm_kernel", e); return TWM_ELAUNCH; }
+    return TWM_OK;
+}
 
 twm_status launch_simt(const twm::GemmParams& p, int mmax, dim3 grid, bool pdl, cudaStream_t stream)
 {
@@ -142,17 +179,21 @@ twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int split
     if (sm_count <= 0) sm_count = kDefaultSms;
     const int nkb = K / 32;
     int kernel = kernel_override;
-    if (kernel == TWM_KERNEL_AUTO) kernel = TWM_KERNEL_SIMT;
-    if (kernel != TWM_KERNEL_SIMT) return TWM_EINVAL;
-    const int rows = std::min(M, 8);                       // rows one launch carries
+    if (kernel == TWM_KERNEL_AUTO) kernel = TWM_KERNEL_TC;
+    if (kernel != TWM_KERNEL_SIMT && kernel != TWM_KERNEL_TC) return TWM_EINVAL;
+    // rows one launch carries; more rows are served by further launches
+    const int rows = std::min(M, kernel == TWM_KERNEL_TC ? 16 : 8);
     const int n_tiles = (N + twm::simt::NT - 1) / twm::simt::NT;
-    const int slots = sm_count * (mmax_for(rows) <= 4 ? 2 : 1);
+    const int slots = sm_count * ((kernel == TWM_KERNEL_TC || mmax_for(rows) <= 4) ? 2 : 1);
+    const int max_bps = kernel == TWM_KERNEL_TC ? twm::tc::ASUM_CAP / mv_for(rows) : nkb;
     int splits, bps;
     if (splits_override > 0) {
         bps = (nkb + splits_override - 1) / splits_override;
+        if (bps > max_bps) return TWM_EINVAL;
         splits = (nkb + bps - 1) / bps;
     } else {
-        choose_splits(n_tiles, nkb, slots, &splits, &bps);
+        choose_splits(n_tiles, nkb, slots, max_bps, &splits, &bps);
+        if (bps > max_bps) return TWM_EINVAL;
     }
     out->kernel = kernel;
     out->n_tile = twm::simt::NT;
@@ -166,9 +207,13 @@ twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int split
 
 size_t twm_workspace_bytes(int M, int N, int K, int group_size)
 {
-    twm_plan_t pl;
-    if (twm_plan(M, N, K, group_size, kDefaultSms, 0, 0, &pl) != TWM_OK) return 0;
-    return pl.workspace_bytes;
+    // the larger of the two kernels' needs: which one runs depends on the activation dtype
+    twm_plan_t tc, simt;
+    size_t need = 0;
+    if (twm_plan(M, N, K, group_size, kDefaultSms, 0, TWM_KERNEL_TC, &tc) == TWM_OK) need = tc.workspace_bytes;
+    if (twm_plan(M, N, K, group_size, kDefaultSms, 0, TWM_KERNEL_SIMT, &simt) == TWM_OK)
+        need = std::max(need, simt.workspace_bytes);
+    return need;
 }
 
 twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
@@ -190,8 +235,13 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
     twm_status st = ensure_device(&sm_count);
     if (st != TWM_OK) return st;
 
+    // The tensor-core kernel takes FP16 activations; FP32 activations (the
+    // reference's own signature) run on the FP32 streaming kernel.
+    int kernel = a->kernel_override;
+    if (kernel == TWM_KERNEL_AUTO) kernel = (a->a_dtype == TWM_F16) ? TWM_KERNEL_TC : TWM_KERNEL_SIMT;
+    if (kernel == TWM_KERNEL_TC && a->a_dtype != TWM_F16) return TWM_EINVAL;
     twm_plan_t pl;
-    st = twm_plan(a->M, a->N, a->K, a->group_size, sm_count, a->splits_override, a->kernel_override, &pl);
+    st = twm_plan(a->M, a->N, a->K, a->group_size, sm_count, a->splits_override, kernel, &pl);
     if (st != TWM_OK) return st;
     if (pl.workspace_bytes > 0) {
         if (!a->workspace || a->workspace_bytes < pl.workspace_bytes) return TWM_EWORKSPACE;
@@ -201,8 +251,9 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
     cudaStream_t stream = (cudaStream_t)stream_;
     const size_t a_elt = a->a_dtype == TWM_F16 ? 2 : 4;
     const size_t c_elt = a->c_dtype == TWM_F16 ? 2 : 4;
-    for (int m0 = 0; m0 < a->M; m0 += 8) {
-        const int rows = std::min(8, a->M - m0);
+    const int row_step = kernel == TWM_KERNEL_TC ? 16 : 8;
+    for (int m0 = 0; m0 < a->M; m0 += row_step) {
+        const int rows = std::min(row_step, a->M - m0);
         twm::GemmParams p;
         memset(&p, 0, sizeof(p));
         p.M = rows; p.N = a->N; p.K = a->K; p.group = a->group_size; p.nkb = a->K / 32;
@@ -215,7 +266,11 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
         p.splits = pl.splits; p.blocks_per_split = pl.blocks_per_split;
         p.accumulate = (a->flags & TWM_FLAG_ACCUMULATE) ? 1 : 0;
         p.packed_offsets = a->packed_offsets; p.scales_offsets = a->scales_offsets; p.expert_idx = a->expert_idx;
-        st = launch_simt(p, mmax_for(rows), dim3(pl.grid_x, pl.grid_y, 1), (a->flags & TWM_FLAG_PDL) != 0, stream);
+        const bool pdl = (a->flags & TWM_FLAG_PDL) != 0;
+        if (kernel == TWM_KERNEL_TC)
+            st = launch_tc(p, mv_for(rows), dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
+        else
+            st = launch_simt(p, mmax_for(rows), dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
         if (st != TWM_OK) return st;
     }
     return TWM_OK;

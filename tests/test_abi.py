@@ -49,7 +49,7 @@ def test_plan_benchmark_shapes(twm_lib):
         assert 148 <= p.grid_x * p.grid_y <= 2 * 148, (n, k, p.grid_x, p.grid_y)
         assert p.blocks_per_split * p.splits >= k // 32 > p.blocks_per_split * (p.splits - 1)
         assert p.workspace_bytes == 16384 + p.splits * n * 4
-        assert twm_lib.twm_workspace_bytes(1, n, k, 128) == p.workspace_bytes
+        assert twm_lib.twm_workspace_bytes(1, n, k, 128) >= p.workspace_bytes
     # deterministic
     a = _plan(twm_lib, 4, 4608, 3584, 32, 148, 0, 0)[1]
     b = _plan(twm_lib, 4, 4608, 3584, 32, 148, 0, 0)[1]
