@@ -44,8 +44,9 @@ typedef enum twm_dtype { TWM_F32 = 0, TWM_F16 = 1 } twm_dtype;
 /* Kernel families twm_plan can choose. */
 enum {
     TWM_KERNEL_AUTO = 0,
-    TWM_KERNEL_SIMT = 1, /* memory-bound streaming kernel, FP32 FMA, M <= 8 */
-    TWM_KERNEL_TC = 2    /* tcgen05 tensor-core kernel, fp16 operands, fp32 accumulate in TMEM */
+    TWM_KERNEL_SIMT = 1, /* streaming kernel, FP32 FMA; the only one that takes FP32 activations */
+    TWM_KERNEL_TC = 2,   /* tcgen05 kernel: weights dequantised into tensor memory, FP32 accumulate in TMEM */
+    TWM_KERNEL_MMA = 3   /* streaming kernel for M <= 8, FP16 activations, warp-level MMA on unpacked registers */
 };
 
 /* Flags of twm_gemm_args.flags. */

@@ -27,14 +27,16 @@
 //                sums of A that fold the "-8" of every nibble.
 //   warp 1       one thread issues tcgen05.mma (A from TMEM, B from shared
 //                memory, D in TMEM): two per 32-block, one for the 2^-24
-//                nibbles and one for the 2^-20 nibbles, into separate
-//                accumulators.  tcgen05.commit releases TMEM slots and hands
-//                accumulators to the epilogue.
-//   warps 8-11   epilogue: at every scale-group boundary read the two
-//                accumulators (tcgen05.ld), combine them, subtract 8*sum(A),
-//                multiply by the group's FP32 scale and add to the running
-//                total in registers.  Products are exact (4-bit x 11-bit) and
-//                the scale is applied in FP32, as in the reference's kernel.
+//                nibbles and one for the 2^-20 nibbles, each into the block's
+//                own accumulator (no accumulate chains).  One tcgen05.commit
+//                per block tells the dequant warps that the slot's A operand is
+//                consumed and the epilogue that its accumulators are complete.
+//   warps 8-11   epilogue: read each block's two accumulators (tcgen05.ld),
+//                combine them into the scale group's sum, and at every group
+//                boundary subtract 8*sum(A), multiply by the group's FP32 scale
+//                and add to the running total in registers.  Products are exact
+//                (4-bit x 11-bit) and the scale is applied in FP32, as in the
+//                reference's kernel.
 // Split-K finish and the programmatic-dependent-launch rules are the same as
 // in the streaming kernel (twm_gemv_simt.cuh).
 #pragma once
@@ -44,38 +46,58 @@
 namespace twm {
 namespace tc {
 
+// Optional cycle accounting per warp role (development builds only: -DTWM_PROF).
+#ifdef TWM_PROF
+__device__ unsigned long long g_prof[64];
+#define PROF_DECL unsigned long long prof_t0 = clock64(), prof_acc[6] = {0, 0, 0, 0, 0, 0}
+#define PROF_BEGIN(t) unsigned long long t = clock64()
+#define PROF_END(t, cat) prof_acc[cat] += clock64() - t
+#define PROF_FLUSH(role)                                                                          \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) {                                        \
+        for (int c_ = 0; c_ < 6; ++c_) atomicAdd(&g_prof[(role) * 8 + c_], prof_acc[c_]);          \
+        atomicAdd(&g_prof[(role) * 8 + 6], clock64() - prof_t0);                                   \
+        atomicAdd(&g_prof[(role) * 8 + 7], 1ull);                                                  \
+    }
+#else
+#define PROF_DECL
+#define PROF_BEGIN(t)
+#define PROF_END(t, cat)
+#define PROF_FLUSH(role)
+#endif
+
 constexpr int NT = 128;               // columns per CTA = MMA M = TMEM lanes
 constexpr int WSTAGE_BLOCKS = 4;      // 32-blocks per ring stage (8 KB)
 constexpr int WSTAGES = 8;            // ring depth: 64 KB in flight per CTA
-constexpr int A_SLOTS = 8;            // TMEM slots for dequantised blocks, 16 columns each
+constexpr int SLOTS = 5;              // TMEM slots: one 32-block's A operand + its two accumulators each
 constexpr int THREADS = 12 * 32;
 constexpr int ASUM_CAP = 2048;        // floats: (blocks in the K slice) * MV must fit
 constexpr int B_BUF_BYTES = 16384;    // one staged activation chunk
 constexpr int EPI_THREADS = 128;
+constexpr int STAGER_THREADS = 64;
 
 template <int NB>
 struct Cfg {
     static constexpr int SLICE_BYTES = NB * 32;                     // NB rows x 16 K-slots x 2 B
     static constexpr int BLOCK_B_BYTES = 2 * SLICE_BYTES;           // "lo" and "hi" slices of a 32-block
     static constexpr int CHUNK_BLOCKS = B_BUF_BYTES / BLOCK_B_BYTES;   // 32-blocks per staged chunk
-    static constexpr int D_COLS = 4 * NB;                           // 2 buffers x (lo, hi) x NB
-    static constexpr int A_COL0 = 0;
-    static constexpr int D_COL0 = A_SLOTS * 16;
-    static constexpr int TMEM_COLS = (A_SLOTS * 16 + D_COLS) <= 256 ? 256 : 512;
+    static constexpr int A_COL0 = 0;                                // A slot s: columns [16 s, 16 s + 16)
+    static constexpr int D_COL0 = SLOTS * 16;                       // D slot s: lo at D_COL0 + 2 NB s, hi NB further
+    static constexpr int USED_COLS = SLOTS * (16 + 2 * NB);
+    static constexpr int TMEM_COLS = USED_COLS <= 256 ? 256 : 512;
+    static_assert(USED_COLS <= 512, "tensor memory holds 512 columns");
 };
 
 struct Smem {
     alignas(128) uint8_t packed[WSTAGES][WSTAGE_BLOCKS * NT * kBlockBytes];
     alignas(128) uint8_t b[2][B_BUF_BYTES];
-    float asum8[ASUM_CAP];            // [block in slice][MV]: -8 * sum of the block's activations
+    alignas(16) float asum8[ASUM_CAP]; // [block in slice][MV]: -8 * sum of the block's activations
     alignas(8) uint64_t w_full[WSTAGES];
     alignas(8) uint64_t w_empty[WSTAGES];
-    alignas(8) uint64_t a_full[A_SLOTS];
-    alignas(8) uint64_t a_empty[A_SLOTS];
+    alignas(8) uint64_t a_full[SLOTS];     // dequant -> MMA: the slot's A operand is in tensor memory
+    alignas(8) uint64_t mma_done[SLOTS];   // MMA (commit) -> dequant and epilogue: A is consumed, D is complete
+    alignas(8) uint64_t d_empty[SLOTS];    // epilogue -> MMA: the slot's accumulators are read out
     alignas(8) uint64_t b_full[2];
     alignas(8) uint64_t b_empty[2];
-    alignas(8) uint64_t d_full[2];
-    alignas(8) uint64_t d_empty[2];
     uint32_t tmem_base;
     int abort_flag;
     int is_last;
@@ -173,15 +195,15 @@ gemm_kernel(const GemmParams p)
     const int b0 = blockIdx.y * p.blocks_per_split;
     const int b1 = min(p.nkb, b0 + p.blocks_per_split);
     const int total_blocks = b1 - b0;
-    const int gb = p.group / kBlockK;                        // 32-blocks per scale group
+    const int gmask = p.group / kBlockK - 1;                 // 32-blocks per scale group (1 or 4), minus one
+    const int gshift = (p.group == 128) ? 2 : 0;
 
     if (tid == 0) {
         for (int s = 0; s < WSTAGES; ++s) { mbar_init(&sm.w_full[s], 1); mbar_init(&sm.w_empty[s], 4); }
-        for (int s = 0; s < A_SLOTS; ++s) { mbar_init(&sm.a_full[s], 4); mbar_init(&sm.a_empty[s], 1); }
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(&sm.b_full[s], 2); mbar_init(&sm.b_empty[s], 1);
-            mbar_init(&sm.d_full[s], 1); mbar_init(&sm.d_empty[s], 4);
+        for (int s = 0; s < SLOTS; ++s) {
+            mbar_init(&sm.a_full[s], 4); mbar_init(&sm.mma_done[s], 1); mbar_init(&sm.d_empty[s], 4);
         }
+        for (int s = 0; s < 2; ++s) { mbar_init(&sm.b_full[s], STAGER_THREADS / 32); mbar_init(&sm.b_empty[s], 1); }
         sm.abort_flag = 0;
         sm.is_last = 0;
         mbar_fence_init();
@@ -224,114 +246,158 @@ gemm_kernel(const GemmParams p)
 
     if (warp == 0) {
         // ---------------------------------------------- TMA producer (packed) --
+        PROF_DECL;
         for (int st = WSTAGES; st < n_wstages; ++st) {
             const int slot = st % WSTAGES;
+            PROF_BEGIN(t0);
             if (!wait_uniform(&sm.w_empty[slot], ((st / WSTAGES) - 1) & 1, abort_flag)) break;
+            PROF_END(t0, 0);
             if (lane == 0) issue_stage(st);
             __syncwarp();
         }
+        PROF_FLUSH(0);
     } else if (warp == 1) {
         // ------------------------------------------------------- MMA issuer --
+        // Every 32-block gets its own pair of accumulators (no accumulate
+        // chain: back-to-back MMAs into one accumulator would each wait out the
+        // tensor pipe's latency); the epilogue adds them up.
         if (lane == 0) {
             uint32_t idesc = 0;
             idesc |= 1u << 4;                         // D format f32
             idesc |= (uint32_t)(NB >> 3) << 17;       // N
             idesc |= (uint32_t)(128 >> 4) << 24;      // M
-            bool ok = true;
-            for (int i = 0; i < total_blocks && ok; ++i) {
-                const int b = b0 + i;
-                const int slot = i % A_SLOTS;
-                const int chunk = i / C::CHUNK_BLOCKS;
-                const int bi = i - chunk * C::CHUNK_BLOCKS;
-                const int gi = b / gb - b0 / gb;
-                const bool first_in_group = (i == 0) || (b % gb == 0);
-                const bool last_in_group = (i == total_blocks - 1) || ((b + 1) % gb == 0);
-                const int dbuf = gi & 1;
-                if (bi == 0) ok = mbar_wait_bounded(&sm.b_full[chunk & 1], (chunk >> 1) & 1, abort_flag);
-                if (ok && first_in_group && gi >= 2) ok = mbar_wait_bounded(&sm.d_empty[dbuf], ((gi >> 1) - 1) & 1, abort_flag);
-                if (ok) ok = mbar_wait_bounded(&sm.a_full[slot], (i / A_SLOTS) & 1, abort_flag);
-                if (!ok) break;
+            const uint64_t desc0[2] = {make_b_desc(smem_u32(&sm.b[0][0])), make_b_desc(smem_u32(&sm.b[1][0]))};
+            PROF_DECL;
+            int slot = 0, use = 0, bi = 0, chunk = 0;
+            for (int i = 0; i < total_blocks; ++i) {
+                PROF_BEGIN(t0);
+                if (bi == 0 && !mbar_wait_bounded(&sm.b_full[chunk & 1], (chunk >> 1) & 1, abort_flag)) break;
+                PROF_END(t0, 0);
+                PROF_BEGIN(t1);
+                if (use > 0 && !mbar_wait_bounded(&sm.d_empty[slot], (use - 1) & 1, abort_flag)) break;
+                PROF_END(t1, 1);
+                PROF_BEGIN(t2);
+                if (!mbar_wait_bounded(&sm.a_full[slot], use & 1, abort_flag)) break;
+                PROF_END(t2, 2);
+                PROF_BEGIN(t3);
                 tc_fence_after();
                 const uint32_t a_addr = tmem_base + C::A_COL0 + slot * 16;
-                const uint32_t d_addr = tmem_base + C::D_COL0 + dbuf * 2 * NB;
-                const uint32_t b_addr = smem_u32(&sm.b[chunk & 1][bi * C::BLOCK_B_BYTES]);
-                tc_mma_ts(d_addr, a_addr, make_b_desc(b_addr), idesc, first_in_group ? 0u : 1u);
-                tc_mma_ts(d_addr + NB, a_addr + 8, make_b_desc(b_addr + C::SLICE_BYTES), idesc, first_in_group ? 0u : 1u);
-                tc_commit(&sm.a_empty[slot]);
-                if (last_in_group) tc_commit(&sm.d_full[dbuf]);
-                if (bi == C::CHUNK_BLOCKS - 1 || i == total_blocks - 1) tc_commit(&sm.b_empty[chunk & 1]);
+                const uint32_t d_addr = tmem_base + C::D_COL0 + slot * 2 * NB;
+                // descriptor start-address field counts 16-byte units
+                const uint64_t bd = desc0[chunk & 1] + (uint64_t)((bi * C::BLOCK_B_BYTES) >> 4);
+                tc_mma_ts(d_addr, a_addr, bd, idesc, 0u);
+                tc_mma_ts(d_addr + NB, a_addr + 8, bd + (uint64_t)(C::SLICE_BYTES >> 4), idesc, 0u);
+                PROF_END(t3, 3);
+                PROF_BEGIN(t4);
+                tc_commit(&sm.mma_done[slot]);
+                const bool chunk_end = (bi == C::CHUNK_BLOCKS - 1) || (i == total_blocks - 1);
+                if (chunk_end) tc_commit(&sm.b_empty[chunk & 1]);
+                PROF_END(t4, 4);
+                if (++slot == SLOTS) { slot = 0; ++use; }
+                if (chunk_end) { bi = 0; ++chunk; } else { ++bi; }
             }
+            PROF_FLUSH(1);
         }
         __syncwarp();
     } else if (warp == 2 || warp == 3) {
         // ---------------------------------------------- activation stagers --
+        // One item = 8 consecutive K of one row (one 16-byte load).  The loads of
+        // a chunk are issued before the wait for its buffer, so their latency
+        // hides behind the MMAs that still read the buffer's previous contents.
         pdl_wait_prior_grids();
-        const int st_tid = tid - 64;                                     // 0..63
+        const int st_tid = tid - 64;
         const __half* A = reinterpret_cast<const __half*>(p.a);
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(A) & 15) == 0) && ((p.lda & 7) == 0);
         const int n_chunks = (total_blocks + C::CHUNK_BLOCKS - 1) / C::CHUNK_BLOCKS;
-        for (int chunk = 0; chunk < n_chunks; ++chunk) {
+        constexpr int PF = 8;                                            // items in flight per thread
+        PROF_DECL;
+        bool ok = true;
+        for (int chunk = 0; chunk < n_chunks && ok; ++chunk) {
             const int buf = chunk & 1;
             const int use = chunk >> 1;
-            if (use > 0 && !wait_uniform(&sm.b_empty[buf], (use - 1) & 1, abort_flag)) break;
             const int cb0 = chunk * C::CHUNK_BLOCKS;
             const int cb = min(C::CHUNK_BLOCKS, total_blocks - cb0);
-            // one item = 8 consecutive K of one row: (row m, block bi, word w)
             const int items = p.M * cb * 4;
-            for (int it0 = 0; it0 < items; it0 += 64) {
-                const int it = it0 + st_tid;
-                float s = 0.0f;
-                if (it < items) {
-                    const int m = it / (cb * 4);
-                    const int rem = it - m * (cb * 4);
-                    const int bi = rem >> 2;
-                    const int w = rem & 3;
-                    const size_t off = (size_t)m * p.lda + (size_t)(b0 + cb0 + bi) * kBlockK + w * 8;
-                    uint4 x;
-                    if (vec_ok) {
-                        x = *reinterpret_cast<const uint4*>(A + off);
-                    } else {
-                        const uint16_t* a16 = reinterpret_cast<const uint16_t*>(A) + off;
-                        x.x = a16[0] | ((uint32_t)a16[1] << 16); x.y = a16[2] | ((uint32_t)a16[3] << 16);
-                        x.z = a16[4] | ((uint32_t)a16[5] << 16); x.w = a16[6] | ((uint32_t)a16[7] << 16);
+            bool waited = false;
+            for (int base = 0; base < items; base += STAGER_THREADS * PF) {
+                uint4 x[PF];
+                PROF_BEGIN(t1);
+#pragma unroll
+                for (int u = 0; u < PF; ++u) {
+                    const int it = base + u * STAGER_THREADS + st_tid;
+                    x[u] = make_uint4(0, 0, 0, 0);
+                    if (it < items) {
+                        const int m = it / (cb * 4);
+                        const int rem = it - m * (cb * 4);
+                        const size_t off = (size_t)m * p.lda + (size_t)(b0 + cb0 + (rem >> 2)) * kBlockK + (rem & 3) * 8;
+                        if (vec_ok) {
+                            x[u] = *reinterpret_cast<const uint4*>(A + off);
+                        } else {
+                            const uint16_t* a16 = reinterpret_cast<const uint16_t*>(A) + off;
+                            x[u].x = a16[0] | ((uint32_t)a16[1] << 16); x[u].y = a16[2] | ((uint32_t)a16[3] << 16);
+                            x[u].z = a16[4] | ((uint32_t)a16[5] << 16); x[u].w = a16[6] | ((uint32_t)a16[7] << 16);
+                        }
                     }
-                    // K order of the "lo" slice: k0,k4,k2,k6 ; of the "hi" slice: k1,k5,k3,k7
-                    uint2 lo, hi;
-                    lo.x = __byte_perm(x.x, x.z, 0x5410); lo.y = __byte_perm(x.y, x.w, 0x5410);
-                    hi.x = __byte_perm(x.x, x.z, 0x7632); hi.y = __byte_perm(x.y, x.w, 0x7632);
-                    uint8_t* base = &sm.b[buf][bi * C::BLOCK_B_BYTES + (m >> 3) * 256 + (w >> 1) * 128 + (m & 7) * 16 + (w & 1) * 8];
-                    *reinterpret_cast<uint2*>(base) = lo;
-                    *reinterpret_cast<uint2*>(base + C::SLICE_BYTES) = hi;
-                    const __half2 h0 = *reinterpret_cast<const __half2*>(&x.x), h1 = *reinterpret_cast<const __half2*>(&x.y);
-                    const __half2 h2 = *reinterpret_cast<const __half2*>(&x.z), h3 = *reinterpret_cast<const __half2*>(&x.w);
-                    const float2 f0 = __half22float2(h0), f1 = __half22float2(h1), f2 = __half22float2(h2), f3 = __half22float2(h3);
-                    s = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
                 }
-                // four consecutive items are the four words of one block
-                s += __shfl_xor_sync(0xffffffffu, s, 1);
-                s += __shfl_xor_sync(0xffffffffu, s, 2);
-                if (it < items && (it & 3) == 0) {
-                    const int m = it / (cb * 4);
-                    const int bi = (it - m * (cb * 4)) >> 2;
-                    sm.asum8[(cb0 + bi) * MV + m] = -8.0f * s;
+                PROF_END(t1, 1);
+                if (!waited) {
+                    PROF_BEGIN(t0);
+                    if (use > 0 && !wait_uniform(&sm.b_empty[buf], (use - 1) & 1, abort_flag)) { ok = false; break; }
+                    PROF_END(t0, 0);
+                    waited = true;
                 }
+                PROF_BEGIN(t2);
+#pragma unroll
+                for (int u = 0; u < PF; ++u) {
+                    const int it = base + u * STAGER_THREADS + st_tid;
+                    float s = 0.0f;
+                    int m = 0, bi = 0;
+                    if (it < items) {
+                        m = it / (cb * 4);
+                        const int rem = it - m * (cb * 4);
+                        bi = rem >> 2;
+                        const int w = rem & 3;
+                        // K order of the "lo" slice: k0,k4,k2,k6 ; of the "hi" slice: k1,k5,k3,k7
+                        uint2 lo, hi;
+                        lo.x = __byte_perm(x[u].x, x[u].z, 0x5410); lo.y = __byte_perm(x[u].y, x[u].w, 0x5410);
+                        hi.x = __byte_perm(x[u].x, x[u].z, 0x7632); hi.y = __byte_perm(x[u].y, x[u].w, 0x7632);
+                        uint8_t* dst = &sm.b[buf][bi * C::BLOCK_B_BYTES + (m >> 3) * 256 + (w >> 1) * 128 + (m & 7) * 16 + (w & 1) * 8];
+                        *reinterpret_cast<uint2*>(dst) = lo;
+                        *reinterpret_cast<uint2*>(dst + C::SLICE_BYTES) = hi;
+                        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&x[u].x));
+                        const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&x[u].y));
+                        const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&x[u].z));
+                        const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&x[u].w));
+                        s = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+                    }
+                    // four consecutive items (lanes) are the four words of one block
+                    s += __shfl_xor_sync(0xffffffffu, s, 1);
+                    s += __shfl_xor_sync(0xffffffffu, s, 2);
+                    if (it < items && (it & 3) == 0) sm.asum8[(cb0 + bi) * MV + m] = -8.0f * s;
+                }
+                PROF_END(t2, 2);
             }
+            if (!ok) break;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> MMA's async reads
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.b_full[buf]);
         }
+        PROF_FLUSH(2);
     } else if (warp >= 4 && warp < 8) {
         // ------------------------------------------------------- dequant --
         const int quarter = warp & 3;
         const int col = quarter * 32 + lane;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + C::A_COL0;
-        bool ok = true;
-        for (int i = 0; i < total_blocks && ok; ++i) {
+        PROF_DECL;
+        int slot = 0, use = 0;
+        for (int i = 0; i < total_blocks; ++i) {
             const int st = i / WSTAGE_BLOCKS;
             const int r = i - st * WSTAGE_BLOCKS;
             const int wslot = st % WSTAGES;
-            if (r == 0) ok = wait_uniform(&sm.w_full[wslot], (st / WSTAGES) & 1, abort_flag);
-            if (!ok) break;
+            PROF_BEGIN(t0);
+            if (r == 0 && !wait_uniform(&sm.w_full[wslot], (st / WSTAGES) & 1, abort_flag)) break;
+            PROF_END(t0, 0);
+            PROF_BEGIN(t1);
             const uint4 v = lds128(&sm.packed[wslot][(r * NT + col) * kBlockBytes]);
             const uint32_t words[4] = {v.x, v.y, v.z, v.w};
             uint32_t regs[16];
@@ -348,17 +414,21 @@ gemm_kernel(const GemmParams p)
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sm.w_empty[wslot]);      // ring stage read out
             }
-            const int slot = i % A_SLOTS;
-            const int use = i / A_SLOTS;
-            if (use > 0) ok = wait_uniform(&sm.a_empty[slot], (use - 1) & 1, abort_flag);
-            if (!ok) break;
+            PROF_END(t1, 1);
+            PROF_BEGIN(t2);
+            if (use > 0 && !wait_uniform(&sm.mma_done[slot], (use - 1) & 1, abort_flag)) break;
+            PROF_END(t2, 2);
+            PROF_BEGIN(t3);
             tc_fence_after();
             tmem_st16(lane_base + slot * 16, regs);
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.a_full[slot]);
+            PROF_END(t3, 3);
+            if (++slot == SLOTS) { slot = 0; ++use; }
         }
+        PROF_FLUSH(3);
     } else if (warp >= 8) {
         // ------------------------------------------------------- epilogue --
         pdl_wait_prior_grids();
@@ -369,40 +439,57 @@ gemm_kernel(const GemmParams p)
         const uint16_t* scales = p.scales;
         if (p.scales_offsets != nullptr) scales += p.scales_offsets[p.expert_idx];
         const uint32_t lane_d = tmem_base + ((uint32_t)(quarter * 32) << 16) + C::D_COL0;
-        float tot[MV];
+        float tot[MV], gsum[MV], a8[MV];
 #pragma unroll
-        for (int m = 0; m < MV; ++m) tot[m] = 0.0f;
-        const int g_first = b0 / gb;
-        const int g_last = (b1 - 1) / gb;
-        bool ok = true;
-        uint16_t s_next = owner ? scales[(size_t)g_first * p.N + n] : (uint16_t)0;
-        for (int g = g_first; g <= g_last && ok; ++g) {
-            const int gi = g - g_first;
-            const int dbuf = gi & 1;
-            const float s = f16_bits_to_f32(s_next);
-            if (g < g_last && owner) s_next = scales[(size_t)(g + 1) * p.N + n];     // prefetch the next group's scale
-            ok = wait_uniform(&sm.d_full[dbuf], (gi >> 1) & 1, abort_flag);
-            if (!ok) break;
+        for (int m = 0; m < MV; ++m) { tot[m] = 0.0f; gsum[m] = 0.0f; a8[m] = 0.0f; }
+        PROF_DECL;
+        uint16_t s_bits = owner ? scales[(size_t)(b0 >> gshift) * p.N + n] : (uint16_t)0;
+        uint16_t s_next = s_bits;
+        int slot = 0, use = 0;
+        for (int i = 0; i < total_blocks; ++i) {
+            const int b = b0 + i;
+            const bool first_in_group = (i == 0) || ((b & gmask) == 0);
+            const bool last_in_group = (i == total_blocks - 1) || (((b + 1) & gmask) == 0);
+            if (first_in_group) {
+                s_bits = s_next;
+                const int g_next = (b >> gshift) + 1;
+                if (owner && (g_next << gshift) < b1) s_next = scales[(size_t)g_next * p.N + n];   // prefetch
+            }
+            PROF_BEGIN(t0);
+            if (!wait_uniform(&sm.mma_done[slot], use & 1, abort_flag)) break;
+            PROF_END(t0, 0);
+            PROF_BEGIN(t1);
             tc_fence_after();
             uint32_t lo[MV], hi[MV];
-            tmem_ld<MV>(lane_d + dbuf * 2 * NB, lo);
-            tmem_ld<MV>(lane_d + dbuf * 2 * NB + NB, hi);
+            tmem_ld<MV>(lane_d + slot * 2 * NB, lo);
+            tmem_ld<MV>(lane_d + slot * 2 * NB + NB, hi);
             tmem_wait_ld();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&sm.d_empty[dbuf]);
-            const int blk_lo = max(g * gb, b0) - b0;
-            const int blk_hi = min((g + 1) * gb, b1) - b0;
-            const float s20 = s * 1048576.0f;                 // 2^20: lo is scaled 2^-24, hi 2^-20
+            if (lane == 0) mbar_arrive(&sm.d_empty[slot]);
+            PROF_END(t1, 1);
+            PROF_BEGIN(t2);
+            // lo holds sum(a*q) * 2^-24, hi holds sum(a*q) * 2^-20
 #pragma unroll
             for (int m = 0; m < MV; ++m) {
-                float a8 = 0.0f;
-                for (int bl = blk_lo; bl < blk_hi; ++bl) a8 += sm.asum8[bl * MV + m];
-                const float v = fmaf(__uint_as_float(lo[m]), 16.0f, __uint_as_float(hi[m]));
-                tot[m] = fmaf(s20, v, tot[m]);
-                tot[m] = fmaf(s, a8, tot[m]);
+                gsum[m] += fmaf(__uint_as_float(lo[m]), 16.0f, __uint_as_float(hi[m]));
+                a8[m] += sm.asum8[i * MV + m];
             }
+            if (last_in_group) {
+                const float s = f16_bits_to_f32(s_bits);
+                const float s20 = s * 1048576.0f;             // 2^20
+#pragma unroll
+                for (int m = 0; m < MV; ++m) {
+                    tot[m] = fmaf(s20, gsum[m], tot[m]);
+                    tot[m] = fmaf(s, a8[m], tot[m]);
+                    gsum[m] = 0.0f;
+                    a8[m] = 0.0f;
+                }
+            }
+            PROF_END(t2, 2);
+            if (++slot == SLOTS) { slot = 0; ++use; }
         }
+        PROF_FLUSH(4);
 
         // --------------------------------------------- store / split-K finish --
         named_bar_sync(2, EPI_THREADS);

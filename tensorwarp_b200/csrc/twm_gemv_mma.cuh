@@ -1,0 +1,361 @@
+// twm_gemv_mma.cuh — the memory-bound W4A16 kernel for M <= 8, FP16 activations.
+//
+// Replaces warp_gemm_tw_marlin_m1 / _m1_direct
+// (crates/kernels/src/quantize.rs:1186-1298) and the launcher's split-K
+// (quantize.rs:1314-1357) on B200, where one SM has to unpack about 46 nibbles
+// per clock to keep up with HBM3e: more than FP32 FMAs (one per nibble plus the
+// unpack) can issue.  Same result definition: w = f32(scale) * (nibble - 8),
+// exact products, FP32 accumulation, the scale applied in FP32 per group.
+//
+// Shape of the work.  A CTA owns 128 columns and a contiguous range of
+// 32-blocks of K.  One producer warp streams packed rows (2 KB contiguous per
+// block) and scale rows into a five-deep shared-memory ring with 1-D bulk
+// copies (TMA unit, mbarrier completion, no multicast).  One stager warp puts
+// the slice's activations into shared memory in the order the tensor-core
+// fragments want them, with the per-group sums that fold the "-8".  Eight
+// consumer warps own 16 columns each for the whole K range, so there is no
+// cross-warp reduction.
+//
+// Register-level unpack.  Lane (g, t) reads u32 word t of column g's and
+// column g+8's 16-byte block (the warp's two loads are each one contiguous
+// 128-byte run).  `v & 0x000F000F` is, as two FP16 bit patterns, the pair of
+// subnormals (q0, q4) * 2^-24; `v & 0x00F000F0` is (q1, q5) * 2^-20; the same
+// on `v >> 8` gives (q2, q6) and (q3, q7).  Five integer instructions turn
+// eight nibbles into four operand registers; no conversion, no floating-point
+// instruction.  The four registers of the two columns are exactly the A
+// fragments of two m16n8k16 MMAs (one per power of two), whose B fragment is
+// the activation of the same K positions.  The accumulators of a scale group
+// are combined as 2^24*lo + 2^20*hi, the group's -8*sum(A) is added, and the
+// FP32 scale multiplies the sum, as the reference's kernel does per block.
+//
+// Split-K finish and the programmatic-dependent-launch rules are those of the
+// FP32 streaming kernel (twm_gemv_simt.cuh).
+#pragma once
+
+#include "twm_common.cuh"
+
+namespace twm {
+namespace mma {
+
+constexpr int NT = 128;          // columns per CTA
+constexpr int SB = 8;            // 32-blocks per ring stage
+constexpr int STAGES = 5;
+constexpr int CONSUMER_WARPS = 8;
+constexpr int CONSUMERS = CONSUMER_WARPS * 32;
+constexpr int THREADS = CONSUMERS + 64;      // + producer warp + stager warp
+constexpr int B_BUF_BYTES = 4096;            // staged activations per chunk buffer
+constexpr int ASUM_GROUPS = 64;              // scale groups per chunk, at most
+
+struct Smem {
+    alignas(128) uint8_t packed[STAGES][SB * NT * kBlockBytes];
+    alignas(128) uint16_t scales[STAGES][SB][NT];
+    alignas(128) uint8_t b[2][B_BUF_BYTES];           // [block in chunk][row m < MP][t] x 16 bytes
+    alignas(16) float asum8[2][ASUM_GROUPS][8];       // -8 * sum of a group's activations, per row
+    alignas(8) uint64_t full[STAGES];
+    alignas(8) uint64_t empty[STAGES];
+    alignas(8) uint64_t b_full[2];
+    alignas(8) uint64_t b_empty[2];
+    int abort_flag;
+    int is_last;
+};
+
+__device__ __forceinline__ void mma_m16n8k16(float (&d)[4], const uint32_t a0, const uint32_t a1, const uint32_t a2,
+                                             const uint32_t a3, const uint32_t b0, const uint32_t b1, const float (&c)[4]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+}
+
+__device__ __forceinline__ uint32_t lds32(const void* p) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)));
+    return v;
+}
+
+// MP = activation rows staged (power of two >= M, <= 8)
+template <int MP>
+__global__ void __launch_bounds__(THREADS, 2)
+gemv_kernel(const GemmParams p)
+{
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int n0 = blockIdx.x * NT;
+    const int cols = min(NT, p.N - n0);
+    const int b0 = blockIdx.y * p.blocks_per_split;
+    const int b1 = min(p.nkb, b0 + p.blocks_per_split);
+    const int total_blocks = b1 - b0;
+    const int n_stages = (total_blocks + SB - 1) / SB;
+    const int gshift = (p.group == 128) ? 2 : 0;             // 32-blocks per scale group = 1 << gshift
+    const int gmask = (1 << gshift) - 1;
+    constexpr int CHUNK_BLOCKS = B_BUF_BYTES / (64 * MP);    // 64, 32, 16, 8: multiples of SB and of a group
+    static_assert(CHUNK_BLOCKS % SB == 0 && CHUNK_BLOCKS <= ASUM_GROUPS, "chunk geometry");
+    const int n_chunks = (total_blocks + CHUNK_BLOCKS - 1) / CHUNK_BLOCKS;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], CONSUMER_WARPS); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&sm.b_full[s], 1); mbar_init(&sm.b_empty[s], CONSUMER_WARPS); }
+        sm.abort_flag = 0;
+        sm.is_last = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+    volatile int* abort_flag = &sm.abort_flag;
+
+    if (warp == CONSUMER_WARPS) {
+        // ------------------------------------------- producer: packed + scales --
+        const uint8_t* packed = p.packed;
+        const uint16_t* scales = p.scales;
+        if (p.packed_offsets != nullptr) {
+            pdl_wait_prior_grids();                       // the offset table may come from the kernel before
+            packed += p.packed_offsets[p.expert_idx];
+            scales += p.scales_offsets[p.expert_idx];
+        }
+        const bool scale_bulk_ok = ((cols & 7) == 0) && ((p.N & 7) == 0) &&
+                                   ((reinterpret_cast<uintptr_t>(scales + n0) & 15) == 0);
+        for (int it = 0; it < n_stages; ++it) {
+            const int slot = it % STAGES;
+            const int use = it / STAGES;
+            if (use > 0) {
+                const bool got = mbar_wait_bounded(&sm.empty[slot], (use - 1) & 1, abort_flag);
+                if (!__all_sync(0xffffffffu, got)) break;
+            }
+            const int bstart = b0 + it * SB;
+            const int nb = min(SB, b1 - bstart);
+            const int srow_first = bstart >> gshift;
+            const int nrows = ((bstart + nb - 1) >> gshift) - srow_first + 1;
+            uint32_t tx = (uint32_t)nb * cols * kBlockBytes;
+            if (scale_bulk_ok) {
+                tx += (uint32_t)nrows * cols * 2;
+            } else {
+                for (int r = 0; r < nrows; ++r) {
+                    const uint16_t* src = scales + (size_t)(srow_first + r) * p.N + n0;
+                    for (int cidx = lane; cidx < cols; cidx += 32) sm.scales[slot][r][cidx] = src[cidx];
+                }
+                __syncwarp();
+            }
+            if (lane == 0) {
+                mbar_arrive_expect_tx(&sm.full[slot], tx);
+                for (int r = 0; r < nb; ++r)
+                    bulk_g2s(&sm.packed[slot][r * NT * kBlockBytes],
+                             packed + ((size_t)(bstart + r) * p.N + n0) * kBlockBytes,
+                             (uint32_t)cols * kBlockBytes, &sm.full[slot]);
+                if (scale_bulk_ok)
+                    for (int r = 0; r < nrows; ++r)
+                        bulk_g2s(&sm.scales[slot][r][0], scales + (size_t)(srow_first + r) * p.N + n0,
+                                 (uint32_t)cols * 2, &sm.full[slot]);
+            }
+            __syncwarp();
+        }
+        return;
+    }
+
+    if (warp == CONSUMER_WARPS + 1) {
+        // ------------------------------------------------ activation stager --
+        // One item = 8 consecutive K of one row, stored as the 16 bytes
+        // {k0,k4 | k2,k6 | k1,k5 | k3,k7}: the B fragments of the block's two MMAs.
+        // Items are numbered so that the 4 << gshift lanes that hold one (scale
+        // group, row) are consecutive: the group's sum of activations is then a
+        // fixed-order warp-shuffle reduction.  K slices start and end on group
+        // boundaries (the host plan sees to that).
+        pdl_wait_prior_grids();
+        const __half* A = reinterpret_cast<const __half*>(p.a);
+        const bool vec_ok = ((reinterpret_cast<uintptr_t>(A) & 15) == 0) && ((p.lda & 7) == 0);
+        constexpr int PF = 8;
+        for (int chunk = 0; chunk < n_chunks; ++chunk) {
+            const int buf = chunk & 1;
+            const int use = chunk >> 1;
+            const int cb0 = chunk * CHUNK_BLOCKS;
+            const int cb = min(CHUNK_BLOCKS, total_blocks - cb0);
+            const int items = cb * MP * 4;                    // item = (((gi * MP) + m) << gshift | bj) * 4 + t
+            bool waited = false, ok = true;
+            for (int base = 0; base < items && ok; base += 32 * PF) {
+                uint4 x[PF];
+#pragma unroll
+                for (int u = 0; u < PF; ++u) {
+                    const int it = base + u * 32 + lane;
+                    x[u] = make_uint4(0, 0, 0, 0);
+                    if (it < items) {
+                        const int tt = it & 3;
+                        const int bj = (it >> 2) & gmask;
+                        const int rest = it >> (2 + gshift);
+                        const int m = rest % MP;
+                        const int bi = ((rest / MP) << gshift) + bj;
+                        if (m < p.M) {
+                            const size_t off = (size_t)m * p.lda + (size_t)(b0 + cb0 + bi) * kBlockK + tt * 8;
+                            if (vec_ok) {
+                                x[u] = *reinterpret_cast<const uint4*>(A + off);
+                            } else {
+                                const uint16_t* a16 = reinterpret_cast<const uint16_t*>(A) + off;
+                                x[u].x = a16[0] | ((uint32_t)a16[1] << 16); x[u].y = a16[2] | ((uint32_t)a16[3] << 16);
+                                x[u].z = a16[4] | ((uint32_t)a16[5] << 16); x[u].w = a16[6] | ((uint32_t)a16[7] << 16);
+                            }
+                        }
+                    }
+                }
+                if (!waited) {
+                    if (use > 0) {
+                        const bool got = mbar_wait_bounded(&sm.b_empty[buf], (use - 1) & 1, abort_flag);
+                        if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+                    }
+                    waited = true;
+                }
+#pragma unroll
+                for (int u = 0; u < PF; ++u) {
+                    const int it = base + u * 32 + lane;
+                    const int tt = it & 3;
+                    const int bj = (it >> 2) & gmask;
+                    const int rest = it >> (2 + gshift);
+                    const int m = rest % MP;
+                    const int gi = rest / MP;
+                    float s = 0.0f;
+                    if (it < items) {
+                        const int bi = (gi << gshift) + bj;
+                        uint4 o;
+                        o.x = __byte_perm(x[u].x, x[u].z, 0x5410); o.y = __byte_perm(x[u].y, x[u].w, 0x5410);
+                        o.z = __byte_perm(x[u].x, x[u].z, 0x7632); o.w = __byte_perm(x[u].y, x[u].w, 0x7632);
+                        *reinterpret_cast<uint4*>(&sm.b[buf][((bi * MP + m) * 4 + tt) * 16]) = o;
+                        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&x[u].x));
+                        const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&x[u].y));
+                        const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&x[u].z));
+                        const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&x[u].w));
+                        s = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+                    }
+                    s += __shfl_xor_sync(0xffffffffu, s, 1);
+                    s += __shfl_xor_sync(0xffffffffu, s, 2);
+                    if (gshift) {                                   // four blocks of a 128-group
+                        s += __shfl_xor_sync(0xffffffffu, s, 4);
+                        s += __shfl_xor_sync(0xffffffffu, s, 8);
+                    }
+                    if (it < items && (it & ((4 << gshift) - 1)) == 0) sm.asum8[buf][gi][m] = -8.0f * s;
+                }
+            }
+            if (!ok) break;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.b_full[buf]);
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------- consumers --
+    const int g = lane >> 2;
+    const int t = lane & 3;
+    const int wcol = warp * 16;                       // this warp's 16 columns inside the tile
+    float tot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float lo[4] = {0.0f, 0.0f, 0.0f, 0.0f}, hi[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const float zero4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    bool ok = true;
+
+    for (int it = 0; it < n_stages; ++it) {
+        const int slot = it % STAGES;
+        const int bstart = b0 + it * SB;
+        const int nb = min(SB, b1 - bstart);
+        const int rel0 = it * SB;                                     // first block of the stage, relative to b0
+        const int chunk = rel0 / CHUNK_BLOCKS;
+        const int buf = chunk & 1;
+        if (ok && (rel0 % CHUNK_BLOCKS) == 0) {
+            const bool got = mbar_wait_bounded(&sm.b_full[buf], (chunk >> 1) & 1, abort_flag);
+            if (!__all_sync(0xffffffffu, got)) ok = false;
+        }
+        if (ok) {
+            const bool got = mbar_wait_bounded(&sm.full[slot], (it / STAGES) & 1, abort_flag);
+            if (!__all_sync(0xffffffffu, got)) ok = false;
+        }
+        if (ok) {
+            const int srow_first = bstart >> gshift;
+#pragma unroll 2
+            for (int r = 0; r < nb; ++r) {
+                const int b = bstart + r;
+                const int bi = rel0 + r - chunk * CHUNK_BLOCKS;       // block inside the chunk
+                const uint8_t* wp = &sm.packed[slot][(r * NT + wcol) * kBlockBytes + lane * 4];
+                const uint32_t v0 = lds32(wp);                        // column g, word t
+                const uint32_t v1 = lds32(wp + 128);                  // column g + 8, word t
+                uint4 xb = make_uint4(0, 0, 0, 0);
+                if (g < MP) xb = lds128(&sm.b[buf][((bi * MP + g) * 4 + t) * 16]);
+                const uint32_t v0s = v0 >> 8, v1s = v1 >> 8;
+                const bool first = ((b & gmask) == 0) || (r == 0 && it == 0);
+                // lo: nibbles (0,4) and (2,6) scaled 2^-24 ; hi: nibbles (1,5) and (3,7) scaled 2^-20
+                if (first) {
+                    mma_m16n8k16(lo, v0 & 0x000F000Fu, v1 & 0x000F000Fu, v0s & 0x000F000Fu, v1s & 0x000F000Fu, xb.x, xb.y, zero4);
+                    mma_m16n8k16(hi, v0 & 0x00F000F0u, v1 & 0x00F000F0u, v0s & 0x00F000F0u, v1s & 0x00F000F0u, xb.z, xb.w, zero4);
+                } else {
+                    mma_m16n8k16(lo, v0 & 0x000F000Fu, v1 & 0x000F000Fu, v0s & 0x000F000Fu, v1s & 0x000F000Fu, xb.x, xb.y, lo);
+                    mma_m16n8k16(hi, v0 & 0x00F000F0u, v1 & 0x00F000F0u, v0s & 0x00F000F0u, v1s & 0x00F000F0u, xb.z, xb.w, hi);
+                }
+                const bool last = (((b + 1) & gmask) == 0) || (b == b1 - 1);
+                if (last) {
+                    const int srow = (b >> gshift) - srow_first;
+                    const float s0 = f16_bits_to_f32(sm.scales[slot][srow][wcol + g]);
+                    const float s1 = f16_bits_to_f32(sm.scales[slot][srow][wcol + g + 8]);
+                    const int gi = (b >> gshift) - ((b0 + chunk * CHUNK_BLOCKS) >> gshift);
+                    const float2 a8 = *reinterpret_cast<const float2*>(&sm.asum8[buf][gi][2 * t]);
+                    const float k20 = 1048576.0f;                     // 2^20
+                    // value = 2^24*lo + 2^20*hi - 8*sum(a)
+                    tot[0] = fmaf(s0, fmaf(fmaf(lo[0], 16.0f, hi[0]), k20, a8.x), tot[0]);
+                    tot[1] = fmaf(s0, fmaf(fmaf(lo[1], 16.0f, hi[1]), k20, a8.y), tot[1]);
+                    tot[2] = fmaf(s1, fmaf(fmaf(lo[2], 16.0f, hi[2]), k20, a8.x), tot[2]);
+                    tot[3] = fmaf(s1, fmaf(fmaf(lo[3], 16.0f, hi[3]), k20, a8.y), tot[3]);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) {
+            if (ok) mbar_arrive(&sm.empty[slot]);
+            const bool chunk_end = ((rel0 + SB) % CHUNK_BLOCKS == 0) || (it == n_stages - 1);
+            if (ok && chunk_end) mbar_arrive(&sm.b_empty[buf]);
+        }
+    }
+
+    // ----------------------------------------------------- store / split-K --
+    named_bar_sync(1, CONSUMERS);
+    if (*abort_flag) return;                  // a wait expired: leave C untouched, the error word is set
+    // lane (g, t) holds C[m = 2t, 2t+1][n = n0 + wcol + g] and the same rows for column + 8
+    const int nA = n0 + wcol + g, nB = nA + 8;
+    const int mA = 2 * t, mB = 2 * t + 1;
+    auto store_c = [&](int m, int n, float v) {
+        if (m >= p.M || n >= p.N) return;
+        const size_t off = (size_t)m * p.ldc + n;
+        if (p.c_is_f16) {
+            __half* cp = reinterpret_cast<__half*>(p.c);
+            if (p.accumulate) v += __half2float(cp[off]);
+            cp[off] = __float2half_rn(v);
+        } else {
+            float* cp = reinterpret_cast<float*>(p.c);
+            if (p.accumulate) v += cp[off];
+            cp[off] = v;
+        }
+    };
+    if (p.splits == 1) {
+        store_c(mA, nA, tot[0]); store_c(mB, nA, tot[1]); store_c(mA, nB, tot[2]); store_c(mB, nB, tot[3]);
+        return;
+    }
+    auto ws_at = [&](int sp, int m, int n) -> float* { return &p.ws_partials[((size_t)sp * p.M + m) * p.N + n]; };
+    if (mA < p.M && nA < p.N) *ws_at(blockIdx.y, mA, nA) = tot[0];
+    if (mB < p.M && nA < p.N) *ws_at(blockIdx.y, mB, nA) = tot[1];
+    if (mA < p.M && nB < p.N) *ws_at(blockIdx.y, mA, nB) = tot[2];
+    if (mB < p.M && nB < p.N) *ws_at(blockIdx.y, mB, nB) = tot[3];
+    __threadfence();
+    named_bar_sync(1, CONSUMERS);
+    if (tid == 0) {
+        const unsigned prev = atomicAdd(&p.ws_counters[blockIdx.x], 1u);
+        sm.is_last = (prev == (unsigned)(p.splits - 1));
+    }
+    named_bar_sync(1, CONSUMERS);
+    if (!sm.is_last) return;
+    __threadfence();
+    auto finish = [&](int m, int n) {
+        if (m >= p.M || n >= p.N) return;
+        float s = 0.0f;
+        for (int sp = 0; sp < p.splits; ++sp) s += ld_cg_f32(ws_at(sp, m, n));
+        store_c(m, n, s);
+    };
+    finish(mA, nA); finish(mB, nA); finish(mA, nB); finish(mB, nB);
+    if (tid == 0) atomicExch(&p.ws_counters[blockIdx.x], 0u);
+}
+
+}  // namespace mma
+}  // namespace twm

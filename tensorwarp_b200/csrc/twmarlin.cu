@@ -15,6 +15,7 @@
 #include "twm_common.cuh"
 #include "twm_gemv_simt.cuh"
 #include "twm_gemm_tc.cuh"
+#include "twm_gemv_mma.cuh"
 #include "twm_layout.cuh"
 
 namespace {
@@ -76,6 +77,14 @@ twm_status ensure_device(int* sm_count_out)
             raise_tc((const void*)twm::tc::gemm_kernel<16, 4>);
             raise_tc((const void*)twm::tc::gemm_kernel<16, 8>);
             raise_tc((const void*)twm::tc::gemm_kernel<16, 16>);
+            auto raise_mma = [&](const void* fn) {
+                if (r == cudaSuccess)
+                    r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(twm::mma::Smem));
+            };
+            raise_mma((const void*)twm::mma::gemv_kernel<1>);
+            raise_mma((const void*)twm::mma::gemv_kernel<2>);
+            raise_mma((const void*)twm::mma::gemv_kernel<4>);
+            raise_mma((const void*)twm::mma::gemv_kernel<8>);
             if (r != cudaSuccess) { set_error("cudaFuncSetAttribute", r); st.status = TWM_ELAUNCH; }
         }
         st.ready = true;
@@ -95,13 +104,14 @@ bool shape_ok(int M, int N, int K, int G)
 // fixed start-up (barrier init, activation staging, warp reduce) worth about
 // 16 such blocks, and a split tile pays the last-arriver's pass over the
 // partials.  `slots` = CTAs that can be resident at once.
-void choose_splits(int n_tiles, int nkb, int slots, int max_bps, int* splits, int* bps)
+void choose_splits(int n_tiles, int nkb, int slots, int max_bps, int align, int* splits, int* bps)
 {
     double best = 1e30;
     int best_s = 1, best_bps = nkb;
     const int smax = std::min(kMaxSplits, nkb);
     for (int s = 1; s <= smax; ++s) {
-        const int b = (nkb + s - 1) / s;
+        int b = (nkb + s - 1) / s;
+        b = (b + align - 1) / align * align;     // slices of whole scale groups where the kernel wants them
         if (b > max_bps && s < smax) continue;   // the kernel's per-slice staging capacity
         const int s_eff = (nkb + b - 1) / b;
         if (s_eff != s) continue;   // same slicing as a smaller s
@@ -143,6 +153,30 @@ twm_status launch_tc(const twm::GemmParams& p, int mv, dim3 grid, bool pdl, cuda
     return TWM_OK;
 }
 
+twm_status launch_mma(const twm::GemmParams& p, int mp, dim3 grid, bool pdl, cudaStream_t stream)
+{
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(twm::mma::THREADS, 1, 1);
+    cfg.dynamicSmemBytes = sizeof(twm::mma::Smem);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cudaError_t e;
+    switch (mp) {
+        case 1: e = cudaLaunchKernelEx(&cfg, twm::mma::gemv_kernel<1>, p); break;
+        case 2: e = cudaLaunchKernelEx(&cfg, twm::mma::gemv_kernel<2>, p); break;
+        case 4: e = cudaLaunchKernelEx(&cfg, twm::mma::gemv_kernel<4>, p); break;
+        default: e = cudaLaunchKernelEx(&cfg, twm::mma::gemv_kernel<8>, p); break;
+    }
+    if (e != cudaSuccess) { set_error("launch mma::gemv_kernel", e); return TWM_ELAUNCH; }
+    return TWM_OK;
+}
+
 twm_status launch_simt(const twm::GemmParams& p, int mmax, dim3 grid, bool pdl, cudaStream_t stream)
 {
     cudaLaunchConfig_t cfg;
@@ -179,20 +213,22 @@ twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int split
     if (sm_count <= 0) sm_count = kDefaultSms;
     const int nkb = K / 32;
     int kernel = kernel_override;
-    if (kernel == TWM_KERNEL_AUTO) kernel = TWM_KERNEL_TC;
-    if (kernel != TWM_KERNEL_SIMT && kernel != TWM_KERNEL_TC) return TWM_EINVAL;
+    if (kernel == TWM_KERNEL_AUTO) kernel = (M <= 8) ? TWM_KERNEL_MMA : TWM_KERNEL_TC;
+    if (kernel != TWM_KERNEL_SIMT && kernel != TWM_KERNEL_TC && kernel != TWM_KERNEL_MMA) return TWM_EINVAL;
     // rows one launch carries; more rows are served by further launches
     const int rows = std::min(M, kernel == TWM_KERNEL_TC ? 16 : 8);
     const int n_tiles = (N + twm::simt::NT - 1) / twm::simt::NT;
-    const int slots = sm_count * ((kernel == TWM_KERNEL_TC || mmax_for(rows) <= 4) ? 2 : 1);
+    const int slots = sm_count * ((kernel != TWM_KERNEL_SIMT || mmax_for(rows) <= 4) ? 2 : 1);
     const int max_bps = kernel == TWM_KERNEL_TC ? twm::tc::ASUM_CAP / mv_for(rows) : nkb;
+    const int align = (kernel == TWM_KERNEL_MMA) ? group_size / 32 : 1;   // whole scale groups per slice
     int splits, bps;
     if (splits_override > 0) {
         bps = (nkb + splits_override - 1) / splits_override;
+        bps = (bps + align - 1) / align * align;
         if (bps > max_bps) return TWM_EINVAL;
         splits = (nkb + bps - 1) / bps;
     } else {
-        choose_splits(n_tiles, nkb, slots, max_bps, &splits, &bps);
+        choose_splits(n_tiles, nkb, slots, max_bps, align, &splits, &bps);
         if (bps > max_bps) return TWM_EINVAL;
     }
     out->kernel = kernel;
@@ -212,6 +248,8 @@ size_t twm_workspace_bytes(int M, int N, int K, int group_size)
     size_t need = 0;
     if (twm_plan(M, N, K, group_size, kDefaultSms, 0, TWM_KERNEL_TC, &tc) == TWM_OK) need = tc.workspace_bytes;
     if (twm_plan(M, N, K, group_size, kDefaultSms, 0, TWM_KERNEL_SIMT, &simt) == TWM_OK)
+        need = std::max(need, simt.workspace_bytes);
+    if (twm_plan(M, N, K, group_size, kDefaultSms, 0, TWM_KERNEL_MMA, &simt) == TWM_OK)
         need = std::max(need, simt.workspace_bytes);
     return need;
 }
@@ -238,8 +276,9 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
     // The tensor-core kernel takes FP16 activations; FP32 activations (the
     // reference's own signature) run on the FP32 streaming kernel.
     int kernel = a->kernel_override;
-    if (kernel == TWM_KERNEL_AUTO) kernel = (a->a_dtype == TWM_F16) ? TWM_KERNEL_TC : TWM_KERNEL_SIMT;
-    if (kernel == TWM_KERNEL_TC && a->a_dtype != TWM_F16) return TWM_EINVAL;
+    if (kernel == TWM_KERNEL_AUTO)
+        kernel = (a->a_dtype != TWM_F16) ? TWM_KERNEL_SIMT : (a->M <= 8 ? TWM_KERNEL_MMA : TWM_KERNEL_TC);
+    if (kernel != TWM_KERNEL_SIMT && a->a_dtype != TWM_F16) return TWM_EINVAL;
     twm_plan_t pl;
     st = twm_plan(a->M, a->N, a->K, a->group_size, sm_count, a->splits_override, kernel, &pl);
     if (st != TWM_OK) return st;
@@ -269,6 +308,8 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
         const bool pdl = (a->flags & TWM_FLAG_PDL) != 0;
         if (kernel == TWM_KERNEL_TC)
             st = launch_tc(p, mv_for(rows), dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
+        else if (kernel == TWM_KERNEL_MMA)
+            st = launch_mma(p, mmax_for(rows), dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
         else
             st = launch_simt(p, mmax_for(rows), dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
         if (st != TWM_OK) return st;
@@ -399,6 +440,18 @@ const char* twm_status_string(twm_status s)
     }
     return "unknown status";
 }
+
+#ifdef TWM_PROF
+// development builds only: read and clear the per-role cycle counters
+int twm_prof_read(unsigned long long* out)
+{
+    cudaDeviceSynchronize();
+    unsigned long long zero[64] = {0};
+    if (cudaMemcpyFromSymbol(out, twm::tc::g_prof, sizeof(zero)) != cudaSuccess) return -1;
+    cudaMemcpyToSymbol(twm::tc::g_prof, zero, sizeof(zero));
+    return 0;
+}
+#endif
 
 const char* twm_last_error(void) { return t_last_error; }
 

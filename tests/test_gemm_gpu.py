@@ -153,12 +153,12 @@ def test_m1_f32_reference_mode(k, n, splits):
     assert np.max(np.abs(y[0] - ko)) <= 1e-5 * max(1.0, float(np.max(np.abs(ko))))
 
 
-@pytest.mark.parametrize("kernel", [_lib.TWM_KERNEL_SIMT, _lib.TWM_KERNEL_TC])
+@pytest.mark.parametrize("kernel", [_lib.TWM_KERNEL_SIMT, _lib.TWM_KERNEL_TC, _lib.TWM_KERNEL_MMA])
 @pytest.mark.parametrize("group", [32, 128])
 @pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 8, 13, 16])
 @pytest.mark.parametrize("k,n", [(128, 33), (384, 257), (1024, 512), (3584, 264)])
 def test_small_m_f16(m, k, n, group, kernel):
-    """FP16 activations and output on both kernel families (streaming FP32-FMA and tcgen05)."""
+    """FP16 activations and output on every kernel family (FP32-FMA, warp-level MMA, tcgen05)."""
     if k % group:
         pytest.skip("K not a multiple of the group")
     _, packed, scales = _quantised(k, n, group, 43)
@@ -168,20 +168,21 @@ def test_small_m_f16(m, k, n, group, kernel):
     assert rel_err_floored(y, ref64) < TOL_F16
     # and bit-identical to rounding the f32-output run to f16 (one rounding, at the end)
     y32 = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float32, kernel_override=kernel)
-    assert rel_err_floored(y32, ref64) < (TOL_TC_F32 if kernel == _lib.TWM_KERNEL_TC else TOL_F32)
+    assert rel_err_floored(y32, ref64) < (TOL_F32 if kernel == _lib.TWM_KERNEL_SIMT else TOL_TC_F32)
     assert np.array_equal(y32.astype(np.float16).astype(np.float32), y)
 
 
+@pytest.mark.parametrize("kernel", [_lib.TWM_KERNEL_TC, _lib.TWM_KERNEL_MMA])
 @pytest.mark.parametrize("splits", [1, 2, 5])
 @pytest.mark.parametrize("k,n,group", [(32, 40, 32), (96, 130, 32), (2048, 300, 128), (4224, 129, 128), (8192, 64, 32)])
-def test_tc_kernel_slices(k, n, group, splits):
-    """tcgen05 kernel: K slices that start and end inside a scale group, more blocks than
-    TMEM slots, ring stages and staged activation chunks, ragged N."""
+def test_tc_kernel_slices(k, n, group, splits, kernel):
+    """Tensor-core kernels: K slices that start and end inside a scale group (tcgen05 kernel),
+    more blocks than TMEM slots, ring stages and staged activation chunks, ragged N."""
     m = 3
     _, packed, scales = _quantised(k, n, group, 45)
     a = seeded_activations(m, k, 1)
     y = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float32,
-                  kernel_override=_lib.TWM_KERNEL_TC, splits_override=splits)
+                  kernel_override=kernel, splits_override=splits)
     assert rel_err_floored(y, oracle.w4a16_f64(a, packed, scales, m, n, k, group)) < TOL_TC_F32
 
 
@@ -272,7 +273,7 @@ def test_deterministic_and_split_invariant():
     k, n, group = 3584, 4608, 128
     _, packed, scales = _quantised(k, n, group, 53)
     a = seeded_activations(1, k, 0)
-    for kernel in (_lib.TWM_KERNEL_SIMT, _lib.TWM_KERNEL_TC):
+    for kernel in (_lib.TWM_KERNEL_SIMT, _lib.TWM_KERNEL_TC, _lib.TWM_KERNEL_MMA):
         runs = [_run_gemm(a, packed, scales, 1, n, k, group, torch.float16, torch.float32, kernel_override=kernel)
                 for _ in range(3)]
         assert np.array_equal(runs[0], runs[1]) and np.array_equal(runs[0], runs[2])
