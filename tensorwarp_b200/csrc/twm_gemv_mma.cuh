@@ -66,14 +66,30 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], const uint32_t a0, c
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
 }
 
-__device__ __forceinline__ uint32_t lds32(const void* p) {
+// loads from 32-bit shared-window addresses (base registers computed once per thread)
+__device__ __forceinline__ uint32_t lds32_at(uint32_t addr) {
     uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)));
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 lds128_at(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float2 lds64f_at(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint16_t lds16_at(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
     return v;
 }
 
-// MP = activation rows staged (power of two >= M, <= 8)
-template <int MP>
+// MP = activation rows staged (power of two >= M, <= 8); GSHIFT = log2(32-blocks per scale group)
+template <int MP, int GSHIFT>
 __global__ void __launch_bounds__(THREADS, 2)
 gemv_kernel(const GemmParams p)
 {
@@ -89,8 +105,8 @@ gemv_kernel(const GemmParams p)
     const int b1 = min(p.nkb, b0 + p.blocks_per_split);
     const int total_blocks = b1 - b0;
     const int n_stages = (total_blocks + SB - 1) / SB;
-    const int gshift = (p.group == 128) ? 2 : 0;             // 32-blocks per scale group = 1 << gshift
-    const int gmask = (1 << gshift) - 1;
+    constexpr int gshift = GSHIFT;                           // 32-blocks per scale group = 1 << gshift
+    constexpr int gmask = (1 << gshift) - 1;
     constexpr int CHUNK_BLOCKS = B_BUF_BYTES / (64 * MP);    // 64, 32, 16, 8: multiples of SB and of a group
     static_assert(CHUNK_BLOCKS % SB == 0 && CHUNK_BLOCKS <= ASUM_GROUPS, "chunk geometry");
     const int n_chunks = (total_blocks + CHUNK_BLOCKS - 1) / CHUNK_BLOCKS;
@@ -227,7 +243,7 @@ gemv_kernel(const GemmParams p)
                     }
                     s += __shfl_xor_sync(0xffffffffu, s, 1);
                     s += __shfl_xor_sync(0xffffffffu, s, 2);
-                    if (gshift) {                                   // four blocks of a 128-group
+                    if (gshift != 0) {                              // four blocks of a 128-group
                         s += __shfl_xor_sync(0xffffffffu, s, 4);
                         s += __shfl_xor_sync(0xffffffffu, s, 8);
                     }
@@ -242,22 +258,29 @@ gemv_kernel(const GemmParams p)
     }
 
     // ---------------------------------------------------------- consumers --
+    // K slices hold whole scale groups and a ring stage holds whole groups, so
+    // the per-stage work unrolls into straight-line code: per 32-block two
+    // 32-bit loads, one 128-bit load, ten integer ops and two MMAs.
     const int g = lane >> 2;
     const int t = lane & 3;
     const int wcol = warp * 16;                       // this warp's 16 columns inside the tile
+    constexpr int GB = 1 << GSHIFT;
     float tot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    float lo[4] = {0.0f, 0.0f, 0.0f, 0.0f}, hi[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     const float zero4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const uint32_t w_base = smem_u32(&sm.packed[0][0]) + wcol * kBlockBytes + lane * 4;
+    const uint32_t s_base = smem_u32(&sm.scales[0][0][0]) + (wcol + g) * 2;
+    const uint32_t b_base = smem_u32(&sm.b[0][0]) + (g * 4 + t) * 16;
+    const uint32_t a8_base = smem_u32(&sm.asum8[0][0][0]) + t * 8;
     bool ok = true;
 
     for (int it = 0; it < n_stages; ++it) {
         const int slot = it % STAGES;
-        const int bstart = b0 + it * SB;
-        const int nb = min(SB, b1 - bstart);
+        const int nb = min(SB, b1 - (b0 + it * SB));
         const int rel0 = it * SB;                                     // first block of the stage, relative to b0
         const int chunk = rel0 / CHUNK_BLOCKS;
         const int buf = chunk & 1;
-        if (ok && (rel0 % CHUNK_BLOCKS) == 0) {
+        const int bi0 = rel0 - chunk * CHUNK_BLOCKS;                  // first block of the stage inside the chunk
+        if (ok && bi0 == 0) {
             const bool got = mbar_wait_bounded(&sm.b_full[buf], (chunk >> 1) & 1, abort_flag);
             if (!__all_sync(0xffffffffu, got)) ok = false;
         }
@@ -266,35 +289,36 @@ gemv_kernel(const GemmParams p)
             if (!__all_sync(0xffffffffu, got)) ok = false;
         }
         if (ok) {
-            const int srow_first = bstart >> gshift;
-#pragma unroll 2
-            for (int r = 0; r < nb; ++r) {
-                const int b = bstart + r;
-                const int bi = rel0 + r - chunk * CHUNK_BLOCKS;       // block inside the chunk
-                const uint8_t* wp = &sm.packed[slot][(r * NT + wcol) * kBlockBytes + lane * 4];
-                const uint32_t v0 = lds32(wp);                        // column g, word t
-                const uint32_t v1 = lds32(wp + 128);                  // column g + 8, word t
-                uint4 xb = make_uint4(0, 0, 0, 0);
-                if (g < MP) xb = lds128(&sm.b[buf][((bi * MP + g) * 4 + t) * 16]);
-                const uint32_t v0s = v0 >> 8, v1s = v1 >> 8;
-                const bool first = ((b & gmask) == 0) || (r == 0 && it == 0);
-                // lo: nibbles (0,4) and (2,6) scaled 2^-24 ; hi: nibbles (1,5) and (3,7) scaled 2^-20
-                if (first) {
-                    mma_m16n8k16(lo, v0 & 0x000F000Fu, v1 & 0x000F000Fu, v0s & 0x000F000Fu, v1s & 0x000F000Fu, xb.x, xb.y, zero4);
-                    mma_m16n8k16(hi, v0 & 0x00F000F0u, v1 & 0x00F000F0u, v0s & 0x00F000F0u, v1s & 0x00F000F0u, xb.z, xb.w, zero4);
-                } else {
-                    mma_m16n8k16(lo, v0 & 0x000F000Fu, v1 & 0x000F000Fu, v0s & 0x000F000Fu, v1s & 0x000F000Fu, xb.x, xb.y, lo);
-                    mma_m16n8k16(hi, v0 & 0x00F000F0u, v1 & 0x00F000F0u, v0s & 0x00F000F0u, v1s & 0x00F000F0u, xb.z, xb.w, hi);
-                }
-                const bool last = (((b + 1) & gmask) == 0) || (b == b1 - 1);
-                if (last) {
-                    const int srow = (b >> gshift) - srow_first;
-                    const float s0 = f16_bits_to_f32(sm.scales[slot][srow][wcol + g]);
-                    const float s1 = f16_bits_to_f32(sm.scales[slot][srow][wcol + g + 8]);
-                    const int gi = (b >> gshift) - ((b0 + chunk * CHUNK_BLOCKS) >> gshift);
-                    const float2 a8 = *reinterpret_cast<const float2*>(&sm.asum8[buf][gi][2 * t]);
+            const uint32_t w_st = w_base + slot * (SB * NT * kBlockBytes);
+            const uint32_t s_st = s_base + slot * (SB * NT * 2);
+            const uint32_t b_st = b_base + buf * B_BUF_BYTES + bi0 * (MP * 64);
+            const uint32_t a8_st = a8_base + (buf * ASUM_GROUPS + (bi0 >> GSHIFT)) * 32;
+#pragma unroll
+            for (int r0 = 0; r0 < SB; r0 += GB) {
+                if (r0 < nb) {
+                    float lo[4], hi[4];
+#pragma unroll
+                    for (int j = 0; j < GB; ++j) {
+                        const int r = r0 + j;
+                        const uint32_t v0 = lds32_at(w_st + r * (NT * kBlockBytes));          // column g, word t
+                        const uint32_t v1 = lds32_at(w_st + r * (NT * kBlockBytes) + 128);    // column g + 8, word t
+                        uint4 xb = make_uint4(0, 0, 0, 0);
+                        if (MP == 8 || g < MP) xb = lds128_at(b_st + r * (MP * 64));
+                        const uint32_t v0s = v0 >> 8, v1s = v1 >> 8;
+                        // lo: nibbles (0,4),(2,6) scaled 2^-24 ; hi: nibbles (1,5),(3,7) scaled 2^-20
+                        if (j == 0) {
+                            mma_m16n8k16(lo, v0 & 0x000F000Fu, v1 & 0x000F000Fu, v0s & 0x000F000Fu, v1s & 0x000F000Fu, xb.x, xb.y, zero4);
+                            mma_m16n8k16(hi, v0 & 0x00F000F0u, v1 & 0x00F000F0u, v0s & 0x00F000F0u, v1s & 0x00F000F0u, xb.z, xb.w, zero4);
+                        } else {
+                            mma_m16n8k16(lo, v0 & 0x000F000Fu, v1 & 0x000F000Fu, v0s & 0x000F000Fu, v1s & 0x000F000Fu, xb.x, xb.y, lo);
+                            mma_m16n8k16(hi, v0 & 0x00F000F0u, v1 & 0x00F000F0u, v0s & 0x00F000F0u, v1s & 0x00F000F0u, xb.z, xb.w, hi);
+                        }
+                    }
+                    // group done: value = 2^24*lo + 2^20*hi - 8*sum(a), times the FP32 scale
+                    const float s0 = f16_bits_to_f32(lds16_at(s_st + (r0 >> GSHIFT) * (NT * 2)));
+                    const float s1 = f16_bits_to_f32(lds16_at(s_st + (r0 >> GSHIFT) * (NT * 2) + 16));
+                    const float2 a8 = lds64f_at(a8_st + (r0 >> GSHIFT) * 32);
                     const float k20 = 1048576.0f;                     // 2^20
-                    // value = 2^24*lo + 2^20*hi - 8*sum(a)
                     tot[0] = fmaf(s0, fmaf(fmaf(lo[0], 16.0f, hi[0]), k20, a8.x), tot[0]);
                     tot[1] = fmaf(s0, fmaf(fmaf(lo[1], 16.0f, hi[1]), k20, a8.y), tot[1]);
                     tot[2] = fmaf(s1, fmaf(fmaf(lo[2], 16.0f, hi[2]), k20, a8.x), tot[2]);

@@ -81,10 +81,14 @@ twm_status ensure_device(int* sm_count_out)
                 if (r == cudaSuccess)
                     r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(twm::mma::Smem));
             };
-            raise_mma((const void*)twm::mma::gemv_kernel<1>);
-            raise_mma((const void*)twm::mma::gemv_kernel<2>);
-            raise_mma((const void*)twm::mma::gemv_kernel<4>);
-            raise_mma((const void*)twm::mma::gemv_kernel<8>);
+            raise_mma((const void*)twm::mma::gemv_kernel<1, 0>);
+            raise_mma((const void*)twm::mma::gemv_kernel<2, 0>);
+            raise_mma((const void*)twm::mma::gemv_kernel<4, 0>);
+            raise_mma((const void*)twm::mma::gemv_kernel<8, 0>);
+            raise_mma((const void*)twm::mma::gemv_kernel<1, 2>);
+            raise_mma((const void*)twm::mma::gemv_kernel<2, 2>);
+            raise_mma((const void*)twm::mma::gemv_kernel<4, 2>);
+            raise_mma((const void*)twm::mma::gemv_kernel<8, 2>);
             if (r != cudaSuccess) { set_error("cudaFuncSetAttribute", r); st.status = TWM_ELAUNCH; }
         }
         st.ready = true;
@@ -167,11 +171,20 @@ twm_status launch_mma(const twm::GemmParams& p, int mp, dim3 grid, bool pdl, cud
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
     cudaError_t e;
-    switch (mp) {
-        case 1: e = cudaLaunchKernelEx(&cfg, twm::mma::gemv_kernel<1>, p); break;
-        case 2: e = cudaLaunchKernelEx(&cfg, twm::mma::gemv_kernel<2>, p); break;
-        case 4: e = cudaLaunchKernelEx(&cfg, twm::mma::gemv_kernel<4>, p); break;
-        default: e = cudaLaunchKernelEx(&cfg, twm::mma::gemv_kernel<8>, p); break;
+    if (p.group == 128) {
+        switch (mp) {
+            case 1: e = cudaLaunchKernelEx(&cfg, twm::mma::gemv_kernel<1, 2>, p); break;
+            case 2: e = cudaLaunchKernelEx(&cfg, twm::mma::gemv_kernel<2, 2>, p); break;
+            case 4: e = cudaLaunchKernelEx(&cfg, twm::mma::gemv_kernel<4, 2>, p); break;
+            default: e = cudaLaunchKernelEx(&cfg, twm::mma::gemv_kernel<8, 2>, p); break;
+        }
+    } else {
+        switch (mp) {
+            case 1: e = cudaLaunchKernelEx(&cfg, twm::mma::gemv_kernel<1, 0>, p); break;
+            case 2: e = cudaLaunchKernelEx(&cfg, twm::mma::gemv_kernel<2, 0>, p); break;
+            case 4: e = cudaLaunchKernelEx(&cfg, twm::mma::gemv_kernel<4, 0>, p); break;
+            default: e = cudaLaunchKernelEx(&cfg, twm::mma::gemv_kernel<8, 0>, p); break;
+        }
     }
     if (e != cudaSuccess) { set_error("launch mma::gemv_kernel", e); return TWM_ELAUNCH; }
     return TWM_OK;
