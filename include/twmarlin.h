@@ -115,6 +115,29 @@ size_t twm_workspace_bytes(int M, int N, int K, int group_size);
 /* Enqueue one GEMM.  See twm_gemm_args. */
 twm_status twm_gemm_w4a16(const twm_gemm_args* args, void* stream);
 
+/* The same GEMM for hosts that cannot give this library any device memory of its own:
+ * an engine that carves the whole GPU into weights and KV cache at start-up and has no
+ * allocator left to ask, or a plugin slot whose contract forbids allocation calls once
+ * serving has begun.  Such a caller cannot create the split-K workspace twm_gemm_w4a16
+ * wants, so this entry point brings its own: a fixed 8 MiB array (twm_static_ws_capacity())
+ * inside the library's device image, present on every GPU that loads the library for as
+ * long as the process lives.  It has no counterpart in the reference, whose split-K adds
+ * into C with atomics and needs no scratch.
+ *
+ * args->workspace and args->workspace_bytes are ignored; inputs and outputs are the
+ * caller's as before.  The call allocates and frees nothing (no cudaMalloc, no pool).
+ * A shape whose split-K plan needs more than the array holds returns TWM_EWORKSPACE with
+ * the two sizes in twm_last_error().  The first call on each device looks the array's
+ * address up (one cudaGetSymbolAddress with that device current); make that first call
+ * before starting any stream capture.  All calls on a device share the one array and it
+ * keeps the previous call's contents: the counters are cleared on the stream before every
+ * launch, and two calls that can overlap on the GPU (different streams) race on it, so
+ * serialise them. */
+twm_status twm_gemm_w4a16_static_ws(const twm_gemm_args* args, void* stream);
+
+/* Bytes of the built-in scratch array used by twm_gemm_w4a16_static_ws. */
+size_t twm_static_ws_capacity(void);
+
 /* Dequantise to a dense [K,N] row-major matrix, f32 (exact) or f16 (round to
  * nearest even of the f32 product).  Replaces warp_dequantize_q4_0 /
  * dequant_q4_to_f16 (quantize.rs:150-175, 534-618) on the TW-Marlin tensors. */

@@ -44,6 +44,8 @@ SIGNATURES = {
     "twm_plan": (C.c_int, [C.c_int] * 7 + [C.POINTER(Plan)]),
     "twm_workspace_bytes": (C.c_size_t, [C.c_int] * 4),
     "twm_gemm_w4a16": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
+    "twm_gemm_w4a16_static_ws": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
+    "twm_static_ws_capacity": (C.c_size_t, []),
     "twm_dequant": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "twm_quantize_pack": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "twm_fuse_n": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.c_int, C.c_int,

@@ -214,6 +214,38 @@ twm_status launch_simt(const twm::GemmParams& p, int mmax, dim3 grid, bool pdl, 
     return TWM_OK;
 }
 
+// Scratch for twm_gemm_w4a16_static_ws: split-K tile counters (first 16 KB) and FP32
+// partial sums.  It lives in the library's own device image, so every GPU that loads
+// the library carries these 8 MiB until the process exits.
+constexpr size_t kStaticWsBytes = 8u << 20;
+static __device__ __align__(256) unsigned char g_static_ws[kStaticWsBytes];
+
+// Device address of g_static_ws per device.  In host code the array's name is only a
+// handle for the runtime, not a pointer a kernel could use; the real address comes from
+// cudaGetSymbolAddress, asked once per device while that device is current.
+void* g_static_ws_ptr[kMaxDevices] = {nullptr};
+std::mutex g_static_ws_mutex;
+
+twm_status static_ws_address(void** out)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { set_error("cudaGetDevice", e); return TWM_ELAUNCH; }
+    if (dev < 0 || dev >= kMaxDevices) return TWM_EINVAL;
+    std::lock_guard<std::mutex> lock(g_static_ws_mutex);
+    if (g_static_ws_ptr[dev] == nullptr) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_ws);
+        if (e != cudaSuccess || ptr == nullptr) {
+            set_error("cudaGetSymbolAddress(g_static_ws)", e);
+            return TWM_ELAUNCH;
+        }
+        g_static_ws_ptr[dev] = ptr;
+    }
+    *out = g_static_ws_ptr[dev];
+    return TWM_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -329,6 +361,47 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
     }
     return TWM_OK;
 }
+
+twm_status twm_gemm_w4a16_static_ws(const twm_gemm_args* a, void* stream_)
+{
+    if (!a) return TWM_EINVAL;
+    if (!shape_ok(a->M, a->N, a->K, a->group_size)) return TWM_EINVAL;
+    if (!a->a || !a->packed || !a->scales || !a->c) return TWM_EINVAL;
+    if ((a->a_dtype != TWM_F32 && a->a_dtype != TWM_F16) || (a->c_dtype != TWM_F32 && a->c_dtype != TWM_F16))
+        return TWM_EINVAL;
+    int sm_count = kDefaultSms;
+    twm_status st = ensure_device(&sm_count);
+    if (st != TWM_OK) return st;
+    // the same kernel choice and plan twm_gemm_w4a16 will make for these arguments
+    int kernel = a->kernel_override;
+    if (kernel == TWM_KERNEL_AUTO)
+        kernel = (a->a_dtype != TWM_F16) ? TWM_KERNEL_SIMT : (a->M <= 8 ? TWM_KERNEL_MMA : TWM_KERNEL_TC);
+    twm_plan_t pl;
+    st = twm_plan(a->M, a->N, a->K, a->group_size, sm_count, a->splits_override, kernel, &pl);
+    if (st != TWM_OK) return st;
+    if (pl.workspace_bytes > kStaticWsBytes) {
+        snprintf(t_last_error, sizeof(t_last_error),
+                 "twm_gemm_w4a16_static_ws: this shape needs %zu bytes of split-K scratch, the built-in array holds %zu; "
+                 "use twm_gemm_w4a16 with a caller-owned workspace", pl.workspace_bytes, kStaticWsBytes);
+        return TWM_EWORKSPACE;
+    }
+    void* ws = nullptr;
+    st = static_ws_address(&ws);
+    if (st != TWM_OK) return st;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (pl.workspace_bytes > 0) {
+        // The array keeps whatever the last call left.  Partial sums are always written before
+        // they are read; the tile counters must start at zero, so they are cleared here.
+        cudaError_t e = cudaMemsetAsync(ws, 0, (size_t)pl.grid_x * sizeof(unsigned int), stream);
+        if (e != cudaSuccess) { set_error("cudaMemsetAsync(static scratch counters)", e); return TWM_ELAUNCH; }
+    }
+    twm_gemm_args b = *a;
+    b.workspace = ws;
+    b.workspace_bytes = kStaticWsBytes;
+    return twm_gemm_w4a16(&b, stream_);
+}
+
+size_t twm_static_ws_capacity(void) { return kStaticWsBytes; }
 
 twm_status twm_dequant(const uint8_t* packed, const uint16_t* scales, void* out, int out_dtype,
                        int K, int N, int group_size, void* stream_)

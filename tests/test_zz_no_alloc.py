@@ -1,0 +1,75 @@
+"""GPU test of twm_gemm_w4a16_static_ws, the GEMM entry point for hosts that cannot hand this
+library a workspace (all device memory is spoken for at start-up, or allocation calls are off
+limits while serving).  It must give what twm_gemm_w4a16 gives with a caller-owned workspace,
+call after call on the shared built-in scratch array.  Named so that pytest collects it last."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from helpers import rel_err_floored, seeded_activations, seeded_weights
+from tensorwarp_b200 import _lib
+from tensorwarp_b200 import quantize as q
+
+pytestmark = pytest.mark.gpu
+
+TOL_F16 = 1e-2          # the tolerance of the other FP16-output GEMM tests
+
+
+def _args(a, p, s, c, m, n, k, group, ws=None):
+    return _lib.GemmArgs(M=m, N=n, K=k, group_size=group, a_dtype=_lib.TWM_F16, c_dtype=_lib.TWM_F16,
+                         a=a.data_ptr(), lda=k, packed=p.data_ptr(), scales=s.data_ptr(), c=c.data_ptr(), ldc=n,
+                         workspace=ws.ptr if ws is not None else None,
+                         workspace_bytes=ws.nbytes if ws is not None else 0)
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 3584, 4608), (4, 2048, 1000)])
+def test_static_scratch_matches_caller_workspace(m, k, n):
+    lib = _lib.lib()
+    group = 128
+    w = seeded_weights(k, n, 91)
+    packed, scales = oracle.quantize_pack(w, k, n, group)
+    a_np = seeded_activations(m, k, 3)
+    a = torch.from_numpy(a_np).cuda().half()
+    p = torch.from_numpy(packed).cuda()
+    s = torch.from_numpy(scales.view(np.float16)).cuda()
+    assert q.plan(m, n, k, group).splits > 1, "the case must exercise the split-K scratch"
+    stream = torch.cuda.current_stream().cuda_stream
+
+    # the existing entry point, with a workspace the caller allocated
+    ws = q.Workspace(q.workspace_bytes(m, n, k, group))
+    c_ref = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
+    _lib.check(lib.twm_gemm_w4a16(C.byref(_args(a, p, s, c_ref, m, n, k, group, ws)), stream), "twm_gemm_w4a16")
+    torch.cuda.synchronize()
+    ref = c_ref.float().cpu().numpy()
+    assert rel_err_floored(ref, oracle.w4a16_f64(a_np, packed, scales, m, n, k, group)) < TOL_F16
+
+    # the new entry point, twice in a row on the shared array, no workspace passed
+    for call in range(2):
+        c_new = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
+        _lib.check(lib.twm_gemm_w4a16_static_ws(C.byref(_args(a, p, s, c_new, m, n, k, group)), stream),
+                   "twm_gemm_w4a16_static_ws")
+        torch.cuda.synchronize()
+        got = c_new.float().cpu().numpy()
+        assert not np.isnan(got).any(), f"call {call}: some outputs were never written"
+        assert rel_err_floored(got, ref.astype(np.float64)) < TOL_F16, f"call {call}"
+    assert q.device_error() == 0
+
+
+def test_static_scratch_rejects_oversized_plans():
+    """A plan that needs more scratch than the array holds is refused before anything is enqueued."""
+    lib = _lib.lib()
+    cap = lib.twm_static_ws_capacity()
+    m, k, n, group = 8, 8192, 65536, 128
+    need = q.plan(m, n, k, group, splits_override=8).workspace_bytes
+    assert need > cap
+    dummy = torch.zeros(64, dtype=torch.uint8, device="cuda")          # never dereferenced: the call fails first
+    args = _lib.GemmArgs(M=m, N=n, K=k, group_size=group, a_dtype=_lib.TWM_F16, c_dtype=_lib.TWM_F16,
+                         a=dummy.data_ptr(), lda=k, packed=dummy.data_ptr(), scales=dummy.data_ptr(),
+                         c=dummy.data_ptr(), ldc=n, splits_override=8)
+    st = lib.twm_gemm_w4a16_static_ws(C.byref(args), torch.cuda.current_stream().cuda_stream)
+    assert st == _lib.TWM_EWORKSPACE
+    msg = lib.twm_last_error().decode()
+    assert str(cap) in msg and str(need) in msg
