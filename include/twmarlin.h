@@ -99,6 +99,8 @@ typedef struct twm_plan_t {
     int blocks_per_split;/* 32-blocks of K per slice (last slice may be shorter) */
     int grid_x, grid_y;  /* n tiles, splits */
     size_t workspace_bytes;
+    int cluster_reduce;  /* 1: the K slices of a tile run as one thread-block cluster and add up in
+                            distributed shared memory; no workspace is touched */
 } twm_plan_t;
 
 /* Replaces the adaptive split-K arithmetic of quantize.rs:1314-1325, re-derived

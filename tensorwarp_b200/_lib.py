@@ -8,7 +8,8 @@ import ctypes as C
 import os
 
 PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG, "libtwmarlin.so")
+# TWMARLIN_LIB points at another build of the same library (e.g. one compiled with other tuning macros)
+LIB_PATH = os.environ.get("TWMARLIN_LIB", os.path.join(PKG, "libtwmarlin.so"))
 
 TWM_OK, TWM_EINVAL, TWM_EALIGN, TWM_EWORKSPACE, TWM_ELAUNCH, TWM_EARCH, TWM_ETIMEOUT = 0, -1, -2, -3, -4, -5, -6
 TWM_F32, TWM_F16 = 0, 1
@@ -35,7 +36,7 @@ class Plan(C.Structure):
     """``twm_plan_t``."""
     _fields_ = [
         ("kernel", C.c_int), ("n_tile", C.c_int), ("splits", C.c_int), ("blocks_per_split", C.c_int),
-        ("grid_x", C.c_int), ("grid_y", C.c_int), ("workspace_bytes", C.c_size_t),
+        ("grid_x", C.c_int), ("grid_y", C.c_int), ("workspace_bytes", C.c_size_t), ("cluster_reduce", C.c_int),
     ]
 
 

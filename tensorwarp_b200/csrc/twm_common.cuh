@@ -1,6 +1,7 @@
 // twm_common.cuh — PTX wrappers and shared definitions for the sm_100a kernels.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
 #include <stdint.h>
@@ -83,12 +84,43 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, u
         : "memory");
 }
 
+// 2-D tiled TMA load (tensor map in kernel-parameter space), completion counted on `bar`.
+// x is the innermost coordinate in elements of the map's data type; x * element size must
+// be a multiple of 16 bytes.  No multicast.
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
 // ------------------------------------------- programmatic dependent launch --
 __device__ __forceinline__ void pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 __device__ __forceinline__ void pdl_wait_prior_grids() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// ------------------------------------------------- thread-block clusters --
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// address of the same shared-memory location in another CTA of the cluster
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t local_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
+// hardware barrier over every thread of every CTA of the cluster (like __syncthreads, not a spin)
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 // ----------------------------------------------------------- named barrier --
@@ -117,6 +149,25 @@ __device__ __forceinline__ float ld_cg_f32(const float* p) {
     return v;
 }
 
+// Optional cycle accounting per warp role (development builds only: -DTWM_PROF).
+#ifdef TWM_PROF
+__device__ unsigned long long g_prof[64];
+#define PROF_DECL unsigned long long prof_t0 = clock64(), prof_acc[6] = {0, 0, 0, 0, 0, 0}
+#define PROF_BEGIN(t) unsigned long long t = clock64()
+#define PROF_END(t, cat) prof_acc[cat] += clock64() - t
+#define PROF_FLUSH(role)                                                                          \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) {                                        \
+        for (int c_ = 0; c_ < 6; ++c_) atomicAdd(&g_prof[(role) * 8 + c_], prof_acc[c_]);          \
+        atomicAdd(&g_prof[(role) * 8 + 6], clock64() - prof_t0);                                   \
+        atomicAdd(&g_prof[(role) * 8 + 7], 1ull);                                                  \
+    }
+#else
+#define PROF_DECL
+#define PROF_BEGIN(t)
+#define PROF_END(t, cat)
+#define PROF_FLUSH(role)
+#endif
+
 // Launch parameters shared by the GEMM kernels.
 struct GemmParams {
     int M, N, K, group;          // group = scale group size (32 or 128)
@@ -132,10 +183,15 @@ struct GemmParams {
     unsigned int* ws_counters;   // [n_tiles], zero between launches
     int splits;
     int blocks_per_split;
+    int cluster_reduce;          // 1: the K slices of a tile form a thread-block cluster and add up in its leader's shared memory
     int accumulate;
     const uint32_t* packed_offsets;
     const uint32_t* scales_offsets;
     int expert_idx;
+    // Tensor map over `packed` seen as u64 [K/32][2N]: one TMA instruction brings a whole
+    // ring stage (box = 256 u64 x map_rows rows = 128 columns x map_rows 32-blocks).
+    int map_rows;                // 0 = no map (1-D bulk copies per row instead)
+    alignas(64) CUtensorMap packed_map;
 };
 
 }  // namespace twm

@@ -46,25 +46,6 @@
 namespace twm {
 namespace tc {
 
-// Optional cycle accounting per warp role (development builds only: -DTWM_PROF).
-#ifdef TWM_PROF
-__device__ unsigned long long g_prof[64];
-#define PROF_DECL unsigned long long prof_t0 = clock64(), prof_acc[6] = {0, 0, 0, 0, 0, 0}
-#define PROF_BEGIN(t) unsigned long long t = clock64()
-#define PROF_END(t, cat) prof_acc[cat] += clock64() - t
-#define PROF_FLUSH(role)                                                                          \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) {                                        \
-        for (int c_ = 0; c_ < 6; ++c_) atomicAdd(&g_prof[(role) * 8 + c_], prof_acc[c_]);          \
-        atomicAdd(&g_prof[(role) * 8 + 6], clock64() - prof_t0);                                   \
-        atomicAdd(&g_prof[(role) * 8 + 7], 1ull);                                                  \
-    }
-#else
-#define PROF_DECL
-#define PROF_BEGIN(t)
-#define PROF_END(t, cat)
-#define PROF_FLUSH(role)
-#endif
-
 constexpr int NT = 128;               // columns per CTA = MMA M = TMEM lanes
 constexpr int WSTAGE_BLOCKS = 4;      // 32-blocks per ring stage (8 KB)
 constexpr int WSTAGES = 8;            // ring depth: 64 KB in flight per CTA

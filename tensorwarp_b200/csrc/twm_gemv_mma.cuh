@@ -38,19 +38,28 @@ namespace twm {
 namespace mma {
 
 constexpr int NT = 128;          // columns per CTA
-constexpr int SB = 8;            // 32-blocks per ring stage
-constexpr int STAGES = 5;
+#ifndef TWM_MMA_SB
+#define TWM_MMA_SB 8
+#endif
+#ifndef TWM_MMA_STAGES
+#define TWM_MMA_STAGES 4
+#endif
+constexpr int SB = TWM_MMA_SB;            // 32-blocks per ring stage
+constexpr int STAGES = TWM_MMA_STAGES;
 constexpr int CONSUMER_WARPS = 8;
 constexpr int CONSUMERS = CONSUMER_WARPS * 32;
 constexpr int THREADS = CONSUMERS + 64;      // + producer warp + stager warp
 constexpr int B_BUF_BYTES = 4096;            // staged activations per chunk buffer
 constexpr int ASUM_GROUPS = 64;              // scale groups per chunk, at most
+constexpr int MAX_CLUSTER = 16;              // K slices that can add up through distributed shared memory
+constexpr int CLUSTER_ROWS = 2;              // ... for up to this many activation rows
 
 struct Smem {
     alignas(128) uint8_t packed[STAGES][SB * NT * kBlockBytes];
     alignas(128) uint16_t scales[STAGES][SB][NT];
     alignas(128) uint8_t b[2][B_BUF_BYTES];           // [block in chunk][row m < MP][t] x 16 bytes
     alignas(16) float asum8[2][ASUM_GROUPS][8];       // -8 * sum of a group's activations, per row
+    alignas(16) float red[MAX_CLUSTER][CLUSTER_ROWS][NT];   // cluster leader only: one partial tile per K slice
     alignas(8) uint64_t full[STAGES];
     alignas(8) uint64_t empty[STAGES];
     alignas(8) uint64_t b_full[2];
@@ -91,7 +100,7 @@ __device__ __forceinline__ uint16_t lds16_at(uint32_t addr) {
 // MP = activation rows staged (power of two >= M, <= 8); GSHIFT = log2(32-blocks per scale group)
 template <int MP, int GSHIFT>
 __global__ void __launch_bounds__(THREADS, 2)
-gemv_kernel(const GemmParams p)
+gemv_kernel(const __grid_constant__ GemmParams p)
 {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
@@ -122,6 +131,13 @@ gemv_kernel(const GemmParams p)
     pdl_launch_dependents();
     volatile int* abort_flag = &sm.abort_flag;
 
+    float tot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const int g = lane >> 2;
+    const int t = lane & 3;
+    const int wcol = warp * 16;                       // a consumer warp's 16 columns inside the tile
+#ifdef TWM_EXP_NOWAIT
+    if (warp >= CONSUMER_WARPS) return;          // development experiment: consumers run on whatever is in shared memory
+#endif
     if (warp == CONSUMER_WARPS) {
         // ------------------------------------------- producer: packed + scales --
         const uint8_t* packed = p.packed;
@@ -133,13 +149,17 @@ gemv_kernel(const GemmParams p)
         }
         const bool scale_bulk_ok = ((cols & 7) == 0) && ((p.N & 7) == 0) &&
                                    ((reinterpret_cast<uintptr_t>(scales + n0) & 15) == 0);
+        PROF_DECL;
         for (int it = 0; it < n_stages; ++it) {
             const int slot = it % STAGES;
             const int use = it / STAGES;
+            PROF_BEGIN(t0);
             if (use > 0) {
                 const bool got = mbar_wait_bounded(&sm.empty[slot], (use - 1) & 1, abort_flag);
                 if (!__all_sync(0xffffffffu, got)) break;
             }
+            PROF_END(t0, 0);
+            PROF_BEGIN(t1);
             const int bstart = b0 + it * SB;
             const int nb = min(SB, b1 - bstart);
             const int srow_first = bstart >> gshift;
@@ -154,23 +174,30 @@ gemv_kernel(const GemmParams p)
                 }
                 __syncwarp();
             }
+            // A full stage of packed rows is one tiled TMA load (128 columns x SB blocks; columns
+            // past N are zero-filled and still counted).  A ragged last stage, or a launch
+            // without a tensor map, copies row by row, one 1-D bulk copy per lane.
+            const bool tiled = (p.map_rows == SB) && (nb == SB) && (p.packed_offsets == nullptr);
+            if (tiled) tx = (uint32_t)SB * NT * kBlockBytes + (scale_bulk_ok ? (uint32_t)nrows * cols * 2 : 0u);
             if (lane == 0) {
                 mbar_arrive_expect_tx(&sm.full[slot], tx);
-                for (int r = 0; r < nb; ++r)
-                    bulk_g2s(&sm.packed[slot][r * NT * kBlockBytes],
-                             packed + ((size_t)(bstart + r) * p.N + n0) * kBlockBytes,
-                             (uint32_t)cols * kBlockBytes, &sm.full[slot]);
-                if (scale_bulk_ok)
-                    for (int r = 0; r < nrows; ++r)
-                        bulk_g2s(&sm.scales[slot][r][0], scales + (size_t)(srow_first + r) * p.N + n0,
-                                 (uint32_t)cols * 2, &sm.full[slot]);
+                if (tiled) tma_load_2d(&sm.packed[slot][0], &p.packed_map, n0 * 2, bstart, &sm.full[slot]);
             }
             __syncwarp();
+            if (!tiled && lane < nb) {
+                bulk_g2s(&sm.packed[slot][lane * NT * kBlockBytes],
+                         packed + ((size_t)(bstart + lane) * p.N + n0) * kBlockBytes,
+                         (uint32_t)cols * kBlockBytes, &sm.full[slot]);
+            } else if (scale_bulk_ok && lane >= 16 && lane - 16 < nrows) {
+                const int r = lane - 16;
+                bulk_g2s(&sm.scales[slot][r][0], scales + (size_t)(srow_first + r) * p.N + n0,
+                         (uint32_t)cols * 2, &sm.full[slot]);
+            }
+            __syncwarp();
+            PROF_END(t1, 1);
         }
-        return;
-    }
-
-    if (warp == CONSUMER_WARPS + 1) {
+        PROF_FLUSH(0);
+    } else if (warp == CONSUMER_WARPS + 1) {
         // ------------------------------------------------ activation stager --
         // One item = 8 consecutive K of one row, stored as the 16 bytes
         // {k0,k4 | k2,k6 | k1,k5 | k3,k7}: the B fragments of the block's two MMAs.
@@ -254,24 +281,19 @@ gemv_kernel(const GemmParams p)
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.b_full[buf]);
         }
-        return;
-    }
-
+    } else {
     // ---------------------------------------------------------- consumers --
     // K slices hold whole scale groups and a ring stage holds whole groups, so
     // the per-stage work unrolls into straight-line code: per 32-block two
     // 32-bit loads, one 128-bit load, ten integer ops and two MMAs.
-    const int g = lane >> 2;
-    const int t = lane & 3;
-    const int wcol = warp * 16;                       // this warp's 16 columns inside the tile
     constexpr int GB = 1 << GSHIFT;
-    float tot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     const float zero4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     const uint32_t w_base = smem_u32(&sm.packed[0][0]) + wcol * kBlockBytes + lane * 4;
     const uint32_t s_base = smem_u32(&sm.scales[0][0][0]) + (wcol + g) * 2;
     const uint32_t b_base = smem_u32(&sm.b[0][0]) + (g * 4 + t) * 16;
     const uint32_t a8_base = smem_u32(&sm.asum8[0][0][0]) + t * 8;
     bool ok = true;
+    PROF_DECL;
 
     for (int it = 0; it < n_stages; ++it) {
         const int slot = it % STAGES;
@@ -280,15 +302,26 @@ gemv_kernel(const GemmParams p)
         const int chunk = rel0 / CHUNK_BLOCKS;
         const int buf = chunk & 1;
         const int bi0 = rel0 - chunk * CHUNK_BLOCKS;                  // first block of the stage inside the chunk
+#ifndef TWM_EXP_NOWAIT
+        PROF_BEGIN(t0);
         if (ok && bi0 == 0) {
             const bool got = mbar_wait_bounded(&sm.b_full[buf], (chunk >> 1) & 1, abort_flag);
             if (!__all_sync(0xffffffffu, got)) ok = false;
         }
+        PROF_END(t0, 0);
+        PROF_BEGIN(t1);
         if (ok) {
             const bool got = mbar_wait_bounded(&sm.full[slot], (it / STAGES) & 1, abort_flag);
             if (!__all_sync(0xffffffffu, got)) ok = false;
         }
+        PROF_END(t1, 1);
+#endif
+        PROF_BEGIN(t2);
+#ifdef TWM_EXP_NOCOMPUTE
+        if (false) {
+#else
         if (ok) {
+#endif
             const uint32_t w_st = w_base + slot * (SB * NT * kBlockBytes);
             const uint32_t s_st = s_base + slot * (SB * NT * 2);
             const uint32_t b_st = b_base + buf * B_BUF_BYTES + bi0 * (MP * 64);
@@ -326,18 +359,23 @@ gemv_kernel(const GemmParams p)
                 }
             }
         }
+        PROF_END(t2, 2);
+        PROF_BEGIN(t3);
         __syncwarp();
         if (lane == 0) {
             if (ok) mbar_arrive(&sm.empty[slot]);
             const bool chunk_end = ((rel0 + SB) % CHUNK_BLOCKS == 0) || (it == n_stages - 1);
             if (ok && chunk_end) mbar_arrive(&sm.b_empty[buf]);
         }
+        PROF_END(t3, 3);
     }
+    PROF_FLUSH(1);
+
+    }   // consumers
 
     // ----------------------------------------------------- store / split-K --
-    named_bar_sync(1, CONSUMERS);
-    if (*abort_flag) return;                  // a wait expired: leave C untouched, the error word is set
-    // lane (g, t) holds C[m = 2t, 2t+1][n = n0 + wcol + g] and the same rows for column + 8
+    // lane (g, t) of a consumer warp holds C[m = 2t, 2t+1][n = n0 + wcol + g] and the same rows for column + 8
+    const bool consumer = warp < CONSUMER_WARPS;
     const int nA = n0 + wcol + g, nB = nA + 8;
     const int mA = 2 * t, mB = 2 * t + 1;
     auto store_c = [&](int m, int n, float v) {
@@ -353,6 +391,34 @@ gemv_kernel(const GemmParams p)
             cp[off] = v;
         }
     };
+
+    if (p.cluster_reduce) {
+        // The K slices of this tile are the CTAs of one cluster.  Each writes its partial tile
+        // into the leader's shared memory (distributed shared memory store), one cluster
+        // barrier, and the leader adds the slices in slice order: no workspace, no atomics,
+        // the same bits whatever order the slices finish in.  Every thread of every CTA
+        // reaches the barrier (all loops above are bounded).
+        const uint32_t rank = cluster_ctarank();
+        if (consumer && t == 0 && *abort_flag == 0) {
+            const uint32_t base = mapa_shared(smem_u32(&sm.red[rank][0][0]), 0);
+            st_cluster_f32(base + (0 * NT + wcol + g) * 4, tot[0]);
+            st_cluster_f32(base + (1 * NT + wcol + g) * 4, tot[1]);
+            st_cluster_f32(base + (0 * NT + wcol + g + 8) * 4, tot[2]);
+            st_cluster_f32(base + (1 * NT + wcol + g + 8) * 4, tot[3]);
+        }
+        cluster_sync_all();
+        if (rank == 0 && tid < CLUSTER_ROWS * NT && *abort_flag == 0) {
+            const int m = tid / NT, col = tid - m * NT;
+            float s = 0.0f;
+            for (int sp = 0; sp < p.splits; ++sp) s += sm.red[sp][m][col];
+            store_c(m, n0 + col, s);
+        }
+        return;
+    }
+
+    if (!consumer) return;
+    named_bar_sync(1, CONSUMERS);
+    if (*abort_flag) return;                  // a wait expired: leave C untouched, the error word is set
     if (p.splits == 1) {
         store_c(mA, nA, tot[0]); store_c(mB, nA, tot[1]); store_c(mA, nB, tot[2]); store_c(mB, nB, tot[3]);
         return;

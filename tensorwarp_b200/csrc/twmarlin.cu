@@ -80,6 +80,8 @@ twm_status ensure_device(int* sm_count_out)
             auto raise_mma = [&](const void* fn) {
                 if (r == cudaSuccess)
                     r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(twm::mma::Smem));
+                if (r == cudaSuccess)      // clusters of up to 16 K slices
+                    r = cudaFuncSetAttribute(fn, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
             };
             raise_mma((const void*)twm::mma::gemv_kernel<1, 0>);
             raise_mma((const void*)twm::mma::gemv_kernel<2, 0>);
@@ -97,6 +99,38 @@ twm_status ensure_device(int* sm_count_out)
     return st.status;
 }
 
+// cuTensorMapEncodeTiled, fetched from the driver once (the library links the runtime only).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode_tiled()
+{
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<EncodeTiledFn>(ptr);
+    }();
+    return fn;
+}
+
+// Tensor map over packed viewed as u64 [K/32 rows][2N]: box = 256 u64 (128 columns) x `rows`.
+// Returns false when the map cannot be made (the kernels then copy row by row).
+bool make_packed_map(CUtensorMap* map, const uint8_t* packed, int N, int nkb, int rows)
+{
+    EncodeTiledFn enc = get_encode_tiled();
+    if (!enc) return false;
+    const cuuint64_t gdim[2] = {(cuuint64_t)N * 2, (cuuint64_t)nkb};
+    const cuuint64_t gstride[1] = {(cuuint64_t)N * 16};
+    const cuuint32_t box[2] = {256, (cuuint32_t)rows};
+    const cuuint32_t estride[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t*>(packed), gdim, gstride, box, estride,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 bool shape_ok(int M, int N, int K, int G)
 {
     return M >= 1 && N >= 1 && K >= 32 && (G == 32 || G == 128) && (K % G) == 0 && (K % 32) == 0 &&
@@ -108,11 +142,15 @@ bool shape_ok(int M, int N, int K, int G)
 // fixed start-up (barrier init, activation staging, warp reduce) worth about
 // 16 such blocks, and a split tile pays the last-arriver's pass over the
 // partials.  `slots` = CTAs that can be resident at once.
-void choose_splits(int n_tiles, int nkb, int slots, int max_bps, int align, int* splits, int* bps)
+// `cluster` = the slices of a tile will be launched as one thread-block cluster.  A cluster
+// lives inside one GPC (8 GPCs share the SMs), so a slice count that does not pack into a
+// GPC's CTA slots costs a second wave: that is counted here.
+void choose_splits(int n_tiles, int nkb, int slots, int max_bps, int align, int max_splits, bool cluster,
+                   int* splits, int* bps)
 {
     double best = 1e30;
     int best_s = 1, best_bps = nkb;
-    const int smax = std::min(kMaxSplits, nkb);
+    const int smax = std::min(max_splits, nkb);
     for (int s = 1; s <= smax; ++s) {
         int b = (nkb + s - 1) / s;
         b = (b + align - 1) / align * align;     // slices of whole scale groups where the kernel wants them
@@ -120,7 +158,13 @@ void choose_splits(int n_tiles, int nkb, int slots, int max_bps, int align, int*
         const int s_eff = (nkb + b - 1) / b;
         if (s_eff != s) continue;   // same slicing as a smaller s
         const long ctas = (long)n_tiles * s_eff;
-        const long waves = (ctas + slots - 1) / slots;
+        long waves = (ctas + slots - 1) / slots;
+        if (cluster && s_eff > 1) {
+            const int slots_per_gpc = slots / 8;
+            const long resident_clusters = 8L * (slots_per_gpc / s_eff);
+            if (resident_clusters == 0) continue;
+            waves = std::max(waves, ((long)n_tiles + resident_clusters - 1) / resident_clusters);
+        }
         double cost = (double)waves * (b + 16.0);
         if (s_eff > 1) cost += 10.0 + 0.25 * s_eff;
         if (cost < best - 1e-9) { best = cost; best_s = s_eff; best_bps = b; }
@@ -165,11 +209,22 @@ twm_status launch_mma(const twm::GemmParams& p, int mp, dim3 grid, bool pdl, cud
     cfg.blockDim = dim3(twm::mma::THREADS, 1, 1);
     cfg.dynamicSmemBytes = sizeof(twm::mma::Smem);
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (p.cluster_reduce) {          // the K slices of one tile (grid y) form one cluster
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1;
+        attr[na].val.clusterDim.y = grid.y;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
+    cfg.numAttrs = na;
     cudaError_t e;
     if (p.group == 128) {
         switch (mp) {
@@ -266,6 +321,8 @@ twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int split
     const int slots = sm_count * ((kernel != TWM_KERNEL_SIMT || mmax_for(rows) <= 4) ? 2 : 1);
     const int max_bps = kernel == TWM_KERNEL_TC ? twm::tc::ASUM_CAP / mv_for(rows) : nkb;
     const int align = (kernel == TWM_KERNEL_MMA) ? group_size / 32 : 1;   // whole scale groups per slice
+    // up to two rows on the streaming MMA kernel: K slices add up inside a cluster (at most 16 slices)
+    const bool can_cluster = (kernel == TWM_KERNEL_MMA) && rows <= twm::mma::CLUSTER_ROWS;
     int splits, bps;
     if (splits_override > 0) {
         bps = (nkb + splits_override - 1) / splits_override;
@@ -273,16 +330,19 @@ twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int split
         if (bps > max_bps) return TWM_EINVAL;
         splits = (nkb + bps - 1) / bps;
     } else {
-        choose_splits(n_tiles, nkb, slots, max_bps, align, &splits, &bps);
+        choose_splits(n_tiles, nkb, slots, max_bps, align, can_cluster ? twm::mma::MAX_CLUSTER : kMaxSplits,
+                      can_cluster, &splits, &bps);
         if (bps > max_bps) return TWM_EINVAL;
     }
+    const bool cluster = can_cluster && splits > 1 && splits <= twm::mma::MAX_CLUSTER;
     out->kernel = kernel;
     out->n_tile = twm::simt::NT;
     out->splits = splits;
     out->blocks_per_split = bps;
     out->grid_x = n_tiles;
     out->grid_y = splits;
-    out->workspace_bytes = splits > 1 ? kCounterBytes + (size_t)splits * rows * N * sizeof(float) : 0;
+    out->workspace_bytes = (splits > 1 && !cluster) ? kCounterBytes + (size_t)splits * rows * N * sizeof(float) : 0;
+    out->cluster_reduce = cluster ? 1 : 0;
     return TWM_OK;
 }
 
@@ -336,6 +396,11 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
     const size_t a_elt = a->a_dtype == TWM_F16 ? 2 : 4;
     const size_t c_elt = a->c_dtype == TWM_F16 ? 2 : 4;
     const int row_step = kernel == TWM_KERNEL_TC ? 16 : 8;
+    CUtensorMap packed_map;
+    int map_rows = 0;
+    if (kernel == TWM_KERNEL_MMA && a->packed_offsets == nullptr && a->N >= 128 &&
+        make_packed_map(&packed_map, a->packed, a->N, a->K / 32, twm::mma::SB))
+        map_rows = twm::mma::SB;
     for (int m0 = 0; m0 < a->M; m0 += row_step) {
         const int rows = std::min(row_step, a->M - m0);
         twm::GemmParams p;
@@ -348,8 +413,11 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
         p.ws_counters = (unsigned int*)a->workspace;
         p.ws_partials = a->workspace ? (float*)((char*)a->workspace + kCounterBytes) : nullptr;
         p.splits = pl.splits; p.blocks_per_split = pl.blocks_per_split;
+        p.cluster_reduce = (pl.cluster_reduce && rows <= twm::mma::CLUSTER_ROWS) ? 1 : 0;
         p.accumulate = (a->flags & TWM_FLAG_ACCUMULATE) ? 1 : 0;
         p.packed_offsets = a->packed_offsets; p.scales_offsets = a->scales_offsets; p.expert_idx = a->expert_idx;
+        p.map_rows = map_rows;
+        if (map_rows) p.packed_map = packed_map;
         const bool pdl = (a->flags & TWM_FLAG_PDL) != 0;
         if (kernel == TWM_KERNEL_TC)
             st = launch_tc(p, mv_for(rows), dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
@@ -533,8 +601,8 @@ int twm_prof_read(unsigned long long* out)
 {
     cudaDeviceSynchronize();
     unsigned long long zero[64] = {0};
-    if (cudaMemcpyFromSymbol(out, twm::tc::g_prof, sizeof(zero)) != cudaSuccess) return -1;
-    cudaMemcpyToSymbol(twm::tc::g_prof, zero, sizeof(zero));
+    if (cudaMemcpyFromSymbol(out, twm::g_prof, sizeof(zero)) != cudaSuccess) return -1;
+    cudaMemcpyToSymbol(twm::g_prof, zero, sizeof(zero));
     return 0;
 }
 #endif

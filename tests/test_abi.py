@@ -43,11 +43,16 @@ def test_plan_benchmark_shapes(twm_lib):
     assert st == 0 and p.splits == 1 and p.grid_x == 296 and p.workspace_bytes == 0
     # small-N shapes must split to cover the machine (the reference's k<2048 cut-off is not inherited)
     for (n, k) in ((4608, 3584), (3584, 3584), (3584, 18944), (9728, 896)):
+        # M=1 on the streaming MMA kernel: the slices of a tile form a cluster, no workspace
         st, p = _plan(twm_lib, 1, n, k, 128, 148, 0, 0)
         assert st == 0
-        assert p.splits > 1, (n, k)
-        assert 148 <= p.grid_x * p.grid_y <= 2 * 148, (n, k, p.grid_x, p.grid_y)
+        assert 1 < p.splits <= 16 and p.cluster_reduce == 1 and p.workspace_bytes == 0, (n, k)
+        assert 100 <= p.grid_x * p.grid_y <= 2 * 148, (n, k, p.grid_x, p.grid_y)
         assert p.blocks_per_split * p.splits >= k // 32 > p.blocks_per_split * (p.splits - 1)
+        assert p.blocks_per_split % 4 == 0          # whole 128-groups per slice
+        # the FP32 kernel (the reference's f32 signature) splits through the workspace
+        st, p = _plan(twm_lib, 1, n, k, 128, 148, 0, _lib.TWM_KERNEL_SIMT)
+        assert st == 0 and p.splits > 1 and p.cluster_reduce == 0
         assert p.workspace_bytes == 16384 + p.splits * n * 4
         assert twm_lib.twm_workspace_bytes(1, n, k, 128) >= p.workspace_bytes
     # deterministic

@@ -318,13 +318,19 @@ def test_accumulate_flag_and_strides():
 
 def test_errors_are_statuses():
     k, n = 3584, 3584
-    a = torch.zeros(k, dtype=torch.float16, device=DEV)
+    a = torch.zeros(k, dtype=torch.float32, device=DEV)
     p = torch.zeros((k // 32, n, 16), dtype=torch.uint8, device=DEV)
     s = torch.zeros((k // 128, n), dtype=torch.float16, device=DEV)
-    c = torch.zeros(n, dtype=torch.float16, device=DEV)
+    c = torch.zeros(n, dtype=torch.float32, device=DEV)
     with pytest.raises(_lib.TwmError) as e:
-        q.gemm_tw_marlin_m1(a, p, s, c, n, k, group_size=128, workspace=None)     # this shape splits
+        q.gemm_tw_marlin_m1(a, p, s, c, n, k, group_size=128, workspace=None)     # the FP32 kernel splits through a workspace
     assert e.value.status == _lib.TWM_EWORKSPACE
     with pytest.raises(_lib.TwmError) as e:
         q.gemm_tw_marlin_m1(a, p, s, c, n, k - 16, group_size=128)
     assert e.value.status == _lib.TWM_EINVAL
+    # FP16 activations, one row: the slices add up inside a cluster, no workspace needed
+    a16 = torch.zeros(k, dtype=torch.float16, device=DEV)
+    c16 = torch.ones(n, dtype=torch.float16, device=DEV)
+    q.gemm_tw_marlin_m1(a16, p, s, c16, n, k, group_size=128, workspace=None)
+    torch.cuda.synchronize()
+    assert torch.all(c16 == 0)
