@@ -211,6 +211,11 @@ def run_ours(args):
     err = q.device_error(stream)
     if err:
         raise RuntimeError(f"device error word {err:#x}")
+    decode = None
+    if not args.no_decode and rank == 0:
+        del weights, graph
+        torch.cuda.empty_cache()
+        decode = decode_tok_s(torch, device)
 
     step_bytes = LAYERS * layer_bytes(m)
     ms_per_step = ms / args.steps
@@ -238,12 +243,50 @@ def run_ours(args):
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks.summary(),
     }
+    if decode is not None:
+        line["decode"] = decode
     if rank == 0:
         if not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(target_seconds=12.0)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def decode_tok_s(torch, device, new_tokens: int = 64, kv_len: int = 2048):
+    """configs[3]: full Qwen2-7B-shaped Q4 decode step (28 layers, FP16 KV prefilled to 2048 tokens of
+    N(0,1), FP16 LM head, greedy) replayed as one CUDA graph; the token never leaves the device."""
+    from tensorwarp_b200 import generate as gen
+    cfg = gen.QWEN2_7B
+    model = gen.Q4Model(cfg, device=device, seed=0)
+    eng = gen.QuantizedGenerationEngine(model)
+    eng.prefill_random_kv(kv_len, seed=2)
+    first = int(torch.randint(0, cfg.vocab, (1,), generator=torch.Generator().manual_seed(3)).item())
+    eng.capture()
+    eng.set_token(first)
+    for _ in range(3):
+        eng.replay()
+    torch.cuda.synchronize()
+    eng.prefill_random_kv(kv_len, seed=2)          # back to position 2048
+    eng.buf.step.zero_()
+    eng.set_token(first)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(eng.stream):
+        e0.record(eng.stream)
+        for _ in range(new_tokens):
+            eng.replay()
+        e1.record(eng.stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    toks = eng.buf.history[:new_tokens].tolist()
+    q4_bytes = cfg.layers * layer_bytes(1)
+    step_bytes = q4_bytes + cfg.vocab * cfg.hidden * 2 + cfg.layers * 2 * (kv_len + new_tokens // 2) * cfg.kv_dim * 2
+    return {"tok_s": round(new_tokens / (ms * 1e-3), 1), "ms_per_token": round(ms / new_tokens, 4),
+            "workload": f"configs[3]: Qwen2-7B-shaped Q4 decode, KV {kv_len} FP16, {new_tokens} greedy tokens, one CUDA graph per token",
+            "launches_per_token": eng.launches_per_step, "bytes_per_token": int(step_bytes),
+            "hbm_gbs": round(step_bytes / (ms / new_tokens * 1e-3) / 1e9, 1),
+            "tokens_in_vocab": bool(all(0 <= t < cfg.vocab for t in toks))}
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, averaged over one layer's four kernels,
@@ -330,6 +373,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-decode", action="store_true", help="skip the configs[3] decode tok/s measurement")
     args = ap.parse_args()
     if args.impl == "reference":
         args.steps = args.steps if args.steps is not None else 5

@@ -168,6 +168,16 @@ __device__ unsigned long long g_prof[64];
 #define PROF_FLUSH(role)
 #endif
 
+#ifdef TWM_TIMELINE
+// development builds only: per-CTA wall-clock marks (globaltimer, ns) of the last launches
+__device__ unsigned long long g_timeline[64 * 512 * 4];
+__device__ unsigned int g_timeline_launch;
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define TL_MARK(launch, idx) if (threadIdx.x == 0 && (launch) < 64) g_timeline[(((launch) * 512) + blockIdx.y * gridDim.x + blockIdx.x) * 4 + (idx)] = gtime()
+#else
+#define TL_MARK(launch, idx)
+#endif
+
 // Launch parameters shared by the GEMM kernels.
 struct GemmParams {
     int M, N, K, group;          // group = scale group size (32 or 128)
@@ -191,6 +201,7 @@ struct GemmParams {
     // Tensor map over `packed` seen as u64 [K/32][2N]: one TMA instruction brings a whole
     // ring stage (box = 256 u64 x map_rows rows = 128 columns x map_rows 32-blocks).
     int map_rows;                // 0 = no map (1-D bulk copies per row instead)
+    int launch_id;               // development builds: index of this launch in the timeline buffer
     alignas(64) CUtensorMap packed_map;
 };
 

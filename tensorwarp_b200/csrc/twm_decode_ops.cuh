@@ -1,0 +1,367 @@
+// twm_decode_ops.cuh — the small kernels either side of the W4A16 GEMMs in one decode step:
+// embedding row, RMSNorm, bias + RoPE + KV append, split-KV decode attention, SwiGLU,
+// FP16 LM head, arg-max.  They exist so that a whole decode step can be captured in one CUDA
+// graph with device-side position/length buffers; the arithmetic follows the reference's
+// kernels of the same role (cited at each kernel), with FP16 storage where the benchmark
+// configuration states FP16 (KV cache, LM head, GEMM inputs) and FP32 for the residual stream.
+//
+// All kernels take part in programmatic dependent launch: they let their dependents start
+// early and wait for the preceding kernel before touching memory.
+#pragma once
+
+#include "twm_common.cuh"
+
+namespace twm {
+namespace ops {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// x[row][h] (f32) = table[token[row]][h] (f16).  Reference: warp_embedding,
+// crates/kernels/src/sampling.rs:16-32 (f32 table there).
+__global__ void __launch_bounds__(256)
+embed_kernel(float* __restrict__ x, const __half* __restrict__ table, const int* __restrict__ tokens, int hidden)
+{
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    const int row = blockIdx.y;
+    const size_t tok = (size_t)tokens[row];
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < hidden; i += gridDim.x * blockDim.x)
+        x[(size_t)row * hidden + i] = __half2float(table[tok * hidden + i]);
+}
+
+// y = f16(x * rsqrt(mean(x^2) + eps) * gamma), one CTA per row.  Reference: warp_rmsnorm,
+// crates/kernels/src/ops.rs:302-336 (one warp per row there; here 256 threads and a fixed-order
+// two-level sum).  With `add` the kernel first does x += add (and stops there when y is null).
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(__half* __restrict__ y, float* __restrict__ x, const float* __restrict__ add,
+               const float* __restrict__ gamma, int hidden, float eps)
+{
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    __shared__ float partial[8];
+    const int row = blockIdx.x;
+    float* xr = x + (size_t)row * hidden;
+    float ss = 0.0f;
+    if (add != nullptr) {
+        // x += add first (fused_residual_rmsnorm, ops.rs:928-962): the all-reduced output of a
+        // row-parallel GEMM joins the residual stream here
+        const float* ar = add + (size_t)row * hidden;
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) { const float v = xr[i] + ar[i]; xr[i] = v; ss = fmaf(v, v, ss); }
+        if (y == nullptr) return;
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) { const float v = xr[i]; ss = fmaf(v, v, ss); }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) tot += partial[w];
+    const float rms = rsqrtf(tot / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+        y[(size_t)row * hidden + i] = __float2half_rn(xr[i] * rms * gamma[i]);
+}
+
+// q/k bias + rotate-half RoPE, v bias, append k and v at position pos_buf[0].  Reference:
+// warp_fused_bias_rope_append_dp, crates/kernels/src/ops.rs:2601-2650 (same formulas: freq =
+// 1/powf(base, 2*pair/head_dim), theta = pos*freq).  qkv is the fused GEMM output
+// [q | k | v] (so no separate split_qkv pass, ops.rs:2255-2298); caches are f16
+// [max_seq][kv_dim].
+__global__ void __launch_bounds__(256)
+rope_append_kernel(__half* __restrict__ q_out, __half* __restrict__ k_cache, __half* __restrict__ v_cache,
+                   const __half* __restrict__ qkv, const float* __restrict__ bias /* [q|k|v] or null */,
+                   int num_heads, int num_kv_heads, int head_dim, const int* __restrict__ pos_buf, int max_seq,
+                   float rope_base)
+{
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    const int pos = pos_buf[0];
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    const int q_total = num_heads * head_dim;
+    const int kv_dim = num_kv_heads * head_dim;
+    const int half_d = head_dim / 2;
+    // one sequence per grid row: its own q, its own cache, the shared position
+    const size_t row = blockIdx.y;
+    qkv += row * (size_t)(q_total + 2 * kv_dim);
+    q_out += row * (size_t)q_total;
+    k_cache += row * (size_t)max_seq * kv_dim;
+    v_cache += row * (size_t)max_seq * kv_dim;
+    if (idx < q_total + kv_dim) {
+        const bool is_q = idx < q_total;
+        const int local = is_q ? idx : idx - q_total;          // index inside q or inside k
+        const int head = local / head_dim;
+        const int d = local - head * head_dim;
+        const int pair = d % half_d;
+        const float freq = 1.0f / powf(rope_base, 2.0f * (float)pair / (float)head_dim);
+        const float theta = (float)pos * freq;
+        const float cos_t = cosf(theta), sin_t = sinf(theta);
+        const int src0 = (is_q ? 0 : q_total) + head * head_dim + pair;
+        float x0 = __half2float(qkv[src0]), x1 = __half2float(qkv[src0 + half_d]);
+        if (bias) { x0 += bias[src0]; x1 += bias[src0 + half_d]; }
+        const float r = (d < half_d) ? x0 * cos_t - x1 * sin_t : x0 * sin_t + x1 * cos_t;
+        if (is_q) q_out[local] = __float2half_rn(r);
+        else if (pos < max_seq) k_cache[(size_t)pos * kv_dim + local] = __float2half_rn(r);
+    }
+    if (idx < kv_dim) {
+        const int src = q_total + kv_dim + idx;
+        float v = __half2float(qkv[src]);
+        if (bias) v += bias[src];
+        if (pos < max_seq) v_cache[(size_t)pos * kv_dim + idx] = __float2half_rn(v);
+    }
+}
+
+// Split-KV decode attention, pass 1.  CTA = (chunk of 128 tokens, kv head); its 8 warps share
+// the kv head's K/V rows between all q heads of the group (GQA), so the cache is read once.
+// Online soft-max per warp, merged through shared memory; writes (max, sum, unnormalised o[128])
+// per (q head, chunk).  The sequence length is read from the device (len_buf[0]), the grid
+// covers max_seq.  Reference: warp_flash_decode_chunk_dl, crates/kernels/src/kv_cache.rs:951-1076.
+constexpr int ATT_CHUNK = 128;
+constexpr int ATT_MAX_GROUP = 8;      // q heads per kv head, at most
+
+template <int HEAD_DIM>
+__global__ void __launch_bounds__(256)
+attn_chunk_kernel(float* __restrict__ part /* [heads][chunks][HEAD_DIM + 2] */, const __half* __restrict__ q,
+                  const __half* __restrict__ k_cache, const __half* __restrict__ v_cache, int num_heads,
+                  int num_kv_heads, const int* __restrict__ len_buf, int max_chunks, int max_seq)
+{
+    static_assert(HEAD_DIM == 128, "lane owns 4 of 128 dims");
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    const int chunk = blockIdx.x, kvh = blockIdx.y;
+    {   // one sequence per grid z: its own q, cache and partials
+        const size_t row = blockIdx.z;
+        q += row * (size_t)num_heads * HEAD_DIM;
+        k_cache += row * (size_t)max_seq * num_kv_heads * HEAD_DIM;
+        v_cache += row * (size_t)max_seq * num_kv_heads * HEAD_DIM;
+        part += row * (size_t)num_heads * max_chunks * (HEAD_DIM + 2);
+    }
+    const int len = len_buf[0];
+    const int t0 = chunk * ATT_CHUNK;
+    const int group = num_heads / num_kv_heads;
+    const int kv_dim = num_kv_heads * HEAD_DIM;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __shared__ float s_m[8][ATT_MAX_GROUP], s_l[8][ATT_MAX_GROUP];
+    __shared__ float s_o[8][ATT_MAX_GROUP][HEAD_DIM];
+    if (t0 >= len) {
+        // empty chunk: mark as such so the merge ignores it
+        if (threadIdx.x < group) {
+            float* dst = part + ((size_t)(kvh * group + threadIdx.x) * max_chunks + chunk) * (HEAD_DIM + 2);
+            dst[HEAD_DIM] = -INFINITY; dst[HEAD_DIM + 1] = 0.0f;
+        }
+        return;
+    }
+    const int t1 = min(len, t0 + ATT_CHUNK);
+    const float scale = rsqrtf((float)HEAD_DIM);
+    float qv[ATT_MAX_GROUP][4];
+#pragma unroll
+    for (int h = 0; h < ATT_MAX_GROUP; ++h) {
+        if (h < group) {
+            const __half2* qp = reinterpret_cast<const __half2*>(q + (size_t)(kvh * group + h) * HEAD_DIM + lane * 4);
+            const float2 a = __half22float2(qp[0]), b = __half22float2(qp[1]);
+            qv[h][0] = a.x * scale; qv[h][1] = a.y * scale; qv[h][2] = b.x * scale; qv[h][3] = b.y * scale;
+        } else { qv[h][0] = qv[h][1] = qv[h][2] = qv[h][3] = 0.0f; }
+    }
+    float m[ATT_MAX_GROUP], l[ATT_MAX_GROUP], o[ATT_MAX_GROUP][4];
+#pragma unroll
+    for (int h = 0; h < ATT_MAX_GROUP; ++h) { m[h] = -INFINITY; l[h] = 0.0f; o[h][0] = o[h][1] = o[h][2] = o[h][3] = 0.0f; }
+    for (int tk = t0 + warp; tk < t1; tk += 8) {
+        const __half2* kp = reinterpret_cast<const __half2*>(k_cache + (size_t)tk * kv_dim + kvh * HEAD_DIM + lane * 4);
+        const __half2* vp = reinterpret_cast<const __half2*>(v_cache + (size_t)tk * kv_dim + kvh * HEAD_DIM + lane * 4);
+        const float2 k0 = __half22float2(kp[0]), k1 = __half22float2(kp[1]);
+        const float2 v0 = __half22float2(vp[0]), v1 = __half22float2(vp[1]);
+#pragma unroll
+        for (int h = 0; h < ATT_MAX_GROUP; ++h) {
+            if (h < group) {
+                float s = qv[h][0] * k0.x + qv[h][1] * k0.y + qv[h][2] * k1.x + qv[h][3] * k1.y;
+                s = warp_sum(s);
+                const float mn = fmaxf(m[h], s);
+                const float corr = __expf(m[h] - mn), pexp = __expf(s - mn);
+                l[h] = l[h] * corr + pexp;
+                o[h][0] = o[h][0] * corr + pexp * v0.x; o[h][1] = o[h][1] * corr + pexp * v0.y;
+                o[h][2] = o[h][2] * corr + pexp * v1.x; o[h][3] = o[h][3] * corr + pexp * v1.y;
+                m[h] = mn;
+            }
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < ATT_MAX_GROUP; ++h) {
+        if (h < group) {
+            if (lane == 0) { s_m[warp][h] = m[h]; s_l[warp][h] = l[h]; }
+            s_o[warp][h][lane * 4 + 0] = o[h][0]; s_o[warp][h][lane * 4 + 1] = o[h][1];
+            s_o[warp][h][lane * 4 + 2] = o[h][2]; s_o[warp][h][lane * 4 + 3] = o[h][3];
+        }
+    }
+    __syncthreads();
+    // merge the 8 warps, fixed order; thread = (q head of the group, dim)
+    for (int idx = threadIdx.x; idx < group * HEAD_DIM; idx += blockDim.x) {
+        const int h = idx / HEAD_DIM, d = idx - h * HEAD_DIM;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) mm = fmaxf(mm, s_m[w][h]);
+        float ll = 0.0f, oo = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            const float c = (s_m[w][h] == -INFINITY) ? 0.0f : __expf(s_m[w][h] - mm);
+            ll += s_l[w][h] * c;
+            oo += s_o[w][h][d] * c;
+        }
+        float* dst = part + ((size_t)(kvh * group + h) * max_chunks + chunk) * (HEAD_DIM + 2);
+        dst[d] = oo;
+        if (d == 0) { dst[HEAD_DIM] = mm; dst[HEAD_DIM + 1] = ll; }
+    }
+}
+
+// Pass 2: merge the chunks of one q head (log-sum-exp weights), write f16.  Reference:
+// warp_flash_decode_reduce, crates/kernels/src/kv_cache.rs:790-841.
+template <int HEAD_DIM>
+__global__ void __launch_bounds__(HEAD_DIM)
+attn_merge_kernel(__half* __restrict__ out, const float* __restrict__ part, const int* __restrict__ len_buf,
+                  int max_chunks)
+{
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    const int head = blockIdx.x, d = threadIdx.x;
+    out += (size_t)blockIdx.y * gridDim.x * HEAD_DIM;
+    part += (size_t)blockIdx.y * gridDim.x * max_chunks * (HEAD_DIM + 2);
+    const int chunks = min(max_chunks, (len_buf[0] + ATT_CHUNK - 1) / ATT_CHUNK);
+    const float* base = part + (size_t)head * max_chunks * (HEAD_DIM + 2);
+    float mm = -INFINITY;
+    for (int c = 0; c < chunks; ++c) mm = fmaxf(mm, base[(size_t)c * (HEAD_DIM + 2) + HEAD_DIM]);
+    float ll = 0.0f, oo = 0.0f;
+    for (int c = 0; c < chunks; ++c) {
+        const float* pc = base + (size_t)c * (HEAD_DIM + 2);
+        const float w = (pc[HEAD_DIM] == -INFINITY) ? 0.0f : __expf(pc[HEAD_DIM] - mm);
+        ll += pc[HEAD_DIM + 1] * w;
+        oo += pc[d] * w;
+    }
+    out[(size_t)head * HEAD_DIM + d] = __float2half_rn(ll > 0.0f ? oo / ll : 0.0f);
+}
+
+// act = silu(gate) * up on the fused gate+up GEMM output [gate | up] (no split_gate_up pass).
+// Reference: warp_fused_silu_mul, crates/kernels/src/ops.rs:966-977 (g / (1 + expf(-g)) * up).
+__global__ void __launch_bounds__(256)
+silu_mul_kernel(__half* __restrict__ act, const __half* __restrict__ gate_up, int ffn, int rows)
+{
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < ffn * rows) {
+        const int r = i / ffn, c = i - r * ffn;
+        const float g = __half2float(gate_up[(size_t)r * 2 * ffn + c]);
+        const float u = __half2float(gate_up[(size_t)r * 2 * ffn + ffn + c]);
+        act[i] = __float2half_rn(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+// FP16 LM head: logits[v] = sum_h x[h] * W[v][h], W row-major f16 [vocab][hidden], FP32
+// accumulate.  One warp per vocabulary row (a row is one contiguous run), 128-bit loads, x in
+// shared memory.  Reference: the LM head is a cuBLAS SGEMM outside the graph
+// (crates/kernels/src/generate.rs:1727-1735); warp_hgemm_m1 (quantize.rs:3682-3716) is the
+// in-tree FP16 GEMV of the same shape.
+__global__ void __launch_bounds__(256)
+lm_head_kernel(float* __restrict__ logits, const __half* __restrict__ x, const __half* __restrict__ w, int hidden,
+               int vocab)
+{
+    pdl_launch_dependents();
+    extern __shared__ __align__(16) uint8_t lm_smem[];
+    __half* xs = reinterpret_cast<__half*>(lm_smem);
+    pdl_wait_prior_grids();
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs[i] = x[i];
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warps_total = gridDim.x * (blockDim.x >> 5);
+    for (int v = blockIdx.x * (blockDim.x >> 5) + warp; v < vocab; v += warps_total) {
+        const uint4* wr = reinterpret_cast<const uint4*>(w + (size_t)v * hidden);
+        const uint4* xr = reinterpret_cast<const uint4*>(xs);
+        float acc = 0.0f;
+        for (int i = lane; i < hidden / 8; i += 32) {
+            const uint4 a = __ldg(wr + i);
+            const uint4 b = xr[i];
+            const __half2* ah = reinterpret_cast<const __half2*>(&a);
+            const __half2* bh = reinterpret_cast<const __half2*>(&b);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 fa = __half22float2(ah[j]), fb = __half22float2(bh[j]);
+                acc = fmaf(fa.x, fb.x, acc);
+                acc = fmaf(fa.y, fb.y, acc);
+            }
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) logits[v] = acc;
+    }
+}
+
+// arg-max with ties to the smallest index, two passes.  Reference: CPU sampling over the full
+// logits after a D2H copy (crates/kernels/src/generate.rs:68-169, 2531-2534); here it stays on
+// the device so the next token never leaves the GPU.
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(float* __restrict__ pval, int* __restrict__ pidx, const float* __restrict__ logits, int n)
+{
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const float v = logits[i];
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+    __shared__ float sv[256];
+    __shared__ int si[256];
+    sv[threadIdx.x] = best; si[threadIdx.x] = bi;
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) {
+        if (threadIdx.x < s) {
+            const float v = sv[threadIdx.x + s]; const int i = si[threadIdx.x + s];
+            if (v > sv[threadIdx.x] || (v == sv[threadIdx.x] && i < si[threadIdx.x])) { sv[threadIdx.x] = v; si[threadIdx.x] = i; }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) { pval[blockIdx.x] = sv[0]; pidx[blockIdx.x] = si[0]; }
+}
+
+// Final pass; also advances the device-side position / length buffers for the next step and
+// appends the token to the output list, so a replayed graph needs no host input at all.
+__global__ void __launch_bounds__(256)
+argmax_final_kernel(int* __restrict__ token_out, int* __restrict__ history, int* __restrict__ pos_buf,
+                    int* __restrict__ len_buf, int* __restrict__ step_buf, const float* __restrict__ pval,
+                    const int* __restrict__ pidx, int nparts)
+{
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    __shared__ float sv[256];
+    __shared__ int si[256];
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < nparts; i += blockDim.x) {
+        const float v = pval[i]; const int ix = pidx[i];
+        if (v > best || (v == best && ix < bi)) { best = v; bi = ix; }
+    }
+    sv[threadIdx.x] = best; si[threadIdx.x] = bi;
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) {
+        if (threadIdx.x < s) {
+            const float v = sv[threadIdx.x + s]; const int i = si[threadIdx.x + s];
+            if (v > sv[threadIdx.x] || (v == sv[threadIdx.x] && i < si[threadIdx.x])) { sv[threadIdx.x] = v; si[threadIdx.x] = i; }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        token_out[0] = si[0];
+        if (history) history[step_buf[0]] = si[0];
+        step_buf[0] += 1;
+        pos_buf[0] += 1;
+        len_buf[0] += 1;
+    }
+}
+
+}  // namespace ops
+}  // namespace twm

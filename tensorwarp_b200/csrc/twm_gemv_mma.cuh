@@ -108,6 +108,7 @@ gemv_kernel(const __grid_constant__ GemmParams p)
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
+    TL_MARK(p.launch_id, 0);
     const int n0 = blockIdx.x * NT;
     const int cols = min(NT, p.N - n0);
     const int b0 = blockIdx.y * p.blocks_per_split;
@@ -287,6 +288,7 @@ gemv_kernel(const __grid_constant__ GemmParams p)
     // the per-stage work unrolls into straight-line code: per 32-block two
     // 32-bit loads, one 128-bit load, ten integer ops and two MMAs.
     constexpr int GB = 1 << GSHIFT;
+    if (warp == 0) { TL_MARK(p.launch_id, 1); }
     const float zero4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     const uint32_t w_base = smem_u32(&sm.packed[0][0]) + wcol * kBlockBytes + lane * 4;
     const uint32_t s_base = smem_u32(&sm.scales[0][0][0]) + (wcol + g) * 2;
@@ -413,6 +415,7 @@ gemv_kernel(const __grid_constant__ GemmParams p)
             for (int sp = 0; sp < p.splits; ++sp) s += sm.red[sp][m][col];
             store_c(m, n0 + col, s);
         }
+        TL_MARK(p.launch_id, 3);
         return;
     }
 
@@ -421,6 +424,7 @@ gemv_kernel(const __grid_constant__ GemmParams p)
     if (*abort_flag) return;                  // a wait expired: leave C untouched, the error word is set
     if (p.splits == 1) {
         store_c(mA, nA, tot[0]); store_c(mB, nA, tot[1]); store_c(mA, nB, tot[2]); store_c(mB, nB, tot[3]);
+        TL_MARK(p.launch_id, 3);
         return;
     }
     auto ws_at = [&](int sp, int m, int n) -> float* { return &p.ws_partials[((size_t)sp * p.M + m) * p.N + n]; };

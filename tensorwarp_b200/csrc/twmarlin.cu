@@ -17,10 +17,15 @@
 #include "twm_gemm_tc.cuh"
 #include "twm_gemv_mma.cuh"
 #include "twm_layout.cuh"
+#include "twm_decode_ops.cuh"
+#include "../../include/twm_decode.h"
 
 namespace {
 
 thread_local char t_last_error[256] = "";
+#ifdef TWM_TIMELINE
+int g_launch_counter = 0;     // development builds only
+#endif
 
 void set_error(const char* where, cudaError_t e)
 {
@@ -303,6 +308,27 @@ twm_status static_ws_address(void** out)
 
 }  // namespace
 
+namespace {
+constexpr int kArgmaxParts = 592;   // 4 CTAs per SM
+
+template <typename... KArgs, typename... Args>
+twm_status launch_op(const char* name, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, int flags,
+                     void* stream_, Args... args)
+{
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = (cudaStream_t)stream_;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (flags & TWM_FLAG_PDL) ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess) { set_error(name, e); return TWM_ELAUNCH; }
+    return TWM_OK;
+}
+}  // namespace
+
 extern "C" {
 
 twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int splits_override,
@@ -417,6 +443,9 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
         p.accumulate = (a->flags & TWM_FLAG_ACCUMULATE) ? 1 : 0;
         p.packed_offsets = a->packed_offsets; p.scales_offsets = a->scales_offsets; p.expert_idx = a->expert_idx;
         p.map_rows = map_rows;
+#ifdef TWM_TIMELINE
+        p.launch_id = g_launch_counter++;
+#endif
         if (map_rows) p.packed_map = packed_map;
         const bool pdl = (a->flags & TWM_FLAG_PDL) != 0;
         if (kernel == TWM_KERNEL_TC)
@@ -581,6 +610,116 @@ twm_status twm_device_error(void* stream_, unsigned int* word)
     return *word ? TWM_ETIMEOUT : TWM_OK;
 }
 
+// ------------------------------------------------------------ decode-step kernels --
+twm_status twm_embed(float* x, const void* table, const int* tokens, int rows, int hidden, int flags, void* stream)
+{
+    if (!x || !table || !tokens || rows < 1 || hidden < 1) return TWM_EINVAL;
+    twm_status st = ensure_device(nullptr);
+    if (st != TWM_OK) return st;
+    return launch_op("twm_embed", twm::ops::embed_kernel, dim3((hidden + 255) / 256, rows), dim3(256), 0, flags, stream,
+                     x, (const __half*)table, tokens, hidden);
+}
+
+twm_status twm_rmsnorm(void* y, const float* x, const float* gamma, int rows, int hidden, float eps, int flags,
+                       void* stream)
+{
+    if (!y || !x || !gamma || rows < 1 || hidden < 1) return TWM_EINVAL;
+    twm_status st = ensure_device(nullptr);
+    if (st != TWM_OK) return st;
+    return launch_op("twm_rmsnorm", twm::ops::rmsnorm_kernel, dim3(rows), dim3(256), 0, flags, stream, (__half*)y,
+                     const_cast<float*>(x), (const float*)nullptr, gamma, hidden, eps);
+}
+
+twm_status twm_add_rmsnorm(void* y, float* x, const float* add, const float* gamma, int rows, int hidden, float eps,
+                           int flags, void* stream)
+{
+    if (!x || !add || (y && !gamma) || rows < 1 || hidden < 1) return TWM_EINVAL;
+    twm_status st = ensure_device(nullptr);
+    if (st != TWM_OK) return st;
+    return launch_op("twm_add_rmsnorm", twm::ops::rmsnorm_kernel, dim3(rows), dim3(256), 0, flags, stream, (__half*)y, x,
+                     add, gamma, hidden, eps);
+}
+
+twm_status twm_rope_append(void* q_out, void* k_cache, void* v_cache, const void* qkv, const float* bias, int rows,
+                           int num_heads, int num_kv_heads, int head_dim, const int* pos_buf, int max_seq,
+                           float rope_base, int flags, void* stream)
+{
+    if (!q_out || !k_cache || !v_cache || !qkv || !pos_buf || rows < 1) return TWM_EINVAL;
+    if (num_heads < 1 || num_kv_heads < 1 || head_dim < 2 || (head_dim & 1) || max_seq < 1) return TWM_EINVAL;
+    twm_status st = ensure_device(nullptr);
+    if (st != TWM_OK) return st;
+    const int total = (num_heads + num_kv_heads) * head_dim;
+    return launch_op("twm_rope_append", twm::ops::rope_append_kernel, dim3((total + 255) / 256, rows), dim3(256), 0, flags,
+                     stream, (__half*)q_out, (__half*)k_cache, (__half*)v_cache, (const __half*)qkv, bias, num_heads,
+                     num_kv_heads, head_dim, pos_buf, max_seq, rope_base);
+}
+
+size_t twm_attn_scratch_bytes(int rows, int num_heads, int head_dim, int max_seq)
+{
+    if (rows < 1 || num_heads < 1 || head_dim < 1 || max_seq < 1) return 0;
+    const size_t chunks = (size_t)(max_seq + twm::ops::ATT_CHUNK - 1) / twm::ops::ATT_CHUNK;
+    return (size_t)rows * num_heads * chunks * (head_dim + 2) * sizeof(float);
+}
+
+twm_status twm_attn_decode(void* out, const void* q, const void* k_cache, const void* v_cache, int rows, int num_heads,
+                           int num_kv_heads, int head_dim, const int* len_buf, int max_seq, void* scratch,
+                           size_t scratch_bytes, int flags, void* stream)
+{
+    if (!out || !q || !k_cache || !v_cache || !len_buf || !scratch || rows < 1 || rows > 65535) return TWM_EINVAL;
+    if (head_dim != 128 || num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads) return TWM_EINVAL;
+    if (num_heads / num_kv_heads > twm::ops::ATT_MAX_GROUP) return TWM_EINVAL;
+    if (scratch_bytes < twm_attn_scratch_bytes(rows, num_heads, head_dim, max_seq)) return TWM_EWORKSPACE;
+    twm_status st = ensure_device(nullptr);
+    if (st != TWM_OK) return st;
+    const int chunks = (max_seq + twm::ops::ATT_CHUNK - 1) / twm::ops::ATT_CHUNK;
+    st = launch_op("twm_attn_decode(chunks)", twm::ops::attn_chunk_kernel<128>, dim3(chunks, num_kv_heads, rows),
+                   dim3(256), 0, flags, stream, (float*)scratch, (const __half*)q, (const __half*)k_cache,
+                   (const __half*)v_cache, num_heads, num_kv_heads, len_buf, chunks, max_seq);
+    if (st != TWM_OK) return st;
+    return launch_op("twm_attn_decode(merge)", twm::ops::attn_merge_kernel<128>, dim3(num_heads, rows), dim3(128), 0, flags,
+                     stream, (__half*)out, (const float*)scratch, len_buf, chunks);
+}
+
+twm_status twm_silu_mul(void* act, const void* gate_up, int rows, int ffn, int flags, void* stream)
+{
+    if (!act || !gate_up || rows < 1 || ffn < 1) return TWM_EINVAL;
+    twm_status st = ensure_device(nullptr);
+    if (st != TWM_OK) return st;
+    return launch_op("twm_silu_mul", twm::ops::silu_mul_kernel, dim3((rows * ffn + 255) / 256), dim3(256), 0, flags,
+                     stream, (__half*)act, (const __half*)gate_up, ffn, rows);
+}
+
+twm_status twm_lm_head(float* logits, const void* x, const void* w, int hidden, int vocab, int flags, void* stream)
+{
+    if (!logits || !x || !w || hidden < 8 || (hidden & 7) || vocab < 1 || hidden > 24576) return TWM_EINVAL;
+    if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(x) & 1)) return TWM_EALIGN;
+    int sms = kDefaultSms;
+    twm_status st = ensure_device(&sms);
+    if (st != TWM_OK) return st;
+    const int grid = std::min((vocab + 7) / 8, sms * 8);
+    return launch_op("twm_lm_head", twm::ops::lm_head_kernel, dim3(grid), dim3(256), (size_t)hidden * 2, flags, stream,
+                     logits, (const __half*)x, (const __half*)w, hidden, vocab);
+}
+
+size_t twm_argmax_scratch_bytes(void) { return (size_t)kArgmaxParts * 8; }
+
+twm_status twm_argmax_advance(int* token_out, int* history, int* pos_buf, int* len_buf, int* step_buf,
+                              const float* logits, int n, void* scratch, size_t scratch_bytes, int flags,
+                              void* stream)
+{
+    if (!token_out || !pos_buf || !len_buf || !step_buf || !logits || !scratch || n < 1) return TWM_EINVAL;
+    if (scratch_bytes < twm_argmax_scratch_bytes()) return TWM_EWORKSPACE;
+    twm_status st = ensure_device(nullptr);
+    if (st != TWM_OK) return st;
+    float* pval = (float*)scratch;
+    int* pidx = (int*)((char*)scratch + (size_t)kArgmaxParts * 4);
+    st = launch_op("twm_argmax(partial)", twm::ops::argmax_partial_kernel, dim3(kArgmaxParts), dim3(256), 0, flags, stream,
+                   pval, pidx, logits, n);
+    if (st != TWM_OK) return st;
+    return launch_op("twm_argmax(final)", twm::ops::argmax_final_kernel, dim3(1), dim3(256), 0, flags, stream, token_out,
+                     history, pos_buf, len_buf, step_buf, (const float*)pval, (const int*)pidx, kArgmaxParts);
+}
+
 const char* twm_status_string(twm_status s)
 {
     switch (s) {
@@ -594,6 +733,15 @@ const char* twm_status_string(twm_status s)
     }
     return "unknown status";
 }
+
+#ifdef TWM_TIMELINE
+int twm_timeline_reset(void) { g_launch_counter = 0; return 0; }
+int twm_timeline_read(unsigned long long* out, int n)
+{
+    cudaDeviceSynchronize();
+    return cudaMemcpyFromSymbol(out, twm::g_timeline, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 #ifdef TWM_PROF
 // development builds only: read and clear the per-role cycle counters

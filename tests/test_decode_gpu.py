@@ -1,0 +1,128 @@
+"""GPU tests of the decode step built from the W4A16 GEMMs and their neighbour kernels, against
+the CPU restatement in oracle/decode_ref.py (teacher-forced logits), plus the reference's own
+self-consistency checks: graph replay == eager launches, two runs identical
+(crates/kernels/src/generate.rs:3811-3841, 3667-3723)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from oracle import decode_ref
+from tensorwarp_b200 import generate as gen
+from tensorwarp_b200 import quantize as q
+
+pytestmark = pytest.mark.gpu
+
+SMALL = gen.TransformerConfig(hidden=256, num_heads=2, num_kv_heads=1, head_dim=128, ffn=512, vocab=1024, layers=2,
+                              rope_theta=1e6, eps=1e-6, max_seq=512, group_size=128, qkv_bias=True)
+GQA = gen.TransformerConfig(hidden=512, num_heads=8, num_kv_heads=2, head_dim=128, ffn=1024, vocab=2000, layers=2,
+                            rope_theta=1e4, eps=1e-5, max_seq=384, group_size=32, qkv_bias=False)
+
+
+def _dense_provider(model):
+    """Dequantised weights for the oracle, from the packed tensors through the CPU oracle's decode."""
+    cfg = model.cfg
+    cache = {}
+
+    def dq(w, k, n):
+        p = w[0].cpu().numpy()
+        s = w[1].cpu().numpy().view(np.uint16)
+        return oracle.dequant_f32(p, s, k, n, cfg.group_size)
+
+    def dense(li, name):
+        key = (li, name)
+        if key in cache:
+            return cache[key]
+        if li == -1:
+            if name == "embed_row":
+                emb = model.embed.float().cpu().numpy()
+                val = lambda tok: emb[int(tok)]
+            elif name == "final_norm":
+                val = model.final_norm.cpu().numpy()
+            else:
+                val = model.lm_head.float().cpu().numpy()
+        else:
+            lw = model.layers[li]
+            if name == "qkv":
+                val = dq(lw.wqkv, cfg.hidden, cfg.q_dim + 2 * cfg.kv_dim)
+            elif name == "o":
+                val = dq(lw.wo, cfg.q_dim, cfg.hidden)
+            elif name == "gu":
+                val = dq(lw.wgu, cfg.hidden, 2 * cfg.ffn)
+            elif name == "down":
+                val = dq(lw.w_down, cfg.ffn, cfg.hidden)
+            elif name == "attn_norm":
+                val = lw.attn_norm.cpu().numpy()
+            elif name == "ffn_norm":
+                val = lw.ffn_norm.cpu().numpy()
+            else:
+                val = lw.bqkv.cpu().numpy() if lw.bqkv is not None else None
+        cache[key] = val
+        return val
+
+    return dense
+
+
+@pytest.mark.parametrize("cfg,prefill", [(SMALL, 100), (GQA, 200), (SMALL, 0)])
+def test_teacher_forced_logits_match_oracle(cfg, prefill):
+    model = gen.Q4Model(cfg, seed=5)
+    eng = gen.QuantizedGenerationEngine(model)
+    if prefill:
+        eng.prefill_random_kv(prefill, seed=2)
+    else:
+        eng.set_position(0)
+    kc = [c.float().cpu().numpy().copy() for c in eng.buf.k_cache]
+    vc = [c.float().cpu().numpy().copy() for c in eng.buf.v_cache]
+    dense = _dense_provider(model)
+    tokens = torch.randint(0, cfg.vocab, (5,), generator=torch.Generator().manual_seed(3)).tolist()
+    greedy_agree = 0
+    for i, tok in enumerate(tokens):
+        eng.set_token(tok)
+        eng.step_eager()
+        torch.cuda.synchronize()
+        logits = eng.buf.logits.cpu().numpy()
+        ref = decode_ref.decode_step(cfg, dense, tok, prefill + i, kc, vc)
+        rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+        err = float(np.max(np.abs(logits - ref))) / rms
+        assert err < 1e-2, (i, err)
+        greedy_agree += int(int(eng.buf.token.item()) == int(np.argmax(ref)))
+        # the appended cache rows are the oracle's, to FP16 rounding of one unit in the last place
+        for li in range(cfg.layers):
+            kg = eng.buf.k_cache[li][prefill + i].float().cpu().numpy()
+            assert np.max(np.abs(kg - kc[li][prefill + i])) <= 2e-3 * max(1.0, float(np.abs(kc[li][prefill + i]).max()))
+    assert int(eng.buf.pos.item()) == prefill + len(tokens)
+    assert int(eng.buf.cache_len.item()) == prefill + len(tokens) + 1
+    assert greedy_agree >= len(tokens) - 1          # near-flat random logits: one near-tie may flip
+    assert q.device_error() == 0
+
+
+def test_graph_replay_equals_eager_and_is_deterministic():
+    cfg = SMALL
+    model = gen.Q4Model(cfg, seed=7)
+    runs = []
+    for mode in ("eager", "graph", "graph"):
+        eng = gen.QuantizedGenerationEngine(model)
+        eng.prefill_random_kv(64, seed=2)
+        if mode == "eager":
+            eng.set_token(17)
+            for _ in range(12):
+                eng.step_eager()
+            torch.cuda.synchronize()
+            toks = eng.buf.history[:12].tolist()
+        else:
+            toks = eng.generate_tw_marlin_graph(17, 12)
+        assert all(0 <= t < cfg.vocab for t in toks)
+        runs.append(toks)
+    assert runs[0] == runs[1] == runs[2]
+    assert q.device_error() == 0
+
+
+def test_without_programmatic_launch_same_tokens():
+    cfg = GQA
+    model = gen.Q4Model(cfg, seed=9)
+    outs = []
+    for pdl in (True, False):
+        eng = gen.QuantizedGenerationEngine(model, use_pdl=pdl)
+        eng.prefill_random_kv(130, seed=2)
+        outs.append(eng.generate_tw_marlin_graph(3, 8))
+    assert outs[0] == outs[1]
