@@ -41,6 +41,7 @@ embed_kernel(float* __restrict__ x, const __half* __restrict__ table, const int*
 // y = f16(x * rsqrt(mean(x^2) + eps) * gamma), one CTA per row.  Reference: warp_rmsnorm,
 // crates/kernels/src/ops.rs:302-336 (one warp per row there; here 256 threads and a fixed-order
 // two-level sum).  With `add` the kernel first does x += add (and stops there when y is null).
+constexpr int RMS_MAX_VEC = 8;        // float4 per thread held in registers: rows up to 8192 floats
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(__half* __restrict__ y, float* __restrict__ x, const float* __restrict__ add,
                const float* __restrict__ gamma, int hidden, float eps)
@@ -50,15 +51,65 @@ rmsnorm_kernel(__half* __restrict__ y, float* __restrict__ x, const float* __res
     __shared__ float partial[8];
     const int row = blockIdx.x;
     float* xr = x + (size_t)row * hidden;
+    const float* ar = add ? add + (size_t)row * hidden : nullptr;
+    const bool vec = ((hidden & 3) == 0) && (hidden <= 256 * 4 * RMS_MAX_VEC) &&
+                     ((reinterpret_cast<uintptr_t>(xr) & 15) == 0) && (!ar || (reinterpret_cast<uintptr_t>(ar) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(gamma) & 15) == 0);
     float ss = 0.0f;
-    if (add != nullptr) {
+    if (vec) {
+        // the whole row sits in registers: every load is issued before the first use
+        const int nvec = hidden >> 2;
+        float4 v[RMS_MAX_VEC];
+#pragma unroll
+        for (int j = 0; j < RMS_MAX_VEC; ++j) {
+            const int i = threadIdx.x + j * 256;
+            v[j] = (i < nvec) ? reinterpret_cast<const float4*>(xr)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        if (ar) {
+#pragma unroll
+            for (int j = 0; j < RMS_MAX_VEC; ++j) {
+                const int i = threadIdx.x + j * 256;
+                if (i < nvec) {
+                    const float4 a = reinterpret_cast<const float4*>(ar)[i];
+                    v[j].x += a.x; v[j].y += a.y; v[j].z += a.z; v[j].w += a.w;
+                    reinterpret_cast<float4*>(xr)[i] = v[j];
+                }
+            }
+            if (y == nullptr) return;
+        }
+#pragma unroll
+        for (int j = 0; j < RMS_MAX_VEC; ++j)
+            ss = fmaf(v[j].x, v[j].x, fmaf(v[j].y, v[j].y, fmaf(v[j].z, v[j].z, fmaf(v[j].w, v[j].w, ss))));
+        ss = warp_sum(ss);
+        if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        float tot = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) tot += partial[w];
+        const float rms = rsqrtf(tot / (float)hidden + eps);
+        __half* yr = y + (size_t)row * hidden;
+#pragma unroll
+        for (int j = 0; j < RMS_MAX_VEC; ++j) {
+            const int i = threadIdx.x + j * 256;
+            if (i < nvec) {
+                const float4 gm = reinterpret_cast<const float4*>(gamma)[i];
+                const __half2 lo = __floats2half2_rn(v[j].x * rms * gm.x, v[j].y * rms * gm.y);
+                const __half2 hi = __floats2half2_rn(v[j].z * rms * gm.z, v[j].w * rms * gm.w);
+                uint2 o;
+                o.x = *reinterpret_cast<const uint32_t*>(&lo);
+                o.y = *reinterpret_cast<const uint32_t*>(&hi);
+                reinterpret_cast<uint2*>(yr)[i] = o;
+            }
+        }
+        return;
+    }
+    if (ar != nullptr) {
         // x += add first (fused_residual_rmsnorm, ops.rs:928-962): the all-reduced output of a
         // row-parallel GEMM joins the residual stream here
-        const float* ar = add + (size_t)row * hidden;
-        for (int i = threadIdx.x; i < hidden; i += blockDim.x) { const float v = xr[i] + ar[i]; xr[i] = v; ss = fmaf(v, v, ss); }
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) { const float t = xr[i] + ar[i]; xr[i] = t; ss = fmaf(t, t, ss); }
         if (y == nullptr) return;
     } else {
-        for (int i = threadIdx.x; i < hidden; i += blockDim.x) { const float v = xr[i]; ss = fmaf(v, v, ss); }
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) { const float t = xr[i]; ss = fmaf(t, t, ss); }
     }
     ss = warp_sum(ss);
     if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = ss;
@@ -119,12 +170,12 @@ rope_append_kernel(__half* __restrict__ q_out, __half* __restrict__ k_cache, __h
     }
 }
 
-// Split-KV decode attention, pass 1.  CTA = (chunk of 128 tokens, kv head); its 8 warps share
+// Split-KV decode attention, pass 1.  CTA = (chunk of ATT_CHUNK tokens, kv head); its 8 warps share
 // the kv head's K/V rows between all q heads of the group (GQA), so the cache is read once.
 // Online soft-max per warp, merged through shared memory; writes (max, sum, unnormalised o[128])
 // per (q head, chunk).  The sequence length is read from the device (len_buf[0]), the grid
 // covers max_seq.  Reference: warp_flash_decode_chunk_dl, crates/kernels/src/kv_cache.rs:951-1076.
-constexpr int ATT_CHUNK = 128;
+constexpr int ATT_CHUNK = 32;       // tokens per CTA: 8 warps x 4 tokens, every K/V row requested before the first use
 constexpr int ATT_MAX_GROUP = 8;      // q heads per kv head, at most
 
 template <int HEAD_DIM>
@@ -173,22 +224,40 @@ attn_chunk_kernel(float* __restrict__ part /* [heads][chunks][HEAD_DIM + 2] */, 
     float m[ATT_MAX_GROUP], l[ATT_MAX_GROUP], o[ATT_MAX_GROUP][4];
 #pragma unroll
     for (int h = 0; h < ATT_MAX_GROUP; ++h) { m[h] = -INFINITY; l[h] = 0.0f; o[h][0] = o[h][1] = o[h][2] = o[h][3] = 0.0f; }
-    for (int tk = t0 + warp; tk < t1; tk += 8) {
-        const __half2* kp = reinterpret_cast<const __half2*>(k_cache + (size_t)tk * kv_dim + kvh * HEAD_DIM + lane * 4);
-        const __half2* vp = reinterpret_cast<const __half2*>(v_cache + (size_t)tk * kv_dim + kvh * HEAD_DIM + lane * 4);
-        const float2 k0 = __half22float2(kp[0]), k1 = __half22float2(kp[1]);
-        const float2 v0 = __half22float2(vp[0]), v1 = __half22float2(vp[1]);
+    // this warp's tokens: t0 + warp, + 8, + 16, + 24; all loads first, then the arithmetic
+    constexpr int TPW = ATT_CHUNK / 8;
+    float2 kf[TPW][2], vf[TPW][2];
 #pragma unroll
-        for (int h = 0; h < ATT_MAX_GROUP; ++h) {
-            if (h < group) {
-                float s = qv[h][0] * k0.x + qv[h][1] * k0.y + qv[h][2] * k1.x + qv[h][3] * k1.y;
-                s = warp_sum(s);
-                const float mn = fmaxf(m[h], s);
-                const float corr = __expf(m[h] - mn), pexp = __expf(s - mn);
-                l[h] = l[h] * corr + pexp;
-                o[h][0] = o[h][0] * corr + pexp * v0.x; o[h][1] = o[h][1] * corr + pexp * v0.y;
-                o[h][2] = o[h][2] * corr + pexp * v1.x; o[h][3] = o[h][3] * corr + pexp * v1.y;
-                m[h] = mn;
+    for (int j = 0; j < TPW; ++j) {
+        const int tk = t0 + warp + 8 * j;
+        if (tk < t1) {
+            const uint2 kr = *reinterpret_cast<const uint2*>(k_cache + (size_t)tk * kv_dim + kvh * HEAD_DIM + lane * 4);
+            const uint2 vr = *reinterpret_cast<const uint2*>(v_cache + (size_t)tk * kv_dim + kvh * HEAD_DIM + lane * 4);
+            kf[j][0] = __half22float2(*reinterpret_cast<const __half2*>(&kr.x));
+            kf[j][1] = __half22float2(*reinterpret_cast<const __half2*>(&kr.y));
+            vf[j][0] = __half22float2(*reinterpret_cast<const __half2*>(&vr.x));
+            vf[j][1] = __half22float2(*reinterpret_cast<const __half2*>(&vr.y));
+        } else {
+            kf[j][0] = kf[j][1] = vf[j][0] = vf[j][1] = make_float2(0.f, 0.f);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < TPW; ++j) {
+        const int tk = t0 + warp + 8 * j;
+        if (tk < t1) {                                   // warp-uniform
+            const float2 k0 = kf[j][0], k1 = kf[j][1], v0 = vf[j][0], v1 = vf[j][1];
+#pragma unroll
+            for (int h = 0; h < ATT_MAX_GROUP; ++h) {
+                if (h < group) {
+                    float s = qv[h][0] * k0.x + qv[h][1] * k0.y + qv[h][2] * k1.x + qv[h][3] * k1.y;
+                    s = warp_sum(s);
+                    const float mn = fmaxf(m[h], s);
+                    const float corr = __expf(m[h] - mn), pexp = __expf(s - mn);
+                    l[h] = l[h] * corr + pexp;
+                    o[h][0] = o[h][0] * corr + pexp * v0.x; o[h][1] = o[h][1] * corr + pexp * v0.y;
+                    o[h][2] = o[h][2] * corr + pexp * v1.x; o[h][3] = o[h][3] * corr + pexp * v1.y;
+                    m[h] = mn;
+                }
             }
         }
     }
@@ -229,20 +298,44 @@ attn_merge_kernel(__half* __restrict__ out, const float* __restrict__ part, cons
 {
     pdl_launch_dependents();
     pdl_wait_prior_grids();
+    constexpr int MAXC = 1024;                       // chunk weights kept in shared memory
+    __shared__ float s_w[MAXC];
+    __shared__ float s_red[HEAD_DIM / 32];
     const int head = blockIdx.x, d = threadIdx.x;
     out += (size_t)blockIdx.y * gridDim.x * HEAD_DIM;
     part += (size_t)blockIdx.y * gridDim.x * max_chunks * (HEAD_DIM + 2);
-    const int chunks = min(max_chunks, (len_buf[0] + ATT_CHUNK - 1) / ATT_CHUNK);
+    const int chunks = min(min(max_chunks, MAXC), (len_buf[0] + ATT_CHUNK - 1) / ATT_CHUNK);
     const float* base = part + (size_t)head * max_chunks * (HEAD_DIM + 2);
-    float mm = -INFINITY;
-    for (int c = 0; c < chunks; ++c) mm = fmaxf(mm, base[(size_t)c * (HEAD_DIM + 2) + HEAD_DIM]);
-    float ll = 0.0f, oo = 0.0f;
-    for (int c = 0; c < chunks; ++c) {
-        const float* pc = base + (size_t)c * (HEAD_DIM + 2);
-        const float w = (pc[HEAD_DIM] == -INFINITY) ? 0.0f : __expf(pc[HEAD_DIM] - mm);
-        ll += pc[HEAD_DIM + 1] * w;
-        oo += pc[d] * w;
+    // every chunk's (max, sum) in one round of loads, one chunk per thread
+    float mloc = -INFINITY;
+    for (int c = d; c < chunks; c += HEAD_DIM) {
+        const float mc = base[(size_t)c * (HEAD_DIM + 2) + HEAD_DIM];
+        s_w[c] = mc;
+        mloc = fmaxf(mloc, mc);
     }
+    mloc = warp_max(mloc);
+    if ((d & 31) == 0) s_red[d >> 5] = mloc;
+    __syncthreads();
+    float mm = s_red[0];
+#pragma unroll
+    for (int w = 1; w < HEAD_DIM / 32; ++w) mm = fmaxf(mm, s_red[w]);
+    float lloc = 0.0f;
+    for (int c = d; c < chunks; c += HEAD_DIM) {
+        const float mc = s_w[c];
+        const float w = (mc == -INFINITY) ? 0.0f : __expf(mc - mm);
+        s_w[c] = w;
+        lloc += base[(size_t)c * (HEAD_DIM + 2) + HEAD_DIM + 1] * w;
+    }
+    __syncthreads();
+    lloc = warp_sum(lloc);
+    if ((d & 31) == 0) s_red[d >> 5] = lloc;
+    __syncthreads();
+    float ll = 0.0f;
+#pragma unroll
+    for (int w = 0; w < HEAD_DIM / 32; ++w) ll += s_red[w];
+    float oo = 0.0f;
+#pragma unroll 16
+    for (int c = 0; c < chunks; ++c) oo = fmaf(base[(size_t)c * (HEAD_DIM + 2) + d], s_w[c], oo);
     out[(size_t)head * HEAD_DIM + d] = __float2half_rn(ll > 0.0f ? oo / ll : 0.0f);
 }
 

@@ -672,6 +672,7 @@ twm_status twm_attn_decode(void* out, const void* q, const void* k_cache, const 
     twm_status st = ensure_device(nullptr);
     if (st != TWM_OK) return st;
     const int chunks = (max_seq + twm::ops::ATT_CHUNK - 1) / twm::ops::ATT_CHUNK;
+    if (chunks > 1024) return TWM_EINVAL;          // the merge pass keeps one weight per chunk in shared memory
     st = launch_op("twm_attn_decode(chunks)", twm::ops::attn_chunk_kernel<128>, dim3(chunks, num_kv_heads, rows),
                    dim3(256), 0, flags, stream, (float*)scratch, (const __half*)q, (const __half*)k_cache,
                    (const __half*)v_cache, num_heads, num_kv_heads, len_buf, chunks, max_seq);

@@ -1,0 +1,88 @@
+"""GPU test of the tensor-parallel layer stack on ONE device: the ranks of a tp=2 (and tp=4) group
+are run phase by phase in one process and their partial outputs are summed where NCCL would
+all-reduce them; the result must match the unsharded stack (tp=1).  The multi-process NCCL run is
+bench.py --gpus N."""
+import numpy as np
+import pytest
+import torch
+
+from tensorwarp_b200 import quantize as q
+from tensorwarp_b200 import tensor_parallel as tp
+from tensorwarp_b200.generate import TransformerConfig
+
+pytestmark = pytest.mark.gpu
+
+CFG = TransformerConfig(hidden=512, num_heads=8, num_kv_heads=4, head_dim=128, ffn=1024, vocab=10, layers=3,
+                        rope_theta=5e5, eps=1e-5, max_seq=256, group_size=128, qkv_bias=False)
+
+
+def _full_layers(cfg, seed):
+    out = []
+    dev = "cuda"
+    for layer in range(cfg.layers):
+        shapes = [(cfg.hidden, cfg.q_dim), (cfg.hidden, cfg.kv_dim), (cfg.hidden, cfg.kv_dim), (cfg.q_dim, cfg.hidden),
+                  (cfg.hidden, cfg.ffn), (cfg.hidden, cfg.ffn), (cfg.ffn, cfg.hidden)]
+        mats = []
+        for pid, (k, n) in enumerate(shapes):
+            gen = torch.Generator(device=dev).manual_seed(seed + 1000 * layer + pid)
+            w = torch.randn((k, n), generator=gen, device=dev) * 0.02
+            mats.append(q.quantize_f32_to_tw_marlin(w, k, n, cfg.group_size))
+        out.append(mats)
+    return out
+
+
+def _run(cfg, full, degree, rows, x0, kv_len):
+    ones = torch.ones(cfg.hidden, device="cuda")
+    stacks = []
+    for r in range(degree):
+        spec = tp.shard_spec(cfg, degree, r)
+        layers = [tp.shard_layer(cfg, spec, *mats, ones, ones) for mats in full]
+        st = tp.TPDecodeStack(cfg, spec, layers, rows, "cuda", all_reduce=lambda t: None)
+        stacks.append(st)
+    # the same random KV cache for every degree: generate the full cache, hand each rank its kv heads
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    for li in range(cfg.layers):
+        kfull = torch.randn((rows, kv_len, cfg.kv_dim), generator=gen, device="cuda").half()
+        vfull = torch.randn((rows, kv_len, cfg.kv_dim), generator=gen, device="cuda").half()
+        for st in stacks:
+            c0, c1 = st.spec.kv_cols
+            st.k_cache[li][:, :kv_len] = kfull[:, :, c0:c1]
+            st.v_cache[li][:, :kv_len] = vfull[:, :, c0:c1]
+    for st in stacks:
+        st.pos.fill_(kv_len)
+        st.cache_len.fill_(kv_len + 1)
+        st.x.copy_(x0)
+    sp = torch.cuda.current_stream().cuda_stream
+
+    def reduce_all():
+        total = sum(st.part for st in stacks)
+        for st in stacks:
+            st.part.copy_(total)
+
+    for li in range(cfg.layers):
+        for st in stacks:
+            st.attn_phase(li, sp)
+        reduce_all()
+        for st in stacks:
+            st.ffn_phase(li, sp)
+        reduce_all()
+    for st in stacks:
+        st.finish(sp)
+    torch.cuda.synchronize()
+    assert q.device_error() == 0
+    return [st.x.cpu().numpy() for st in stacks]
+
+
+@pytest.mark.parametrize("rows", [1, 3])
+def test_sharded_stack_equals_unsharded(rows):
+    cfg = CFG
+    full = _full_layers(cfg, 21)
+    x0 = torch.randn((rows, cfg.hidden), generator=torch.Generator().manual_seed(5)).cuda()
+    ref = _run(cfg, full, 1, rows, x0, 100)[0]
+    rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+    for degree in (2, 4):
+        outs = _run(cfg, full, degree, rows, x0, 100)
+        for o in outs[1:]:
+            assert np.array_equal(o, outs[0])                 # every rank ends with the same activations
+        err = float(np.max(np.abs(outs[0] - ref))) / rms
+        assert err < 2e-3, (degree, err)                      # FP32 partials, different summation order only
