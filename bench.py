@@ -289,6 +289,122 @@ def decode_tok_s(torch, device, new_tokens: int = 64, kv_len: int = 2048):
             "tokens_in_vocab": bool(all(0 <= t < cfg.vocab for t in toks))}
 
 
+# ------------------------------------------------------------- tensor parallel --
+
+def run_tp(args):
+    """N > 1: configs[4], the Llama-3-70B-shaped Q4 decode layer stack (80 layers), tensor-parallel over
+    the N GPUs of one box.  QKV and gate+up column-sharded, o and down row-sharded with an NCCL
+    all-reduce (FP32 partials) after each; KV length 4096; M = 1 (headline) and M = 32.  One step =
+    the 80-layer stack once, one CUDA graph per rank.  Strong scaling: the model is fixed, each
+    rank holds 1/N of it."""
+    import torch
+    import torch.distributed as dist
+
+    from tensorwarp_b200 import quantize as q
+    from tensorwarp_b200 import tensor_parallel as tp
+
+    world = int(os.environ["WORLD_SIZE"])
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=device)
+
+    kv_len = 4096
+    base = tp.LLAMA3_70B
+    cfg = type(base)(**{**base.__dict__, "max_seq": kv_len + 128})
+    spec = tp.shard_spec(cfg, world, rank)
+    layers = [tp.random_shard_layer(cfg, spec, li, device) for li in range(cfg.layers)]
+    torch.cuda.synchronize()
+    hd = cfg.head_dim
+    shard_gemms = [(cfg.hidden, spec.n_qkv), ((spec.q_heads[1] - spec.q_heads[0]) * hd, cfg.hidden),
+                   (cfg.hidden, spec.n_gu), (spec.n_gu // 2, cfg.hidden)]
+
+    def stack_bytes(m):
+        return cfg.layers * sum(algorithmic_bytes(m, n, k, cfg.group_size, 2, 4 if n == cfg.hidden else 2)
+                                for k, n in shard_gemms)
+
+    results = {}
+    clocks_summary = None
+    for rows in (1, 32):
+        stack = tp.TPDecodeStack(cfg, spec, layers, rows, device, all_reduce=lambda t: dist.all_reduce(t))
+        stack.prefill_random_kv(kv_len, seed=2)
+        host_x = torch.randn((rows, cfg.hidden), generator=torch.Generator().manual_seed(7)).pin_memory()
+        host_out = torch.empty((rows, cfg.hidden)).pin_memory()
+        stream = torch.cuda.Stream(device)
+        with torch.cuda.stream(stream):
+            stack.x.copy_(host_x, non_blocking=True)
+            stack.forward(stream.cuda_stream)                 # eager once (NCCL and kernel warm-up)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                stack.forward(stream.cuda_stream)
+            for _ in range(args.warmup):
+                graph.replay()
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with ClockSampler(local_rank) as clocks:
+                e0.record(stream)
+                for _ in range(args.steps):
+                    graph.replay()
+                e1.record(stream)
+                torch.cuda.synchronize()
+            dist.barrier()
+            t = torch.tensor([e0.elapsed_time(e1)], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item()) / args.steps
+            # end to end: activations from pinned host memory in, result back out, every step
+            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            f0.record(stream)
+            for _ in range(args.steps):
+                stack.x.copy_(host_x, non_blocking=True)
+                graph.replay()
+                host_out.copy_(stack.x, non_blocking=True)
+            f1.record(stream)
+            torch.cuda.synchronize()
+            t = torch.tensor([f0.elapsed_time(f1)], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = float(t.item()) / args.steps
+        total_bytes = world * stack_bytes(rows)
+        results[rows] = {"ms_per_step": round(ms, 4), "gbs": round(total_bytes / (ms * 1e-3) / 1e9, 1),
+                         "e2e_gbs": round(total_bytes / (e2e_ms * 1e-3) / 1e9, 1), "launches": stack.launches,
+                         "allreduce_bytes": rows * cfg.hidden * 4, "allreduces_per_step": 2 * cfg.layers,
+                         "h2d": rows * cfg.hidden * 4, "d2h": rows * cfg.hidden * 4,
+                         "finite": bool(torch.isfinite(stack.x).all().item())}
+        if rows == 1:
+            clocks_summary = clocks.summary()
+        del stack, graph
+        torch.cuda.empty_cache()
+    err = q.device_error()
+    if err:
+        raise RuntimeError(f"device error word {err:#x}")
+    peak, peak_kind = measured_peak_gbs()
+    r1 = results[1]
+    gemm_launches = 4 * cfg.layers
+    line = {
+        "metric": METRIC, "value": r1["gbs"], "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": r1["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
+        "config": {"workload": f"configs[4]: Llama-3-70B-shaped Q4 decode layer stack, 80 layers, tensor parallel tp={world}, "
+                               "M=1, KV 4096, Q4 group-128",
+                   "l2": f"inputs larger than L2: {stack_bytes(1) / 1e9:.2f} GB of weights streamed per rank per step",
+                   "launch": "one CUDA graph per rank; NCCL all-reduce (FP32, [M,8192]) after o and down",
+                   "parallelism": f"tp{world}"},
+        "roofline": {"bound": "hbm", "achieved": round(r1["gbs"] / world, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(r1["gbs"] / world / peak, 4), "peak_kind": peak_kind,
+                     "kernel": "twm::mma::gemv_kernel<1,2> (per rank, whole step incl. collectives)", "traffic": None},
+        "e2e": {"value": r1["e2e_gbs"], "unit": UNIT, "h2d_bytes_per_step": r1["h2d"], "d2h_bytes_per_step": r1["d2h"]},
+        "gpu_launches": r1["launches"] * args.steps,
+        "clocks": clocks_summary,
+        "tp": {"m1": r1, "m32": results[32], "gemm_launches_per_step": gemm_launches},
+    }
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, averaged over one layer's four kernels,
 # from the ncu capture summarised under profiles/ (None until that capture exists)
 TRAFFIC_PER_LAUNCH = None
@@ -381,9 +497,14 @@ def main():
         args.steps = min(args.steps, 20)          # each step is seconds of CPU work
         run_reference(args)
     else:
-        args.steps = args.steps if args.steps is not None else 50
+        world = int(os.environ.get("WORLD_SIZE", "1"))
         args.warmup = max(args.warmup if args.warmup is not None else 5, 3)
-        run_ours(args)
+        if world > 1:
+            args.steps = args.steps if args.steps is not None else 20
+            run_tp(args)
+        else:
+            args.steps = args.steps if args.steps is not None else 50
+            run_ours(args)
 
 
 if __name__ == "__main__":
