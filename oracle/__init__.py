@@ -134,11 +134,13 @@ def w4a16_threaded(a, packed, scales, M: int, N: int, K: int, group: int = 32):
     return c, int(used)
 
 
-def w4a16_f64(a, packed, scales, M: int, N: int, K: int, group: int = 32) -> np.ndarray:
+def w4a16_f64(a, packed, scales, M: int, N: int, K: int, group: int = 32, weights_f16: bool = False) -> np.ndarray:
+    """f64-accumulated result.  weights_f16: the weights are first rounded to f16, the operand a
+    tensor-core path multiplies with (dequant_q4_to_f16, quantize.rs:534-571)."""
     a = _f32(a)
     c = np.empty((M, N), dtype=np.float64)
-    lib().twmo_w4a16_f64acc(_p(a), _p(packed), _p(scales), _p(c), C.c_int(M), C.c_int(N),
-                            C.c_int(K), C.c_int(group))
+    fn = lib().twmo_w4a16_f64acc_w16 if weights_f16 else lib().twmo_w4a16_f64acc
+    fn(_p(a), _p(packed), _p(scales), _p(c), C.c_int(M), C.c_int(N), C.c_int(K), C.c_int(group))
     return c
 
 

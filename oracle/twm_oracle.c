@@ -332,6 +332,28 @@ void twmo_w4a16_f64acc(const float *a, const uint8_t *packed, const uint16_t *sc
         }
 }
 
+/* f64-accumulate result with the weights first rounded to f16, fp16_rn(f32(scale) * (nibble - 8)):
+ * the operand a tensor-core path feeds its MMA (what dequant_q4_to_f16 produces,
+ * crates/kernels/src/quantize.rs:534-571).  Adjudicator for such a path. */
+void twmo_w4a16_f64acc_w16(const float *a, const uint8_t *packed, const uint16_t *scales, double *c,
+                           int M, int N, int K, int group)
+{
+#ifdef _OPENMP
+#pragma omp parallel for schedule(static)
+#endif
+    for (long n = 0; n < N; n++)
+        for (long m = 0; m < M; m++) {
+            double sum = 0.0;
+            for (long k = 0; k < K; k++) {
+                float w32 = twmo_f16_to_f32(scales[(k / group) * (long)N + n]) *
+                            (float)(nibble_at(packed, N, k, n) - 8);
+                double w = (double)twmo_f16_to_f32(twmo_f32_to_f16(w32));
+                sum += (double)a[m * K + k] * w;
+            }
+            c[m * N + n] = sum;
+        }
+}
+
 /* The reference's M=1 CUDA kernel restated operation for operation for a K
  * range of 32-blocks [g0,g1): per block gdot = sum_j fma(A[32g+j], nib_j-8, gdot)
  * in increasing j, then dot = fma(gdot, scale, dot)

@@ -1,44 +1,40 @@
-// twm_gemm_tc.cuh — the tcgen05 / TMEM W4A16 kernel (FP16 activations).
+// twm_gemm_tc.cuh — the tcgen05 / TMEM W4A16 kernel (FP16 activations, M >= 9).
 //
 // The contraction C[m][n] = sum_k A[m][k] * w[k][n] runs on the 5th-generation
 // tensor cores with the roles swapped: the 128 weight columns of a CTA are the
 // MMA's M dimension (one TMEM lane per column), the activation rows are its N
-// dimension (padded to NB), and K advances 16 at a time.  There is no
-// counterpart in the reference: its only batched W4A16 kernel is a 32x32 SIMT
-// tile kernel on another layout (crates/kernels/src/quantize.rs:186-246), and
-// its TW-Marlin kernel is M=1 only (quantize.rs:1186-1298).  Same result
-// definition as those: w = f32(scale) * (nibble - 8), FP32 accumulation.
+// dimension (padded to NB = 16, 32 or 64), and K advances 16 at a time.  There
+// is no counterpart in the reference: its only batched W4A16 kernel is a 32x32
+// SIMT tile kernel on another layout (crates/kernels/src/quantize.rs:186-246),
+// and its TW-Marlin kernel is M=1 only (quantize.rs:1186-1298).  The MMA's
+// weight operand is fp16_rn(f32(scale) * (nibble - 8)), i.e. exactly what the
+// reference's dequant_q4_to_f16 produces (quantize.rs:534-571); accumulation
+// is FP32 in tensor memory over the whole K slice.
 //
 // Data path per CTA (128 columns x a K slice):
-//   warp 0       streams packed rows into a shared-memory ring with 1-D bulk
-//                copies (TMA unit, mbarrier completion; no multicast).
-//   warps 4-7    "dequant": each thread owns one column = one TMEM lane.  It
-//                reads its 16-byte block (one 128-bit shared load, conflict
-//                free) and turns the four u32 words into sixteen half2
-//                registers with five integer ops per word, no conversion and
-//                no floating-point op: a nibble left in place in a 16-bit half,
-//                `v & 0x000F000F` or `v & 0x00F000F0`, IS the FP16 subnormal
-//                q * 2^-24 (resp. q * 2^-20) exactly.  tcgen05.st puts the
-//                registers into TMEM as the MMA's A operand.  The weights never
-//                go back to shared memory.
-//   warps 2-3    stage the activations of the slice into shared memory as the
-//                MMA's B operand (K-major core matrices, no swizzle), in the K
-//                order the nibble extraction produces, and compute the block
-//                sums of A that fold the "-8" of every nibble.
-//   warp 1       one thread issues tcgen05.mma (A from TMEM, B from shared
-//                memory, D in TMEM): two per 32-block, one for the 2^-24
-//                nibbles and one for the 2^-20 nibbles, each into the block's
-//                own accumulator (no accumulate chains).  One tcgen05.commit
-//                per block tells the dequant warps that the slot's A operand is
-//                consumed and the epilogue that its accumulators are complete.
-//   warps 8-11   epilogue: read each block's two accumulators (tcgen05.ld),
-//                combine them into the scale group's sum, and at every group
-//                boundary subtract 8*sum(A), multiply by the group's FP32 scale
-//                and add to the running total in registers.  Products are exact
-//                (4-bit x 11-bit) and the scale is applied in FP32, as in the
-//                reference's kernel.
+//   warp 0       streams packed rows into a shared-memory ring: one tiled TMA
+//                load per stage of four 32-blocks (no multicast), 1-D bulk
+//                copies row by row for ragged stages.
+//   warps 4-11   "dequant", two sets of four warps taking alternate blocks;
+//                each thread owns one column = one TMEM lane.  It reads its
+//                16-byte block (one conflict-free 128-bit shared load); per u32
+//                word one shift and four LOP3 `(v & mask) | 0x64006400` give the
+//                FP16 pairs (1024 + q) resp. (1024 + 16 q); one HSUB2 / HFMA2
+//                makes them q - 8 exactly and one HMUL2 applies the group's
+//                scale.  tcgen05.st writes the sixteen registers into tensor
+//                memory as the MMA's A operand: the weights never go back to
+//                shared memory.
+//   warps 2-3    stage the slice's activations into shared memory as the MMA's
+//                B operand (K-major 8x16-byte core matrices, no swizzle), in the
+//                K order the nibble extraction produces (k0,k4,k1,k5,k2,k6,k3,k7).
+//   warp 1       one thread issues tcgen05.mma.cta_group::1.kind::f16 (A from
+//                TMEM, B from shared memory, D in TMEM), two per 32-block, all
+//                accumulating into the CTA's one [128 x NB] FP32 accumulator;
+//                tcgen05.commit frees the A slot and, at the end, releases D.
+//   warps 4-7    after their last block: epilogue, tcgen05.ld of D, FP16/FP32
+//                store or split-K partial.
 // Split-K finish and the programmatic-dependent-launch rules are the same as
-// in the streaming kernel (twm_gemv_simt.cuh).
+// in the streaming kernels.
 #pragma once
 
 #include "twm_common.cuh"
@@ -49,36 +45,36 @@ namespace tc {
 constexpr int NT = 128;               // columns per CTA = MMA M = TMEM lanes
 constexpr int WSTAGE_BLOCKS = 4;      // 32-blocks per ring stage (8 KB)
 constexpr int WSTAGES = 8;            // ring depth: 64 KB in flight per CTA
-constexpr int SLOTS = 5;              // TMEM slots: one 32-block's A operand + its two accumulators each
+constexpr int SLOTS = 8;              // TMEM slots holding one dequantised 32-block (16 columns) each
 constexpr int THREADS = 12 * 32;
-constexpr int ASUM_CAP = 2048;        // floats: (blocks in the K slice) * MV must fit
 constexpr int B_BUF_BYTES = 16384;    // one staged activation chunk
 constexpr int EPI_THREADS = 128;
 constexpr int STAGER_THREADS = 64;
+constexpr int DEQ_SETS = 2;           // dequant warp sets, alternate blocks
 
 template <int NB>
 struct Cfg {
     static constexpr int SLICE_BYTES = NB * 32;                     // NB rows x 16 K-slots x 2 B
-    static constexpr int BLOCK_B_BYTES = 2 * SLICE_BYTES;           // "lo" and "hi" slices of a 32-block
+    static constexpr int BLOCK_B_BYTES = 2 * SLICE_BYTES;           // the two K=16 slices of a 32-block
     static constexpr int CHUNK_BLOCKS = B_BUF_BYTES / BLOCK_B_BYTES;   // 32-blocks per staged chunk
     static constexpr int A_COL0 = 0;                                // A slot s: columns [16 s, 16 s + 16)
-    static constexpr int D_COL0 = SLOTS * 16;                       // D slot s: lo at D_COL0 + 2 NB s, hi NB further
-    static constexpr int USED_COLS = SLOTS * (16 + 2 * NB);
+    static constexpr int D_COL0 = SLOTS * 16;                       // the accumulator: NB columns
+    static constexpr int USED_COLS = SLOTS * 16 + NB;
     static constexpr int TMEM_COLS = USED_COLS <= 256 ? 256 : 512;
     static_assert(USED_COLS <= 512, "tensor memory holds 512 columns");
+    static_assert(CHUNK_BLOCKS >= 2 && (CHUNK_BLOCKS % 2) == 0, "chunk geometry");
 };
 
 struct Smem {
     alignas(128) uint8_t packed[WSTAGES][WSTAGE_BLOCKS * NT * kBlockBytes];
     alignas(128) uint8_t b[2][B_BUF_BYTES];
-    alignas(16) float asum8[ASUM_CAP]; // [block in slice][MV]: -8 * sum of the block's activations
     alignas(8) uint64_t w_full[WSTAGES];
     alignas(8) uint64_t w_empty[WSTAGES];
     alignas(8) uint64_t a_full[SLOTS];     // dequant -> MMA: the slot's A operand is in tensor memory
-    alignas(8) uint64_t mma_done[SLOTS];   // MMA (commit) -> dequant and epilogue: A is consumed, D is complete
-    alignas(8) uint64_t d_empty[SLOTS];    // epilogue -> MMA: the slot's accumulators are read out
+    alignas(8) uint64_t a_empty[SLOTS];    // MMA (commit) -> dequant: the slot's A operand is consumed
     alignas(8) uint64_t b_full[2];
     alignas(8) uint64_t b_empty[2];
+    alignas(8) uint64_t d_full;            // MMA (commit) -> epilogue: the accumulator is complete
     uint32_t tmem_base;
     int abort_flag;
     int is_last;
@@ -159,10 +155,10 @@ __device__ __forceinline__ bool wait_uniform(uint64_t* bar, uint32_t parity, vol
     return __all_sync(0xffffffffu, got);
 }
 
-// NB = MMA N (activation rows padded), MV = rows the epilogue carries (power of two >= M, <= NB)
-template <int NB, int MV>
+// NB = MMA N (activation rows padded to 16, 32 or 64)
+template <int NB>
 __global__ void __launch_bounds__(THREADS, (Cfg<NB>::TMEM_COLS <= 256) ? 2 : 1)
-gemm_kernel(const GemmParams p)
+gemm_kernel(const __grid_constant__ GemmParams p)
 {
     using C = Cfg<NB>;
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -176,15 +172,13 @@ gemm_kernel(const GemmParams p)
     const int b0 = blockIdx.y * p.blocks_per_split;
     const int b1 = min(p.nkb, b0 + p.blocks_per_split);
     const int total_blocks = b1 - b0;
-    const int gmask = p.group / kBlockK - 1;                 // 32-blocks per scale group (1 or 4), minus one
     const int gshift = (p.group == 128) ? 2 : 0;
 
     if (tid == 0) {
-        for (int s = 0; s < WSTAGES; ++s) { mbar_init(&sm.w_full[s], 1); mbar_init(&sm.w_empty[s], 4); }
-        for (int s = 0; s < SLOTS; ++s) {
-            mbar_init(&sm.a_full[s], 4); mbar_init(&sm.mma_done[s], 1); mbar_init(&sm.d_empty[s], 4);
-        }
+        for (int s = 0; s < WSTAGES; ++s) { mbar_init(&sm.w_full[s], 1); mbar_init(&sm.w_empty[s], 4 * DEQ_SETS); }
+        for (int s = 0; s < SLOTS; ++s) { mbar_init(&sm.a_full[s], 4); mbar_init(&sm.a_empty[s], 1); }
         for (int s = 0; s < 2; ++s) { mbar_init(&sm.b_full[s], STAGER_THREADS / 32); mbar_init(&sm.b_empty[s], 1); }
+        mbar_init(&sm.d_full, 1);
         sm.abort_flag = 0;
         sm.is_last = 0;
         mbar_fence_init();
@@ -198,24 +192,29 @@ gemm_kernel(const GemmParams p)
     // while an earlier kernel's CTA may still hold this SM's tensor memory.
     const uint8_t* packed = p.packed;
     const int n_wstages = (total_blocks + WSTAGE_BLOCKS - 1) / WSTAGE_BLOCKS;
-    auto issue_stage = [&](int st) {
+    auto issue_stage = [&](int st) {                       // executed by the whole warp
         const int slot = st % WSTAGES;
         const int bstart = b0 + st * WSTAGE_BLOCKS;
         const int nb = min(WSTAGE_BLOCKS, b1 - bstart);
-        mbar_arrive_expect_tx(&sm.w_full[slot], (uint32_t)nb * cols * kBlockBytes);
-        for (int r = 0; r < nb; ++r)
-            bulk_g2s(&sm.packed[slot][r * NT * kBlockBytes],
-                     packed + ((size_t)(bstart + r) * p.N + n0) * kBlockBytes,
+        const bool tiled = (p.map_rows == WSTAGE_BLOCKS) && (nb == WSTAGE_BLOCKS) && (p.packed_offsets == nullptr);
+        if (lane == 0) {
+            mbar_arrive_expect_tx(&sm.w_full[slot], tiled ? (uint32_t)WSTAGE_BLOCKS * NT * kBlockBytes
+                                                          : (uint32_t)nb * cols * kBlockBytes);
+            if (tiled) tma_load_2d(&sm.packed[slot][0], &p.packed_map, n0 * 2, bstart, &sm.w_full[slot]);
+        }
+        __syncwarp();
+        if (!tiled && lane < nb)
+            bulk_g2s(&sm.packed[slot][lane * NT * kBlockBytes],
+                     packed + ((size_t)(bstart + lane) * p.N + n0) * kBlockBytes,
                      (uint32_t)cols * kBlockBytes, &sm.w_full[slot]);
+        __syncwarp();
     };
     if (warp == 0) {
         if (p.packed_offsets != nullptr) {
             pdl_wait_prior_grids();                  // the offset table may come from the kernel before
             packed += p.packed_offsets[p.expert_idx];
         }
-        if (lane == 0)
-            for (int st = 0; st < min(n_wstages, WSTAGES); ++st) issue_stage(st);
-        __syncwarp();
+        for (int st = 0; st < min(n_wstages, WSTAGES); ++st) issue_stage(st);
     } else if (warp == 1) {
         tmem_alloc(&sm.tmem_base, C::TMEM_COLS);
         tc_fence_before();
@@ -233,58 +232,53 @@ gemm_kernel(const GemmParams p)
             PROF_BEGIN(t0);
             if (!wait_uniform(&sm.w_empty[slot], ((st / WSTAGES) - 1) & 1, abort_flag)) break;
             PROF_END(t0, 0);
-            if (lane == 0) issue_stage(st);
-            __syncwarp();
+            issue_stage(st);
         }
         PROF_FLUSH(0);
     } else if (warp == 1) {
         // ------------------------------------------------------- MMA issuer --
-        // Every 32-block gets its own pair of accumulators (no accumulate
-        // chain: back-to-back MMAs into one accumulator would each wait out the
-        // tensor pipe's latency); the epilogue adds them up.
         if (lane == 0) {
             uint32_t idesc = 0;
             idesc |= 1u << 4;                         // D format f32
             idesc |= (uint32_t)(NB >> 3) << 17;       // N
             idesc |= (uint32_t)(128 >> 4) << 24;      // M
             const uint64_t desc0[2] = {make_b_desc(smem_u32(&sm.b[0][0])), make_b_desc(smem_u32(&sm.b[1][0]))};
+            const uint32_t d_addr = tmem_base + C::D_COL0;
             PROF_DECL;
             int slot = 0, use = 0, bi = 0, chunk = 0;
+            bool ok = true;
             for (int i = 0; i < total_blocks; ++i) {
                 PROF_BEGIN(t0);
-                if (bi == 0 && !mbar_wait_bounded(&sm.b_full[chunk & 1], (chunk >> 1) & 1, abort_flag)) break;
+                if (bi == 0 && !mbar_wait_bounded(&sm.b_full[chunk & 1], (chunk >> 1) & 1, abort_flag)) { ok = false; break; }
                 PROF_END(t0, 0);
-                PROF_BEGIN(t1);
-                if (use > 0 && !mbar_wait_bounded(&sm.d_empty[slot], (use - 1) & 1, abort_flag)) break;
-                PROF_END(t1, 1);
                 PROF_BEGIN(t2);
-                if (!mbar_wait_bounded(&sm.a_full[slot], use & 1, abort_flag)) break;
+                if (!mbar_wait_bounded(&sm.a_full[slot], use & 1, abort_flag)) { ok = false; break; }
                 PROF_END(t2, 2);
                 PROF_BEGIN(t3);
                 tc_fence_after();
                 const uint32_t a_addr = tmem_base + C::A_COL0 + slot * 16;
-                const uint32_t d_addr = tmem_base + C::D_COL0 + slot * 2 * NB;
                 // descriptor start-address field counts 16-byte units
                 const uint64_t bd = desc0[chunk & 1] + (uint64_t)((bi * C::BLOCK_B_BYTES) >> 4);
-                tc_mma_ts(d_addr, a_addr, bd, idesc, 0u);
-                tc_mma_ts(d_addr + NB, a_addr + 8, bd + (uint64_t)(C::SLICE_BYTES >> 4), idesc, 0u);
+                tc_mma_ts(d_addr, a_addr, bd, idesc, i == 0 ? 0u : 1u);
+                tc_mma_ts(d_addr, a_addr + 8, bd + (uint64_t)(C::SLICE_BYTES >> 4), idesc, 1u);
                 PROF_END(t3, 3);
                 PROF_BEGIN(t4);
-                tc_commit(&sm.mma_done[slot]);
+                tc_commit(&sm.a_empty[slot]);
                 const bool chunk_end = (bi == C::CHUNK_BLOCKS - 1) || (i == total_blocks - 1);
                 if (chunk_end) tc_commit(&sm.b_empty[chunk & 1]);
                 PROF_END(t4, 4);
                 if (++slot == SLOTS) { slot = 0; ++use; }
                 if (chunk_end) { bi = 0; ++chunk; } else { ++bi; }
             }
+            if (ok) tc_commit(&sm.d_full);
             PROF_FLUSH(1);
         }
         __syncwarp();
     } else if (warp == 2 || warp == 3) {
         // ---------------------------------------------- activation stagers --
-        // One item = 8 consecutive K of one row (one 16-byte load).  The loads of
-        // a chunk are issued before the wait for its buffer, so their latency
-        // hides behind the MMAs that still read the buffer's previous contents.
+        // One item = 8 consecutive K of one row (one 16-byte load), stored as one 16-byte core-matrix
+        // row in the order k0,k4,k1,k5,k2,k6,k3,k7.  The loads of a chunk are issued before the wait
+        // for its buffer, so their latency hides behind the MMAs still reading the buffer.
         pdl_wait_prior_grids();
         const int st_tid = tid - 64;
         const __half* A = reinterpret_cast<const __half*>(p.a);
@@ -298,7 +292,7 @@ gemm_kernel(const GemmParams p)
             const int use = chunk >> 1;
             const int cb0 = chunk * C::CHUNK_BLOCKS;
             const int cb = min(C::CHUNK_BLOCKS, total_blocks - cb0);
-            const int items = p.M * cb * 4;
+            const int items = p.M * cb * 4;                              // item = (m * cb + bi) * 4 + w
             bool waited = false;
             for (int base = 0; base < items; base += STAGER_THREADS * PF) {
                 uint4 x[PF];
@@ -331,30 +325,20 @@ gemm_kernel(const GemmParams p)
 #pragma unroll
                 for (int u = 0; u < PF; ++u) {
                     const int it = base + u * STAGER_THREADS + st_tid;
-                    float s = 0.0f;
-                    int m = 0, bi = 0;
                     if (it < items) {
-                        m = it / (cb * 4);
+                        const int m = it / (cb * 4);
                         const int rem = it - m * (cb * 4);
-                        bi = rem >> 2;
-                        const int w = rem & 3;
-                        // K order of the "lo" slice: k0,k4,k2,k6 ; of the "hi" slice: k1,k5,k3,k7
-                        uint2 lo, hi;
-                        lo.x = __byte_perm(x[u].x, x[u].z, 0x5410); lo.y = __byte_perm(x[u].y, x[u].w, 0x5410);
-                        hi.x = __byte_perm(x[u].x, x[u].z, 0x7632); hi.y = __byte_perm(x[u].y, x[u].w, 0x7632);
-                        uint8_t* dst = &sm.b[buf][bi * C::BLOCK_B_BYTES + (m >> 3) * 256 + (w >> 1) * 128 + (m & 7) * 16 + (w & 1) * 8];
-                        *reinterpret_cast<uint2*>(dst) = lo;
-                        *reinterpret_cast<uint2*>(dst + C::SLICE_BYTES) = hi;
-                        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&x[u].x));
-                        const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&x[u].y));
-                        const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&x[u].z));
-                        const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&x[u].w));
-                        s = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+                        const int bi = rem >> 2;
+                        const int w = rem & 3;              // words 0,1 feed the block's first MMA, words 2,3 its second
+                        uint4 o;
+                        o.x = __byte_perm(x[u].x, x[u].z, 0x5410);      // k0,k4
+                        o.y = __byte_perm(x[u].x, x[u].z, 0x7632);      // k1,k5
+                        o.z = __byte_perm(x[u].y, x[u].w, 0x5410);      // k2,k6
+                        o.w = __byte_perm(x[u].y, x[u].w, 0x7632);      // k3,k7
+                        uint8_t* dst = &sm.b[buf][bi * C::BLOCK_B_BYTES + (w >> 1) * C::SLICE_BYTES + (m >> 3) * 256 +
+                                                  (w & 1) * 128 + (m & 7) * 16];
+                        *reinterpret_cast<uint4*>(dst) = o;
                     }
-                    // four consecutive items (lanes) are the four words of one block
-                    s += __shfl_xor_sync(0xffffffffu, s, 1);
-                    s += __shfl_xor_sync(0xffffffffu, s, 2);
-                    if (it < items && (it & 3) == 0) sm.asum8[(cb0 + bi) * MV + m] = -8.0f * s;
                 }
                 PROF_END(t2, 2);
             }
@@ -364,19 +348,37 @@ gemm_kernel(const GemmParams p)
             if (lane == 0) mbar_arrive(&sm.b_full[buf]);
         }
         PROF_FLUSH(2);
-    } else if (warp >= 4 && warp < 8) {
+    } else {
         // ------------------------------------------------------- dequant --
+        const int set = (warp - 4) >> 2;                       // 0: even blocks, 1: odd blocks
         const int quarter = warp & 3;
         const int col = quarter * 32 + lane;
+        const int n = n0 + col;
+        const bool owner = n < p.N;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + C::A_COL0;
+        const uint16_t* scales = p.scales;
+        if (p.scales_offsets != nullptr) {
+            pdl_wait_prior_grids();                  // the offset table may come from the kernel before
+            scales += p.scales_offsets[p.expert_idx];
+        }
         PROF_DECL;
-        int slot = 0, use = 0;
-        for (int i = 0; i < total_blocks; ++i) {
+        bool ok = true;
+        int cur_group = -1;
+        __half2 s2 = __float2half2_rn(0.0f);
+        const __half2 k1032 = __float2half2_rn(1032.0f), k16th = __float2half2_rn(0.0625f), k72 = __float2half2_rn(-72.0f);
+        for (int i = set; i < total_blocks; i += DEQ_SETS) {
             const int st = i / WSTAGE_BLOCKS;
             const int r = i - st * WSTAGE_BLOCKS;
             const int wslot = st % WSTAGES;
+            const int b = b0 + i;
+            if ((b >> gshift) != cur_group) {                  // the group's FP16 scale of this column, as a pair
+                cur_group = b >> gshift;
+                const uint16_t sb = owner ? __ldg(scales + (size_t)cur_group * p.N + n) : (uint16_t)0;
+                s2 = __half2half2(__ushort_as_half(sb));
+            }
             PROF_BEGIN(t0);
-            if (r == 0 && !wait_uniform(&sm.w_full[wslot], (st / WSTAGES) & 1, abort_flag)) break;
+            // this set's first block of a stage: r = set, since a stage holds an even number of blocks
+            if (r < DEQ_SETS && !wait_uniform(&sm.w_full[wslot], (st / WSTAGES) & 1, abort_flag)) { ok = false; break; }
             PROF_END(t0, 0);
             PROF_BEGIN(t1);
             const uint4 v = lds128(&sm.packed[wslot][(r * NT + col) * kBlockBytes]);
@@ -386,18 +388,30 @@ gemm_kernel(const GemmParams p)
             for (int w = 0; w < 4; ++w) {
                 const uint32_t x = words[w];
                 const uint32_t x8 = x >> 8;
-                regs[2 * w] = x & 0x000F000Fu;          // (k0, k4) * 2^-24
-                regs[2 * w + 1] = x8 & 0x000F000Fu;     // (k2, k6) * 2^-24
-                regs[8 + 2 * w] = x & 0x00F000F0u;      // (k1, k5) * 2^-20
-                regs[8 + 2 * w + 1] = x8 & 0x00F000F0u; // (k3, k7) * 2^-20
+                uint32_t t0b = (x & 0x000F000Fu) | 0x64006400u;      // 1024 + (k0, k4)
+                uint32_t t1b = (x & 0x00F000F0u) | 0x64006400u;      // 1024 + 16 (k1, k5)
+                uint32_t t2b = (x8 & 0x000F000Fu) | 0x64006400u;     // 1024 + (k2, k6)
+                uint32_t t3b = (x8 & 0x00F000F0u) | 0x64006400u;     // 1024 + 16 (k3, k7)
+                const __half2 q0 = __hsub2(*reinterpret_cast<__half2*>(&t0b), k1032);          // q - 8, exact
+                const __half2 q1 = __hfma2(*reinterpret_cast<__half2*>(&t1b), k16th, k72);
+                const __half2 q2 = __hsub2(*reinterpret_cast<__half2*>(&t2b), k1032);
+                const __half2 q3 = __hfma2(*reinterpret_cast<__half2*>(&t3b), k16th, k72);
+                const __half2 w0 = __hmul2(q0, s2), w1 = __hmul2(q1, s2), w2 = __hmul2(q2, s2), w3 = __hmul2(q3, s2);
+                regs[4 * w + 0] = *reinterpret_cast<const uint32_t*>(&w0);
+                regs[4 * w + 1] = *reinterpret_cast<const uint32_t*>(&w1);
+                regs[4 * w + 2] = *reinterpret_cast<const uint32_t*>(&w2);
+                regs[4 * w + 3] = *reinterpret_cast<const uint32_t*>(&w3);
             }
-            if (r == WSTAGE_BLOCKS - 1 || i == total_blocks - 1) {
+            // this set's last block of the stage (or of the slice): the stage is read out
+            if (r + DEQ_SETS >= WSTAGE_BLOCKS || i + DEQ_SETS >= total_blocks) {
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&sm.w_empty[wslot]);      // ring stage read out
+                if (lane == 0) mbar_arrive(&sm.w_empty[wslot]);
             }
             PROF_END(t1, 1);
+            const int slot = i % SLOTS;
+            const int use = i / SLOTS;
             PROF_BEGIN(t2);
-            if (use > 0 && !wait_uniform(&sm.mma_done[slot], (use - 1) & 1, abort_flag)) break;
+            if (use > 0 && !wait_uniform(&sm.a_empty[slot], (use - 1) & 1, abort_flag)) { ok = false; break; }
             PROF_END(t2, 2);
             PROF_BEGIN(t3);
             tc_fence_after();
@@ -407,120 +421,71 @@ gemm_kernel(const GemmParams p)
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.a_full[slot]);
             PROF_END(t3, 3);
-            if (++slot == SLOTS) { slot = 0; ++use; }
         }
         PROF_FLUSH(3);
-    } else if (warp >= 8) {
-        // ------------------------------------------------------- epilogue --
-        pdl_wait_prior_grids();
-        const int quarter = warp & 3;
-        const int col = quarter * 32 + lane;
-        const int n = n0 + col;
-        const bool owner = n < p.N;
-        const uint16_t* scales = p.scales;
-        if (p.scales_offsets != nullptr) scales += p.scales_offsets[p.expert_idx];
-        const uint32_t lane_d = tmem_base + ((uint32_t)(quarter * 32) << 16) + C::D_COL0;
-        float tot[MV], gsum[MV], a8[MV];
-#pragma unroll
-        for (int m = 0; m < MV; ++m) { tot[m] = 0.0f; gsum[m] = 0.0f; a8[m] = 0.0f; }
-        PROF_DECL;
-        uint16_t s_bits = owner ? scales[(size_t)(b0 >> gshift) * p.N + n] : (uint16_t)0;
-        uint16_t s_next = s_bits;
-        int slot = 0, use = 0;
-        for (int i = 0; i < total_blocks; ++i) {
-            const int b = b0 + i;
-            const bool first_in_group = (i == 0) || ((b & gmask) == 0);
-            const bool last_in_group = (i == total_blocks - 1) || (((b + 1) & gmask) == 0);
-            if (first_in_group) {
-                s_bits = s_next;
-                const int g_next = (b >> gshift) + 1;
-                if (owner && (g_next << gshift) < b1) s_next = scales[(size_t)g_next * p.N + n];   // prefetch
-            }
-            PROF_BEGIN(t0);
-            if (!wait_uniform(&sm.mma_done[slot], use & 1, abort_flag)) break;
-            PROF_END(t0, 0);
-            PROF_BEGIN(t1);
-            tc_fence_after();
-            uint32_t lo[MV], hi[MV];
-            tmem_ld<MV>(lane_d + slot * 2 * NB, lo);
-            tmem_ld<MV>(lane_d + slot * 2 * NB + NB, hi);
-            tmem_wait_ld();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sm.d_empty[slot]);
-            PROF_END(t1, 1);
-            PROF_BEGIN(t2);
-            // lo holds sum(a*q) * 2^-24, hi holds sum(a*q) * 2^-20
-#pragma unroll
-            for (int m = 0; m < MV; ++m) {
-                gsum[m] += fmaf(__uint_as_float(lo[m]), 16.0f, __uint_as_float(hi[m]));
-                a8[m] += sm.asum8[i * MV + m];
-            }
-            if (last_in_group) {
-                const float s = f16_bits_to_f32(s_bits);
-                const float s20 = s * 1048576.0f;             // 2^20
-#pragma unroll
-                for (int m = 0; m < MV; ++m) {
-                    tot[m] = fmaf(s20, gsum[m], tot[m]);
-                    tot[m] = fmaf(s, a8[m], tot[m]);
-                    gsum[m] = 0.0f;
-                    a8[m] = 0.0f;
-                }
-            }
-            PROF_END(t2, 2);
-            if (++slot == SLOTS) { slot = 0; ++use; }
-        }
-        PROF_FLUSH(4);
 
-        // --------------------------------------------- store / split-K finish --
-        named_bar_sync(2, EPI_THREADS);
-        const bool aborted = (*abort_flag != 0);
-        auto store_c = [&](int m, float v) {
-            const size_t off = (size_t)m * p.ldc + n;
-            if (p.c_is_f16) {
-                __half* cp = reinterpret_cast<__half*>(p.c);
-                if (p.accumulate) v += __half2float(cp[off]);
-                cp[off] = __float2half_rn(v);
-            } else {
-                float* cp = reinterpret_cast<float*>(p.c);
-                if (p.accumulate) v += cp[off];
-                cp[off] = v;
-            }
-        };
-        if (!aborted) {
-            if (p.splits == 1) {
-                if (owner) {
-#pragma unroll
-                    for (int m = 0; m < MV; ++m)
-                        if (m < p.M) store_c(m, tot[m]);
+        if (set == 0) {
+            // --------------------------------------------------- epilogue --
+            // (a K slice with a single block leaves set 1 idle; stages whose odd block is missing are
+            //  released by set 0 alone: see the w_empty arrival count below)
+            pdl_wait_prior_grids();
+            bool have = ok && wait_uniform(&sm.d_full, 0, abort_flag);
+            named_bar_sync(2, EPI_THREADS);
+            have = have && (*abort_flag == 0);
+            const uint32_t lane_d = tmem_base + ((uint32_t)(quarter * 32) << 16) + C::D_COL0;
+            auto store_c = [&](int m, float vv) {
+                const size_t off = (size_t)m * p.ldc + n;
+                if (p.c_is_f16) {
+                    __half* cp = reinterpret_cast<__half*>(p.c);
+                    if (p.accumulate) vv += __half2float(cp[off]);
+                    cp[off] = __float2half_rn(vv);
+                } else {
+                    float* cp = reinterpret_cast<float*>(p.c);
+                    if (p.accumulate) vv += cp[off];
+                    cp[off] = vv;
                 }
-            } else {
-                if (owner) {
+            };
+            if (have) {
+                tc_fence_after();
 #pragma unroll
-                    for (int m = 0; m < MV; ++m)
-                        if (m < p.M) p.ws_partials[((size_t)blockIdx.y * p.M + m) * p.N + n] = tot[m];
-                }
-                __threadfence();
-                named_bar_sync(2, EPI_THREADS);
-                if (tid == 8 * 32) {
-                    const unsigned prev = atomicAdd(&p.ws_counters[blockIdx.x], 1u);
-                    sm.is_last = (prev == (unsigned)(p.splits - 1));
-                }
-                named_bar_sync(2, EPI_THREADS);
-                if (sm.is_last) {
-                    __threadfence();
-                    if (owner) {
+                for (int c0 = 0; c0 < NB; c0 += 16) {
+                    if (c0 < p.M) {                                        // warp-uniform
+                        uint32_t d[16];
+                        tmem_ld<16>(lane_d + c0, d);
+                        tmem_wait_ld();
+                        if (owner) {
 #pragma unroll
-                        for (int m = 0; m < MV; ++m) {
-                            if (m < p.M) {
-                                float s = 0.0f;
-                                for (int sp = 0; sp < p.splits; ++sp)
-                                    s += ld_cg_f32(&p.ws_partials[((size_t)sp * p.M + m) * p.N + n]);
-                                store_c(m, s);
+                            for (int j = 0; j < 16; ++j) {
+                                const int m = c0 + j;
+                                if (m < p.M) {
+                                    if (p.splits == 1) store_c(m, __uint_as_float(d[j]));
+                                    else p.ws_partials[((size_t)blockIdx.y * p.M + m) * p.N + n] = __uint_as_float(d[j]);
+                                }
                             }
                         }
                     }
-                    if (tid == 8 * 32) atomicExch(&p.ws_counters[blockIdx.x], 0u);
+                }
+                tc_fence_before();
+                if (p.splits > 1) {
+                    __threadfence();
+                    named_bar_sync(2, EPI_THREADS);
+                    if (tid == 4 * 32) {
+                        const unsigned prev = atomicAdd(&p.ws_counters[blockIdx.x], 1u);
+                        sm.is_last = (prev == (unsigned)(p.splits - 1));
+                    }
+                    named_bar_sync(2, EPI_THREADS);
+                    if (sm.is_last) {
+                        __threadfence();
+                        if (owner) {
+                            for (int m = 0; m < p.M; ++m) {
+                                float acc = 0.0f;
+                                for (int sp = 0; sp < p.splits; ++sp)
+                                    acc += ld_cg_f32(&p.ws_partials[((size_t)sp * p.M + m) * p.N + n]);
+                                store_c(m, acc);
+                            }
+                        }
+                        if (tid == 4 * 32) atomicExch(&p.ws_counters[blockIdx.x], 0u);
+                    }
                 }
             }
         }

@@ -77,11 +77,9 @@ twm_status ensure_device(int* sm_count_out)
                 if (r == cudaSuccess)
                     r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(twm::tc::Smem));
             };
-            raise_tc((const void*)twm::tc::gemm_kernel<16, 1>);
-            raise_tc((const void*)twm::tc::gemm_kernel<16, 2>);
-            raise_tc((const void*)twm::tc::gemm_kernel<16, 4>);
-            raise_tc((const void*)twm::tc::gemm_kernel<16, 8>);
-            raise_tc((const void*)twm::tc::gemm_kernel<16, 16>);
+            raise_tc((const void*)twm::tc::gemm_kernel<16>);
+            raise_tc((const void*)twm::tc::gemm_kernel<32>);
+            raise_tc((const void*)twm::tc::gemm_kernel<64>);
             auto raise_mma = [&](const void* fn) {
                 if (r == cudaSuccess)
                     r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(twm::mma::Smem));
@@ -179,9 +177,9 @@ void choose_splits(int n_tiles, int nkb, int slots, int max_bps, int align, int 
 }
 
 int mmax_for(int M) { return M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : 8)); }
-int mv_for(int M) { return M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : (M <= 8 ? 8 : 16))); }
+constexpr int kTcRows = 64;      // activation rows one tcgen05 launch carries
 
-twm_status launch_tc(const twm::GemmParams& p, int mv, dim3 grid, bool pdl, cudaStream_t stream)
+twm_status launch_tc(const twm::GemmParams& p, int rows, dim3 grid, bool pdl, cudaStream_t stream)
 {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
@@ -195,13 +193,9 @@ twm_status launch_tc(const twm::GemmParams& p, int mv, dim3 grid, bool pdl, cuda
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
     cudaError_t e;
-    switch (mv) {
-        case 1: e = cudaLaunchKernelEx(&cfg, twm::tc::gemm_kernel<16, 1>, p); break;
-        case 2: e = cudaLaunchKernelEx(&cfg, twm::tc::gemm_kernel<16, 2>, p); break;
-        case 4: e = cudaLaunchKernelEx(&cfg, twm::tc::gemm_kernel<16, 4>, p); break;
-        case 8: e = cudaLaunchKernelEx(&cfg, twm::tc::gemm_kernel<16, 8>, p); break;
-        default: e = cudaLaunchKernelEx(&cfg, twm::tc::gemm_kernel<16, 16>, p); break;
-    }
+    if (rows <= 16) e = cudaLaunchKernelEx(&cfg, twm::tc::gemm_kernel<16>, p);
+    else if (rows <= 32) e = cudaLaunchKernelEx(&cfg, twm::tc::gemm_kernel<32>, p);
+    else e = cudaLaunchKernelEx(&cfg, twm::tc::gemm_kernel<64>, p);
     if (e != cudaSuccess) { set_error("launch tc::gemm_kernel", e); return TWM_ELAUNCH; }
     return TWM_OK;
 }
@@ -342,10 +336,10 @@ twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int split
     if (kernel == TWM_KERNEL_AUTO) kernel = (M <= 8) ? TWM_KERNEL_MMA : TWM_KERNEL_TC;
     if (kernel != TWM_KERNEL_SIMT && kernel != TWM_KERNEL_TC && kernel != TWM_KERNEL_MMA) return TWM_EINVAL;
     // rows one launch carries; more rows are served by further launches
-    const int rows = std::min(M, kernel == TWM_KERNEL_TC ? 16 : 8);
+    const int rows = std::min(M, kernel == TWM_KERNEL_TC ? kTcRows : 8);
     const int n_tiles = (N + twm::simt::NT - 1) / twm::simt::NT;
     const int slots = sm_count * ((kernel != TWM_KERNEL_SIMT || mmax_for(rows) <= 4) ? 2 : 1);
-    const int max_bps = kernel == TWM_KERNEL_TC ? twm::tc::ASUM_CAP / mv_for(rows) : nkb;
+    const int max_bps = nkb;
     const int align = (kernel == TWM_KERNEL_MMA) ? group_size / 32 : 1;   // whole scale groups per slice
     // up to two rows on the streaming MMA kernel: K slices add up inside a cluster (at most 16 slices)
     const bool can_cluster = (kernel == TWM_KERNEL_MMA) && rows <= twm::mma::CLUSTER_ROWS;
@@ -421,12 +415,13 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
     cudaStream_t stream = (cudaStream_t)stream_;
     const size_t a_elt = a->a_dtype == TWM_F16 ? 2 : 4;
     const size_t c_elt = a->c_dtype == TWM_F16 ? 2 : 4;
-    const int row_step = kernel == TWM_KERNEL_TC ? 16 : 8;
+    const int row_step = kernel == TWM_KERNEL_TC ? kTcRows : 8;
     CUtensorMap packed_map;
     int map_rows = 0;
-    if (kernel == TWM_KERNEL_MMA && a->packed_offsets == nullptr && a->N >= 128 &&
-        make_packed_map(&packed_map, a->packed, a->N, a->K / 32, twm::mma::SB))
-        map_rows = twm::mma::SB;
+    if (a->packed_offsets == nullptr && a->N >= 128 && kernel != TWM_KERNEL_SIMT) {
+        const int want = kernel == TWM_KERNEL_MMA ? twm::mma::SB : twm::tc::WSTAGE_BLOCKS;
+        if (make_packed_map(&packed_map, a->packed, a->N, a->K / 32, want)) map_rows = want;
+    }
     for (int m0 = 0; m0 < a->M; m0 += row_step) {
         const int rows = std::min(row_step, a->M - m0);
         twm::GemmParams p;
@@ -449,7 +444,7 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
         if (map_rows) p.packed_map = packed_map;
         const bool pdl = (a->flags & TWM_FLAG_PDL) != 0;
         if (kernel == TWM_KERNEL_TC)
-            st = launch_tc(p, mv_for(rows), dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
+            st = launch_tc(p, rows, dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
         else if (kernel == TWM_KERNEL_MMA)
             st = launch_mma(p, mmax_for(rows), dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
         else

@@ -17,10 +17,25 @@ DEV = "cuda"
 TOL_F16 = 1e-2
 # f32 output of the FP32-FMA kernel: only summation order differs from the oracle
 TOL_F32 = 1e-3
-# f32 output of the tcgen05 kernel: products are exact, but the tensor core's FP32 accumulator
-# aligns addends with fewer guard bits than an IEEE fused multiply-add chain (about 1e-6 of the
-# output RMS observed); still two orders below the FP16 rounding of the final store
+# f32 output of the tensor-core kernels: the tensor core's FP32 accumulator aligns addends with
+# fewer guard bits than an IEEE fused multiply-add chain (about 1e-6 of the output RMS observed);
+# still two orders below the FP16 rounding of the final store
 TOL_TC_F32 = 5e-3
+# The tcgen05 kernel multiplies with FP16 weights fp16_rn(scale * (nibble - 8)), as the reference's
+# dequantise-to-FP16 route does (quantize.rs:534-571).  It is checked tightly against the oracle
+# that rounds the weights the same way, and against the exact-weight oracle by the absolute bound
+# below (that rounding moves an output by about 2^-12 of the output RMS, whatever its own size).
+TC_ABS_VS_EXACT = 2e-3
+
+
+def _tc_ref(a, packed, scales, m, n, k, group, kernel):
+    """The adjudicating oracle for a kernel family."""
+    return oracle.w4a16_f64(a, packed, scales, m, n, k, group, weights_f16=(kernel == _lib.TWM_KERNEL_TC))
+
+
+def _abs_err_over_rms(y, ref64):
+    rms = float(np.sqrt(np.mean(np.asarray(ref64, dtype=np.float64) ** 2))) + 1e-30
+    return float(np.max(np.abs(np.asarray(y, dtype=np.float64) - ref64))) / rms
 
 
 def _to_dev(x, dtype=None):
@@ -164,8 +179,9 @@ def test_small_m_f16(m, k, n, group, kernel):
     _, packed, scales = _quantised(k, n, group, 43)
     a = seeded_activations(m, k, 0)
     y = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float16, kernel_override=kernel)
-    ref64 = oracle.w4a16_f64(a, packed, scales, m, n, k, group)
+    ref64 = _tc_ref(a, packed, scales, m, n, k, group, kernel)
     assert rel_err_floored(y, ref64) < TOL_F16
+    assert _abs_err_over_rms(y, oracle.w4a16_f64(a, packed, scales, m, n, k, group)) < TC_ABS_VS_EXACT
     # and bit-identical to rounding the f32-output run to f16 (one rounding, at the end)
     y32 = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float32, kernel_override=kernel)
     assert rel_err_floored(y32, ref64) < (TOL_F32 if kernel == _lib.TWM_KERNEL_SIMT else TOL_TC_F32)
@@ -183,7 +199,7 @@ def test_tc_kernel_slices(k, n, group, splits, kernel):
     a = seeded_activations(m, k, 1)
     y = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float32,
                   kernel_override=kernel, splits_override=splits)
-    assert rel_err_floored(y, oracle.w4a16_f64(a, packed, scales, m, n, k, group)) < TOL_TC_F32
+    assert rel_err_floored(y, _tc_ref(a, packed, scales, m, n, k, group, kernel)) < TOL_TC_F32
 
 
 def test_tc_kernel_rejects_f32_activations():
@@ -195,13 +211,45 @@ def test_tc_kernel_rejects_f32_activations():
     assert e.value.status == _lib.TWM_EINVAL
 
 
-@pytest.mark.parametrize("m", [9, 16, 19])
-def test_m_beyond_eight(m):
-    k, n, group = 512, 200, 128
+@pytest.mark.parametrize("group", [32, 128])
+@pytest.mark.parametrize("m", [9, 16, 19, 32, 33, 64, 70, 130])
+def test_m_beyond_eight(m, group):
+    """The tcgen05 kernel's three accumulator widths (16, 32, 64 rows) and more rows than one launch carries."""
+    k, n = 512, 200
     _, packed, scales = _quantised(k, n, group, 47)
     a = seeded_activations(m, k, 0)
     y = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float16)
-    assert rel_err_floored(y, oracle.w4a16_f64(a, packed, scales, m, n, k, group)) < TOL_F16
+    assert rel_err_floored(y, oracle.w4a16_f64(a, packed, scales, m, n, k, group, weights_f16=True)) < TOL_F16
+    assert _abs_err_over_rms(y, oracle.w4a16_f64(a, packed, scales, m, n, k, group)) < TC_ABS_VS_EXACT
+    # FP32 rows from the FP32-FMA kernel agree too (m > 8 there is served by several launches)
+    y32 = _run_gemm(a, packed, scales, m, n, k, group, torch.float32, torch.float32)
+    assert rel_err_floored(y32, oracle.w4a16_f64(a, packed, scales, m, n, k, group)) < TOL_F32
+
+
+def test_config2_shape_m64():
+    """configs[2] at M = 64 on the 7B gate+up shape (K=3584, N=37888), tcgen05 kernel."""
+    k, n, m, group = 3584, 37888, 64, 128
+    w = torch.randn((k, n), generator=torch.Generator(device=DEV).manual_seed(77), device=DEV) * 0.02
+    p, s = q.quantize_f32_to_tw_marlin(w, k, n, group)
+    del w
+    a = seeded_activations(m, k, 0)
+    c = torch.full((m, n), float("nan"), dtype=torch.float16, device=DEV)
+    q.gemm_tw_marlin(_to_dev(a, torch.float16), p, s, c, m, n, k, group_size=group, flags=_lib.TWM_FLAG_PDL)
+    torch.cuda.synchronize()
+    assert q.device_error() == 0
+    # a column slice against the oracle (the whole matrix would take minutes on the CPU)
+    cols = slice(12800, 12800 + 384)
+    packed = p.cpu().numpy()[:, cols].copy()
+    scales = s.cpu().numpy().view(np.uint16)[:, cols].copy()
+    ref = oracle.w4a16_f64(a, packed, scales, m, 384, k, group, weights_f16=True)
+    assert rel_err_floored(c[:, cols].float().cpu().numpy(), ref) < TOL_F16
+    # and a size-independent property on the whole output: every element written, linear in the activations
+    assert not torch.isnan(c).any()
+    c2 = torch.empty_like(c)
+    q.gemm_tw_marlin(_to_dev(2.0 * a, torch.float16), p, s, c2, m, n, k, group_size=group)
+    torch.cuda.synchronize()
+    normal = (c.abs() < 30000) & (c.abs() > 1e-3)
+    assert torch.equal(c2[normal], 2 * c[normal])
 
 
 def test_config0_shape_vs_literal_cpu_path():
