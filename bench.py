@@ -406,8 +406,8 @@ def run_tp(args):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, averaged over one layer's four kernels,
-# from the ncu capture summarised under profiles/ (None until that capture exists)
-TRAFFIC_PER_LAUNCH = None
+# from the ncu capture summarised in profiles/bench_config1_launch_list.md
+TRAFFIC_PER_LAUNCH = 30116928
 
 
 # ------------------------------------------------------- CPU baseline arm --
