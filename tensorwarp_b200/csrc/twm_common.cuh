@@ -94,6 +94,13 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         : "memory");
 }
 
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+        : "memory");
+}
+
 // ------------------------------------------- programmatic dependent launch --
 __device__ __forceinline__ void pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -203,6 +210,8 @@ struct GemmParams {
     int map_rows;                // 0 = no map (1-D bulk copies per row instead)
     int launch_id;               // development builds: index of this launch in the timeline buffer
     alignas(64) CUtensorMap packed_map;
+    // tcgen05 kernel: tensor map over the launch's permuted activations, f16 [K/8][rows][8]
+    alignas(64) CUtensorMap act_map;
 };
 
 }  // namespace twm

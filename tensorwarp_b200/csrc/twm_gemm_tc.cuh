@@ -24,9 +24,11 @@
 //                scale.  tcgen05.st writes the sixteen registers into tensor
 //                memory as the MMA's A operand: the weights never go back to
 //                shared memory.
-//   warps 2-3    stage the slice's activations into shared memory as the MMA's
-//                B operand (K-major 8x16-byte core matrices, no swizzle), in the
-//                K order the nibble extraction produces (k0,k4,k1,k5,k2,k6,k3,k7).
+//   (pre-pass)   permute_activations_kernel rewrites the launch's activation rows
+//                once into [K/8][rows][8] FP16 with the K order the nibble
+//                extraction produces inside every 8 (k0,k4,k1,k5,k2,k6,k3,k7), so
+//                that warp 0 can bring the MMA's B operand for a stage (K-major
+//                8x16-byte core matrices, no swizzle) with one tiled TMA load.
 //   warp 1       one thread issues tcgen05.mma.cta_group::1.kind::f16 (A from
 //                TMEM, B from shared memory, D in TMEM), two per 32-block, all
 //                accumulating into the CTA's one [128 x NB] FP32 accumulator;
@@ -44,36 +46,36 @@ namespace tc {
 
 constexpr int NT = 128;               // columns per CTA = MMA M = TMEM lanes
 constexpr int WSTAGE_BLOCKS = 4;      // 32-blocks per ring stage (8 KB)
-constexpr int WSTAGES = 8;            // ring depth: 64 KB in flight per CTA
-constexpr int SLOTS = 8;              // TMEM slots holding one dequantised 32-block (16 columns) each
+constexpr int WSTAGES = 6;            // packed ring depth: 48 KB in flight per CTA
+constexpr int BSTAGES = 3;            // activation ring depth (one stage = the same four 32-blocks)
+constexpr int ASLOTS = 3;             // TMEM slots holding one dequantised ring stage (4 blocks x 16 columns) each
 constexpr int THREADS = 12 * 32;
-constexpr int B_BUF_BYTES = 16384;    // one staged activation chunk
 constexpr int EPI_THREADS = 128;
-constexpr int STAGER_THREADS = 64;
+constexpr int B_STAGE_KCORES = WSTAGE_BLOCKS * 4;     // 8-wide K cores per activation stage
 constexpr int DEQ_SETS = 2;           // dequant warp sets, alternate blocks
 
 template <int NB>
 struct Cfg {
-    static constexpr int SLICE_BYTES = NB * 32;                     // NB rows x 16 K-slots x 2 B
-    static constexpr int BLOCK_B_BYTES = 2 * SLICE_BYTES;           // the two K=16 slices of a 32-block
-    static constexpr int CHUNK_BLOCKS = B_BUF_BYTES / BLOCK_B_BYTES;   // 32-blocks per staged chunk
-    static constexpr int A_COL0 = 0;                                // A slot s: columns [16 s, 16 s + 16)
-    static constexpr int D_COL0 = SLOTS * 16;                       // the accumulator: NB columns
-    static constexpr int USED_COLS = SLOTS * 16 + NB;
+    static constexpr int KCORE_BYTES = NB * 16;                     // one K core: NB rows x 8 K x 2 B
+    static constexpr int B_STAGE_BYTES = B_STAGE_KCORES * KCORE_BYTES;
+    static constexpr int A_SLOT_COLS = WSTAGE_BLOCKS * 16;          // A slot s: columns [64 s, 64 s + 64)
+    static constexpr int A_COL0 = 0;
+    static constexpr int D_COL0 = ASLOTS * A_SLOT_COLS;             // the accumulator: NB columns
+    static constexpr int USED_COLS = ASLOTS * A_SLOT_COLS + NB;
     static constexpr int TMEM_COLS = USED_COLS <= 256 ? 256 : 512;
     static_assert(USED_COLS <= 512, "tensor memory holds 512 columns");
-    static_assert(CHUNK_BLOCKS >= 2 && (CHUNK_BLOCKS % 2) == 0, "chunk geometry");
 };
 
+template <int NB>
 struct Smem {
     alignas(128) uint8_t packed[WSTAGES][WSTAGE_BLOCKS * NT * kBlockBytes];
-    alignas(128) uint8_t b[2][B_BUF_BYTES];
+    alignas(128) uint8_t b[BSTAGES][Cfg<NB>::B_STAGE_BYTES];     // [K core][row][8 K]
     alignas(8) uint64_t w_full[WSTAGES];
     alignas(8) uint64_t w_empty[WSTAGES];
-    alignas(8) uint64_t a_full[SLOTS];     // dequant -> MMA: the slot's A operand is in tensor memory
-    alignas(8) uint64_t a_empty[SLOTS];    // MMA (commit) -> dequant: the slot's A operand is consumed
-    alignas(8) uint64_t b_full[2];
-    alignas(8) uint64_t b_empty[2];
+    alignas(8) uint64_t a_full[ASLOTS];      // dequant -> MMA: a stage's A operands are in tensor memory
+    alignas(8) uint64_t a_empty[ASLOTS];     // MMA (commit) -> dequant: the stage's A operands are consumed
+    alignas(8) uint64_t b_full[BSTAGES];
+    alignas(8) uint64_t b_empty[BSTAGES];
     alignas(8) uint64_t d_full;            // MMA (commit) -> epilogue: the accumulator is complete
     uint32_t tmem_base;
     int abort_flag;
@@ -137,14 +139,14 @@ __device__ __forceinline__ void tmem_ld<16>(uint32_t taddr, uint32_t (&v)[16]) {
 }
 
 // Shared-memory matrix descriptor, K-major, no swizzle: core matrices are 8 rows
-// x 16 bytes stored as 128 contiguous bytes; the next core matrix along K lies
-// 128 bytes further (leading offset), the next 8 rows 256 bytes further (stride
-// offset).  Descriptor version 1 = sm_100.
-__device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
+// x 16 bytes stored as 128 contiguous bytes; `lbo_bytes` is the distance to the
+// next core matrix along K (leading offset), `sbo_bytes` to the next 8 rows
+// (stride offset).  Descriptor version 1 = sm_100.
+__device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
     uint64_t d = 0;
     d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)(128u >> 4) << 16;
-    d |= (uint64_t)(256u >> 4) << 32;
+    d |= (uint64_t)(lbo_bytes >> 4) << 16;
+    d |= (uint64_t)(sbo_bytes >> 4) << 32;
     d |= (uint64_t)1 << 46;
     return d;
 }
@@ -162,7 +164,7 @@ gemm_kernel(const __grid_constant__ GemmParams p)
 {
     using C = Cfg<NB>;
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
+    Smem<NB>& sm = *reinterpret_cast<Smem<NB>*>(smem_raw);
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -176,8 +178,8 @@ gemm_kernel(const __grid_constant__ GemmParams p)
 
     if (tid == 0) {
         for (int s = 0; s < WSTAGES; ++s) { mbar_init(&sm.w_full[s], 1); mbar_init(&sm.w_empty[s], 4 * DEQ_SETS); }
-        for (int s = 0; s < SLOTS; ++s) { mbar_init(&sm.a_full[s], 4); mbar_init(&sm.a_empty[s], 1); }
-        for (int s = 0; s < 2; ++s) { mbar_init(&sm.b_full[s], STAGER_THREADS / 32); mbar_init(&sm.b_empty[s], 1); }
+        for (int s = 0; s < ASLOTS; ++s) { mbar_init(&sm.a_full[s], 4 * DEQ_SETS); mbar_init(&sm.a_empty[s], 1); }
+        for (int s = 0; s < BSTAGES; ++s) { mbar_init(&sm.b_full[s], 1); mbar_init(&sm.b_empty[s], 1); }
         mbar_init(&sm.d_full, 1);
         sm.abort_flag = 0;
         sm.is_last = 0;
@@ -225,15 +227,38 @@ gemm_kernel(const __grid_constant__ GemmParams p)
     const uint32_t tmem_base = sm.tmem_base;
 
     if (warp == 0) {
-        // ---------------------------------------------- TMA producer (packed) --
+        // ------------------------------ TMA producer (packed, then activations) --
+        // Weight stages WSTAGES.. and all activation stages.  Activations come from the
+        // pre-pass kernel, so they wait for the preceding grid; weights never do.
         PROF_DECL;
-        for (int st = WSTAGES; st < n_wstages; ++st) {
-            const int slot = st % WSTAGES;
-            PROF_BEGIN(t0);
-            if (!wait_uniform(&sm.w_empty[slot], ((st / WSTAGES) - 1) & 1, abort_flag)) break;
-            PROF_END(t0, 0);
-            issue_stage(st);
+        pdl_wait_prior_grids();
+        auto issue_b = [&](int st) {
+            if (lane == 0) {
+                const int bs = st % BSTAGES;
+                mbar_arrive_expect_tx(&sm.b_full[bs], (uint32_t)C::B_STAGE_BYTES);
+                tma_load_2d(&sm.b[bs][0], &p.act_map, 0, (b0 + st * WSTAGE_BLOCKS) * 4, &sm.b_full[bs]);
+            }
+            __syncwarp();
+        };
+        // Two independent streams, each as far ahead as its ring allows: activation stages
+        // (BSTAGES deep) and weight stages (WSTAGES deep).  Single polls, so neither ring
+        // waits for the other; the idle counter bounds the loop.
+        int bst = 0, wst = min(n_wstages, WSTAGES);
+        uint32_t idle = 0;
+        while ((bst < n_wstages || wst < n_wstages) && idle < (1u << 22)) {
+            bool progress = false;
+            if (bst < n_wstages) {
+                bool free_b = bst < BSTAGES;
+                if (!free_b) free_b = mbar_try_wait(&sm.b_empty[bst % BSTAGES], ((bst / BSTAGES) - 1) & 1);
+                if (__all_sync(0xffffffffu, free_b)) { issue_b(bst); ++bst; progress = true; }
+            }
+            if (wst < n_wstages) {
+                const bool free_w = mbar_try_wait(&sm.w_empty[wst % WSTAGES], ((wst / WSTAGES) - 1) & 1);
+                if (__all_sync(0xffffffffu, free_w)) { issue_stage(wst); ++wst; progress = true; }
+            }
+            if (progress) { idle = 0; } else { ++idle; if (idle > 64) __nanosleep(64); if (*abort_flag) break; }
         }
+        if (bst < n_wstages || wst < n_wstages) { *abort_flag = 1; atomicOr(&g_error_word, 1u); }
         PROF_FLUSH(0);
     } else if (warp == 1) {
         // ------------------------------------------------------- MMA issuer --
@@ -242,112 +267,49 @@ gemm_kernel(const __grid_constant__ GemmParams p)
             idesc |= 1u << 4;                         // D format f32
             idesc |= (uint32_t)(NB >> 3) << 17;       // N
             idesc |= (uint32_t)(128 >> 4) << 24;      // M
-            const uint64_t desc0[2] = {make_b_desc(smem_u32(&sm.b[0][0])), make_b_desc(smem_u32(&sm.b[1][0]))};
             const uint32_t d_addr = tmem_base + C::D_COL0;
+            // One pass per ring stage (four 32-blocks): two waits, eight MMAs back to back, two
+            // commits.  The issuing thread's own instruction stream is the scarce resource here
+            // (about 46 clk per tcgen05.mma, as much again per commit or barrier poll).
+            const uint64_t kcore_step = (uint64_t)(C::KCORE_BYTES >> 4);           // descriptor address units
             PROF_DECL;
-            int slot = 0, use = 0, bi = 0, chunk = 0;
             bool ok = true;
-            for (int i = 0; i < total_blocks; ++i) {
+            for (int st = 0; st < n_wstages; ++st) {
+                const int aslot = st % ASLOTS;
+                const int bs = st % BSTAGES;
+                const int nb = min(WSTAGE_BLOCKS, total_blocks - st * WSTAGE_BLOCKS);
                 PROF_BEGIN(t0);
-                if (bi == 0 && !mbar_wait_bounded(&sm.b_full[chunk & 1], (chunk >> 1) & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait_bounded(&sm.b_full[bs], (st / BSTAGES) & 1, abort_flag)) { ok = false; break; }
                 PROF_END(t0, 0);
                 PROF_BEGIN(t2);
-                if (!mbar_wait_bounded(&sm.a_full[slot], use & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait_bounded(&sm.a_full[aslot], (st / ASLOTS) & 1, abort_flag)) { ok = false; break; }
                 PROF_END(t2, 2);
                 PROF_BEGIN(t3);
                 tc_fence_after();
-                const uint32_t a_addr = tmem_base + C::A_COL0 + slot * 16;
-                // descriptor start-address field counts 16-byte units
-                const uint64_t bd = desc0[chunk & 1] + (uint64_t)((bi * C::BLOCK_B_BYTES) >> 4);
-                tc_mma_ts(d_addr, a_addr, bd, idesc, i == 0 ? 0u : 1u);
-                tc_mma_ts(d_addr, a_addr + 8, bd + (uint64_t)(C::SLICE_BYTES >> 4), idesc, 1u);
+                uint32_t a_addr = tmem_base + C::A_COL0 + aslot * C::A_SLOT_COLS;
+                // a block's four K cores sit C::KCORE_BYTES apart; 8-row groups 128 bytes apart
+                uint64_t bd = make_b_desc(smem_u32(&sm.b[bs][0]), C::KCORE_BYTES, 128);
+#pragma unroll
+                for (int bi = 0; bi < WSTAGE_BLOCKS; ++bi) {
+                    if (bi < nb) {
+                        tc_mma_ts(d_addr, a_addr, bd, idesc, (st == 0 && bi == 0) ? 0u : 1u);
+                        tc_mma_ts(d_addr, a_addr + 8, bd + 2 * kcore_step, idesc, 1u);
+                    }
+                    a_addr += 16;
+                    bd += 4 * kcore_step;
+                }
                 PROF_END(t3, 3);
                 PROF_BEGIN(t4);
-                tc_commit(&sm.a_empty[slot]);
-                const bool chunk_end = (bi == C::CHUNK_BLOCKS - 1) || (i == total_blocks - 1);
-                if (chunk_end) tc_commit(&sm.b_empty[chunk & 1]);
+                tc_commit(&sm.a_empty[aslot]);
+                tc_commit(&sm.b_empty[bs]);
                 PROF_END(t4, 4);
-                if (++slot == SLOTS) { slot = 0; ++use; }
-                if (chunk_end) { bi = 0; ++chunk; } else { ++bi; }
             }
             if (ok) tc_commit(&sm.d_full);
             PROF_FLUSH(1);
         }
         __syncwarp();
     } else if (warp == 2 || warp == 3) {
-        // ---------------------------------------------- activation stagers --
-        // One item = 8 consecutive K of one row (one 16-byte load), stored as one 16-byte core-matrix
-        // row in the order k0,k4,k1,k5,k2,k6,k3,k7.  The loads of a chunk are issued before the wait
-        // for its buffer, so their latency hides behind the MMAs still reading the buffer.
-        pdl_wait_prior_grids();
-        const int st_tid = tid - 64;
-        const __half* A = reinterpret_cast<const __half*>(p.a);
-        const bool vec_ok = ((reinterpret_cast<uintptr_t>(A) & 15) == 0) && ((p.lda & 7) == 0);
-        const int n_chunks = (total_blocks + C::CHUNK_BLOCKS - 1) / C::CHUNK_BLOCKS;
-        constexpr int PF = 8;                                            // items in flight per thread
-        PROF_DECL;
-        bool ok = true;
-        for (int chunk = 0; chunk < n_chunks && ok; ++chunk) {
-            const int buf = chunk & 1;
-            const int use = chunk >> 1;
-            const int cb0 = chunk * C::CHUNK_BLOCKS;
-            const int cb = min(C::CHUNK_BLOCKS, total_blocks - cb0);
-            const int items = p.M * cb * 4;                              // item = (m * cb + bi) * 4 + w
-            bool waited = false;
-            for (int base = 0; base < items; base += STAGER_THREADS * PF) {
-                uint4 x[PF];
-                PROF_BEGIN(t1);
-#pragma unroll
-                for (int u = 0; u < PF; ++u) {
-                    const int it = base + u * STAGER_THREADS + st_tid;
-                    x[u] = make_uint4(0, 0, 0, 0);
-                    if (it < items) {
-                        const int m = it / (cb * 4);
-                        const int rem = it - m * (cb * 4);
-                        const size_t off = (size_t)m * p.lda + (size_t)(b0 + cb0 + (rem >> 2)) * kBlockK + (rem & 3) * 8;
-                        if (vec_ok) {
-                            x[u] = *reinterpret_cast<const uint4*>(A + off);
-                        } else {
-                            const uint16_t* a16 = reinterpret_cast<const uint16_t*>(A) + off;
-                            x[u].x = a16[0] | ((uint32_t)a16[1] << 16); x[u].y = a16[2] | ((uint32_t)a16[3] << 16);
-                            x[u].z = a16[4] | ((uint32_t)a16[5] << 16); x[u].w = a16[6] | ((uint32_t)a16[7] << 16);
-                        }
-                    }
-                }
-                PROF_END(t1, 1);
-                if (!waited) {
-                    PROF_BEGIN(t0);
-                    if (use > 0 && !wait_uniform(&sm.b_empty[buf], (use - 1) & 1, abort_flag)) { ok = false; break; }
-                    PROF_END(t0, 0);
-                    waited = true;
-                }
-                PROF_BEGIN(t2);
-#pragma unroll
-                for (int u = 0; u < PF; ++u) {
-                    const int it = base + u * STAGER_THREADS + st_tid;
-                    if (it < items) {
-                        const int m = it / (cb * 4);
-                        const int rem = it - m * (cb * 4);
-                        const int bi = rem >> 2;
-                        const int w = rem & 3;              // words 0,1 feed the block's first MMA, words 2,3 its second
-                        uint4 o;
-                        o.x = __byte_perm(x[u].x, x[u].z, 0x5410);      // k0,k4
-                        o.y = __byte_perm(x[u].x, x[u].z, 0x7632);      // k1,k5
-                        o.z = __byte_perm(x[u].y, x[u].w, 0x5410);      // k2,k6
-                        o.w = __byte_perm(x[u].y, x[u].w, 0x7632);      // k3,k7
-                        uint8_t* dst = &sm.b[buf][bi * C::BLOCK_B_BYTES + (w >> 1) * C::SLICE_BYTES + (m >> 3) * 256 +
-                                                  (w & 1) * 128 + (m & 7) * 16];
-                        *reinterpret_cast<uint4*>(dst) = o;
-                    }
-                }
-                PROF_END(t2, 2);
-            }
-            if (!ok) break;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> MMA's async reads
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sm.b_full[buf]);
-        }
-        PROF_FLUSH(2);
+        // spare warps (the dequant warps must start at a multiple of four: TMEM lane quarters)
     } else {
         // ------------------------------------------------------- dequant --
         const int set = (warp - 4) >> 2;                       // 0: even blocks, 1: odd blocks
@@ -366,61 +328,72 @@ gemm_kernel(const __grid_constant__ GemmParams p)
         int cur_group = -1;
         __half2 s2 = __float2half2_rn(0.0f);
         const __half2 k1032 = __float2half2_rn(1032.0f), k16th = __float2half2_rn(0.0625f), k72 = __float2half2_rn(-72.0f);
-        for (int i = set; i < total_blocks; i += DEQ_SETS) {
-            const int st = i / WSTAGE_BLOCKS;
-            const int r = i - st * WSTAGE_BLOCKS;
+        for (int st = 0; st < n_wstages; ++st) {
             const int wslot = st % WSTAGES;
-            const int b = b0 + i;
-            if ((b >> gshift) != cur_group) {                  // the group's FP16 scale of this column, as a pair
-                cur_group = b >> gshift;
-                const uint16_t sb = owner ? __ldg(scales + (size_t)cur_group * p.N + n) : (uint16_t)0;
-                s2 = __half2half2(__ushort_as_half(sb));
-            }
+            const int aslot = st % ASLOTS;
+            const int nb = min(WSTAGE_BLOCKS, total_blocks - st * WSTAGE_BLOCKS);
             PROF_BEGIN(t0);
-            // this set's first block of a stage: r = set, since a stage holds an even number of blocks
-            if (r < DEQ_SETS && !wait_uniform(&sm.w_full[wslot], (st / WSTAGES) & 1, abort_flag)) { ok = false; break; }
+            if (!wait_uniform(&sm.w_full[wslot], (st / WSTAGES) & 1, abort_flag)) { ok = false; break; }
             PROF_END(t0, 0);
-            PROF_BEGIN(t1);
-            const uint4 v = lds128(&sm.packed[wslot][(r * NT + col) * kBlockBytes]);
-            const uint32_t words[4] = {v.x, v.y, v.z, v.w};
-            uint32_t regs[16];
+            bool slot_free = (st < ASLOTS);
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                const uint32_t x = words[w];
-                const uint32_t x8 = x >> 8;
-                uint32_t t0b = (x & 0x000F000Fu) | 0x64006400u;      // 1024 + (k0, k4)
-                uint32_t t1b = (x & 0x00F000F0u) | 0x64006400u;      // 1024 + 16 (k1, k5)
-                uint32_t t2b = (x8 & 0x000F000Fu) | 0x64006400u;     // 1024 + (k2, k6)
-                uint32_t t3b = (x8 & 0x00F000F0u) | 0x64006400u;     // 1024 + 16 (k3, k7)
-                const __half2 q0 = __hsub2(*reinterpret_cast<__half2*>(&t0b), k1032);          // q - 8, exact
-                const __half2 q1 = __hfma2(*reinterpret_cast<__half2*>(&t1b), k16th, k72);
-                const __half2 q2 = __hsub2(*reinterpret_cast<__half2*>(&t2b), k1032);
-                const __half2 q3 = __hfma2(*reinterpret_cast<__half2*>(&t3b), k16th, k72);
-                const __half2 w0 = __hmul2(q0, s2), w1 = __hmul2(q1, s2), w2 = __hmul2(q2, s2), w3 = __hmul2(q3, s2);
-                regs[4 * w + 0] = *reinterpret_cast<const uint32_t*>(&w0);
-                regs[4 * w + 1] = *reinterpret_cast<const uint32_t*>(&w1);
-                regs[4 * w + 2] = *reinterpret_cast<const uint32_t*>(&w2);
-                regs[4 * w + 3] = *reinterpret_cast<const uint32_t*>(&w3);
+            for (int rr = 0; rr < WSTAGE_BLOCKS / DEQ_SETS; ++rr) {
+                const int r = set + rr * DEQ_SETS;                 // this set's blocks of the stage: set, set + 2
+                if (r < nb) {                                      // warp-uniform
+                    const int b = b0 + st * WSTAGE_BLOCKS + r;
+                    if ((b >> gshift) != cur_group) {              // the group's FP16 scale of this column, as a pair
+                        cur_group = b >> gshift;
+                        const uint16_t sb = owner ? __ldg(scales + (size_t)cur_group * p.N + n) : (uint16_t)0;
+                        s2 = __half2half2(__ushort_as_half(sb));
+                    }
+                    PROF_BEGIN(t1);
+                    const uint4 v = lds128(&sm.packed[wslot][(r * NT + col) * kBlockBytes]);
+                    const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+                    uint32_t regs[16];
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        const uint32_t x = words[w];
+                        const uint32_t x8 = x >> 8;
+                        uint32_t t0b = (x & 0x000F000Fu) | 0x64006400u;      // 1024 + (k0, k4)
+                        uint32_t t1b = (x & 0x00F000F0u) | 0x64006400u;      // 1024 + 16 (k1, k5)
+                        uint32_t t2b = (x8 & 0x000F000Fu) | 0x64006400u;     // 1024 + (k2, k6)
+                        uint32_t t3b = (x8 & 0x00F000F0u) | 0x64006400u;     // 1024 + 16 (k3, k7)
+                        const __half2 q0 = __hsub2(*reinterpret_cast<__half2*>(&t0b), k1032);          // q - 8, exact
+                        const __half2 q1 = __hfma2(*reinterpret_cast<__half2*>(&t1b), k16th, k72);
+                        const __half2 q2 = __hsub2(*reinterpret_cast<__half2*>(&t2b), k1032);
+                        const __half2 q3 = __hfma2(*reinterpret_cast<__half2*>(&t3b), k16th, k72);
+                        const __half2 w0 = __hmul2(q0, s2), w1 = __hmul2(q1, s2), w2 = __hmul2(q2, s2), w3 = __hmul2(q3, s2);
+                        regs[4 * w + 0] = *reinterpret_cast<const uint32_t*>(&w0);
+                        regs[4 * w + 1] = *reinterpret_cast<const uint32_t*>(&w1);
+                        regs[4 * w + 2] = *reinterpret_cast<const uint32_t*>(&w2);
+                        regs[4 * w + 3] = *reinterpret_cast<const uint32_t*>(&w3);
+                    }
+                    PROF_END(t1, 1);
+                    if (!slot_free) {                              // the MMAs that read this slot's previous contents are done
+                        PROF_BEGIN(t2);
+                        if (!wait_uniform(&sm.a_empty[aslot], ((st / ASLOTS) - 1) & 1, abort_flag)) { ok = false; break; }
+                        PROF_END(t2, 2);
+                        tc_fence_after();
+                        slot_free = true;
+                    }
+                    PROF_BEGIN(t3);
+                    tmem_st16(lane_base + aslot * C::A_SLOT_COLS + r * 16, regs);
+                    PROF_END(t3, 3);
+                }
             }
-            // this set's last block of the stage (or of the slice): the stage is read out
-            if (r + DEQ_SETS >= WSTAGE_BLOCKS || i + DEQ_SETS >= total_blocks) {
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sm.w_empty[wslot]);
+            if (!ok) break;
+            if (!slot_free) {      // a warp without a block in this (ragged) stage still keeps the slot's phases in step
+                if (!wait_uniform(&sm.a_empty[aslot], ((st / ASLOTS) - 1) & 1, abort_flag)) { ok = false; break; }
             }
-            PROF_END(t1, 1);
-            const int slot = i % SLOTS;
-            const int use = i / SLOTS;
-            PROF_BEGIN(t2);
-            if (use > 0 && !wait_uniform(&sm.a_empty[slot], (use - 1) & 1, abort_flag)) { ok = false; break; }
-            PROF_END(t2, 2);
-            PROF_BEGIN(t3);
-            tc_fence_after();
-            tmem_st16(lane_base + slot * 16, regs);
+            PROF_BEGIN(t4);
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&sm.a_full[slot]);
-            PROF_END(t3, 3);
+            if (lane == 0) {
+                mbar_arrive(&sm.a_full[aslot]);            // this warp's share of the stage is in tensor memory
+                mbar_arrive(&sm.w_empty[wslot]);           // and read out of the ring
+            }
+            PROF_END(t4, 4);
         }
         PROF_FLUSH(3);
 
@@ -498,6 +471,34 @@ gemm_kernel(const __grid_constant__ GemmParams p)
         tc_fence_after();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
     }
+}
+
+// Pre-pass of the tcgen05 kernel: rows [0, rows) of the activations, f16 [rows][lda], rewritten as
+// [K/8][rows][8] with the eight K of a core in the order k0,k4,k1,k5,k2,k6,k3,k7 (the order in which
+// the dequant warps lay nibbles into tensor memory).  One thread per (K core, row).
+__global__ void __launch_bounds__(256)
+permute_activations_kernel(__half* __restrict__ out, const __half* __restrict__ a, long lda, int rows, int kcores)
+{
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * kcores) return;
+    const int kc = idx / rows, m = idx - kc * rows;
+    const __half* src = a + (size_t)m * lda + (size_t)kc * 8;
+    uint4 x;
+    if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+        x = *reinterpret_cast<const uint4*>(src);
+    } else {
+        const uint16_t* s16 = reinterpret_cast<const uint16_t*>(src);
+        x.x = s16[0] | ((uint32_t)s16[1] << 16); x.y = s16[2] | ((uint32_t)s16[3] << 16);
+        x.z = s16[4] | ((uint32_t)s16[5] << 16); x.w = s16[6] | ((uint32_t)s16[7] << 16);
+    }
+    uint4 o;
+    o.x = __byte_perm(x.x, x.z, 0x5410);      // k0,k4
+    o.y = __byte_perm(x.x, x.z, 0x7632);      // k1,k5
+    o.z = __byte_perm(x.y, x.w, 0x5410);      // k2,k6
+    o.w = __byte_perm(x.y, x.w, 0x7632);      // k3,k7
+    reinterpret_cast<uint4*>(out)[idx] = o;
 }
 
 }  // namespace tc

@@ -37,6 +37,15 @@ constexpr int kDefaultSms = 148;
 constexpr int kMaxSplits = 64;
 constexpr size_t kCounterBytes = 16384;   // 4096 tile counters at the head of the workspace
 
+// Dynamic shared memory of a tcgen05 launch.  Each CTA allocates 256 of the SM's 512 tensor-memory
+// columns, so at most two fit; asking for at least 80 KB keeps a third CTA off the SM (it would
+// sit in tcgen05.alloc until another CTA ends, and the SMs would finish unevenly).
+size_t tc_smem_bytes(int rows)
+{
+    const size_t need = rows <= 16 ? sizeof(twm::tc::Smem<16>) : (rows <= 32 ? sizeof(twm::tc::Smem<32>) : sizeof(twm::tc::Smem<64>));
+    return std::max(need, (size_t)80 * 1024);
+}
+
 struct DeviceState {
     bool ready = false;
     twm_status status = TWM_OK;
@@ -73,13 +82,13 @@ twm_status ensure_device(int* sm_count_out)
             raise((const void*)twm::simt::gemv_kernel<2>);
             raise((const void*)twm::simt::gemv_kernel<4>);
             raise((const void*)twm::simt::gemv_kernel<8>);
-            auto raise_tc = [&](const void* fn) {
+            auto raise_tc = [&](const void* fn, size_t bytes) {
                 if (r == cudaSuccess)
-                    r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(twm::tc::Smem));
+                    r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
             };
-            raise_tc((const void*)twm::tc::gemm_kernel<16>);
-            raise_tc((const void*)twm::tc::gemm_kernel<32>);
-            raise_tc((const void*)twm::tc::gemm_kernel<64>);
+            raise_tc((const void*)twm::tc::gemm_kernel<16>, tc_smem_bytes(16));
+            raise_tc((const void*)twm::tc::gemm_kernel<32>, tc_smem_bytes(32));
+            raise_tc((const void*)twm::tc::gemm_kernel<64>, tc_smem_bytes(64));
             auto raise_mma = [&](const void* fn) {
                 if (r == cudaSuccess)
                     r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(twm::mma::Smem));
@@ -130,6 +139,22 @@ bool make_packed_map(CUtensorMap* map, const uint8_t* packed, int N, int nkb, in
     const cuuint32_t box[2] = {256, (cuuint32_t)rows};
     const cuuint32_t estride[2] = {1, 1};
     return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t*>(packed), gdim, gstride, box, estride,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Tensor map over the permuted activations of one tcgen05 launch, f16 [K/8][rows][8], seen as
+// 32-bit words [K/8][rows * 4]: a box of nb_rows * 4 words x 16 K cores is one ring stage (four
+// 32-blocks) landing as [K core][row][16 bytes]; words past rows * 4 read as zero.
+bool make_act_map(CUtensorMap* map, const void* xp, int rows, int K, int nb_rows)
+{
+    EncodeTiledFn enc = get_encode_tiled();
+    if (!enc) return false;
+    const cuuint64_t gdim[2] = {(cuuint64_t)rows * 4, (cuuint64_t)K / 8};
+    const cuuint64_t gstride[1] = {(cuuint64_t)rows * 16};
+    const cuuint32_t box[2] = {(cuuint32_t)nb_rows * 4, (cuuint32_t)twm::tc::B_STAGE_KCORES};
+    const cuuint32_t estride[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(xp), gdim, gstride, box, estride,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -185,7 +210,7 @@ twm_status launch_tc(const twm::GemmParams& p, int rows, dim3 grid, bool pdl, cu
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = grid;
     cfg.blockDim = dim3(twm::tc::THREADS, 1, 1);
-    cfg.dynamicSmemBytes = sizeof(twm::tc::Smem);
+    cfg.dynamicSmemBytes = tc_smem_bytes(rows);
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -362,6 +387,9 @@ twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int split
     out->grid_x = n_tiles;
     out->grid_y = splits;
     out->workspace_bytes = (splits > 1 && !cluster) ? kCounterBytes + (size_t)splits * rows * N * sizeof(float) : 0;
+    if (kernel == TWM_KERNEL_TC)    // + the launch's activations in the MMA's K order, behind the split-K part
+        out->workspace_bytes = kCounterBytes + (splits > 1 ? (size_t)splits * rows * N * sizeof(float) : 0) +
+                               256 + (size_t)rows * K * 2;
     out->cluster_reduce = cluster ? 1 : 0;
     return TWM_OK;
 }
@@ -443,8 +471,22 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
 #endif
         if (map_rows) p.packed_map = packed_map;
         const bool pdl = (a->flags & TWM_FLAG_PDL) != 0;
-        if (kernel == TWM_KERNEL_TC)
+        if (kernel == TWM_KERNEL_TC) {
+            // pre-pass: this launch's rows in [K/8][rows][8] order, then the GEMM loads them by TMA
+            const size_t part_bytes = pl.splits > 1 ? (size_t)pl.splits * std::min(a->M, kTcRows) * a->N * sizeof(float) : 0;
+            char* xp = (char*)a->workspace + kCounterBytes + ((part_bytes + 255) / 256) * 256;
+            const int nb_rows = rows <= 16 ? 16 : (rows <= 32 ? 32 : 64);
+            if (!make_act_map(&p.act_map, xp, rows, a->K, nb_rows)) {
+                snprintf(t_last_error, sizeof(t_last_error), "cuTensorMapEncodeTiled failed for the activation map");
+                return TWM_ELAUNCH;
+            }
+            const int items = rows * (a->K / 8);
+            st = launch_op("permute_activations_kernel", twm::tc::permute_activations_kernel, dim3((items + 255) / 256),
+                           dim3(256), 0, a->flags & TWM_FLAG_PDL, stream_, (__half*)xp, (const __half*)p.a, p.lda, rows,
+                           a->K / 8);
+            if (st != TWM_OK) return st;
             st = launch_tc(p, rows, dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
+        }
         else if (kernel == TWM_KERNEL_MMA)
             st = launch_mma(p, mmax_for(rows), dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
         else
