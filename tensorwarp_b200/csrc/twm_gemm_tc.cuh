@@ -325,8 +325,16 @@ gemm_kernel(const __grid_constant__ GemmParams p)
         }
         PROF_DECL;
         bool ok = true;
-        int cur_group = -1;
-        __half2 s2 = __float2half2_rn(0.0f);
+        // FP16 scale of this column for each of this set's two blocks of a stage, requested one
+        // stage ahead so that the L2 round trip is never waited for
+        auto load_scale = [&](int st, int rr) -> uint16_t {
+            const int i = st * WSTAGE_BLOCKS + set + rr * DEQ_SETS;
+            if (!owner || i >= total_blocks) return (uint16_t)0;
+            return __ldg(scales + (size_t)((b0 + i) >> gshift) * p.N + n);
+        };
+        uint16_t s_next[WSTAGE_BLOCKS / DEQ_SETS];
+#pragma unroll
+        for (int rr = 0; rr < WSTAGE_BLOCKS / DEQ_SETS; ++rr) s_next[rr] = load_scale(0, rr);
         const __half2 k1032 = __float2half2_rn(1032.0f), k16th = __float2half2_rn(0.0625f), k72 = __float2half2_rn(-72.0f);
         for (int st = 0; st < n_wstages; ++st) {
             const int wslot = st % WSTAGES;
@@ -336,16 +344,17 @@ gemm_kernel(const __grid_constant__ GemmParams p)
             if (!wait_uniform(&sm.w_full[wslot], (st / WSTAGES) & 1, abort_flag)) { ok = false; break; }
             PROF_END(t0, 0);
             bool slot_free = (st < ASLOTS);
+            uint16_t s_cur[WSTAGE_BLOCKS / DEQ_SETS];
+#pragma unroll
+            for (int rr = 0; rr < WSTAGE_BLOCKS / DEQ_SETS; ++rr) {
+                s_cur[rr] = s_next[rr];
+                s_next[rr] = load_scale(st + 1, rr);
+            }
 #pragma unroll
             for (int rr = 0; rr < WSTAGE_BLOCKS / DEQ_SETS; ++rr) {
                 const int r = set + rr * DEQ_SETS;                 // this set's blocks of the stage: set, set + 2
                 if (r < nb) {                                      // warp-uniform
-                    const int b = b0 + st * WSTAGE_BLOCKS + r;
-                    if ((b >> gshift) != cur_group) {              // the group's FP16 scale of this column, as a pair
-                        cur_group = b >> gshift;
-                        const uint16_t sb = owner ? __ldg(scales + (size_t)cur_group * p.N + n) : (uint16_t)0;
-                        s2 = __half2half2(__ushort_as_half(sb));
-                    }
+                    const __half2 s2 = __half2half2(__ushort_as_half(s_cur[rr]));
                     PROF_BEGIN(t1);
                     const uint4 v = lds128(&sm.packed[wslot][(r * NT + col) * kBlockBytes]);
                     const uint32_t words[4] = {v.x, v.y, v.z, v.w};
