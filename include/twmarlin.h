@@ -60,6 +60,19 @@ enum {
     TWM_FLAG_ACCUMULATE = 2 /* c += result instead of c = result (residual add fused in the epilogue) */
 };
 
+/* Receive buffers of a tensor-parallel group for the one-shot all-reduce that is fused into
+ * the row-parallel GEMM (no counterpart in the reference, whose multi-GPU helper sums on the host,
+ * crates/kernels/src/multi_gpu.rs:329-366).  Every rank owns one buffer of twm_comm_bytes() in its
+ * own GPU's memory, zeroed once, and knows every rank's buffer address (CUDA IPC between
+ * processes: twm_ipc_*).  data[s] / flags[s] / state are produced by twm_comm_layout(). */
+typedef struct twm_comm {
+    int n_ranks, rank;
+    long slot_elems;          /* floats per (set, source rank) slot: >= M * ldc of the GEMMs that use it */
+    float* data[8];           /* rank s's slots, as addressable from this rank */
+    unsigned int* flags[8];   /* rank s's arrival flags */
+    unsigned int* state;      /* this rank's own state words */
+} twm_comm;
+
 /* One GEMM  C[M,N] = A[M,K] x dequant(packed, scales).
  * Replaces gemm_tw_marlin_m1 (quantize.rs:1301-1360) for M = 1 with f32 A/C,
  * gemm_tw_marlin_m1_from_buffer (quantize.rs:1731-1782; pass offset pointers)
@@ -89,6 +102,11 @@ typedef struct twm_gemm_args {
     const uint32_t* packed_offsets;
     const uint32_t* scales_offsets;
     int expert_idx;
+    /* Tensor-parallel row shard: when comm != NULL the FP32 result is not stored to `c` but pushed
+     * into every rank's receive buffer (plain stores over NVLink into the peer's own memory, tile
+     * by tile as the tiles finish), and the grid's last CTA raises the arrival flags.  The sum is
+     * taken by twm_allreduce_add_rmsnorm on each rank.  M <= 2, FP16 activations. */
+    const twm_comm* comm;
 } twm_gemm_args;
 
 /* What the heuristic decided for a shape; pure host arithmetic. */
@@ -116,6 +134,28 @@ size_t twm_workspace_bytes(int M, int N, int K, int group_size);
 
 /* Enqueue one GEMM.  See twm_gemm_args. */
 twm_status twm_gemm_w4a16(const twm_gemm_args* args, void* stream);
+
+/* Bytes of one rank's receive buffer, and the addresses inside a buffer that starts at `base`
+ * (`base` may be a peer's buffer as mapped into this process). */
+size_t twm_comm_bytes(int n_ranks, long slot_elems);
+twm_status twm_comm_layout(void* base, int n_ranks, long slot_elems, float** data, unsigned int** flags,
+                           unsigned int** state);
+
+/* Second half of the one-shot all-reduce, fused with the residual add and RMSNorm that follow a
+ * row-parallel GEMM (fused_residual_rmsnorm, crates/kernels/src/ops.rs:928-962): waits, with a
+ * bound, for every rank's partial, x += sum over ranks in rank order, y = rmsnorm(x) (y_f16 may be
+ * NULL).  Every rank must enqueue the same sequence of comm GEMMs and of these calls. */
+twm_status twm_allreduce_add_rmsnorm(void* y_f16, float* x, const twm_comm* comm, const float* gamma, int rows,
+                                     int hidden, float eps, int flags, void* stream);
+
+/* Device memory that other processes on the same box can map (CUDA IPC): allocation (zeroed),
+ * 64-byte handle, mapping a peer's handle, and their inverses.  Set-up calls: they allocate and
+ * synchronise. */
+twm_status twm_ipc_alloc(size_t bytes, void** ptr);
+twm_status twm_ipc_free(void* ptr);
+twm_status twm_ipc_get_handle(void* ptr, unsigned char handle[64]);
+twm_status twm_ipc_open(const unsigned char handle[64], void** ptr);
+twm_status twm_ipc_close(void* ptr);
 
 /* The same GEMM for hosts that cannot give this library any device memory of its own:
  * an engine that carves the whole GPU into weights and KV cache at start-up and has no

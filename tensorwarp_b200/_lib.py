@@ -29,7 +29,14 @@ class GemmArgs(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("splits_override", C.c_int), ("kernel_override", C.c_int), ("flags", C.c_int),
         ("packed_offsets", C.c_void_p), ("scales_offsets", C.c_void_p), ("expert_idx", C.c_int),
+        ("comm", C.c_void_p),
     ]
+
+
+class Comm(C.Structure):
+    """``twm_comm``."""
+    _fields_ = [("n_ranks", C.c_int), ("rank", C.c_int), ("slot_elems", C.c_long),
+                ("data", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("state", C.c_void_p)]
 
 
 class Plan(C.Structure):
@@ -55,6 +62,16 @@ SIGNATURES = {
                               C.c_void_p, C.c_void_p]),
     "twm_slice_k_offsets": (C.c_int, [C.c_int] * 5 + [C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     "twm_device_error": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint)]),
+    "twm_comm_bytes": (C.c_size_t, [C.c_int, C.c_long]),
+    "twm_comm_layout": (C.c_int, [C.c_void_p, C.c_int, C.c_long, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                                  C.POINTER(C.c_void_p)]),
+    "twm_allreduce_add_rmsnorm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float,
+                                            C.c_int, C.c_void_p]),
+    "twm_ipc_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
+    "twm_ipc_free": (C.c_int, [C.c_void_p]),
+    "twm_ipc_get_handle": (C.c_int, [C.c_void_p, C.c_char_p]),
+    "twm_ipc_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "twm_ipc_close": (C.c_int, [C.c_void_p]),
     # include/twm_decode.h
     "twm_embed": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "twm_rmsnorm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p]),

@@ -130,6 +130,21 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// --------------------------------------------- system-scope flags (peers) --
+__device__ __forceinline__ void st_release_sys_u32(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned int ld_volatile_u32(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 // ----------------------------------------------------------- named barrier --
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
@@ -205,6 +220,17 @@ struct GemmParams {
     const uint32_t* packed_offsets;
     const uint32_t* scales_offsets;
     int expert_idx;
+    // Row-parallel output pushed straight to every tensor-parallel peer (one-shot all-reduce,
+    // first half).  n_peers = 0: normal store to c.  Otherwise every stored value goes, as FP32,
+    // to slot `peer_rank` of the current buffer set in each peer's receive buffer
+    // (peer_data[s] + ((set * n_peers + peer_rank) * peer_slot_elems) + m * ldc + n), and the last
+    // CTA of the grid publishes the peers' flags.  The state words live in this rank's memory.
+    int n_peers;
+    int peer_rank;
+    long peer_slot_elems;
+    float* peer_data[8];
+    unsigned int* peer_flags[8];     // [set][source rank] words, 8 words apart
+    unsigned int* comm_state;        // [0] operation sequence number, [1] CTAs done, [2] consumer CTAs done
     // Tensor map over `packed` seen as u64 [K/32][2N]: one TMA instruction brings a whole
     // ring stage (box = 256 u64 x map_rows rows = 128 columns x map_rows 32-blocks).
     int map_rows;                // 0 = no map (1-D bulk copies per row instead)

@@ -122,6 +122,71 @@ rmsnorm_kernel(__half* __restrict__ y, float* __restrict__ x, const float* __res
         y[(size_t)row * hidden + i] = __float2half_rn(xr[i] * rms * gamma[i]);
 }
 
+// One-shot all-reduce, second half, fused with the residual add and the RMSNorm that follow a
+// row-parallel GEMM: wait (bounded) until every rank's partial for the current operation has
+// arrived in THIS GPU's receive buffer (the GEMM epilogues of all ranks stored them there over
+// NVLink), add the slots in rank order (every rank gets the same bits), x += sum, y = norm(x).
+// One CTA per row; the last CTA to finish advances the operation sequence number.  The
+// reference sums partial outputs on the host (crates/kernels/src/multi_gpu.rs:329-366).
+__global__ void __launch_bounds__(256)
+allreduce_add_rmsnorm_kernel(__half* __restrict__ y, float* __restrict__ x, const float* __restrict__ recv,
+                             const unsigned int* __restrict__ flags, unsigned int* __restrict__ state,
+                             const float* __restrict__ gamma, int hidden, float eps, int n_ranks, long slot_elems)
+{
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    __shared__ float partial[8];
+    __shared__ int s_ok;
+    const int row = blockIdx.x;
+    const unsigned int seq = ld_volatile_u32(state);
+    const unsigned int set = seq & 1u;
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < n_ranks) {
+        // about a second of polling at most; then the error word is set and the step's result is void
+        const unsigned int* f = flags + (set * n_ranks + threadIdx.x) * 8;
+        bool got = false;
+        for (unsigned int i = 0; i < (1u << 22) && !got; ++i) {
+            got = ld_acquire_sys_u32(f) == seq + 1u;
+            if (!got && i > 32) __nanosleep(128);
+        }
+        if (!got) { s_ok = 0; atomicOr(&g_error_word, 4u); }
+    }
+    __syncthreads();
+    float* xr = x + (size_t)row * hidden;
+    const float* base = recv + (size_t)set * n_ranks * slot_elems + (size_t)row * hidden;
+    float ss = 0.0f;
+    if (s_ok) {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            float acc = 0.0f;
+            for (int r = 0; r < n_ranks; ++r) acc += __ldcg(base + (size_t)r * slot_elems + i);
+            const float v = xr[i] + acc;
+            xr[i] = v;
+            ss = fmaf(v, v, ss);
+        }
+    }
+    if (y != nullptr) {
+        ss = warp_sum(ss);
+        if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        float tot = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) tot += partial[w];
+        const float rms = rsqrtf(tot / (float)hidden + eps);
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+            y[(size_t)row * hidden + i] = __float2half_rn(xr[i] * rms * gamma[i]);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(&state[2], 1u) == gridDim.x - 1) {      // every row has read its slots
+            atomicExch(&state[2], 0u);
+            __threadfence();
+            atomicAdd(&state[0], 1u);                         // next operation, other buffer set
+        }
+    }
+}
+
 // q/k bias + rotate-half RoPE, v bias, append k and v at position pos_buf[0].  Reference:
 // warp_fused_bias_rope_append_dp, crates/kernels/src/ops.rs:2601-2650 (same formulas: freq =
 // 1/powf(base, 2*pair/head_dim), theta = pos*freq).  qkv is the fused GEMM output

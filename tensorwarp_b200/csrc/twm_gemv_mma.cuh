@@ -380,9 +380,18 @@ gemv_kernel(const __grid_constant__ GemmParams p)
     const bool consumer = warp < CONSUMER_WARPS;
     const int nA = n0 + wcol + g, nB = nA + 8;
     const int mA = 2 * t, mB = 2 * t + 1;
+    // tensor-parallel push: this launch's sequence number and buffer set (stable for the whole
+    // launch: only the consumer kernel that follows advances it)
+    const unsigned int comm_seq = p.n_peers ? ld_volatile_u32(p.comm_state) : 0u;
     auto store_c = [&](int m, int n, float v) {
         if (m >= p.M || n >= p.N) return;
         const size_t off = (size_t)m * p.ldc + n;
+        if (p.n_peers) {
+            // plain stores into every peer's receive slot (its own GPU's memory), this rank's own included
+            const size_t slot = ((size_t)(comm_seq & 1u) * p.n_peers + p.peer_rank) * p.peer_slot_elems + off;
+            for (int s = 0; s < p.n_peers; ++s) p.peer_data[s][slot] = v;
+            return;
+        }
         if (p.c_is_f16) {
             __half* cp = reinterpret_cast<__half*>(p.c);
             if (p.accumulate) v += __half2float(cp[off]);
@@ -391,6 +400,19 @@ gemv_kernel(const __grid_constant__ GemmParams p)
             float* cp = reinterpret_cast<float*>(p.c);
             if (p.accumulate) v += cp[off];
             cp[off] = v;
+        }
+    };
+
+    // After a CTA's stores (if any): make them visible system-wide and count the CTA; the last CTA
+    // of the grid tells every peer that this rank's partial for operation comm_seq is complete.
+    auto comm_cta_done = [&]() {            // called by thread 0 after a CTA-wide barrier
+        __threadfence_system();
+        const unsigned int total = gridDim.x * gridDim.y;
+        if (atomicAdd(&p.comm_state[1], 1u) == total - 1) {
+            atomicExch(&p.comm_state[1], 0u);
+            __threadfence_system();
+            for (int s = 0; s < p.n_peers; ++s)
+                st_release_sys_u32(p.peer_flags[s] + ((comm_seq & 1u) * p.n_peers + p.peer_rank) * 8, comm_seq + 1u);
         }
     };
 
@@ -415,15 +437,27 @@ gemv_kernel(const __grid_constant__ GemmParams p)
             for (int sp = 0; sp < p.splits; ++sp) s += sm.red[sp][m][col];
             store_c(m, n0 + col, s);
         }
+        if (p.n_peers) {
+            __threadfence_system();
+            __syncthreads();
+            if (tid == 0) comm_cta_done();
+        }
         TL_MARK(p.launch_id, 3);
         return;
     }
 
     if (!consumer) return;
     named_bar_sync(1, CONSUMERS);
-    if (*abort_flag) return;                  // a wait expired: leave C untouched, the error word is set
+    if (*abort_flag && !p.n_peers) return;    // a wait expired: leave C untouched, the error word is set
     if (p.splits == 1) {
-        store_c(mA, nA, tot[0]); store_c(mB, nA, tot[1]); store_c(mA, nB, tot[2]); store_c(mB, nB, tot[3]);
+        if (*abort_flag == 0) {
+            store_c(mA, nA, tot[0]); store_c(mB, nA, tot[1]); store_c(mA, nB, tot[2]); store_c(mB, nB, tot[3]);
+        }
+        if (p.n_peers) {
+            __threadfence_system();
+            named_bar_sync(1, CONSUMERS);
+            if (tid == 0) comm_cta_done();
+        }
         TL_MARK(p.launch_id, 3);
         return;
     }

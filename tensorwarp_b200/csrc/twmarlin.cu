@@ -440,6 +440,13 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
         if (reinterpret_cast<uintptr_t>(a->workspace) & 15) return TWM_EALIGN;
     }
 
+    if (a->comm) {
+        // pushing the result to tensor-parallel peers: streaming MMA kernel, no workspace-based split
+        const twm_comm* cm = a->comm;
+        if (kernel != TWM_KERNEL_MMA || a->M > twm::mma::CLUSTER_ROWS || (pl.splits > 1 && !pl.cluster_reduce)) return TWM_EINVAL;
+        if (cm->n_ranks < 1 || cm->n_ranks > 8 || cm->rank < 0 || cm->rank >= cm->n_ranks || !cm->state) return TWM_EINVAL;
+        if (cm->slot_elems < (long)a->M * a->ldc) return TWM_EINVAL;
+    }
     cudaStream_t stream = (cudaStream_t)stream_;
     const size_t a_elt = a->a_dtype == TWM_F16 ? 2 : 4;
     const size_t c_elt = a->c_dtype == TWM_F16 ? 2 : 4;
@@ -465,6 +472,11 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
         p.cluster_reduce = (pl.cluster_reduce && rows <= twm::mma::CLUSTER_ROWS) ? 1 : 0;
         p.accumulate = (a->flags & TWM_FLAG_ACCUMULATE) ? 1 : 0;
         p.packed_offsets = a->packed_offsets; p.scales_offsets = a->scales_offsets; p.expert_idx = a->expert_idx;
+        if (a->comm) {
+            p.n_peers = a->comm->n_ranks; p.peer_rank = a->comm->rank; p.peer_slot_elems = a->comm->slot_elems;
+            for (int r = 0; r < a->comm->n_ranks; ++r) { p.peer_data[r] = a->comm->data[r]; p.peer_flags[r] = a->comm->flags[r]; }
+            p.comm_state = a->comm->state;
+        }
         p.map_rows = map_rows;
 #ifdef TWM_TIMELINE
         p.launch_id = g_launch_counter++;
@@ -737,6 +749,86 @@ twm_status twm_lm_head(float* logits, const void* x, const void* w, int hidden, 
     const int grid = std::min((vocab + 7) / 8, sms * 8);
     return launch_op("twm_lm_head", twm::ops::lm_head_kernel, dim3(grid), dim3(256), (size_t)hidden * 2, flags, stream,
                      logits, (const __half*)x, (const __half*)w, hidden, vocab);
+}
+
+// ------------------------------------------------------- tensor-parallel plumbing --
+namespace {
+constexpr size_t kCommHeaderBytes = 4096;      // state words (first 256 bytes) and flags (from byte 1024)
+}
+
+size_t twm_comm_bytes(int n_ranks, long slot_elems)
+{
+    if (n_ranks < 1 || n_ranks > 8 || slot_elems < 1) return 0;
+    return kCommHeaderBytes + (size_t)2 * n_ranks * slot_elems * sizeof(float);
+}
+
+twm_status twm_comm_layout(void* base, int n_ranks, long slot_elems, float** data, unsigned int** flags,
+                           unsigned int** state)
+{
+    if (!base || n_ranks < 1 || n_ranks > 8 || slot_elems < 1) return TWM_EINVAL;
+    if (reinterpret_cast<uintptr_t>(base) & 255) return TWM_EALIGN;
+    if (state) *state = (unsigned int*)base;
+    if (flags) *flags = (unsigned int*)((char*)base + 1024);
+    if (data) *data = (float*)((char*)base + kCommHeaderBytes);
+    return TWM_OK;
+}
+
+twm_status twm_allreduce_add_rmsnorm(void* y, float* x, const twm_comm* comm, const float* gamma, int rows, int hidden,
+                                     float eps, int flags, void* stream)
+{
+    if (!x || !comm || (y && !gamma) || rows < 1 || hidden < 1) return TWM_EINVAL;
+    if (comm->n_ranks < 1 || comm->n_ranks > 8 || comm->rank < 0 || comm->rank >= comm->n_ranks) return TWM_EINVAL;
+    if (comm->slot_elems < (long)rows * hidden) return TWM_EINVAL;
+    twm_status st = ensure_device(nullptr);
+    if (st != TWM_OK) return st;
+    return launch_op("twm_allreduce_add_rmsnorm", twm::ops::allreduce_add_rmsnorm_kernel, dim3(rows), dim3(256), 0, flags,
+                     stream, (__half*)y, x, (const float*)comm->data[comm->rank], (const unsigned int*)comm->flags[comm->rank],
+                     comm->state, gamma, hidden, eps, comm->n_ranks, comm->slot_elems);
+}
+
+twm_status twm_ipc_alloc(size_t bytes, void** ptr)
+{
+    if (!ptr || bytes == 0) return TWM_EINVAL;
+    cudaError_t e = cudaMalloc(ptr, bytes);
+    if (e == cudaSuccess) e = cudaMemset(*ptr, 0, bytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) { set_error("twm_ipc_alloc", e); return TWM_ELAUNCH; }
+    return TWM_OK;
+}
+
+twm_status twm_ipc_free(void* ptr)
+{
+    cudaError_t e = cudaFree(ptr);
+    if (e != cudaSuccess) { set_error("twm_ipc_free", e); return TWM_ELAUNCH; }
+    return TWM_OK;
+}
+
+twm_status twm_ipc_get_handle(void* ptr, unsigned char handle[64])
+{
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    if (!ptr || !handle) return TWM_EINVAL;
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, ptr);
+    if (e != cudaSuccess) { set_error("cudaIpcGetMemHandle", e); return TWM_ELAUNCH; }
+    memcpy(handle, &h, 64);
+    return TWM_OK;
+}
+
+twm_status twm_ipc_open(const unsigned char handle[64], void** ptr)
+{
+    if (!ptr || !handle) return TWM_EINVAL;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    cudaError_t e = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) { set_error("cudaIpcOpenMemHandle", e); return TWM_ELAUNCH; }
+    return TWM_OK;
+}
+
+twm_status twm_ipc_close(void* ptr)
+{
+    cudaError_t e = cudaIpcCloseMemHandle(ptr);
+    if (e != cudaSuccess) { set_error("cudaIpcCloseMemHandle", e); return TWM_ELAUNCH; }
+    return TWM_OK;
 }
 
 size_t twm_argmax_scratch_bytes(void) { return (size_t)kArgmaxParts * 8; }

@@ -120,15 +120,91 @@ def random_shard_layer(cfg: TransformerConfig, spec: ShardSpec, layer: int, devi
                           wgu=rnd(h, spec.n_gu, 4), w_down=rnd(nf, h, 6))
 
 
+class PeerComm:
+    """One rank's view of the group's receive buffers for the one-shot all-reduce that the
+    row-parallel GEMMs push into (``twm_comm``).  Between processes the buffers are shared through
+    CUDA IPC; inside one process (tests on a single GPU) they are plain allocations."""
+
+    def __init__(self, n_ranks: int, rank: int, slot_elems: int, bases: List[int], owned: Optional[int] = None,
+                 opened: Optional[List[int]] = None):
+        lib = _lib.lib()
+        self.n_ranks, self.rank, self.slot_elems = n_ranks, rank, slot_elems
+        self._owned, self._opened = owned, opened or []
+        self.struct = _lib.Comm(n_ranks=n_ranks, rank=rank, slot_elems=slot_elems)
+        for s_, base in enumerate(bases):
+            d, f, st = C.c_void_p(), C.c_void_p(), C.c_void_p()
+            check(lib.twm_comm_layout(C.c_void_p(base), n_ranks, slot_elems, C.byref(d), C.byref(f), C.byref(st)),
+                  "twm_comm_layout")
+            self.struct.data[s_] = d.value
+            self.struct.flags[s_] = f.value
+            if s_ == rank:
+                self.struct.state = st.value
+
+    @property
+    def ptr(self) -> int:
+        return C.addressof(self.struct)
+
+    @staticmethod
+    def _alloc(nbytes: int) -> int:
+        p = C.c_void_p()
+        check(_lib.lib().twm_ipc_alloc(nbytes, C.byref(p)), "twm_ipc_alloc")
+        return p.value
+
+    @classmethod
+    def local_group(cls, n_ranks: int, slot_elems: int) -> List["PeerComm"]:
+        """All ranks in this process, on the current device (single-GPU emulation)."""
+        nbytes = _lib.lib().twm_comm_bytes(n_ranks, slot_elems)
+        bases = [cls._alloc(nbytes) for _ in range(n_ranks)]
+        return [cls(n_ranks, r, slot_elems, bases, owned=bases[r]) for r in range(n_ranks)]
+
+    @classmethod
+    def distributed(cls, slot_elems: int) -> "PeerComm":
+        """One rank per process under torch.distributed: allocate, exchange IPC handles, map the peers."""
+        import torch.distributed as dist
+        lib = _lib.lib()
+        n, r = dist.get_world_size(), dist.get_rank()
+        mine = cls._alloc(lib.twm_comm_bytes(n, slot_elems))
+        hbuf = C.create_string_buffer(64)
+        check(lib.twm_ipc_get_handle(C.c_void_p(mine), hbuf), "twm_ipc_get_handle")
+        handles: List[Optional[bytes]] = [None] * n
+        dist.all_gather_object(handles, bytes(hbuf.raw))
+        bases, opened = [], []
+        for s_ in range(n):
+            if s_ == r:
+                bases.append(mine)
+            else:
+                p = C.c_void_p()
+                check(lib.twm_ipc_open(C.create_string_buffer(handles[s_], 64), C.byref(p)), "twm_ipc_open")
+                bases.append(p.value)
+                opened.append(p.value)
+        dist.barrier()
+        return cls(n, r, slot_elems, bases, owned=mine, opened=opened)
+
+    def close(self) -> None:
+        lib = _lib.lib()
+        for p in self._opened:
+            lib.twm_ipc_close(C.c_void_p(p))
+        self._opened = []
+        if self._owned is not None:
+            lib.twm_ipc_free(C.c_void_p(self._owned))
+            self._owned = None
+
+
 class TPDecodeStack:
     """One rank's decode layer stack for `rows` sequences decoding in lock step (configs[4]: the
     layer stack only, no embedding or LM head)."""
 
     def __init__(self, cfg: TransformerConfig, spec: ShardSpec, layers: List[TPLayerWeights], rows: int, device,
-                 all_reduce: Callable[[torch.Tensor], None], use_pdl: bool = True):
+                 all_reduce: Callable[[torch.Tensor], None], use_pdl: bool = True, comm: Optional[PeerComm] = None):
         self.cfg, self.spec, self.layers, self.rows = cfg, spec, layers, rows
         self.device = torch.device(device)
         self.all_reduce = all_reduce
+        # With `comm` (and at most two rows) the row-parallel GEMMs push their FP32 result straight
+        # into every rank's receive buffer and the following add + RMSNorm kernel takes the sum:
+        # no collective call, no extra launch.  Otherwise `all_reduce` (NCCL) runs on `part`.
+        self.comm = comm if (comm is not None and rows <= 2) else None
+        if self.comm is not None and self.comm.slot_elems < rows * cfg.hidden:
+            raise ValueError("comm slots are smaller than rows * hidden")
         self.flags = _lib.TWM_FLAG_PDL if use_pdl else 0
         f16, f32, i32 = torch.float16, torch.float32, torch.int32
         dev, m, h, hd = self.device, rows, cfg.hidden, cfg.head_dim
@@ -163,25 +239,35 @@ class TPDecodeStack:
         self.pos.fill_(length)
         self.cache_len.fill_(length + 1)
 
-    def _gemm(self, a, w, c, n_out, k_in, stream_ptr):
+    def _gemm(self, a, w, c, n_out, k_in, stream_ptr, push=False):
         args = _lib.GemmArgs(M=self.rows, N=n_out, K=k_in, group_size=self.cfg.group_size, a_dtype=_lib.TWM_F16,
                              c_dtype=_lib.TWM_F32 if c.dtype == torch.float32 else _lib.TWM_F16,
                              a=a.data_ptr(), lda=k_in, packed=w[0].data_ptr(), scales=w[1].data_ptr(),
                              c=c.data_ptr(), ldc=n_out, workspace=self.workspace.ptr,
-                             workspace_bytes=self.workspace.nbytes, flags=self.flags)
+                             workspace_bytes=self.workspace.nbytes, flags=self.flags,
+                             comm=self.comm.ptr if (push and self.comm is not None) else None)
         check(_lib.lib().twm_gemm_w4a16(C.byref(args), stream_ptr), "twm_gemm_w4a16")
         self.launches += 1
 
+    def _join_and_norm(self, y_ptr, gamma_ptr, stream_ptr) -> None:
+        """The summed output of the last row-parallel GEMM joins the residual stream, then RMSNorm."""
+        lib, cfg = _lib.lib(), self.cfg
+        if self.comm is not None:
+            check(lib.twm_allreduce_add_rmsnorm(y_ptr, self.x.data_ptr(), self.comm.ptr, gamma_ptr, self.rows, cfg.hidden,
+                                                cfg.eps, self.flags, stream_ptr), "twm_allreduce_add_rmsnorm")
+        else:
+            check(lib.twm_add_rmsnorm(y_ptr, self.x.data_ptr(), self.part.data_ptr(), gamma_ptr, self.rows, cfg.hidden,
+                                      cfg.eps, self.flags, stream_ptr), "twm_add_rmsnorm")
+
     def attn_phase(self, li: int, stream_ptr: int) -> None:
         """Norm, column-parallel QKV, RoPE/append, attention, row-parallel o: leaves this rank's
-        partial o output in `part` (to be summed over ranks)."""
+        partial o output in `part` (to be summed over ranks) or, with `comm`, in every rank's slot."""
         lib, cfg, fl, m, lw, hd = _lib.lib(), self.cfg, self.flags, self.rows, self.layers[li], self.cfg.head_dim
         if li == 0:
             check(lib.twm_rmsnorm(self.normed.data_ptr(), self.x.data_ptr(), lw.attn_norm.data_ptr(), m, cfg.hidden,
                                   cfg.eps, fl, stream_ptr), "twm_rmsnorm")
-        else:           # the previous layer's all-reduced down output joins the residual stream here
-            check(lib.twm_add_rmsnorm(self.normed.data_ptr(), self.x.data_ptr(), self.part.data_ptr(),
-                                      lw.attn_norm.data_ptr(), m, cfg.hidden, cfg.eps, fl, stream_ptr), "twm_add_rmsnorm")
+        else:           # the previous layer's summed down output joins the residual stream here
+            self._join_and_norm(self.normed.data_ptr(), lw.attn_norm.data_ptr(), stream_ptr)
         self._gemm(self.normed, lw.wqkv, self.qkv, self.spec.n_qkv, cfg.hidden, stream_ptr)            # column-parallel
         check(lib.twm_rope_append(self.q.data_ptr(), self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(),
                                   self.qkv.data_ptr(), lw.bqkv.data_ptr() if lw.bqkv is not None else None, m,
@@ -192,24 +278,22 @@ class TPDecodeStack:
                                   cfg.max_seq, self.attn_scratch.data_ptr(), self.attn_scratch.numel(), fl,
                                   stream_ptr), "twm_attn_decode")
         self.launches += 4
-        self._gemm(self.attn, lw.wo, self.part, cfg.hidden, self.hq * hd, stream_ptr)                   # row-parallel
+        self._gemm(self.attn, lw.wo, self.part, cfg.hidden, self.hq * hd, stream_ptr, push=True)        # row-parallel
 
     def ffn_phase(self, li: int, stream_ptr: int) -> None:
         """Add the all-reduced o output, norm, column-parallel gate+up, SwiGLU, row-parallel down:
         leaves this rank's partial down output in `part`."""
         lib, cfg, fl, m, lw = _lib.lib(), self.cfg, self.flags, self.rows, self.layers[li]
-        check(lib.twm_add_rmsnorm(self.normed.data_ptr(), self.x.data_ptr(), self.part.data_ptr(),
-                                  lw.ffn_norm.data_ptr(), m, cfg.hidden, cfg.eps, fl, stream_ptr), "twm_add_rmsnorm")
+        self._join_and_norm(self.normed.data_ptr(), lw.ffn_norm.data_ptr(), stream_ptr)
         self._gemm(self.normed, lw.wgu, self.gate_up, self.spec.n_gu, cfg.hidden, stream_ptr)            # column-parallel
         check(lib.twm_silu_mul(self.act.data_ptr(), self.gate_up.data_ptr(), m, self.spec.n_gu // 2, fl, stream_ptr),
               "twm_silu_mul")
         self.launches += 2
-        self._gemm(self.act, lw.w_down, self.part, cfg.hidden, self.spec.n_gu // 2, stream_ptr)         # row-parallel
+        self._gemm(self.act, lw.w_down, self.part, cfg.hidden, self.spec.n_gu // 2, stream_ptr, push=True)   # row-parallel
 
     def finish(self, stream_ptr: int) -> None:
-        """The last layer's all-reduced down output joins the residual stream."""
-        check(_lib.lib().twm_add_rmsnorm(None, self.x.data_ptr(), self.part.data_ptr(), None, self.rows, self.cfg.hidden,
-                                         self.cfg.eps, self.flags, stream_ptr), "twm_add_rmsnorm")
+        """The last layer's summed down output joins the residual stream."""
+        self._join_and_norm(None, None, stream_ptr)
         self.launches += 1
 
     def forward(self, stream_ptr: int) -> None:
@@ -218,7 +302,9 @@ class TPDecodeStack:
         self.launches = 0
         for li in range(len(self.layers)):
             self.attn_phase(li, stream_ptr)
-            self.all_reduce(self.part)
+            if self.comm is None:
+                self.all_reduce(self.part)
             self.ffn_phase(li, stream_ptr)
-            self.all_reduce(self.part)
+            if self.comm is None:
+                self.all_reduce(self.part)
         self.finish(stream_ptr)

@@ -31,13 +31,14 @@ def _full_layers(cfg, seed):
     return out
 
 
-def _run(cfg, full, degree, rows, x0, kv_len):
+def _run(cfg, full, degree, rows, x0, kv_len, fused=False):
     ones = torch.ones(cfg.hidden, device="cuda")
     stacks = []
+    comms = tp.PeerComm.local_group(degree, rows * cfg.hidden) if fused else [None] * degree
     for r in range(degree):
         spec = tp.shard_spec(cfg, degree, r)
         layers = [tp.shard_layer(cfg, spec, *mats, ones, ones) for mats in full]
-        st = tp.TPDecodeStack(cfg, spec, layers, rows, "cuda", all_reduce=lambda t: None)
+        st = tp.TPDecodeStack(cfg, spec, layers, rows, "cuda", all_reduce=lambda t: None, comm=comms[r])
         stacks.append(st)
     # the same random KV cache for every degree: generate the full cache, hand each rank its kv heads
     gen = torch.Generator(device="cuda").manual_seed(11)
@@ -55,6 +56,8 @@ def _run(cfg, full, degree, rows, x0, kv_len):
     sp = torch.cuda.current_stream().cuda_stream
 
     def reduce_all():
+        if fused:          # the GEMM epilogues already pushed every rank's partial into every rank's buffer
+            return
         total = sum(st.part for st in stacks)
         for st in stacks:
             st.part.copy_(total)
@@ -70,10 +73,14 @@ def _run(cfg, full, degree, rows, x0, kv_len):
         st.finish(sp)
     torch.cuda.synchronize()
     assert q.device_error() == 0
-    return [st.x.cpu().numpy() for st in stacks]
+    out = [st.x.cpu().numpy() for st in stacks]
+    for c in comms:
+        if c is not None:
+            c.close()
+    return out
 
 
-@pytest.mark.parametrize("rows", [1, 3])
+@pytest.mark.parametrize("rows", [1, 2, 3])
 def test_sharded_stack_equals_unsharded(rows):
     cfg = CFG
     full = _full_layers(cfg, 21)
@@ -86,3 +93,9 @@ def test_sharded_stack_equals_unsharded(rows):
             assert np.array_equal(o, outs[0])                 # every rank ends with the same activations
         err = float(np.max(np.abs(outs[0] - ref))) / rms
         assert err < 2e-3, (degree, err)                      # FP32 partials, different summation order only
+        if rows <= 2:
+            # the fused path: GEMM epilogues push into the peers' buffers, add+RMSNorm takes the sum
+            fused = _run(cfg, full, degree, rows, x0, 100, fused=True)
+            for o in fused[1:]:
+                assert np.array_equal(o, fused[0])
+            assert float(np.max(np.abs(fused[0] - ref))) / rms < 2e-3, degree
