@@ -128,14 +128,15 @@ rmsnorm_kernel(__half* __restrict__ y, float* __restrict__ x, const float* __res
 // NVLink), add the slots in rank order (every rank gets the same bits), x += sum, y = norm(x).
 // One CTA per row; the last CTA to finish advances the operation sequence number.  The
 // reference sums partial outputs on the host (crates/kernels/src/multi_gpu.rs:329-366).
-__global__ void __launch_bounds__(256)
+constexpr int ARN_THREADS = 1024;
+__global__ void __launch_bounds__(ARN_THREADS)
 allreduce_add_rmsnorm_kernel(__half* __restrict__ y, float* __restrict__ x, const float* __restrict__ recv,
                              const unsigned int* __restrict__ flags, unsigned int* __restrict__ state,
                              const float* __restrict__ gamma, int hidden, float eps, int n_ranks, long slot_elems)
 {
     pdl_launch_dependents();
     pdl_wait_prior_grids();
-    __shared__ float partial[8];
+    __shared__ float partial[ARN_THREADS / 32];
     __shared__ int s_ok;
     const int row = blockIdx.x;
     const unsigned int seq = ld_volatile_u32(state);
@@ -148,7 +149,7 @@ allreduce_add_rmsnorm_kernel(__half* __restrict__ y, float* __restrict__ x, cons
         bool got = false;
         for (unsigned int i = 0; i < (1u << 22) && !got; ++i) {
             got = ld_acquire_sys_u32(f) == seq + 1u;
-            if (!got && i > 32) __nanosleep(128);
+            if (!got && i > 64) __nanosleep(128);
         }
         if (!got) { s_ok = 0; atomicOr(&g_error_word, 4u); }
     }
@@ -156,13 +157,37 @@ allreduce_add_rmsnorm_kernel(__half* __restrict__ y, float* __restrict__ x, cons
     float* xr = x + (size_t)row * hidden;
     const float* base = recv + (size_t)set * n_ranks * slot_elems + (size_t)row * hidden;
     float ss = 0.0f;
+    // hidden is a multiple of 4 (checked by the host); each thread keeps at most VPT float4 of x
+    constexpr int VPT = 4;
+    const int nvec = hidden >> 2;
+    float4 keep[VPT];
     if (s_ok) {
-        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-            float acc = 0.0f;
-            for (int r = 0; r < n_ranks; ++r) acc += __ldcg(base + (size_t)r * slot_elems + i);
-            const float v = xr[i] + acc;
-            xr[i] = v;
-            ss = fmaf(v, v, ss);
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int i = threadIdx.x + j * ARN_THREADS;
+            if (i < nvec) {
+                float4 acc = __ldcg(reinterpret_cast<const float4*>(base) + i);
+                for (int r = 1; r < n_ranks; ++r) {
+                    const float4 t = __ldcg(reinterpret_cast<const float4*>(base + (size_t)r * slot_elems) + i);
+                    acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+                }
+                float4 v = reinterpret_cast<float4*>(xr)[i];
+                v.x += acc.x; v.y += acc.y; v.z += acc.z; v.w += acc.w;
+                reinterpret_cast<float4*>(xr)[i] = v;
+                keep[j] = v;
+                ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+            }
+        }
+        for (int i = threadIdx.x + VPT * ARN_THREADS; i < nvec; i += ARN_THREADS) {      // very wide rows
+            float4 acc = __ldcg(reinterpret_cast<const float4*>(base) + i);
+            for (int r = 1; r < n_ranks; ++r) {
+                const float4 t = __ldcg(reinterpret_cast<const float4*>(base + (size_t)r * slot_elems) + i);
+                acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+            }
+            float4 v = reinterpret_cast<float4*>(xr)[i];
+            v.x += acc.x; v.y += acc.y; v.z += acc.z; v.w += acc.w;
+            reinterpret_cast<float4*>(xr)[i] = v;
+            ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
         }
     }
     if (y != nullptr) {
@@ -171,10 +196,34 @@ allreduce_add_rmsnorm_kernel(__half* __restrict__ y, float* __restrict__ x, cons
         __syncthreads();
         float tot = 0.0f;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) tot += partial[w];
+        for (int w = 0; w < ARN_THREADS / 32; ++w) tot += partial[w];
         const float rms = rsqrtf(tot / (float)hidden + eps);
-        for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-            y[(size_t)row * hidden + i] = __float2half_rn(xr[i] * rms * gamma[i]);
+        __half* yr = y + (size_t)row * hidden;
+        if (s_ok) {
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int i = threadIdx.x + j * ARN_THREADS;
+                if (i < nvec) {
+                    const float4 g = __ldg(reinterpret_cast<const float4*>(gamma) + i);
+                    const __half2 h0 = __floats2half2_rn(keep[j].x * rms * g.x, keep[j].y * rms * g.y);
+                    const __half2 h1 = __floats2half2_rn(keep[j].z * rms * g.z, keep[j].w * rms * g.w);
+                    uint2 o;
+                    o.x = *reinterpret_cast<const unsigned int*>(&h0);
+                    o.y = *reinterpret_cast<const unsigned int*>(&h1);
+                    reinterpret_cast<uint2*>(yr)[i] = o;
+                }
+            }
+            for (int i = threadIdx.x + VPT * ARN_THREADS; i < nvec; i += ARN_THREADS) {
+                const float4 v = reinterpret_cast<const float4*>(xr)[i];
+                const float4 g = __ldg(reinterpret_cast<const float4*>(gamma) + i);
+                const __half2 h0 = __floats2half2_rn(v.x * rms * g.x, v.y * rms * g.y);
+                const __half2 h1 = __floats2half2_rn(v.z * rms * g.z, v.w * rms * g.w);
+                uint2 o;
+                o.x = *reinterpret_cast<const unsigned int*>(&h0);
+                o.y = *reinterpret_cast<const unsigned int*>(&h1);
+                reinterpret_cast<uint2*>(yr)[i] = o;
+            }
+        }
     }
     __syncthreads();
     if (threadIdx.x == 0) {

@@ -405,12 +405,14 @@ gemv_kernel(const __grid_constant__ GemmParams p)
 
     // After a CTA's stores (if any): make them visible system-wide and count the CTA; the last CTA
     // of the grid tells every peer that this rank's partial for operation comm_seq is complete.
-    auto comm_cta_done = [&]() {            // called by thread 0 after a CTA-wide barrier
+    // Called by ONE thread of each storing CTA after a CTA-wide barrier: the barrier orders the
+    // CTA's stores before this thread, its system-scope fence is cumulative over them, and the
+    // release stores of the last CTA carry every counted CTA's stores with them.  (A fence by
+    // every thread would cost a link round trip each.)
+    auto comm_cta_done = [&](unsigned int total) {
         __threadfence_system();
-        const unsigned int total = gridDim.x * gridDim.y;
         if (atomicAdd(&p.comm_state[1], 1u) == total - 1) {
             atomicExch(&p.comm_state[1], 0u);
-            __threadfence_system();
             for (int s = 0; s < p.n_peers; ++s)
                 st_release_sys_u32(p.peer_flags[s] + ((comm_seq & 1u) * p.n_peers + p.peer_rank) * 8, comm_seq + 1u);
         }
@@ -437,10 +439,9 @@ gemv_kernel(const __grid_constant__ GemmParams p)
             for (int sp = 0; sp < p.splits; ++sp) s += sm.red[sp][m][col];
             store_c(m, n0 + col, s);
         }
-        if (p.n_peers) {
-            __threadfence_system();
+        if (p.n_peers && rank == 0) {       // only the cluster leaders store
             __syncthreads();
-            if (tid == 0) comm_cta_done();
+            if (tid == 0) comm_cta_done(gridDim.x);
         }
         TL_MARK(p.launch_id, 3);
         return;
@@ -454,9 +455,8 @@ gemv_kernel(const __grid_constant__ GemmParams p)
             store_c(mA, nA, tot[0]); store_c(mB, nA, tot[1]); store_c(mA, nB, tot[2]); store_c(mB, nB, tot[3]);
         }
         if (p.n_peers) {
-            __threadfence_system();
             named_bar_sync(1, CONSUMERS);
-            if (tid == 0) comm_cta_done();
+            if (tid == 0) comm_cta_done(gridDim.x * gridDim.y);
         }
         TL_MARK(p.launch_id, 3);
         return;

@@ -778,10 +778,11 @@ twm_status twm_allreduce_add_rmsnorm(void* y, float* x, const twm_comm* comm, co
 {
     if (!x || !comm || (y && !gamma) || rows < 1 || hidden < 1) return TWM_EINVAL;
     if (comm->n_ranks < 1 || comm->n_ranks > 8 || comm->rank < 0 || comm->rank >= comm->n_ranks) return TWM_EINVAL;
-    if (comm->slot_elems < (long)rows * hidden) return TWM_EINVAL;
+    if (comm->slot_elems < (long)rows * hidden || (hidden & 3) || (comm->slot_elems & 3)) return TWM_EINVAL;
     twm_status st = ensure_device(nullptr);
     if (st != TWM_OK) return st;
-    return launch_op("twm_allreduce_add_rmsnorm", twm::ops::allreduce_add_rmsnorm_kernel, dim3(rows), dim3(256), 0, flags,
+    return launch_op("twm_allreduce_add_rmsnorm", twm::ops::allreduce_add_rmsnorm_kernel, dim3(rows),
+                     dim3(twm::ops::ARN_THREADS), 0, flags,
                      stream, (__half*)y, x, (const float*)comm->data[comm->rank], (const unsigned int*)comm->flags[comm->rank],
                      comm->state, gamma, hidden, eps, comm->n_ranks, comm->slot_elems);
 }
