@@ -46,7 +46,11 @@ enum {
     TWM_KERNEL_AUTO = 0,
     TWM_KERNEL_SIMT = 1, /* streaming kernel, FP32 FMA; the only one that takes FP32 activations */
     TWM_KERNEL_TC = 2,   /* tcgen05 kernel: weights dequantised into tensor memory, FP32 accumulate in TMEM */
-    TWM_KERNEL_MMA = 3   /* streaming kernel for M <= 8, FP16 activations, warp-level MMA on unpacked registers */
+    TWM_KERNEL_MMA = 3,  /* streaming kernel for M <= 8, FP16 activations, warp-level MMA on unpacked registers,
+                            128-column tiles with split-K: small N, indirect (expert) weights, N not a multiple of 8 */
+    TWM_KERNEL_STRIP = 4 /* same arithmetic, one CTA per SM owning 32-column strips over the whole K: no split-K, no
+                            workspace, half an SM per launch so that consecutive GEMMs overlap.  Never picked by
+                            the heuristic (measured slower on B200); N % 8 == 0, activations must fit in shared memory */
 };
 
 /* Flags of twm_gemm_args.flags. */
@@ -105,13 +109,13 @@ typedef struct twm_gemm_args {
     /* Tensor-parallel row shard: when comm != NULL the FP32 result is not stored to `c` but pushed
      * into every rank's receive buffer (plain stores over NVLink into the peer's own memory, tile
      * by tile as the tiles finish), and the grid's last CTA raises the arrival flags.  The sum is
-     * taken by twm_allreduce_add_rmsnorm on each rank.  M <= 2, FP16 activations. */
+     * taken by twm_allreduce_add_rmsnorm on each rank.  M <= 8, FP16 activations. */
     const twm_comm* comm;
 } twm_gemm_args;
 
 /* What the heuristic decided for a shape; pure host arithmetic. */
 typedef struct twm_plan_t {
-    int kernel;          /* TWM_KERNEL_SIMT or TWM_KERNEL_TC */
+    int kernel;          /* the TWM_KERNEL_* that will run */
     int n_tile;          /* columns per CTA */
     int splits;          /* K slices; 1 = no workspace traffic */
     int blocks_per_split;/* 32-blocks of K per slice (last slice may be shorter) */

@@ -192,10 +192,10 @@ __device__ unsigned long long g_prof[64];
 
 #ifdef TWM_TIMELINE
 // development builds only: per-CTA wall-clock marks (globaltimer, ns) of the last launches
-__device__ unsigned long long g_timeline[64 * 512 * 4];
+__device__ unsigned long long g_timeline[64 * 512 * 8];
 __device__ unsigned int g_timeline_launch;
 __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define TL_MARK(launch, idx) if (threadIdx.x == 0 && (launch) < 64) g_timeline[(((launch) * 512) + blockIdx.y * gridDim.x + blockIdx.x) * 4 + (idx)] = gtime()
+#define TL_MARK(launch, idx) if (threadIdx.x == 0 && (launch) < 64) g_timeline[(((launch) * 512) + blockIdx.y * gridDim.x + blockIdx.x) * 8 + (idx)] = gtime()
 #else
 #define TL_MARK(launch, idx)
 #endif
@@ -233,9 +233,12 @@ struct GemmParams {
     unsigned int* comm_state;        // [0] operation sequence number, [1] CTAs done, [2] consumer CTAs done
     // Tensor map over `packed` seen as u64 [K/32][2N]: one TMA instruction brings a whole
     // ring stage (box = 256 u64 x map_rows rows = 128 columns x map_rows 32-blocks).
+    int strip_stages;            // strip kernel: depth of the weight ring (what fits beside the activations)
     int map_rows;                // 0 = no map (1-D bulk copies per row instead)
     int launch_id;               // development builds: index of this launch in the timeline buffer
     alignas(64) CUtensorMap packed_map;
+    // strip kernel: tensor map over the scales, f16 [K/G][N], box = 32 columns x one stage's rows
+    alignas(64) CUtensorMap scale_map;
     // tcgen05 kernel: tensor map over the launch's permuted activations, f16 [K/8][rows][8]
     alignas(64) CUtensorMap act_map;
 };

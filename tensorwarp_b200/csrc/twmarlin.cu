@@ -16,6 +16,7 @@
 #include "twm_gemv_simt.cuh"
 #include "twm_gemm_tc.cuh"
 #include "twm_gemv_mma.cuh"
+#include "twm_gemv_strip.cuh"
 #include "twm_layout.cuh"
 #include "twm_decode_ops.cuh"
 #include "../../include/twm_decode.h"
@@ -103,6 +104,18 @@ twm_status ensure_device(int* sm_count_out)
             raise_mma((const void*)twm::mma::gemv_kernel<2, 2>);
             raise_mma((const void*)twm::mma::gemv_kernel<4, 2>);
             raise_mma((const void*)twm::mma::gemv_kernel<8, 2>);
+            auto raise_strip = [&](const void* fn) {
+                if (r == cudaSuccess)
+                    r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, twm::strip::SMEM_BUDGET);
+            };
+            raise_strip((const void*)twm::strip::gemv_kernel<1, 0>);
+            raise_strip((const void*)twm::strip::gemv_kernel<2, 0>);
+            raise_strip((const void*)twm::strip::gemv_kernel<4, 0>);
+            raise_strip((const void*)twm::strip::gemv_kernel<8, 0>);
+            raise_strip((const void*)twm::strip::gemv_kernel<1, 2>);
+            raise_strip((const void*)twm::strip::gemv_kernel<2, 2>);
+            raise_strip((const void*)twm::strip::gemv_kernel<4, 2>);
+            raise_strip((const void*)twm::strip::gemv_kernel<8, 2>);
             if (r != cudaSuccess) { set_error("cudaFuncSetAttribute", r); st.status = TWM_ELAUNCH; }
         }
         st.ready = true;
@@ -128,17 +141,31 @@ EncodeTiledFn get_encode_tiled()
     return fn;
 }
 
-// Tensor map over packed viewed as u64 [K/32 rows][2N]: box = 256 u64 (128 columns) x `rows`.
+// Tensor map over packed viewed as u64 [K/32 rows][2N]: box = 2 * `cols` u64 x `rows`.
 // Returns false when the map cannot be made (the kernels then copy row by row).
-bool make_packed_map(CUtensorMap* map, const uint8_t* packed, int N, int nkb, int rows)
+bool make_packed_map(CUtensorMap* map, const uint8_t* packed, int N, int nkb, int rows, int cols = 128)
 {
     EncodeTiledFn enc = get_encode_tiled();
     if (!enc) return false;
     const cuuint64_t gdim[2] = {(cuuint64_t)N * 2, (cuuint64_t)nkb};
     const cuuint64_t gstride[1] = {(cuuint64_t)N * 16};
-    const cuuint32_t box[2] = {256, (cuuint32_t)rows};
+    const cuuint32_t box[2] = {(cuuint32_t)cols * 2, (cuuint32_t)rows};
     const cuuint32_t estride[2] = {1, 1};
     return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t*>(packed), gdim, gstride, box, estride,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Tensor map over the scales, f16 [K/G rows][N] (N a multiple of 8): box = `cols` x `rows`.
+bool make_scale_map(CUtensorMap* map, const uint16_t* scales, int N, int n_rows, int rows, int cols)
+{
+    EncodeTiledFn enc = get_encode_tiled();
+    if (!enc || (N & 7)) return false;
+    const cuuint64_t gdim[2] = {(cuuint64_t)N, (cuuint64_t)n_rows};
+    const cuuint64_t gstride[1] = {(cuuint64_t)N * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)cols, (cuuint32_t)rows};
+    const cuuint32_t estride[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<uint16_t*>(scales), gdim, gstride, box, estride,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -202,6 +229,75 @@ void choose_splits(int n_tiles, int nkb, int slots, int max_bps, int align, int 
 }
 
 int mmax_for(int M) { return M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : 8)); }
+
+// Which kernel serves FP16 activations when the caller leaves the choice open.  The strip
+// kernel wants enough 32-column strips to occupy most SMs (it never splits K), scale rows that
+// a tensor map can describe (N a multiple of 8) and weights addressed directly.
+// The rows' activations for the whole K must fit in shared memory beside the weight ring.
+constexpr int kStripMinStrips = 96;
+bool strip_fits(int M, int K, int G) { return twm::strip::pick_stages(K / 32, G, mmax_for(std::min(M, 8))) > 0; }
+bool strip_eligible(int M, int N, int K, int G, bool indirect)
+{
+    return !indirect && (N & 7) == 0 && (N + twm::strip::NT - 1) / twm::strip::NT >= kStripMinStrips && strip_fits(M, K, G);
+}
+int auto_kernel(int M, int N, int K, int G, bool a_is_f16, bool indirect, int splits_override)
+{
+    if (!a_is_f16) return TWM_KERNEL_SIMT;
+    if (M > 8) return TWM_KERNEL_TC;
+    // The strip kernel is not chosen here: measured on the 7B decode chain it is slower than the
+    // split-K kernel (one CTA per SM cannot unpack at HBM rate); it runs when asked for by name.
+    (void)N; (void)K; (void)G; (void)indirect; (void)splits_override;
+    return TWM_KERNEL_MMA;
+}
+
+int resolve_kernel(const twm_gemm_args* a)
+{
+    if (a->kernel_override != TWM_KERNEL_AUTO) return a->kernel_override;
+    int kernel = auto_kernel(a->M, a->N, a->K, a->group_size, a->a_dtype == TWM_F16, a->packed_offsets != nullptr,
+                             a->splits_override);
+    // the scale tensor map needs a 16-byte aligned base (a sub-buffer may not have one)
+    if (kernel == TWM_KERNEL_STRIP && (reinterpret_cast<uintptr_t>(a->scales) & 15)) kernel = TWM_KERNEL_MMA;
+    return kernel;
+}
+
+template <int MP, int GS>
+cudaError_t launch_strip_one(cudaLaunchConfig_t& cfg, const twm::GemmParams& p)
+{
+    cfg.dynamicSmemBytes = twm::strip::make_layout(p.nkb, p.group, MP, p.strip_stages).total;
+    return cudaLaunchKernelEx(&cfg, twm::strip::gemv_kernel<MP, GS>, p);
+}
+
+twm_status launch_strip(const twm::GemmParams& p, int mp, dim3 grid, bool pdl, cudaStream_t stream)
+{
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(twm::strip::THREADS, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cudaError_t e;
+    if (p.group == 128) {
+        switch (mp) {
+            case 1: e = launch_strip_one<1, 2>(cfg, p); break;
+            case 2: e = launch_strip_one<2, 2>(cfg, p); break;
+            case 4: e = launch_strip_one<4, 2>(cfg, p); break;
+            default: e = launch_strip_one<8, 2>(cfg, p); break;
+        }
+    } else {
+        switch (mp) {
+            case 1: e = launch_strip_one<1, 0>(cfg, p); break;
+            case 2: e = launch_strip_one<2, 0>(cfg, p); break;
+            case 4: e = launch_strip_one<4, 0>(cfg, p); break;
+            default: e = launch_strip_one<8, 0>(cfg, p); break;
+        }
+    }
+    if (e != cudaSuccess) { set_error("launch strip::gemv_kernel", e); return TWM_ELAUNCH; }
+    return TWM_OK;
+}
 constexpr int kTcRows = 64;      // activation rows one tcgen05 launch carries
 
 twm_status launch_tc(const twm::GemmParams& p, int rows, dim3 grid, bool pdl, cudaStream_t stream)
@@ -358,7 +454,22 @@ twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int split
     if (sm_count <= 0) sm_count = kDefaultSms;
     const int nkb = K / 32;
     int kernel = kernel_override;
-    if (kernel == TWM_KERNEL_AUTO) kernel = (M <= 8) ? TWM_KERNEL_MMA : TWM_KERNEL_TC;
+    if (kernel == TWM_KERNEL_AUTO) kernel = auto_kernel(M, N, K, group_size, true, false, splits_override);
+    if (kernel == TWM_KERNEL_STRIP) {
+        // one CTA per SM at most, each taking whole strips in turn: no K slices, no workspace
+        if ((N & 7) != 0 || splits_override > 1 || !strip_fits(M, K, group_size)) return TWM_EINVAL;
+        const int n_strips = (N + twm::strip::NT - 1) / twm::strip::NT;
+        const int rounds = (n_strips + sm_count - 1) / sm_count;
+        out->kernel = kernel;
+        out->n_tile = twm::strip::NT;
+        out->splits = 1;
+        out->blocks_per_split = nkb;
+        out->grid_x = (n_strips + rounds - 1) / rounds;
+        out->grid_y = 1;
+        out->workspace_bytes = 0;
+        out->cluster_reduce = 0;
+        return TWM_OK;
+    }
     if (kernel != TWM_KERNEL_SIMT && kernel != TWM_KERNEL_TC && kernel != TWM_KERNEL_MMA) return TWM_EINVAL;
     // rows one launch carries; more rows are served by further launches
     const int rows = std::min(M, kernel == TWM_KERNEL_TC ? kTcRows : 8);
@@ -428,10 +539,9 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
 
     // The tensor-core kernel takes FP16 activations; FP32 activations (the
     // reference's own signature) run on the FP32 streaming kernel.
-    int kernel = a->kernel_override;
-    if (kernel == TWM_KERNEL_AUTO)
-        kernel = (a->a_dtype != TWM_F16) ? TWM_KERNEL_SIMT : (a->M <= 8 ? TWM_KERNEL_MMA : TWM_KERNEL_TC);
+    const int kernel = resolve_kernel(a);
     if (kernel != TWM_KERNEL_SIMT && a->a_dtype != TWM_F16) return TWM_EINVAL;
+    if (kernel == TWM_KERNEL_STRIP && a->packed_offsets != nullptr) return TWM_EINVAL;
     twm_plan_t pl;
     st = twm_plan(a->M, a->N, a->K, a->group_size, sm_count, a->splits_override, kernel, &pl);
     if (st != TWM_OK) return st;
@@ -443,7 +553,9 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
     if (a->comm) {
         // pushing the result to tensor-parallel peers: streaming MMA kernel, no workspace-based split
         const twm_comm* cm = a->comm;
-        if (kernel != TWM_KERNEL_MMA || a->M > twm::mma::CLUSTER_ROWS || (pl.splits > 1 && !pl.cluster_reduce)) return TWM_EINVAL;
+        const bool mma_ok = kernel == TWM_KERNEL_MMA && a->M <= twm::mma::CLUSTER_ROWS && (pl.splits == 1 || pl.cluster_reduce);
+        const bool strip_ok = kernel == TWM_KERNEL_STRIP && a->M <= 8;
+        if (!mma_ok && !strip_ok) return TWM_EINVAL;
         if (cm->n_ranks < 1 || cm->n_ranks > 8 || cm->rank < 0 || cm->rank >= cm->n_ranks || !cm->state) return TWM_EINVAL;
         if (cm->slot_elems < (long)a->M * a->ldc) return TWM_EINVAL;
     }
@@ -451,9 +563,17 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
     const size_t a_elt = a->a_dtype == TWM_F16 ? 2 : 4;
     const size_t c_elt = a->c_dtype == TWM_F16 ? 2 : 4;
     const int row_step = kernel == TWM_KERNEL_TC ? kTcRows : 8;
-    CUtensorMap packed_map;
+    CUtensorMap packed_map, scale_map;
     int map_rows = 0;
-    if (a->packed_offsets == nullptr && a->N >= 128 && kernel != TWM_KERNEL_SIMT) {
+    if (kernel == TWM_KERNEL_STRIP) {
+        const int srows = twm::strip::SBLK / (a->group_size / 32);
+        if (!make_packed_map(&packed_map, a->packed, a->N, a->K / 32, twm::strip::SBLK, twm::strip::NT) ||
+            !make_scale_map(&scale_map, a->scales, a->N, a->K / a->group_size, srows, twm::strip::NT)) {
+            snprintf(t_last_error, sizeof(t_last_error), "cuTensorMapEncodeTiled failed for the strip kernel's maps");
+            return TWM_ELAUNCH;
+        }
+        map_rows = twm::strip::SBLK;
+    } else if (a->packed_offsets == nullptr && a->N >= 128 && kernel != TWM_KERNEL_SIMT) {
         const int want = kernel == TWM_KERNEL_MMA ? twm::mma::SB : twm::tc::WSTAGE_BLOCKS;
         if (make_packed_map(&packed_map, a->packed, a->N, a->K / 32, want)) map_rows = want;
     }
@@ -482,6 +602,10 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
         p.launch_id = g_launch_counter++;
 #endif
         if (map_rows) p.packed_map = packed_map;
+        if (kernel == TWM_KERNEL_STRIP) {
+            p.scale_map = scale_map;
+            p.strip_stages = twm::strip::pick_stages(p.nkb, p.group, mmax_for(rows));
+        }
         const bool pdl = (a->flags & TWM_FLAG_PDL) != 0;
         if (kernel == TWM_KERNEL_TC) {
             // pre-pass: this launch's rows in [K/8][rows][8] order, then the GEMM loads them by TMA
@@ -499,6 +623,8 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
             if (st != TWM_OK) return st;
             st = launch_tc(p, rows, dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
         }
+        else if (kernel == TWM_KERNEL_STRIP)
+            st = launch_strip(p, mmax_for(rows), dim3(pl.grid_x, 1, 1), pdl, stream);
         else if (kernel == TWM_KERNEL_MMA)
             st = launch_mma(p, mmax_for(rows), dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
         else
@@ -519,9 +645,7 @@ twm_status twm_gemm_w4a16_static_ws(const twm_gemm_args* a, void* stream_)
     twm_status st = ensure_device(&sm_count);
     if (st != TWM_OK) return st;
     // the same kernel choice and plan twm_gemm_w4a16 will make for these arguments
-    int kernel = a->kernel_override;
-    if (kernel == TWM_KERNEL_AUTO)
-        kernel = (a->a_dtype != TWM_F16) ? TWM_KERNEL_SIMT : (a->M <= 8 ? TWM_KERNEL_MMA : TWM_KERNEL_TC);
+    const int kernel = resolve_kernel(a);
     twm_plan_t pl;
     st = twm_plan(a->M, a->N, a->K, a->group_size, sm_count, a->splits_override, kernel, &pl);
     if (st != TWM_OK) return st;

@@ -99,3 +99,52 @@ def test_sharded_stack_equals_unsharded(rows):
             for o in fused[1:]:
                 assert np.array_equal(o, fused[0])
             assert float(np.max(np.abs(fused[0] - ref))) / rms < 2e-3, degree
+
+
+@pytest.mark.parametrize("kernel,rows", [(3, 1), (3, 2), (4, 1), (4, 3), (4, 8)])
+def test_row_parallel_push_and_sum(kernel, rows):
+    """The row-parallel GEMM with `comm` on both streaming kernels, then the consumer: every rank's
+    x + sum over ranks equals x + the unsharded GEMM, and all ranks hold the same bits.  Run twice
+    in a row: the sequence number alternates between the two buffer sets."""
+    import ctypes as C
+    from tensorwarp_b200 import _lib
+    lib = _lib.lib()
+    degree, k, n, group = 2, 2048, 3072, 128
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    w = torch.randn((k, n), generator=gen, device="cuda") * 0.02
+    packed, scales = q.quantize_f32_to_tw_marlin(w, k, n, group)
+    a = torch.randn((rows, k), generator=gen, device="cuda").half()
+    full = torch.zeros((rows, n), device="cuda")
+    q.gemm_tw_marlin(a, packed, scales, full, rows, n, k, group_size=group, workspace=q.Workspace(1 << 22))
+    comms = tp.PeerComm.local_group(degree, rows * n)
+    gamma = torch.ones(n, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    kb = k // degree
+    shards = []
+    for r in range(degree):
+        p_r = packed.view(k // 32, n, 16)[r * kb // 32:(r + 1) * kb // 32].contiguous()
+        s_r = scales.view(k // group, n)[r * kb // group:(r + 1) * kb // group].contiguous()
+        shards.append((p_r, s_r, a[:, r * kb:(r + 1) * kb].contiguous()))
+    for step in range(2):
+        xs = [torch.full((rows, n), 0.5 * (step + 1), device="cuda") for _ in range(degree)]
+        dummy = torch.zeros((rows, n), device="cuda")
+        for r in range(degree):                         # every rank's producer first ...
+            p_r, s_r, a_r = shards[r]
+            args = _lib.GemmArgs(M=rows, N=n, K=kb, group_size=group, a_dtype=_lib.TWM_F16, c_dtype=_lib.TWM_F32,
+                                 a=a_r.data_ptr(), lda=kb, packed=p_r.data_ptr(), scales=s_r.data_ptr(),
+                                 c=dummy.data_ptr(), ldc=n, kernel_override=kernel, comm=comms[r].ptr)
+            _lib.check(lib.twm_gemm_w4a16(C.byref(args), stream), "twm_gemm_w4a16")
+        ys = [torch.zeros((rows, n), device="cuda", dtype=torch.float16) for _ in range(degree)]
+        for r in range(degree):                         # ... then every rank's consumer
+            _lib.check(lib.twm_allreduce_add_rmsnorm(ys[r].data_ptr(), xs[r].data_ptr(), comms[r].ptr, gamma.data_ptr(),
+                                                     rows, n, 1e-5, 0, stream), "twm_allreduce_add_rmsnorm")
+        torch.cuda.synchronize()
+        assert q.device_error() == 0
+        want = full + 0.5 * (step + 1)
+        for r in range(degree):
+            assert torch.equal(xs[r], xs[0]) and torch.equal(ys[r], ys[0])
+        rms = float(want.pow(2).mean().sqrt())
+        assert float((xs[0] - want).abs().max()) / rms < 2e-3
+        assert torch.all(dummy == 0)                    # with comm the result goes to the peers only
+    for c in comms:
+        c.close()
