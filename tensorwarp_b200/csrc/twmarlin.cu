@@ -200,7 +200,7 @@ bool shape_ok(int M, int N, int K, int G)
 // `cluster` = the slices of a tile will be launched as one thread-block cluster.  A cluster
 // lives inside one GPC (8 GPCs share the SMs), so a slice count that does not pack into a
 // GPC's CTA slots costs a second wave: that is counted here.
-void choose_splits(int n_tiles, int nkb, int slots, int max_bps, int align, int max_splits, bool cluster,
+void choose_splits(int n_tiles, int nkb, int slots, int sm_count, int max_bps, int align, int max_splits, bool cluster,
                    int* splits, int* bps)
 {
     double best = 1e30;
@@ -215,8 +215,11 @@ void choose_splits(int n_tiles, int nkb, int slots, int max_bps, int align, int 
         const long ctas = (long)n_tiles * s_eff;
         long waves = (ctas + slots - 1) / slots;
         if (cluster && s_eff > 1) {
-            const int slots_per_gpc = slots / 8;
-            const long resident_clusters = 8L * (slots_per_gpc / s_eff);
+            // Measured on B200: the CTAs of a cluster land on s distinct SMs of one GPC, one CTA
+            // slot "layer" at a time, so a GPC of 18 SMs with two slots per SM holds
+            // 2 * floor(18 / s) clusters (4 of size 7, not 5).
+            const int sms_per_gpc = sm_count / 8;
+            const long resident_clusters = 8L * (slots / sm_count) * (sms_per_gpc / s_eff);
             if (resident_clusters == 0) continue;
             waves = std::max(waves, ((long)n_tiles + resident_clusters - 1) / resident_clusters);
         }
@@ -486,7 +489,7 @@ twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int split
         if (bps > max_bps) return TWM_EINVAL;
         splits = (nkb + bps - 1) / bps;
     } else {
-        choose_splits(n_tiles, nkb, slots, max_bps, align, can_cluster ? twm::mma::MAX_CLUSTER : kMaxSplits,
+        choose_splits(n_tiles, nkb, slots, sm_count, max_bps, align, can_cluster ? twm::mma::MAX_CLUSTER : kMaxSplits,
                       can_cluster, &splits, &bps);
         if (bps > max_bps) return TWM_EINVAL;
     }
