@@ -239,6 +239,8 @@ struct GemmParams {
     alignas(64) CUtensorMap packed_map;
     // strip kernel: tensor map over the scales, f16 [K/G][N], box = 32 columns x one stage's rows
     alignas(64) CUtensorMap scale_map;
+    // tcgen05 kernel: -8 * sum of a scale group's activations per row, FP32 [K/G][NB] (written by the pre-pass)
+    const float* tc_a8;
     // tcgen05 kernel: tensor map over the launch's permuted activations, f16 [K/8][rows][8]
     alignas(64) CUtensorMap act_map;
 };

@@ -3,38 +3,39 @@
 // The contraction C[m][n] = sum_k A[m][k] * w[k][n] runs on the 5th-generation
 // tensor cores with the roles swapped: the 128 weight columns of a CTA are the
 // MMA's M dimension (one TMEM lane per column), the activation rows are its N
-// dimension (padded to NB = 16, 32 or 64), and K advances 16 at a time.  There
+// dimension (padded to NB = 16 or 32), and K advances 16 at a time.  There
 // is no counterpart in the reference: its only batched W4A16 kernel is a 32x32
 // SIMT tile kernel on another layout (crates/kernels/src/quantize.rs:186-246),
-// and its TW-Marlin kernel is M=1 only (quantize.rs:1186-1298).  The MMA's
-// weight operand is fp16_rn(f32(scale) * (nibble - 8)), i.e. exactly what the
-// reference's dequant_q4_to_f16 produces (quantize.rs:534-571); accumulation
-// is FP32 in tensor memory over the whole K slice.
+// and its TW-Marlin kernel is M=1 only (quantize.rs:1186-1298).  Result
+// definition as in the streaming kernels: w = f32(scale) * (nibble - 8), exact
+// products, FP32 accumulation, the FP32 scale applied per group.
 //
-// Data path per CTA (128 columns x a K slice):
-//   warp 0       streams packed rows into a shared-memory ring: one tiled TMA
-//                load per stage of four 32-blocks (no multicast), 1-D bulk
-//                copies row by row for ragged stages.
-//   warps 4-11   "dequant", two sets of four warps taking alternate blocks;
-//                each thread owns one column = one TMEM lane.  It reads its
-//                16-byte block (one conflict-free 128-bit shared load); per u32
-//                word one shift and four LOP3 `(v & mask) | 0x64006400` give the
-//                FP16 pairs (1024 + q) resp. (1024 + 16 q); one HSUB2 / HFMA2
-//                makes them q - 8 exactly and one HMUL2 applies the group's
-//                scale.  tcgen05.st writes the sixteen registers into tensor
-//                memory as the MMA's A operand: the weights never go back to
-//                shared memory.
-//   (pre-pass)   permute_activations_kernel rewrites the launch's activation rows
-//                once into [K/8][rows][8] FP16 with the K order the nibble
-//                extraction produces inside every 8 (k0,k4,k1,k5,k2,k6,k3,k7), so
-//                that warp 0 can bring the MMA's B operand for a stage (K-major
-//                8x16-byte core matrices, no swizzle) with one tiled TMA load.
-//   warp 1       one thread issues tcgen05.mma.cta_group::1.kind::f16 (A from
-//                TMEM, B from shared memory, D in TMEM), two per 32-block, all
-//                accumulating into the CTA's one [128 x NB] FP32 accumulator;
-//                tcgen05.commit frees the A slot and, at the end, releases D.
-//   warps 4-7    after their last block: epilogue, tcgen05.ld of D, FP16/FP32
-//                store or split-K partial.
+// The weight operand is never converted.  A nibble left in place in its 16-bit
+// half IS an FP16 subnormal: `v & 0x000F000F` = (q0, q4) * 2^-24, `v & 0x00F000F0`
+// = (q1, q5) * 2^-20, the same on `v >> 8` for (q2, q6), (q3, q7): five integer
+// instructions per eight nibbles, and the sixteen registers of a 32-block go into
+// tensor memory with one tcgen05.st as the MMA's A operand.  The factor 16 of the
+// odd nibbles is taken out of their activations (times 2^-4, exact) by the
+// pre-pass; the "-8" becomes -8 * sum of the group's activations (FP32 table from
+// the pre-pass); the scale meets the accumulator when a group's sum is read back.
+//
+// Data path per CTA (128 columns x a K slice of whole scale groups):
+//   warp 12      streams packed rows (one tiled TMA load per stage of four
+//                32-blocks, 6 deep) and the pre-permuted activations (one tiled
+//                TMA load per stage, K-major 8x16-byte core matrices, no swizzle).
+//   warps 0-7    unpack: two sets of four warps; each thread owns one column =
+//                one TMEM lane; per stage a set unpacks two of the four blocks
+//                into the stage's A slot in tensor memory.
+//   warps 8-11   read-back: each thread owns one column; for every finished scale
+//                group it reads the accumulator (tcgen05.ld), multiplies by its
+//                column's scale and adds into registers; at the end it stores C.
+//   warp 13      one thread issues tcgen05.mma.cta_group::1.kind::f16 (A from
+//                TMEM, B from shared memory, D in TMEM), two per 32-block; every
+//                scale group starts a fresh accumulator (two, used in turn);
+//                tcgen05.commit hands the accumulator to the readers and frees
+//                the A slot and activation stage.
+// Tensor memory: ASLOTS x 64 columns of A operands + 2 x NB accumulator columns
+// <= 256, so two CTAs share an SM.
 // Split-K finish and the programmatic-dependent-launch rules are the same as
 // in the streaming kernels.
 #pragma once
@@ -47,36 +48,43 @@ namespace tc {
 constexpr int NT = 128;               // columns per CTA = MMA M = TMEM lanes
 constexpr int WSTAGE_BLOCKS = 4;      // 32-blocks per ring stage (8 KB)
 constexpr int WSTAGES = 6;            // packed ring depth: 48 KB in flight per CTA
-constexpr int BSTAGES = 3;            // activation ring depth (one stage = the same four 32-blocks)
-constexpr int ASLOTS = 3;             // TMEM slots holding one dequantised ring stage (4 blocks x 16 columns) each
-constexpr int THREADS = 12 * 32;
-constexpr int EPI_THREADS = 128;
+constexpr int DEQ_SETS = 2;           // unpack warp sets, alternate blocks
+constexpr int DEQ_THREADS = DEQ_SETS * 128;
+constexpr int EPI_THREADS = 128;      // the four read-back warps
+constexpr int WARP_READ0 = 8, WARP_TMA = 12, WARP_MMA = 13;
+constexpr int THREADS = 14 * 32;
 constexpr int B_STAGE_KCORES = WSTAGE_BLOCKS * 4;     // 8-wide K cores per activation stage
-constexpr int DEQ_SETS = 2;           // dequant warp sets, alternate blocks
+constexpr int TMEM_COLS = 256;
+constexpr int A8_SMEM_FLOATS = 8192;  // the K slice's -8*sum table is copied into shared memory when it fits (32 KB)
 
 template <int NB>
 struct Cfg {
+    static constexpr int ASLOTS = 3;                                // stages of A operands (and of activations) in flight
     static constexpr int KCORE_BYTES = NB * 16;                     // one K core: NB rows x 8 K x 2 B
     static constexpr int B_STAGE_BYTES = B_STAGE_KCORES * KCORE_BYTES;
     static constexpr int A_SLOT_COLS = WSTAGE_BLOCKS * 16;          // A slot s: columns [64 s, 64 s + 64)
-    static constexpr int A_COL0 = 0;
-    static constexpr int D_COL0 = ASLOTS * A_SLOT_COLS;             // the accumulator: NB columns
-    static constexpr int USED_COLS = ASLOTS * A_SLOT_COLS + NB;
-    static constexpr int TMEM_COLS = USED_COLS <= 256 ? 256 : 512;
-    static_assert(USED_COLS <= 512, "tensor memory holds 512 columns");
+    static constexpr int D_COL0 = ASLOTS * A_SLOT_COLS;             // two accumulators of NB columns
+    static_assert(D_COL0 + 2 * NB <= TMEM_COLS, "tensor memory budget of a CTA");
 };
 
 template <int NB>
 struct Smem {
     alignas(128) uint8_t packed[WSTAGES][WSTAGE_BLOCKS * NT * kBlockBytes];
-    alignas(128) uint8_t b[BSTAGES][Cfg<NB>::B_STAGE_BYTES];     // [K core][row][8 K]
+    alignas(128) uint8_t b[Cfg<NB>::ASLOTS][Cfg<NB>::B_STAGE_BYTES];          // [K core][row][8 K]
+    alignas(16) float a8[A8_SMEM_FLOATS];                                     // [group of the slice][NB]
     alignas(8) uint64_t w_full[WSTAGES];
     alignas(8) uint64_t w_empty[WSTAGES];
-    alignas(8) uint64_t a_full[ASLOTS];      // dequant -> MMA: a stage's A operands are in tensor memory
-    alignas(8) uint64_t a_empty[ASLOTS];     // MMA (commit) -> dequant: the stage's A operands are consumed
-    alignas(8) uint64_t b_full[BSTAGES];
-    alignas(8) uint64_t b_empty[BSTAGES];
-    alignas(8) uint64_t d_full;            // MMA (commit) -> epilogue: the accumulator is complete
+    alignas(8) uint64_t a_full[Cfg<NB>::ASLOTS];     // unpack -> MMA: a stage's A operands are in tensor memory
+    alignas(8) uint64_t ab_empty[Cfg<NB>::ASLOTS];   // MMA (commit) -> unpack and TMA: A slot and activation stage are consumed
+    alignas(8) uint64_t b_full[Cfg<NB>::ASLOTS];
+    alignas(8) uint64_t d_full[2];                   // MMA (commit) -> readers: a scale group's accumulator is complete
+    alignas(8) uint64_t d_empty[2];                  // readers -> MMA: the accumulator has been read
+    // group-128 path (a stage is one scale group): everything the MMA thread waits for before a
+    // stage arrives on ONE barrier (8 unpack warps + the activation stage's bytes + the 4 readers
+    // that freed the accumulator two stages ago), and one commit per stage tells everybody that
+    // the stage's MMAs are done (accumulator complete, A slot and activation stage free)
+    alignas(8) uint64_t ready[Cfg<NB>::ASLOTS];
+    alignas(8) uint64_t done[4];
     uint32_t tmem_base;
     int abort_flag;
     int is_last;
@@ -157,12 +165,13 @@ __device__ __forceinline__ bool wait_uniform(uint64_t* bar, uint32_t parity, vol
     return __all_sync(0xffffffffu, got);
 }
 
-// NB = MMA N (activation rows padded to 16, 32 or 64)
+// NB = MMA N (activation rows padded to 16 or 32)
 template <int NB>
-__global__ void __launch_bounds__(THREADS, (Cfg<NB>::TMEM_COLS <= 256) ? 2 : 1)
+__global__ void __launch_bounds__(THREADS, 2)
 gemm_kernel(const __grid_constant__ GemmParams p)
 {
     using C = Cfg<NB>;
+    constexpr int ASLOTS = C::ASLOTS;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     Smem<NB>& sm = *reinterpret_cast<Smem<NB>*>(smem_raw);
 
@@ -171,16 +180,24 @@ gemm_kernel(const __grid_constant__ GemmParams p)
     const int lane = tid & 31;
     const int n0 = blockIdx.x * NT;
     const int cols = min(NT, p.N - n0);
-    const int b0 = blockIdx.y * p.blocks_per_split;
+    const int b0 = blockIdx.y * p.blocks_per_split;          // a multiple of the group's blocks (host plan)
     const int b1 = min(p.nkb, b0 + p.blocks_per_split);
     const int total_blocks = b1 - b0;
     const int gshift = (p.group == 128) ? 2 : 0;
+    const int n_wstages = (total_blocks + WSTAGE_BLOCKS - 1) / WSTAGE_BLOCKS;
+    const bool lean = (gshift == 2);         // one scale group per stage
 
     if (tid == 0) {
         for (int s = 0; s < WSTAGES; ++s) { mbar_init(&sm.w_full[s], 1); mbar_init(&sm.w_empty[s], 4 * DEQ_SETS); }
-        for (int s = 0; s < ASLOTS; ++s) { mbar_init(&sm.a_full[s], 4 * DEQ_SETS); mbar_init(&sm.a_empty[s], 1); }
-        for (int s = 0; s < BSTAGES; ++s) { mbar_init(&sm.b_full[s], 1); mbar_init(&sm.b_empty[s], 1); }
-        mbar_init(&sm.d_full, 1);
+        for (int s = 0; s < ASLOTS; ++s) {
+            mbar_init(&sm.a_full[s], 4 * DEQ_SETS); mbar_init(&sm.ab_empty[s], 1); mbar_init(&sm.b_full[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) { mbar_init(&sm.d_full[s], 1); mbar_init(&sm.d_empty[s], EPI_THREADS / 32); }
+        for (int s = 0; s < ASLOTS; ++s) mbar_init(&sm.ready[s], 4 * DEQ_SETS + 1 + EPI_THREADS / 32);
+        for (int s = 0; s < 4; ++s) mbar_init(&sm.done[s], 1);
+        // the first two stages find their accumulators free: the readers' arrivals are made here
+        for (int s = 0; s < 2; ++s)
+            for (int i = 0; i < EPI_THREADS / 32; ++i) mbar_arrive(&sm.ready[s]);
         sm.abort_flag = 0;
         sm.is_last = 0;
         mbar_fence_init();
@@ -189,11 +206,10 @@ gemm_kernel(const __grid_constant__ GemmParams p)
     pdl_launch_dependents();
     volatile int* abort_flag = &sm.abort_flag;
 
-    // TMA producer state (warp 0).  The first ring-full of stages is issued
-    // before the TMEM allocation below, so that weights are already streaming
-    // while an earlier kernel's CTA may still hold this SM's tensor memory.
+    // TMA producer state (warp 12).  The first ring-full of stages is issued before the TMEM
+    // allocation below, so that weights are already streaming while an earlier kernel's CTA may
+    // still hold this SM's tensor memory.
     const uint8_t* packed = p.packed;
-    const int n_wstages = (total_blocks + WSTAGE_BLOCKS - 1) / WSTAGE_BLOCKS;
     auto issue_stage = [&](int st) {                       // executed by the whole warp
         const int slot = st % WSTAGES;
         const int bstart = b0 + st * WSTAGE_BLOCKS;
@@ -211,14 +227,14 @@ gemm_kernel(const __grid_constant__ GemmParams p)
                      (uint32_t)cols * kBlockBytes, &sm.w_full[slot]);
         __syncwarp();
     };
-    if (warp == 0) {
+    if (warp == WARP_TMA) {
         if (p.packed_offsets != nullptr) {
             pdl_wait_prior_grids();                  // the offset table may come from the kernel before
             packed += p.packed_offsets[p.expert_idx];
         }
         for (int st = 0; st < min(n_wstages, WSTAGES); ++st) issue_stage(st);
-    } else if (warp == 1) {
-        tmem_alloc(&sm.tmem_base, C::TMEM_COLS);
+    } else if (warp == WARP_MMA) {
+        tmem_alloc(&sm.tmem_base, TMEM_COLS);
         tc_fence_before();
     }
     // every role needs the TMEM base address
@@ -226,30 +242,31 @@ gemm_kernel(const __grid_constant__ GemmParams p)
     tc_fence_after();
     const uint32_t tmem_base = sm.tmem_base;
 
-    if (warp == 0) {
+    if (warp == WARP_TMA) {
         // ------------------------------ TMA producer (packed, then activations) --
         // Weight stages WSTAGES.. and all activation stages.  Activations come from the
         // pre-pass kernel, so they wait for the preceding grid; weights never do.
-        PROF_DECL;
         pdl_wait_prior_grids();
         auto issue_b = [&](int st) {
             if (lane == 0) {
-                const int bs = st % BSTAGES;
-                mbar_arrive_expect_tx(&sm.b_full[bs], (uint32_t)C::B_STAGE_BYTES);
-                tma_load_2d(&sm.b[bs][0], &p.act_map, 0, (b0 + st * WSTAGE_BLOCKS) * 4, &sm.b_full[bs]);
+                const int bs = st % ASLOTS;
+                uint64_t* bar = lean ? &sm.ready[bs] : &sm.b_full[bs];
+                mbar_arrive_expect_tx(bar, (uint32_t)C::B_STAGE_BYTES);
+                tma_load_2d(&sm.b[bs][0], &p.act_map, 0, (b0 + st * WSTAGE_BLOCKS) * 4, bar);
             }
             __syncwarp();
         };
-        // Two independent streams, each as far ahead as its ring allows: activation stages
-        // (BSTAGES deep) and weight stages (WSTAGES deep).  Single polls, so neither ring
-        // waits for the other; the idle counter bounds the loop.
+        // Two independent streams, each as far ahead as its ring allows.  Single polls, so
+        // neither ring waits for the other; the idle counter bounds the loop.
         int bst = 0, wst = min(n_wstages, WSTAGES);
         uint32_t idle = 0;
         while ((bst < n_wstages || wst < n_wstages) && idle < (1u << 22)) {
             bool progress = false;
             if (bst < n_wstages) {
-                bool free_b = bst < BSTAGES;
-                if (!free_b) free_b = mbar_try_wait(&sm.b_empty[bst % BSTAGES], ((bst / BSTAGES) - 1) & 1);
+                bool free_b = bst < ASLOTS;
+                if (!free_b)
+                    free_b = lean ? mbar_try_wait(&sm.done[(bst - ASLOTS) & 3], ((bst - ASLOTS) >> 2) & 1)
+                                  : mbar_try_wait(&sm.ab_empty[bst % ASLOTS], ((bst / ASLOTS) - 1) & 1);
                 if (__all_sync(0xffffffffu, free_b)) { issue_b(bst); ++bst; progress = true; }
             }
             if (wst < n_wstages) {
@@ -259,103 +276,130 @@ gemm_kernel(const __grid_constant__ GemmParams p)
             if (progress) { idle = 0; } else { ++idle; if (idle > 64) __nanosleep(64); if (*abort_flag) break; }
         }
         if (bst < n_wstages || wst < n_wstages) { *abort_flag = 1; atomicOr(&g_error_word, 1u); }
-        PROF_FLUSH(0);
-    } else if (warp == 1) {
+    } else if (warp == WARP_MMA) {
         // ------------------------------------------------------- MMA issuer --
         if (lane == 0) {
             uint32_t idesc = 0;
             idesc |= 1u << 4;                         // D format f32
             idesc |= (uint32_t)(NB >> 3) << 17;       // N
             idesc |= (uint32_t)(128 >> 4) << 24;      // M
-            const uint32_t d_addr = tmem_base + C::D_COL0;
-            // One pass per ring stage (four 32-blocks): two waits, eight MMAs back to back, two
-            // commits.  The issuing thread's own instruction stream is the scarce resource here
-            // (about 46 clk per tcgen05.mma, as much again per commit or barrier poll).
             const uint64_t kcore_step = (uint64_t)(C::KCORE_BYTES >> 4);           // descriptor address units
-            PROF_DECL;
+            int gq = 0;                               // scale groups started so far: accumulator gq & 1
             bool ok = true;
-            for (int st = 0; st < n_wstages; ++st) {
+            PROF_DECL;
+            // accumulator for group gq: wait until the readers have taken its previous contents
+            auto open_group = [&]() -> uint32_t {
+                const int db = gq & 1;
+                PROF_BEGIN(t1);
+                if (gq >= 2 && !mbar_wait_bounded(&sm.d_empty[db], ((gq >> 1) - 1) & 1, abort_flag)) ok = false;
+                PROF_END(t1, 1);
+                tc_fence_after();
+                return tmem_base + C::D_COL0 + db * NB;
+            };
+            if (lean) {
+                // per stage: one wait, eight MMAs into accumulator st & 1, one commit
+                for (int st = 0; st < n_wstages; ++st) {
+                    const int aslot = st % ASLOTS;
+                    PROF_BEGIN(t0);
+                    if (!mbar_wait_bounded(&sm.ready[aslot], (st / ASLOTS) & 1, abort_flag)) break;
+                    PROF_END(t0, 0);
+                    tc_fence_after();
+                    PROF_BEGIN(t3);
+                    const uint32_t d_addr = tmem_base + C::D_COL0 + (st & 1) * NB;
+                    uint32_t a_addr = tmem_base + aslot * C::A_SLOT_COLS;
+                    uint64_t bd = make_b_desc(smem_u32(&sm.b[aslot][0]), C::KCORE_BYTES, 128);
+#pragma unroll
+                    for (int bi = 0; bi < WSTAGE_BLOCKS; ++bi) {
+                        tc_mma_ts(d_addr, a_addr, bd, idesc, bi == 0 ? 0u : 1u);
+                        tc_mma_ts(d_addr, a_addr + 8, bd + 2 * kcore_step, idesc, 1u);
+                        a_addr += 16;
+                        bd += 4 * kcore_step;
+                    }
+                    PROF_END(t3, 3);
+                    PROF_BEGIN(t4);
+                    tc_commit(&sm.done[st & 3]);
+                    PROF_END(t4, 4);
+                }
+            } else
+            for (int st = 0; st < n_wstages && ok; ++st) {
                 const int aslot = st % ASLOTS;
-                const int bs = st % BSTAGES;
                 const int nb = min(WSTAGE_BLOCKS, total_blocks - st * WSTAGE_BLOCKS);
                 PROF_BEGIN(t0);
-                if (!mbar_wait_bounded(&sm.b_full[bs], (st / BSTAGES) & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait_bounded(&sm.b_full[aslot], (st / ASLOTS) & 1, abort_flag)) { ok = false; break; }
                 PROF_END(t0, 0);
                 PROF_BEGIN(t2);
                 if (!mbar_wait_bounded(&sm.a_full[aslot], (st / ASLOTS) & 1, abort_flag)) { ok = false; break; }
                 PROF_END(t2, 2);
-                PROF_BEGIN(t3);
                 tc_fence_after();
-                uint32_t a_addr = tmem_base + C::A_COL0 + aslot * C::A_SLOT_COLS;
+                uint32_t a_addr = tmem_base + aslot * C::A_SLOT_COLS;
                 // a block's four K cores sit C::KCORE_BYTES apart; 8-row groups 128 bytes apart
-                uint64_t bd = make_b_desc(smem_u32(&sm.b[bs][0]), C::KCORE_BYTES, 128);
+                uint64_t bd = make_b_desc(smem_u32(&sm.b[aslot][0]), C::KCORE_BYTES, 128);
+                if (gshift == 2) {
+                    // the stage is one scale group: eight MMAs into one fresh accumulator
+                    const uint32_t d_addr = open_group();
+                    if (!ok) break;
+                    PROF_BEGIN(t3);
 #pragma unroll
-                for (int bi = 0; bi < WSTAGE_BLOCKS; ++bi) {
-                    if (bi < nb) {
-                        tc_mma_ts(d_addr, a_addr, bd, idesc, (st == 0 && bi == 0) ? 0u : 1u);
-                        tc_mma_ts(d_addr, a_addr + 8, bd + 2 * kcore_step, idesc, 1u);
+                    for (int bi = 0; bi < WSTAGE_BLOCKS; ++bi) {
+                        if (bi < nb) {
+                            tc_mma_ts(d_addr, a_addr, bd, idesc, bi == 0 ? 0u : 1u);
+                            tc_mma_ts(d_addr, a_addr + 8, bd + 2 * kcore_step, idesc, 1u);
+                        }
+                        a_addr += 16;
+                        bd += 4 * kcore_step;
                     }
-                    a_addr += 16;
-                    bd += 4 * kcore_step;
+                    PROF_END(t3, 3);
+                    PROF_BEGIN(t4);
+                    tc_commit(&sm.d_full[gq & 1]);
+                    PROF_END(t4, 4);
+                    ++gq;
+                } else {
+                    // every 32-block is a scale group
+                    for (int bi = 0; bi < nb && ok; ++bi) {
+                        const uint32_t d_addr = open_group();
+                        if (!ok) break;
+                        tc_mma_ts(d_addr, a_addr, bd, idesc, 0u);
+                        tc_mma_ts(d_addr, a_addr + 8, bd + 2 * kcore_step, idesc, 1u);
+                        tc_commit(&sm.d_full[gq & 1]);
+                        ++gq;
+                        a_addr += 16;
+                        bd += 4 * kcore_step;
+                    }
                 }
-                PROF_END(t3, 3);
-                PROF_BEGIN(t4);
-                tc_commit(&sm.a_empty[aslot]);
-                tc_commit(&sm.b_empty[bs]);
-                PROF_END(t4, 4);
+                PROF_BEGIN(t5);
+                tc_commit(&sm.ab_empty[aslot]);
+                PROF_END(t5, 4);
             }
-            if (ok) tc_commit(&sm.d_full);
             PROF_FLUSH(1);
         }
         __syncwarp();
-    } else if (warp == 2 || warp == 3) {
-        // spare warps (the dequant warps must start at a multiple of four: TMEM lane quarters)
-    } else {
-        // ------------------------------------------------------- dequant --
-        const int set = (warp - 4) >> 2;                       // 0: even blocks, 1: odd blocks
+    } else if (warp < WARP_READ0) {
+        // ------------------------------------------------------------ unpack --
+        const int set = warp >> 2;                             // 0: even blocks, 1: odd blocks
         const int quarter = warp & 3;
         const int col = quarter * 32 + lane;
-        const int n = n0 + col;
-        const bool owner = n < p.N;
-        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + C::A_COL0;
-        const uint16_t* scales = p.scales;
-        if (p.scales_offsets != nullptr) {
-            pdl_wait_prior_grids();                  // the offset table may come from the kernel before
-            scales += p.scales_offsets[p.expert_idx];
-        }
+        const uint32_t lane_tmem = tmem_base + ((uint32_t)(quarter * 32) << 16);
         PROF_DECL;
-        bool ok = true;
-        // FP16 scale of this column for each of this set's two blocks of a stage, requested one
-        // stage ahead so that the L2 round trip is never waited for
-        auto load_scale = [&](int st, int rr) -> uint16_t {
-            const int i = st * WSTAGE_BLOCKS + set + rr * DEQ_SETS;
-            if (!owner || i >= total_blocks) return (uint16_t)0;
-            return __ldg(scales + (size_t)((b0 + i) >> gshift) * p.N + n);
-        };
-        uint16_t s_next[WSTAGE_BLOCKS / DEQ_SETS];
-#pragma unroll
-        for (int rr = 0; rr < WSTAGE_BLOCKS / DEQ_SETS; ++rr) s_next[rr] = load_scale(0, rr);
-        const __half2 k1032 = __float2half2_rn(1032.0f), k16th = __float2half2_rn(0.0625f), k72 = __float2half2_rn(-72.0f);
         for (int st = 0; st < n_wstages; ++st) {
             const int wslot = st % WSTAGES;
             const int aslot = st % ASLOTS;
             const int nb = min(WSTAGE_BLOCKS, total_blocks - st * WSTAGE_BLOCKS);
             PROF_BEGIN(t0);
-            if (!wait_uniform(&sm.w_full[wslot], (st / WSTAGES) & 1, abort_flag)) { ok = false; break; }
+            if (!wait_uniform(&sm.w_full[wslot], (st / WSTAGES) & 1, abort_flag)) break;
             PROF_END(t0, 0);
-            bool slot_free = (st < ASLOTS);
-            uint16_t s_cur[WSTAGE_BLOCKS / DEQ_SETS];
-#pragma unroll
-            for (int rr = 0; rr < WSTAGE_BLOCKS / DEQ_SETS; ++rr) {
-                s_cur[rr] = s_next[rr];
-                s_next[rr] = load_scale(st + 1, rr);
+            PROF_BEGIN(t2);
+            if (st >= ASLOTS) {        // the MMAs that read this slot's previous contents are done
+                uint64_t* bar = lean ? &sm.done[(st - ASLOTS) & 3] : &sm.ab_empty[aslot];
+                const uint32_t par = lean ? (((st - ASLOTS) >> 2) & 1) : (((st / ASLOTS) - 1) & 1);
+                if (!wait_uniform(bar, par, abort_flag)) break;
+                tc_fence_after();
             }
+            PROF_END(t2, 2);
+            PROF_BEGIN(t1);
 #pragma unroll
             for (int rr = 0; rr < WSTAGE_BLOCKS / DEQ_SETS; ++rr) {
                 const int r = set + rr * DEQ_SETS;                 // this set's blocks of the stage: set, set + 2
                 if (r < nb) {                                      // warp-uniform
-                    const __half2 s2 = __half2half2(__ushort_as_half(s_cur[rr]));
-                    PROF_BEGIN(t1);
                     const uint4 v = lds128(&sm.packed[wslot][(r * NT + col) * kBlockBytes]);
                     const uint32_t words[4] = {v.x, v.y, v.z, v.w};
                     uint32_t regs[16];
@@ -363,112 +407,133 @@ gemm_kernel(const __grid_constant__ GemmParams p)
                     for (int w = 0; w < 4; ++w) {
                         const uint32_t x = words[w];
                         const uint32_t x8 = x >> 8;
-                        uint32_t t0b = (x & 0x000F000Fu) | 0x64006400u;      // 1024 + (k0, k4)
-                        uint32_t t1b = (x & 0x00F000F0u) | 0x64006400u;      // 1024 + 16 (k1, k5)
-                        uint32_t t2b = (x8 & 0x000F000Fu) | 0x64006400u;     // 1024 + (k2, k6)
-                        uint32_t t3b = (x8 & 0x00F000F0u) | 0x64006400u;     // 1024 + 16 (k3, k7)
-                        const __half2 q0 = __hsub2(*reinterpret_cast<__half2*>(&t0b), k1032);          // q - 8, exact
-                        const __half2 q1 = __hfma2(*reinterpret_cast<__half2*>(&t1b), k16th, k72);
-                        const __half2 q2 = __hsub2(*reinterpret_cast<__half2*>(&t2b), k1032);
-                        const __half2 q3 = __hfma2(*reinterpret_cast<__half2*>(&t3b), k16th, k72);
-                        const __half2 w0 = __hmul2(q0, s2), w1 = __hmul2(q1, s2), w2 = __hmul2(q2, s2), w3 = __hmul2(q3, s2);
-                        regs[4 * w + 0] = *reinterpret_cast<const uint32_t*>(&w0);
-                        regs[4 * w + 1] = *reinterpret_cast<const uint32_t*>(&w1);
-                        regs[4 * w + 2] = *reinterpret_cast<const uint32_t*>(&w2);
-                        regs[4 * w + 3] = *reinterpret_cast<const uint32_t*>(&w3);
+                        regs[4 * w + 0] = x & 0x000F000Fu;         // (k0, k4) * 2^-24
+                        regs[4 * w + 1] = x & 0x00F000F0u;         // (k1, k5) * 2^-20: their activations carry 2^-4
+                        regs[4 * w + 2] = x8 & 0x000F000Fu;        // (k2, k6) * 2^-24
+                        regs[4 * w + 3] = x8 & 0x00F000F0u;        // (k3, k7) * 2^-20
                     }
-                    PROF_END(t1, 1);
-                    if (!slot_free) {                              // the MMAs that read this slot's previous contents are done
-                        PROF_BEGIN(t2);
-                        if (!wait_uniform(&sm.a_empty[aslot], ((st / ASLOTS) - 1) & 1, abort_flag)) { ok = false; break; }
-                        PROF_END(t2, 2);
-                        tc_fence_after();
-                        slot_free = true;
-                    }
-                    PROF_BEGIN(t3);
-                    tmem_st16(lane_base + aslot * C::A_SLOT_COLS + r * 16, regs);
-                    PROF_END(t3, 3);
+                    tmem_st16(lane_tmem + aslot * C::A_SLOT_COLS + r * 16, regs);
                 }
             }
-            if (!ok) break;
-            if (!slot_free) {      // a warp without a block in this (ragged) stage still keeps the slot's phases in step
-                if (!wait_uniform(&sm.a_empty[aslot], ((st / ASLOTS) - 1) & 1, abort_flag)) { ok = false; break; }
-            }
+            PROF_END(t1, 1);
             PROF_BEGIN(t4);
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(&sm.a_full[aslot]);            // this warp's share of the stage is in tensor memory
-                mbar_arrive(&sm.w_empty[wslot]);           // and read out of the ring
+                mbar_arrive(lean ? &sm.ready[aslot] : &sm.a_full[aslot]);   // this warp's share of the stage is in tensor memory
+                mbar_arrive(&sm.w_empty[wslot]);                             // and read out of the ring
             }
             PROF_END(t4, 4);
         }
         PROF_FLUSH(3);
+    } else if (warp < WARP_TMA) {
+        // ------------------------------------- per-group read-back and epilogue --
+        const int quarter = warp & 3;
+        const int col = quarter * 32 + lane;
+        const int n = n0 + col;
+        const bool owner = n < p.N;
+        const uint32_t lane_tmem = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const uint16_t* scales = p.scales;
+        pdl_wait_prior_grids();          // the -8*sum table comes from the pre-pass; C may be read by the kernel before
+        if (p.scales_offsets != nullptr) scales += p.scales_offsets[p.expert_idx];
+        float acc[NB];
+#pragma unroll
+        for (int j = 0; j < NB; ++j) acc[j] = 0.0f;
+        bool ok = true;
+        const int n_groups = (gshift == 2) ? n_wstages : total_blocks;
+        const int grow0 = b0 >> gshift;
+        auto load_scale = [&](int gq) -> uint16_t {
+            return (owner && gq < n_groups) ? __ldg(scales + (size_t)(grow0 + gq) * p.N + n) : (uint16_t)0;
+        };
+        uint16_t s_next = load_scale(0);
+        // the slice's rows of the -8*sum table: into shared memory when they fit, else read from global
+        const bool a8_local = n_groups * NB <= A8_SMEM_FLOATS;
+        if (a8_local) {
+            const float4* src = reinterpret_cast<const float4*>(p.tc_a8 + (size_t)grow0 * NB);
+            float4* dst = reinterpret_cast<float4*>(sm.a8);
+            for (int i = tid - WARP_READ0 * 32; i < n_groups * NB / 4; i += EPI_THREADS) dst[i] = __ldg(src + i);
+        }
+        named_bar_sync(2, EPI_THREADS);
+        PROF_DECL;
+        for (int gq = 0; gq < n_groups; ++gq) {
+            // accumulator of scale group gq: acc += s * (2^24 D - 8 sum(a))
+            const int db = gq & 1;
+            const float sg = f16_bits_to_f32(s_next);
+            s_next = load_scale(gq + 1);
+            const float4* a8p = a8_local ? reinterpret_cast<const float4*>(sm.a8 + gq * NB)
+                                         : reinterpret_cast<const float4*>(p.tc_a8 + (size_t)(grow0 + gq) * NB);
+            PROF_BEGIN(t0);
+            {
+                uint64_t* bar = lean ? &sm.done[gq & 3] : &sm.d_full[db];
+                const uint32_t par = lean ? ((gq >> 2) & 1) : ((gq >> 1) & 1);
+                if (!wait_uniform(bar, par, abort_flag)) { ok = false; break; }
+            }
+            PROF_END(t0, 0);
+            tc_fence_after();
+            PROF_BEGIN(t1);
+#pragma unroll
+            for (int c0 = 0; c0 < NB; c0 += 16) {
+                if (c0 < p.M) {                                        // warp-uniform
+                    uint32_t d[16];
+                    tmem_ld<16>(lane_tmem + C::D_COL0 + db * NB + c0, d);
+                    const float4 q0 = a8p[c0 / 4], q1 = a8p[c0 / 4 + 1], q2 = a8p[c0 / 4 + 2], q3 = a8p[c0 / 4 + 3];
+                    const float a8[16] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w,
+                                          q2.x, q2.y, q2.z, q2.w, q3.x, q3.y, q3.z, q3.w};
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        acc[c0 + j] = fmaf(sg, fmaf(__uint_as_float(d[j]), 16777216.0f, a8[j]), acc[c0 + j]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(lean ? &sm.ready[(gq + 2) % ASLOTS] : &sm.d_empty[db]);   // the accumulator is free again
+            PROF_END(t1, 1);
+        }
+        PROF_FLUSH(2);
+        ok = ok && (*abort_flag == 0);
 
-        if (set == 0) {
-            // --------------------------------------------------- epilogue --
-            // (a K slice with a single block leaves set 1 idle; stages whose odd block is missing are
-            //  released by set 0 alone: see the w_empty arrival count below)
-            pdl_wait_prior_grids();
-            bool have = ok && wait_uniform(&sm.d_full, 0, abort_flag);
-            named_bar_sync(2, EPI_THREADS);
-            have = have && (*abort_flag == 0);
-            const uint32_t lane_d = tmem_base + ((uint32_t)(quarter * 32) << 16) + C::D_COL0;
-            auto store_c = [&](int m, float vv) {
-                const size_t off = (size_t)m * p.ldc + n;
-                if (p.c_is_f16) {
-                    __half* cp = reinterpret_cast<__half*>(p.c);
-                    if (p.accumulate) vv += __half2float(cp[off]);
-                    cp[off] = __float2half_rn(vv);
-                } else {
-                    float* cp = reinterpret_cast<float*>(p.c);
-                    if (p.accumulate) vv += cp[off];
-                    cp[off] = vv;
-                }
-            };
-            if (have) {
-                tc_fence_after();
+        auto store_c = [&](int m, float vv) {
+            const size_t off = (size_t)m * p.ldc + n;
+            if (p.c_is_f16) {
+                __half* cp = reinterpret_cast<__half*>(p.c);
+                if (p.accumulate) vv += __half2float(cp[off]);
+                cp[off] = __float2half_rn(vv);
+            } else {
+                float* cp = reinterpret_cast<float*>(p.c);
+                if (p.accumulate) vv += cp[off];
+                cp[off] = vv;
+            }
+        };
+        if (ok && owner) {
 #pragma unroll
-                for (int c0 = 0; c0 < NB; c0 += 16) {
-                    if (c0 < p.M) {                                        // warp-uniform
-                        uint32_t d[16];
-                        tmem_ld<16>(lane_d + c0, d);
-                        tmem_wait_ld();
-                        if (owner) {
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) {
-                                const int m = c0 + j;
-                                if (m < p.M) {
-                                    if (p.splits == 1) store_c(m, __uint_as_float(d[j]));
-                                    else p.ws_partials[((size_t)blockIdx.y * p.M + m) * p.N + n] = __uint_as_float(d[j]);
-                                }
-                            }
-                        }
+            for (int j = 0; j < NB; ++j) {
+                if (j < p.M) {
+                    if (p.splits == 1) store_c(j, acc[j]);
+                    else p.ws_partials[((size_t)blockIdx.y * p.M + j) * p.N + n] = acc[j];
+                }
+            }
+        }
+        if (p.splits > 1) {
+            __threadfence();
+            named_bar_sync(3, EPI_THREADS);
+            if (tid == WARP_READ0 * 32) {
+                const unsigned prev = atomicAdd(&p.ws_counters[blockIdx.x], 1u);
+                sm.is_last = (prev == (unsigned)(p.splits - 1));
+            }
+            named_bar_sync(3, EPI_THREADS);
+            if (sm.is_last) {
+                __threadfence();
+                if (owner && *abort_flag == 0) {
+                    for (int m = 0; m < p.M; ++m) {
+                        float s = 0.0f;
+                        for (int sp = 0; sp < p.splits; ++sp)
+                            s += ld_cg_f32(&p.ws_partials[((size_t)sp * p.M + m) * p.N + n]);
+                        store_c(m, s);
                     }
                 }
-                tc_fence_before();
-                if (p.splits > 1) {
-                    __threadfence();
-                    named_bar_sync(2, EPI_THREADS);
-                    if (tid == 4 * 32) {
-                        const unsigned prev = atomicAdd(&p.ws_counters[blockIdx.x], 1u);
-                        sm.is_last = (prev == (unsigned)(p.splits - 1));
-                    }
-                    named_bar_sync(2, EPI_THREADS);
-                    if (sm.is_last) {
-                        __threadfence();
-                        if (owner) {
-                            for (int m = 0; m < p.M; ++m) {
-                                float acc = 0.0f;
-                                for (int sp = 0; sp < p.splits; ++sp)
-                                    acc += ld_cg_f32(&p.ws_partials[((size_t)sp * p.M + m) * p.N + n]);
-                                store_c(m, acc);
-                            }
-                        }
-                        if (tid == 4 * 32) atomicExch(&p.ws_counters[blockIdx.x], 0u);
-                    }
-                }
+                if (tid == WARP_READ0 * 32) atomicExch(&p.ws_counters[blockIdx.x], 0u);
             }
         }
     }
@@ -476,20 +541,54 @@ gemm_kernel(const __grid_constant__ GemmParams p)
     // ------------------------------------------------------------ teardown --
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == WARP_MMA) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, C::TMEM_COLS);
+        tmem_dealloc(tmem_base, TMEM_COLS);
     }
 }
 
-// Pre-pass of the tcgen05 kernel: rows [0, rows) of the activations, f16 [rows][lda], rewritten as
-// [K/8][rows][8] with the eight K of a core in the order k0,k4,k1,k5,k2,k6,k3,k7 (the order in which
-// the dequant warps lay nibbles into tensor memory).  One thread per (K core, row).
+// Pre-pass of the tcgen05 kernel, one launch per GEMM launch.
+// Blocks [0, perm_blocks): rows [0, rows) of the activations, f16 [rows][lda], rewritten as
+// [K/8][rows][8] with the eight K of a core in the order k0,k4,k1,k5,k2,k6,k3,k7 (the order in
+// which the unpack lays nibbles into tensor memory), the odd ones times 2^-4 (their nibbles sit
+// four bits higher in the operand).  One thread per (K core, row).
+// Remaining blocks: the table a8[g][m] = -8 * sum of row m's activations over scale group g, FP32,
+// [K/G][nb_pad] (rows past `rows` zero), summed in a fixed order by group/8 lanes per (g, m).
 __global__ void __launch_bounds__(256)
-permute_activations_kernel(__half* __restrict__ out, const __half* __restrict__ a, long lda, int rows, int kcores)
+permute_activations_kernel(__half* __restrict__ out, float* __restrict__ a8, const __half* __restrict__ a, long lda,
+                           int rows, int kcores, int perm_blocks, int group, int nb_pad)
 {
     pdl_launch_dependents();
     pdl_wait_prior_grids();
+    if ((int)blockIdx.x >= perm_blocks) {
+        // group/8 consecutive lanes share one (g, m): each adds 8 values, then a fixed shuffle tree
+        const int lpg = group >> 3;                                     // 4 or 16 lanes
+        const int idx = ((int)blockIdx.x - perm_blocks) * blockDim.x + threadIdx.x;
+        const int ngroups = kcores * 8 / group;
+        const int item = idx / lpg, part = idx - item * lpg;
+        const bool live = item < ngroups * nb_pad;
+        const int g = live ? item / nb_pad : 0, m = live ? item - g * nb_pad : 0;
+        float s = 0.0f;
+        if (live && m < rows) {
+            const __half* src = a + (size_t)m * lda + (size_t)g * group + part * 8;
+            uint4 x;
+            if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+                x = *reinterpret_cast<const uint4*>(src);
+            } else {
+                const uint16_t* s16 = reinterpret_cast<const uint16_t*>(src);
+                x.x = s16[0] | ((uint32_t)s16[1] << 16); x.y = s16[2] | ((uint32_t)s16[3] << 16);
+                x.z = s16[4] | ((uint32_t)s16[5] << 16); x.w = s16[6] | ((uint32_t)s16[7] << 16);
+            }
+            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&x.x));
+            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&x.y));
+            const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&x.z));
+            const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&x.w));
+            s = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+        }
+        for (int d = 1; d < lpg; d <<= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+        if (live && part == 0) a8[item] = -8.0f * s;
+        return;
+    }
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= rows * kcores) return;
     const int kc = idx / rows, m = idx - kc * rows;
@@ -502,11 +601,16 @@ permute_activations_kernel(__half* __restrict__ out, const __half* __restrict__ 
         x.x = s16[0] | ((uint32_t)s16[1] << 16); x.y = s16[2] | ((uint32_t)s16[3] << 16);
         x.z = s16[4] | ((uint32_t)s16[5] << 16); x.w = s16[6] | ((uint32_t)s16[7] << 16);
     }
+    const __half2 sixteenth = __float2half2_rn(0.0625f);
+    uint32_t y1 = __byte_perm(x.x, x.z, 0x7632);      // k1,k5
+    uint32_t y3 = __byte_perm(x.y, x.w, 0x7632);      // k3,k7
+    const __half2 h1 = __hmul2(*reinterpret_cast<__half2*>(&y1), sixteenth);
+    const __half2 h3 = __hmul2(*reinterpret_cast<__half2*>(&y3), sixteenth);
     uint4 o;
-    o.x = __byte_perm(x.x, x.z, 0x5410);      // k0,k4
-    o.y = __byte_perm(x.x, x.z, 0x7632);      // k1,k5
-    o.z = __byte_perm(x.y, x.w, 0x5410);      // k2,k6
-    o.w = __byte_perm(x.y, x.w, 0x7632);      // k3,k7
+    o.x = __byte_perm(x.x, x.z, 0x5410);              // k0,k4
+    o.y = *reinterpret_cast<const uint32_t*>(&h1);
+    o.z = __byte_perm(x.y, x.w, 0x5410);              // k2,k6
+    o.w = *reinterpret_cast<const uint32_t*>(&h3);
     reinterpret_cast<uint4*>(out)[idx] = o;
 }
 

@@ -43,7 +43,7 @@ constexpr size_t kCounterBytes = 16384;   // 4096 tile counters at the head of t
 // sit in tcgen05.alloc until another CTA ends, and the SMs would finish unevenly).
 size_t tc_smem_bytes(int rows)
 {
-    const size_t need = rows <= 16 ? sizeof(twm::tc::Smem<16>) : (rows <= 32 ? sizeof(twm::tc::Smem<32>) : sizeof(twm::tc::Smem<64>));
+    const size_t need = rows <= 16 ? sizeof(twm::tc::Smem<16>) : sizeof(twm::tc::Smem<32>);
     return std::max(need, (size_t)80 * 1024);
 }
 
@@ -89,7 +89,6 @@ twm_status ensure_device(int* sm_count_out)
             };
             raise_tc((const void*)twm::tc::gemm_kernel<16>, tc_smem_bytes(16));
             raise_tc((const void*)twm::tc::gemm_kernel<32>, tc_smem_bytes(32));
-            raise_tc((const void*)twm::tc::gemm_kernel<64>, tc_smem_bytes(64));
             auto raise_mma = [&](const void* fn) {
                 if (r == cudaSuccess)
                     r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(twm::mma::Smem));
@@ -301,7 +300,7 @@ twm_status launch_strip(const twm::GemmParams& p, int mp, dim3 grid, bool pdl, c
     if (e != cudaSuccess) { set_error("launch strip::gemv_kernel", e); return TWM_ELAUNCH; }
     return TWM_OK;
 }
-constexpr int kTcRows = 64;      // activation rows one tcgen05 launch carries
+constexpr int kTcRows = 32;      // activation rows one tcgen05 launch carries
 
 twm_status launch_tc(const twm::GemmParams& p, int rows, dim3 grid, bool pdl, cudaStream_t stream)
 {
@@ -318,8 +317,7 @@ twm_status launch_tc(const twm::GemmParams& p, int rows, dim3 grid, bool pdl, cu
     cfg.numAttrs = pdl ? 1 : 0;
     cudaError_t e;
     if (rows <= 16) e = cudaLaunchKernelEx(&cfg, twm::tc::gemm_kernel<16>, p);
-    else if (rows <= 32) e = cudaLaunchKernelEx(&cfg, twm::tc::gemm_kernel<32>, p);
-    else e = cudaLaunchKernelEx(&cfg, twm::tc::gemm_kernel<64>, p);
+    else e = cudaLaunchKernelEx(&cfg, twm::tc::gemm_kernel<32>, p);
     if (e != cudaSuccess) { set_error("launch tc::gemm_kernel", e); return TWM_ELAUNCH; }
     return TWM_OK;
 }
@@ -479,7 +477,7 @@ twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int split
     const int n_tiles = (N + twm::simt::NT - 1) / twm::simt::NT;
     const int slots = sm_count * ((kernel != TWM_KERNEL_SIMT || mmax_for(rows) <= 4) ? 2 : 1);
     const int max_bps = nkb;
-    const int align = (kernel == TWM_KERNEL_MMA) ? group_size / 32 : 1;   // whole scale groups per slice
+    const int align = (kernel == TWM_KERNEL_MMA || kernel == TWM_KERNEL_TC) ? group_size / 32 : 1;   // whole scale groups per slice
     // up to two rows on the streaming MMA kernel: K slices add up inside a cluster (at most 16 slices)
     const bool can_cluster = (kernel == TWM_KERNEL_MMA) && rows <= twm::mma::CLUSTER_ROWS;
     int splits, bps;
@@ -501,9 +499,9 @@ twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int split
     out->grid_x = n_tiles;
     out->grid_y = splits;
     out->workspace_bytes = (splits > 1 && !cluster) ? kCounterBytes + (size_t)splits * rows * N * sizeof(float) : 0;
-    if (kernel == TWM_KERNEL_TC)    // + the launch's activations in the MMA's K order, behind the split-K part
+    if (kernel == TWM_KERNEL_TC)    // + the launch's activations in the MMA's K order and their per-group sums, behind the split-K part
         out->workspace_bytes = kCounterBytes + (splits > 1 ? (size_t)splits * rows * N * sizeof(float) : 0) +
-                               256 + (size_t)rows * K * 2;
+                               256 + (size_t)rows * K * 2 + 256 + (size_t)(K / group_size) * kTcRows * sizeof(float);
     out->cluster_reduce = cluster ? 1 : 0;
     return TWM_OK;
 }
@@ -614,15 +612,19 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
             // pre-pass: this launch's rows in [K/8][rows][8] order, then the GEMM loads them by TMA
             const size_t part_bytes = pl.splits > 1 ? (size_t)pl.splits * std::min(a->M, kTcRows) * a->N * sizeof(float) : 0;
             char* xp = (char*)a->workspace + kCounterBytes + ((part_bytes + 255) / 256) * 256;
-            const int nb_rows = rows <= 16 ? 16 : (rows <= 32 ? 32 : 64);
+            const int nb_rows = rows <= 16 ? 16 : 32;
             if (!make_act_map(&p.act_map, xp, rows, a->K, nb_rows)) {
                 snprintf(t_last_error, sizeof(t_last_error), "cuTensorMapEncodeTiled failed for the activation map");
                 return TWM_ELAUNCH;
             }
+            char* a8 = xp + (((size_t)rows * a->K * 2 + 255) / 256) * 256;
+            p.tc_a8 = (const float*)a8;
             const int items = rows * (a->K / 8);
-            st = launch_op("permute_activations_kernel", twm::tc::permute_activations_kernel, dim3((items + 255) / 256),
-                           dim3(256), 0, a->flags & TWM_FLAG_PDL, stream_, (__half*)xp, (const __half*)p.a, p.lda, rows,
-                           a->K / 8);
+            const int perm_blocks = (items + 255) / 256;
+            const int sum_blocks = ((a->K / a->group_size) * nb_rows * (a->group_size / 8) + 255) / 256;
+            st = launch_op("permute_activations_kernel", twm::tc::permute_activations_kernel, dim3(perm_blocks + sum_blocks),
+                           dim3(256), 0, a->flags & TWM_FLAG_PDL, stream_, (__half*)xp, (float*)a8, (const __half*)p.a, p.lda,
+                           rows, a->K / 8, perm_blocks, a->group_size, nb_rows);
             if (st != TWM_OK) return st;
             st = launch_tc(p, rows, dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
         }

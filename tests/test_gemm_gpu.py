@@ -21,16 +21,15 @@ TOL_F32 = 1e-3
 # fewer guard bits than an IEEE fused multiply-add chain (about 1e-6 of the output RMS observed);
 # still two orders below the FP16 rounding of the final store
 TOL_TC_F32 = 5e-3
-# The tcgen05 kernel multiplies with FP16 weights fp16_rn(scale * (nibble - 8)), as the reference's
-# dequantise-to-FP16 route does (quantize.rs:534-571).  It is checked tightly against the oracle
-# that rounds the weights the same way, and against the exact-weight oracle by the absolute bound
-# below (that rounding moves an output by about 2^-12 of the output RMS, whatever its own size).
+# Every kernel multiplies exact weights f32(scale) * (nibble - 8).  The tcgen05 kernel gives the
+# activations of odd K a factor 2^-4 (exact except below 2^-10, where FP16 runs out of exponent);
+# the absolute bound below, in units of the output RMS, covers that on top of the relative test.
 TC_ABS_VS_EXACT = 2e-3
 
 
 def _tc_ref(a, packed, scales, m, n, k, group, kernel):
     """The adjudicating oracle for a kernel family."""
-    return oracle.w4a16_f64(a, packed, scales, m, n, k, group, weights_f16=(kernel == _lib.TWM_KERNEL_TC))
+    return oracle.w4a16_f64(a, packed, scales, m, n, k, group)
 
 
 def _abs_err_over_rms(y, ref64):
@@ -258,12 +257,12 @@ def test_tc_kernel_rejects_f32_activations():
 @pytest.mark.parametrize("group", [32, 128])
 @pytest.mark.parametrize("m", [9, 16, 19, 32, 33, 64, 70, 130])
 def test_m_beyond_eight(m, group):
-    """The tcgen05 kernel's three accumulator widths (16, 32, 64 rows) and more rows than one launch carries."""
+    """The tcgen05 kernel's two accumulator widths (16, 32 rows) and more rows than one launch carries."""
     k, n = 512, 200
     _, packed, scales = _quantised(k, n, group, 47)
     a = seeded_activations(m, k, 0)
     y = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float16)
-    assert rel_err_floored(y, oracle.w4a16_f64(a, packed, scales, m, n, k, group, weights_f16=True)) < TOL_F16
+    assert rel_err_floored(y, oracle.w4a16_f64(a, packed, scales, m, n, k, group)) < TOL_F16
     assert _abs_err_over_rms(y, oracle.w4a16_f64(a, packed, scales, m, n, k, group)) < TC_ABS_VS_EXACT
     # FP32 rows from the FP32-FMA kernel agree too (m > 8 there is served by several launches)
     y32 = _run_gemm(a, packed, scales, m, n, k, group, torch.float32, torch.float32)
@@ -286,15 +285,19 @@ def test_config2_shape_m64():
     cols = slice(12800, 12800 + 384)
     packed = p.cpu().numpy()[:, cols].copy()
     scales = s.cpu().numpy().view(np.uint16)[:, cols].copy()
-    ref = oracle.w4a16_f64(a, packed, scales, m, 384, k, group, weights_f16=True)
+    ref = oracle.w4a16_f64(a, packed, scales, m, 384, k, group)
     assert rel_err_floored(c[:, cols].float().cpu().numpy(), ref) < TOL_F16
     # and a size-independent property on the whole output: every element written, linear in the activations
     assert not torch.isnan(c).any()
     c2 = torch.empty_like(c)
     q.gemm_tw_marlin(_to_dev(2.0 * a, torch.float16), p, s, c2, m, n, k, group_size=group, workspace=ws)
     torch.cuda.synchronize()
+    # (the kernel gives the activations of odd K a factor 2^-4, which rounds for |a| < 2^-10: doubling
+    #  such an activation is then not exactly doubling its product, so this is "within one FP16 step")
     normal = (c.abs() < 30000) & (c.abs() > 1e-3)
-    assert torch.equal(c2[normal], 2 * c[normal])
+    step = (2 * c[normal]).abs().float() * 2.0 ** -10
+    assert torch.all((c2[normal].float() - 2 * c[normal].float()).abs() <= step)
+    assert (c2[normal] != 2 * c[normal]).float().mean() < 1e-3
 
 
 def test_config0_shape_vs_literal_cpu_path():
