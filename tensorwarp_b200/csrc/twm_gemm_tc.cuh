@@ -50,20 +50,27 @@ constexpr int WSTAGE_BLOCKS = 4;      // 32-blocks per ring stage (8 KB)
 constexpr int WSTAGES = 6;            // packed ring depth: 48 KB in flight per CTA
 constexpr int DEQ_SETS = 2;           // unpack warp sets, alternate blocks
 constexpr int DEQ_THREADS = DEQ_SETS * 128;
-constexpr int EPI_THREADS = 128;      // the four read-back warps
-constexpr int WARP_READ0 = 8, WARP_TMA = 12, WARP_MMA = 13;
-constexpr int THREADS = 14 * 32;
+constexpr int WARP_READ0 = 8;         // first read-back warp
 constexpr int B_STAGE_KCORES = WSTAGE_BLOCKS * 4;     // 8-wide K cores per activation stage
-constexpr int TMEM_COLS = 256;
 constexpr int A8_SMEM_FLOATS = 8192;  // the K slice's -8*sum table is copied into shared memory when it fits (32 KB)
 
 template <int NB>
 struct Cfg {
-    static constexpr int ASLOTS = 3;                                // stages of A operands (and of activations) in flight
+    static constexpr int ASLOTS = (NB == 64) ? 2 : 3;               // stages of A operands (and of activations) in flight
     static constexpr int KCORE_BYTES = NB * 16;                     // one K core: NB rows x 8 K x 2 B
     static constexpr int B_STAGE_BYTES = B_STAGE_KCORES * KCORE_BYTES;
     static constexpr int A_SLOT_COLS = WSTAGE_BLOCKS * 16;          // A slot s: columns [64 s, 64 s + 64)
     static constexpr int D_COL0 = ASLOTS * A_SLOT_COLS;             // two accumulators of NB columns
+    // 256 tensor-memory columns, two CTAs per SM; four read-back warps per 32 accumulator columns
+    // (64 rows: two A slots instead of three, eight read-back warps).
+    static constexpr int TMEM_COLS = (D_COL0 + 2 * NB <= 256) ? 256 : 512;
+    static constexpr int READ_SETS = (NB + 31) / 32;
+    static constexpr int READ_COLS = NB / READ_SETS;                // accumulator columns per read-back warp
+    static constexpr int EPI_THREADS = READ_SETS * 128;
+    static constexpr int WARP_TMA = WARP_READ0 + 4 * READ_SETS;
+    static constexpr int WARP_MMA = WARP_TMA + 1;
+    static constexpr int THREADS = (WARP_MMA + 1) * 32;
+    static constexpr int CTAS_PER_SM = (TMEM_COLS == 256) ? 2 : 1;
     static_assert(D_COL0 + 2 * NB <= TMEM_COLS, "tensor memory budget of a CTA");
 };
 
@@ -167,11 +174,16 @@ __device__ __forceinline__ bool wait_uniform(uint64_t* bar, uint32_t parity, vol
 
 // NB = MMA N (activation rows padded to 16 or 32)
 template <int NB>
-__global__ void __launch_bounds__(THREADS, 2)
+__global__ void __launch_bounds__(Cfg<NB>::THREADS, Cfg<NB>::CTAS_PER_SM)
 gemm_kernel(const __grid_constant__ GemmParams p)
 {
     using C = Cfg<NB>;
     constexpr int ASLOTS = C::ASLOTS;
+    constexpr int TMEM_COLS = C::TMEM_COLS;
+    constexpr int EPI_THREADS = C::EPI_THREADS;
+    constexpr int WARP_TMA = C::WARP_TMA;
+    constexpr int WARP_MMA = C::WARP_MMA;
+    constexpr int RC = C::READ_COLS;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     Smem<NB>& sm = *reinterpret_cast<Smem<NB>*>(smem_raw);
 
@@ -430,6 +442,8 @@ gemm_kernel(const __grid_constant__ GemmParams p)
     } else if (warp < WARP_TMA) {
         // ------------------------------------- per-group read-back and epilogue --
         const int quarter = warp & 3;
+        const int rset = (warp - WARP_READ0) >> 2;            // which RC accumulator columns (activation rows) this warp takes
+        const int row0 = rset * RC;
         const int col = quarter * 32 + lane;
         const int n = n0 + col;
         const bool owner = n < p.N;
@@ -437,9 +451,9 @@ gemm_kernel(const __grid_constant__ GemmParams p)
         const uint16_t* scales = p.scales;
         pdl_wait_prior_grids();          // the -8*sum table comes from the pre-pass; C may be read by the kernel before
         if (p.scales_offsets != nullptr) scales += p.scales_offsets[p.expert_idx];
-        float acc[NB];
+        float acc[RC];
 #pragma unroll
-        for (int j = 0; j < NB; ++j) acc[j] = 0.0f;
+        for (int j = 0; j < RC; ++j) acc[j] = 0.0f;
         bool ok = true;
         const int n_groups = (gshift == 2) ? n_wstages : total_blocks;
         const int grow0 = b0 >> gshift;
@@ -473,16 +487,15 @@ gemm_kernel(const __grid_constant__ GemmParams p)
             tc_fence_after();
             PROF_BEGIN(t1);
 #pragma unroll
-            for (int c0 = 0; c0 < NB; c0 += 16) {
-                if (c0 < p.M) {                                        // warp-uniform
-                    uint32_t d[16];
-                    tmem_ld<16>(lane_tmem + C::D_COL0 + db * NB + c0, d);
-                    const float4 q0 = a8p[c0 / 4], q1 = a8p[c0 / 4 + 1], q2 = a8p[c0 / 4 + 2], q3 = a8p[c0 / 4 + 3];
-                    const float a8[16] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w,
-                                          q2.x, q2.y, q2.z, q2.w, q3.x, q3.y, q3.z, q3.w};
+            for (int c0 = 0; c0 < RC; c0 += 8) {
+                if (row0 + c0 < p.M) {                                 // warp-uniform
+                    uint32_t d[8];
+                    tmem_ld<8>(lane_tmem + C::D_COL0 + db * NB + row0 + c0, d);
+                    const float4 q0 = a8p[(row0 + c0) / 4], q1 = a8p[(row0 + c0) / 4 + 1];
+                    const float a8[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
                     tmem_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
+                    for (int j = 0; j < 8; ++j)
                         acc[c0 + j] = fmaf(sg, fmaf(__uint_as_float(d[j]), 16777216.0f, a8[j]), acc[c0 + j]);
                 }
             }
@@ -508,10 +521,11 @@ gemm_kernel(const __grid_constant__ GemmParams p)
         };
         if (ok && owner) {
 #pragma unroll
-            for (int j = 0; j < NB; ++j) {
-                if (j < p.M) {
-                    if (p.splits == 1) store_c(j, acc[j]);
-                    else p.ws_partials[((size_t)blockIdx.y * p.M + j) * p.N + n] = acc[j];
+            for (int j = 0; j < RC; ++j) {
+                const int m = row0 + j;
+                if (m < p.M) {
+                    if (p.splits == 1) store_c(m, acc[j]);
+                    else p.ws_partials[((size_t)blockIdx.y * p.M + m) * p.N + n] = acc[j];
                 }
             }
         }
@@ -526,7 +540,7 @@ gemm_kernel(const __grid_constant__ GemmParams p)
             if (sm.is_last) {
                 __threadfence();
                 if (owner && *abort_flag == 0) {
-                    for (int m = 0; m < p.M; ++m) {
+                    for (int m = row0; m < min(p.M, row0 + RC); ++m) {
                         float s = 0.0f;
                         for (int sp = 0; sp < p.splits; ++sp)
                             s += ld_cg_f32(&p.ws_partials[((size_t)sp * p.M + m) * p.N + n]);

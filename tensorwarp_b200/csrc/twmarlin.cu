@@ -43,7 +43,7 @@ constexpr size_t kCounterBytes = 16384;   // 4096 tile counters at the head of t
 // sit in tcgen05.alloc until another CTA ends, and the SMs would finish unevenly).
 size_t tc_smem_bytes(int rows)
 {
-    const size_t need = rows <= 16 ? sizeof(twm::tc::Smem<16>) : sizeof(twm::tc::Smem<32>);
+    const size_t need = rows <= 16 ? sizeof(twm::tc::Smem<16>) : (rows <= 32 ? sizeof(twm::tc::Smem<32>) : sizeof(twm::tc::Smem<64>));
     return std::max(need, (size_t)80 * 1024);
 }
 
@@ -89,6 +89,7 @@ twm_status ensure_device(int* sm_count_out)
             };
             raise_tc((const void*)twm::tc::gemm_kernel<16>, tc_smem_bytes(16));
             raise_tc((const void*)twm::tc::gemm_kernel<32>, tc_smem_bytes(32));
+            raise_tc((const void*)twm::tc::gemm_kernel<64>, tc_smem_bytes(64));
             auto raise_mma = [&](const void* fn) {
                 if (r == cudaSuccess)
                     r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(twm::mma::Smem));
@@ -242,14 +243,16 @@ bool strip_eligible(int M, int N, int K, int G, bool indirect)
 {
     return !indirect && (N & 7) == 0 && (N + twm::strip::NT - 1) / twm::strip::NT >= kStripMinStrips && strip_fits(M, K, G);
 }
+// Measured on the 7B gate+up shape (us per launch in a dependent chain): the streaming MMA kernel
+// 15.7 / 16.2 / 20.3 / 30.7 at M = 1 / 2 / 4 / 8, the tcgen05 kernel 26-27 for any M up to 16.
+constexpr int kTcFromRows = 5;
 int auto_kernel(int M, int N, int K, int G, bool a_is_f16, bool indirect, int splits_override)
 {
     if (!a_is_f16) return TWM_KERNEL_SIMT;
-    if (M > 8) return TWM_KERNEL_TC;
     // The strip kernel is not chosen here: measured on the 7B decode chain it is slower than the
     // split-K kernel (one CTA per SM cannot unpack at HBM rate); it runs when asked for by name.
     (void)N; (void)K; (void)G; (void)indirect; (void)splits_override;
-    return TWM_KERNEL_MMA;
+    return M >= kTcFromRows ? TWM_KERNEL_TC : TWM_KERNEL_MMA;
 }
 
 int resolve_kernel(const twm_gemm_args* a)
@@ -257,8 +260,14 @@ int resolve_kernel(const twm_gemm_args* a)
     if (a->kernel_override != TWM_KERNEL_AUTO) return a->kernel_override;
     int kernel = auto_kernel(a->M, a->N, a->K, a->group_size, a->a_dtype == TWM_F16, a->packed_offsets != nullptr,
                              a->splits_override);
-    // the scale tensor map needs a 16-byte aligned base (a sub-buffer may not have one)
-    if (kernel == TWM_KERNEL_STRIP && (reinterpret_cast<uintptr_t>(a->scales) & 15)) kernel = TWM_KERNEL_MMA;
+    // five to eight rows: the tcgen05 kernel when the caller's workspace holds its pre-pass
+    // output, else the streaming kernel (which needs less or none)
+    if (kernel == TWM_KERNEL_TC && a->M <= 8) {
+        twm_plan_t pl;
+        if (twm_plan(a->M, a->N, a->K, a->group_size, kDefaultSms, a->splits_override, TWM_KERNEL_TC, &pl) != TWM_OK ||
+            !a->workspace || a->workspace_bytes < pl.workspace_bytes)
+            kernel = TWM_KERNEL_MMA;
+    }
     return kernel;
 }
 
@@ -300,14 +309,14 @@ twm_status launch_strip(const twm::GemmParams& p, int mp, dim3 grid, bool pdl, c
     if (e != cudaSuccess) { set_error("launch strip::gemv_kernel", e); return TWM_ELAUNCH; }
     return TWM_OK;
 }
-constexpr int kTcRows = 32;      // activation rows one tcgen05 launch carries
+constexpr int kTcRows = 64;      // activation rows one tcgen05 launch carries
 
 twm_status launch_tc(const twm::GemmParams& p, int rows, dim3 grid, bool pdl, cudaStream_t stream)
 {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = grid;
-    cfg.blockDim = dim3(twm::tc::THREADS, 1, 1);
+    cfg.blockDim = dim3(rows <= 32 ? twm::tc::Cfg<32>::THREADS : twm::tc::Cfg<64>::THREADS, 1, 1);
     cfg.dynamicSmemBytes = tc_smem_bytes(rows);
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -317,7 +326,8 @@ twm_status launch_tc(const twm::GemmParams& p, int rows, dim3 grid, bool pdl, cu
     cfg.numAttrs = pdl ? 1 : 0;
     cudaError_t e;
     if (rows <= 16) e = cudaLaunchKernelEx(&cfg, twm::tc::gemm_kernel<16>, p);
-    else e = cudaLaunchKernelEx(&cfg, twm::tc::gemm_kernel<32>, p);
+    else if (rows <= 32) e = cudaLaunchKernelEx(&cfg, twm::tc::gemm_kernel<32>, p);
+    else e = cudaLaunchKernelEx(&cfg, twm::tc::gemm_kernel<64>, p);
     if (e != cudaSuccess) { set_error("launch tc::gemm_kernel", e); return TWM_ELAUNCH; }
     return TWM_OK;
 }
@@ -612,7 +622,7 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
             // pre-pass: this launch's rows in [K/8][rows][8] order, then the GEMM loads them by TMA
             const size_t part_bytes = pl.splits > 1 ? (size_t)pl.splits * std::min(a->M, kTcRows) * a->N * sizeof(float) : 0;
             char* xp = (char*)a->workspace + kCounterBytes + ((part_bytes + 255) / 256) * 256;
-            const int nb_rows = rows <= 16 ? 16 : 32;
+            const int nb_rows = rows <= 16 ? 16 : (rows <= 32 ? 32 : 64);
             if (!make_act_map(&p.act_map, xp, rows, a->K, nb_rows)) {
                 snprintf(t_last_error, sizeof(t_last_error), "cuTensorMapEncodeTiled failed for the activation map");
                 return TWM_ELAUNCH;

@@ -63,7 +63,7 @@ def test_static_scratch_rejects_oversized_plans():
     lib = _lib.lib()
     cap = lib.twm_static_ws_capacity()
     m, k, n, group = 8, 8192, 65536, 128
-    need = q.plan(m, n, k, group, splits_override=8).workspace_bytes
+    need = q.plan(m, n, k, group, splits_override=8, kernel_override=_lib.TWM_KERNEL_MMA).workspace_bytes
     assert need > cap
     dummy = torch.zeros(64, dtype=torch.uint8, device="cuda")          # never dereferenced: the call fails first
     args = _lib.GemmArgs(M=m, N=n, K=k, group_size=group, a_dtype=_lib.TWM_F16, c_dtype=_lib.TWM_F16,
