@@ -212,8 +212,11 @@ def run_ours(args):
     if err:
         raise RuntimeError(f"device error word {err:#x}")
     decode = None
+    sweep = None
     if not args.no_decode and rank == 0:
         del weights, graph
+        torch.cuda.empty_cache()
+        sweep = m_sweep(torch, q, device)
         torch.cuda.empty_cache()
         decode = decode_tok_s(torch, device)
 
@@ -245,12 +248,69 @@ def run_ours(args):
     }
     if decode is not None:
         line["decode"] = decode
+    if sweep is not None:
+        line["m_sweep"] = sweep
     if rank == 0:
         if not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(target_seconds=12.0)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def m_sweep(torch, q, device):
+    """configs[2]: the 7B gate+up shape (K=3584, N=37888, G=128, FP16) at M = 1..256, eight distinct
+    weight sets per graph (568 MB, larger than L2), programmatic dependent launch; microseconds per
+    GEMM (for M above one launch's rows: all its launches), the kernel the heuristic chose, HBM and
+    tensor fractions of the measured peaks."""
+    from tensorwarp_b200 import _lib
+    k, n, copies = 3584, 37888, 8
+    names = {_lib.TWM_KERNEL_SIMT: "simt", _lib.TWM_KERNEL_TC: "tcgen05", _lib.TWM_KERNEL_MMA: "mma", _lib.TWM_KERNEL_STRIP: "strip"}
+    peak, _ = measured_peak_gbs()
+    tf_peak = 1629.9
+    try:
+        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) as f:
+            tf_peak = float(json.load(f).get("bf16_tflops", tf_peak))
+    except (OSError, ValueError):
+        pass
+    ws = []
+    for i in range(copies):
+        w = torch.randn((k, n), generator=torch.Generator(device=device).manual_seed(200 + i), device=device) * 0.02
+        ws.append(q.quantize_f32_to_tw_marlin(w, k, n, GROUP))
+        del w
+    out = []
+    for m in (1, 2, 4, 8, 16, 32, 64, 128, 256):
+        a = torch.randn((m, k), generator=torch.Generator(device=device).manual_seed(m), device=device).half()
+        c = torch.empty((m, n), dtype=torch.float16, device=device)
+        wsb = q.Workspace(q.workspace_bytes(m, n, k, GROUP), device)
+        stream = torch.cuda.Stream(device)
+
+        def enqueue():
+            for p_, s_ in ws:
+                q.gemm_tw_marlin(a, p_, s_, c, m, n, k, group_size=GROUP, workspace=wsb, flags=_lib.TWM_FLAG_PDL)
+
+        with torch.cuda.stream(stream):
+            enqueue()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                enqueue()
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(5):
+                graph.replay()
+            e1.record(stream)
+            torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (5 * copies)
+        b = algorithmic_bytes(m, n, k, GROUP)
+        kern = q.plan(m, n, k, GROUP).kernel
+        out.append({"m": m, "us": round(us, 2), "kernel": names.get(kern, str(kern)),
+                    "hbm_frac": round(b / us / 1e3 / peak, 3), "tensor_frac": round(2.0 * m * k * n / us / 1e6 / tf_peak, 4)})
+        del graph
+    return out
 
 
 def decode_tok_s(torch, device, new_tokens: int = 64, kv_len: int = 2048):

@@ -53,16 +53,6 @@ enum {
                             the heuristic (measured slower on B200); N % 8 == 0, activations must fit in shared memory */
 };
 
-/* Fused activation prologues (twm_gemm_args.a_op), streaming MMA kernel, M <= 8.  They replace the
- * separate passes the reference runs before these GEMMs in a decode step. */
-typedef enum {
-    TWM_A_PLAIN = 0,     /* a is the activation matrix */
-    TWM_A_SILU_MUL = 1,  /* a is the fused gate+up output, FP16 [M][lda >= 2K] = [gate | up]: the GEMM multiplies
-                            fp16(silu(gate) * up) (warp_fused_silu_mul, crates/kernels/src/ops.rs:966-977, then down) */
-    TWM_A_RMSNORM = 2    /* a is the FP32 residual stream [M][lda]: the GEMM multiplies fp16(x * rstd * gamma), rstd over
-                            the K values of the row (rmsnorm, ops.rs:302-336, then QKV or gate+up); a_dtype = TWM_F32 */
-} twm_a_op;
-
 /* Flags of twm_gemm_args.flags. */
 enum {
     /* Launch with programmatic stream serialisation: the kernel may start
@@ -121,12 +111,6 @@ typedef struct twm_gemm_args {
      * by tile as the tiles finish), and the grid's last CTA raises the arrival flags.  The sum is
      * taken by twm_allreduce_add_rmsnorm on each rank.  M <= 8, FP16 activations. */
     const twm_comm* comm;
-    /* Fused activation prologue (twm_a_op; 0 = none).  Non-zero selects the streaming MMA kernel (M <= 8).
-     * TWM_A_SILU_MUL: a, lda describe [gate | up], 16-byte aligned, lda % 8 == 0.
-     * TWM_A_RMSNORM: a is FP32 (a_dtype = TWM_F32), 16-byte aligned, lda % 4 == 0; a_gamma FP32 [K], a_eps. */
-    int a_op;
-    const float* a_gamma;
-    float a_eps;
 } twm_gemm_args;
 
 /* What the heuristic decided for a shape; pure host arithmetic. */

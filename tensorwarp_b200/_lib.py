@@ -13,7 +13,6 @@ LIB_PATH = os.environ.get("TWMARLIN_LIB", os.path.join(PKG, "libtwmarlin.so"))
 
 TWM_OK, TWM_EINVAL, TWM_EALIGN, TWM_EWORKSPACE, TWM_ELAUNCH, TWM_EARCH, TWM_ETIMEOUT = 0, -1, -2, -3, -4, -5, -6
 TWM_F32, TWM_F16 = 0, 1
-TWM_A_PLAIN, TWM_A_SILU_MUL, TWM_A_RMSNORM = 0, 1, 2
 TWM_KERNEL_AUTO, TWM_KERNEL_SIMT, TWM_KERNEL_TC, TWM_KERNEL_MMA, TWM_KERNEL_STRIP = 0, 1, 2, 3, 4
 TWM_FLAG_PDL, TWM_FLAG_ACCUMULATE = 1, 2
 
@@ -31,7 +30,6 @@ class GemmArgs(C.Structure):
         ("splits_override", C.c_int), ("kernel_override", C.c_int), ("flags", C.c_int),
         ("packed_offsets", C.c_void_p), ("scales_offsets", C.c_void_p), ("expert_idx", C.c_int),
         ("comm", C.c_void_p),
-        ("a_op", C.c_int), ("a_gamma", C.c_void_p), ("a_eps", C.c_float),
     ]
 
 

@@ -233,10 +233,6 @@ struct GemmParams {
     unsigned int* comm_state;        // [0] operation sequence number, [1] CTAs done, [2] consumer CTAs done
     // Tensor map over `packed` seen as u64 [K/32][2N]: one TMA instruction brings a whole
     // ring stage (box = 256 u64 x map_rows rows = 128 columns x map_rows 32-blocks).
-    // streaming MMA kernel: what the stager makes the FP16 activations from (TWM_A_*)
-    int a_op;
-    const float* a_gamma;        // TWM_A_RMSNORM: the norm's weight, FP32 [K]
-    float a_eps;
     int strip_stages;            // strip kernel: depth of the weight ring (what fits beside the activations)
     int map_rows;                // 0 = no map (1-D bulk copies per row instead)
     int launch_id;               // development builds: index of this launch in the timeline buffer

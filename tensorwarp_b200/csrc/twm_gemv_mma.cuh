@@ -60,7 +60,6 @@ struct Smem {
     alignas(128) uint8_t b[2][B_BUF_BYTES];           // [block in chunk][row m < MP][t] x 16 bytes
     alignas(16) float asum8[2][ASUM_GROUPS][8];       // -8 * sum of a group's activations, per row
     alignas(16) float red[MAX_CLUSTER][CLUSTER_ROWS][NT];   // cluster leader only: one partial tile per K slice
-    float ssq_part[CONSUMER_WARPS + 1][8];            // fused RMSNorm: per-warp sums of squares, per row
     alignas(8) uint64_t full[STAGES];
     alignas(8) uint64_t empty[STAGES];
     alignas(8) uint64_t b_full[2];
@@ -137,33 +136,6 @@ gemv_kernel(const __grid_constant__ GemmParams p)
     const int g = lane >> 2;
     const int t = lane & 3;
     const int wcol = warp * 16;                       // a consumer warp's 16 columns inside the tile
-
-    // Fused RMSNorm prologue: every row's sum of squares over the WHOLE K (not just this CTA's
-    // slice), by the consumer and stager warps together (the producer goes on streaming
-    // weights), in a fixed order: lane partials, warp shuffle tree, warps 0..8 in turn.
-    if (p.a_op == TWM_A_RMSNORM && warp != CONSUMER_WARPS) {
-        pdl_wait_prior_grids();
-        const int widx = (warp < CONSUMER_WARPS) ? warp : CONSUMER_WARPS;
-        const int idx = widx * 32 + lane;
-        constexpr int NTHR = (CONSUMER_WARPS + 1) * 32;
-        for (int m = 0; m < MP; ++m) {
-            float ss = 0.0f;
-            if (m < p.M) {
-                const float4* xr = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.a) + (size_t)m * p.lda);
-                for (int i = idx; i < (p.K >> 2); i += NTHR) {
-                    const float4 v = xr[i];
-                    ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
-                }
-            }
-            ss += __shfl_xor_sync(0xffffffffu, ss, 16);
-            ss += __shfl_xor_sync(0xffffffffu, ss, 8);
-            ss += __shfl_xor_sync(0xffffffffu, ss, 4);
-            ss += __shfl_xor_sync(0xffffffffu, ss, 2);
-            ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-            if (lane == 0) sm.ssq_part[widx][m] = ss;
-        }
-        named_bar_sync(4, NTHR);
-    }
 #ifdef TWM_EXP_NOWAIT
     if (warp >= CONSUMER_WARPS) return;          // development experiment: consumers run on whatever is in shared memory
 #endif
@@ -237,17 +209,6 @@ gemv_kernel(const __grid_constant__ GemmParams p)
         pdl_wait_prior_grids();
         const __half* A = reinterpret_cast<const __half*>(p.a);
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(A) & 15) == 0) && ((p.lda & 7) == 0);
-        float rstd[MP];
-#pragma unroll
-        for (int m = 0; m < MP; ++m) {
-            rstd[m] = 0.0f;
-            if (p.a_op == TWM_A_RMSNORM) {
-                float tot_sq = 0.0f;
-#pragma unroll
-                for (int w = 0; w <= CONSUMER_WARPS; ++w) tot_sq += sm.ssq_part[w][m];
-                rstd[m] = rsqrtf(tot_sq / (float)p.K + p.a_eps);
-            }
-        }
         constexpr int PF = 8;
         for (int chunk = 0; chunk < n_chunks; ++chunk) {
             const int buf = chunk & 1;
@@ -270,35 +231,7 @@ gemv_kernel(const __grid_constant__ GemmParams p)
                         const int bi = ((rest / MP) << gshift) + bj;
                         if (m < p.M) {
                             const size_t off = (size_t)m * p.lda + (size_t)(b0 + cb0 + bi) * kBlockK + tt * 8;
-                            if (p.a_op == TWM_A_SILU_MUL) {
-                                // [gate | up] -> fp16(silu(gate) * up), the formula of the separate pass
-                                const uint4 g4 = *reinterpret_cast<const uint4*>(A + off);
-                                const uint4 u4 = *reinterpret_cast<const uint4*>(A + off + p.K);
-                                const __half2* gh = reinterpret_cast<const __half2*>(&g4);
-                                const __half2* uh = reinterpret_cast<const __half2*>(&u4);
-                                uint32_t o[4];
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    const float2 gf = __half22float2(gh[e]), uf = __half22float2(uh[e]);
-                                    const __half2 r = __floats2half2_rn(gf.x / (1.0f + expf(-gf.x)) * uf.x,
-                                                                        gf.y / (1.0f + expf(-gf.y)) * uf.y);
-                                    o[e] = *reinterpret_cast<const uint32_t*>(&r);
-                                }
-                                x[u] = make_uint4(o[0], o[1], o[2], o[3]);
-                            } else if (p.a_op == TWM_A_RMSNORM) {
-                                // FP32 residual row -> fp16(x * rstd * gamma), the formula of the separate pass
-                                const float* X = reinterpret_cast<const float*>(p.a) + off;
-                                const float* Gm = p.a_gamma + (size_t)(b0 + cb0 + bi) * kBlockK + tt * 8;
-                                const float4 x0 = *reinterpret_cast<const float4*>(X), x1 = *reinterpret_cast<const float4*>(X + 4);
-                                const float4 g0 = __ldg(reinterpret_cast<const float4*>(Gm)), g1 = __ldg(reinterpret_cast<const float4*>(Gm + 4));
-                                const float r = rstd[m];
-                                const __half2 h0 = __floats2half2_rn(x0.x * r * g0.x, x0.y * r * g0.y);
-                                const __half2 h1 = __floats2half2_rn(x0.z * r * g0.z, x0.w * r * g0.w);
-                                const __half2 h2 = __floats2half2_rn(x1.x * r * g1.x, x1.y * r * g1.y);
-                                const __half2 h3 = __floats2half2_rn(x1.z * r * g1.z, x1.w * r * g1.w);
-                                x[u] = make_uint4(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1),
-                                                  *reinterpret_cast<const uint32_t*>(&h2), *reinterpret_cast<const uint32_t*>(&h3));
-                            } else if (vec_ok) {
+                            if (vec_ok) {
                                 x[u] = *reinterpret_cast<const uint4*>(A + off);
                             } else {
                                 const uint16_t* a16 = reinterpret_cast<const uint16_t*>(A) + off;
@@ -385,7 +318,6 @@ gemv_kernel(const __grid_constant__ GemmParams p)
         }
         PROF_END(t1, 1);
 #endif
-        if (it == 0 && warp == 0) { TL_MARK(p.launch_id, 4); }
         PROF_BEGIN(t2);
 #ifdef TWM_EXP_NOCOMPUTE
         if (false) {
@@ -440,7 +372,6 @@ gemv_kernel(const __grid_constant__ GemmParams p)
         PROF_END(t3, 3);
     }
     PROF_FLUSH(1);
-    if (warp == 0) { TL_MARK(p.launch_id, 2); }
 
     }   // consumers
 

@@ -258,7 +258,6 @@ int auto_kernel(int M, int N, int K, int G, bool a_is_f16, bool indirect, int sp
 int resolve_kernel(const twm_gemm_args* a)
 {
     if (a->kernel_override != TWM_KERNEL_AUTO) return a->kernel_override;
-    if (a->a_op != TWM_A_PLAIN) return TWM_KERNEL_MMA;          // the prologues live in that kernel's stager
     int kernel = auto_kernel(a->M, a->N, a->K, a->group_size, a->a_dtype == TWM_F16, a->packed_offsets != nullptr,
                              a->splits_override);
     // five to eight rows: the tcgen05 kernel when the caller's workspace holds its pre-pass
@@ -552,21 +551,7 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
     // The tensor-core kernel takes FP16 activations; FP32 activations (the
     // reference's own signature) run on the FP32 streaming kernel.
     const int kernel = resolve_kernel(a);
-    if (a->a_op != TWM_A_PLAIN) {
-        if (kernel != TWM_KERNEL_MMA || a->M > 8) return TWM_EINVAL;
-        if (a->a_op == TWM_A_SILU_MUL) {
-            if (a->a_dtype != TWM_F16 || a->lda < 2L * a->K) return TWM_EINVAL;
-            if ((reinterpret_cast<uintptr_t>(a->a) & 15) || (a->lda & 7)) return TWM_EALIGN;
-        } else if (a->a_op == TWM_A_RMSNORM) {
-            if (a->a_dtype != TWM_F32 || !a->a_gamma || !(a->a_eps >= 0.0f)) return TWM_EINVAL;
-            if ((reinterpret_cast<uintptr_t>(a->a) & 15) || (reinterpret_cast<uintptr_t>(a->a_gamma) & 15) || (a->lda & 3))
-                return TWM_EALIGN;
-        } else {
-            return TWM_EINVAL;
-        }
-    } else if (kernel != TWM_KERNEL_SIMT && a->a_dtype != TWM_F16) {
-        return TWM_EINVAL;
-    }
+    if (kernel != TWM_KERNEL_SIMT && a->a_dtype != TWM_F16) return TWM_EINVAL;
     if (kernel == TWM_KERNEL_STRIP && a->packed_offsets != nullptr) return TWM_EINVAL;
     twm_plan_t pl;
     st = twm_plan(a->M, a->N, a->K, a->group_size, sm_count, a->splits_override, kernel, &pl);
@@ -617,7 +602,6 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
         p.splits = pl.splits; p.blocks_per_split = pl.blocks_per_split;
         p.cluster_reduce = (pl.cluster_reduce && rows <= twm::mma::CLUSTER_ROWS) ? 1 : 0;
         p.accumulate = (a->flags & TWM_FLAG_ACCUMULATE) ? 1 : 0;
-        p.a_op = a->a_op; p.a_gamma = a->a_gamma; p.a_eps = a->a_eps;
         p.packed_offsets = a->packed_offsets; p.scales_offsets = a->scales_offsets; p.expert_idx = a->expert_idx;
         if (a->comm) {
             p.n_peers = a->comm->n_ranks; p.peer_rank = a->comm->rank; p.peer_slot_elems = a->comm->slot_elems;

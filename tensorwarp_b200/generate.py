@@ -130,11 +130,8 @@ class Q4DecodeBuffers:
 class QuantizedGenerationEngine:
     """Decode engine on TW-Marlin weights (generate.rs:1191-2547, Q4 + marlin + graph path)."""
 
-    def __init__(self, model: Q4Model, use_pdl: bool = True, fused_prologues: bool = True):
+    def __init__(self, model: Q4Model, use_pdl: bool = True):
         self.model = model
-        # RMSNorm and SwiGLU folded into the stager of the GEMM that consumes them (7 launches a
-        # layer instead of 10); False keeps the separate passes (the reference's launch sequence)
-        self.fused_prologues = fused_prologues
         self.cfg = model.cfg
         self.buf = Q4DecodeBuffers(model.cfg, model.device)
         self.flags = _lib.TWM_FLAG_PDL if use_pdl else 0
@@ -167,29 +164,21 @@ class QuantizedGenerationEngine:
         lib, cfg, b, fl = _lib.lib(), self.cfg, self.buf, self.flags
         n = 0
 
-        def gemm(a, w, c, n_out, k_in, accumulate=False, a_op=_lib.TWM_A_PLAIN, gamma=None):
-            args = _lib.GemmArgs(M=1, N=n_out, K=k_in, group_size=cfg.group_size,
-                                 a_dtype=_lib.TWM_F32 if a.dtype == torch.float32 else _lib.TWM_F16,
+        def gemm(a, w, c, n_out, k_in, accumulate=False):
+            args = _lib.GemmArgs(M=1, N=n_out, K=k_in, group_size=cfg.group_size, a_dtype=_lib.TWM_F16,
                                  c_dtype=_lib.TWM_F32 if c.dtype == torch.float32 else _lib.TWM_F16,
-                                 a=a.data_ptr(), lda=a.shape[-1], packed=w[0].data_ptr(), scales=w[1].data_ptr(),
+                                 a=a.data_ptr(), lda=k_in, packed=w[0].data_ptr(), scales=w[1].data_ptr(),
                                  c=c.data_ptr(), ldc=n_out, workspace=b.workspace.ptr,
                                  workspace_bytes=b.workspace.nbytes,
-                                 flags=fl | (_lib.TWM_FLAG_ACCUMULATE if accumulate else 0),
-                                 a_op=a_op, a_gamma=gamma.data_ptr() if gamma is not None else None, a_eps=cfg.eps)
+                                 flags=fl | (_lib.TWM_FLAG_ACCUMULATE if accumulate else 0))
             check(lib.twm_gemm_w4a16(C.byref(args), stream_ptr), "twm_gemm_w4a16")
-
-        fused = self.fused_prologues
 
         check(lib.twm_embed(b.x.data_ptr(), self.model.embed.data_ptr(), b.token.data_ptr(), 1, cfg.hidden, fl,
                             stream_ptr), "twm_embed"); n += 1
         for li, lw in enumerate(self.model.layers):
-            if fused:       # qkv = W(rmsnorm(x)): the norm happens in the GEMM's stager
-                gemm(b.x, lw.wqkv, b.qkv, cfg.q_dim + 2 * cfg.kv_dim, cfg.hidden, a_op=_lib.TWM_A_RMSNORM,
-                     gamma=lw.attn_norm); n += 1
-            else:
-                check(lib.twm_rmsnorm(b.normed.data_ptr(), b.x.data_ptr(), lw.attn_norm.data_ptr(), 1, cfg.hidden, cfg.eps,
-                                      fl, stream_ptr), "twm_rmsnorm"); n += 1
-                gemm(b.normed, lw.wqkv, b.qkv, cfg.q_dim + 2 * cfg.kv_dim, cfg.hidden); n += 1
+            check(lib.twm_rmsnorm(b.normed.data_ptr(), b.x.data_ptr(), lw.attn_norm.data_ptr(), 1, cfg.hidden, cfg.eps,
+                                  fl, stream_ptr), "twm_rmsnorm"); n += 1
+            gemm(b.normed, lw.wqkv, b.qkv, cfg.q_dim + 2 * cfg.kv_dim, cfg.hidden); n += 1
             check(lib.twm_rope_append(b.q.data_ptr(), b.k_cache[li].data_ptr(), b.v_cache[li].data_ptr(),
                                       b.qkv.data_ptr(), lw.bqkv.data_ptr() if lw.bqkv is not None else None,
                                       1, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, b.pos.data_ptr(), cfg.max_seq,
@@ -199,17 +188,12 @@ class QuantizedGenerationEngine:
                                       b.cache_len.data_ptr(), cfg.max_seq, b.attn_scratch.data_ptr(),
                                       b.attn_scratch.numel(), fl, stream_ptr), "twm_attn_decode"); n += 2
             gemm(b.attn, lw.wo, b.x, cfg.hidden, cfg.q_dim, accumulate=True); n += 1            # x += o(attn)
-            if fused:
-                gemm(b.x, lw.wgu, b.gate_up, 2 * cfg.ffn, cfg.hidden, a_op=_lib.TWM_A_RMSNORM, gamma=lw.ffn_norm); n += 1
-                gemm(b.gate_up, lw.w_down, b.x, cfg.hidden, cfg.ffn, accumulate=True,
-                     a_op=_lib.TWM_A_SILU_MUL); n += 1                                          # x += down(silu(gate) * up)
-            else:
-                check(lib.twm_rmsnorm(b.normed.data_ptr(), b.x.data_ptr(), lw.ffn_norm.data_ptr(), 1, cfg.hidden, cfg.eps,
-                                      fl, stream_ptr), "twm_rmsnorm"); n += 1
-                gemm(b.normed, lw.wgu, b.gate_up, 2 * cfg.ffn, cfg.hidden); n += 1
-                check(lib.twm_silu_mul(b.act.data_ptr(), b.gate_up.data_ptr(), 1, cfg.ffn, fl, stream_ptr),
-                      "twm_silu_mul"); n += 1
-                gemm(b.act, lw.w_down, b.x, cfg.hidden, cfg.ffn, accumulate=True); n += 1       # x += down(act)
+            check(lib.twm_rmsnorm(b.normed.data_ptr(), b.x.data_ptr(), lw.ffn_norm.data_ptr(), 1, cfg.hidden, cfg.eps,
+                                  fl, stream_ptr), "twm_rmsnorm"); n += 1
+            gemm(b.normed, lw.wgu, b.gate_up, 2 * cfg.ffn, cfg.hidden); n += 1
+            check(lib.twm_silu_mul(b.act.data_ptr(), b.gate_up.data_ptr(), 1, cfg.ffn, fl, stream_ptr),
+                  "twm_silu_mul"); n += 1
+            gemm(b.act, lw.w_down, b.x, cfg.hidden, cfg.ffn, accumulate=True); n += 1           # x += down(act)
         check(lib.twm_rmsnorm(b.normed.data_ptr(), b.x.data_ptr(), self.model.final_norm.data_ptr(), 1, cfg.hidden,
                               cfg.eps, fl, stream_ptr), "twm_rmsnorm"); n += 1
         check(lib.twm_lm_head(b.logits.data_ptr(), b.normed.data_ptr(), self.model.lm_head.data_ptr(), cfg.hidden,

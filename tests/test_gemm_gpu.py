@@ -430,58 +430,3 @@ def test_errors_are_statuses():
     q.gemm_tw_marlin_m1(a16, p, s, c16, n, k, group_size=128, workspace=None)
     torch.cuda.synchronize()
     assert torch.all(c16 == 0)
-
-
-@pytest.mark.parametrize("group", [32, 128])
-@pytest.mark.parametrize("m", [1, 2, 3, 8])
-def test_fused_prologues(m, group):
-    """SwiGLU and RMSNorm folded into the GEMM's activation staging give what the separate passes
-    followed by the plain GEMM give: the same bits for SwiGLU (same formula, same plan), and for
-    RMSNorm the same up to the rare FP16 flip of a normalised activation (the sum of squares is
-    taken in another order)."""
-    import ctypes as C
-    lib = _lib.lib()
-    k, n = 2176, 1304
-    _, packed, scales = _quantised(k, n, group, 61)
-    pd, sd = _to_dev(packed), _to_dev(scales.view(np.float16))
-    ws = q.Workspace(1 << 24)
-    stream = torch.cuda.current_stream().cuda_stream
-    gen = torch.Generator(device=DEV).manual_seed(9)
-
-    def gemm(a, lda, a_dtype, a_op=0, gamma=None):
-        c = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
-        args = _lib.GemmArgs(M=m, N=n, K=k, group_size=group, a_dtype=a_dtype, c_dtype=_lib.TWM_F32, a=a.data_ptr(), lda=lda,
-                             packed=pd.data_ptr(), scales=sd.data_ptr(), c=c.data_ptr(), ldc=n, workspace=ws.ptr,
-                             workspace_bytes=ws.nbytes, kernel_override=_lib.TWM_KERNEL_MMA, a_op=a_op,
-                             a_gamma=gamma.data_ptr() if gamma is not None else None, a_eps=1e-6)
-        _lib.check(lib.twm_gemm_w4a16(C.byref(args), stream), "twm_gemm_w4a16")
-        torch.cuda.synchronize()
-        return c
-
-    # SwiGLU: [gate | up] -> act, then down
-    gate_up = torch.randn((m, 2 * k), generator=gen, device=DEV).half()
-    act = torch.empty((m, k), dtype=torch.float16, device=DEV)
-    _lib.check(lib.twm_silu_mul(act.data_ptr(), gate_up.data_ptr(), m, k, 0, stream), "twm_silu_mul")
-    ref = gemm(act, k, _lib.TWM_F16)
-    got = gemm(gate_up, 2 * k, _lib.TWM_F16, a_op=_lib.TWM_A_SILU_MUL)
-    assert torch.equal(got, ref)
-    gf, uf = gate_up[:, :k].float().cpu().numpy(), gate_up[:, k:].float().cpu().numpy()
-    act_np = (gf / (1.0 + np.exp(-gf)) * uf).astype(np.float16).astype(np.float32)
-    assert rel_err_floored(got.cpu().numpy(), oracle.w4a16_f64(act_np, packed, scales, m, n, k, group)) < TOL_TC_F32
-
-    # RMSNorm: FP32 residual row -> normalised FP16, then the projection
-    x = torch.randn((m, k), generator=gen, device=DEV) * 3.0
-    gamma = torch.rand(k, generator=gen, device=DEV) + 0.5
-    normed = torch.empty((m, k), dtype=torch.float16, device=DEV)
-    _lib.check(lib.twm_rmsnorm(normed.data_ptr(), x.data_ptr(), gamma.data_ptr(), m, k, 1e-6, 0, stream), "twm_rmsnorm")
-    ref = gemm(normed, k, _lib.TWM_F16)
-    got = gemm(x, k, _lib.TWM_F32, a_op=_lib.TWM_A_RMSNORM, gamma=gamma)
-    rms = float(ref.pow(2).mean().sqrt())
-    assert float((got - ref).abs().max()) < 2e-3 * rms
-    assert float((got != ref).float().mean()) < 0.5           # most outputs see no flipped activation at all
-    assert q.device_error() == 0
-    # the prologues are the streaming MMA kernel's: other kernels refuse them
-    bad = _lib.GemmArgs(M=m, N=n, K=k, group_size=group, a_dtype=_lib.TWM_F16, c_dtype=_lib.TWM_F32, a=gate_up.data_ptr(),
-                        lda=2 * k, packed=pd.data_ptr(), scales=sd.data_ptr(), c=ref.data_ptr(), ldc=n, workspace=ws.ptr,
-                        workspace_bytes=ws.nbytes, kernel_override=_lib.TWM_KERNEL_TC, a_op=_lib.TWM_A_SILU_MUL)
-    assert lib.twm_gemm_w4a16(C.byref(bad), stream) == _lib.TWM_EINVAL
