@@ -151,13 +151,13 @@ def run_ours(args):
     stream = torch.cuda.Stream(device)
     flags = _lib.TWM_FLAG_PDL        # weights are constants: let each GEMM prefetch them early
 
-    def enqueue_all():
+    def enqueue_all(extra_flags=0):
         ao = co = 0
         for layer in range(LAYERS):
             for pid, (_, k, n) in enumerate(LAYER_GEMMS):
                 p, s = weights[layer][pid]
                 q.gemm_tw_marlin_m1(dev_a[ao:ao + k], p, s, dev_c[co:co + n], n, k, group_size=GROUP,
-                                    workspace=ws, flags=flags)
+                                    workspace=ws, flags=flags | extra_flags)
                 ao += k
                 co += n
 
@@ -208,6 +208,31 @@ def run_ours(args):
             t = torch.tensor([e2e_ms], device=device)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             e2e_ms = float(t.item())
+    # Diagnostic, not the headline: the same 112 GEMMs (each has its own activation and output
+    # slice, so they ARE independent) launched with TWM_FLAG_INDEPENDENT, i.e. without the wait
+    # for the launch before that a decode step needs.  The difference to `value` is what the
+    # dependency between consecutive launches costs.
+    independent = None
+    if rank == 0:
+        with torch.cuda.stream(stream):
+            ref_c = dev_c.clone()
+            dev_c.zero_()
+            graph_i = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph_i, stream=stream):
+                enqueue_all(_lib.TWM_FLAG_INDEPENDENT)
+            for _ in range(args.warmup):
+                graph_i.replay()
+            torch.cuda.synchronize()
+            same = bool(torch.equal(dev_c, ref_c))
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g0.record(stream)
+            for _ in range(args.steps):
+                graph_i.replay()
+            g1.record(stream)
+            torch.cuda.synchronize()
+            ind_ms = g0.elapsed_time(g1) / args.steps
+        independent = {"ms_per_step": round(ind_ms, 4), "same_bits_as_dependent_run": same}
+        del graph_i
     err = q.device_error(stream)
     if err:
         raise RuntimeError(f"device error word {err:#x}")
@@ -246,6 +271,11 @@ def run_ours(args):
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks.summary(),
     }
+    if independent is not None:
+        ind_gbs = step_bytes / (independent["ms_per_step"] * 1e-3) / 1e9
+        independent.update({"gbs": round(ind_gbs, 1), "hbm_frac": round(ind_gbs / peak, 4),
+                            "note": "same GEMM set without the wait for the preceding launch (TWM_FLAG_INDEPENDENT); diagnostic"})
+        line["independent_launches"] = independent
     if decode is not None:
         line["decode"] = decode
     if sweep is not None:

@@ -61,7 +61,13 @@ enum {
      * workspace or `c`.  Set it when the weights are constants (the decode
      * loop); leave it clear when the preceding kernel writes packed/scales. */
     TWM_FLAG_PDL = 1,
-    TWM_FLAG_ACCUMULATE = 2 /* c += result instead of c = result (residual add fused in the epilogue) */
+    TWM_FLAG_ACCUMULATE = 2, /* c += result instead of c = result (residual add fused in the epilogue) */
+    /* With TWM_FLAG_PDL: the caller asserts that the kernel launched before this one on the stream
+     * neither writes this call's a nor reads or writes its c.  The launch then does not wait for that
+     * kernel at all, and the two overlap CTA by CTA.  Honoured by the streaming MMA kernel when its
+     * plan needs no workspace (M <= 2); ignored (the launch waits) otherwise.  A decode step has no
+     * such pair of GEMMs; the flag exists to measure what the dependency between launches costs. */
+    TWM_FLAG_INDEPENDENT = 4
 };
 
 /* Receive buffers of a tensor-parallel group for the one-shot all-reduce that is fused into

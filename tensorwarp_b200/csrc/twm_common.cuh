@@ -217,6 +217,7 @@ struct GemmParams {
     int blocks_per_split;
     int cluster_reduce;          // 1: the K slices of a tile form a thread-block cluster and add up in its leader's shared memory
     int accumulate;
+    int no_wait;                 // the caller vouches that nothing this launch touches depends on the launch before it
     const uint32_t* packed_offsets;
     const uint32_t* scales_offsets;
     int expert_idx;

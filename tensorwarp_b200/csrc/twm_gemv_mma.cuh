@@ -206,7 +206,7 @@ gemv_kernel(const __grid_constant__ GemmParams p)
         // group, row) are consecutive: the group's sum of activations is then a
         // fixed-order warp-shuffle reduction.  K slices start and end on group
         // boundaries (the host plan sees to that).
-        pdl_wait_prior_grids();
+        if (!p.no_wait) pdl_wait_prior_grids();
         const __half* A = reinterpret_cast<const __half*>(p.a);
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(A) & 15) == 0) && ((p.lda & 7) == 0);
         constexpr int PF = 8;

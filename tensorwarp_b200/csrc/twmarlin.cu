@@ -602,6 +602,8 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
         p.splits = pl.splits; p.blocks_per_split = pl.blocks_per_split;
         p.cluster_reduce = (pl.cluster_reduce && rows <= twm::mma::CLUSTER_ROWS) ? 1 : 0;
         p.accumulate = (a->flags & TWM_FLAG_ACCUMULATE) ? 1 : 0;
+        p.no_wait = ((a->flags & TWM_FLAG_INDEPENDENT) && (a->flags & TWM_FLAG_PDL) && kernel == TWM_KERNEL_MMA &&
+                     pl.workspace_bytes == 0 && !p.accumulate && a->packed_offsets == nullptr && !a->comm) ? 1 : 0;
         p.packed_offsets = a->packed_offsets; p.scales_offsets = a->scales_offsets; p.expert_idx = a->expert_idx;
         if (a->comm) {
             p.n_peers = a->comm->n_ranks; p.peer_rank = a->comm->rank; p.peer_slot_elems = a->comm->slot_elems;
