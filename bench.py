@@ -238,10 +238,13 @@ def run_ours(args):
         raise RuntimeError(f"device error word {err:#x}")
     decode = None
     sweep = None
+    config0 = None
     if not args.no_decode and rank == 0:
         del weights, graph
         torch.cuda.empty_cache()
         sweep = m_sweep(torch, q, device)
+        torch.cuda.empty_cache()
+        config0 = config0_gemv(torch, q, device)
         torch.cuda.empty_cache()
         decode = decode_tok_s(torch, device)
 
@@ -280,12 +283,55 @@ def run_ours(args):
         line["decode"] = decode
     if sweep is not None:
         line["m_sweep"] = sweep
+    if config0 is not None:
+        line["config0"] = config0
     if rank == 0:
         if not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(target_seconds=12.0)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def config0_gemv(torch, q, device):
+    """configs[0]: the Qwen2-0.5B gate+up GEMV (M=1, K=896, N=9728, G=128, FP16), 64 distinct weight
+    sets per graph (279 MB, larger than L2), programmatic dependent launch."""
+    from tensorwarp_b200 import _lib
+    k, n, copies = 896, 9728, 64
+    peak, _ = measured_peak_gbs()
+    ws = []
+    for i in range(copies):
+        w = torch.randn((k, n), generator=torch.Generator(device=device).manual_seed(300 + i), device=device) * 0.02
+        ws.append(q.quantize_f32_to_tw_marlin(w, k, n, GROUP))
+        del w
+    a = torch.randn((1, k), generator=torch.Generator(device=device).manual_seed(0), device=device).half()
+    c = torch.empty((1, n), dtype=torch.float16, device=device)
+    wsb = q.Workspace(q.workspace_bytes(1, n, k, GROUP), device)
+    stream = torch.cuda.Stream(device)
+
+    def enqueue():
+        for p_, s_ in ws:
+            q.gemm_tw_marlin(a, p_, s_, c, 1, n, k, group_size=GROUP, workspace=wsb, flags=_lib.TWM_FLAG_PDL)
+
+    with torch.cuda.stream(stream):
+        enqueue()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            enqueue()
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(10):
+            graph.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (10 * copies)
+    b = algorithmic_bytes(1, n, k, GROUP)
+    return {"workload": "configs[0]: M=1, K=896, N=9728, G=128, FP16", "us": round(us, 2),
+            "gbs": round(b / us / 1e3, 1), "hbm_frac": round(b / us / 1e3 / peak, 3)}
 
 
 def m_sweep(torch, q, device):

@@ -51,7 +51,13 @@ constexpr int CONSUMERS = CONSUMER_WARPS * 32;
 constexpr int THREADS = CONSUMERS + 64;      // + producer warp + stager warp
 constexpr int B_BUF_BYTES = 4096;            // staged activations per chunk buffer
 constexpr int ASUM_GROUPS = 64;              // scale groups per chunk, at most
-constexpr int MAX_CLUSTER = 16;              // K slices that can add up through distributed shared memory
+#ifndef TWM_MMA_MAX_CLUSTER
+#define TWM_MMA_MAX_CLUSTER 16
+#endif
+#ifndef TWM_MMA_MIN_CTAS
+#define TWM_MMA_MIN_CTAS 2
+#endif
+constexpr int MAX_CLUSTER = TWM_MMA_MAX_CLUSTER;   // K slices that can add up through distributed shared memory
 constexpr int CLUSTER_ROWS = 2;              // ... for up to this many activation rows
 
 struct Smem {
@@ -99,7 +105,7 @@ __device__ __forceinline__ uint16_t lds16_at(uint32_t addr) {
 
 // MP = activation rows staged (power of two >= M, <= 8); GSHIFT = log2(32-blocks per scale group)
 template <int MP, int GSHIFT>
-__global__ void __launch_bounds__(THREADS, 2)
+__global__ void __launch_bounds__(THREADS, TWM_MMA_MIN_CTAS)
 gemv_kernel(const __grid_constant__ GemmParams p)
 {
     extern __shared__ __align__(128) uint8_t smem_raw[];
