@@ -57,19 +57,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait.  Returns false when the limit ran out; the caller must then
 // stop using the data that barrier guards.  `abort_flag` (shared memory) lets
 // one expired wait shorten every later wait in the CTA.
-// A waiter that is not on the critical path: sleeps from the first miss, so that its polling does
-// not take issue slots from the warps that are (same bound, same abort rule).
-__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < (1u << 22); ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        __nanosleep(i > 4096 ? 256 : 100);
-        if ((i & 63) == 63 && *abort_flag) break;
-    }
-    *abort_flag = 1;
-    atomicOr(&g_error_word, 1u);
-    return false;
-}
-
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
                                                   volatile int* abort_flag) {
     // ~2^22 polls with back-off: of the order of a second, far beyond any real

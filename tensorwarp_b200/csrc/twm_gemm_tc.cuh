@@ -171,12 +171,6 @@ __device__ __forceinline__ bool wait_uniform(uint64_t* bar, uint32_t parity, vol
     const bool got = mbar_wait_bounded(bar, parity, abort_flag);
     return __all_sync(0xffffffffu, got);
 }
-// the same for waits that have slack (they sleep between polls: see mbar_wait_relaxed)
-__device__ __forceinline__ bool wait_uniform_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    const bool got = mbar_wait_relaxed(bar, parity, abort_flag);
-    return __all_sync(0xffffffffu, got);
-}
-
 // NB = MMA N (activation rows padded to 16 or 32)
 template <int NB>
 __global__ void __launch_bounds__(Cfg<NB>::THREADS, Cfg<NB>::CTAS_PER_SM)
@@ -290,7 +284,7 @@ gemm_kernel(const __grid_constant__ GemmParams p)
                 const bool free_w = mbar_try_wait(&sm.w_empty[wst % WSTAGES], ((wst / WSTAGES) - 1) & 1);
                 if (__all_sync(0xffffffffu, free_w)) { issue_stage(wst); ++wst; progress = true; }
             }
-            if (progress) { idle = 0; } else { ++idle; __nanosleep(idle > 4096 ? 256 : 100); if (*abort_flag) break; }
+            if (progress) { idle = 0; } else { ++idle; if (idle > 64) __nanosleep(64); if (*abort_flag) break; }
         }
         if (bst < n_wstages || wst < n_wstages) { *abort_flag = 1; atomicOr(&g_error_word, 1u); }
     } else if (warp == WARP_MMA) {
@@ -408,7 +402,7 @@ gemm_kernel(const __grid_constant__ GemmParams p)
             if (st >= ASLOTS) {        // the MMAs that read this slot's previous contents are done
                 uint64_t* bar = lean ? &sm.done[(st - ASLOTS) & 3] : &sm.ab_empty[aslot];
                 const uint32_t par = lean ? (((st - ASLOTS) >> 2) & 1) : (((st / ASLOTS) - 1) & 1);
-                if (!wait_uniform_relaxed(bar, par, abort_flag)) break;
+                if (!wait_uniform(bar, par, abort_flag)) break;
                 tc_fence_after();
             }
             PROF_END(t2, 2);
@@ -486,7 +480,7 @@ gemm_kernel(const __grid_constant__ GemmParams p)
             {
                 uint64_t* bar = lean ? &sm.done[gq & 3] : &sm.d_full[db];
                 const uint32_t par = lean ? ((gq >> 2) & 1) : ((gq >> 1) & 1);
-                if (!wait_uniform_relaxed(bar, par, abort_flag)) { ok = false; break; }
+                if (!wait_uniform(bar, par, abort_flag)) { ok = false; break; }
             }
             PROF_END(t0, 0);
             tc_fence_after();

@@ -430,3 +430,26 @@ def test_errors_are_statuses():
     q.gemm_tw_marlin_m1(a16, p, s, c16, n, k, group_size=128, workspace=None)
     torch.cuda.synchronize()
     assert torch.all(c16 == 0)
+
+
+def test_independent_launch_flag_same_bits():
+    """TWM_FLAG_INDEPENDENT (no wait for the preceding launch): four GEMMs with their own inputs
+    and outputs, launched back to back, give the bits of the ordinary launches."""
+    shapes = [(3584, 4608), (3584, 3584), (1024, 9728), (2048, 1024)]
+    group = 128
+    ws = q.Workspace(1 << 24)
+    mats, outs = [], {}
+    for i, (k, n) in enumerate(shapes):
+        _, packed, scales = _quantised(k, n, group, 80 + i)
+        mats.append((_to_dev(packed), _to_dev(scales.view(np.float16)), _to_dev(seeded_activations(1, k, i), torch.float16)))
+    for flags in (0, _lib.TWM_FLAG_PDL, _lib.TWM_FLAG_PDL | _lib.TWM_FLAG_INDEPENDENT):
+        cs = [torch.full((1, n), float("nan"), dtype=torch.float16, device=DEV) for _, n in shapes]
+        for rep in range(3):
+            for (k, n), (p, s, a), c in zip(shapes, mats, cs):
+                q.gemm_tw_marlin(a, p, s, c, 1, n, k, group_size=group, workspace=ws, flags=flags)
+        torch.cuda.synchronize()
+        outs[flags] = [c.clone() for c in cs]
+    for flags in outs:
+        for c, ref in zip(outs[flags], outs[0]):
+            assert torch.equal(c, ref)
+    assert q.device_error() == 0
