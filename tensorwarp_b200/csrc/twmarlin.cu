@@ -262,6 +262,7 @@ int resolve_kernel(const twm_gemm_args* a)
                              a->splits_override);
     // five to eight rows: the tcgen05 kernel when the caller's workspace holds its pre-pass
     // output, else the streaming kernel (which needs less or none)
+    if (kernel == TWM_KERNEL_TC && a->M <= 8 && a->comm) kernel = TWM_KERNEL_MMA;    // the peer push lives in the streaming kernels
     if (kernel == TWM_KERNEL_TC && a->M <= 8) {
         twm_plan_t pl;
         if (twm_plan(a->M, a->N, a->K, a->group_size, kDefaultSms, a->splits_override, TWM_KERNEL_TC, &pl) != TWM_OK ||
