@@ -9,6 +9,7 @@ import torch
 import oracle
 from oracle import decode_ref
 from tensorwarp_b200 import generate as gen
+from tensorwarp_b200 import _lib
 from tensorwarp_b200 import quantize as q
 
 pytestmark = pytest.mark.gpu
@@ -126,3 +127,47 @@ def test_without_programmatic_launch_same_tokens():
         eng.prefill_random_kv(130, seed=2)
         outs.append(eng.generate_tw_marlin_graph(3, 8))
     assert outs[0] == outs[1]
+
+
+@pytest.mark.parametrize("length", [1, 31, 500, 2049])
+@pytest.mark.parametrize("heads,kv_heads,rows", [(28, 4, 1), (8, 8, 2), (16, 2, 3)])
+def test_attention_against_float64(length, heads, kv_heads, rows):
+    """twm_attn_decode (split-KV chunk kernel + merge kernel) with two cache capacities (the grid
+    covers the capacity, the length comes from the device) against a float64 soft-max attention
+    on the same cache contents."""
+    lib = _lib.lib()
+    hd = 128
+    g = torch.Generator(device="cuda").manual_seed(length * 31 + heads)
+    qv = torch.randn((rows, heads * hd), generator=g, device="cuda").half()
+    kv_dim = kv_heads * hd
+    kc = torch.randn((rows, length, kv_dim), generator=g, device="cuda").half()
+    vc = torch.randn((rows, length, kv_dim), generator=g, device="cuda").half()
+    len_buf = torch.tensor([length], dtype=torch.int32, device="cuda")
+    outs = []
+    for max_seq in (max(length, 2100), 9000):
+        k_cache = torch.zeros((rows, max_seq, kv_dim), dtype=torch.float16, device="cuda")
+        v_cache = torch.zeros_like(k_cache)
+        k_cache[:, :length] = kc
+        v_cache[:, :length] = vc
+        out = torch.full((rows, heads * hd), float("nan"), dtype=torch.float16, device="cuda")
+        scratch = torch.zeros(lib.twm_attn_scratch_bytes(rows, heads, hd, max_seq), dtype=torch.uint8, device="cuda")
+        _lib.check(lib.twm_attn_decode(out.data_ptr(), qv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), rows, heads,
+                                       kv_heads, hd, len_buf.data_ptr(), max_seq, scratch.data_ptr(), scratch.numel(), 0,
+                                       torch.cuda.current_stream().cuda_stream), "twm_attn_decode")
+        torch.cuda.synchronize()
+        outs.append(out.float().cpu().numpy())
+    qn = qv.float().cpu().numpy().astype(np.float64).reshape(rows, heads, hd)
+    kn = kc.float().cpu().numpy().astype(np.float64).reshape(rows, length, kv_heads, hd)
+    vn = vc.float().cpu().numpy().astype(np.float64).reshape(rows, length, kv_heads, hd)
+    group = heads // kv_heads
+    ref = np.zeros((rows, heads, hd))
+    for r in range(rows):
+        for h in range(heads):
+            s = kn[r, :, h // group] @ qn[r, h] / np.sqrt(hd)
+            p = np.exp(s - s.max())
+            ref[r, h] = (p / p.sum()) @ vn[r, :, h // group]
+    ref = ref.reshape(rows, heads * hd)
+    for o in outs:
+        assert np.max(np.abs(o - ref)) < 4e-3          # FP16 output of values of order one
+    assert np.max(np.abs(outs[0] - outs[1])) < 2e-3
+    assert q.device_error() == 0
