@@ -453,3 +453,17 @@ def test_independent_launch_flag_same_bits():
         for c, ref in zip(outs[flags], outs[0]):
             assert torch.equal(c, ref)
     assert q.device_error() == 0
+
+
+@pytest.mark.parametrize("k,n", [(8192, 1280), (1024, 8192), (8192, 7168), (3584, 8192), (8192, 2560), (2048, 8192)])
+def test_tensor_parallel_shard_shapes(k, n):
+    """The per-rank GEMM shapes of the 70B-shaped stack at tp = 8 and tp = 4 (M = 1, G = 128): the plan
+    reaches its largest cluster (16 K slices) on the tp = 8 QKV shard."""
+    group = 128
+    _, packed, scales = _quantised(k, n, group, 90 + (k + n) % 7)
+    a = seeded_activations(1, k, 4)
+    y = _run_gemm(a, packed, scales, 1, n, k, group, torch.float16, torch.float32, flags=_lib.TWM_FLAG_PDL)
+    assert rel_err_floored(y, oracle.w4a16_f64(a, packed, scales, 1, n, k, group)) < TOL_TC_F32
+    if (k, n) == (8192, 1280):
+        p = q.plan(1, n, k, group)
+        assert p.splits == 16 and p.cluster_reduce == 1
