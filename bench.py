@@ -391,38 +391,49 @@ def m_sweep(torch, q, device):
 
 def decode_tok_s(torch, device, new_tokens: int = 64, kv_len: int = 2048):
     """configs[3]: full Qwen2-7B-shaped Q4 decode step (28 layers, FP16 KV prefilled to 2048 tokens of
-    N(0,1), FP16 LM head, greedy) replayed as one CUDA graph; the token never leaves the device."""
+    N(0,1), FP16 LM head, greedy) replayed as one CUDA graph; the token never leaves the device.
+    Also timed, as a side figure: the same step with the LM head as a TW-Marlin GEMM (the reference's
+    forward_lm_head_tw_marlin option)."""
     from tensorwarp_b200 import generate as gen
     cfg = gen.QWEN2_7B
     model = gen.Q4Model(cfg, device=device, seed=0)
-    eng = gen.QuantizedGenerationEngine(model)
-    eng.prefill_random_kv(kv_len, seed=2)
     first = int(torch.randint(0, cfg.vocab, (1,), generator=torch.Generator().manual_seed(3)).item())
-    eng.capture()
-    eng.set_token(first)
-    for _ in range(3):
-        eng.replay()
-    torch.cuda.synchronize()
-    eng.prefill_random_kv(kv_len, seed=2)          # back to position 2048
-    eng.buf.step.zero_()
-    eng.set_token(first)
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(eng.stream):
-        e0.record(eng.stream)
-        for _ in range(new_tokens):
+
+    def run(q4_lm_head):
+        eng = gen.QuantizedGenerationEngine(model, q4_lm_head=q4_lm_head)
+        eng.prefill_random_kv(kv_len, seed=2)
+        eng.capture()
+        eng.set_token(first)
+        for _ in range(3):
             eng.replay()
-        e1.record(eng.stream)
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
-    toks = eng.buf.history[:new_tokens].tolist()
+        torch.cuda.synchronize()
+        eng.prefill_random_kv(kv_len, seed=2)          # back to position 2048
+        eng.buf.step.zero_()
+        eng.set_token(first)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(eng.stream):
+            e0.record(eng.stream)
+            for _ in range(new_tokens):
+                eng.replay()
+            e1.record(eng.stream)
+        torch.cuda.synchronize()
+        toks = eng.buf.history[:new_tokens].tolist()
+        return e0.elapsed_time(e1), eng.launches_per_step, bool(all(0 <= t < cfg.vocab for t in toks))
+
+    ms, launches, in_vocab = run(False)
     q4_bytes = cfg.layers * layer_bytes(1)
-    step_bytes = q4_bytes + cfg.vocab * cfg.hidden * 2 + cfg.layers * 2 * (kv_len + new_tokens // 2) * cfg.kv_dim * 2
-    return {"tok_s": round(new_tokens / (ms * 1e-3), 1), "ms_per_token": round(ms / new_tokens, 4),
-            "workload": f"configs[3]: Qwen2-7B-shaped Q4 decode, KV {kv_len} FP16, {new_tokens} greedy tokens, one CUDA graph per token",
-            "launches_per_token": eng.launches_per_step, "bytes_per_token": int(step_bytes),
-            "hbm_gbs": round(step_bytes / (ms / new_tokens * 1e-3) / 1e9, 1),
-            "tokens_in_vocab": bool(all(0 <= t < cfg.vocab for t in toks))}
+    kv_bytes = cfg.layers * 2 * (kv_len + new_tokens // 2) * cfg.kv_dim * 2
+    step_bytes = q4_bytes + cfg.vocab * cfg.hidden * 2 + kv_bytes
+    out = {"tok_s": round(new_tokens / (ms * 1e-3), 1), "ms_per_token": round(ms / new_tokens, 4),
+           "workload": f"configs[3]: Qwen2-7B-shaped Q4 decode, KV {kv_len} FP16, {new_tokens} greedy tokens, one CUDA graph per token",
+           "launches_per_token": launches, "bytes_per_token": int(step_bytes),
+           "hbm_gbs": round(step_bytes / (ms / new_tokens * 1e-3) / 1e9, 1), "tokens_in_vocab": in_vocab}
+    ms4, _, in_vocab4 = run(True)
+    step_bytes4 = q4_bytes + algorithmic_bytes(1, cfg.vocab, cfg.hidden, GROUP, 2, 4) + kv_bytes
+    out["q4_lm_head"] = {"tok_s": round(new_tokens / (ms4 * 1e-3), 1), "ms_per_token": round(ms4 / new_tokens, 4),
+                         "bytes_per_token": int(step_bytes4), "tokens_in_vocab": in_vocab4}
+    return out
 
 
 # ------------------------------------------------------------- tensor parallel --

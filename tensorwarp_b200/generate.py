@@ -92,8 +92,19 @@ class Q4Model:
         self.embed = (torch.randn((cfg.vocab, cfg.hidden), generator=gen, device=self.device) * 0.02).half()
         gen = torch.Generator(device=self.device).manual_seed(seed + 900002)
         self.lm_head = (torch.randn((cfg.vocab, cfg.hidden), generator=gen, device=self.device) * 0.02).half()
+        self.lm_head_q4 = None          # (packed, scales) of the same matrix, made on demand
         self.final_norm = torch.ones(cfg.hidden, device=self.device)
         torch.cuda.synchronize(self.device)
+
+    def quantize_lm_head(self):
+        """The LM head as a TW-Marlin tensor ([vocab, hidden] is already the [N, K] form the quantiser
+        takes), for forward_lm_head_tw_marlin (generate.rs:1750-1761)."""
+        if self.lm_head_q4 is None:
+            cfg = self.cfg
+            self.lm_head_q4 = q.quantize_f32_to_tw_marlin(self.lm_head.float().contiguous(), cfg.hidden, cfg.vocab,
+                                                          cfg.group_size, w_is_nk=True)
+            torch.cuda.synchronize(self.device)
+        return self.lm_head_q4
 
 
 class Q4DecodeBuffers:
@@ -130,8 +141,13 @@ class Q4DecodeBuffers:
 class QuantizedGenerationEngine:
     """Decode engine on TW-Marlin weights (generate.rs:1191-2547, Q4 + marlin + graph path)."""
 
-    def __init__(self, model: Q4Model, use_pdl: bool = True):
+    def __init__(self, model: Q4Model, use_pdl: bool = True, q4_lm_head: bool = False):
         self.model = model
+        # the reference's graph path keeps the LM head outside the graph in FP32/FP16 (generate.rs:2530-2534)
+        # and has a Q4 one as an option (forward_lm_head_tw_marlin, generate.rs:1750-1761): same here
+        self.q4_lm_head = q4_lm_head
+        if q4_lm_head:
+            model.quantize_lm_head()
         self.cfg = model.cfg
         self.buf = Q4DecodeBuffers(model.cfg, model.device)
         self.flags = _lib.TWM_FLAG_PDL if use_pdl else 0
@@ -196,8 +212,11 @@ class QuantizedGenerationEngine:
             gemm(b.act, lw.w_down, b.x, cfg.hidden, cfg.ffn, accumulate=True); n += 1           # x += down(act)
         check(lib.twm_rmsnorm(b.normed.data_ptr(), b.x.data_ptr(), self.model.final_norm.data_ptr(), 1, cfg.hidden,
                               cfg.eps, fl, stream_ptr), "twm_rmsnorm"); n += 1
-        check(lib.twm_lm_head(b.logits.data_ptr(), b.normed.data_ptr(), self.model.lm_head.data_ptr(), cfg.hidden,
-                              cfg.vocab, fl, stream_ptr), "twm_lm_head"); n += 1
+        if self.q4_lm_head:
+            gemm(b.normed, self.model.lm_head_q4, b.logits, cfg.vocab, cfg.hidden); n += 1
+        else:
+            check(lib.twm_lm_head(b.logits.data_ptr(), b.normed.data_ptr(), self.model.lm_head.data_ptr(), cfg.hidden,
+                                  cfg.vocab, fl, stream_ptr), "twm_lm_head"); n += 1
         check(lib.twm_argmax_advance(b.token.data_ptr(), b.history.data_ptr(), b.pos.data_ptr(),
                                      b.cache_len.data_ptr(), b.step.data_ptr(), b.logits.data_ptr(), cfg.vocab,
                                      b.argmax_scratch.data_ptr(), b.argmax_scratch.numel(), fl, stream_ptr),

@@ -171,3 +171,32 @@ def test_attention_against_float64(length, heads, kv_heads, rows):
         assert np.max(np.abs(o - ref)) < 4e-3          # FP16 output of values of order one
     assert np.max(np.abs(outs[0] - outs[1])) < 2e-3
     assert q.device_error() == 0
+
+
+def test_q4_lm_head_option():
+    """The LM head as a TW-Marlin GEMM inside the step (forward_lm_head_tw_marlin,
+    generate.rs:1750-1761): logits equal the oracle's W4A16 product of the step's final normed
+    activations, and the rest of the step is the one the FP16 head sees."""
+    cfg = GQA
+    model = gen.Q4Model(cfg, seed=11)
+    engs = []
+    for q4 in (False, True):
+        eng = gen.QuantizedGenerationEngine(model, q4_lm_head=q4)
+        eng.prefill_random_kv(70, seed=2)
+        eng.set_token(5)
+        eng.step_eager()
+        torch.cuda.synchronize()
+        engs.append(eng)
+    assert torch.equal(engs[0].buf.normed, engs[1].buf.normed)
+    packed, scales = model.lm_head_q4
+    normed = engs[1].buf.normed.float().cpu().numpy()[None]
+    ref = oracle.w4a16_f64(normed, packed.cpu().numpy(), scales.cpu().numpy().view(np.uint16), 1, cfg.vocab, cfg.hidden,
+                           cfg.group_size)
+    got = engs[1].buf.logits.cpu().numpy()[None]
+    rms = float(np.sqrt(np.mean(ref ** 2)))
+    assert float(np.max(np.abs(got - ref))) < 1e-3 * rms
+    # the quantised head stays close to the FP16 one (4-bit weights: a few per cent of the logit RMS)
+    fp16 = engs[0].buf.logits.cpu().numpy()[None]
+    assert float(np.sqrt(np.mean((got - fp16) ** 2))) < 0.2 * float(np.sqrt(np.mean(fp16 ** 2)))
+    assert engs[0].launches_per_step == engs[1].launches_per_step
+    assert q.device_error() == 0
