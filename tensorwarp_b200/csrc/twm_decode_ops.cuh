@@ -284,16 +284,23 @@ rope_append_kernel(__half* __restrict__ q_out, __half* __restrict__ k_cache, __h
     }
 }
 
-// Split-KV decode attention, pass 1.  CTA = (chunk of ATT_CHUNK tokens, kv head); its 8 warps share
-// the kv head's K/V rows between all q heads of the group (GQA), so the cache is read once.
-// Online soft-max per warp, merged through shared memory; writes (max, sum, unnormalised o[128])
-// per (q head, chunk).  The sequence length is read from the device (len_buf[0]), the grid
-// covers max_seq.  Reference: warp_flash_decode_chunk_dl, crates/kernels/src/kv_cache.rs:951-1076.
-constexpr int ATT_CHUNK = 32;       // tokens per CTA: 8 warps x 4 tokens, every K/V row requested before the first use
+// Split-KV decode attention, pass 1.  CTA = (chunk of ATT_CHUNK = 32 tokens, kv head); warp h of the
+// CTA takes q head h of the group (GQA: the kv head's rows come from L1 for all but the first warp).
+//   scores: one token per LANE, no cross-lane reduction per score: the lane walks its token's K
+//           row (all 16 loads issued before the first use) against q_h in shared memory;
+//   soft-max statistics: one warp max and one warp sum for the 32 tokens;
+//   P.V: lanes own 4 of the 128 dims; the 32 probabilities go round by shuffle; V rows are read
+//        coalesced, sixteen in flight.
+// About 16 instructions per (token, head); the earlier one-token-per-warp loop with a shuffle
+// reduction per score needed 87 (5.0 M warp instructions per call at 2049 tokens x 28 heads) and
+// was bound by instruction issue.  Writes (max, sum, unnormalised o[128]) per (q head, chunk).  The
+// sequence length is read from the device (len_buf[0]), the grid covers max_seq.  Reference:
+// warp_flash_decode_chunk_dl, crates/kernels/src/kv_cache.rs:951-1076.
+constexpr int ATT_CHUNK = 32;       // tokens per CTA = lanes of a warp
 constexpr int ATT_MAX_GROUP = 8;      // q heads per kv head, at most
 
 template <int HEAD_DIM>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(ATT_MAX_GROUP * 32)
 attn_chunk_kernel(float* __restrict__ part /* [heads][chunks][HEAD_DIM + 2] */, const __half* __restrict__ q,
                   const __half* __restrict__ k_cache, const __half* __restrict__ v_cache, int num_heads,
                   int num_kv_heads, const int* __restrict__ len_buf, int max_chunks, int max_seq)
@@ -309,98 +316,83 @@ attn_chunk_kernel(float* __restrict__ part /* [heads][chunks][HEAD_DIM + 2] */, 
         v_cache += row * (size_t)max_seq * num_kv_heads * HEAD_DIM;
         part += row * (size_t)num_heads * max_chunks * (HEAD_DIM + 2);
     }
-    const int len = len_buf[0];
+    const int len = min(len_buf[0], max_seq);            // never past the cache
     const int t0 = chunk * ATT_CHUNK;
-    const int group = num_heads / num_kv_heads;
+    const int group = num_heads / num_kv_heads;          // = warps of this CTA (the host launches group x 32 threads)
     const int kv_dim = num_kv_heads * HEAD_DIM;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    __shared__ float s_m[8][ATT_MAX_GROUP], s_l[8][ATT_MAX_GROUP];
-    __shared__ float s_o[8][ATT_MAX_GROUP][HEAD_DIM];
+    const int h = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* dst = part + ((size_t)(kvh * group + h) * max_chunks + chunk) * (HEAD_DIM + 2);
     if (t0 >= len) {
         // empty chunk: mark as such so the merge ignores it
-        if (threadIdx.x < group) {
-            float* dst = part + ((size_t)(kvh * group + threadIdx.x) * max_chunks + chunk) * (HEAD_DIM + 2);
-            dst[HEAD_DIM] = -INFINITY; dst[HEAD_DIM + 1] = 0.0f;
-        }
+        if (lane == 0) { dst[HEAD_DIM] = -INFINITY; dst[HEAD_DIM + 1] = 0.0f; }
         return;
     }
-    const int t1 = min(len, t0 + ATT_CHUNK);
-    const float scale = rsqrtf((float)HEAD_DIM);
-    float qv[ATT_MAX_GROUP][4];
+    const int nt = min(ATT_CHUNK, len - t0);             // tokens of this chunk (CTA-uniform)
+    const bool valid = lane < nt;
+    __shared__ __align__(16) float q_s[ATT_MAX_GROUP][HEAD_DIM];
+    // every global load the warp needs until the scores are done, up front: its q row, this lane's
+    // whole K row, its 4 dims of the first sixteen V rows
+    const uint2 qr = *reinterpret_cast<const uint2*>(q + (size_t)(kvh * group + h) * HEAD_DIM + lane * 4);
+    uint4 kr[HEAD_DIM / 8];
+    {
+        const uint4* krow = reinterpret_cast<const uint4*>(k_cache + (size_t)(t0 + (valid ? lane : 0)) * kv_dim + kvh * HEAD_DIM);
 #pragma unroll
-    for (int h = 0; h < ATT_MAX_GROUP; ++h) {
-        if (h < group) {
-            const __half2* qp = reinterpret_cast<const __half2*>(q + (size_t)(kvh * group + h) * HEAD_DIM + lane * 4);
-            const float2 a = __half22float2(qp[0]), b = __half22float2(qp[1]);
-            qv[h][0] = a.x * scale; qv[h][1] = a.y * scale; qv[h][2] = b.x * scale; qv[h][3] = b.y * scale;
-        } else { qv[h][0] = qv[h][1] = qv[h][2] = qv[h][3] = 0.0f; }
+        for (int dc = 0; dc < HEAD_DIM / 8; ++dc) kr[dc] = krow[dc];
     }
-    float m[ATT_MAX_GROUP], l[ATT_MAX_GROUP], o[ATT_MAX_GROUP][4];
+    const __half* vbase = v_cache + (size_t)t0 * kv_dim + kvh * HEAD_DIM + lane * 4;
+    uint2 vr[16];
 #pragma unroll
-    for (int h = 0; h < ATT_MAX_GROUP; ++h) { m[h] = -INFINITY; l[h] = 0.0f; o[h][0] = o[h][1] = o[h][2] = o[h][3] = 0.0f; }
-    // this warp's tokens: t0 + warp, + 8, + 16, + 24; all loads first, then the arithmetic
-    constexpr int TPW = ATT_CHUNK / 8;
-    float2 kf[TPW][2], vf[TPW][2];
+    for (int j = 0; j < 16; ++j) vr[j] = (j < nt) ? *reinterpret_cast<const uint2*>(vbase + (size_t)j * kv_dim) : make_uint2(0, 0);
+    {
+        const float scale = rsqrtf((float)HEAD_DIM);
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&qr.x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&qr.y));
+        *reinterpret_cast<float4*>(&q_s[h][lane * 4]) = make_float4(a.x * scale, a.y * scale, b.x * scale, b.y * scale);
+    }
+    __syncwarp();
+    // ---- score of this lane's token ----
+    float sc = 0.0f;
 #pragma unroll
-    for (int j = 0; j < TPW; ++j) {
-        const int tk = t0 + warp + 8 * j;
-        if (tk < t1) {
-            const uint2 kr = *reinterpret_cast<const uint2*>(k_cache + (size_t)tk * kv_dim + kvh * HEAD_DIM + lane * 4);
-            const uint2 vr = *reinterpret_cast<const uint2*>(v_cache + (size_t)tk * kv_dim + kvh * HEAD_DIM + lane * 4);
-            kf[j][0] = __half22float2(*reinterpret_cast<const __half2*>(&kr.x));
-            kf[j][1] = __half22float2(*reinterpret_cast<const __half2*>(&kr.y));
-            vf[j][0] = __half22float2(*reinterpret_cast<const __half2*>(&vr.x));
-            vf[j][1] = __half22float2(*reinterpret_cast<const __half2*>(&vr.y));
-        } else {
-            kf[j][0] = kf[j][1] = vf[j][0] = vf[j][1] = make_float2(0.f, 0.f);
-        }
+    for (int dc = 0; dc < HEAD_DIM / 8; ++dc) {
+        const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kr[dc].x));
+        const float2 k1 = __half22float2(*reinterpret_cast<const __half2*>(&kr[dc].y));
+        const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&kr[dc].z));
+        const float2 k3 = __half22float2(*reinterpret_cast<const __half2*>(&kr[dc].w));
+        const float4 qa = *reinterpret_cast<const float4*>(&q_s[h][dc * 8]);
+        const float4 qb = *reinterpret_cast<const float4*>(&q_s[h][dc * 8 + 4]);
+        sc = fmaf(k0.x, qa.x, fmaf(k0.y, qa.y, fmaf(k1.x, qa.z, fmaf(k1.y, qa.w,
+             fmaf(k2.x, qb.x, fmaf(k2.y, qb.y, fmaf(k3.x, qb.z, fmaf(k3.y, qb.w, sc))))))));
+    }
+    // the second sixteen V rows are requested now (the K registers are free), used after the first sixteen
+    uint2 vr2[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+        vr2[j] = (16 + j < nt) ? *reinterpret_cast<const uint2*>(vbase + (size_t)(16 + j) * kv_dim) : make_uint2(0, 0);
+    // ---- soft-max statistics of the chunk ----
+    const float sv = valid ? sc : -INFINITY;
+    const float mw = warp_max(sv);
+    const float pr = valid ? __expf(sv - mw) : 0.0f;
+    const float lw = warp_sum(pr);
+    // ---- o[dims of this lane] = sum_t p[t] * v_t ----
+    float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const float pt = __shfl_sync(0xffffffffu, pr, j);              // 0 for tokens past the end
+        const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&vr[j].x));
+        const float2 v1 = __half22float2(*reinterpret_cast<const __half2*>(&vr[j].y));
+        o0 = fmaf(pt, v0.x, o0); o1 = fmaf(pt, v0.y, o1); o2 = fmaf(pt, v1.x, o2); o3 = fmaf(pt, v1.y, o3);
     }
 #pragma unroll
-    for (int j = 0; j < TPW; ++j) {
-        const int tk = t0 + warp + 8 * j;
-        if (tk < t1) {                                   // warp-uniform
-            const float2 k0 = kf[j][0], k1 = kf[j][1], v0 = vf[j][0], v1 = vf[j][1];
-#pragma unroll
-            for (int h = 0; h < ATT_MAX_GROUP; ++h) {
-                if (h < group) {
-                    float s = qv[h][0] * k0.x + qv[h][1] * k0.y + qv[h][2] * k1.x + qv[h][3] * k1.y;
-                    s = warp_sum(s);
-                    const float mn = fmaxf(m[h], s);
-                    const float corr = __expf(m[h] - mn), pexp = __expf(s - mn);
-                    l[h] = l[h] * corr + pexp;
-                    o[h][0] = o[h][0] * corr + pexp * v0.x; o[h][1] = o[h][1] * corr + pexp * v0.y;
-                    o[h][2] = o[h][2] * corr + pexp * v1.x; o[h][3] = o[h][3] * corr + pexp * v1.y;
-                    m[h] = mn;
-                }
-            }
-        }
+    for (int j = 0; j < 16; ++j) {
+        const float pt = __shfl_sync(0xffffffffu, pr, 16 + j);
+        const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&vr2[j].x));
+        const float2 v1 = __half22float2(*reinterpret_cast<const __half2*>(&vr2[j].y));
+        o0 = fmaf(pt, v0.x, o0); o1 = fmaf(pt, v0.y, o1); o2 = fmaf(pt, v1.x, o2); o3 = fmaf(pt, v1.y, o3);
     }
-#pragma unroll
-    for (int h = 0; h < ATT_MAX_GROUP; ++h) {
-        if (h < group) {
-            if (lane == 0) { s_m[warp][h] = m[h]; s_l[warp][h] = l[h]; }
-            s_o[warp][h][lane * 4 + 0] = o[h][0]; s_o[warp][h][lane * 4 + 1] = o[h][1];
-            s_o[warp][h][lane * 4 + 2] = o[h][2]; s_o[warp][h][lane * 4 + 3] = o[h][3];
-        }
-    }
-    __syncthreads();
-    // merge the 8 warps, fixed order; thread = (q head of the group, dim)
-    for (int idx = threadIdx.x; idx < group * HEAD_DIM; idx += blockDim.x) {
-        const int h = idx / HEAD_DIM, d = idx - h * HEAD_DIM;
-        float mm = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < 8; ++w) mm = fmaxf(mm, s_m[w][h]);
-        float ll = 0.0f, oo = 0.0f;
-#pragma unroll
-        for (int w = 0; w < 8; ++w) {
-            const float c = (s_m[w][h] == -INFINITY) ? 0.0f : __expf(s_m[w][h] - mm);
-            ll += s_l[w][h] * c;
-            oo += s_o[w][h][d] * c;
-        }
-        float* dst = part + ((size_t)(kvh * group + h) * max_chunks + chunk) * (HEAD_DIM + 2);
-        dst[d] = oo;
-        if (d == 0) { dst[HEAD_DIM] = mm; dst[HEAD_DIM + 1] = ll; }
-    }
+    // a partial is HEAD_DIM + 2 floats long, so its start is 8-byte aligned only: two float2 stores
+    *reinterpret_cast<float2*>(dst + lane * 4) = make_float2(o0, o1);
+    *reinterpret_cast<float2*>(dst + lane * 4 + 2) = make_float2(o2, o3);
+    if (lane == 0) { dst[HEAD_DIM] = mw; dst[HEAD_DIM + 1] = lw; }
 }
 
 // Pass 2: merge the chunks of one q head (log-sum-exp weights), write f16.  Reference:

@@ -866,7 +866,7 @@ twm_status twm_attn_decode(void* out, const void* q, const void* k_cache, const 
     const int chunks = (max_seq + twm::ops::ATT_CHUNK - 1) / twm::ops::ATT_CHUNK;
     if (chunks > 1024) return TWM_EINVAL;          // the merge pass keeps one weight per chunk in shared memory
     st = launch_op("twm_attn_decode(chunks)", twm::ops::attn_chunk_kernel<128>, dim3(chunks, num_kv_heads, rows),
-                   dim3(256), 0, flags, stream, (float*)scratch, (const __half*)q, (const __half*)k_cache,
+                   dim3(32 * (num_heads / num_kv_heads)), 0, flags, stream, (float*)scratch, (const __half*)q, (const __half*)k_cache,
                    (const __half*)v_cache, num_heads, num_kv_heads, len_buf, chunks, max_seq);
     if (st != TWM_OK) return st;
     return launch_op("twm_attn_decode(merge)", twm::ops::attn_merge_kernel<128>, dim3(num_heads, rows), dim3(128), 0, flags,
