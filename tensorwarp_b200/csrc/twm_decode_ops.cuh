@@ -285,12 +285,14 @@ rope_append_kernel(__half* __restrict__ q_out, __half* __restrict__ k_cache, __h
 }
 
 // Split-KV decode attention, pass 1.  CTA = (chunk of ATT_CHUNK = 32 tokens, kv head); warp h of the
-// CTA takes q head h of the group (GQA: the kv head's rows come from L1 for all but the first warp).
+// CTA takes q head h of the group.  The CTA first copies the chunk's K and V rows (8 KB each) to
+// shared memory with coalesced 16-byte loads, every load issued before the first store, so the
+// rows leave L2 once per CTA however many q heads share the kv head.  Then per warp:
 //   scores: one token per LANE, no cross-lane reduction per score: the lane walks its token's K
-//           row (all 16 loads issued before the first use) against q_h in shared memory;
+//           row (rows padded by 16 bytes: the 128-bit reads of a quarter warp hit 32 distinct banks)
+//           against q_h, also in shared memory (broadcast reads);
 //   soft-max statistics: one warp max and one warp sum for the 32 tokens;
-//   P.V: lanes own 4 of the 128 dims; the 32 probabilities go round by shuffle; V rows are read
-//        coalesced, sixteen in flight.
+//   P.V: lanes own 4 of the 128 dims; the 32 probabilities go round by shuffle.
 // About 16 instructions per (token, head); the earlier one-token-per-warp loop with a shuffle
 // reduction per score needed 87 (5.0 M warp instructions per call at 2049 tokens x 28 heads) and
 // was bound by instruction issue.  Writes (max, sum, unnormalised o[128]) per (q head, chunk).  The
@@ -306,6 +308,10 @@ attn_chunk_kernel(float* __restrict__ part /* [heads][chunks][HEAD_DIM + 2] */, 
                   int num_kv_heads, const int* __restrict__ len_buf, int max_chunks, int max_seq)
 {
     static_assert(HEAD_DIM == 128, "lane owns 4 of 128 dims");
+    constexpr int ROW_BYTES = HEAD_DIM * 2;                 // one token's K (or V) row of this kv head
+    constexpr int KROW = ROW_BYTES + 16;                    // padded K row in shared memory
+    constexpr int PIECES = ATT_CHUNK * ROW_BYTES / 16;      // 16-byte pieces of the chunk's K (or V): 512
+    constexpr int PER_ROW = ROW_BYTES / 16;                 // 16
     pdl_launch_dependents();
     pdl_wait_prior_grids();
     const int chunk = blockIdx.x, kvh = blockIdx.y;
@@ -328,46 +334,63 @@ attn_chunk_kernel(float* __restrict__ part /* [heads][chunks][HEAD_DIM + 2] */, 
         return;
     }
     const int nt = min(ATT_CHUNK, len - t0);             // tokens of this chunk (CTA-uniform)
-    const bool valid = lane < nt;
+    __shared__ __align__(16) unsigned char k_s[ATT_CHUNK * KROW];
+    __shared__ __align__(16) unsigned char v_s[ATT_CHUNK * ROW_BYTES];
     __shared__ __align__(16) float q_s[ATT_MAX_GROUP][HEAD_DIM];
-    // every global load the warp needs until the scores are done, up front: its q row, this lane's
-    // whole K row, its 4 dims of the first sixteen V rows
     const uint2 qr = *reinterpret_cast<const uint2*>(q + (size_t)(kvh * group + h) * HEAD_DIM + lane * 4);
-    uint4 kr[HEAD_DIM / 8];
     {
-        const uint4* krow = reinterpret_cast<const uint4*>(k_cache + (size_t)(t0 + (valid ? lane : 0)) * kv_dim + kvh * HEAD_DIM);
+        // K and V of the chunk: piece i is bytes [16 i, 16 i + 16) of the chunk's rows laid end to end;
+        // rows past the sequence end are zero-filled (their probability is 0, and 0 x garbage could be NaN)
+        const unsigned char* kg = reinterpret_cast<const unsigned char*>(k_cache + (size_t)t0 * kv_dim + kvh * HEAD_DIM);
+        const unsigned char* vg = reinterpret_cast<const unsigned char*>(v_cache + (size_t)t0 * kv_dim + kvh * HEAD_DIM);
+        const size_t row_stride = (size_t)kv_dim * 2;
+        constexpr int BATCH = 3;                         // 3 x 224 threads cover the 512 pieces of a 7-head group at once
+        for (int i0 = threadIdx.x; i0 < PIECES; i0 += BATCH * blockDim.x) {
+            uint4 kk[BATCH], vv[BATCH];
 #pragma unroll
-        for (int dc = 0; dc < HEAD_DIM / 8; ++dc) kr[dc] = krow[dc];
+            for (int b = 0; b < BATCH; ++b) {
+                const int i = i0 + b * blockDim.x;
+                const int tok = i / PER_ROW, piece = i % PER_ROW;
+                const bool in = (i < PIECES) && (tok < nt);
+                kk[b] = in ? *reinterpret_cast<const uint4*>(kg + tok * row_stride + piece * 16) : make_uint4(0, 0, 0, 0);
+                vv[b] = in ? *reinterpret_cast<const uint4*>(vg + tok * row_stride + piece * 16) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int b = 0; b < BATCH; ++b) {
+                const int i = i0 + b * blockDim.x;
+                if (i < PIECES) {
+                    const int tok = i / PER_ROW, piece = i % PER_ROW;
+                    *reinterpret_cast<uint4*>(k_s + tok * KROW + piece * 16) = kk[b];
+                    *reinterpret_cast<uint4*>(v_s + i * 16) = vv[b];
+                }
+            }
+        }
     }
-    const __half* vbase = v_cache + (size_t)t0 * kv_dim + kvh * HEAD_DIM + lane * 4;
-    uint2 vr[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) vr[j] = (j < nt) ? *reinterpret_cast<const uint2*>(vbase + (size_t)j * kv_dim) : make_uint2(0, 0);
     {
         const float scale = rsqrtf((float)HEAD_DIM);
         const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&qr.x));
         const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&qr.y));
         *reinterpret_cast<float4*>(&q_s[h][lane * 4]) = make_float4(a.x * scale, a.y * scale, b.x * scale, b.y * scale);
     }
-    __syncwarp();
+    __syncthreads();
     // ---- score of this lane's token ----
+    const bool valid = lane < nt;
     float sc = 0.0f;
+    {
+        const uint4* krow = reinterpret_cast<const uint4*>(k_s + lane * KROW);
 #pragma unroll
-    for (int dc = 0; dc < HEAD_DIM / 8; ++dc) {
-        const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kr[dc].x));
-        const float2 k1 = __half22float2(*reinterpret_cast<const __half2*>(&kr[dc].y));
-        const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&kr[dc].z));
-        const float2 k3 = __half22float2(*reinterpret_cast<const __half2*>(&kr[dc].w));
-        const float4 qa = *reinterpret_cast<const float4*>(&q_s[h][dc * 8]);
-        const float4 qb = *reinterpret_cast<const float4*>(&q_s[h][dc * 8 + 4]);
-        sc = fmaf(k0.x, qa.x, fmaf(k0.y, qa.y, fmaf(k1.x, qa.z, fmaf(k1.y, qa.w,
-             fmaf(k2.x, qb.x, fmaf(k2.y, qb.y, fmaf(k3.x, qb.z, fmaf(k3.y, qb.w, sc))))))));
+        for (int dc = 0; dc < HEAD_DIM / 8; ++dc) {
+            const uint4 kr = krow[dc];
+            const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kr.x));
+            const float2 k1 = __half22float2(*reinterpret_cast<const __half2*>(&kr.y));
+            const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&kr.z));
+            const float2 k3 = __half22float2(*reinterpret_cast<const __half2*>(&kr.w));
+            const float4 qa = *reinterpret_cast<const float4*>(&q_s[h][dc * 8]);
+            const float4 qb = *reinterpret_cast<const float4*>(&q_s[h][dc * 8 + 4]);
+            sc = fmaf(k0.x, qa.x, fmaf(k0.y, qa.y, fmaf(k1.x, qa.z, fmaf(k1.y, qa.w,
+                 fmaf(k2.x, qb.x, fmaf(k2.y, qb.y, fmaf(k3.x, qb.z, fmaf(k3.y, qb.w, sc))))))));
+        }
     }
-    // the second sixteen V rows are requested now (the K registers are free), used after the first sixteen
-    uint2 vr2[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j)
-        vr2[j] = (16 + j < nt) ? *reinterpret_cast<const uint2*>(vbase + (size_t)(16 + j) * kv_dim) : make_uint2(0, 0);
     // ---- soft-max statistics of the chunk ----
     const float sv = valid ? sc : -INFINITY;
     const float mw = warp_max(sv);
@@ -375,18 +398,13 @@ attn_chunk_kernel(float* __restrict__ part /* [heads][chunks][HEAD_DIM + 2] */, 
     const float lw = warp_sum(pr);
     // ---- o[dims of this lane] = sum_t p[t] * v_t ----
     float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
+    const uint2* vcol = reinterpret_cast<const uint2*>(v_s) + lane;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
+    for (int j = 0; j < ATT_CHUNK; ++j) {
         const float pt = __shfl_sync(0xffffffffu, pr, j);              // 0 for tokens past the end
-        const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&vr[j].x));
-        const float2 v1 = __half22float2(*reinterpret_cast<const __half2*>(&vr[j].y));
-        o0 = fmaf(pt, v0.x, o0); o1 = fmaf(pt, v0.y, o1); o2 = fmaf(pt, v1.x, o2); o3 = fmaf(pt, v1.y, o3);
-    }
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const float pt = __shfl_sync(0xffffffffu, pr, 16 + j);
-        const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&vr2[j].x));
-        const float2 v1 = __half22float2(*reinterpret_cast<const __half2*>(&vr2[j].y));
+        const uint2 vr = vcol[j * (ROW_BYTES / 8)];
+        const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&vr.x));
+        const float2 v1 = __half22float2(*reinterpret_cast<const __half2*>(&vr.y));
         o0 = fmaf(pt, v0.x, o0); o1 = fmaf(pt, v0.y, o1); o2 = fmaf(pt, v1.x, o2); o3 = fmaf(pt, v1.y, o3);
     }
     // a partial is HEAD_DIM + 2 floats long, so its start is 8-byte aligned only: two float2 stores
@@ -395,54 +413,77 @@ attn_chunk_kernel(float* __restrict__ part /* [heads][chunks][HEAD_DIM + 2] */, 
     if (lane == 0) { dst[HEAD_DIM] = mw; dst[HEAD_DIM + 1] = lw; }
 }
 
-// Pass 2: merge the chunks of one q head (log-sum-exp weights), write f16.  Reference:
-// warp_flash_decode_reduce, crates/kernels/src/kv_cache.rs:790-841.
+// Pass 2: merge the chunks of one q head (log-sum-exp weights), write f16.  CTA = q head, 4 x 128
+// threads: thread (part, d) sums dimension d over every fourth chunk, eight loads in flight.
+// Reference: warp_flash_decode_reduce, crates/kernels/src/kv_cache.rs:790-841.
+constexpr int ATT_MERGE_PARTS = 4;
 template <int HEAD_DIM>
-__global__ void __launch_bounds__(HEAD_DIM)
+__global__ void __launch_bounds__(HEAD_DIM * ATT_MERGE_PARTS)
 attn_merge_kernel(__half* __restrict__ out, const float* __restrict__ part, const int* __restrict__ len_buf,
                   int max_chunks)
 {
     pdl_launch_dependents();
     pdl_wait_prior_grids();
     constexpr int MAXC = 1024;                       // chunk weights kept in shared memory
+    constexpr int THREADS = HEAD_DIM * ATT_MERGE_PARTS, WARPS = THREADS / 32, STRIDE = HEAD_DIM + 2;
     __shared__ float s_w[MAXC];
-    __shared__ float s_red[HEAD_DIM / 32];
-    const int head = blockIdx.x, d = threadIdx.x;
+    __shared__ float s_l[MAXC];
+    __shared__ float s_max[WARPS], s_sum[WARPS];
+    __shared__ float s_o[ATT_MERGE_PARTS][HEAD_DIM];
+    const int head = blockIdx.x, tid = threadIdx.x, d = tid % HEAD_DIM, prt = tid / HEAD_DIM;
     out += (size_t)blockIdx.y * gridDim.x * HEAD_DIM;
-    part += (size_t)blockIdx.y * gridDim.x * max_chunks * (HEAD_DIM + 2);
+    part += (size_t)blockIdx.y * gridDim.x * max_chunks * STRIDE;
     const int chunks = min(min(max_chunks, MAXC), (len_buf[0] + ATT_CHUNK - 1) / ATT_CHUNK);
-    const float* base = part + (size_t)head * max_chunks * (HEAD_DIM + 2);
+    const float* base = part + (size_t)head * max_chunks * STRIDE;
     // every chunk's (max, sum) in one round of loads, one chunk per thread
     float mloc = -INFINITY;
-    for (int c = d; c < chunks; c += HEAD_DIM) {
-        const float mc = base[(size_t)c * (HEAD_DIM + 2) + HEAD_DIM];
-        s_w[c] = mc;
-        mloc = fmaxf(mloc, mc);
+    for (int c = tid; c < chunks; c += THREADS) {
+        const float2 ml = *reinterpret_cast<const float2*>(base + (size_t)c * STRIDE + HEAD_DIM);
+        s_w[c] = ml.x;
+        s_l[c] = ml.y;
+        mloc = fmaxf(mloc, ml.x);
     }
     mloc = warp_max(mloc);
-    if ((d & 31) == 0) s_red[d >> 5] = mloc;
+    if ((tid & 31) == 0) s_max[tid >> 5] = mloc;
     __syncthreads();
-    float mm = s_red[0];
+    float mm = s_max[0];
 #pragma unroll
-    for (int w = 1; w < HEAD_DIM / 32; ++w) mm = fmaxf(mm, s_red[w]);
+    for (int w = 1; w < WARPS; ++w) mm = fmaxf(mm, s_max[w]);
     float lloc = 0.0f;
-    for (int c = d; c < chunks; c += HEAD_DIM) {
+    for (int c = tid; c < chunks; c += THREADS) {
         const float mc = s_w[c];
         const float w = (mc == -INFINITY) ? 0.0f : __expf(mc - mm);
         s_w[c] = w;
-        lloc += base[(size_t)c * (HEAD_DIM + 2) + HEAD_DIM + 1] * w;
+        lloc += s_l[c] * w;
     }
-    __syncthreads();
     lloc = warp_sum(lloc);
-    if ((d & 31) == 0) s_red[d >> 5] = lloc;
+    if ((tid & 31) == 0) s_sum[tid >> 5] = lloc;
     __syncthreads();
-    float ll = 0.0f;
-#pragma unroll
-    for (int w = 0; w < HEAD_DIM / 32; ++w) ll += s_red[w];
     float oo = 0.0f;
-#pragma unroll 16
-    for (int c = 0; c < chunks; ++c) oo = fmaf(base[(size_t)c * (HEAD_DIM + 2) + d], s_w[c], oo);
-    out[(size_t)head * HEAD_DIM + d] = __float2half_rn(ll > 0.0f ? oo / ll : 0.0f);
+    for (int c0 = prt; c0 < chunks; c0 += ATT_MERGE_PARTS * 8) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int c = c0 + j * ATT_MERGE_PARTS;
+            v[j] = (c < chunks) ? base[(size_t)c * STRIDE + d] : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int c = c0 + j * ATT_MERGE_PARTS;
+            oo = fmaf(v[j], (c < chunks) ? s_w[c] : 0.0f, oo);
+        }
+    }
+    s_o[prt][d] = oo;
+    __syncthreads();
+    if (prt == 0) {
+        float ll = 0.0f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) ll += s_sum[w];
+        float tot = s_o[0][d];
+#pragma unroll
+        for (int p = 1; p < ATT_MERGE_PARTS; ++p) tot += s_o[p][d];
+        out[(size_t)head * HEAD_DIM + d] = __float2half_rn(ll > 0.0f ? tot / ll : 0.0f);
+    }
 }
 
 // act = silu(gate) * up on the fused gate+up GEMM output [gate | up] (no split_gate_up pass).

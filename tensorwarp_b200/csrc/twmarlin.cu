@@ -869,7 +869,7 @@ twm_status twm_attn_decode(void* out, const void* q, const void* k_cache, const 
                    dim3(32 * (num_heads / num_kv_heads)), 0, flags, stream, (float*)scratch, (const __half*)q, (const __half*)k_cache,
                    (const __half*)v_cache, num_heads, num_kv_heads, len_buf, chunks, max_seq);
     if (st != TWM_OK) return st;
-    return launch_op("twm_attn_decode(merge)", twm::ops::attn_merge_kernel<128>, dim3(num_heads, rows), dim3(128), 0, flags,
+    return launch_op("twm_attn_decode(merge)", twm::ops::attn_merge_kernel<128>, dim3(num_heads, rows), dim3(128 * twm::ops::ATT_MERGE_PARTS), 0, flags,
                      stream, (__half*)out, (const float*)scratch, len_buf, chunks);
 }
 
