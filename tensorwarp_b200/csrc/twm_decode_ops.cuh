@@ -293,9 +293,9 @@ rope_append_kernel(__half* __restrict__ q_out, __half* __restrict__ k_cache, __h
 //           against q_h, also in shared memory (broadcast reads);
 //   soft-max statistics: one warp max and one warp sum for the 32 tokens;
 //   P.V: lanes own 4 of the 128 dims; the 32 probabilities go round by shuffle.
-// About 16 instructions per (token, head); the earlier one-token-per-warp loop with a shuffle
-// reduction per score needed 87 (5.0 M warp instructions per call at 2049 tokens x 28 heads) and
-// was bound by instruction issue.  Writes (max, sum, unnormalised o[128]) per (q head, chunk).  The
+// About 28 warp instructions per (token, head), staging included (1.64 M per call at 2049 tokens x
+// 28 heads); the earlier one-token-per-warp loop with a shuffle reduction per score needed 87
+// (5.0 M) and 123 registers.  Writes (max, sum, unnormalised o[128]) per (q head, chunk).  The
 // sequence length is read from the device (len_buf[0]), the grid covers max_seq.  Reference:
 // warp_flash_decode_chunk_dl, crates/kernels/src/kv_cache.rs:951-1076.
 constexpr int ATT_CHUNK = 32;       // tokens per CTA = lanes of a warp
