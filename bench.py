@@ -558,7 +558,12 @@ def run_tp(args):
         short[coll] = st2.x.clone()
         del st2
     rel = float((short["fused"] - short["nccl"]).abs().max() / short["nccl"].pow(2).mean().sqrt())
-    if not rel < 1e-3:
+    # With two ranks both paths add the same two FP32 partials (same bits in every run so far).  With
+    # more, NCCL's order of additions is its own while the fused path adds in rank order: the FP32 sums
+    # differ in the last bit, an FP16 rounding of a normed activation can flip, and one flip moves the
+    # output by about 1e-3 of its RMS (measured 1.2e-3 at four ranks).
+    tol = 1e-3 if world == 2 else 1e-2
+    if not rel < tol:
         raise RuntimeError(f"fused all-reduce result differs from the NCCL path: {rel}")
     dist.barrier()
     comm.close()
