@@ -46,11 +46,8 @@ enum {
     TWM_KERNEL_AUTO = 0,
     TWM_KERNEL_SIMT = 1, /* streaming kernel, FP32 FMA; the only one that takes FP32 activations */
     TWM_KERNEL_TC = 2,   /* tcgen05 kernel: weights dequantised into tensor memory, FP32 accumulate in TMEM */
-    TWM_KERNEL_MMA = 3,  /* streaming kernel for M <= 8, FP16 activations, warp-level MMA on unpacked registers,
-                            128-column tiles with split-K: small N, indirect (expert) weights, N not a multiple of 8 */
-    TWM_KERNEL_STRIP = 4 /* same arithmetic, one CTA per SM owning 32-column strips over the whole K: no split-K, no
-                            workspace, half an SM per launch so that consecutive GEMMs overlap.  Never picked by
-                            the heuristic (measured slower on B200); N % 8 == 0, activations must fit in shared memory */
+    TWM_KERNEL_MMA = 3   /* streaming kernel for M <= 8, FP16 activations, warp-level MMA on unpacked registers,
+                            128-column tiles with split-K (inside a thread-block cluster for M <= 2) */
 };
 
 /* Flags of twm_gemm_args.flags. */
@@ -81,6 +78,8 @@ typedef struct twm_comm {
     float* data[8];           /* rank s's slots, as addressable from this rank */
     unsigned int* flags[8];   /* rank s's arrival flags */
     unsigned int* state;      /* this rank's own state words */
+    unsigned long long wait_ns; /* how long twm_allreduce_add_rmsnorm waits for the peers' partials before it gives
+                                 up, sets the device error word and leaves x untouched; 0 = two seconds */
 } twm_comm;
 
 /* One GEMM  C[M,N] = A[M,K] x dequant(packed, scales).
@@ -166,6 +165,56 @@ twm_status twm_ipc_free(void* ptr);
 twm_status twm_ipc_get_handle(void* ptr, unsigned char handle[64]);
 twm_status twm_ipc_open(const unsigned char handle[64], void** ptr);
 twm_status twm_ipc_close(void* ptr);
+
+/* ---- A list of GEMMs as one persistent launch ------------------------------------------------
+ * The reference's decode step enqueues its GEMMs one kernel at a time
+ * (forward_decode_tw_marlin_graph, crates/kernels/src/generate.rs:2149-2206, each through
+ * gemm_tw_marlin_m1, quantize.rs:1301-1360).  A chain takes the same list of GEMMs and runs it as
+ * ONE cooperative kernel: GEMM i sees everything GEMMs 0..i-1 wrote, exactly as if they had been
+ * enqueued one after another on the stream, but the packed weights of GEMM i+1 are already
+ * streaming into shared memory while GEMM i finishes; only the reader of a GEMM's activations
+ * waits (bounded, on a counter in device memory) for the GEMM that produces them.
+ * Restrictions: M <= 8, FP16 activations, no expert indirection, no peer push.
+ *
+ * twm_chain_create is a set-up call: it allocates the chain's device memory (GEMM table, split
+ * partials, counters; twm_chain_info reports the size) and synchronises.  twm_chain_launch only
+ * enqueues and is legal during stream capture.  One chain runs on one stream at a time. */
+enum {
+    TWM_A_PLAIN = 0,     /* a is f16 [M][lda] */
+    TWM_A_SILU_MUL = 1   /* a is f16 [M][lda] holding [gate | up] (up at column K): the GEMM reads
+                            silu(gate) * up, rounded to f16 as twm_silu_mul would have stored it
+                            (fused_silu_mul, crates/kernels/src/ops.rs:966-977) */
+};
+
+typedef struct twm_chain_op {
+    twm_gemm_args gemm;  /* workspace, *_override, *_offsets and comm must be zero; flags: TWM_FLAG_ACCUMULATE,
+                            and TWM_FLAG_INDEPENDENT = this GEMM reads nothing an earlier GEMM of the chain
+                            writes (it does not wait; a later dependent GEMM still waits for it and for
+                            everything before it) */
+    int a_prologue;      /* TWM_A_* */
+} twm_chain_op;
+
+typedef struct twm_chain twm_chain;      /* opaque */
+
+typedef struct twm_chain_info_t {
+    int count;           /* GEMMs */
+    int grid;            /* CTAs of the launch (resident CTAs per SM x SMs) */
+    int rows;            /* activation rows staged per GEMM (power of two >= the largest M) */
+    size_t device_bytes; /* device memory the chain holds */
+    int split_tiles;     /* tiles that are summed through partials, over the whole chain */
+    int max_pieces;      /* most pieces any tile is cut into */
+} twm_chain_info_t;
+
+twm_status twm_chain_create(const twm_chain_op* ops, int count, twm_chain** out);
+twm_status twm_chain_launch(twm_chain* chain, void* stream);
+twm_status twm_chain_info(const twm_chain* chain, twm_chain_info_t* out);
+twm_status twm_chain_destroy(twm_chain* chain);
+
+/* How a chain deals one GEMM to its CTAs (pure host arithmetic, the same code the kernel runs):
+ * the pieces (tile, first and last+1 32-block of K, index of the piece within its tile, pieces of
+ * that tile) of `rank` out of `grid` for a GEMM of n_tiles x nkb 32-blocks.  Writes at most
+ * `max_out` entries of five ints each and returns the count in *n_out. */
+twm_status twm_chain_partition(int n_tiles, int nkb, int grid, int rank, int max_out, int* out5, int* n_out);
 
 /* The same GEMM for hosts that cannot give this library any device memory of its own:
  * an engine that carves the whole GPU into weights and KV cache at start-up and has no

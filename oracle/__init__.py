@@ -177,5 +177,10 @@ def fuse_n(mats, K: int, group: int = 32):
     return out_p, out_s
 
 
+def set_threads(n: int) -> None:
+    """Use `n` host threads in the threaded routines from now on."""
+    lib().twmo_set_num_threads(C.c_int(int(n)))
+
+
 def num_threads() -> int:
     return int(lib().twmo_num_threads())

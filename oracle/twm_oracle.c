@@ -433,6 +433,18 @@ void twmo_fuse_n(const uint8_t *const *srcs, const int *ns, int count, int rows,
     }
 }
 
+/* Host threads the threaded routines use from now on (a launcher such as torchrun sets
+ * OMP_NUM_THREADS=1 in the environment; the benchmark's CPU arm overrides that with the cores
+ * the process may actually run on). */
+void twmo_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int twmo_num_threads(void)
 {
 #ifdef _OPENMP

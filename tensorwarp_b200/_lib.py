@@ -13,8 +13,9 @@ LIB_PATH = os.environ.get("TWMARLIN_LIB", os.path.join(PKG, "libtwmarlin.so"))
 
 TWM_OK, TWM_EINVAL, TWM_EALIGN, TWM_EWORKSPACE, TWM_ELAUNCH, TWM_EARCH, TWM_ETIMEOUT = 0, -1, -2, -3, -4, -5, -6
 TWM_F32, TWM_F16 = 0, 1
-TWM_KERNEL_AUTO, TWM_KERNEL_SIMT, TWM_KERNEL_TC, TWM_KERNEL_MMA, TWM_KERNEL_STRIP = 0, 1, 2, 3, 4
+TWM_KERNEL_AUTO, TWM_KERNEL_SIMT, TWM_KERNEL_TC, TWM_KERNEL_MMA = 0, 1, 2, 3
 TWM_FLAG_PDL, TWM_FLAG_ACCUMULATE, TWM_FLAG_INDEPENDENT = 1, 2, 4
+TWM_A_PLAIN, TWM_A_SILU_MUL = 0, 1
 
 
 class GemmArgs(C.Structure):
@@ -36,7 +37,19 @@ class GemmArgs(C.Structure):
 class Comm(C.Structure):
     """``twm_comm``."""
     _fields_ = [("n_ranks", C.c_int), ("rank", C.c_int), ("slot_elems", C.c_long),
-                ("data", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("state", C.c_void_p)]
+                ("data", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("state", C.c_void_p),
+                ("wait_ns", C.c_ulonglong)]
+
+
+class ChainOp(C.Structure):
+    """``twm_chain_op``."""
+    _fields_ = [("gemm", GemmArgs), ("a_prologue", C.c_int)]
+
+
+class ChainInfo(C.Structure):
+    """``twm_chain_info_t``."""
+    _fields_ = [("count", C.c_int), ("grid", C.c_int), ("rows", C.c_int), ("device_bytes", C.c_size_t),
+                ("split_tiles", C.c_int), ("max_pieces", C.c_int)]
 
 
 class Plan(C.Structure):
@@ -54,6 +67,11 @@ SIGNATURES = {
     "twm_gemm_w4a16": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
     "twm_gemm_w4a16_static_ws": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
     "twm_static_ws_capacity": (C.c_size_t, []),
+    "twm_chain_create": (C.c_int, [C.POINTER(ChainOp), C.c_int, C.POINTER(C.c_void_p)]),
+    "twm_chain_launch": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "twm_chain_info": (C.c_int, [C.c_void_p, C.POINTER(ChainInfo)]),
+    "twm_chain_destroy": (C.c_int, [C.c_void_p]),
+    "twm_chain_partition": (C.c_int, [C.c_int] * 5 + [C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "twm_dequant": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "twm_quantize_pack": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "twm_fuse_n": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.c_int, C.c_int,

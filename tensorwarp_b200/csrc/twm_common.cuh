@@ -171,35 +171,6 @@ __device__ __forceinline__ float ld_cg_f32(const float* p) {
     return v;
 }
 
-// Optional cycle accounting per warp role (development builds only: -DTWM_PROF).
-#ifdef TWM_PROF
-__device__ unsigned long long g_prof[64];
-#define PROF_DECL unsigned long long prof_t0 = clock64(), prof_acc[6] = {0, 0, 0, 0, 0, 0}
-#define PROF_BEGIN(t) unsigned long long t = clock64()
-#define PROF_END(t, cat) prof_acc[cat] += clock64() - t
-#define PROF_FLUSH(role)                                                                          \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) {                                        \
-        for (int c_ = 0; c_ < 6; ++c_) atomicAdd(&g_prof[(role) * 8 + c_], prof_acc[c_]);          \
-        atomicAdd(&g_prof[(role) * 8 + 6], clock64() - prof_t0);                                   \
-        atomicAdd(&g_prof[(role) * 8 + 7], 1ull);                                                  \
-    }
-#else
-#define PROF_DECL
-#define PROF_BEGIN(t)
-#define PROF_END(t, cat)
-#define PROF_FLUSH(role)
-#endif
-
-#ifdef TWM_TIMELINE
-// development builds only: per-CTA wall-clock marks (globaltimer, ns) of the last launches
-__device__ unsigned long long g_timeline[64 * 512 * 8];
-__device__ unsigned int g_timeline_launch;
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define TL_MARK(launch, idx) if (threadIdx.x == 0 && (launch) < 64) g_timeline[(((launch) * 512) + blockIdx.y * gridDim.x + blockIdx.x) * 8 + (idx)] = gtime()
-#else
-#define TL_MARK(launch, idx)
-#endif
-
 // Launch parameters shared by the GEMM kernels.
 struct GemmParams {
     int M, N, K, group;          // group = scale group size (32 or 128)
@@ -234,12 +205,8 @@ struct GemmParams {
     unsigned int* comm_state;        // [0] operation sequence number, [1] CTAs done, [2] consumer CTAs done
     // Tensor map over `packed` seen as u64 [K/32][2N]: one TMA instruction brings a whole
     // ring stage (box = 256 u64 x map_rows rows = 128 columns x map_rows 32-blocks).
-    int strip_stages;            // strip kernel: depth of the weight ring (what fits beside the activations)
     int map_rows;                // 0 = no map (1-D bulk copies per row instead)
-    int launch_id;               // development builds: index of this launch in the timeline buffer
     alignas(64) CUtensorMap packed_map;
-    // strip kernel: tensor map over the scales, f16 [K/G][N], box = 32 columns x one stage's rows
-    alignas(64) CUtensorMap scale_map;
     // tcgen05 kernel: -8 * sum of a scale group's activations per row, FP32 [K/G][NB] (written by the pre-pass)
     const float* tc_a8;
     // tcgen05 kernel: tensor map over the launch's permuted activations, f16 [K/8][rows][8]

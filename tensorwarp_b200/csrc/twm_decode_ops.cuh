@@ -38,9 +38,19 @@ embed_kernel(float* __restrict__ x, const __half* __restrict__ table, const int*
         x[(size_t)row * hidden + i] = __half2float(table[tok * hidden + i]);
 }
 
+// Sum of squares of a row in ONE fixed order that every kernel below follows, so that a row
+// normalised by the one-CTA kernel and the same row normalised by the multi-CTA all-reduce kernel
+// come out with the same bits: the row is cut into segments of 256 float4; inside a segment
+// thread t takes vector t with a four-term fused chain, the 32 lanes of a warp add up by an
+// xor tree, the eight warps are added in warp order; the segments are added in segment order.
+constexpr int RMS_SEG_VECS = 256;     // float4 per segment = threads per CTA
+__device__ __forceinline__ float sumsq4(const float4 v) {
+    return fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
+}
+
 // y = f16(x * rsqrt(mean(x^2) + eps) * gamma), one CTA per row.  Reference: warp_rmsnorm,
-// crates/kernels/src/ops.rs:302-336 (one warp per row there; here 256 threads and a fixed-order
-// two-level sum).  With `add` the kernel first does x += add (and stops there when y is null).
+// crates/kernels/src/ops.rs:302-336 (one warp per row there; here 256 threads and the fixed-order
+// segment sum above).  With `add` the kernel first does x += add (and stops there when y is null).
 constexpr int RMS_MAX_VEC = 8;        // float4 per thread held in registers: rows up to 8192 floats
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(__half* __restrict__ y, float* __restrict__ x, const float* __restrict__ add,
@@ -48,17 +58,18 @@ rmsnorm_kernel(__half* __restrict__ y, float* __restrict__ x, const float* __res
 {
     pdl_launch_dependents();
     pdl_wait_prior_grids();
-    __shared__ float partial[8];
+    constexpr int RMS_MAX_SEGS = 16;                  // rows up to 16384 floats in the fixed order; longer rows: plain pass
+    __shared__ float partial[RMS_MAX_SEGS][8];
     const int row = blockIdx.x;
     float* xr = x + (size_t)row * hidden;
     const float* ar = add ? add + (size_t)row * hidden : nullptr;
-    const bool vec = ((hidden & 3) == 0) && (hidden <= 256 * 4 * RMS_MAX_VEC) &&
+    const bool vec = ((hidden & 3) == 0) && (hidden <= 256 * 4 * RMS_MAX_SEGS) &&
                      ((reinterpret_cast<uintptr_t>(xr) & 15) == 0) && (!ar || (reinterpret_cast<uintptr_t>(ar) & 15) == 0) &&
                      ((reinterpret_cast<uintptr_t>(gamma) & 15) == 0);
-    float ss = 0.0f;
     if (vec) {
         // the whole row sits in registers: every load is issued before the first use
         const int nvec = hidden >> 2;
+        const int nseg = (nvec + RMS_SEG_VECS - 1) / RMS_SEG_VECS;
         float4 v[RMS_MAX_VEC];
 #pragma unroll
         for (int j = 0; j < RMS_MAX_VEC; ++j) {
@@ -75,17 +86,38 @@ rmsnorm_kernel(__half* __restrict__ y, float* __restrict__ x, const float* __res
                     reinterpret_cast<float4*>(xr)[i] = v[j];
                 }
             }
+            for (int j = RMS_MAX_VEC; j < nseg; ++j) {        // segments past the registers
+                const int i = threadIdx.x + j * 256;
+                if (i < nvec) {
+                    float4 t = reinterpret_cast<const float4*>(xr)[i];
+                    const float4 a = reinterpret_cast<const float4*>(ar)[i];
+                    t.x += a.x; t.y += a.y; t.z += a.z; t.w += a.w;
+                    reinterpret_cast<float4*>(xr)[i] = t;
+                }
+            }
             if (y == nullptr) return;
         }
 #pragma unroll
-        for (int j = 0; j < RMS_MAX_VEC; ++j)
-            ss = fmaf(v[j].x, v[j].x, fmaf(v[j].y, v[j].y, fmaf(v[j].z, v[j].z, fmaf(v[j].w, v[j].w, ss))));
-        ss = warp_sum(ss);
-        if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = ss;
+        for (int j = 0; j < RMS_MAX_VEC; ++j) {
+            if (j < nseg) {                                   // CTA-uniform
+                const float ss = warp_sum(sumsq4(v[j]));
+                if ((threadIdx.x & 31) == 0) partial[j][threadIdx.x >> 5] = ss;
+            }
+        }
+        for (int j = RMS_MAX_VEC; j < nseg; ++j) {
+            const int i = threadIdx.x + j * 256;              // each thread re-reads what it wrote itself
+            const float4 t = (i < nvec) ? reinterpret_cast<const float4*>(xr)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float ss = warp_sum(sumsq4(t));
+            if ((threadIdx.x & 31) == 0) partial[j][threadIdx.x >> 5] = ss;
+        }
         __syncthreads();
         float tot = 0.0f;
+        for (int j = 0; j < nseg; ++j) {
+            float sj = 0.0f;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) tot += partial[w];
+            for (int w = 0; w < 8; ++w) sj += partial[j][w];
+            tot += sj;
+        }
         const float rms = rsqrtf(tot / (float)hidden + eps);
         __half* yr = y + (size_t)row * hidden;
 #pragma unroll
@@ -101,8 +133,23 @@ rmsnorm_kernel(__half* __restrict__ y, float* __restrict__ x, const float* __res
                 reinterpret_cast<uint2*>(yr)[i] = o;
             }
         }
+        for (int j = RMS_MAX_VEC; j < nseg; ++j) {
+            const int i = threadIdx.x + j * 256;
+            if (i < nvec) {
+                const float4 t = reinterpret_cast<const float4*>(xr)[i];
+                const float4 gm = reinterpret_cast<const float4*>(gamma)[i];
+                const __half2 lo = __floats2half2_rn(t.x * rms * gm.x, t.y * rms * gm.y);
+                const __half2 hi = __floats2half2_rn(t.z * rms * gm.z, t.w * rms * gm.w);
+                uint2 o;
+                o.x = *reinterpret_cast<const uint32_t*>(&lo);
+                o.y = *reinterpret_cast<const uint32_t*>(&hi);
+                reinterpret_cast<uint2*>(yr)[i] = o;
+            }
+        }
         return;
     }
+    // rows longer than 16384 floats, or not 16-byte aligned: a plain strided pass
+    float ss = 0.0f;
     if (ar != nullptr) {
         // x += add first (fused_residual_rmsnorm, ops.rs:928-962): the all-reduced output of a
         // row-parallel GEMM joins the residual stream here
@@ -112,11 +159,11 @@ rmsnorm_kernel(__half* __restrict__ y, float* __restrict__ x, const float* __res
         for (int i = threadIdx.x; i < hidden; i += blockDim.x) { const float t = xr[i]; ss = fmaf(t, t, ss); }
     }
     ss = warp_sum(ss);
-    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = ss;
+    if ((threadIdx.x & 31) == 0) partial[0][threadIdx.x >> 5] = ss;
     __syncthreads();
     float tot = 0.0f;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) tot += partial[w];
+    for (int w = 0; w < 8; ++w) tot += partial[0][w];
     const float rms = rsqrtf(tot / (float)hidden + eps);
     for (int i = threadIdx.x; i < hidden; i += blockDim.x)
         y[(size_t)row * hidden + i] = __float2half_rn(xr[i] * rms * gamma[i]);
@@ -126,95 +173,106 @@ rmsnorm_kernel(__half* __restrict__ y, float* __restrict__ x, const float* __res
 // row-parallel GEMM: wait (bounded) until every rank's partial for the current operation has
 // arrived in THIS GPU's receive buffer (the GEMM epilogues of all ranks stored them there over
 // NVLink), add the slots in rank order (every rank gets the same bits), x += sum, y = norm(x).
-// One CTA per row; the last CTA to finish advances the operation sequence number.  The
-// reference sums partial outputs on the host (crates/kernels/src/multi_gpu.rs:329-366).
-constexpr int ARN_THREADS = 1024;
+// A row is shared by the CTAs of one thread-block cluster (grid x), one 256-vector segment per
+// CTA and pass; the segments' sums of squares meet in every CTA's shared memory (distributed
+// shared memory stores, one cluster barrier) and are added in segment order, which is the order
+// rmsnorm_kernel uses.  The last CTA of the grid advances the operation sequence number.
+// The reference sums partial outputs on the host (crates/kernels/src/multi_gpu.rs:329-366).
+constexpr int ARN_THREADS = 256;
+constexpr int ARN_MAX_SEGS = 16;        // rows up to 16384 floats
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 __global__ void __launch_bounds__(ARN_THREADS)
 allreduce_add_rmsnorm_kernel(__half* __restrict__ y, float* __restrict__ x, const float* __restrict__ recv,
                              const unsigned int* __restrict__ flags, unsigned int* __restrict__ state,
-                             const float* __restrict__ gamma, int hidden, float eps, int n_ranks, long slot_elems)
+                             const float* __restrict__ gamma, int hidden, float eps, int n_ranks, long slot_elems,
+                             unsigned long long wait_ns)
 {
     pdl_launch_dependents();
+    // every CTA of the cluster has started once it has arrived here: only then may the others
+    // store into its shared memory
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
     pdl_wait_prior_grids();
-    __shared__ float partial[ARN_THREADS / 32];
+    __shared__ float partial[8];
+    __shared__ float segtot[ARN_MAX_SEGS];
     __shared__ int s_ok;
-    const int row = blockIdx.x;
+    const int row = blockIdx.y;
+    const int ncta = gridDim.x;                      // = cluster size
+    const int crank = (int)cluster_ctarank();
     const unsigned int seq = ld_volatile_u32(state);
     const unsigned int set = seq & 1u;
     if (threadIdx.x == 0) s_ok = 1;
     __syncthreads();
     if (threadIdx.x < n_ranks) {
-        // about a second of polling at most; then the error word is set and the step's result is void
+        // bounded by the wall clock (wait_ns) and, should the clock misbehave, by a poll count;
+        // then the error word is set and the step's result is void
         const unsigned int* f = flags + (set * n_ranks + threadIdx.x) * 8;
+        const unsigned long long t0 = globaltimer_ns();
         bool got = false;
-        for (unsigned int i = 0; i < (1u << 22) && !got; ++i) {
+        for (unsigned int i = 0; i < (1u << 26) && !got; ++i) {
             got = ld_acquire_sys_u32(f) == seq + 1u;
-            if (!got && i > 64) __nanosleep(128);
+            if (!got && i > 64) {
+                __nanosleep(128);
+                if ((i & 15) == 0 && globaltimer_ns() - t0 > wait_ns) break;
+            }
         }
         if (!got) { s_ok = 0; atomicOr(&g_error_word, 4u); }
     }
     __syncthreads();
+    const bool okk = s_ok != 0;
     float* xr = x + (size_t)row * hidden;
     const float* base = recv + (size_t)set * n_ranks * slot_elems + (size_t)row * hidden;
-    float ss = 0.0f;
-    // hidden is a multiple of 4 (checked by the host); each thread keeps at most VPT float4 of x
-    constexpr int VPT = 4;
-    const int nvec = hidden >> 2;
-    float4 keep[VPT];
-    if (s_ok) {
+    const int nvec = hidden >> 2;                    // hidden is a multiple of 4 (checked by the host)
+    const int nseg = (nvec + RMS_SEG_VECS - 1) / RMS_SEG_VECS;
+    constexpr int KEEP = 2;                          // segments per CTA (the host launches nseg CTAs up to 8, then 8)
+    float4 keep[KEEP];
+    asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
 #pragma unroll
-        for (int j = 0; j < VPT; ++j) {
-            const int i = threadIdx.x + j * ARN_THREADS;
-            if (i < nvec) {
-                float4 acc = __ldcg(reinterpret_cast<const float4*>(base) + i);
-                for (int r = 1; r < n_ranks; ++r) {
-                    const float4 t = __ldcg(reinterpret_cast<const float4*>(base + (size_t)r * slot_elems) + i);
-                    acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
-                }
-                float4 v = reinterpret_cast<float4*>(xr)[i];
-                v.x += acc.x; v.y += acc.y; v.z += acc.z; v.w += acc.w;
-                reinterpret_cast<float4*>(xr)[i] = v;
-                keep[j] = v;
-                ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
-            }
-        }
-        for (int i = threadIdx.x + VPT * ARN_THREADS; i < nvec; i += ARN_THREADS) {      // very wide rows
+    for (int kept = 0; kept < KEEP; ++kept) {
+        const int seg = crank + kept * ncta;
+        if (seg >= nseg) break;                      // CTA-uniform
+        const int i = seg * RMS_SEG_VECS + threadIdx.x;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (okk && i < nvec) {
             float4 acc = __ldcg(reinterpret_cast<const float4*>(base) + i);
             for (int r = 1; r < n_ranks; ++r) {
                 const float4 t = __ldcg(reinterpret_cast<const float4*>(base + (size_t)r * slot_elems) + i);
                 acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
             }
-            float4 v = reinterpret_cast<float4*>(xr)[i];
+            v = reinterpret_cast<float4*>(xr)[i];
             v.x += acc.x; v.y += acc.y; v.z += acc.z; v.w += acc.w;
             reinterpret_cast<float4*>(xr)[i] = v;
-            ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+        }
+        keep[kept] = v;
+        if (y != nullptr) {
+            const float ss = warp_sum(sumsq4(v));
+            if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = ss;
+            __syncthreads();
+            if (threadIdx.x < ncta) {
+                // this segment's sum, in warp order, into every CTA of the cluster
+                float sj = 0.0f;
+#pragma unroll
+                for (int w = 0; w < 8; ++w) sj += partial[w];
+                st_cluster_f32(mapa_shared(smem_u32(&segtot[seg]), threadIdx.x), sj);
+            }
+            __syncthreads();
         }
     }
-    if (y != nullptr) {
-        ss = warp_sum(ss);
-        if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = ss;
-        __syncthreads();
+    cluster_sync_all();                              // also: nobody leaves while its shared memory may still be written
+    if (y != nullptr && okk) {
         float tot = 0.0f;
-#pragma unroll
-        for (int w = 0; w < ARN_THREADS / 32; ++w) tot += partial[w];
+        for (int sg = 0; sg < nseg; ++sg) tot += segtot[sg];
         const float rms = rsqrtf(tot / (float)hidden + eps);
         __half* yr = y + (size_t)row * hidden;
-        if (s_ok) {
 #pragma unroll
-            for (int j = 0; j < VPT; ++j) {
-                const int i = threadIdx.x + j * ARN_THREADS;
-                if (i < nvec) {
-                    const float4 g = __ldg(reinterpret_cast<const float4*>(gamma) + i);
-                    const __half2 h0 = __floats2half2_rn(keep[j].x * rms * g.x, keep[j].y * rms * g.y);
-                    const __half2 h1 = __floats2half2_rn(keep[j].z * rms * g.z, keep[j].w * rms * g.w);
-                    uint2 o;
-                    o.x = *reinterpret_cast<const unsigned int*>(&h0);
-                    o.y = *reinterpret_cast<const unsigned int*>(&h1);
-                    reinterpret_cast<uint2*>(yr)[i] = o;
-                }
-            }
-            for (int i = threadIdx.x + VPT * ARN_THREADS; i < nvec; i += ARN_THREADS) {
-                const float4 v = reinterpret_cast<const float4*>(xr)[i];
+        for (int kept = 0; kept < KEEP; ++kept) {
+            const int seg = crank + kept * ncta;
+            const int i = seg * RMS_SEG_VECS + threadIdx.x;
+            if (seg < nseg && i < nvec) {
+                const float4 v = keep[kept];
                 const float4 g = __ldg(reinterpret_cast<const float4*>(gamma) + i);
                 const __half2 h0 = __floats2half2_rn(v.x * rms * g.x, v.y * rms * g.y);
                 const __half2 h1 = __floats2half2_rn(v.z * rms * g.z, v.w * rms * g.w);
@@ -228,7 +286,7 @@ allreduce_add_rmsnorm_kernel(__half* __restrict__ y, float* __restrict__ x, cons
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
-        if (atomicAdd(&state[2], 1u) == gridDim.x - 1) {      // every row has read its slots
+        if (atomicAdd(&state[2], 1u) == gridDim.x * gridDim.y - 1) {      // every CTA has read its slots
             atomicExch(&state[2], 0u);
             __threadfence();
             atomicAdd(&state[0], 1u);                         // next operation, other buffer set

@@ -297,13 +297,10 @@ gemm_kernel(const __grid_constant__ GemmParams p)
             const uint64_t kcore_step = (uint64_t)(C::KCORE_BYTES >> 4);           // descriptor address units
             int gq = 0;                               // scale groups started so far: accumulator gq & 1
             bool ok = true;
-            PROF_DECL;
             // accumulator for group gq: wait until the readers have taken its previous contents
             auto open_group = [&]() -> uint32_t {
                 const int db = gq & 1;
-                PROF_BEGIN(t1);
                 if (gq >= 2 && !mbar_wait_bounded(&sm.d_empty[db], ((gq >> 1) - 1) & 1, abort_flag)) ok = false;
-                PROF_END(t1, 1);
                 tc_fence_after();
                 return tmem_base + C::D_COL0 + db * NB;
             };
@@ -311,11 +308,8 @@ gemm_kernel(const __grid_constant__ GemmParams p)
                 // per stage: one wait, eight MMAs into accumulator st & 1, one commit
                 for (int st = 0; st < n_wstages; ++st) {
                     const int aslot = st % ASLOTS;
-                    PROF_BEGIN(t0);
                     if (!mbar_wait_bounded(&sm.ready[aslot], (st / ASLOTS) & 1, abort_flag)) break;
-                    PROF_END(t0, 0);
                     tc_fence_after();
-                    PROF_BEGIN(t3);
                     const uint32_t d_addr = tmem_base + C::D_COL0 + (st & 1) * NB;
                     uint32_t a_addr = tmem_base + aslot * C::A_SLOT_COLS;
                     uint64_t bd = make_b_desc(smem_u32(&sm.b[aslot][0]), C::KCORE_BYTES, 128);
@@ -326,21 +320,14 @@ gemm_kernel(const __grid_constant__ GemmParams p)
                         a_addr += 16;
                         bd += 4 * kcore_step;
                     }
-                    PROF_END(t3, 3);
-                    PROF_BEGIN(t4);
                     tc_commit(&sm.done[st & 3]);
-                    PROF_END(t4, 4);
                 }
             } else
             for (int st = 0; st < n_wstages && ok; ++st) {
                 const int aslot = st % ASLOTS;
                 const int nb = min(WSTAGE_BLOCKS, total_blocks - st * WSTAGE_BLOCKS);
-                PROF_BEGIN(t0);
                 if (!mbar_wait_bounded(&sm.b_full[aslot], (st / ASLOTS) & 1, abort_flag)) { ok = false; break; }
-                PROF_END(t0, 0);
-                PROF_BEGIN(t2);
                 if (!mbar_wait_bounded(&sm.a_full[aslot], (st / ASLOTS) & 1, abort_flag)) { ok = false; break; }
-                PROF_END(t2, 2);
                 tc_fence_after();
                 uint32_t a_addr = tmem_base + aslot * C::A_SLOT_COLS;
                 // a block's four K cores sit C::KCORE_BYTES apart; 8-row groups 128 bytes apart
@@ -349,7 +336,6 @@ gemm_kernel(const __grid_constant__ GemmParams p)
                     // the stage is one scale group: eight MMAs into one fresh accumulator
                     const uint32_t d_addr = open_group();
                     if (!ok) break;
-                    PROF_BEGIN(t3);
 #pragma unroll
                     for (int bi = 0; bi < WSTAGE_BLOCKS; ++bi) {
                         if (bi < nb) {
@@ -359,10 +345,7 @@ gemm_kernel(const __grid_constant__ GemmParams p)
                         a_addr += 16;
                         bd += 4 * kcore_step;
                     }
-                    PROF_END(t3, 3);
-                    PROF_BEGIN(t4);
                     tc_commit(&sm.d_full[gq & 1]);
-                    PROF_END(t4, 4);
                     ++gq;
                 } else {
                     // every 32-block is a scale group
@@ -377,11 +360,8 @@ gemm_kernel(const __grid_constant__ GemmParams p)
                         bd += 4 * kcore_step;
                     }
                 }
-                PROF_BEGIN(t5);
                 tc_commit(&sm.ab_empty[aslot]);
-                PROF_END(t5, 4);
             }
-            PROF_FLUSH(1);
         }
         __syncwarp();
     } else if (warp < WARP_READ0) {
@@ -390,23 +370,17 @@ gemm_kernel(const __grid_constant__ GemmParams p)
         const int quarter = warp & 3;
         const int col = quarter * 32 + lane;
         const uint32_t lane_tmem = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        PROF_DECL;
         for (int st = 0; st < n_wstages; ++st) {
             const int wslot = st % WSTAGES;
             const int aslot = st % ASLOTS;
             const int nb = min(WSTAGE_BLOCKS, total_blocks - st * WSTAGE_BLOCKS);
-            PROF_BEGIN(t0);
             if (!wait_uniform(&sm.w_full[wslot], (st / WSTAGES) & 1, abort_flag)) break;
-            PROF_END(t0, 0);
-            PROF_BEGIN(t2);
             if (st >= ASLOTS) {        // the MMAs that read this slot's previous contents are done
                 uint64_t* bar = lean ? &sm.done[(st - ASLOTS) & 3] : &sm.ab_empty[aslot];
                 const uint32_t par = lean ? (((st - ASLOTS) >> 2) & 1) : (((st / ASLOTS) - 1) & 1);
                 if (!wait_uniform(bar, par, abort_flag)) break;
                 tc_fence_after();
             }
-            PROF_END(t2, 2);
-            PROF_BEGIN(t1);
 #pragma unroll
             for (int rr = 0; rr < WSTAGE_BLOCKS / DEQ_SETS; ++rr) {
                 const int r = set + rr * DEQ_SETS;                 // this set's blocks of the stage: set, set + 2
@@ -426,8 +400,6 @@ gemm_kernel(const __grid_constant__ GemmParams p)
                     tmem_st16(lane_tmem + aslot * C::A_SLOT_COLS + r * 16, regs);
                 }
             }
-            PROF_END(t1, 1);
-            PROF_BEGIN(t4);
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
@@ -435,9 +407,7 @@ gemm_kernel(const __grid_constant__ GemmParams p)
                 mbar_arrive(lean ? &sm.ready[aslot] : &sm.a_full[aslot]);   // this warp's share of the stage is in tensor memory
                 mbar_arrive(&sm.w_empty[wslot]);                             // and read out of the ring
             }
-            PROF_END(t4, 4);
         }
-        PROF_FLUSH(3);
     } else if (warp < WARP_TMA) {
         // ------------------------------------- per-group read-back and epilogue --
         const int quarter = warp & 3;
@@ -468,7 +438,6 @@ gemm_kernel(const __grid_constant__ GemmParams p)
             for (int i = tid - WARP_READ0 * 32; i < n_groups * NB / 4; i += EPI_THREADS) dst[i] = __ldg(src + i);
         }
         named_bar_sync(2, EPI_THREADS);
-        PROF_DECL;
         for (int gq = 0; gq < n_groups; ++gq) {
             // accumulator of scale group gq: acc += s * (2^24 D - 8 sum(a))
             const int db = gq & 1;
@@ -476,15 +445,12 @@ gemm_kernel(const __grid_constant__ GemmParams p)
             s_next = load_scale(gq + 1);
             const float4* a8p = a8_local ? reinterpret_cast<const float4*>(sm.a8 + gq * NB)
                                          : reinterpret_cast<const float4*>(p.tc_a8 + (size_t)(grow0 + gq) * NB);
-            PROF_BEGIN(t0);
             {
                 uint64_t* bar = lean ? &sm.done[gq & 3] : &sm.d_full[db];
                 const uint32_t par = lean ? ((gq >> 2) & 1) : ((gq >> 1) & 1);
                 if (!wait_uniform(bar, par, abort_flag)) { ok = false; break; }
             }
-            PROF_END(t0, 0);
             tc_fence_after();
-            PROF_BEGIN(t1);
 #pragma unroll
             for (int c0 = 0; c0 < RC; c0 += 8) {
                 if (row0 + c0 < p.M) {                                 // warp-uniform
@@ -501,9 +467,7 @@ gemm_kernel(const __grid_constant__ GemmParams p)
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(lean ? &sm.ready[(gq + 2) % ASLOTS] : &sm.d_empty[db]);   // the accumulator is free again
-            PROF_END(t1, 1);
         }
-        PROF_FLUSH(2);
         ok = ok && (*abort_flag == 0);
 
         auto store_c = [&](int m, float vv) {

@@ -114,7 +114,6 @@ gemv_kernel(const __grid_constant__ GemmParams p)
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    TL_MARK(p.launch_id, 0);
     const int n0 = blockIdx.x * NT;
     const int cols = min(NT, p.N - n0);
     const int b0 = blockIdx.y * p.blocks_per_split;
@@ -142,9 +141,6 @@ gemv_kernel(const __grid_constant__ GemmParams p)
     const int g = lane >> 2;
     const int t = lane & 3;
     const int wcol = warp * 16;                       // a consumer warp's 16 columns inside the tile
-#ifdef TWM_EXP_NOWAIT
-    if (warp >= CONSUMER_WARPS) return;          // development experiment: consumers run on whatever is in shared memory
-#endif
     if (warp == CONSUMER_WARPS) {
         // ------------------------------------------- producer: packed + scales --
         const uint8_t* packed = p.packed;
@@ -156,17 +152,13 @@ gemv_kernel(const __grid_constant__ GemmParams p)
         }
         const bool scale_bulk_ok = ((cols & 7) == 0) && ((p.N & 7) == 0) &&
                                    ((reinterpret_cast<uintptr_t>(scales + n0) & 15) == 0);
-        PROF_DECL;
         for (int it = 0; it < n_stages; ++it) {
             const int slot = it % STAGES;
             const int use = it / STAGES;
-            PROF_BEGIN(t0);
             if (use > 0) {
                 const bool got = mbar_wait_bounded(&sm.empty[slot], (use - 1) & 1, abort_flag);
                 if (!__all_sync(0xffffffffu, got)) break;
             }
-            PROF_END(t0, 0);
-            PROF_BEGIN(t1);
             const int bstart = b0 + it * SB;
             const int nb = min(SB, b1 - bstart);
             const int srow_first = bstart >> gshift;
@@ -201,9 +193,7 @@ gemv_kernel(const __grid_constant__ GemmParams p)
                          (uint32_t)cols * 2, &sm.full[slot]);
             }
             __syncwarp();
-            PROF_END(t1, 1);
         }
-        PROF_FLUSH(0);
     } else if (warp == CONSUMER_WARPS + 1) {
         // ------------------------------------------------ activation stager --
         // One item = 8 consecutive K of one row, stored as the 16 bytes
@@ -216,7 +206,7 @@ gemv_kernel(const __grid_constant__ GemmParams p)
         const __half* A = reinterpret_cast<const __half*>(p.a);
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(A) & 15) == 0) && ((p.lda & 7) == 0);
         constexpr int PF = 8;
-        for (int chunk = 0; chunk < n_chunks; ++chunk) {
+        for (int chunk = 1; chunk < n_chunks; ++chunk) {     // chunk 0 is staged by the consumer warps (below)
             const int buf = chunk & 1;
             const int use = chunk >> 1;
             const int cb0 = chunk * CHUNK_BLOCKS;
@@ -224,6 +214,7 @@ gemv_kernel(const __grid_constant__ GemmParams p)
             const int items = cb * MP * 4;                    // item = (((gi * MP) + m) << gshift | bj) * 4 + t
             bool waited = false, ok = true;
             for (int base = 0; base < items && ok; base += 32 * PF) {
+                const int live = min(PF, (items - base + 31) >> 5);     // rounds of 32 items that hold anything (warp-uniform)
                 uint4 x[PF];
 #pragma unroll
                 for (int u = 0; u < PF; ++u) {
@@ -256,6 +247,7 @@ gemv_kernel(const __grid_constant__ GemmParams p)
                 }
 #pragma unroll
                 for (int u = 0; u < PF; ++u) {
+                    if (u >= live) break;                            // nothing in the later rounds: skip their shuffles too
                     const int it = base + u * 32 + lane;
                     const int tt = it & 3;
                     const int bj = (it >> 2) & gmask;
@@ -294,14 +286,60 @@ gemv_kernel(const __grid_constant__ GemmParams p)
     // the per-stage work unrolls into straight-line code: per 32-block two
     // 32-bit loads, one 128-bit load, ten integer ops and two MMAs.
     constexpr int GB = 1 << GSHIFT;
-    if (warp == 0) { TL_MARK(p.launch_id, 1); }
+    {
+        // The first chunk of activations (at most 256 items) is staged by the 256 consumer threads,
+        // one item each, in the stager's layout and summation order: the launch's first multiply
+        // then waits for one round of loads instead of the stager warp's eight.
+        if (!p.no_wait) pdl_wait_prior_grids();
+        const __half* A = reinterpret_cast<const __half*>(p.a);
+        const bool vec_ok = ((reinterpret_cast<uintptr_t>(A) & 15) == 0) && ((p.lda & 7) == 0);
+        const int items = min(CHUNK_BLOCKS, total_blocks) * MP * 4;
+        const int it = tid;
+        const int tt = it & 3;
+        const int bj = (it >> 2) & gmask;
+        const int rest = it >> (2 + gshift);
+        const int m = rest % MP;
+        const int gi = rest / MP;
+        const int bi = (gi << gshift) + bj;
+        uint4 x = make_uint4(0, 0, 0, 0);
+        if (it < items && m < p.M) {
+            const size_t off = (size_t)m * p.lda + (size_t)(b0 + bi) * kBlockK + tt * 8;
+            if (vec_ok) {
+                x = *reinterpret_cast<const uint4*>(A + off);
+            } else {
+                const uint16_t* a16 = reinterpret_cast<const uint16_t*>(A) + off;
+                x.x = a16[0] | ((uint32_t)a16[1] << 16); x.y = a16[2] | ((uint32_t)a16[3] << 16);
+                x.z = a16[4] | ((uint32_t)a16[5] << 16); x.w = a16[6] | ((uint32_t)a16[7] << 16);
+            }
+        }
+        float s = 0.0f;
+        if (it < items) {
+            uint4 o;
+            o.x = __byte_perm(x.x, x.z, 0x5410); o.y = __byte_perm(x.y, x.w, 0x5410);
+            o.z = __byte_perm(x.x, x.z, 0x7632); o.w = __byte_perm(x.y, x.w, 0x7632);
+            *reinterpret_cast<uint4*>(&sm.b[0][((bi * MP + m) * 4 + tt) * 16]) = o;
+            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&x.x));
+            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&x.y));
+            const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&x.z));
+            const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&x.w));
+            s = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+        }
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        if (gshift != 0) {
+            s += __shfl_xor_sync(0xffffffffu, s, 4);
+            s += __shfl_xor_sync(0xffffffffu, s, 8);
+        }
+        if (it < items && (it & ((4 << gshift) - 1)) == 0) sm.asum8[0][gi][m] = -8.0f * s;
+        named_bar_sync(1, CONSUMERS);
+        if (tid == 0) mbar_arrive(&sm.b_full[0]);
+    }
     const float zero4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     const uint32_t w_base = smem_u32(&sm.packed[0][0]) + wcol * kBlockBytes + lane * 4;
     const uint32_t s_base = smem_u32(&sm.scales[0][0][0]) + (wcol + g) * 2;
     const uint32_t b_base = smem_u32(&sm.b[0][0]) + (g * 4 + t) * 16;
     const uint32_t a8_base = smem_u32(&sm.asum8[0][0][0]) + t * 8;
     bool ok = true;
-    PROF_DECL;
 
     for (int it = 0; it < n_stages; ++it) {
         const int slot = it % STAGES;
@@ -310,26 +348,15 @@ gemv_kernel(const __grid_constant__ GemmParams p)
         const int chunk = rel0 / CHUNK_BLOCKS;
         const int buf = chunk & 1;
         const int bi0 = rel0 - chunk * CHUNK_BLOCKS;                  // first block of the stage inside the chunk
-#ifndef TWM_EXP_NOWAIT
-        PROF_BEGIN(t0);
         if (ok && bi0 == 0) {
             const bool got = mbar_wait_bounded(&sm.b_full[buf], (chunk >> 1) & 1, abort_flag);
             if (!__all_sync(0xffffffffu, got)) ok = false;
         }
-        PROF_END(t0, 0);
-        PROF_BEGIN(t1);
         if (ok) {
             const bool got = mbar_wait_bounded(&sm.full[slot], (it / STAGES) & 1, abort_flag);
             if (!__all_sync(0xffffffffu, got)) ok = false;
         }
-        PROF_END(t1, 1);
-#endif
-        PROF_BEGIN(t2);
-#ifdef TWM_EXP_NOCOMPUTE
-        if (false) {
-#else
         if (ok) {
-#endif
             const uint32_t w_st = w_base + slot * (SB * NT * kBlockBytes);
             const uint32_t s_st = s_base + slot * (SB * NT * 2);
             const uint32_t b_st = b_base + buf * B_BUF_BYTES + bi0 * (MP * 64);
@@ -367,17 +394,13 @@ gemv_kernel(const __grid_constant__ GemmParams p)
                 }
             }
         }
-        PROF_END(t2, 2);
-        PROF_BEGIN(t3);
         __syncwarp();
         if (lane == 0) {
             if (ok) mbar_arrive(&sm.empty[slot]);
             const bool chunk_end = ((rel0 + SB) % CHUNK_BLOCKS == 0) || (it == n_stages - 1);
             if (ok && chunk_end) mbar_arrive(&sm.b_empty[buf]);
         }
-        PROF_END(t3, 3);
     }
-    PROF_FLUSH(1);
 
     }   // consumers
 
@@ -449,7 +472,6 @@ gemv_kernel(const __grid_constant__ GemmParams p)
             __syncthreads();
             if (tid == 0) comm_cta_done(gridDim.x);
         }
-        TL_MARK(p.launch_id, 3);
         return;
     }
 
@@ -464,7 +486,6 @@ gemv_kernel(const __grid_constant__ GemmParams p)
             named_bar_sync(1, CONSUMERS);
             if (tid == 0) comm_cta_done(gridDim.x * gridDim.y);
         }
-        TL_MARK(p.launch_id, 3);
         return;
     }
     auto ws_at = [&](int sp, int m, int n) -> float* { return &p.ws_partials[((size_t)sp * p.M + m) * p.N + n]; };

@@ -12,12 +12,14 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <new>
+#include <vector>
 
 #include "twm_common.cuh"
 #include "twm_gemv_simt.cuh"
 #include "twm_gemm_tc.cuh"
 #include "twm_gemv_mma.cuh"
-#include "twm_gemv_strip.cuh"
+#include "twm_chain.cuh"
 #include "twm_layout.cuh"
 #include "twm_decode_ops.cuh"
 #include "../../include/twm_decode.h"
@@ -25,9 +27,6 @@
 namespace {
 
 thread_local char t_last_error[256] = "";
-#ifdef TWM_TIMELINE
-int g_launch_counter = 0;     // development builds only
-#endif
 
 void set_error(const char* where, cudaError_t e)
 {
@@ -105,18 +104,14 @@ twm_status ensure_device(int* sm_count_out)
             raise_mma((const void*)twm::mma::gemv_kernel<2, 2>);
             raise_mma((const void*)twm::mma::gemv_kernel<4, 2>);
             raise_mma((const void*)twm::mma::gemv_kernel<8, 2>);
-            auto raise_strip = [&](const void* fn) {
+            auto raise_chain = [&](const void* fn) {
                 if (r == cudaSuccess)
-                    r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, twm::strip::SMEM_BUDGET);
+                    r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(twm::chain::Smem));
             };
-            raise_strip((const void*)twm::strip::gemv_kernel<1, 0>);
-            raise_strip((const void*)twm::strip::gemv_kernel<2, 0>);
-            raise_strip((const void*)twm::strip::gemv_kernel<4, 0>);
-            raise_strip((const void*)twm::strip::gemv_kernel<8, 0>);
-            raise_strip((const void*)twm::strip::gemv_kernel<1, 2>);
-            raise_strip((const void*)twm::strip::gemv_kernel<2, 2>);
-            raise_strip((const void*)twm::strip::gemv_kernel<4, 2>);
-            raise_strip((const void*)twm::strip::gemv_kernel<8, 2>);
+            raise_chain((const void*)twm::chain::chain_kernel<1>);
+            raise_chain((const void*)twm::chain::chain_kernel<2>);
+            raise_chain((const void*)twm::chain::chain_kernel<4>);
+            raise_chain((const void*)twm::chain::chain_kernel<8>);
             if (r != cudaSuccess) { set_error("cudaFuncSetAttribute", r); st.status = TWM_ELAUNCH; }
         }
         st.ready = true;
@@ -153,20 +148,6 @@ bool make_packed_map(CUtensorMap* map, const uint8_t* packed, int N, int nkb, in
     const cuuint32_t box[2] = {(cuuint32_t)cols * 2, (cuuint32_t)rows};
     const cuuint32_t estride[2] = {1, 1};
     return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t*>(packed), gdim, gstride, box, estride,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-// Tensor map over the scales, f16 [K/G rows][N] (N a multiple of 8): box = `cols` x `rows`.
-bool make_scale_map(CUtensorMap* map, const uint16_t* scales, int N, int n_rows, int rows, int cols)
-{
-    EncodeTiledFn enc = get_encode_tiled();
-    if (!enc || (N & 7)) return false;
-    const cuuint64_t gdim[2] = {(cuuint64_t)N, (cuuint64_t)n_rows};
-    const cuuint64_t gstride[1] = {(cuuint64_t)N * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)cols, (cuuint32_t)rows};
-    const cuuint32_t estride[2] = {1, 1};
-    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<uint16_t*>(scales), gdim, gstride, box, estride,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -234,24 +215,12 @@ void choose_splits(int n_tiles, int nkb, int slots, int sm_count, int max_bps, i
 
 int mmax_for(int M) { return M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : 8)); }
 
-// Which kernel serves FP16 activations when the caller leaves the choice open.  The strip
-// kernel wants enough 32-column strips to occupy most SMs (it never splits K), scale rows that
-// a tensor map can describe (N a multiple of 8) and weights addressed directly.
-// The rows' activations for the whole K must fit in shared memory beside the weight ring.
-constexpr int kStripMinStrips = 96;
-bool strip_fits(int M, int K, int G) { return twm::strip::pick_stages(K / 32, G, mmax_for(std::min(M, 8))) > 0; }
-bool strip_eligible(int M, int N, int K, int G, bool indirect)
-{
-    return !indirect && (N & 7) == 0 && (N + twm::strip::NT - 1) / twm::strip::NT >= kStripMinStrips && strip_fits(M, K, G);
-}
 // Measured on the 7B gate+up shape (us per launch in a dependent chain): the streaming MMA kernel
 // 15.7 / 16.2 / 20.3 / 30.7 at M = 1 / 2 / 4 / 8, the tcgen05 kernel 26-27 for any M up to 16.
 constexpr int kTcFromRows = 5;
 int auto_kernel(int M, int N, int K, int G, bool a_is_f16, bool indirect, int splits_override)
 {
     if (!a_is_f16) return TWM_KERNEL_SIMT;
-    // The strip kernel is not chosen here: measured on the 7B decode chain it is slower than the
-    // split-K kernel (one CTA per SM cannot unpack at HBM rate); it runs when asked for by name.
     (void)N; (void)K; (void)G; (void)indirect; (void)splits_override;
     return M >= kTcFromRows ? TWM_KERNEL_TC : TWM_KERNEL_MMA;
 }
@@ -273,44 +242,6 @@ int resolve_kernel(const twm_gemm_args* a)
     return kernel;
 }
 
-template <int MP, int GS>
-cudaError_t launch_strip_one(cudaLaunchConfig_t& cfg, const twm::GemmParams& p)
-{
-    cfg.dynamicSmemBytes = twm::strip::make_layout(p.nkb, p.group, MP, p.strip_stages).total;
-    return cudaLaunchKernelEx(&cfg, twm::strip::gemv_kernel<MP, GS>, p);
-}
-
-twm_status launch_strip(const twm::GemmParams& p, int mp, dim3 grid, bool pdl, cudaStream_t stream)
-{
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(twm::strip::THREADS, 1, 1);
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
-    cudaError_t e;
-    if (p.group == 128) {
-        switch (mp) {
-            case 1: e = launch_strip_one<1, 2>(cfg, p); break;
-            case 2: e = launch_strip_one<2, 2>(cfg, p); break;
-            case 4: e = launch_strip_one<4, 2>(cfg, p); break;
-            default: e = launch_strip_one<8, 2>(cfg, p); break;
-        }
-    } else {
-        switch (mp) {
-            case 1: e = launch_strip_one<1, 0>(cfg, p); break;
-            case 2: e = launch_strip_one<2, 0>(cfg, p); break;
-            case 4: e = launch_strip_one<4, 0>(cfg, p); break;
-            default: e = launch_strip_one<8, 0>(cfg, p); break;
-        }
-    }
-    if (e != cudaSuccess) { set_error("launch strip::gemv_kernel", e); return TWM_ELAUNCH; }
-    return TWM_OK;
-}
 constexpr int kTcRows = 64;      // activation rows one tcgen05 launch carries
 
 twm_status launch_tc(const twm::GemmParams& p, int rows, dim3 grid, bool pdl, cudaStream_t stream)
@@ -468,21 +399,6 @@ twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int split
     const int nkb = K / 32;
     int kernel = kernel_override;
     if (kernel == TWM_KERNEL_AUTO) kernel = auto_kernel(M, N, K, group_size, true, false, splits_override);
-    if (kernel == TWM_KERNEL_STRIP) {
-        // one CTA per SM at most, each taking whole strips in turn: no K slices, no workspace
-        if ((N & 7) != 0 || splits_override > 1 || !strip_fits(M, K, group_size)) return TWM_EINVAL;
-        const int n_strips = (N + twm::strip::NT - 1) / twm::strip::NT;
-        const int rounds = (n_strips + sm_count - 1) / sm_count;
-        out->kernel = kernel;
-        out->n_tile = twm::strip::NT;
-        out->splits = 1;
-        out->blocks_per_split = nkb;
-        out->grid_x = (n_strips + rounds - 1) / rounds;
-        out->grid_y = 1;
-        out->workspace_bytes = 0;
-        out->cluster_reduce = 0;
-        return TWM_OK;
-    }
     if (kernel != TWM_KERNEL_SIMT && kernel != TWM_KERNEL_TC && kernel != TWM_KERNEL_MMA) return TWM_EINVAL;
     // rows one launch carries; more rows are served by further launches
     const int rows = std::min(M, kernel == TWM_KERNEL_TC ? kTcRows : 8);
@@ -554,7 +470,6 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
     // reference's own signature) run on the FP32 streaming kernel.
     const int kernel = resolve_kernel(a);
     if (kernel != TWM_KERNEL_SIMT && a->a_dtype != TWM_F16) return TWM_EINVAL;
-    if (kernel == TWM_KERNEL_STRIP && a->packed_offsets != nullptr) return TWM_EINVAL;
     twm_plan_t pl;
     st = twm_plan(a->M, a->N, a->K, a->group_size, sm_count, a->splits_override, kernel, &pl);
     if (st != TWM_OK) return st;
@@ -567,8 +482,7 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
         // pushing the result to tensor-parallel peers: streaming MMA kernel, no workspace-based split
         const twm_comm* cm = a->comm;
         const bool mma_ok = kernel == TWM_KERNEL_MMA && a->M <= twm::mma::CLUSTER_ROWS && (pl.splits == 1 || pl.cluster_reduce);
-        const bool strip_ok = kernel == TWM_KERNEL_STRIP && a->M <= 8;
-        if (!mma_ok && !strip_ok) return TWM_EINVAL;
+        if (!mma_ok) return TWM_EINVAL;
         if (cm->n_ranks < 1 || cm->n_ranks > 8 || cm->rank < 0 || cm->rank >= cm->n_ranks || !cm->state) return TWM_EINVAL;
         if (cm->slot_elems < (long)a->M * a->ldc) return TWM_EINVAL;
     }
@@ -576,17 +490,9 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
     const size_t a_elt = a->a_dtype == TWM_F16 ? 2 : 4;
     const size_t c_elt = a->c_dtype == TWM_F16 ? 2 : 4;
     const int row_step = kernel == TWM_KERNEL_TC ? kTcRows : 8;
-    CUtensorMap packed_map, scale_map;
+    CUtensorMap packed_map;
     int map_rows = 0;
-    if (kernel == TWM_KERNEL_STRIP) {
-        const int srows = twm::strip::SBLK / (a->group_size / 32);
-        if (!make_packed_map(&packed_map, a->packed, a->N, a->K / 32, twm::strip::SBLK, twm::strip::NT) ||
-            !make_scale_map(&scale_map, a->scales, a->N, a->K / a->group_size, srows, twm::strip::NT)) {
-            snprintf(t_last_error, sizeof(t_last_error), "cuTensorMapEncodeTiled failed for the strip kernel's maps");
-            return TWM_ELAUNCH;
-        }
-        map_rows = twm::strip::SBLK;
-    } else if (a->packed_offsets == nullptr && a->N >= 128 && kernel != TWM_KERNEL_SIMT) {
+    if (a->packed_offsets == nullptr && a->N >= 128 && kernel != TWM_KERNEL_SIMT) {
         const int want = kernel == TWM_KERNEL_MMA ? twm::mma::SB : twm::tc::WSTAGE_BLOCKS;
         if (make_packed_map(&packed_map, a->packed, a->N, a->K / 32, want)) map_rows = want;
     }
@@ -613,14 +519,7 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
             p.comm_state = a->comm->state;
         }
         p.map_rows = map_rows;
-#ifdef TWM_TIMELINE
-        p.launch_id = g_launch_counter++;
-#endif
         if (map_rows) p.packed_map = packed_map;
-        if (kernel == TWM_KERNEL_STRIP) {
-            p.scale_map = scale_map;
-            p.strip_stages = twm::strip::pick_stages(p.nkb, p.group, mmax_for(rows));
-        }
         const bool pdl = (a->flags & TWM_FLAG_PDL) != 0;
         if (kernel == TWM_KERNEL_TC) {
             // pre-pass: this launch's rows in [K/8][rows][8] order, then the GEMM loads them by TMA
@@ -642,8 +541,6 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
             if (st != TWM_OK) return st;
             st = launch_tc(p, rows, dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
         }
-        else if (kernel == TWM_KERNEL_STRIP)
-            st = launch_strip(p, mmax_for(rows), dim3(pl.grid_x, 1, 1), pdl, stream);
         else if (kernel == TWM_KERNEL_MMA)
             st = launch_mma(p, mmax_for(rows), dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
         else
@@ -691,6 +588,231 @@ twm_status twm_gemm_w4a16_static_ws(const twm_gemm_args* a, void* stream_)
 }
 
 size_t twm_static_ws_capacity(void) { return kStaticWsBytes; }
+
+// ------------------------------------------------------------------ GEMM chains --
+struct twm_chain {
+    int device = 0;
+    int count = 0;
+    int grid = 0;
+    int rows = 1;                 // MP of the kernel
+    void* mem = nullptr;          // one allocation: state, counters, partials, GEMM table
+    size_t bytes = 0;
+    twm::chain::State* state = nullptr;
+    unsigned int* done = nullptr;
+    twm::chain::Op* ops = nullptr;
+    int split_tiles = 0;
+    int max_pieces = 1;
+};
+
+namespace {
+size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+const void* chain_kernel_for(int rows)
+{
+    switch (rows) {
+        case 1: return (const void*)twm::chain::chain_kernel<1>;
+        case 2: return (const void*)twm::chain::chain_kernel<2>;
+        case 4: return (const void*)twm::chain::chain_kernel<4>;
+        default: return (const void*)twm::chain::chain_kernel<8>;
+    }
+}
+}  // namespace
+
+twm_status twm_chain_partition(int n_tiles, int nkb, int grid, int rank, int max_out, int* out5, int* n_out)
+{
+    if (n_tiles < 1 || nkb < 1 || grid < 1 || rank < 0 || rank >= grid || max_out < 0 || !n_out || (max_out > 0 && !out5))
+        return TWM_EINVAL;
+    const int upt = (nkb + twm::chain::UNIT - 1) / twm::chain::UNIT;
+    const long long total = (long long)n_tiles * upt;
+    if (total > 0x7fffffffLL) return TWM_EINVAL;
+    const int ranks = (int)std::min<long long>(grid, total);
+    twm::chain::Walker w;
+    w.start(rank, (int)total, ranks, upt, nkb);
+    twm::chain::Piece pc;
+    int n = 0;
+    while (w.next(pc)) {
+        if (n < max_out) {
+            int* o = out5 + 5 * n;
+            o[0] = pc.tile; o[1] = pc.blk0; o[2] = pc.blk1; o[3] = pc.slot; o[4] = pc.n_pieces;
+        }
+        ++n;
+    }
+    *n_out = n;
+    return TWM_OK;
+}
+
+twm_status twm_chain_create(const twm_chain_op* ops, int count, twm_chain** out)
+{
+    if (!ops || !out || count < 1 || count > 4096) return TWM_EINVAL;
+    *out = nullptr;
+    int sm_count = kDefaultSms;
+    twm_status st = ensure_device(&sm_count);
+    if (st != TWM_OK) return st;
+    int max_m = 1;
+    for (int i = 0; i < count; ++i) {
+        const twm_gemm_args& a = ops[i].gemm;
+        if (!shape_ok(a.M, a.N, a.K, a.group_size) || a.M > 8) return TWM_EINVAL;
+        if (!a.a || !a.packed || !a.scales || !a.c) return TWM_EINVAL;
+        if (a.a_dtype != TWM_F16 || (a.c_dtype != TWM_F32 && a.c_dtype != TWM_F16)) return TWM_EINVAL;
+        if (ops[i].a_prologue != TWM_A_PLAIN && ops[i].a_prologue != TWM_A_SILU_MUL) return TWM_EINVAL;
+        if (a.lda < (ops[i].a_prologue == TWM_A_SILU_MUL ? 2L * a.K : (long)a.K) || a.ldc < a.N) return TWM_EINVAL;
+        if (a.packed_offsets || a.scales_offsets || a.comm || a.splits_override || a.kernel_override) return TWM_EINVAL;
+        if (reinterpret_cast<uintptr_t>(a.packed) & 15) return TWM_EALIGN;
+        if ((reinterpret_cast<uintptr_t>(a.scales) & 1) || (reinterpret_cast<uintptr_t>(a.a) & 1)) return TWM_EALIGN;
+        if (reinterpret_cast<uintptr_t>(a.c) & (a.c_dtype == TWM_F16 ? 1 : 3)) return TWM_EALIGN;
+        max_m = std::max(max_m, a.M);
+    }
+    twm_chain* ch = new (std::nothrow) twm_chain();
+    if (!ch) return TWM_ELAUNCH;
+    cudaGetDevice(&ch->device);
+    ch->count = count;
+    ch->rows = mmax_for(max_m);
+    int per_sm = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, chain_kernel_for(ch->rows), twm::chain::THREADS,
+                                                                  sizeof(twm::chain::Smem));
+    if (e != cudaSuccess || per_sm < 1) {
+        if (e != cudaSuccess) set_error("cudaOccupancyMaxActiveBlocksPerMultiprocessor(chain_kernel)", e);
+        else snprintf(t_last_error, sizeof(t_last_error), "chain_kernel does not fit on an SM");
+        delete ch;
+        return TWM_ELAUNCH;
+    }
+    ch->grid = sm_count * std::min(per_sm, twm::chain::CTAS_PER_SM);
+
+    // the deal of every GEMM: pieces per tile decide the partial scratch
+    std::vector<twm::chain::Op> table(count);
+    std::vector<size_t> part_off(count), cnt_off(count);
+    size_t part_bytes = 0, n_counters = 0;
+    int dependent_from = 0;          // first GEMM a dependent GEMM must wait for
+    for (int i = 0; i < count; ++i) {
+        const twm_gemm_args& a = ops[i].gemm;
+        twm::chain::Op& op = table[i];
+        memset(&op, 0, sizeof(op));
+        op.packed = a.packed; op.scales = a.scales; op.a = a.a; op.c = a.c;
+        op.lda = a.lda; op.ldc = a.ldc;
+        op.M = a.M; op.N = a.N; op.K = a.K; op.nkb = a.K / 32;
+        op.gshift = a.group_size == 128 ? 2 : 0;
+        op.n_tiles = (a.N + twm::chain::NT - 1) / twm::chain::NT;
+        op.units_per_tile = (op.nkb + twm::chain::UNIT - 1) / twm::chain::UNIT;
+        const long long total = (long long)op.n_tiles * op.units_per_tile;
+        if (total > 0x7fffffffLL) { delete ch; return TWM_EINVAL; }
+        op.total_units = (int)total;
+        op.ranks = (int)std::min<long long>(ch->grid, total);
+        op.rot = (int)(((long long)i * 97) % ch->grid);
+        op.a_kind = ops[i].a_prologue == TWM_A_SILU_MUL ? twm::chain::A_SILU_MUL : twm::chain::A_F16;
+        op.c_is_f16 = a.c_dtype == TWM_F16;
+        op.accumulate = (a.flags & TWM_FLAG_ACCUMULATE) ? 1 : 0;
+        if (a.flags & TWM_FLAG_INDEPENDENT) {
+            op.wait_from = i;                       // waits for nothing
+        } else {
+            op.wait_from = dependent_from;          // everything since (and including) the last dependent GEMM
+            dependent_from = i;
+        }
+        op.use_maps = 0;
+        if (a.N >= 128 && make_packed_map(&op.map8, a.packed, a.N, op.nkb, twm::chain::SB) &&
+            make_packed_map(&op.map4, a.packed, a.N, op.nkb, twm::chain::UNIT))
+            op.use_maps = 1;
+        int max_pieces = 1;
+        for (int t = 0; t < op.n_tiles; ++t) {
+            const int first = twm::chain::rank_of_unit((long long)t * op.units_per_tile, op.total_units, op.ranks);
+            const int last = twm::chain::rank_of_unit((long long)(t + 1) * op.units_per_tile - 1, op.total_units, op.ranks);
+            const int pieces = last - first + 1;
+            max_pieces = std::max(max_pieces, pieces);
+            if (pieces > 1) ++ch->split_tiles;
+        }
+        op.max_pieces = max_pieces;
+        ch->max_pieces = std::max(ch->max_pieces, max_pieces);
+        part_off[i] = part_bytes;
+        if (max_pieces > 1) part_bytes += round_up((size_t)op.n_tiles * max_pieces * a.M * twm::chain::NT * sizeof(float), 256);
+        cnt_off[i] = n_counters;
+        n_counters += op.n_tiles;
+    }
+    const size_t off_done = sizeof(twm::chain::State);
+    const size_t off_cnt = off_done + round_up((size_t)count * 4, 256);
+    const size_t off_part = off_cnt + round_up(n_counters * 4, 256);
+    const size_t off_ops = off_part + part_bytes;
+    ch->bytes = off_ops + (size_t)count * sizeof(twm::chain::Op);
+    e = cudaMalloc(&ch->mem, ch->bytes);
+    if (e == cudaSuccess) e = cudaMemset(ch->mem, 0, off_part);      // state and counters start at zero
+    if (e != cudaSuccess) {
+        set_error("twm_chain_create (allocation)", e);
+        if (ch->mem) cudaFree(ch->mem);
+        delete ch;
+        return TWM_ELAUNCH;
+    }
+    char* base = (char*)ch->mem;
+    ch->state = (twm::chain::State*)base;
+    ch->done = (unsigned int*)(base + off_done);
+    ch->ops = (twm::chain::Op*)(base + off_ops);
+    for (int i = 0; i < count; ++i) {
+        table[i].partials = (float*)(base + off_part + part_off[i]);
+        table[i].tile_counters = (unsigned int*)(base + off_cnt) + cnt_off[i];
+    }
+    twm::chain::State hs;
+    memset(&hs, 0, sizeof(hs));
+    hs.n_tile_counters = (unsigned int)n_counters;
+    hs.all_tile_counters = (unsigned int*)(base + off_cnt);
+    e = cudaMemcpy(ch->state, &hs, sizeof(hs), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(ch->ops, table.data(), (size_t)count * sizeof(twm::chain::Op), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        set_error("twm_chain_create (copy)", e);
+        cudaFree(ch->mem);
+        delete ch;
+        return TWM_ELAUNCH;
+    }
+    *out = ch;
+    return TWM_OK;
+}
+
+twm_status twm_chain_launch(twm_chain* ch, void* stream_)
+{
+    if (!ch || !ch->mem) return TWM_EINVAL;
+    int dev = -1;
+    cudaGetDevice(&dev);
+    if (dev != ch->device) {
+        snprintf(t_last_error, sizeof(t_last_error), "twm_chain_launch: the chain was created on device %d, current device is %d",
+                 ch->device, dev);
+        return TWM_ELAUNCH;
+    }
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(ch->grid, 1, 1);
+    cfg.blockDim = dim3(twm::chain::THREADS, 1, 1);
+    cfg.dynamicSmemBytes = sizeof(twm::chain::Smem);
+    cfg.stream = (cudaStream_t)stream_;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;     // the CTAs wait on one another: all of them must be resident
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const twm::chain::Op* ops = ch->ops;
+    cudaError_t e;
+    switch (ch->rows) {
+        case 1: e = cudaLaunchKernelEx(&cfg, twm::chain::chain_kernel<1>, ops, ch->count, ch->state, ch->done); break;
+        case 2: e = cudaLaunchKernelEx(&cfg, twm::chain::chain_kernel<2>, ops, ch->count, ch->state, ch->done); break;
+        case 4: e = cudaLaunchKernelEx(&cfg, twm::chain::chain_kernel<4>, ops, ch->count, ch->state, ch->done); break;
+        default: e = cudaLaunchKernelEx(&cfg, twm::chain::chain_kernel<8>, ops, ch->count, ch->state, ch->done); break;
+    }
+    if (e != cudaSuccess) { set_error("launch chain::chain_kernel", e); return TWM_ELAUNCH; }
+    return TWM_OK;
+}
+
+twm_status twm_chain_info(const twm_chain* ch, twm_chain_info_t* out)
+{
+    if (!ch || !out) return TWM_EINVAL;
+    out->count = ch->count; out->grid = ch->grid; out->rows = ch->rows; out->device_bytes = ch->bytes;
+    out->split_tiles = ch->split_tiles; out->max_pieces = ch->max_pieces;
+    return TWM_OK;
+}
+
+twm_status twm_chain_destroy(twm_chain* ch)
+{
+    if (!ch) return TWM_EINVAL;
+    cudaError_t e = ch->mem ? cudaFree(ch->mem) : cudaSuccess;
+    delete ch;
+    if (e != cudaSuccess) { set_error("twm_chain_destroy", e); return TWM_ELAUNCH; }
+    return TWM_OK;
+}
 
 twm_status twm_dequant(const uint8_t* packed, const uint16_t* scales, void* out, int out_dtype,
                        int K, int N, int group_size, void* stream_)
@@ -919,15 +1041,38 @@ twm_status twm_comm_layout(void* base, int n_ranks, long slot_elems, float** dat
 twm_status twm_allreduce_add_rmsnorm(void* y, float* x, const twm_comm* comm, const float* gamma, int rows, int hidden,
                                      float eps, int flags, void* stream)
 {
-    if (!x || !comm || (y && !gamma) || rows < 1 || hidden < 1) return TWM_EINVAL;
+    if (!x || !comm || (y && !gamma) || rows < 1 || rows > 65535 || hidden < 1) return TWM_EINVAL;
     if (comm->n_ranks < 1 || comm->n_ranks > 8 || comm->rank < 0 || comm->rank >= comm->n_ranks) return TWM_EINVAL;
     if (comm->slot_elems < (long)rows * hidden || (hidden & 3) || (comm->slot_elems & 3)) return TWM_EINVAL;
+    if (hidden > 4 * twm::ops::RMS_SEG_VECS * twm::ops::ARN_MAX_SEGS) return TWM_EINVAL;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (gamma && (reinterpret_cast<uintptr_t>(gamma) & 15)) ||
+        (y && (reinterpret_cast<uintptr_t>(y) & 7)))
+        return TWM_EALIGN;
     twm_status st = ensure_device(nullptr);
     if (st != TWM_OK) return st;
-    return launch_op("twm_allreduce_add_rmsnorm", twm::ops::allreduce_add_rmsnorm_kernel, dim3(rows),
-                     dim3(twm::ops::ARN_THREADS), 0, flags,
-                     stream, (__half*)y, x, (const float*)comm->data[comm->rank], (const unsigned int*)comm->flags[comm->rank],
-                     comm->state, gamma, hidden, eps, comm->n_ranks, comm->slot_elems);
+    // one 256-vector segment of the row per CTA up to eight CTAs (one cluster per row), two beyond that
+    const int nseg = (hidden / 4 + twm::ops::RMS_SEG_VECS - 1) / twm::ops::RMS_SEG_VECS;
+    const int ncta = std::min(nseg, 8);
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(ncta, rows, 1);
+    cfg.blockDim = dim3(twm::ops::ARN_THREADS, 1, 1);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ncta;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (flags & TWM_FLAG_PDL) ? 2 : 1;
+    const unsigned long long wait_ns = comm->wait_ns ? comm->wait_ns : 2000000000ull;     // two seconds unless the caller says otherwise
+    cudaError_t e = cudaLaunchKernelEx(&cfg, twm::ops::allreduce_add_rmsnorm_kernel, (__half*)y, x,
+                                       (const float*)comm->data[comm->rank], (const unsigned int*)comm->flags[comm->rank],
+                                       comm->state, gamma, hidden, eps, comm->n_ranks, comm->slot_elems, wait_ns);
+    if (e != cudaSuccess) { set_error("twm_allreduce_add_rmsnorm", e); return TWM_ELAUNCH; }
+    return TWM_OK;
 }
 
 twm_status twm_ipc_alloc(size_t bytes, void** ptr)
@@ -1008,24 +1153,11 @@ const char* twm_status_string(twm_status s)
     return "unknown status";
 }
 
-#ifdef TWM_TIMELINE
-int twm_timeline_reset(void) { g_launch_counter = 0; return 0; }
-int twm_timeline_read(unsigned long long* out, int n)
+#ifdef TWM_CHAIN_TL
+int twm_chain_timeline_read(unsigned long long* out, int n)
 {
     cudaDeviceSynchronize();
-    return cudaMemcpyFromSymbol(out, twm::g_timeline, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : -1;
-}
-#endif
-
-#ifdef TWM_PROF
-// development builds only: read and clear the per-role cycle counters
-int twm_prof_read(unsigned long long* out)
-{
-    cudaDeviceSynchronize();
-    unsigned long long zero[64] = {0};
-    if (cudaMemcpyFromSymbol(out, twm::g_prof, sizeof(zero)) != cudaSuccess) return -1;
-    cudaMemcpyToSymbol(twm::g_prof, zero, sizeof(zero));
-    return 0;
+    return cudaMemcpyFromSymbol(out, twm::chain::g_chain_tl, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : -1;
 }
 #endif
 

@@ -217,6 +217,87 @@ def slice_tw_marlin_k(packed: torch.Tensor, scales: torch.Tensor, k: int, n: int
     return p, s
 
 
+class GemmChain:
+    """A list of GEMMs that run, in order, as ONE persistent launch (``twm_chain_*``).
+
+    The reference enqueues the four GEMMs of a layer one kernel at a time
+    (generate.rs:2149-2206); a chain keeps the weight stream going across the boundaries
+    between them.  ``add`` takes the arguments of ``gemm_tw_marlin``; ``build`` is the set-up
+    call (allocates); ``launch`` only enqueues."""
+
+    def __init__(self):
+        self._ops = []
+        self._keep = []            # the tensors the device-side table points at
+        self._handle = None
+
+    def add(self, a: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, c: torch.Tensor, m: int, n: int, k: int,
+            *, group_size: int = BLOCK_SIZE, flags: int = 0, silu_mul: bool = False) -> "GemmChain":
+        """C[m,n] (+)= A x dequant(packed, scales).  With ``silu_mul`` A is the fused gate+up
+        output [m, 2k] and the GEMM reads silu(gate) * up."""
+        if self._handle is not None:
+            raise TwmError(_lib.TWM_EINVAL, "GemmChain.add after build")
+        _require_cuda(a, packed, scales, c)
+        if a.dtype != torch.float16 or c.dtype not in _DTYPES:
+            raise TwmError(_lib.TWM_EINVAL, "GemmChain.add: A must be float16, C float16 or float32")
+        need_a = m * k * (2 if silu_mul else 1)
+        if a.numel() < need_a or c.numel() < m * n:
+            raise TwmError(_lib.TWM_EINVAL, "GemmChain.add: A or C smaller than the stated shape")
+        if packed.numel() < (k // 32) * n * 16 or scales.numel() < (k // group_size) * n:
+            raise TwmError(_lib.TWM_EINVAL, "GemmChain.add: packed or scales smaller than the stated shape")
+        lda = a.stride(0) if a.dim() == 2 else k * (2 if silu_mul else 1)
+        ldc = c.stride(0) if c.dim() == 2 else n
+        op = _lib.ChainOp()
+        op.gemm = GemmArgs(M=m, N=n, K=k, group_size=group_size, a_dtype=_lib.TWM_F16, c_dtype=_DTYPES[c.dtype],
+                           a=a.data_ptr(), lda=lda, packed=packed.data_ptr(), scales=scales.data_ptr(),
+                           c=c.data_ptr(), ldc=ldc, flags=flags)
+        op.a_prologue = _lib.TWM_A_SILU_MUL if silu_mul else _lib.TWM_A_PLAIN
+        self._ops.append(op)
+        self._keep.append((a, packed, scales, c))
+        return self
+
+    def build(self) -> "GemmChain":
+        n = len(self._ops)
+        arr = (_lib.ChainOp * n)(*self._ops)
+        h = C.c_void_p()
+        check(_lib.lib().twm_chain_create(arr, n, C.byref(h)), "twm_chain_create")
+        self._handle = h
+        return self
+
+    @property
+    def info(self) -> "_lib.ChainInfo":
+        out = _lib.ChainInfo()
+        check(_lib.lib().twm_chain_info(self._handle, C.byref(out)), "twm_chain_info")
+        return out
+
+    def launch(self, stream: Optional[torch.cuda.Stream] = None) -> None:
+        if self._handle is None:
+            self.build()
+        check(_lib.lib().twm_chain_launch(self._handle, _stream_ptr(stream)), "twm_chain_launch")
+
+    def close(self) -> None:
+        if self._handle is not None:
+            _lib.lib().twm_chain_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def chain_partition(n_tiles: int, nkb: int, grid: int, rank: int):
+    """The pieces (tile, blk0, blk1, slot, n_pieces) a chain gives `rank` of `grid` for one GEMM."""
+    cap = 64
+    while True:
+        buf = (C.c_int * (5 * cap))()
+        n = C.c_int(0)
+        check(_lib.lib().twm_chain_partition(n_tiles, nkb, grid, rank, cap, buf, C.byref(n)), "twm_chain_partition")
+        if n.value <= cap:
+            return [tuple(buf[5 * i:5 * i + 5]) for i in range(n.value)]
+        cap = n.value
+
+
 def device_error(stream=None) -> int:
     """Read and clear the device-side error word (synchronises the stream)."""
     w = C.c_uint(0)

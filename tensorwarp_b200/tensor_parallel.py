@@ -126,11 +126,12 @@ class PeerComm:
     CUDA IPC; inside one process (tests on a single GPU) they are plain allocations."""
 
     def __init__(self, n_ranks: int, rank: int, slot_elems: int, bases: List[int], owned: Optional[int] = None,
-                 opened: Optional[List[int]] = None):
+                 opened: Optional[List[int]] = None, wait_ms: float = 0.0):
         lib = _lib.lib()
         self.n_ranks, self.rank, self.slot_elems = n_ranks, rank, slot_elems
         self._owned, self._opened = owned, opened or []
-        self.struct = _lib.Comm(n_ranks=n_ranks, rank=rank, slot_elems=slot_elems)
+        # wait_ms: how long the consumer kernel waits for the peers' partials (0 = the library's two seconds)
+        self.struct = _lib.Comm(n_ranks=n_ranks, rank=rank, slot_elems=slot_elems, wait_ns=int(wait_ms * 1e6))
         for s_, base in enumerate(bases):
             d, f, st = C.c_void_p(), C.c_void_p(), C.c_void_p()
             check(lib.twm_comm_layout(C.c_void_p(base), n_ranks, slot_elems, C.byref(d), C.byref(f), C.byref(st)),
@@ -151,14 +152,14 @@ class PeerComm:
         return p.value
 
     @classmethod
-    def local_group(cls, n_ranks: int, slot_elems: int) -> List["PeerComm"]:
+    def local_group(cls, n_ranks: int, slot_elems: int, wait_ms: float = 0.0) -> List["PeerComm"]:
         """All ranks in this process, on the current device (single-GPU emulation)."""
         nbytes = _lib.lib().twm_comm_bytes(n_ranks, slot_elems)
         bases = [cls._alloc(nbytes) for _ in range(n_ranks)]
-        return [cls(n_ranks, r, slot_elems, bases, owned=bases[r]) for r in range(n_ranks)]
+        return [cls(n_ranks, r, slot_elems, bases, owned=bases[r], wait_ms=wait_ms) for r in range(n_ranks)]
 
     @classmethod
-    def distributed(cls, slot_elems: int) -> "PeerComm":
+    def distributed(cls, slot_elems: int, wait_ms: float = 0.0) -> "PeerComm":
         """One rank per process under torch.distributed: allocate, exchange IPC handles, map the peers."""
         import torch.distributed as dist
         lib = _lib.lib()
@@ -178,7 +179,7 @@ class PeerComm:
                 bases.append(p.value)
                 opened.append(p.value)
         dist.barrier()
-        return cls(n, r, slot_elems, bases, owned=mine, opened=opened)
+        return cls(n, r, slot_elems, bases, owned=mine, opened=opened, wait_ms=wait_ms)
 
     def close(self) -> None:
         lib = _lib.lib()

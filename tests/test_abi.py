@@ -46,15 +46,6 @@ def test_plan_benchmark_shapes(twm_lib):
     # gate+up of the 7B shape: 296 tiles fill 148 SMs twice over -> never split
     st, p = _plan(twm_lib, 1, 37888, 3584, 128, 148, 0, 0)
     assert st == 0 and p.splits == 1 and p.grid_x == 296 and p.workspace_bytes == 0
-    # the strip kernel, by name: one CTA per SM at most, every CTA the same number of 32-column
-    # strips, whole K, no workspace
-    for (n, k, grid) in ((37888, 3584, 148), (4608, 3584, 144), (3584, 3584, 112), (3584, 18944, 112), (8192, 1024, 128)):
-        st, p = _plan(twm_lib, 1, n, k, 128, 148, 0, _lib.TWM_KERNEL_STRIP)
-        assert st == 0 and p.kernel == _lib.TWM_KERNEL_STRIP and p.n_tile == 32, (n, k)
-        assert (p.splits, p.grid_x, p.grid_y, p.workspace_bytes, p.cluster_reduce) == (1, grid, 1, 0, 0), (n, k, p.grid_x)
-    # it wants N a multiple of 8 and the rows' activations in shared memory beside a three-stage ring
-    assert _plan(twm_lib, 1, 4612, 3584, 128, 148, 0, _lib.TWM_KERNEL_STRIP)[0] == _lib.TWM_EINVAL
-    assert _plan(twm_lib, 8, 4608, 3584, 128, 148, 0, _lib.TWM_KERNEL_STRIP)[0] == _lib.TWM_EINVAL
     # the heuristic stays on the split-K kernel for FP16 activations up to eight rows
     assert _plan(twm_lib, 1, 4608, 3584, 128, 148, 0, 0)[1].kernel == _lib.TWM_KERNEL_MMA
     # small-N shapes must split to cover the machine (the reference's k<2048 cut-off is not inherited)

@@ -187,50 +187,6 @@ def test_small_m_f16(m, k, n, group, kernel):
     assert np.array_equal(y32.astype(np.float16).astype(np.float32), y)
 
 
-@pytest.mark.parametrize("group", [32, 128])
-@pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 8])
-@pytest.mark.parametrize("k,n", [(128, 40), (384, 264), (1024, 512), (3584, 264), (4224, 136), (256, 9728), (2176, 6400)])
-def test_strip_kernel(m, k, n, group):
-    """The strip kernel (one CTA per SM, 32-column strips over the whole K, four K phases per
-    strip): a single ragged stage, K that ends inside a ring stage and inside an activation
-    chunk, a ragged last strip, several strips per CTA with the ring running on across them."""
-    if k % group:
-        pytest.skip("K not a multiple of the group")
-    kern = _lib.TWM_KERNEL_STRIP
-    mp = 1 if m <= 1 else 2 if m <= 2 else 4 if m <= 4 else 8
-    try:
-        q.plan(m, n, k, group, kernel_override=kern)
-    except q.TwmError:
-        # the rows' activations must fit in shared memory beside a three-stage ring: refused, not mis-run
-        assert (k // 32) * 64 * mp >= 48 * 1024
-        return
-    _, packed, scales = _quantised(k, n, group, 47)
-    a = seeded_activations(m, k, 2)
-    ref64 = oracle.w4a16_f64(a, packed, scales, m, n, k, group)
-    y32 = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float32, kernel_override=kern)
-    assert rel_err_floored(y32, ref64) < TOL_TC_F32
-    y = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float16, kernel_override=kern,
-                  flags=_lib.TWM_FLAG_PDL)
-    assert np.array_equal(y32.astype(np.float16).astype(np.float32), y)       # one rounding, at the end
-    again = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float32, kernel_override=kern)
-    assert np.array_equal(again, y32)                                         # fixed summation order
-
-
-def test_strip_kernel_accumulate_and_strides():
-    k, n, m, group = 1152, 264, 3, 128
-    _, packed, scales = _quantised(k, n, group, 71)
-    a = seeded_activations(m, k, 0)
-    a_wide = torch.zeros((m, k + 64), dtype=torch.float16, device=DEV)
-    a_wide[:, :k] = _to_dev(a, torch.float16)
-    c_wide = torch.ones((m, n + 8), dtype=torch.float32, device=DEV)
-    q.gemm_tw_marlin(a_wide[:, :k], _to_dev(packed), _to_dev(scales.view(np.float16)), c_wide[:, :n], m, n, k,
-                     group_size=group, flags=_lib.TWM_FLAG_ACCUMULATE, kernel_override=_lib.TWM_KERNEL_STRIP)
-    torch.cuda.synchronize()
-    ref64 = oracle.w4a16_f64(a, packed, scales, m, n, k, group) + 1.0
-    assert rel_err_floored(c_wide[:, :n].cpu().numpy(), ref64) < TOL_F32
-    assert torch.all(c_wide[:, n:] == 1.0)        # the padding columns are not touched
-
-
 @pytest.mark.parametrize("kernel", [_lib.TWM_KERNEL_TC, _lib.TWM_KERNEL_MMA])
 @pytest.mark.parametrize("splits", [1, 2, 5])
 @pytest.mark.parametrize("k,n,group", [(32, 40, 32), (96, 130, 32), (2048, 300, 128), (4224, 129, 128), (8192, 64, 32)])
@@ -369,7 +325,7 @@ def test_deterministic_and_split_invariant():
     k, n, group = 3584, 4608, 128
     _, packed, scales = _quantised(k, n, group, 53)
     a = seeded_activations(1, k, 0)
-    for kernel in (_lib.TWM_KERNEL_SIMT, _lib.TWM_KERNEL_TC, _lib.TWM_KERNEL_MMA, _lib.TWM_KERNEL_STRIP):
+    for kernel in (_lib.TWM_KERNEL_SIMT, _lib.TWM_KERNEL_TC, _lib.TWM_KERNEL_MMA):
         runs = [_run_gemm(a, packed, scales, 1, n, k, group, torch.float16, torch.float32, kernel_override=kernel)
                 for _ in range(3)]
         assert np.array_equal(runs[0], runs[1]) and np.array_equal(runs[0], runs[2])

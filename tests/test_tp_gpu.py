@@ -101,15 +101,15 @@ def test_sharded_stack_equals_unsharded(rows):
             assert float(np.max(np.abs(fused[0] - ref))) / rms < 2e-3, degree
 
 
-@pytest.mark.parametrize("kernel,rows", [(3, 1), (3, 2), (4, 1), (4, 3), (4, 8)])
-def test_row_parallel_push_and_sum(kernel, rows):
-    """The row-parallel GEMM with `comm` on both streaming kernels, then the consumer: every rank's
+@pytest.mark.parametrize("kernel,rows,n", [(3, 1, 3072), (3, 2, 3072), (3, 1, 8192), (3, 2, 16384), (3, 1, 512)])
+def test_row_parallel_push_and_sum(kernel, rows, n):
+    """The row-parallel GEMM with `comm` on the streaming MMA kernel, then the consumer: every rank's
     x + sum over ranks equals x + the unsharded GEMM, and all ranks hold the same bits.  Run twice
     in a row: the sequence number alternates between the two buffer sets."""
     import ctypes as C
     from tensorwarp_b200 import _lib
     lib = _lib.lib()
-    degree, k, n, group = 2, 2048, 3072, 128
+    degree, k, group = 2, 2048 if n <= 3072 else 512, 128
     gen = torch.Generator(device="cuda").manual_seed(5)
     w = torch.randn((k, n), generator=gen, device="cuda") * 0.02
     packed, scales = q.quantize_f32_to_tw_marlin(w, k, n, group)
@@ -125,6 +125,13 @@ def test_row_parallel_push_and_sum(kernel, rows):
         p_r = packed.view(k // 32, n, 16)[r * kb // 32:(r + 1) * kb // 32].contiguous()
         s_r = scales.view(k // group, n)[r * kb // group:(r + 1) * kb // group].contiguous()
         shards.append((p_r, s_r, a[:, r * kb:(r + 1) * kb].contiguous()))
+    # each rank's partial as the same kernel stores it without `comm`: what an NCCL all-reduce would add up
+    parts = []
+    for r in range(degree):
+        p_r, s_r, a_r = shards[r]
+        part = torch.zeros((rows, n), device="cuda")
+        q.gemm_tw_marlin(a_r, p_r, s_r, part, rows, n, kb, group_size=group, kernel_override=kernel)
+        parts.append(part)
     for step in range(2):
         xs = [torch.full((rows, n), 0.5 * (step + 1), device="cuda") for _ in range(degree)]
         dummy = torch.zeros((rows, n), device="cuda")
@@ -146,5 +153,47 @@ def test_row_parallel_push_and_sum(kernel, rows):
         rms = float(want.pow(2).mean().sqrt())
         assert float((xs[0] - want).abs().max()) / rms < 2e-3
         assert torch.all(dummy == 0)                    # with comm the result goes to the peers only
+        # the one-CTA add + RMSNorm on the rank-order sum of the partials (the NCCL path's kernel) gives the
+        # same bits as the multi-CTA consumer: both take the sum of squares in the same order
+        x_ref = torch.full((rows, n), 0.5 * (step + 1), device="cuda")
+        y_ref = torch.zeros((rows, n), device="cuda", dtype=torch.float16)
+        summed = parts[0] + parts[1]
+        _lib.check(lib.twm_add_rmsnorm(y_ref.data_ptr(), x_ref.data_ptr(), summed.data_ptr(), gamma.data_ptr(), rows, n,
+                                       1e-5, 0, stream), "twm_add_rmsnorm")
+        torch.cuda.synchronize()
+        assert torch.equal(xs[0], x_ref) and torch.equal(ys[0], y_ref)
     for c in comms:
         c.close()
+
+
+def test_consumer_wait_runs_out_without_a_producer():
+    """A consumer whose peers never deliver: the bounded wait (50 ms here, a field of twm_comm) expires, the
+    kernel returns, the device error word carries bit 2, x is left as it was, and the context stays usable.
+    Nothing hangs and nothing faults: the failure is a flag that nobody sets."""
+    import ctypes as C
+    from tensorwarp_b200 import _lib
+    lib = _lib.lib()
+    rows, n = 1, 2048
+    comms = tp.PeerComm.local_group(2, rows * n, wait_ms=50.0)
+    x = torch.full((rows, n), 3.0, device="cuda")
+    y = torch.full((rows, n), 7.0, device="cuda", dtype=torch.float16)
+    gamma = torch.ones(n, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    assert q.device_error() == 0
+    _lib.check(lib.twm_allreduce_add_rmsnorm(y.data_ptr(), x.data_ptr(), comms[0].ptr, gamma.data_ptr(), rows, n, 1e-5,
+                                             0, stream), "twm_allreduce_add_rmsnorm")
+    torch.cuda.synchronize()
+    word = C.c_uint(0)
+    assert lib.twm_device_error(stream, C.byref(word)) == _lib.TWM_ETIMEOUT
+    assert word.value & 4
+    assert torch.all(x == 3.0) and torch.all(y == 7.0)
+    assert q.device_error() == 0                       # reading cleared it
+    # the context is alive: an ordinary GEMM still runs
+    w = torch.randn((256, 128), device="cuda") * 0.02
+    p, s = q.quantize_f32_to_tw_marlin(w, 256, 128, 128)
+    c = torch.zeros(128, dtype=torch.float16, device="cuda")
+    q.gemm_tw_marlin_m1(torch.ones(256, dtype=torch.float16, device="cuda"), p, s, c, 128, 256, group_size=128)
+    torch.cuda.synchronize()
+    assert q.device_error() == 0
+    for c_ in comms:
+        c_.close()
