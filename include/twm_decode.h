@@ -62,11 +62,13 @@ twm_status twm_lm_head(float* logits, const void* x_f16, const void* w_f16, int 
 /* Bytes of scratch twm_argmax_advance needs. */
 size_t twm_argmax_scratch_bytes(void);
 
-/* token_out[0] = argmax(logits) (ties: smallest index); history[step_buf[0]] = token (history may be
- * NULL); then step_buf[0]++, pos_buf[0]++, len_buf[0]++.  Replaces the host-side sampling after a
- * full-logits copy (generate.rs:2514, 2531-2534) for greedy decoding. */
-twm_status twm_argmax_advance(int* token_out, int* history, int* pos_buf, int* len_buf, int* step_buf,
-                              const float* logits, int n, void* scratch, size_t scratch_bytes, int flags,
+/* token_out[0] = argmax(logits) (ties: smallest index; 0 when no logit is a number);
+ * history[step_buf[0]] = token when step_buf[0] < history_capacity (history may be NULL: a full
+ * list is simply not written past its end); then step_buf[0]++, pos_buf[0]++, len_buf[0]++.
+ * Replaces the host-side sampling after a full-logits copy (generate.rs:2514, 2531-2534) for
+ * greedy decoding. */
+twm_status twm_argmax_advance(int* token_out, int* history, int history_capacity, int* pos_buf, int* len_buf,
+                              int* step_buf, const float* logits, int n, void* scratch, size_t scratch_bytes, int flags,
                               void* stream);
 
 #ifdef __cplusplus

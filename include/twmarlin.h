@@ -63,7 +63,9 @@ enum {
      * neither writes this call's a nor reads or writes its c.  The launch then does not wait for that
      * kernel at all, and the two overlap CTA by CTA.  Honoured by the streaming MMA kernel when its
      * plan needs no workspace (M <= 2); ignored (the launch waits) otherwise.  A decode step has no
-     * such pair of GEMMs; the flag exists to measure what the dependency between launches costs. */
+     * such pair of GEMMs; the flag exists to measure what the dependency between launches costs.
+     * The launch still ends after the kernel ahead of it (one warp waits for that kernel before the
+     * CTA exits), so a later kernel that waits for this one has waited for everything before it. */
     TWM_FLAG_INDEPENDENT = 4
 };
 
@@ -100,7 +102,10 @@ typedef struct twm_gemm_args {
     long ldc;
     void* workspace;         /* split-K scratch from twm_workspace_bytes(); may be NULL when 0 bytes are needed.
                                 Zero it once after allocation; the kernels leave its counters at zero.
-                                One workspace serves one stream at a time. */
+                                One workspace serves one stream at a time.  Without one (or with too small
+                                a one) the streaming kernels run a plan that does not split K (slower on
+                                small N); TWM_EWORKSPACE is returned only where scratch is indispensable:
+                                the tcgen05 kernel, or a split count the caller asked for. */
     size_t workspace_bytes;
     int splits_override;     /* 0 = heuristic */
     int kernel_override;     /* TWM_KERNEL_* ; 0 = heuristic */
@@ -114,7 +119,8 @@ typedef struct twm_gemm_args {
     /* Tensor-parallel row shard: when comm != NULL the FP32 result is not stored to `c` but pushed
      * into every rank's receive buffer (plain stores over NVLink into the peer's own memory, tile
      * by tile as the tiles finish), and the grid's last CTA raises the arrival flags.  The sum is
-     * taken by twm_allreduce_add_rmsnorm on each rank.  M <= 8, FP16 activations. */
+     * taken by twm_allreduce_add_rmsnorm on each rank.  M <= 2 (the plan must be one K slice per tile or
+     * a cluster reduce), FP16 activations, streaming MMA kernel. */
     const twm_comm* comm;
 } twm_gemm_args;
 

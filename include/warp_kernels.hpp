@@ -83,7 +83,7 @@ inline void gemm(const TA* a, long lda, const uint8_t* packed, const uint16_t* s
 template <typename TA, typename TC>
 inline void gemm_tw_marlin_m1(const GpuTensor<TA>& a, const GpuTensor<uint8_t>& packed, const GpuTensor<f16>& scales,
                               GpuTensor<TC>& c, uint32_t n, uint32_t k, const Workspace& ws = {}, void* stream = nullptr,
-                              uint32_t group_size = BLOCK_SIZE, int flags = TWM_FLAG_PDL) {
+                              uint32_t group_size = BLOCK_SIZE, int flags = 0) {
     if (k % BLOCK_SIZE != 0) throw DeviceError(TWM_EINVAL, "gemm_tw_marlin_m1: k % 32 != 0");
     if (a.numel < k || c.numel < n || packed.numel < (size_t)(k / 32) * n * 16 || scales.numel < (size_t)(k / group_size) * n)
         throw DeviceError(TWM_EINVAL, "gemm_tw_marlin_m1: a tensor is smaller than the stated shape");
@@ -95,7 +95,7 @@ inline void gemm_tw_marlin_m1(const GpuTensor<TA>& a, const GpuTensor<uint8_t>& 
 template <typename TA, typename TC>
 inline void gemm_tw_marlin(const GpuTensor<TA>& a, const GpuTensor<uint8_t>& packed, const GpuTensor<f16>& scales,
                            GpuTensor<TC>& c, uint32_t m, uint32_t n, uint32_t k, const Workspace& ws, void* stream = nullptr,
-                           uint32_t group_size = BLOCK_SIZE, int flags = TWM_FLAG_PDL) {
+                           uint32_t group_size = BLOCK_SIZE, int flags = 0) {
     if (a.numel < (size_t)m * k || c.numel < (size_t)m * n) throw DeviceError(TWM_EINVAL, "gemm_tw_marlin: A or C too small");
     detail::gemm(a.data, (long)k, packed.data, reinterpret_cast<const uint16_t*>(scales.data), c.data, (long)n, m, n, k, group_size,
                  ws, stream, flags, nullptr, nullptr, 0);
@@ -106,7 +106,7 @@ template <typename TA, typename TC>
 inline void gemm_tw_marlin_m1_from_buffer(const GpuTensor<TA>& a, const GpuTensor<uint8_t>& packed_buf, size_t packed_offset,
                                           const GpuTensor<f16>& scales_buf, size_t scales_offset, GpuTensor<TC>& c, uint32_t n,
                                           uint32_t k, const Workspace& ws = {}, void* stream = nullptr,
-                                          uint32_t group_size = BLOCK_SIZE, int flags = TWM_FLAG_PDL) {
+                                          uint32_t group_size = BLOCK_SIZE, int flags = 0) {
     if (packed_offset > packed_buf.numel || scales_offset > scales_buf.numel)
         throw DeviceError(TWM_EINVAL, "gemm_tw_marlin_m1_from_buffer: offset past the buffer");
     GpuTensor<uint8_t> p{packed_buf.data + packed_offset, packed_buf.numel - packed_offset};
@@ -121,7 +121,7 @@ inline void gemm_tw_marlin_m1_indirect(const GpuTensor<TA>& a, const GpuTensor<u
                                        const GpuTensor<uint32_t>& packed_offsets, const GpuTensor<f16>& scales_buf,
                                        const GpuTensor<uint32_t>& scales_offsets, uint32_t expert_idx, GpuTensor<TC>& c,
                                        uint32_t n, uint32_t k, const Workspace& ws = {}, void* stream = nullptr,
-                                       uint32_t group_size = BLOCK_SIZE, int flags = TWM_FLAG_PDL) {
+                                       uint32_t group_size = BLOCK_SIZE, int flags = 0) {
     if (k % BLOCK_SIZE != 0) throw DeviceError(TWM_EINVAL, "gemm_tw_marlin_m1_indirect: k % 32 != 0");
     if (expert_idx >= packed_offsets.numel || expert_idx >= scales_offsets.numel)
         throw DeviceError(TWM_EINVAL, "gemm_tw_marlin_m1_indirect: expert index past the offset tables");

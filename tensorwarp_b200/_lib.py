@@ -103,7 +103,7 @@ SIGNATURES = {
     "twm_silu_mul": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "twm_lm_head": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "twm_argmax_scratch_bytes": (C.c_size_t, []),
-    "twm_argmax_advance": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
+    "twm_argmax_advance": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
                                      C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]),
     "twm_status_string": (C.c_char_p, [C.c_int]),
     "twm_last_error": (C.c_char_p, []),

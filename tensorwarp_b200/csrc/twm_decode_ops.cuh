@@ -629,9 +629,9 @@ argmax_partial_kernel(float* __restrict__ pval, int* __restrict__ pidx, const fl
 // Final pass; also advances the device-side position / length buffers for the next step and
 // appends the token to the output list, so a replayed graph needs no host input at all.
 __global__ void __launch_bounds__(256)
-argmax_final_kernel(int* __restrict__ token_out, int* __restrict__ history, int* __restrict__ pos_buf,
-                    int* __restrict__ len_buf, int* __restrict__ step_buf, const float* __restrict__ pval,
-                    const int* __restrict__ pidx, int nparts)
+argmax_final_kernel(int* __restrict__ token_out, int* __restrict__ history, int history_capacity,
+                    int* __restrict__ pos_buf, int* __restrict__ len_buf, int* __restrict__ step_buf,
+                    const float* __restrict__ pval, const int* __restrict__ pidx, int nparts, int n)
 {
     pdl_launch_dependents();
     pdl_wait_prior_grids();
@@ -653,8 +653,12 @@ argmax_final_kernel(int* __restrict__ token_out, int* __restrict__ history, int*
         __syncthreads();
     }
     if (threadIdx.x == 0) {
-        token_out[0] = si[0];
-        if (history) history[step_buf[0]] = si[0];
+        // every logit NaN or -inf leaves the index at its start value: token 0 then, never an index
+        // past the vocabulary (the next step's embedding lookup uses it as a row number)
+        const int tok = (si[0] >= 0 && si[0] < n) ? si[0] : 0;
+        token_out[0] = tok;
+        const int step = step_buf[0];
+        if (history && step >= 0 && step < history_capacity) history[step] = tok;     // a full list is not overrun
         step_buf[0] += 1;
         pos_buf[0] += 1;
         len_buf[0] += 1;

@@ -42,7 +42,7 @@ constexpr int NT = 128;          // columns per CTA
 #define TWM_MMA_SB 8
 #endif
 #ifndef TWM_MMA_STAGES
-#define TWM_MMA_STAGES 4
+#define TWM_MMA_STAGES 5
 #endif
 constexpr int SB = TWM_MMA_SB;            // 32-blocks per ring stage
 constexpr int STAGES = TWM_MMA_STAGES;
@@ -58,14 +58,14 @@ constexpr int ASUM_GROUPS = 64;              // scale groups per chunk, at most
 #define TWM_MMA_MIN_CTAS 2
 #endif
 constexpr int MAX_CLUSTER = TWM_MMA_MAX_CLUSTER;   // K slices that can add up through distributed shared memory
-constexpr int CLUSTER_ROWS = 2;              // ... for up to this many activation rows
+constexpr int CLUSTER_ROWS = 2;              // ... for up to this many activation rows (K slices x rows <= MAX_CLUSTER)
 
 struct Smem {
     alignas(128) uint8_t packed[STAGES][SB * NT * kBlockBytes];
     alignas(128) uint16_t scales[STAGES][SB][NT];
     alignas(128) uint8_t b[2][B_BUF_BYTES];           // [block in chunk][row m < MP][t] x 16 bytes
     alignas(16) float asum8[2][ASUM_GROUPS][8];       // -8 * sum of a group's activations, per row
-    alignas(16) float red[MAX_CLUSTER][CLUSTER_ROWS][NT];   // cluster leader only: one partial tile per K slice
+    alignas(16) float red[MAX_CLUSTER][NT];           // cluster leader only: row (slice * M + m) = one K slice's sums of activation row m
     alignas(8) uint64_t full[STAGES];
     alignas(8) uint64_t empty[STAGES];
     alignas(8) uint64_t b_full[2];
@@ -135,6 +135,9 @@ gemv_kernel(const __grid_constant__ GemmParams p)
     }
     __syncthreads();
     pdl_launch_dependents();
+    // Cluster launches: a CTA may store into the leader's shared memory only once the leader has
+    // started.  Everybody arrives here, and waits just before the first such store.
+    if (p.cluster_reduce) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
     volatile int* abort_flag = &sm.abort_flag;
 
     float tot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -194,6 +197,9 @@ gemv_kernel(const __grid_constant__ GemmParams p)
             }
             __syncwarp();
         }
+        // A launch that does not wait for its predecessor must still not END before it: the kernel
+        // after this one waits for this one only.  This warp has nothing left to do.
+        if (p.no_wait) pdl_wait_prior_grids();
     } else if (warp == CONSUMER_WARPS + 1) {
         // ------------------------------------------------ activation stager --
         // One item = 8 consecutive K of one row, stored as the 16 bytes
@@ -441,6 +447,7 @@ gemv_kernel(const __grid_constant__ GemmParams p)
     auto comm_cta_done = [&](unsigned int total) {
         __threadfence_system();
         if (atomicAdd(&p.comm_state[1], 1u) == total - 1) {
+            __threadfence_system();          // acquire side: the other CTAs' counted stores come before the flags below
             atomicExch(&p.comm_state[1], 0u);
             for (int s = 0; s < p.n_peers; ++s)
                 st_release_sys_u32(p.peer_flags[s] + ((comm_seq & 1u) * p.n_peers + p.peer_rank) * 8, comm_seq + 1u);
@@ -454,18 +461,21 @@ gemv_kernel(const __grid_constant__ GemmParams p)
         // the same bits whatever order the slices finish in.  Every thread of every CTA
         // reaches the barrier (all loops above are bounded).
         const uint32_t rank = cluster_ctarank();
+        asm volatile("barrier.cluster.wait.aligned;" ::: "memory");      // pairs with the arrive at the top: every CTA of the cluster runs
         if (consumer && t == 0 && *abort_flag == 0) {
-            const uint32_t base = mapa_shared(smem_u32(&sm.red[rank][0][0]), 0);
-            st_cluster_f32(base + (0 * NT + wcol + g) * 4, tot[0]);
-            st_cluster_f32(base + (1 * NT + wcol + g) * 4, tot[1]);
-            st_cluster_f32(base + (0 * NT + wcol + g + 8) * 4, tot[2]);
-            st_cluster_f32(base + (1 * NT + wcol + g + 8) * 4, tot[3]);
+            const uint32_t base = mapa_shared(smem_u32(&sm.red[rank * p.M][0]), 0);
+            st_cluster_f32(base + (wcol + g) * 4, tot[0]);
+            st_cluster_f32(base + (wcol + g + 8) * 4, tot[2]);
+            if (p.M > 1) {
+                st_cluster_f32(base + (NT + wcol + g) * 4, tot[1]);
+                st_cluster_f32(base + (NT + wcol + g + 8) * 4, tot[3]);
+            }
         }
         cluster_sync_all();
-        if (rank == 0 && tid < CLUSTER_ROWS * NT && *abort_flag == 0) {
+        if (rank == 0 && tid < p.M * NT && *abort_flag == 0) {
             const int m = tid / NT, col = tid - m * NT;
             float s = 0.0f;
-            for (int sp = 0; sp < p.splits; ++sp) s += sm.red[sp][m][col];
+            for (int sp = 0; sp < p.splits; ++sp) s += sm.red[sp * p.M + m][col];
             store_c(m, n0 + col, s);
         }
         if (p.n_peers && rank == 0) {       // only the cluster leaders store

@@ -415,11 +415,11 @@ twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int split
         if (bps > max_bps) return TWM_EINVAL;
         splits = (nkb + bps - 1) / bps;
     } else {
-        choose_splits(n_tiles, nkb, slots, sm_count, max_bps, align, can_cluster ? twm::mma::MAX_CLUSTER : kMaxSplits,
+        choose_splits(n_tiles, nkb, slots, sm_count, max_bps, align, can_cluster ? twm::mma::MAX_CLUSTER / rows : kMaxSplits,
                       can_cluster, &splits, &bps);
         if (bps > max_bps) return TWM_EINVAL;
     }
-    const bool cluster = can_cluster && splits > 1 && splits <= twm::mma::MAX_CLUSTER;
+    const bool cluster = can_cluster && splits > 1 && splits * rows <= twm::mma::MAX_CLUSTER;
     out->kernel = kernel;
     out->n_tile = twm::simt::NT;
     out->splits = splits;
@@ -473,6 +473,14 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
     twm_plan_t pl;
     st = twm_plan(a->M, a->N, a->K, a->group_size, sm_count, a->splits_override, kernel, &pl);
     if (st != TWM_OK) return st;
+    if (pl.workspace_bytes > 0 && (!a->workspace || a->workspace_bytes < pl.workspace_bytes) &&
+        kernel != TWM_KERNEL_TC && a->splits_override == 0) {
+        // The reference's call has no scratch argument (its split-K adds into C with atomics,
+        // quantize.rs:1337-1357).  A caller that passes none still gets its GEMM: one K slice per
+        // tile, nothing to add up, at the price of fewer CTAs on small N.
+        st = twm_plan(a->M, a->N, a->K, a->group_size, sm_count, 1, kernel, &pl);
+        if (st != TWM_OK) return st;
+    }
     if (pl.workspace_bytes > 0) {
         if (!a->workspace || a->workspace_bytes < pl.workspace_bytes) return TWM_EWORKSPACE;
         if (reinterpret_cast<uintptr_t>(a->workspace) & 15) return TWM_EALIGN;
@@ -552,16 +560,34 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
 
 twm_status twm_gemm_w4a16_static_ws(const twm_gemm_args* a, void* stream_)
 {
+    // everything twm_gemm_w4a16 checks before it enqueues, checked here first: a call that is going
+    // to be refused must not have put the counter clearing on the stream already
     if (!a) return TWM_EINVAL;
     if (!shape_ok(a->M, a->N, a->K, a->group_size)) return TWM_EINVAL;
     if (!a->a || !a->packed || !a->scales || !a->c) return TWM_EINVAL;
     if ((a->a_dtype != TWM_F32 && a->a_dtype != TWM_F16) || (a->c_dtype != TWM_F32 && a->c_dtype != TWM_F16))
         return TWM_EINVAL;
+    if (a->lda < a->K || a->ldc < a->N) return TWM_EINVAL;
+    if ((a->packed_offsets == nullptr) != (a->scales_offsets == nullptr)) return TWM_EINVAL;
+    if (a->packed_offsets && a->expert_idx < 0) return TWM_EINVAL;
+    if (reinterpret_cast<uintptr_t>(a->packed) & 15) return TWM_EALIGN;
+    if (reinterpret_cast<uintptr_t>(a->scales) & 1) return TWM_EALIGN;
+    if (reinterpret_cast<uintptr_t>(a->a) & (a->a_dtype == TWM_F16 ? 1 : 3)) return TWM_EALIGN;
+    if (reinterpret_cast<uintptr_t>(a->c) & (a->c_dtype == TWM_F16 ? 1 : 3)) return TWM_EALIGN;
     int sm_count = kDefaultSms;
     twm_status st = ensure_device(&sm_count);
     if (st != TWM_OK) return st;
-    // the same kernel choice and plan twm_gemm_w4a16 will make for these arguments
-    const int kernel = resolve_kernel(a);
+    void* ws = nullptr;
+    st = static_ws_address(&ws);
+    if (st != TWM_OK) return st;
+    // The call that will run: the caller's arguments with the built-in array as its workspace.  The
+    // kernel choice and the plan are made for THAT call (a workspace of this size can change the
+    // choice for five to eight rows), so the capacity check and the clearing below match what runs.
+    twm_gemm_args b = *a;
+    b.workspace = ws;
+    b.workspace_bytes = kStaticWsBytes;
+    const int kernel = resolve_kernel(&b);
+    if (kernel != TWM_KERNEL_SIMT && a->a_dtype != TWM_F16) return TWM_EINVAL;
     twm_plan_t pl;
     st = twm_plan(a->M, a->N, a->K, a->group_size, sm_count, a->splits_override, kernel, &pl);
     if (st != TWM_OK) return st;
@@ -571,19 +597,12 @@ twm_status twm_gemm_w4a16_static_ws(const twm_gemm_args* a, void* stream_)
                  "use twm_gemm_w4a16 with a caller-owned workspace", pl.workspace_bytes, kStaticWsBytes);
         return TWM_EWORKSPACE;
     }
-    void* ws = nullptr;
-    st = static_ws_address(&ws);
-    if (st != TWM_OK) return st;
-    cudaStream_t stream = (cudaStream_t)stream_;
     if (pl.workspace_bytes > 0) {
         // The array keeps whatever the last call left.  Partial sums are always written before
         // they are read; the tile counters must start at zero, so they are cleared here.
-        cudaError_t e = cudaMemsetAsync(ws, 0, (size_t)pl.grid_x * sizeof(unsigned int), stream);
+        cudaError_t e = cudaMemsetAsync(ws, 0, (size_t)pl.grid_x * sizeof(unsigned int), (cudaStream_t)stream_);
         if (e != cudaSuccess) { set_error("cudaMemsetAsync(static scratch counters)", e); return TWM_ELAUNCH; }
     }
-    twm_gemm_args b = *a;
-    b.workspace = ws;
-    b.workspace_bytes = kStaticWsBytes;
     return twm_gemm_w4a16(&b, stream_);
 }
 
@@ -1122,11 +1141,12 @@ twm_status twm_ipc_close(void* ptr)
 
 size_t twm_argmax_scratch_bytes(void) { return (size_t)kArgmaxParts * 8; }
 
-twm_status twm_argmax_advance(int* token_out, int* history, int* pos_buf, int* len_buf, int* step_buf,
-                              const float* logits, int n, void* scratch, size_t scratch_bytes, int flags,
+twm_status twm_argmax_advance(int* token_out, int* history, int history_capacity, int* pos_buf, int* len_buf,
+                              int* step_buf, const float* logits, int n, void* scratch, size_t scratch_bytes, int flags,
                               void* stream)
 {
     if (!token_out || !pos_buf || !len_buf || !step_buf || !logits || !scratch || n < 1) return TWM_EINVAL;
+    if (history && history_capacity < 1) return TWM_EINVAL;
     if (scratch_bytes < twm_argmax_scratch_bytes()) return TWM_EWORKSPACE;
     twm_status st = ensure_device(nullptr);
     if (st != TWM_OK) return st;
@@ -1136,7 +1156,7 @@ twm_status twm_argmax_advance(int* token_out, int* history, int* pos_buf, int* l
                    pval, pidx, logits, n);
     if (st != TWM_OK) return st;
     return launch_op("twm_argmax(final)", twm::ops::argmax_final_kernel, dim3(1), dim3(256), 0, flags, stream, token_out,
-                     history, pos_buf, len_buf, step_buf, (const float*)pval, (const int*)pidx, kArgmaxParts);
+                     history, history_capacity, pos_buf, len_buf, step_buf, (const float*)pval, (const int*)pidx, kArgmaxParts, n);
 }
 
 const char* twm_status_string(twm_status s)

@@ -172,13 +172,17 @@ class QuantizedGenerationEngine:
     def set_token(self, token: int) -> None:
         self.buf.token.fill_(int(token))
 
+    def reset_history(self) -> None:
+        """Start the generated-token list over (the step counter indexes it)."""
+        self.buf.step.zero_()
+
     # ------------------------------------------------------------------- step --
-    def forward_decode_tw_marlin_graph(self, stream_ptr: int) -> int:
-        """Enqueue one decode step (embedding .. arg-max) on the stream; returns the number of
-        kernel launches.  Launch order follows generate.rs:2149-2206 with the split/add passes
-        folded into their neighbours."""
+    def _step_ops(self, stream_ptr: int):
+        """One decode step as an ordered list of (category, launches, enqueue) triples: the launch
+        order of generate.rs:2149-2206 with the split/add passes folded into their neighbours.  The
+        categories are the rows of the reference's profile table (generate.rs:2380-2396)."""
         lib, cfg, b, fl = _lib.lib(), self.cfg, self.buf, self.flags
-        n = 0
+        ops = []
 
         def gemm(a, w, c, n_out, k_in, accumulate=False):
             args = _lib.GemmArgs(M=1, N=n_out, K=k_in, group_size=cfg.group_size, a_dtype=_lib.TWM_F16,
@@ -187,42 +191,89 @@ class QuantizedGenerationEngine:
                                  c=c.data_ptr(), ldc=n_out, workspace=b.workspace.ptr,
                                  workspace_bytes=b.workspace.nbytes,
                                  flags=fl | (_lib.TWM_FLAG_ACCUMULATE if accumulate else 0))
-            check(lib.twm_gemm_w4a16(C.byref(args), stream_ptr), "twm_gemm_w4a16")
+            return lambda: check(lib.twm_gemm_w4a16(C.byref(args), stream_ptr), "twm_gemm_w4a16")
 
-        check(lib.twm_embed(b.x.data_ptr(), self.model.embed.data_ptr(), b.token.data_ptr(), 1, cfg.hidden, fl,
-                            stream_ptr), "twm_embed"); n += 1
+        ops.append(("embedding", 1, lambda: check(lib.twm_embed(b.x.data_ptr(), self.model.embed.data_ptr(), b.token.data_ptr(),
+                                                                 1, cfg.hidden, fl, stream_ptr), "twm_embed")))
         for li, lw in enumerate(self.model.layers):
-            check(lib.twm_rmsnorm(b.normed.data_ptr(), b.x.data_ptr(), lw.attn_norm.data_ptr(), 1, cfg.hidden, cfg.eps,
-                                  fl, stream_ptr), "twm_rmsnorm"); n += 1
-            gemm(b.normed, lw.wqkv, b.qkv, cfg.q_dim + 2 * cfg.kv_dim, cfg.hidden); n += 1
-            check(lib.twm_rope_append(b.q.data_ptr(), b.k_cache[li].data_ptr(), b.v_cache[li].data_ptr(),
-                                      b.qkv.data_ptr(), lw.bqkv.data_ptr() if lw.bqkv is not None else None,
-                                      1, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, b.pos.data_ptr(), cfg.max_seq,
-                                      cfg.rope_theta, fl, stream_ptr), "twm_rope_append"); n += 1
-            check(lib.twm_attn_decode(b.attn.data_ptr(), b.q.data_ptr(), b.k_cache[li].data_ptr(),
-                                      b.v_cache[li].data_ptr(), 1, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim,
-                                      b.cache_len.data_ptr(), cfg.max_seq, b.attn_scratch.data_ptr(),
-                                      b.attn_scratch.numel(), fl, stream_ptr), "twm_attn_decode"); n += 2
-            gemm(b.attn, lw.wo, b.x, cfg.hidden, cfg.q_dim, accumulate=True); n += 1            # x += o(attn)
-            check(lib.twm_rmsnorm(b.normed.data_ptr(), b.x.data_ptr(), lw.ffn_norm.data_ptr(), 1, cfg.hidden, cfg.eps,
-                                  fl, stream_ptr), "twm_rmsnorm"); n += 1
-            gemm(b.normed, lw.wgu, b.gate_up, 2 * cfg.ffn, cfg.hidden); n += 1
-            check(lib.twm_silu_mul(b.act.data_ptr(), b.gate_up.data_ptr(), 1, cfg.ffn, fl, stream_ptr),
-                  "twm_silu_mul"); n += 1
-            gemm(b.act, lw.w_down, b.x, cfg.hidden, cfg.ffn, accumulate=True); n += 1           # x += down(act)
-        check(lib.twm_rmsnorm(b.normed.data_ptr(), b.x.data_ptr(), self.model.final_norm.data_ptr(), 1, cfg.hidden,
-                              cfg.eps, fl, stream_ptr), "twm_rmsnorm"); n += 1
+            ops.append(("attn_rmsnorm", 1, lambda lw=lw: check(lib.twm_rmsnorm(
+                b.normed.data_ptr(), b.x.data_ptr(), lw.attn_norm.data_ptr(), 1, cfg.hidden, cfg.eps, fl, stream_ptr), "twm_rmsnorm")))
+            ops.append(("qkv_gemm", 1, gemm(b.normed, lw.wqkv, b.qkv, cfg.q_dim + 2 * cfg.kv_dim, cfg.hidden)))
+            ops.append(("rope_kv_append", 1, lambda li=li, lw=lw: check(lib.twm_rope_append(
+                b.q.data_ptr(), b.k_cache[li].data_ptr(), b.v_cache[li].data_ptr(), b.qkv.data_ptr(),
+                lw.bqkv.data_ptr() if lw.bqkv is not None else None, 1, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim,
+                b.pos.data_ptr(), cfg.max_seq, cfg.rope_theta, fl, stream_ptr), "twm_rope_append")))
+            ops.append(("attention", 2, lambda li=li: check(lib.twm_attn_decode(
+                b.attn.data_ptr(), b.q.data_ptr(), b.k_cache[li].data_ptr(), b.v_cache[li].data_ptr(), 1, cfg.num_heads,
+                cfg.num_kv_heads, cfg.head_dim, b.cache_len.data_ptr(), cfg.max_seq, b.attn_scratch.data_ptr(),
+                b.attn_scratch.numel(), fl, stream_ptr), "twm_attn_decode")))
+            ops.append(("out_gemm", 1, gemm(b.attn, lw.wo, b.x, cfg.hidden, cfg.q_dim, accumulate=True)))          # x += o(attn)
+            ops.append(("ffn_rmsnorm", 1, lambda lw=lw: check(lib.twm_rmsnorm(
+                b.normed.data_ptr(), b.x.data_ptr(), lw.ffn_norm.data_ptr(), 1, cfg.hidden, cfg.eps, fl, stream_ptr), "twm_rmsnorm")))
+            ops.append(("gate_up_gemm", 1, gemm(b.normed, lw.wgu, b.gate_up, 2 * cfg.ffn, cfg.hidden)))
+            ops.append(("silu_mul", 1, lambda: check(lib.twm_silu_mul(b.act.data_ptr(), b.gate_up.data_ptr(), 1, cfg.ffn, fl,
+                                                                       stream_ptr), "twm_silu_mul")))
+            ops.append(("down_gemm", 1, gemm(b.act, lw.w_down, b.x, cfg.hidden, cfg.ffn, accumulate=True)))         # x += down(act)
+        ops.append(("final_rmsnorm", 1, lambda: check(lib.twm_rmsnorm(b.normed.data_ptr(), b.x.data_ptr(),
+                                                                      self.model.final_norm.data_ptr(), 1, cfg.hidden, cfg.eps,
+                                                                      fl, stream_ptr), "twm_rmsnorm")))
         if self.q4_lm_head:
-            gemm(b.normed, self.model.lm_head_q4, b.logits, cfg.vocab, cfg.hidden); n += 1
+            ops.append(("lm_head", 1, gemm(b.normed, self.model.lm_head_q4, b.logits, cfg.vocab, cfg.hidden)))
         else:
-            check(lib.twm_lm_head(b.logits.data_ptr(), b.normed.data_ptr(), self.model.lm_head.data_ptr(), cfg.hidden,
-                                  cfg.vocab, fl, stream_ptr), "twm_lm_head"); n += 1
-        check(lib.twm_argmax_advance(b.token.data_ptr(), b.history.data_ptr(), b.pos.data_ptr(),
-                                     b.cache_len.data_ptr(), b.step.data_ptr(), b.logits.data_ptr(), cfg.vocab,
-                                     b.argmax_scratch.data_ptr(), b.argmax_scratch.numel(), fl, stream_ptr),
-              "twm_argmax_advance"); n += 2
+            ops.append(("lm_head", 1, lambda: check(lib.twm_lm_head(b.logits.data_ptr(), b.normed.data_ptr(),
+                                                                    self.model.lm_head.data_ptr(), cfg.hidden, cfg.vocab, fl,
+                                                                    stream_ptr), "twm_lm_head")))
+        ops.append(("argmax_advance", 2, lambda: check(lib.twm_argmax_advance(
+            b.token.data_ptr(), b.history.data_ptr(), b.history.numel(), b.pos.data_ptr(), b.cache_len.data_ptr(),
+            b.step.data_ptr(), b.logits.data_ptr(), cfg.vocab, b.argmax_scratch.data_ptr(), b.argmax_scratch.numel(), fl,
+            stream_ptr), "twm_argmax_advance")))
+        return ops
+
+    def forward_decode_tw_marlin_graph(self, stream_ptr: int) -> int:
+        """Enqueue one decode step (embedding .. arg-max) on the stream; returns the number of
+        kernel launches (forward_decode_tw_marlin_graph, generate.rs:2124-2211)."""
+        n = 0
+        for _, launches, enqueue in self._step_ops(stream_ptr):
+            enqueue()
+            n += launches
         self.launches_per_step = n
         return n
+
+    def profile_decode_tw_marlin(self, steps: int = 3) -> dict:
+        """Per-operation time of a decode step (profile_decode_tw_marlin, generate.rs:2216-2408): every
+        operation of `steps` eager steps is bracketed by CUDA events on the engine's stream (the
+        reference brackets with host synchronisations, which also counts launch latency).  Returns
+        {"ops": {category: {"us", "us_per_layer", "pct"}}, "total_us", "gemm_us", "non_gemm_us",
+        "embed_us"} per step.  Position and cache length are put back afterwards."""
+        b = self.buf
+        saved = (b.pos.clone(), b.cache_len.clone(), b.step.clone(), b.token.clone())
+        acc: dict = {}
+        with torch.cuda.stream(self.stream):
+            self.forward_decode_tw_marlin_graph(self.stream.cuda_stream)          # warm
+            for _ in range(steps):
+                events = []
+                for cat, _, enqueue in self._step_ops(self.stream.cuda_stream):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(self.stream)
+                    enqueue()
+                    e1.record(self.stream)
+                    events.append((cat, e0, e1))
+                torch.cuda.synchronize()
+                for cat, e0, e1 in events:
+                    acc[cat] = acc.get(cat, 0.0) + e0.elapsed_time(e1) * 1e3
+            b.pos.copy_(saved[0]); b.cache_len.copy_(saved[1]); b.step.copy_(saved[2]); b.token.copy_(saved[3])
+            torch.cuda.synchronize()
+        per_step = {k: v / steps for k, v in acc.items()}
+        total = sum(per_step.values())
+        layered = {"attn_rmsnorm", "qkv_gemm", "rope_kv_append", "attention", "out_gemm", "ffn_rmsnorm", "gate_up_gemm",
+                   "silu_mul", "down_gemm"}
+        nl = max(len(self.model.layers), 1)
+        table = {k: {"us": round(v, 1), "us_per_layer": round(v / nl, 2) if k in layered else None,
+                     "pct": round(100.0 * v / total, 1)} for k, v in per_step.items()}
+        gemm_us = sum(v for k, v in per_step.items() if k.endswith("_gemm"))
+        return {"ops": table, "total_us": round(total, 1), "gemm_us": round(gemm_us, 1),
+                "non_gemm_us": round(total - gemm_us - per_step.get("embedding", 0.0), 1),
+                "embed_us": round(per_step.get("embedding", 0.0), 1)}
 
     def step_eager(self) -> None:
         with torch.cuda.stream(self.stream):
@@ -254,6 +305,13 @@ class QuantizedGenerationEngine:
             self.capture()
         self.set_token(first_token)
         start = int(self.buf.step.item())
+        pos = int(self.buf.pos.item())
+        if pos + max_tokens > self.cfg.max_seq:
+            raise _lib.TwmError(_lib.TWM_EINVAL, f"generate_tw_marlin_graph: position {pos} + {max_tokens} tokens runs past "
+                                                 f"the cache (max_seq {self.cfg.max_seq})")
+        if start + max_tokens > self.buf.history.numel():
+            raise _lib.TwmError(_lib.TWM_EINVAL, f"generate_tw_marlin_graph: {start} + {max_tokens} tokens do not fit the "
+                                                 f"token list ({self.buf.history.numel()} entries); reset_history() first")
         for _ in range(max_tokens):
             self.graph.replay()
         torch.cuda.synchronize()

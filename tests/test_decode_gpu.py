@@ -36,8 +36,7 @@ def _dense_provider(model):
             return cache[key]
         if li == -1:
             if name == "embed_row":
-                emb = model.embed.float().cpu().numpy()
-                val = lambda tok: emb[int(tok)]
+                val = lambda tok: model.embed[int(tok)].float().cpu().numpy()      # one row at a time: the table is large
             elif name == "final_norm":
                 val = model.final_norm.cpu().numpy()
             else:
@@ -95,6 +94,87 @@ def test_teacher_forced_logits_match_oracle(cfg, prefill):
     assert int(eng.buf.cache_len.item()) == prefill + len(tokens) + 1
     assert greedy_agree >= len(tokens) - 1          # near-flat random logits: one near-tie may flip
     assert q.device_error() == 0
+
+
+def test_config3_dimensions_two_layers_teacher_forced():
+    """configs[3] at its own shape: Qwen2-7B dimensions (hidden 3584, 28 query / 4 KV heads of 128, ffn
+    18944, vocabulary 152064, QKV bias), KV cache prefilled to 2048 tokens, FP16 LM head; two of the 28
+    layers (the oracle's dense FP32 copy of one layer is 0.9 GB), two teacher-forced steps."""
+    cfg = gen.TransformerConfig(hidden=3584, num_heads=28, num_kv_heads=4, head_dim=128, ffn=18944, vocab=152064, layers=2,
+                                rope_theta=1e6, eps=1e-6, max_seq=2304, group_size=128, qkv_bias=True)
+    prefill = 2048
+    model = gen.Q4Model(cfg, seed=0)
+    eng = gen.QuantizedGenerationEngine(model)
+    eng.prefill_random_kv(prefill, seed=2)
+    kc = [c.float().cpu().numpy().copy() for c in eng.buf.k_cache]
+    vc = [c.float().cpu().numpy().copy() for c in eng.buf.v_cache]
+    dense = _dense_provider(model)
+    tokens = torch.randint(0, cfg.vocab, (2,), generator=torch.Generator().manual_seed(3)).tolist()
+    for i, tok in enumerate(tokens):
+        eng.set_token(tok)
+        eng.step_eager()
+        torch.cuda.synchronize()
+        logits = eng.buf.logits.cpu().numpy()
+        ref = decode_ref.decode_step(cfg, dense, tok, prefill + i, kc, vc)
+        rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+        err = float(np.max(np.abs(logits - ref))) / rms
+        assert err < 1e-2, (i, err)
+        # the greedy token is the oracle's, or a near-tie of it (random-init logits are nearly flat)
+        tok_gpu = int(eng.buf.token.item())
+        assert 0 <= tok_gpu < cfg.vocab
+        assert ref[tok_gpu] >= float(ref.max()) - 1e-2 * rms
+        for li in range(cfg.layers):
+            kg = eng.buf.k_cache[li][prefill + i].float().cpu().numpy()
+            assert np.max(np.abs(kg - kc[li][prefill + i])) <= 2e-3 * max(1.0, float(np.abs(kc[li][prefill + i]).max()))
+    assert int(eng.buf.cache_len.item()) == prefill + len(tokens) + 1
+    assert q.device_error() == 0
+    # the same two steps as a captured graph, with the Q4 LM head option: tokens stay inside the vocabulary
+    eng2 = gen.QuantizedGenerationEngine(model, q4_lm_head=True)
+    eng2.prefill_random_kv(prefill, seed=2)
+    toks = eng2.generate_tw_marlin_graph(tokens[0], 2)
+    assert all(0 <= t < cfg.vocab for t in toks)
+    assert q.device_error() == 0
+
+
+def test_generate_refuses_to_run_past_the_cache_or_the_token_list():
+    """The host checks the bounds the device buffers have (max_seq rows of cache, max_seq token slots);
+    at the last position one more token is still fine."""
+    cfg = SMALL
+    model = gen.Q4Model(cfg, seed=3)
+    eng = gen.QuantizedGenerationEngine(model)
+    eng.prefill_random_kv(cfg.max_seq - 1, seed=2)
+    toks = eng.generate_tw_marlin_graph(1, 1)            # writes row max_seq - 1: the last one
+    assert len(toks) == 1 and 0 <= toks[0] < cfg.vocab
+    with pytest.raises(_lib.TwmError):
+        eng.generate_tw_marlin_graph(1, 1)               # the cache is full now
+    eng.prefill_random_kv(10, seed=2)
+    eng.buf.step.fill_(cfg.max_seq - 2)
+    with pytest.raises(_lib.TwmError):
+        eng.generate_tw_marlin_graph(1, 5)               # the token list would overflow
+    eng.reset_history()
+    assert len(eng.generate_tw_marlin_graph(1, 5)) == 5
+    # a replay past the list's end does not write past it (the device-side guard)
+    eng.buf.step.fill_(cfg.max_seq)
+    guard = eng.buf.history.clone()
+    eng.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(eng.buf.history, guard)
+    assert q.device_error() == 0
+
+
+def test_argmax_of_all_nan_logits_is_token_zero():
+    lib = _lib.lib()
+    n = 5000
+    logits = torch.full((n,), float("nan"), device="cuda")
+    tok = torch.full((1,), -5, dtype=torch.int32, device="cuda")
+    hist = torch.full((4,), -1, dtype=torch.int32, device="cuda")
+    pos, ln, step = (torch.zeros(1, dtype=torch.int32, device="cuda") for _ in range(3))
+    scratch = torch.zeros(lib.twm_argmax_scratch_bytes(), dtype=torch.uint8, device="cuda")
+    _lib.check(lib.twm_argmax_advance(tok.data_ptr(), hist.data_ptr(), 4, pos.data_ptr(), ln.data_ptr(), step.data_ptr(),
+                                      logits.data_ptr(), n, scratch.data_ptr(), scratch.numel(), 0,
+                                      torch.cuda.current_stream().cuda_stream), "twm_argmax_advance")
+    torch.cuda.synchronize()
+    assert int(tok.item()) == 0 and hist.tolist() == [0, -1, -1, -1] and int(step.item()) == 1
 
 
 def test_graph_replay_equals_eager_and_is_deterministic():

@@ -225,9 +225,11 @@ def test_m_beyond_eight(m, group):
     assert rel_err_floored(y32, oracle.w4a16_f64(a, packed, scales, m, n, k, group)) < TOL_F32
 
 
-def test_config2_shape_m64():
-    """configs[2] at M = 64 on the 7B gate+up shape (K=3584, N=37888), tcgen05 kernel."""
-    k, n, m, group = 3584, 37888, 64, 128
+@pytest.mark.parametrize("m", [16, 32, 64, 128, 256])
+def test_config2_shapes_beyond_eight_rows(m):
+    """configs[2] at M = 16 ... 256 on the 7B gate+up shape (K=3584, N=37888), the full launch; a
+    384-column slice of it against the oracle, every element for "written" and for linearity."""
+    k, n, group = 3584, 37888, 128
     w = torch.randn((k, n), generator=torch.Generator(device=DEV).manual_seed(77), device=DEV) * 0.02
     p, s = q.quantize_f32_to_tw_marlin(w, k, n, group)
     del w
@@ -243,17 +245,35 @@ def test_config2_shape_m64():
     scales = s.cpu().numpy().view(np.uint16)[:, cols].copy()
     ref = oracle.w4a16_f64(a, packed, scales, m, 384, k, group)
     assert rel_err_floored(c[:, cols].float().cpu().numpy(), ref) < TOL_F16
-    # and a size-independent property on the whole output: every element written, linear in the activations
+    # and size-independent properties on the whole output: every element written, linear in the activations
     assert not torch.isnan(c).any()
     c2 = torch.empty_like(c)
     q.gemm_tw_marlin(_to_dev(2.0 * a, torch.float16), p, s, c2, m, n, k, group_size=group, workspace=ws)
     torch.cuda.synchronize()
-    # (the kernel gives the activations of odd K a factor 2^-4, which rounds for |a| < 2^-10: doubling
-    #  such an activation is then not exactly doubling its product, so this is "within one FP16 step")
+    # (doubling an activation doubles its products exactly unless an intermediate FP16 value leaves the
+    #  normal range, so this is "within one FP16 step", and equal almost everywhere)
     normal = (c.abs() < 30000) & (c.abs() > 1e-3)
     step = (2 * c[normal]).abs().float() * 2.0 ** -10
     assert torch.all((c2[normal].float() - 2 * c[normal].float()).abs() <= step)
     assert (c2[normal] != 2 * c[normal]).float().mean() < 1e-3
+
+
+@pytest.mark.parametrize("m", [16, 64, 200])
+def test_tensor_core_kernel_with_tiny_activation_rows(m):
+    """Rows whose activations are tiny (1e-4 ... 1e-3) beside ordinary rows: the tensor-core kernels
+    keep them to the stated bound against the exact-weight oracle (FP16 operands run out of exponent
+    below 2^-14, so such rows are not bit-exact, only accurate to a fraction of their own RMS)."""
+    k, n, group = 2048, 512, 128
+    _, packed, scales = _quantised(k, n, group, 91)
+    a = seeded_activations(m, k, 3)
+    a[1] *= 1e-4
+    a[m - 1] *= 1e-3
+    a = a.astype(np.float16).astype(np.float32)
+    y = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float32)
+    ref = oracle.w4a16_f64(a, packed, scales, m, n, k, group)
+    for row in (0, 1, m - 1):
+        rms = float(np.sqrt(np.mean(ref[row] ** 2)))
+        assert float(np.max(np.abs(y[row] - ref[row]))) < 1e-2 * rms, row
 
 
 def test_config0_shape_vs_literal_cpu_path():
@@ -374,8 +394,14 @@ def test_errors_are_statuses():
     p = torch.zeros((k // 32, n, 16), dtype=torch.uint8, device=DEV)
     s = torch.zeros((k // 128, n), dtype=torch.float16, device=DEV)
     c = torch.zeros(n, dtype=torch.float32, device=DEV)
+    # the reference's own call has no scratch argument: without a workspace the FP32 kernel runs unsplit
+    c.fill_(1.0)
+    q.gemm_tw_marlin_m1(a, p, s, c, n, k, group_size=128, workspace=None)
+    torch.cuda.synchronize()
+    assert torch.all(c == 0)
+    # a split count the caller asks for needs its scratch
     with pytest.raises(_lib.TwmError) as e:
-        q.gemm_tw_marlin_m1(a, p, s, c, n, k, group_size=128, workspace=None)     # the FP32 kernel splits through a workspace
+        q.gemm_tw_marlin_m1(a, p, s, c, n, k, group_size=128, workspace=None, splits_override=4)
     assert e.value.status == _lib.TWM_EWORKSPACE
     with pytest.raises(_lib.TwmError) as e:
         q.gemm_tw_marlin_m1(a, p, s, c, n, k - 16, group_size=128)

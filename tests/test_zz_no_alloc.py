@@ -18,15 +18,18 @@ pytestmark = pytest.mark.gpu
 TOL_F16 = 1e-2          # the tolerance of the other FP16-output GEMM tests
 
 
-def _args(a, p, s, c, m, n, k, group, ws=None):
+def _args(a, p, s, c, m, n, k, group, ws=None, splits=0):
     return _lib.GemmArgs(M=m, N=n, K=k, group_size=group, a_dtype=_lib.TWM_F16, c_dtype=_lib.TWM_F16,
                          a=a.data_ptr(), lda=k, packed=p.data_ptr(), scales=s.data_ptr(), c=c.data_ptr(), ldc=n,
                          workspace=ws.ptr if ws is not None else None,
-                         workspace_bytes=ws.nbytes if ws is not None else 0)
+                         workspace_bytes=ws.nbytes if ws is not None else 0, splits_override=splits)
 
 
-@pytest.mark.parametrize("m,k,n", [(3, 3584, 4608), (4, 2048, 1000)])
-def test_static_scratch_matches_caller_workspace(m, k, n):
+@pytest.mark.parametrize("m,k,n,splits", [(3, 3584, 4608, 0), (4, 2048, 1000, 0), (8, 3584, 1024, 0), (16, 2048, 640, 0),
+                                            (3, 2048, 1000, 5)])
+def test_static_scratch_matches_caller_workspace(m, k, n, splits):
+    """Rows 3-4: the streaming kernel's split-K partials live in the array; rows 8 and 16: the tensor-core
+    kernel's pre-pass output and partials; the last case: a split count the caller asked for."""
     lib = _lib.lib()
     group = 128
     w = seeded_weights(k, n, 91)
@@ -35,13 +38,13 @@ def test_static_scratch_matches_caller_workspace(m, k, n):
     a = torch.from_numpy(a_np).cuda().half()
     p = torch.from_numpy(packed).cuda()
     s = torch.from_numpy(scales.view(np.float16)).cuda()
-    assert q.plan(m, n, k, group).workspace_bytes > 0, "the case must exercise the split-K scratch"
+    assert q.plan(m, n, k, group, splits_override=splits).workspace_bytes > 0, "the case must exercise the scratch"
     stream = torch.cuda.current_stream().cuda_stream
 
     # the existing entry point, with a workspace the caller allocated
-    ws = q.Workspace(q.workspace_bytes(m, n, k, group))
+    ws = q.Workspace(max(q.workspace_bytes(m, n, k, group), q.plan(m, n, k, group, splits_override=splits).workspace_bytes))
     c_ref = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
-    _lib.check(lib.twm_gemm_w4a16(C.byref(_args(a, p, s, c_ref, m, n, k, group, ws)), stream), "twm_gemm_w4a16")
+    _lib.check(lib.twm_gemm_w4a16(C.byref(_args(a, p, s, c_ref, m, n, k, group, ws, splits)), stream), "twm_gemm_w4a16")
     torch.cuda.synchronize()
     ref = c_ref.float().cpu().numpy()
     assert rel_err_floored(ref, oracle.w4a16_f64(a_np, packed, scales, m, n, k, group)) < TOL_F16
@@ -49,7 +52,7 @@ def test_static_scratch_matches_caller_workspace(m, k, n):
     # the new entry point, twice in a row on the shared array, no workspace passed
     for call in range(2):
         c_new = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
-        _lib.check(lib.twm_gemm_w4a16_static_ws(C.byref(_args(a, p, s, c_new, m, n, k, group)), stream),
+        _lib.check(lib.twm_gemm_w4a16_static_ws(C.byref(_args(a, p, s, c_new, m, n, k, group, None, splits)), stream),
                    "twm_gemm_w4a16_static_ws")
         torch.cuda.synchronize()
         got = c_new.float().cpu().numpy()
