@@ -187,9 +187,11 @@ twm_status twm_ipc_close(void* ptr);
  * enqueues and is legal during stream capture.  One chain runs on one stream at a time. */
 enum {
     TWM_A_PLAIN = 0,     /* a is f16 [M][lda] */
-    TWM_A_SILU_MUL = 1   /* a is f16 [M][lda] holding [gate | up] (up at column K): the GEMM reads
+    TWM_A_SILU_MUL = 1,  /* a is f16 [M][lda] holding [gate | up] (up at column K): the GEMM reads
                             silu(gate) * up, rounded to f16 as twm_silu_mul would have stored it
                             (fused_silu_mul, crates/kernels/src/ops.rs:966-977) */
+    TWM_A_GEGLU = 2      /* the same with tanh-gelu(gate) * up (batched_marlin_split_geglu,
+                            crates/kernels/src/moe_batched_marlin.rs:138-152); expert GEMVs only */
 };
 
 typedef struct twm_chain_op {
@@ -221,6 +223,45 @@ twm_status twm_chain_destroy(twm_chain* chain);
  * that tile) of `rank` out of `grid` for a GEMM of n_tiles x nkb 32-blocks.  Writes at most
  * `max_out` entries of five ints each and returns the count in *n_out. */
 twm_status twm_chain_partition(int n_tiles, int nkb, int grid, int rank, int max_out, int* out5, int* n_out);
+
+/* ---- Batched expert GEMVs of a mixture-of-experts layer, M = 1 --------------------------------
+ * Replace batched_marlin_gate_up, batched_marlin_split_geglu and batched_marlin_down_axpy
+ * (crates/kernels/src/moe_batched_marlin.rs:21-233): all top_k chosen experts in one launch, the
+ * choice read on the device (topk_ids holds expert numbers as floats, as the reference's router
+ * writes them), so no host round trip.  All experts' TW-Marlin tensors lie in two buffers,
+ * expert e at packed_base + e * packed_bytes_per_expert and scales_base + e * scales_per_expert.
+ * Differences from the reference: activations and gate+up outputs are FP16 (as everywhere in
+ * this library); the gated activation is computed by the down GEMV as it reads [gate | up], so
+ * there is no separate split/GEGLU pass; the weighted sum over experts is added in slot order
+ * (inside a thread-block cluster, or through the workspace when K slices x top_k exceeds a
+ * cluster), never with atomics, so it gives the same bits every run. */
+typedef struct twm_moe_args {
+    int top_k;                   /* experts chosen for this token */
+    int N, K, group_size;        /* every expert's matrix is [K, N] */
+    const void* a;               /* f16.  a_slot_stride = 0: one row shared by all slots (gate+up);
+                                    otherwise slot s reads a + s * a_slot_stride.  With a_prologue
+                                    SILU_MUL / GEGLU a row is [gate | up] of 2K values. */
+    long a_slot_stride;
+    int a_prologue;              /* TWM_A_* */
+    const uint8_t* packed_base;
+    const uint16_t* scales_base;
+    size_t packed_bytes_per_expert;   /* multiple of 16 */
+    size_t scales_per_expert;         /* elements */
+    const float* topk_ids;       /* device, [top_k] */
+    const float* topk_weights;   /* device, [top_k]: twm_moe_down_axpy only (NULL for twm_moe_gate_up) */
+    void* c;                     /* gate_up: slot s writes c + s * c_slot_stride ([N] values);
+                                    down_axpy: one row [N] = sum over slots of weight * product
+                                    (added to what c holds with TWM_FLAG_ACCUMULATE) */
+    int c_dtype;
+    long c_slot_stride;
+    void* workspace;             /* twm_moe_workspace_bytes(); zeroed once; may be NULL when that is 0 */
+    size_t workspace_bytes;
+    int flags;                   /* TWM_FLAG_PDL, TWM_FLAG_ACCUMULATE */
+} twm_moe_args;
+
+size_t twm_moe_workspace_bytes(int top_k, int N, int K, int group_size);
+twm_status twm_moe_gate_up(const twm_moe_args* args, void* stream);
+twm_status twm_moe_down_axpy(const twm_moe_args* args, void* stream);
 
 /* The same GEMM for hosts that cannot give this library any device memory of its own:
  * an engine that carves the whole GPU into weights and KV cache at start-up and has no
@@ -257,6 +298,14 @@ twm_status twm_dequant(const uint8_t* packed, const uint16_t* scales, void* out,
  * as the reference's CPU quantiser for group_size 32. */
 twm_status twm_quantize_pack(const float* w, int w_is_nk, int K, int N, int group_size,
                              uint8_t* packed, uint16_t* scales, void* stream);
+
+/* Column-major Q4_0 blocks -> TW-Marlin, on the device.  col_major_q4 holds the 20-byte blocks
+ * [f32 scale][16 nibble bytes] of column c, 32-block g at byte (c * K/32 + g) * 20, the layout every
+ * consumer in the reference reads (quantize.rs:217, 554, 726, 932).  Writes packed [K/32][N][16]
+ * and f16 scales [K/32][N] (scale group 32: a Q4_0 block has one scale per 32 values).  Replaces
+ * reorder_to_tw_marlin (quantize.rs:912-956), which copies to the host, permutes and uploads. */
+twm_status twm_reorder_to_tw_marlin(const uint8_t* col_major_q4, int K, int N, uint8_t* packed, uint16_t* scales,
+                                    void* stream);
 
 /* Concatenate `count` TW-Marlin matrices along N (fuse_tw_marlin_n,
  * quantize.rs:1018-1063).  packed_srcs/scales_srcs/ns are HOST arrays of

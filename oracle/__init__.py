@@ -177,6 +177,58 @@ def fuse_n(mats, K: int, group: int = 32):
     return out_p, out_s
 
 
+def reorder_to_tw_marlin(blocks, K: int, N: int):
+    """Column-major 20-byte Q4_0 blocks -> (packed u8 [K/32, N, 16], scales u16 [K/32, N]) (quantize.rs:912-956)."""
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+    assert blocks.size == (K // 32) * N * 20
+    packed = np.empty((K // 32, N, 16), dtype=np.uint8)
+    scales = np.empty((K // 32, N), dtype=np.uint16)
+    if lib().twmo_reorder_to_tw_marlin(_p(blocks), C.c_int(K), C.c_int(N), _p(packed), _p(scales)) != 0:
+        raise ValueError("twmo_reorder_to_tw_marlin: bad shape")
+    return packed, scales
+
+
+def tw_marlin_to_q4_0_blocks(packed, scales, K: int, N: int) -> np.ndarray:
+    """The column-major Q4_0 block form of a group-32 TW-Marlin tensor (test input builder)."""
+    out = np.empty((K // 32) * N * 20, dtype=np.uint8)
+    if lib().twmo_tw_marlin_to_q4_0_blocks(_p(np.ascontiguousarray(packed)), _p(np.ascontiguousarray(scales)), C.c_int(K),
+                                           C.c_int(N), _p(out)) != 0:
+        raise ValueError("twmo_tw_marlin_to_q4_0_blocks: bad shape")
+    return out
+
+
+def moe_gate_up(a, packed_base, scales_base, topk_ids, packed_bytes_per_expert: int, scales_per_expert: int,
+                K: int, N: int, group: int = 32) -> np.ndarray:
+    """batched_marlin_gate_up (moe_batched_marlin.rs:21-74) -> f32 [top_k, N]."""
+    a, ids = _f32(a), _f32(topk_ids)
+    out = np.empty((ids.size, N), dtype=np.float32)
+    lib().twmo_moe_gate_up(_p(a), _p(packed_base), _p(scales_base), _p(ids), C.c_long(packed_bytes_per_expert),
+                           C.c_long(scales_per_expert), C.c_int(ids.size), C.c_int(K), C.c_int(N), C.c_int(group), _p(out))
+    return out
+
+
+def moe_split_geglu(gate_up, moe_dim: int) -> np.ndarray:
+    """batched_marlin_split_geglu (moe_batched_marlin.rs:138-152) -> f32 [top_k, moe_dim]."""
+    gu = _f32(gate_up)
+    top_k = gu.size // (2 * moe_dim)
+    out = np.empty((top_k, moe_dim), dtype=np.float32)
+    lib().twmo_moe_split_geglu(_p(gu), C.c_int(top_k), C.c_int(moe_dim), _p(out))
+    return out
+
+
+def moe_down_axpy(a_all, packed_base, scales_base, topk_ids, topk_weights, packed_bytes_per_expert: int,
+                  scales_per_expert: int, K: int, N: int, group: int = 32, acc=None):
+    """batched_marlin_down_axpy (moe_batched_marlin.rs:78-134), experts added in slot order.
+    -> (acc f32 [N], the same sum accumulated in f64)."""
+    a_all, ids, wts = _f32(a_all), _f32(topk_ids), _f32(topk_weights)
+    out = np.zeros(N, dtype=np.float32) if acc is None else _f32(acc).copy()
+    out64 = out.astype(np.float64)
+    lib().twmo_moe_down_axpy(_p(a_all), C.c_long(a_all.shape[-1]), _p(packed_base), _p(scales_base), _p(ids), _p(wts),
+                             C.c_long(packed_bytes_per_expert), C.c_long(scales_per_expert), C.c_int(ids.size), C.c_int(K),
+                             C.c_int(N), C.c_int(group), _p(out), _p(out64))
+    return out, out64
+
+
 def set_threads(n: int) -> None:
     """Use `n` host threads in the threaded routines from now on."""
     lib().twmo_set_num_threads(C.c_int(int(n)))

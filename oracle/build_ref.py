@@ -24,14 +24,17 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 OUT_SO = os.path.join(OUT_DIR, "libtwm_ref.so")
 
-# constant name -> kernel it defines (all in crates/kernels/src/quantize.rs)
+# (file under crates/kernels/src, constant name): the kernel string it holds
 WANTED = [
-    "QUANTIZE_Q4_0_SRC",             # quantize.rs:103-146
-    "DEQUANTIZE_Q4_0_SRC",           # quantize.rs:150-175
-    "GEMM_Q4_0_SRC",                 # quantize.rs:186-246
-    "DEQUANT_Q4_TO_F16_SRC",         # quantize.rs:534-571
-    "GEMM_TW_MARLIN_M1_SRC",         # quantize.rs:1186-1245
-    "GEMM_TW_MARLIN_M1_DIRECT_SRC",  # quantize.rs:1249-1298
+    ("quantize.rs", "QUANTIZE_Q4_0_SRC"),                       # quantize.rs:103-146
+    ("quantize.rs", "DEQUANTIZE_Q4_0_SRC"),                     # quantize.rs:150-175
+    ("quantize.rs", "GEMM_Q4_0_SRC"),                           # quantize.rs:186-246
+    ("quantize.rs", "DEQUANT_Q4_TO_F16_SRC"),                   # quantize.rs:534-571
+    ("quantize.rs", "GEMM_TW_MARLIN_M1_SRC"),                   # quantize.rs:1186-1245
+    ("quantize.rs", "GEMM_TW_MARLIN_M1_DIRECT_SRC"),            # quantize.rs:1249-1298
+    ("moe_batched_marlin.rs", "BATCHED_MARLIN_GATE_UP_SRC"),    # moe_batched_marlin.rs:21-74
+    ("moe_batched_marlin.rs", "BATCHED_MARLIN_DOWN_AXPY_SRC"),  # moe_batched_marlin.rs:78-134
+    ("moe_batched_marlin.rs", "BATCHED_SPLIT_GEGLU_SRC"),       # moe_batched_marlin.rs:138-152
 ]
 
 
@@ -46,18 +49,20 @@ def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("TWM_REFERENCE_ROOT", "/root/reference"))
     args = ap.parse_args()
-    rs = os.path.join(args.reference, "crates", "kernels", "src", "quantize.rs")
-    if not os.path.exists(rs):
+    src_dir = os.path.join(args.reference, "crates", "kernels", "src")
+    if not os.path.exists(os.path.join(src_dir, "quantize.rs")):
         print(f"build_ref: no reference tree at {args.reference}; keeping any prebuilt {OUT_SO}")
         return 0
-    with open(rs, "r", encoding="utf-8") as f:
-        text = f.read()
+    texts = {}
+    for fname in sorted({f for f, _ in WANTED}):
+        with open(os.path.join(src_dir, fname), "r", encoding="utf-8") as f:
+            texts[fname] = f.read()
     os.makedirs(OUT_DIR, exist_ok=True)
     with tempfile.TemporaryDirectory() as tmp:
         inc = os.path.join(tmp, "ref_kernels.inc")
         with open(inc, "w", encoding="utf-8") as f:
-            for name in WANTED:
-                body = extract(text, name)
+            for fname, name in WANTED:
+                body = extract(texts[fname], name)
                 # two constants define the same helper macro name TILE; keep each body self-contained
                 f.write(f"// ---- {name}\n{body}\n#undef TILE\n")
         cmd = ["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-shared",

@@ -26,6 +26,10 @@ def lib() -> C.CDLL:
         _lib.twmref_dequantize_q4_0.argtypes = [v, v, C.c_uint, v]
         _lib.twmref_gemm_q4_0.argtypes = [v, v, v, C.c_uint, C.c_uint, C.c_uint, v]
         _lib.twmref_dequant_q4_to_f16.argtypes = [v, v, C.c_uint, C.c_uint, v]
+        u = C.c_uint
+        _lib.twmref_batched_marlin_gate_up.argtypes = [v, v, v, v, v, u, u, u, u, u, v]
+        _lib.twmref_batched_marlin_down_axpy.argtypes = [v, v, v, v, v, v, u, u, u, u, u, v]
+        _lib.twmref_batched_marlin_split_geglu.argtypes = [v, v, u, u, v]
     return _lib
 
 
@@ -58,5 +62,27 @@ def gemm_q4_0(c_ptr, a_ptr, bq_ptr, m, n, k, stream=0):
 
 def dequant_q4_to_f16(out_ptr, bq_ptr, k, n, stream=0):
     rc = lib().twmref_dequant_q4_to_f16(out_ptr, bq_ptr, k, n, stream)
+    if rc != 0:
+        raise RuntimeError(f"reference kernel launch failed: {rc}")
+
+
+def batched_marlin_gate_up(c_ptr, a_ptr, packed_ptr, scales_ptr, ids_ptr, packed_bytes_per_expert, scales_per_expert, n, k,
+                           top_k, stream=0):
+    rc = lib().twmref_batched_marlin_gate_up(c_ptr, a_ptr, packed_ptr, scales_ptr, ids_ptr, packed_bytes_per_expert,
+                                             scales_per_expert, n, k, top_k, stream)
+    if rc != 0:
+        raise RuntimeError(f"reference kernel launch failed: {rc}")
+
+
+def batched_marlin_down_axpy(acc_ptr, a_ptr, packed_ptr, scales_ptr, ids_ptr, weights_ptr, packed_bytes_per_expert,
+                             scales_per_expert, n, k, top_k, stream=0):
+    rc = lib().twmref_batched_marlin_down_axpy(acc_ptr, a_ptr, packed_ptr, scales_ptr, ids_ptr, weights_ptr,
+                                               packed_bytes_per_expert, scales_per_expert, n, k, top_k, stream)
+    if rc != 0:
+        raise RuntimeError(f"reference kernel launch failed: {rc}")
+
+
+def batched_marlin_split_geglu(out_ptr, gate_up_ptr, moe_dim, top_k, stream=0):
+    rc = lib().twmref_batched_marlin_split_geglu(out_ptr, gate_up_ptr, moe_dim, top_k, stream)
     if rc != 0:
         raise RuntimeError(f"reference kernel launch failed: {rc}")

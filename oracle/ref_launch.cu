@@ -11,6 +11,7 @@
 //   dequantize_q4_0       crates/kernels/src/quantize.rs:150-175
 //   gemm_q4_0             crates/kernels/src/quantize.rs:1840-1844 (32x32 tiles)
 //   dequant_q4_to_f16     crates/kernels/src/quantize.rs:600-606 (one thread per element)
+//   batched_marlin_*      crates/kernels/src/moe_batched_marlin.rs:155-233 (256 threads, grid (ceil(n/256), top_k))
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
 #include <stdint.h>
@@ -88,6 +89,45 @@ extern "C" int twmref_dequant_q4_to_f16(void* out, const unsigned char* b_quant,
     unsigned total = k * n;
     warp_dequant_q4_to_f16<<<(total + 255u) / 256u, 256, 0, (cudaStream_t)stream_>>>(
         (__half*)out, b_quant, k, n, k / 32u);
+    REF_CHECK();
+    return 0;
+}
+
+extern "C" int twmref_batched_marlin_gate_up(float* c, const float* a, const unsigned char* packed_base,
+                                             const unsigned short* scales_base, const float* topk_ids,
+                                             unsigned packed_bytes_per_expert, unsigned scales_per_expert, unsigned n,
+                                             unsigned k, unsigned top_k, void* stream_)
+{
+    if (k % 32u) return -1;
+    dim3 grid((n + 255u) / 256u, top_k, 1), block(256, 1, 1);
+    batched_marlin_gate_up<<<grid, block, 0, (cudaStream_t)stream_>>>(c, a, packed_base, scales_base, topk_ids,
+                                                                      packed_bytes_per_expert, scales_per_expert, (int)k,
+                                                                      (int)n, (int)(k / 32u));
+    REF_CHECK();
+    return 0;
+}
+
+extern "C" int twmref_batched_marlin_down_axpy(float* acc, const float* a_all, const unsigned char* packed_base,
+                                               const unsigned short* scales_base, const float* topk_ids,
+                                               const float* topk_weights, unsigned packed_bytes_per_expert,
+                                               unsigned scales_per_expert, unsigned n, unsigned k, unsigned top_k,
+                                               void* stream_)
+{
+    if (k % 32u) return -1;
+    dim3 grid((n + 255u) / 256u, top_k, 1), block(256, 1, 1);
+    batched_marlin_down_axpy<<<grid, block, 0, (cudaStream_t)stream_>>>(acc, a_all, packed_base, scales_base, topk_ids,
+                                                                        topk_weights, packed_bytes_per_expert,
+                                                                        scales_per_expert, (int)k, (int)n, (int)(k / 32u),
+                                                                        (int)k);
+    REF_CHECK();
+    return 0;
+}
+
+extern "C" int twmref_batched_marlin_split_geglu(float* out, const float* gate_up, unsigned moe_dim, unsigned top_k,
+                                                 void* stream_)
+{
+    dim3 grid((moe_dim + 255u) / 256u, top_k, 1), block(256, 1, 1);
+    batched_marlin_split_geglu<<<grid, block, 0, (cudaStream_t)stream_>>>(out, gate_up, (int)moe_dim);
     REF_CHECK();
     return 0;
 }

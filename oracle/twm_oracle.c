@@ -433,6 +433,127 @@ void twmo_fuse_n(const uint8_t *const *srcs, const int *ns, int count, int rows,
     }
 }
 
+/* ------------------------------------------- Q4_0 column blocks -> TW-Marlin -- */
+
+/* reorder_to_tw_marlin, crates/kernels/src/quantize.rs:912-956.  src holds the 20-byte Q4_0
+ * blocks [f32 scale][16 bytes of nibbles] of column `col`, 32-block `g` at byte
+ * (col * nkb + g) * 20 (the layout every consumer in the reference reads: quantize.rs:217, 554,
+ * 726, 932).  The nibble bytes are copied as they are; the scale is rounded to f16
+ * (half::f16::from_f32 = round to nearest even).  Scale group 32 only: a Q4_0 block carries
+ * one scale per 32 values. */
+int twmo_reorder_to_tw_marlin(const uint8_t *src, int K, int N, uint8_t *packed, uint16_t *scales)
+{
+    if (K < 32 || (K % 32) || N < 1)
+        return -1;
+    const long nkb = K / 32;
+    for (long col = 0; col < N; col++) {
+        for (long g = 0; g < nkb; g++) {
+            const uint8_t *blk = src + (col * nkb + g) * 20;
+            float scale;
+            memcpy(&scale, blk, 4);
+            scales[g * N + col] = twmo_f32_to_f16(scale);
+            memcpy(packed + (g * N + col) * 16, blk + 4, 16);
+        }
+    }
+    return 0;
+}
+
+/* The inverse direction of the layout only (not in the reference; used by tests to build
+ * column-block inputs from TW-Marlin tensors): scale widened back to f32. */
+int twmo_tw_marlin_to_q4_0_blocks(const uint8_t *packed, const uint16_t *scales, int K, int N, uint8_t *dst)
+{
+    if (K < 32 || (K % 32) || N < 1)
+        return -1;
+    const long nkb = K / 32;
+    for (long col = 0; col < N; col++) {
+        for (long g = 0; g < nkb; g++) {
+            uint8_t *blk = dst + (col * nkb + g) * 20;
+            float scale = twmo_f16_to_f32(scales[g * N + col]);
+            memcpy(blk, &scale, 4);
+            memcpy(blk + 4, packed + (g * N + col) * 16, 16);
+        }
+    }
+    return 0;
+}
+
+/* ------------------------------------------------- batched expert GEMVs (MoE) -- */
+
+/* One expert's M=1 product in the operation order of the reference's batched kernels
+ * (crates/kernels/src/moe_batched_marlin.rs:53-69 and 111-127): per 32-block a running sum
+ * `gdot += a * (float)(nibble - 8)` over the 32 values in K order, then `dot += gdot * scale`.
+ * These are separate multiplies and adds in the source; nvcc contracts them into fused
+ * multiply-adds, which is what runs, so fmaf is used here (as in twmo_m1_kernel_order).
+ * `group` generalises the scale lookup (32 = the reference). */
+static float moe_expert_dot(const float *a, const uint8_t *packed, const uint16_t *scales, int K, int N, int group, long n)
+{
+    const int nkb = K / 32;
+    float dot = 0.0f;
+    for (int g = 0; g < nkb; g++) {
+        const float scale = twmo_f16_to_f32(scales[(long)((g * 32) / group) * N + n]);
+        const uint8_t *blk = packed + ((long)g * N + n) * 16;
+        float gdot = 0.0f;
+        for (int j = 0; j < 32; j++) {
+            const int q = (j & 1) ? (blk[j >> 1] >> 4) : (blk[j >> 1] & 0x0F);
+            gdot = fmaf(a[g * 32 + j], (float)(q - 8), gdot);
+        }
+        dot = fmaf(gdot, scale, dot);
+    }
+    return dot;
+}
+
+/* batched_marlin_gate_up (moe_batched_marlin.rs:21-74): out[e][n] for the top_k experts named
+ * (as floats) in topk_ids; one shared input row. */
+void twmo_moe_gate_up(const float *a, const uint8_t *packed_base, const uint16_t *scales_base, const float *topk_ids,
+                      long packed_bytes_per_expert, long scales_per_expert, int top_k, int K, int N, int group, float *out)
+{
+    for (int e = 0; e < top_k; e++) {
+        const int eid = (int)topk_ids[e];
+        const uint8_t *packed = packed_base + (long)eid * packed_bytes_per_expert;
+        const uint16_t *scales = scales_base + (long)eid * scales_per_expert;
+#pragma omp parallel for schedule(static)
+        for (long n = 0; n < N; n++)
+            out[(long)e * N + n] = moe_expert_dot(a, packed, scales, K, N, group, n);
+    }
+}
+
+/* batched_marlin_split_geglu (moe_batched_marlin.rs:138-152): out[e][i] = gelu_tanh(gate) * up. */
+void twmo_moe_split_geglu(const float *gate_up, int top_k, int moe_dim, float *out)
+{
+    for (int e = 0; e < top_k; e++) {
+        const float *gu = gate_up + (long)e * 2 * moe_dim;
+        for (int i = 0; i < moe_dim; i++) {
+            const float g = gu[i], u = gu[moe_dim + i];
+            const float gelu_g = 0.5f * g * (1.0f + tanhf(0.7978845608f * (g + 0.044715f * g * g * g)));
+            out[(long)e * moe_dim + i] = gelu_g * u;
+        }
+    }
+}
+
+/* batched_marlin_down_axpy (moe_batched_marlin.rs:78-134): acc[n] += weight[e] * dot_e[n].  The
+ * reference adds with atomicAdd, in whatever order the experts' CTAs arrive; this restatement
+ * adds in slot order e = 0 .. top_k-1 (double accumulation in *acc64 when given, for adjudication). */
+void twmo_moe_down_axpy(const float *a_all, long a_stride, const uint8_t *packed_base, const uint16_t *scales_base,
+                        const float *topk_ids, const float *topk_weights, long packed_bytes_per_expert,
+                        long scales_per_expert, int top_k, int K, int N, int group, float *acc, double *acc64)
+{
+#pragma omp parallel for schedule(static)
+    for (long n = 0; n < N; n++) {
+        float s = acc[n];
+        double s64 = acc64 ? acc64[n] : 0.0;
+        for (int e = 0; e < top_k; e++) {
+            const int eid = (int)topk_ids[e];
+            const float d = moe_expert_dot(a_all + (long)e * a_stride, packed_base + (long)eid * packed_bytes_per_expert,
+                                           scales_base + (long)eid * scales_per_expert, K, N, group, n);
+            s += topk_weights[e] * d;
+            s64 += (double)topk_weights[e] * (double)d;
+        }
+        acc[n] = s;
+        if (acc64)
+            acc64[n] = s64;
+    }
+}
+
+
 /* Host threads the threaded routines use from now on (a launcher such as torchrun sets
  * OMP_NUM_THREADS=1 in the environment; the benchmark's CPU arm overrides that with the cores
  * the process may actually run on). */

@@ -15,7 +15,7 @@ TWM_OK, TWM_EINVAL, TWM_EALIGN, TWM_EWORKSPACE, TWM_ELAUNCH, TWM_EARCH, TWM_ETIM
 TWM_F32, TWM_F16 = 0, 1
 TWM_KERNEL_AUTO, TWM_KERNEL_SIMT, TWM_KERNEL_TC, TWM_KERNEL_MMA = 0, 1, 2, 3
 TWM_FLAG_PDL, TWM_FLAG_ACCUMULATE, TWM_FLAG_INDEPENDENT = 1, 2, 4
-TWM_A_PLAIN, TWM_A_SILU_MUL = 0, 1
+TWM_A_PLAIN, TWM_A_SILU_MUL, TWM_A_GEGLU = 0, 1, 2
 
 
 class GemmArgs(C.Structure):
@@ -39,6 +39,17 @@ class Comm(C.Structure):
     _fields_ = [("n_ranks", C.c_int), ("rank", C.c_int), ("slot_elems", C.c_long),
                 ("data", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("state", C.c_void_p),
                 ("wait_ns", C.c_ulonglong)]
+
+
+class MoeArgs(C.Structure):
+    """``twm_moe_args``."""
+    _fields_ = [("top_k", C.c_int), ("N", C.c_int), ("K", C.c_int), ("group_size", C.c_int),
+                ("a", C.c_void_p), ("a_slot_stride", C.c_long), ("a_prologue", C.c_int),
+                ("packed_base", C.c_void_p), ("scales_base", C.c_void_p),
+                ("packed_bytes_per_expert", C.c_size_t), ("scales_per_expert", C.c_size_t),
+                ("topk_ids", C.c_void_p), ("topk_weights", C.c_void_p),
+                ("c", C.c_void_p), ("c_dtype", C.c_int), ("c_slot_stride", C.c_long),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("flags", C.c_int)]
 
 
 class ChainOp(C.Structure):
@@ -67,6 +78,9 @@ SIGNATURES = {
     "twm_gemm_w4a16": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
     "twm_gemm_w4a16_static_ws": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
     "twm_static_ws_capacity": (C.c_size_t, []),
+    "twm_moe_workspace_bytes": (C.c_size_t, [C.c_int] * 4),
+    "twm_moe_gate_up": (C.c_int, [C.POINTER(MoeArgs), C.c_void_p]),
+    "twm_moe_down_axpy": (C.c_int, [C.POINTER(MoeArgs), C.c_void_p]),
     "twm_chain_create": (C.c_int, [C.POINTER(ChainOp), C.c_int, C.POINTER(C.c_void_p)]),
     "twm_chain_launch": (C.c_int, [C.c_void_p, C.c_void_p]),
     "twm_chain_info": (C.c_int, [C.c_void_p, C.POINTER(ChainInfo)]),
@@ -74,6 +88,7 @@ SIGNATURES = {
     "twm_chain_partition": (C.c_int, [C.c_int] * 5 + [C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "twm_dequant": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "twm_quantize_pack": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "twm_reorder_to_tw_marlin": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "twm_fuse_n": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.c_int, C.c_int,
                              C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "twm_slice_n": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,

@@ -192,6 +192,19 @@ struct GemmParams {
     const uint32_t* packed_offsets;
     const uint32_t* scales_offsets;
     int expert_idx;
+    // Batched expert GEMVs (mixture of experts): n_experts > 0 makes grid z the top-k slot.  Slot z
+    // multiplies the weights of expert (int)expert_ids[z] (read on the device) with its own input
+    // row (a + z * a_expert_stride; stride 0 = one shared row).  Without expert_weights every slot
+    // stores its own output row (c + z * c_expert_stride); with them the slots' results are
+    // multiplied by expert_weights[z] and added up, in slot order, into the one output row.
+    int n_experts;
+    int reduce_slices;           // K slices x slots that add up into one output tile (1 = none)
+    int a_kind;                  // 0: a is f16; 1: SwiGLU, 2: tanh-GEGLU of a row [gate | up] (up at column K)
+    const float* expert_ids;
+    const float* expert_weights;
+    size_t packed_expert_stride; // bytes
+    size_t scales_expert_stride; // elements
+    long a_expert_stride, c_expert_stride;   // elements
     // Row-parallel output pushed straight to every tensor-parallel peer (one-shot all-reduce,
     // first half).  n_peers = 0: normal store to c.  Otherwise every stored value goes, as FP32,
     // to slot `peer_rank` of the current buffer set in each peer's receive buffer
@@ -209,6 +222,8 @@ struct GemmParams {
     alignas(64) CUtensorMap packed_map;
     // tcgen05 kernel: -8 * sum of a scale group's activations per row, FP32 [K/G][NB] (written by the pre-pass)
     const float* tc_a8;
+    // tcgen05 kernel: 2^-e per row, undoing the pre-pass's power-of-two row scale, FP32 [NB]
+    const float* tc_rowscale;
     // tcgen05 kernel: tensor map over the launch's permuted activations, f16 [K/8][rows][8]
     alignas(64) CUtensorMap act_map;
 };

@@ -487,8 +487,9 @@ gemm_kernel(const __grid_constant__ GemmParams p)
             for (int j = 0; j < RC; ++j) {
                 const int m = row0 + j;
                 if (m < p.M) {
-                    if (p.splits == 1) store_c(m, acc[j]);
-                    else p.ws_partials[((size_t)blockIdx.y * p.M + m) * p.N + n] = acc[j];
+                    const float v = acc[j] * __ldg(p.tc_rowscale + m);       // undo the pre-pass's power-of-two row scale (exact)
+                    if (p.splits == 1) store_c(m, v);
+                    else p.ws_partials[((size_t)blockIdx.y * p.M + m) * p.N + n] = v;
                 }
             }
         }
@@ -524,71 +525,101 @@ gemm_kernel(const __grid_constant__ GemmParams p)
     }
 }
 
-// Pre-pass of the tcgen05 kernel, one launch per GEMM launch.
-// Blocks [0, perm_blocks): rows [0, rows) of the activations, f16 [rows][lda], rewritten as
-// [K/8][rows][8] with the eight K of a core in the order k0,k4,k1,k5,k2,k6,k3,k7 (the order in
-// which the unpack lays nibbles into tensor memory), the odd ones times 2^-4 (their nibbles sit
-// four bits higher in the operand).  One thread per (K core, row).
-// Remaining blocks: the table a8[g][m] = -8 * sum of row m's activations over scale group g, FP32,
-// [K/G][nb_pad] (rows past `rows` zero), summed in a fixed order by group/8 lanes per (g, m).
+// Pre-pass of the tcgen05 kernel, one launch per GEMM launch, one CTA per activation row.
+//
+// out: the row rewritten as [K/8][rows][8] with the eight K of a core in the order
+// k0,k4,k1,k5,k2,k6,k3,k7 (the order in which the unpack lays nibbles into tensor memory), the odd
+// ones times 2^-4 (their nibbles sit four bits higher in the operand).
+// So that the factor 2^-4 never pushes an activation out of FP16's normal range, the whole row is
+// first multiplied by a power of two 2^e chosen from the row's largest magnitude (the largest
+// value lands in [2^13, 2^14)); powers of two are exact, and the GEMM's epilogue multiplies the
+// row's results by 2^-e (rowscale).  A row of tiny activations (1e-4, say) therefore keeps all of
+// its bits; only elements more than 2^13 below their own row's maximum can still round, and they
+// do not matter to that row's sums.
+// a8[g][m] = -8 * sum of the scaled row's activations over scale group g, FP32, [K/G][nb_pad]
+// (rows past `rows` zero), summed in a fixed order: 8 values per thread, then a shuffle tree over
+// the group's group/8 consecutive threads.
 __global__ void __launch_bounds__(256)
-permute_activations_kernel(__half* __restrict__ out, float* __restrict__ a8, const __half* __restrict__ a, long lda,
-                           int rows, int kcores, int perm_blocks, int group, int nb_pad)
+permute_activations_kernel(__half* __restrict__ out, float* __restrict__ a8, float* __restrict__ rowscale,
+                           const __half* __restrict__ a, long lda, int rows, int kcores, int group, int nb_pad)
 {
     pdl_launch_dependents();
     pdl_wait_prior_grids();
-    if ((int)blockIdx.x >= perm_blocks) {
-        // group/8 consecutive lanes share one (g, m): each adds 8 values, then a fixed shuffle tree
-        const int lpg = group >> 3;                                     // 4 or 16 lanes
-        const int idx = ((int)blockIdx.x - perm_blocks) * blockDim.x + threadIdx.x;
-        const int ngroups = kcores * 8 / group;
-        const int item = idx / lpg, part = idx - item * lpg;
-        const bool live = item < ngroups * nb_pad;
-        const int g = live ? item / nb_pad : 0, m = live ? item - g * nb_pad : 0;
-        float s = 0.0f;
-        if (live && m < rows) {
-            const __half* src = a + (size_t)m * lda + (size_t)g * group + part * 8;
-            uint4 x;
-            if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-                x = *reinterpret_cast<const uint4*>(src);
-            } else {
-                const uint16_t* s16 = reinterpret_cast<const uint16_t*>(src);
-                x.x = s16[0] | ((uint32_t)s16[1] << 16); x.y = s16[2] | ((uint32_t)s16[3] << 16);
-                x.z = s16[4] | ((uint32_t)s16[5] << 16); x.w = s16[6] | ((uint32_t)s16[7] << 16);
-            }
-            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&x.x));
-            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&x.y));
-            const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&x.z));
-            const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&x.w));
-            s = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
-        }
-        for (int d = 1; d < lpg; d <<= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
-        if (live && part == 0) a8[item] = -8.0f * s;
+    __shared__ float s_max[8];
+    const int m = blockIdx.x;                         // < nb_pad
+    const int lpg = group >> 3;                       // threads per scale group: 4 or 16
+    const int ngroups = kcores * 8 / group;
+    if (m >= rows) {                                  // padding rows of the table
+        for (int g = threadIdx.x; g < ngroups; g += 256) a8[(size_t)g * nb_pad + m] = 0.0f;
+        if (threadIdx.x == 0) rowscale[m] = 1.0f;
         return;
     }
-    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= rows * kcores) return;
-    const int kc = idx / rows, m = idx - kc * rows;
-    const __half* src = a + (size_t)m * lda + (size_t)kc * 8;
-    uint4 x;
-    if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-        x = *reinterpret_cast<const uint4*>(src);
-    } else {
+    const __half* row = a + (size_t)m * lda;
+    const bool vec_ok = ((reinterpret_cast<uintptr_t>(row) & 15) == 0);
+    auto load8 = [&](int kc) -> uint4 {
+        const __half* src = row + (size_t)kc * 8;
+        if (vec_ok) return *reinterpret_cast<const uint4*>(src);
         const uint16_t* s16 = reinterpret_cast<const uint16_t*>(src);
+        uint4 x;
         x.x = s16[0] | ((uint32_t)s16[1] << 16); x.y = s16[2] | ((uint32_t)s16[3] << 16);
         x.z = s16[4] | ((uint32_t)s16[5] << 16); x.w = s16[6] | ((uint32_t)s16[7] << 16);
+        return x;
+    };
+    // pass 1: the row's largest magnitude (as FP16 bit patterns without the sign: ordered like the values)
+    uint32_t mx = 0;
+    for (int kc = threadIdx.x; kc < kcores; kc += 256) {
+        const uint4 x = load8(kc);
+        const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            mx = max(mx, w[j] & 0x7FFFu);
+            mx = max(mx, (w[j] >> 16) & 0x7FFFu);
+        }
     }
-    const __half2 sixteenth = __float2half2_rn(0.0625f);
-    uint32_t y1 = __byte_perm(x.x, x.z, 0x7632);      // k1,k5
-    uint32_t y3 = __byte_perm(x.y, x.w, 0x7632);      // k3,k7
-    const __half2 h1 = __hmul2(*reinterpret_cast<__half2*>(&y1), sixteenth);
-    const __half2 h3 = __hmul2(*reinterpret_cast<__half2*>(&y3), sixteenth);
-    uint4 o;
-    o.x = __byte_perm(x.x, x.z, 0x5410);              // k0,k4
-    o.y = *reinterpret_cast<const uint32_t*>(&h1);
-    o.z = __byte_perm(x.y, x.w, 0x5410);              // k2,k6
-    o.w = *reinterpret_cast<const uint32_t*>(&h3);
-    reinterpret_cast<uint4*>(out)[idx] = o;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = __uint_as_float(mx);
+    __syncthreads();
+    mx = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) mx = max(mx, __float_as_uint(s_max[w]));
+    // exponent of the largest value: FP16 exponent field minus 15 (subnormals count as -14); infinities
+    // and NaNs are left alone (scale 1)
+    int e = 0;
+    const int ef = (int)(mx >> 10);
+    if (mx != 0 && ef < 31) e = 13 - (max(ef, 1) - 15);
+    e = min(max(e, -3), 14);                           // 2^e itself must be a normal FP16 number for the multiply below
+    const __half2 up = __float2half2_rn(exp2f((float)e));
+    const __half2 up16th = __float2half2_rn(exp2f((float)(e - 4)));
+    if (threadIdx.x == 0) rowscale[m] = exp2f((float)-e);
+    // pass 2: scale, permute, write; per-group sums of the scaled values
+    for (int kc0 = 0; kc0 < kcores; kc0 += 256) {
+        const int kc = kc0 + threadIdx.x;
+        float s = 0.0f;
+        if (kc < kcores) {
+            const uint4 x = load8(kc);
+            uint32_t y0 = __byte_perm(x.x, x.z, 0x5410);      // k0,k4
+            uint32_t y1 = __byte_perm(x.x, x.z, 0x7632);      // k1,k5
+            uint32_t y2 = __byte_perm(x.y, x.w, 0x5410);      // k2,k6
+            uint32_t y3 = __byte_perm(x.y, x.w, 0x7632);      // k3,k7
+            const __half2 h0 = __hmul2(*reinterpret_cast<__half2*>(&y0), up);
+            const __half2 h1 = __hmul2(*reinterpret_cast<__half2*>(&y1), up16th);
+            const __half2 h2 = __hmul2(*reinterpret_cast<__half2*>(&y2), up);
+            const __half2 h3 = __hmul2(*reinterpret_cast<__half2*>(&y3), up16th);
+            uint4 o;
+            o.x = *reinterpret_cast<const uint32_t*>(&h0);
+            o.y = *reinterpret_cast<const uint32_t*>(&h1);
+            o.z = *reinterpret_cast<const uint32_t*>(&h2);
+            o.w = *reinterpret_cast<const uint32_t*>(&h3);
+            reinterpret_cast<uint4*>(out)[(size_t)kc * rows + m] = o;
+            // the group sum is of the values the MMA multiplies: the even ones as stored, the odd ones
+            // times 16 again (exact)
+            const float2 f0 = __half22float2(h0), f1 = __half22float2(h1), f2 = __half22float2(h2), f3 = __half22float2(h3);
+            s = ((f0.x + f0.y) + (f2.x + f2.y)) + 16.0f * ((f1.x + f1.y) + (f3.x + f3.y));
+        }
+        for (int d = 1; d < lpg; d <<= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+        if (kc < kcores && (kc & (lpg - 1)) == 0) a8[(size_t)(kc / lpg) * nb_pad + m] = -8.0f * s;
+    }
 }
 
 }  // namespace tc

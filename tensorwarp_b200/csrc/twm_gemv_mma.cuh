@@ -103,8 +103,46 @@ __device__ __forceinline__ uint16_t lds16_at(uint32_t addr) {
     return v;
 }
 
-// MP = activation rows staged (power of two >= M, <= 8); GSHIFT = log2(32-blocks per scale group)
-template <int MP, int GSHIFT>
+// Eight consecutive K of one activation row as eight f16.  kind 0: the row holds them; kind 1 / 2:
+// the row is a fused [gate | up] GEMM output (up at column K) and the GEMM reads
+// silu(gate) * up (crates/kernels/src/ops.rs:966-977) or tanh-gelu(gate) * up
+// (crates/kernels/src/moe_batched_marlin.rs:138-152), computed in FP32 and rounded to f16.
+__device__ __forceinline__ uint4 load_act8(const __half* p8, int up_offset, int kind, bool vec_ok) {
+    auto ld8 = [&](const __half* q8) -> uint4 {
+        if (vec_ok) return *reinterpret_cast<const uint4*>(q8);
+        const uint16_t* a16 = reinterpret_cast<const uint16_t*>(q8);
+        uint4 x;
+        x.x = a16[0] | ((uint32_t)a16[1] << 16); x.y = a16[2] | ((uint32_t)a16[3] << 16);
+        x.z = a16[4] | ((uint32_t)a16[5] << 16); x.w = a16[6] | ((uint32_t)a16[7] << 16);
+        return x;
+    };
+    const uint4 gt = ld8(p8);
+    if (kind == 0) return gt;
+    const uint4 up = ld8(p8 + up_offset);
+    const __half2* gh = reinterpret_cast<const __half2*>(&gt);
+    const __half2* uh = reinterpret_cast<const __half2*>(&up);
+    uint4 o;
+    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 gf = __half22float2(gh[j]), uf = __half22float2(uh[j]);
+        float r0, r1;
+        if (kind == 1) {
+            r0 = gf.x / (1.0f + expf(-gf.x)) * uf.x;
+            r1 = gf.y / (1.0f + expf(-gf.y)) * uf.y;
+        } else {
+            r0 = 0.5f * gf.x * (1.0f + tanhf(0.7978845608f * (gf.x + 0.044715f * gf.x * gf.x * gf.x))) * uf.x;
+            r1 = 0.5f * gf.y * (1.0f + tanhf(0.7978845608f * (gf.y + 0.044715f * gf.y * gf.y * gf.y))) * uf.y;
+        }
+        const __half2 r = __floats2half2_rn(r0, r1);
+        ow[j] = *reinterpret_cast<const uint32_t*>(&r);
+    }
+    return o;
+}
+
+// MP = activation rows staged (power of two >= M, <= 8); GSHIFT = log2(32-blocks per scale group);
+// AKIND = what the activation rows hold (0: f16 values; 1 / 2: [gate | up], see load_act8)
+template <int MP, int GSHIFT, int AKIND = 0>
 __global__ void __launch_bounds__(THREADS, TWM_MMA_MIN_CTAS)
 gemv_kernel(const __grid_constant__ GemmParams p)
 {
@@ -125,6 +163,8 @@ gemv_kernel(const __grid_constant__ GemmParams p)
     constexpr int CHUNK_BLOCKS = B_BUF_BYTES / (64 * MP);    // 64, 32, 16, 8: multiples of SB and of a group
     static_assert(CHUNK_BLOCKS % SB == 0 && CHUNK_BLOCKS <= ASUM_GROUPS, "chunk geometry");
     const int n_chunks = (total_blocks + CHUNK_BLOCKS - 1) / CHUNK_BLOCKS;
+    const int slot = p.n_experts ? (int)blockIdx.z : 0;      // top-k slot of a batched expert GEMV
+    const __half* A_base = reinterpret_cast<const __half*>(p.a) + (size_t)slot * p.a_expert_stride;
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], CONSUMER_WARPS); }
@@ -152,6 +192,12 @@ gemv_kernel(const __grid_constant__ GemmParams p)
             pdl_wait_prior_grids();                       // the offset table may come from the kernel before
             packed += p.packed_offsets[p.expert_idx];
             scales += p.scales_offsets[p.expert_idx];
+        }
+        if (p.n_experts) {
+            pdl_wait_prior_grids();                       // the router's choice comes from the kernel before
+            const size_t eid = (size_t)(int)p.expert_ids[slot];
+            packed += eid * p.packed_expert_stride;
+            scales += eid * p.scales_expert_stride;
         }
         const bool scale_bulk_ok = ((cols & 7) == 0) && ((p.N & 7) == 0) &&
                                    ((reinterpret_cast<uintptr_t>(scales + n0) & 15) == 0);
@@ -209,8 +255,9 @@ gemv_kernel(const __grid_constant__ GemmParams p)
         // fixed-order warp-shuffle reduction.  K slices start and end on group
         // boundaries (the host plan sees to that).
         if (!p.no_wait) pdl_wait_prior_grids();
-        const __half* A = reinterpret_cast<const __half*>(p.a);
-        const bool vec_ok = ((reinterpret_cast<uintptr_t>(A) & 15) == 0) && ((p.lda & 7) == 0);
+        const __half* A = A_base;
+        const bool vec_ok = ((reinterpret_cast<uintptr_t>(A) & 15) == 0) && ((p.lda & 7) == 0) &&
+                            ((p.a_expert_stride & 7) == 0);
         constexpr int PF = 8;
         for (int chunk = 1; chunk < n_chunks; ++chunk) {     // chunk 0 is staged by the consumer warps (below)
             const int buf = chunk & 1;
@@ -226,7 +273,7 @@ gemv_kernel(const __grid_constant__ GemmParams p)
                 for (int u = 0; u < PF; ++u) {
                     const int it = base + u * 32 + lane;
                     x[u] = make_uint4(0, 0, 0, 0);
-                    if (it < items) {
+                    if (u < live && it < items) {
                         const int tt = it & 3;
                         const int bj = (it >> 2) & gmask;
                         const int rest = it >> (2 + gshift);
@@ -234,13 +281,7 @@ gemv_kernel(const __grid_constant__ GemmParams p)
                         const int bi = ((rest / MP) << gshift) + bj;
                         if (m < p.M) {
                             const size_t off = (size_t)m * p.lda + (size_t)(b0 + cb0 + bi) * kBlockK + tt * 8;
-                            if (vec_ok) {
-                                x[u] = *reinterpret_cast<const uint4*>(A + off);
-                            } else {
-                                const uint16_t* a16 = reinterpret_cast<const uint16_t*>(A) + off;
-                                x[u].x = a16[0] | ((uint32_t)a16[1] << 16); x[u].y = a16[2] | ((uint32_t)a16[3] << 16);
-                                x[u].z = a16[4] | ((uint32_t)a16[5] << 16); x[u].w = a16[6] | ((uint32_t)a16[7] << 16);
-                            }
+                            x[u] = load_act8(A + off, p.K, AKIND, vec_ok);
                         }
                     }
                 }
@@ -297,8 +338,9 @@ gemv_kernel(const __grid_constant__ GemmParams p)
         // one item each, in the stager's layout and summation order: the launch's first multiply
         // then waits for one round of loads instead of the stager warp's eight.
         if (!p.no_wait) pdl_wait_prior_grids();
-        const __half* A = reinterpret_cast<const __half*>(p.a);
-        const bool vec_ok = ((reinterpret_cast<uintptr_t>(A) & 15) == 0) && ((p.lda & 7) == 0);
+        const __half* A = A_base;
+        const bool vec_ok = ((reinterpret_cast<uintptr_t>(A) & 15) == 0) && ((p.lda & 7) == 0) &&
+                            ((p.a_expert_stride & 7) == 0);
         const int items = min(CHUNK_BLOCKS, total_blocks) * MP * 4;
         const int it = tid;
         const int tt = it & 3;
@@ -310,13 +352,7 @@ gemv_kernel(const __grid_constant__ GemmParams p)
         uint4 x = make_uint4(0, 0, 0, 0);
         if (it < items && m < p.M) {
             const size_t off = (size_t)m * p.lda + (size_t)(b0 + bi) * kBlockK + tt * 8;
-            if (vec_ok) {
-                x = *reinterpret_cast<const uint4*>(A + off);
-            } else {
-                const uint16_t* a16 = reinterpret_cast<const uint16_t*>(A) + off;
-                x.x = a16[0] | ((uint32_t)a16[1] << 16); x.y = a16[2] | ((uint32_t)a16[3] << 16);
-                x.z = a16[4] | ((uint32_t)a16[5] << 16); x.w = a16[6] | ((uint32_t)a16[7] << 16);
-            }
+            x = load_act8(A + off, p.K, AKIND, vec_ok);
         }
         float s = 0.0f;
         if (it < items) {
@@ -418,9 +454,15 @@ gemv_kernel(const __grid_constant__ GemmParams p)
     // tensor-parallel push: this launch's sequence number and buffer set (stable for the whole
     // launch: only the consumer kernel that follows advances it)
     const unsigned int comm_seq = p.n_peers ? ld_volatile_u32(p.comm_state) : 0u;
+    if (p.expert_weights != nullptr && consumer) {
+        // weighted sum over the slots: every slice carries its slot's router weight into the reduction
+        const float wgt = __ldg(p.expert_weights + slot);
+        tot[0] *= wgt; tot[1] *= wgt; tot[2] *= wgt; tot[3] *= wgt;
+    }
+    const size_t c_slot_off = (p.n_experts && p.expert_weights == nullptr) ? (size_t)slot * p.c_expert_stride : 0;
     auto store_c = [&](int m, int n, float v) {
         if (m >= p.M || n >= p.N) return;
-        const size_t off = (size_t)m * p.ldc + n;
+        const size_t off = (size_t)m * p.ldc + n + c_slot_off;
         if (p.n_peers) {
             // plain stores into every peer's receive slot (its own GPU's memory), this rank's own included
             const size_t slot = ((size_t)(comm_seq & 1u) * p.n_peers + p.peer_rank) * p.peer_slot_elems + off;
@@ -475,7 +517,7 @@ gemv_kernel(const __grid_constant__ GemmParams p)
         if (rank == 0 && tid < p.M * NT && *abort_flag == 0) {
             const int m = tid / NT, col = tid - m * NT;
             float s = 0.0f;
-            for (int sp = 0; sp < p.splits; ++sp) s += sm.red[sp * p.M + m][col];
+            for (int sp = 0; sp < p.reduce_slices; ++sp) s += sm.red[sp * p.M + m][col];      // slices in (slot, K slice) order
             store_c(m, n0 + col, s);
         }
         if (p.n_peers && rank == 0) {       // only the cluster leaders store
@@ -488,7 +530,7 @@ gemv_kernel(const __grid_constant__ GemmParams p)
     if (!consumer) return;
     named_bar_sync(1, CONSUMERS);
     if (*abort_flag && !p.n_peers) return;    // a wait expired: leave C untouched, the error word is set
-    if (p.splits == 1) {
+    if (p.reduce_slices == 1) {
         if (*abort_flag == 0) {
             store_c(mA, nA, tot[0]); store_c(mB, nA, tot[1]); store_c(mA, nB, tot[2]); store_c(mB, nB, tot[3]);
         }
@@ -499,15 +541,16 @@ gemv_kernel(const __grid_constant__ GemmParams p)
         return;
     }
     auto ws_at = [&](int sp, int m, int n) -> float* { return &p.ws_partials[((size_t)sp * p.M + m) * p.N + n]; };
-    if (mA < p.M && nA < p.N) *ws_at(blockIdx.y, mA, nA) = tot[0];
-    if (mB < p.M && nA < p.N) *ws_at(blockIdx.y, mB, nA) = tot[1];
-    if (mA < p.M && nB < p.N) *ws_at(blockIdx.y, mA, nB) = tot[2];
-    if (mB < p.M && nB < p.N) *ws_at(blockIdx.y, mB, nB) = tot[3];
+    const int my_slice = slot * p.splits + blockIdx.y;                 // (slot, K slice) order
+    if (mA < p.M && nA < p.N) *ws_at(my_slice, mA, nA) = tot[0];
+    if (mB < p.M && nA < p.N) *ws_at(my_slice, mB, nA) = tot[1];
+    if (mA < p.M && nB < p.N) *ws_at(my_slice, mA, nB) = tot[2];
+    if (mB < p.M && nB < p.N) *ws_at(my_slice, mB, nB) = tot[3];
     __threadfence();
     named_bar_sync(1, CONSUMERS);
     if (tid == 0) {
         const unsigned prev = atomicAdd(&p.ws_counters[blockIdx.x], 1u);
-        sm.is_last = (prev == (unsigned)(p.splits - 1));
+        sm.is_last = (prev == (unsigned)(p.reduce_slices - 1));
     }
     named_bar_sync(1, CONSUMERS);
     if (!sm.is_last) return;
@@ -515,7 +558,7 @@ gemv_kernel(const __grid_constant__ GemmParams p)
     auto finish = [&](int m, int n) {
         if (m >= p.M || n >= p.N) return;
         float s = 0.0f;
-        for (int sp = 0; sp < p.splits; ++sp) s += ld_cg_f32(ws_at(sp, m, n));
+        for (int sp = 0; sp < p.reduce_slices; ++sp) s += ld_cg_f32(ws_at(sp, m, n));
         store_c(m, n, s);
     };
     finish(mA, nA); finish(mB, nA); finish(mA, nB); finish(mB, nB);

@@ -95,5 +95,35 @@ dequant_kernel(const uint8_t* __restrict__ packed, const uint16_t* __restrict__ 
     }
 }
 
+// Column-major 20-byte Q4_0 blocks ([f32 scale][16 nibble bytes], block (col, g) at byte
+// (col * nkb + g) * 20) -> TW-Marlin packed [g][col][16] and f16 scales [g][col]; replaces the host
+// loop of reorder_to_tw_marlin (crates/kernels/src/quantize.rs:912-956: download, permute on the
+// CPU, upload).  A 32 x 32 tile of blocks goes through shared memory so that the reads run along
+// g (contiguous in the source) and the writes along col (contiguous in the destination).
+__global__ void __launch_bounds__(1024)
+reorder_q4_0_kernel(const uint32_t* __restrict__ src /* 5 words per block */, int nkb, int N,
+                    uint8_t* __restrict__ packed, uint16_t* __restrict__ scales)
+{
+    __shared__ uint32_t tile[32][32][5 + 1];        // [col][g][word], padded against bank conflicts
+    const int g0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+    {
+        const int g = g0 + threadIdx.x, col = c0 + threadIdx.y;
+        if (g < nkb && col < N) {
+            const uint32_t* blk = src + ((size_t)col * nkb + g) * 5;
+#pragma unroll
+            for (int w = 0; w < 5; ++w) tile[threadIdx.y][threadIdx.x][w] = blk[w];
+        }
+    }
+    __syncthreads();
+    {
+        const int col = c0 + threadIdx.x, g = g0 + threadIdx.y;
+        if (g < nkb && col < N) {
+            const uint32_t* t = tile[threadIdx.x][threadIdx.y];
+            scales[(size_t)g * N + col] = __half_as_ushort(__float2half_rn(__uint_as_float(t[0])));
+            *reinterpret_cast<uint4*>(packed + ((size_t)g * N + col) * kBlockBytes) = make_uint4(t[1], t[2], t[3], t[4]);
+        }
+    }
+}
+
 }  // namespace layout
 }  // namespace twm

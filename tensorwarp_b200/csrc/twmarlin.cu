@@ -104,6 +104,10 @@ twm_status ensure_device(int* sm_count_out)
             raise_mma((const void*)twm::mma::gemv_kernel<2, 2>);
             raise_mma((const void*)twm::mma::gemv_kernel<4, 2>);
             raise_mma((const void*)twm::mma::gemv_kernel<8, 2>);
+            raise_mma((const void*)twm::mma::gemv_kernel<1, 0, 1>);      // expert GEMVs reading [gate | up]
+            raise_mma((const void*)twm::mma::gemv_kernel<1, 0, 2>);
+            raise_mma((const void*)twm::mma::gemv_kernel<1, 2, 1>);
+            raise_mma((const void*)twm::mma::gemv_kernel<1, 2, 2>);
             auto raise_chain = [&](const void* fn) {
                 if (r == cudaSuccess)
                     r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(twm::chain::Smem));
@@ -280,17 +284,23 @@ twm_status launch_mma(const twm::GemmParams& p, int mp, dim3 grid, bool pdl, cud
         attr[na].val.programmaticStreamSerializationAllowed = 1;
         ++na;
     }
-    if (p.cluster_reduce) {          // the K slices of one tile (grid y) form one cluster
-        attr[na].id = cudaLaunchAttributeClusterDimension;
+    if (p.cluster_reduce) {          // the K slices of one tile (grid y) form one cluster;
+        attr[na].id = cudaLaunchAttributeClusterDimension;      // with a weighted expert sum, so do the slots (grid z)
         attr[na].val.clusterDim.x = 1;
         attr[na].val.clusterDim.y = grid.y;
-        attr[na].val.clusterDim.z = 1;
+        attr[na].val.clusterDim.z = (p.n_experts && p.expert_weights) ? grid.z : 1;
         ++na;
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
     cudaError_t e;
-    if (p.group == 128) {
+    if (p.a_kind != 0) {            // gated-activation prologue: one activation row only (expert GEMVs)
+        if (mp != 1) return TWM_EINVAL;
+        if (p.group == 128) e = p.a_kind == 1 ? cudaLaunchKernelEx(&cfg, twm::mma::gemv_kernel<1, 2, 1>, p)
+                                              : cudaLaunchKernelEx(&cfg, twm::mma::gemv_kernel<1, 2, 2>, p);
+        else e = p.a_kind == 1 ? cudaLaunchKernelEx(&cfg, twm::mma::gemv_kernel<1, 0, 1>, p)
+                               : cudaLaunchKernelEx(&cfg, twm::mma::gemv_kernel<1, 0, 2>, p);
+    } else if (p.group == 128) {
         switch (mp) {
             case 1: e = cudaLaunchKernelEx(&cfg, twm::mma::gemv_kernel<1, 2>, p); break;
             case 2: e = cudaLaunchKernelEx(&cfg, twm::mma::gemv_kernel<2, 2>, p); break;
@@ -429,7 +439,8 @@ twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int split
     out->workspace_bytes = (splits > 1 && !cluster) ? kCounterBytes + (size_t)splits * rows * N * sizeof(float) : 0;
     if (kernel == TWM_KERNEL_TC)    // + the launch's activations in the MMA's K order and their per-group sums, behind the split-K part
         out->workspace_bytes = kCounterBytes + (splits > 1 ? (size_t)splits * rows * N * sizeof(float) : 0) +
-                               256 + (size_t)rows * K * 2 + 256 + (size_t)(K / group_size) * kTcRows * sizeof(float);
+                               256 + (size_t)rows * K * 2 + 256 + (size_t)(K / group_size) * kTcRows * sizeof(float) +
+                               256 + (size_t)kTcRows * sizeof(float);
     out->cluster_reduce = cluster ? 1 : 0;
     return TWM_OK;
 }
@@ -516,6 +527,7 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
         p.ws_counters = (unsigned int*)a->workspace;
         p.ws_partials = a->workspace ? (float*)((char*)a->workspace + kCounterBytes) : nullptr;
         p.splits = pl.splits; p.blocks_per_split = pl.blocks_per_split;
+        p.reduce_slices = pl.splits;
         p.cluster_reduce = (pl.cluster_reduce && rows <= twm::mma::CLUSTER_ROWS) ? 1 : 0;
         p.accumulate = (a->flags & TWM_FLAG_ACCUMULATE) ? 1 : 0;
         p.no_wait = ((a->flags & TWM_FLAG_INDEPENDENT) && (a->flags & TWM_FLAG_PDL) && kernel == TWM_KERNEL_MMA &&
@@ -539,13 +551,12 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
                 return TWM_ELAUNCH;
             }
             char* a8 = xp + (((size_t)rows * a->K * 2 + 255) / 256) * 256;
+            char* rs = a8 + (((size_t)(a->K / a->group_size) * kTcRows * sizeof(float) + 255) / 256) * 256;
             p.tc_a8 = (const float*)a8;
-            const int items = rows * (a->K / 8);
-            const int perm_blocks = (items + 255) / 256;
-            const int sum_blocks = ((a->K / a->group_size) * nb_rows * (a->group_size / 8) + 255) / 256;
-            st = launch_op("permute_activations_kernel", twm::tc::permute_activations_kernel, dim3(perm_blocks + sum_blocks),
-                           dim3(256), 0, a->flags & TWM_FLAG_PDL, stream_, (__half*)xp, (float*)a8, (const __half*)p.a, p.lda,
-                           rows, a->K / 8, perm_blocks, a->group_size, nb_rows);
+            p.tc_rowscale = (const float*)rs;
+            st = launch_op("permute_activations_kernel", twm::tc::permute_activations_kernel, dim3(nb_rows),
+                           dim3(256), 0, a->flags & TWM_FLAG_PDL, stream_, (__half*)xp, (float*)a8, (float*)rs,
+                           (const __half*)p.a, p.lda, rows, a->K / 8, a->group_size, nb_rows);
             if (st != TWM_OK) return st;
             st = launch_tc(p, rows, dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
         }
@@ -607,6 +618,93 @@ twm_status twm_gemm_w4a16_static_ws(const twm_gemm_args* a, void* stream_)
 }
 
 size_t twm_static_ws_capacity(void) { return kStaticWsBytes; }
+
+// ------------------------------------------------------- batched expert GEMVs (MoE) --
+namespace {
+struct MoePlan { int splits, bps, cluster; size_t workspace_bytes; };
+
+// K slices so that n_tiles x top_k x splits CTAs come close to the resident slots; a sum over the
+// slots runs inside a cluster when K slices x slots fit one, else through the workspace.
+MoePlan moe_plan(int top_k, int N, int K, int group_size, int sm_count, bool weighted)
+{
+    const int nkb = K / 32, align = group_size / 32;
+    const int n_tiles = (N + twm::mma::NT - 1) / twm::mma::NT;
+    const int slots = 2 * sm_count;
+    const int max_by_k = std::max(1, nkb / std::max(align, 4));          // at least four 32-blocks per slice
+    int splits = std::max(1, slots / std::max(1, n_tiles * top_k));
+    splits = std::min(splits, max_by_k);
+    if (!weighted) splits = std::min(splits, twm::mma::MAX_CLUSTER);
+    else if (splits * top_k > twm::mma::MAX_CLUSTER && top_k <= twm::mma::MAX_CLUSTER)
+        splits = std::max(1, std::min(splits, twm::mma::MAX_CLUSTER / top_k)) ;    // prefer the cluster: no workspace traffic
+    splits = std::min(splits, kMaxSplits);
+    int bps = (nkb + splits - 1) / splits;
+    bps = (bps + align - 1) / align * align;
+    splits = (nkb + bps - 1) / bps;
+    MoePlan pl;
+    pl.splits = splits; pl.bps = bps;
+    const int slices = weighted ? splits * top_k : splits;
+    pl.cluster = (slices > 1 && slices <= twm::mma::MAX_CLUSTER) ? 1 : 0;
+    pl.workspace_bytes = (slices > 1 && !pl.cluster) ? kCounterBytes + (size_t)slices * N * sizeof(float) : 0;
+    return pl;
+}
+
+twm_status moe_launch(const twm_moe_args* a, bool weighted, void* stream_)
+{
+    if (!a) return TWM_EINVAL;
+    if (!shape_ok(1, a->N, a->K, a->group_size) || a->top_k < 1 || a->top_k > 64) return TWM_EINVAL;
+    if (!a->a || !a->packed_base || !a->scales_base || !a->topk_ids || !a->c) return TWM_EINVAL;
+    if (weighted != (a->topk_weights != nullptr)) return TWM_EINVAL;
+    if (a->c_dtype != TWM_F32 && a->c_dtype != TWM_F16) return TWM_EINVAL;
+    if (a->a_prologue < TWM_A_PLAIN || a->a_prologue > TWM_A_GEGLU) return TWM_EINVAL;
+    if (a->a_slot_stride < 0 || (!weighted && a->c_slot_stride < a->N)) return TWM_EINVAL;
+    if ((reinterpret_cast<uintptr_t>(a->packed_base) & 15) || (a->packed_bytes_per_expert & 15)) return TWM_EALIGN;
+    if ((reinterpret_cast<uintptr_t>(a->scales_base) & 1) || (reinterpret_cast<uintptr_t>(a->a) & 1)) return TWM_EALIGN;
+    if (reinterpret_cast<uintptr_t>(a->c) & (a->c_dtype == TWM_F16 ? 1 : 3)) return TWM_EALIGN;
+    int sm_count = kDefaultSms;
+    twm_status st = ensure_device(&sm_count);
+    if (st != TWM_OK) return st;
+    const MoePlan pl = moe_plan(a->top_k, a->N, a->K, a->group_size, sm_count, weighted);
+    if (pl.workspace_bytes > 0) {
+        if (!a->workspace || a->workspace_bytes < pl.workspace_bytes) return TWM_EWORKSPACE;
+        if (reinterpret_cast<uintptr_t>(a->workspace) & 15) return TWM_EALIGN;
+    }
+    twm::GemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.M = 1; p.N = a->N; p.K = a->K; p.group = a->group_size; p.nkb = a->K / 32;
+    p.a_is_f16 = 1; p.c_is_f16 = a->c_dtype == TWM_F16;
+    p.a = a->a; p.lda = a->a_prologue == TWM_A_PLAIN ? a->K : 2L * a->K;
+    p.packed = a->packed_base; p.scales = a->scales_base;
+    p.c = a->c; p.ldc = a->N;
+    p.ws_counters = (unsigned int*)a->workspace;
+    p.ws_partials = a->workspace ? (float*)((char*)a->workspace + kCounterBytes) : nullptr;
+    p.splits = pl.splits; p.blocks_per_split = pl.bps;
+    p.reduce_slices = weighted ? pl.splits * a->top_k : pl.splits;
+    p.cluster_reduce = pl.cluster;
+    p.accumulate = (a->flags & TWM_FLAG_ACCUMULATE) ? 1 : 0;
+    p.n_experts = a->top_k;
+    p.a_kind = a->a_prologue;
+    p.expert_ids = a->topk_ids;
+    p.expert_weights = weighted ? a->topk_weights : nullptr;
+    p.packed_expert_stride = a->packed_bytes_per_expert;
+    p.scales_expert_stride = a->scales_per_expert;
+    p.a_expert_stride = a->a_slot_stride;
+    p.c_expert_stride = a->c_slot_stride;
+    p.map_rows = 0;                 // the expert is chosen on the device: rows are copied one by one, no tensor map
+    const int n_tiles = (a->N + twm::mma::NT - 1) / twm::mma::NT;
+    return launch_mma(p, 1, dim3(n_tiles, pl.splits, a->top_k), (a->flags & TWM_FLAG_PDL) != 0, (cudaStream_t)stream_);
+}
+}  // namespace
+
+size_t twm_moe_workspace_bytes(int top_k, int N, int K, int group_size)
+{
+    if (!shape_ok(1, N, K, group_size) || top_k < 1 || top_k > 64) return 0;
+    return std::max(moe_plan(top_k, N, K, group_size, kDefaultSms, true).workspace_bytes,
+                    moe_plan(top_k, N, K, group_size, kDefaultSms, false).workspace_bytes);
+}
+
+twm_status twm_moe_gate_up(const twm_moe_args* args, void* stream) { return moe_launch(args, false, stream); }
+
+twm_status twm_moe_down_axpy(const twm_moe_args* args, void* stream) { return moe_launch(args, true, stream); }
 
 // ------------------------------------------------------------------ GEMM chains --
 struct twm_chain {
@@ -869,6 +967,25 @@ twm_status twm_quantize_pack(const float* w, int w_is_nk, int K, int N, int grou
         twm::layout::quantize_pack_kernel<128><<<grid, 128, 0, stream>>>(w, w_is_nk, K, N, packed, scales);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { set_error("launch quantize_pack_kernel", e); return TWM_ELAUNCH; }
+    return TWM_OK;
+}
+
+twm_status twm_reorder_to_tw_marlin(const uint8_t* col_major_q4, int K, int N, uint8_t* packed, uint16_t* scales,
+                                    void* stream_)
+{
+    if (!col_major_q4 || !packed || !scales || K < 32 || (K % 32) || N < 1) return TWM_EINVAL;
+    if ((reinterpret_cast<uintptr_t>(col_major_q4) & 3) || (reinterpret_cast<uintptr_t>(packed) & 15) ||
+        (reinterpret_cast<uintptr_t>(scales) & 1))
+        return TWM_EALIGN;
+    twm_status st = ensure_device(nullptr);
+    if (st != TWM_OK) return st;
+    const int nkb = K / 32;
+    dim3 grid((nkb + 31) / 32, (N + 31) / 32, 1);
+    if (grid.y > 65535) return TWM_EINVAL;
+    twm::layout::reorder_q4_0_kernel<<<grid, dim3(32, 32, 1), 0, (cudaStream_t)stream_>>>(
+        reinterpret_cast<const uint32_t*>(col_major_q4), nkb, N, packed, scales);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { set_error("launch reorder_q4_0_kernel", e); return TWM_ELAUNCH; }
     return TWM_OK;
 }
 

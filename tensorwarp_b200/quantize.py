@@ -155,6 +155,20 @@ def quantize_f32_to_tw_marlin(weights: torch.Tensor, k: int, n: int, group_size:
     return packed, scales
 
 
+def reorder_to_tw_marlin(col_major_q4: torch.Tensor, k: int, n: int, *, stream=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Column-major Q4_0 blocks (20 bytes each: f32 scale + 16 nibble bytes, block (col, g) at
+    (col * k/32 + g) * 20) -> (packed u8 [k/32, n, 16], scales f16 [k/32, n]), on the device
+    (reorder_to_tw_marlin, quantize.rs:912-917; the reference does this on the host)."""
+    _require_cuda(col_major_q4)
+    if col_major_q4.dtype != torch.uint8 or col_major_q4.numel() != (k // 32) * n * 20 or not col_major_q4.is_contiguous():
+        raise TwmError(_lib.TWM_EINVAL, "reorder_to_tw_marlin: need contiguous uint8 of (k/32)*n*20 bytes")
+    packed = torch.empty((k // 32, n, 16), dtype=torch.uint8, device=col_major_q4.device)
+    scales = torch.empty((k // 32, n), dtype=torch.float16, device=col_major_q4.device)
+    check(_lib.lib().twm_reorder_to_tw_marlin(col_major_q4.data_ptr(), k, n, packed.data_ptr(), scales.data_ptr(),
+                                              _stream_ptr(stream)), "twm_reorder_to_tw_marlin")
+    return packed, scales
+
+
 def cpu_quantize_tw_marlin(data_nk: torch.Tensor, k: int, n: int, group_size: int = BLOCK_SIZE):
     """Same tensors as the reference's CPU quantiser of this name
     (gemma_moe_q4.rs:218-254), produced on the device from [N,K] input."""
@@ -215,6 +229,56 @@ def slice_tw_marlin_k(packed: torch.Tensor, scales: torch.Tensor, k: int, n: int
     p = packed.view(-1)[po.value:po.value + (k_len // 32) * n * 16].view(k_len // 32, n, 16)
     s = scales.view(-1)[so.value:so.value + (k_len // group_size) * n].view(k_len // group_size, n)
     return p, s
+
+
+def moe_workspace_bytes(top_k: int, n: int, k: int, group_size: int = BLOCK_SIZE) -> int:
+    return int(_lib.lib().twm_moe_workspace_bytes(top_k, n, k, group_size))
+
+
+def _moe_args(a, a_slot_stride, a_prologue, packed_buf, scales_buf, topk_ids, topk_weights, c, c_slot_stride,
+              packed_bytes_per_expert, scales_per_expert, n, k, top_k, group_size, workspace, flags):
+    _require_cuda(a, packed_buf, scales_buf, topk_ids, c)
+    if a.dtype != torch.float16 or c.dtype not in _DTYPES or topk_ids.dtype != torch.float32:
+        raise TwmError(_lib.TWM_EINVAL, "expert GEMV: activations float16, output float16/float32, expert ids float32")
+    return _lib.MoeArgs(top_k=top_k, N=n, K=k, group_size=group_size, a=a.data_ptr(), a_slot_stride=a_slot_stride,
+                        a_prologue=a_prologue, packed_base=packed_buf.data_ptr(), scales_base=scales_buf.data_ptr(),
+                        packed_bytes_per_expert=packed_bytes_per_expert, scales_per_expert=scales_per_expert,
+                        topk_ids=topk_ids.data_ptr(),
+                        topk_weights=topk_weights.data_ptr() if topk_weights is not None else None,
+                        c=c.data_ptr(), c_dtype=_DTYPES[c.dtype], c_slot_stride=c_slot_stride,
+                        workspace=workspace.ptr if workspace is not None else None,
+                        workspace_bytes=workspace.nbytes if workspace is not None else 0, flags=flags)
+
+
+def batched_marlin_gate_up(input: torch.Tensor, packed_buf: torch.Tensor, scales_buf: torch.Tensor, topk_ids: torch.Tensor,
+                           output: torch.Tensor, packed_bytes_per_expert: int, scales_per_expert: int, n: int, k: int,
+                           top_k: int, *, group_size: int = BLOCK_SIZE, workspace: Optional[Workspace] = None,
+                           stream=None, flags: int = 0) -> None:
+    """All top_k experts' gate+up GEMVs in one launch (batched_marlin_gate_up,
+    moe_batched_marlin.rs:155-185): output[e, :] = input x W[topk_ids[e]].  `input` is one f16 row of
+    k values, `output` is [top_k, n]."""
+    args = _moe_args(input, 0, _lib.TWM_A_PLAIN, packed_buf, scales_buf, topk_ids, None, output, n,
+                     packed_bytes_per_expert, scales_per_expert, n, k, top_k, group_size, workspace, flags)
+    check(_lib.lib().twm_moe_gate_up(C.byref(args), _stream_ptr(stream)), "twm_moe_gate_up")
+
+
+def batched_marlin_down_axpy(gate_up_all: torch.Tensor, packed_buf: torch.Tensor, scales_buf: torch.Tensor,
+                             topk_ids: torch.Tensor, topk_weights: torch.Tensor, acc: torch.Tensor,
+                             packed_bytes_per_expert: int, scales_per_expert: int, n: int, k: int, top_k: int, *,
+                             activation: str = "geglu", group_size: int = BLOCK_SIZE,
+                             workspace: Optional[Workspace] = None, stream=None, flags: int = 0) -> None:
+    """All top_k experts' down GEMVs and the router-weighted sum in one launch
+    (batched_marlin_split_geglu + batched_marlin_down_axpy, moe_batched_marlin.rs:187-233).
+    gate_up_all is the gate+up output [top_k, 2k] (f16): the kernel reads gelu_tanh(gate) * up
+    ("geglu"), silu(gate) * up ("swiglu"), or with activation="none" a [top_k, k] tensor as it is.
+    acc[n] = (acc[n] with TWM_FLAG_ACCUMULATE) + sum over slots in slot order."""
+    pro = {"geglu": _lib.TWM_A_GEGLU, "swiglu": _lib.TWM_A_SILU_MUL, "none": _lib.TWM_A_PLAIN}[activation]
+    stride = k if pro == _lib.TWM_A_PLAIN else 2 * k
+    if topk_weights.dtype != torch.float32:
+        raise TwmError(_lib.TWM_EINVAL, "batched_marlin_down_axpy: router weights must be float32")
+    args = _moe_args(gate_up_all, stride, pro, packed_buf, scales_buf, topk_ids, topk_weights, acc, 0,
+                     packed_bytes_per_expert, scales_per_expert, n, k, top_k, group_size, workspace, flags)
+    check(_lib.lib().twm_moe_down_axpy(C.byref(args), _stream_ptr(stream)), "twm_moe_down_axpy")
 
 
 class GemmChain:
@@ -330,6 +394,23 @@ class TWMarlinWeights:
     bv: Optional[torch.Tensor] = None
     wqkv: Optional[Tuple[torch.Tensor, torch.Tensor]] = field(default=None)
     wgu: Optional[Tuple[torch.Tensor, torch.Tensor]] = field(default=None)
+
+    @classmethod
+    def from_quantized(cls, qw: dict, hidden: int, kv_dim: int, ffn: int, fuse: bool = False) -> "TWMarlinWeights":
+        """From a layer held as column-major Q4_0 blocks (TWMarlinWeights::from_quantized,
+        quantize.rs:1090-1134).  `qw` maps the reference's field names (wq, wk, wv, wo, w_gate, w_up,
+        w_down: uint8 block tensors; attn_norm, ffn_norm: f32; optional bq, bk, bv) to tensors.  Scale
+        group 32, as the blocks carry it."""
+        def r(name, k, n):
+            return reorder_to_tw_marlin(qw[name], k, n)
+        out = cls(hidden=hidden, kv_dim=kv_dim, ffn=ffn, group_size=32, attn_norm=qw["attn_norm"].clone(),
+                  ffn_norm=qw["ffn_norm"].clone(), wq=r("wq", hidden, hidden), wk=r("wk", hidden, kv_dim),
+                  wv=r("wv", hidden, kv_dim), wo=r("wo", hidden, hidden), w_gate=r("w_gate", hidden, ffn),
+                  w_up=r("w_up", hidden, ffn), w_down=r("w_down", ffn, hidden),
+                  bq=qw.get("bq"), bk=qw.get("bk"), bv=qw.get("bv"))
+        if fuse:
+            out.fuse_projections()
+        return out
 
     def fuse_projections(self) -> None:
         """Build the fused QKV and gate+up matrices (quantize.rs:1138-1165)."""
