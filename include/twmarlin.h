@@ -46,6 +46,8 @@ enum {
     TWM_KERNEL_AUTO = 0,
     TWM_KERNEL_SIMT = 1, /* streaming kernel, FP32 FMA; the only one that takes FP32 activations */
     TWM_KERNEL_TC = 2,   /* tcgen05 kernel: weights dequantised into tensor memory, FP32 accumulate in TMEM */
+    TWM_KERNEL_TCW = 4,  /* tcgen05 kernel for many rows (65 .. 128 per launch, group 128, N >= 128): the activation rows
+                            are the MMA's M dimension, the unpacked weights its N = 128 */
     TWM_KERNEL_MMA = 3   /* streaming kernel for M <= 8, FP16 activations, warp-level MMA on unpacked registers,
                             128-column tiles with split-K (inside a thread-block cluster for M <= 2) */
 };

@@ -143,15 +143,6 @@ struct Smem {
     int last_cta;
 };
 
-// Development builds only (-DTWM_CHAIN_TL): wall-clock marks of the first CTAs, per GEMM and role.
-#ifdef TWM_CHAIN_TL
-__device__ unsigned long long g_chain_tl[8 * 128 * 16];
-__device__ __forceinline__ unsigned long long chain_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define CTL(op, idx) do { if (cta < 8 && (op) < 128 && lane == 0) g_chain_tl[((cta * 128) + (op)) * 16 + (idx)] = chain_gtime(); } while (0)
-#else
-#define CTL(op, idx) do { } while (0)
-#endif
-
 __device__ __forceinline__ unsigned int ld_acquire_gpu_u32(const unsigned int* p) {
     unsigned int v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -287,8 +278,6 @@ chain_kernel(const Op* __restrict__ ops, int n_ops, State* __restrict__ st, unsi
         bool ok = true;
         prefetch_op(1);
         for (int oi = 0; oi < n_ops && ok; ++oi) {
-            CTL(oi, 0);
-            bool first_tma = true;
             prefetch_op(oi + 2);
             const Op& op = ops[oi];
             const int N = op.N, gshift = op.gshift;
@@ -340,7 +329,6 @@ chain_kernel(const Op* __restrict__ ops, int n_ops, State* __restrict__ st, unsi
                                  (uint32_t)cols * 2, &sm.full[slot]);
                     }
                     __syncwarp();
-                    if (first_tma) { CTL(oi, 1); first_tma = false; }
                 }
             }
         }
@@ -356,8 +344,6 @@ chain_kernel(const Op* __restrict__ ops, int n_ops, State* __restrict__ st, unsi
             Walker w;
             w.start(my_rank(op.rot), op.total_units, op.ranks, op.units_per_tile, op.nkb);
             if (w.u >= w.u1) continue;         // nothing to do for this GEMM: nothing to wait for either
-            CTL(oi, 2);
-            bool first_chunk = true;
             const int gshift = op.gshift;
             const int gmask = (1 << gshift) - 1;
             const int M = op.M, K = op.K;
@@ -400,7 +386,6 @@ chain_kernel(const Op* __restrict__ ops, int n_ops, State* __restrict__ st, unsi
                 if (!got) ok = false;
             }
             if (!ok) break;
-            CTL(oi, 3);
             Piece pc;
             while (ok && w.next(pc)) {
                 const int total_blocks = pc.blk1 - pc.blk0;
@@ -453,7 +438,6 @@ chain_kernel(const Op* __restrict__ ops, int n_ops, State* __restrict__ st, unsi
                                 }
                             }
                         }
-                        if (first_chunk) { CTL(oi, 10); }
                         if (!waited) {
                             if (use > 0) {
                                 const bool got = mbar_wait_bounded(&sm.b_empty[buf], (use - 1) & 1, abort_flag);
@@ -492,7 +476,6 @@ chain_kernel(const Op* __restrict__ ops, int n_ops, State* __restrict__ st, unsi
                     if (!ok) break;
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sm.b_full[buf]);
-                    if (first_chunk) { CTL(oi, 4); first_chunk = false; }
                 }
             }
         }
@@ -517,7 +500,6 @@ chain_kernel(const Op* __restrict__ ops, int n_ops, State* __restrict__ st, unsi
                     const bool got = mbar_wait_bounded(&sm.out_full[ob], use & 1, abort_flag);
                     if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
                 }
-                CTL(oi, 8);
                 float4 v[MP];
 #pragma unroll
                 for (int m = 0; m < MP; ++m) v[m] = *reinterpret_cast<const float4*>(&sm.out[ob][m][lane * 4]);
@@ -587,12 +569,10 @@ chain_kernel(const Op* __restrict__ ops, int n_ops, State* __restrict__ st, unsi
                     for (int m = 0; m < MP; ++m)
                         if (m < M) store4(m, v[m]);
                     __syncwarp();
-                    CTL(oi, 9);
                     if (lane == 0) {
                         if (pc.n_pieces > 1) op.tile_counters[pc.tile] = 0u;     // nobody touches it again in this launch
                         red_release_gpu_add(&done[oi], 1u);                      // one more tile of this GEMM is in memory
                     }
-                    CTL(oi, 7);
                 }
             }
         }
@@ -613,7 +593,6 @@ chain_kernel(const Op* __restrict__ ops, int n_ops, State* __restrict__ st, unsi
             w.start(my_rank(op.rot), op.total_units, op.ranks, op.units_per_tile, op.nkb);
             const int gshift = op.gshift;
             Piece pc;
-            bool first_stage = true;
             while (w.next(pc)) {
                 float tot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                 const int total_blocks = pc.blk1 - pc.blk0;
@@ -635,8 +614,6 @@ chain_kernel(const Op* __restrict__ ops, int n_ops, State* __restrict__ st, unsi
                         const bool got = mbar_wait_bounded(&sm.full[slot], (it / STAGES) & 1, abort_flag);
                         if (!__all_sync(0xffffffffu, got)) ok = false;
                     }
-                    if (first_stage && warp == 0) { CTL(oi, 5); }
-                    first_stage = false;
                     if (ok) {
                         const uint32_t w_st = w_base + slot * (SB * NT * kBlockBytes);
                         const uint32_t s_st = s_base + slot * (SB * NT * 2);
@@ -653,7 +630,6 @@ chain_kernel(const Op* __restrict__ ops, int n_ops, State* __restrict__ st, unsi
                     }
                 }
                 cs += n_chunks;
-                if (warp == 0) { CTL(oi, 6); }
                 // ---- the piece is done: leave its sums in shared memory for the epilogue warp ----
                 // lane (g, t) holds C[m = 2t, 2t+1][column wcol + g] and the same rows for column + 8
                 const int ob = pcount % OUT_BUFS;

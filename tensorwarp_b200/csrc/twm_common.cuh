@@ -222,8 +222,6 @@ struct GemmParams {
     alignas(64) CUtensorMap packed_map;
     // tcgen05 kernel: -8 * sum of a scale group's activations per row, FP32 [K/G][NB] (written by the pre-pass)
     const float* tc_a8;
-    // tcgen05 kernel: 2^-e per row, undoing the pre-pass's power-of-two row scale, FP32 [NB]
-    const float* tc_rowscale;
     // tcgen05 kernel: tensor map over the launch's permuted activations, f16 [K/8][rows][8]
     alignas(64) CUtensorMap act_map;
 };

@@ -13,11 +13,13 @@
 // The weight operand is never converted.  A nibble left in place in its 16-bit
 // half IS an FP16 subnormal: `v & 0x000F000F` = (q0, q4) * 2^-24, `v & 0x00F000F0`
 // = (q1, q5) * 2^-20, the same on `v >> 8` for (q2, q6), (q3, q7): five integer
-// instructions per eight nibbles, and the sixteen registers of a 32-block go into
-// tensor memory with one tcgen05.st as the MMA's A operand.  The factor 16 of the
-// odd nibbles is taken out of their activations (times 2^-4, exact) by the
-// pre-pass; the "-8" becomes -8 * sum of the group's activations (FP32 table from
-// the pre-pass); the scale meets the accumulator when a group's sum is read back.
+// instructions per eight nibbles; one FP16 multiply by 2^-4 brings each odd pair
+// down to 2^-24 as well (a subnormal times a power of two: exact), and the sixteen
+// registers of a 32-block go into tensor memory with one tcgen05.st as the MMA's A
+// operand.  The activations enter as they are (the pre-pass only reorders them), so
+// every product is exact whatever their magnitude; the "-8" becomes -8 * sum of the
+// group's activations (FP32 table from the pre-pass); the scale meets the
+// accumulator when a group's sum is read back.
 //
 // Data path per CTA (128 columns x a K slice of whole scale groups):
 //   warp 12      streams packed rows (one tiled TMA load per stage of four
@@ -53,6 +55,13 @@ constexpr int DEQ_THREADS = DEQ_SETS * 128;
 constexpr int WARP_READ0 = 8;         // first read-back warp
 constexpr int B_STAGE_KCORES = WSTAGE_BLOCKS * 4;     // 8-wide K cores per activation stage
 constexpr int A8_SMEM_FLOATS = 8192;  // the K slice's -8*sum table is copied into shared memory when it fits (32 KB)
+
+// (n << 4) * 2^-24 as two FP16 subnormals -> n * 2^-24: exact, and on the FP16 pipe, which the unpack leaves idle
+__device__ __forceinline__ uint32_t sixteenth(uint32_t pair)
+{
+    const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&pair), __float2half2_rn(0.0625f));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
 
 template <int NB>
 struct Cfg {
@@ -393,9 +402,9 @@ gemm_kernel(const __grid_constant__ GemmParams p)
                         const uint32_t x = words[w];
                         const uint32_t x8 = x >> 8;
                         regs[4 * w + 0] = x & 0x000F000Fu;         // (k0, k4) * 2^-24
-                        regs[4 * w + 1] = x & 0x00F000F0u;         // (k1, k5) * 2^-20: their activations carry 2^-4
+                        regs[4 * w + 1] = sixteenth(x & 0x00F000F0u);         // (k1, k5) * 2^-20, times 2^-4
                         regs[4 * w + 2] = x8 & 0x000F000Fu;        // (k2, k6) * 2^-24
-                        regs[4 * w + 3] = x8 & 0x00F000F0u;        // (k3, k7) * 2^-20
+                        regs[4 * w + 3] = sixteenth(x8 & 0x00F000F0u);        // (k3, k7) * 2^-20, times 2^-4
                     }
                     tmem_st16(lane_tmem + aslot * C::A_SLOT_COLS + r * 16, regs);
                 }
@@ -435,7 +444,7 @@ gemm_kernel(const __grid_constant__ GemmParams p)
         if (a8_local) {
             const float4* src = reinterpret_cast<const float4*>(p.tc_a8 + (size_t)grow0 * NB);
             float4* dst = reinterpret_cast<float4*>(sm.a8);
-            for (int i = tid - WARP_READ0 * 32; i < n_groups * NB / 4; i += EPI_THREADS) dst[i] = __ldg(src + i);
+            for (int i = tid - WARP_READ0 * 32; i < n_groups * NB / 4; i += EPI_THREADS) dst[i] = __ldcg(src + i);       // not through L1: see twm_gemm_tcw.cuh
         }
         named_bar_sync(2, EPI_THREADS);
         for (int gq = 0; gq < n_groups; ++gq) {
@@ -456,7 +465,8 @@ gemm_kernel(const __grid_constant__ GemmParams p)
                 if (row0 + c0 < p.M) {                                 // warp-uniform
                     uint32_t d[8];
                     tmem_ld<8>(lane_tmem + C::D_COL0 + db * NB + row0 + c0, d);
-                    const float4 q0 = a8p[(row0 + c0) / 4], q1 = a8p[(row0 + c0) / 4 + 1];
+                    const float4 q0 = a8_local ? a8p[(row0 + c0) / 4] : __ldcg(a8p + (row0 + c0) / 4);
+                    const float4 q1 = a8_local ? a8p[(row0 + c0) / 4 + 1] : __ldcg(a8p + (row0 + c0) / 4 + 1);
                     const float a8[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
                     tmem_wait_ld();
 #pragma unroll
@@ -487,7 +497,7 @@ gemm_kernel(const __grid_constant__ GemmParams p)
             for (int j = 0; j < RC; ++j) {
                 const int m = row0 + j;
                 if (m < p.M) {
-                    const float v = acc[j] * __ldg(p.tc_rowscale + m);       // undo the pre-pass's power-of-two row scale (exact)
+                    const float v = acc[j];
                     if (p.splits == 1) store_c(m, v);
                     else p.ws_partials[((size_t)blockIdx.y * p.M + m) * p.N + n] = v;
                 }
@@ -525,101 +535,66 @@ gemm_kernel(const __grid_constant__ GemmParams p)
     }
 }
 
-// Pre-pass of the tcgen05 kernel, one launch per GEMM launch, one CTA per activation row.
-//
-// out: the row rewritten as [K/8][rows][8] with the eight K of a core in the order
-// k0,k4,k1,k5,k2,k6,k3,k7 (the order in which the unpack lays nibbles into tensor memory), the odd
-// ones times 2^-4 (their nibbles sit four bits higher in the operand).
-// So that the factor 2^-4 never pushes an activation out of FP16's normal range, the whole row is
-// first multiplied by a power of two 2^e chosen from the row's largest magnitude (the largest
-// value lands in [2^13, 2^14)); powers of two are exact, and the GEMM's epilogue multiplies the
-// row's results by 2^-e (rowscale).  A row of tiny activations (1e-4, say) therefore keeps all of
-// its bits; only elements more than 2^13 below their own row's maximum can still round, and they
-// do not matter to that row's sums.
-// a8[g][m] = -8 * sum of the scaled row's activations over scale group g, FP32, [K/G][nb_pad]
-// (rows past `rows` zero), summed in a fixed order: 8 values per thread, then a shuffle tree over
-// the group's group/8 consecutive threads.
+// Pre-pass of the tcgen05 kernels, one launch per GEMM launch.
+// Blocks [0, perm_blocks): rows [0, rows) of the activations, f16 [rows][lda], rewritten as
+// [K/8][rows][8] with the eight K of a core in the order k0,k4,k1,k5,k2,k6,k3,k7 (the order in
+// which the unpack lays nibbles into the operand); the values themselves are not touched, so any
+// FP16 activation, subnormals included, enters the products exactly.  One thread per (K core, row).
+// Remaining blocks: the table a8[g][m] = -8 * sum of row m's activations over scale group g, FP32,
+// [K/G][nb_pad] (rows past `rows` zero), summed in a fixed order by group/8 lanes per (g, m).
 __global__ void __launch_bounds__(256)
-permute_activations_kernel(__half* __restrict__ out, float* __restrict__ a8, float* __restrict__ rowscale,
-                           const __half* __restrict__ a, long lda, int rows, int kcores, int group, int nb_pad)
+permute_activations_kernel(__half* __restrict__ out, float* __restrict__ a8, const __half* __restrict__ a, long lda,
+                           int rows, int kcores, int perm_blocks, int group, int nb_pad)
 {
     pdl_launch_dependents();
     pdl_wait_prior_grids();
-    __shared__ float s_max[8];
-    const int m = blockIdx.x;                         // < nb_pad
-    const int lpg = group >> 3;                       // threads per scale group: 4 or 16
-    const int ngroups = kcores * 8 / group;
-    if (m >= rows) {                                  // padding rows of the table
-        for (int g = threadIdx.x; g < ngroups; g += 256) a8[(size_t)g * nb_pad + m] = 0.0f;
-        if (threadIdx.x == 0) rowscale[m] = 1.0f;
-        return;
-    }
-    const __half* row = a + (size_t)m * lda;
-    const bool vec_ok = ((reinterpret_cast<uintptr_t>(row) & 15) == 0);
-    auto load8 = [&](int kc) -> uint4 {
-        const __half* src = row + (size_t)kc * 8;
-        if (vec_ok) return *reinterpret_cast<const uint4*>(src);
-        const uint16_t* s16 = reinterpret_cast<const uint16_t*>(src);
-        uint4 x;
-        x.x = s16[0] | ((uint32_t)s16[1] << 16); x.y = s16[2] | ((uint32_t)s16[3] << 16);
-        x.z = s16[4] | ((uint32_t)s16[5] << 16); x.w = s16[6] | ((uint32_t)s16[7] << 16);
-        return x;
-    };
-    // pass 1: the row's largest magnitude (as FP16 bit patterns without the sign: ordered like the values)
-    uint32_t mx = 0;
-    for (int kc = threadIdx.x; kc < kcores; kc += 256) {
-        const uint4 x = load8(kc);
-        const uint32_t w[4] = {x.x, x.y, x.z, x.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            mx = max(mx, w[j] & 0x7FFFu);
-            mx = max(mx, (w[j] >> 16) & 0x7FFFu);
-        }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = __uint_as_float(mx);
-    __syncthreads();
-    mx = 0;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) mx = max(mx, __float_as_uint(s_max[w]));
-    // exponent of the largest value: FP16 exponent field minus 15 (subnormals count as -14); infinities
-    // and NaNs are left alone (scale 1)
-    int e = 0;
-    const int ef = (int)(mx >> 10);
-    if (mx != 0 && ef < 31) e = 13 - (max(ef, 1) - 15);
-    e = min(max(e, -3), 14);                           // 2^e itself must be a normal FP16 number for the multiply below
-    const __half2 up = __float2half2_rn(exp2f((float)e));
-    const __half2 up16th = __float2half2_rn(exp2f((float)(e - 4)));
-    if (threadIdx.x == 0) rowscale[m] = exp2f((float)-e);
-    // pass 2: scale, permute, write; per-group sums of the scaled values
-    for (int kc0 = 0; kc0 < kcores; kc0 += 256) {
-        const int kc = kc0 + threadIdx.x;
+    if ((int)blockIdx.x >= perm_blocks) {
+        // group/8 consecutive lanes share one (g, m): each adds 8 values, then a fixed shuffle tree
+        const int lpg = group >> 3;                                     // 4 or 16 lanes
+        const int idx = ((int)blockIdx.x - perm_blocks) * blockDim.x + threadIdx.x;
+        const int ngroups = kcores * 8 / group;
+        const int item = idx / lpg, part = idx - item * lpg;
+        const bool live = item < ngroups * nb_pad;
+        const int g = live ? item / nb_pad : 0, m = live ? item - g * nb_pad : 0;
         float s = 0.0f;
-        if (kc < kcores) {
-            const uint4 x = load8(kc);
-            uint32_t y0 = __byte_perm(x.x, x.z, 0x5410);      // k0,k4
-            uint32_t y1 = __byte_perm(x.x, x.z, 0x7632);      // k1,k5
-            uint32_t y2 = __byte_perm(x.y, x.w, 0x5410);      // k2,k6
-            uint32_t y3 = __byte_perm(x.y, x.w, 0x7632);      // k3,k7
-            const __half2 h0 = __hmul2(*reinterpret_cast<__half2*>(&y0), up);
-            const __half2 h1 = __hmul2(*reinterpret_cast<__half2*>(&y1), up16th);
-            const __half2 h2 = __hmul2(*reinterpret_cast<__half2*>(&y2), up);
-            const __half2 h3 = __hmul2(*reinterpret_cast<__half2*>(&y3), up16th);
-            uint4 o;
-            o.x = *reinterpret_cast<const uint32_t*>(&h0);
-            o.y = *reinterpret_cast<const uint32_t*>(&h1);
-            o.z = *reinterpret_cast<const uint32_t*>(&h2);
-            o.w = *reinterpret_cast<const uint32_t*>(&h3);
-            reinterpret_cast<uint4*>(out)[(size_t)kc * rows + m] = o;
-            // the group sum is of the values the MMA multiplies: the even ones as stored, the odd ones
-            // times 16 again (exact)
-            const float2 f0 = __half22float2(h0), f1 = __half22float2(h1), f2 = __half22float2(h2), f3 = __half22float2(h3);
-            s = ((f0.x + f0.y) + (f2.x + f2.y)) + 16.0f * ((f1.x + f1.y) + (f3.x + f3.y));
+        if (live && m < rows) {
+            const __half* src = a + (size_t)m * lda + (size_t)g * group + part * 8;
+            uint4 x;
+            if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+                x = *reinterpret_cast<const uint4*>(src);
+            } else {
+                const uint16_t* s16 = reinterpret_cast<const uint16_t*>(src);
+                x.x = s16[0] | ((uint32_t)s16[1] << 16); x.y = s16[2] | ((uint32_t)s16[3] << 16);
+                x.z = s16[4] | ((uint32_t)s16[5] << 16); x.w = s16[6] | ((uint32_t)s16[7] << 16);
+            }
+            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&x.x));
+            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&x.y));
+            const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&x.z));
+            const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&x.w));
+            s = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
         }
         for (int d = 1; d < lpg; d <<= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
-        if (kc < kcores && (kc & (lpg - 1)) == 0) a8[(size_t)(kc / lpg) * nb_pad + m] = -8.0f * s;
+        if (live && part == 0) a8[item] = -8.0f * s;
+        return;
     }
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * kcores) return;
+    const int kc = idx / rows, m = idx - kc * rows;
+    const __half* src = a + (size_t)m * lda + (size_t)kc * 8;
+    uint4 x;
+    if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+        x = *reinterpret_cast<const uint4*>(src);
+    } else {
+        const uint16_t* s16 = reinterpret_cast<const uint16_t*>(src);
+        x.x = s16[0] | ((uint32_t)s16[1] << 16); x.y = s16[2] | ((uint32_t)s16[3] << 16);
+        x.z = s16[4] | ((uint32_t)s16[5] << 16); x.w = s16[6] | ((uint32_t)s16[7] << 16);
+    }
+    uint4 o;
+    o.x = __byte_perm(x.x, x.z, 0x5410);              // k0,k4
+    o.y = __byte_perm(x.x, x.z, 0x7632);              // k1,k5
+    o.z = __byte_perm(x.y, x.w, 0x5410);              // k2,k6
+    o.w = __byte_perm(x.y, x.w, 0x7632);              // k3,k7
+    reinterpret_cast<uint4*>(out)[idx] = o;
 }
 
 }  // namespace tc

@@ -18,6 +18,7 @@
 #include "twm_common.cuh"
 #include "twm_gemv_simt.cuh"
 #include "twm_gemm_tc.cuh"
+#include "twm_gemm_tcw.cuh"
 #include "twm_gemv_mma.cuh"
 #include "twm_chain.cuh"
 #include "twm_layout.cuh"
@@ -90,6 +91,7 @@ twm_status ensure_device(int* sm_count_out)
             raise_tc((const void*)twm::tc::gemm_kernel<16>, tc_smem_bytes(16));
             raise_tc((const void*)twm::tc::gemm_kernel<32>, tc_smem_bytes(32));
             raise_tc((const void*)twm::tc::gemm_kernel<64>, tc_smem_bytes(64));
+            raise_tc((const void*)twm::tcw::gemm_kernel, sizeof(twm::tcw::Smem));
             auto raise_mma = [&](const void* fn) {
                 if (r == cudaSuccess)
                     r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(twm::mma::Smem));
@@ -172,6 +174,22 @@ bool make_act_map(CUtensorMap* map, const void* xp, int rows, int K, int nb_rows
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Tensor map over the permuted activations of one wide tcgen05 launch, f16 [K/8][rows][8], seen as
+// 64-bit words [K/8][rows * 2]: a box of 256 words x 16 K cores is one scale group of 128 K for
+// 128 rows, landing as [K core][row][16 bytes]; rows past `rows` read as zero.
+bool make_act_map_wide(CUtensorMap* map, const void* xp, int rows, int K)
+{
+    EncodeTiledFn enc = get_encode_tiled();
+    if (!enc) return false;
+    const cuuint64_t gdim[2] = {(cuuint64_t)rows * 2, (cuuint64_t)K / 8};
+    const cuuint64_t gstride[1] = {(cuuint64_t)rows * 16};
+    const cuuint32_t box[2] = {(cuuint32_t)twm::tcw::MB * 2, (cuuint32_t)twm::tcw::A_KCORES};
+    const cuuint32_t estride[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(xp), gdim, gstride, box, estride,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 bool shape_ok(int M, int N, int K, int G)
 {
     return M >= 1 && N >= 1 && K >= 32 && (G == 32 || G == 128) && (K % G) == 0 && (K % 32) == 0 &&
@@ -222,10 +240,15 @@ int mmax_for(int M) { return M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : 8)); }
 // Measured on the 7B gate+up shape (us per launch in a dependent chain): the streaming MMA kernel
 // 15.7 / 16.2 / 20.3 / 30.7 at M = 1 / 2 / 4 / 8, the tcgen05 kernel 26-27 for any M up to 16.
 constexpr int kTcFromRows = 5;
+// Measured on the 7B gate+up shape: 64 rows 51.6 us on the weight-stationary kernel against 58.0 on the wide one,
+// 96 rows 76 against 59, 128 rows 79 (as two launches of 64; one launch with a 128-row accumulator was no faster) against 60.
+constexpr int kTcwFromRows = 65;
 int auto_kernel(int M, int N, int K, int G, bool a_is_f16, bool indirect, int splits_override)
 {
     if (!a_is_f16) return TWM_KERNEL_SIMT;
-    (void)N; (void)K; (void)G; (void)indirect; (void)splits_override;
+    (void)K; (void)splits_override;
+    // many rows: the wide tcgen05 kernel (rows on the MMA's M dimension); it wants group 128 and full 128-column tiles
+    if (M >= kTcwFromRows && G == 128 && N >= 128 && !indirect) return TWM_KERNEL_TCW;
     return M >= kTcFromRows ? TWM_KERNEL_TC : TWM_KERNEL_MMA;
 }
 
@@ -247,6 +270,25 @@ int resolve_kernel(const twm_gemm_args* a)
 }
 
 constexpr int kTcRows = 64;      // activation rows one tcgen05 launch carries
+constexpr int kTcwRows = twm::tcw::MB;   // ... and one wide tcgen05 launch
+
+twm_status launch_tcw(const twm::GemmParams& p, dim3 grid, bool pdl, cudaStream_t stream)
+{
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(twm::tcw::THREADS, 1, 1);
+    cfg.dynamicSmemBytes = sizeof(twm::tcw::Smem);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, twm::tcw::gemm_kernel, p);
+    if (e != cudaSuccess) { set_error("launch tcw::gemm_kernel", e); return TWM_ELAUNCH; }
+    return TWM_OK;
+}
 
 twm_status launch_tc(const twm::GemmParams& p, int rows, dim3 grid, bool pdl, cudaStream_t stream)
 {
@@ -396,6 +438,17 @@ twm_status launch_op(const char* name, void (*kernel)(KArgs...), dim3 grid, dim3
     if (e != cudaSuccess) { set_error(name, e); return TWM_ELAUNCH; }
     return TWM_OK;
 }
+
+// The pre-pass of the tcgen05 kernels: the launch's rows in [K/8][rows][8] order and the -8 * sum table.
+twm_status launch_prepass(__half* xp, float* a8, const __half* a, long lda, int rows, int K, int group, int nb_pad,
+                          unsigned flags, void* stream)
+{
+    const int items = rows * (K / 8);
+    const int perm_blocks = (items + 255) / 256;
+    const int sum_blocks = ((K / group) * nb_pad * (group / 8) + 255) / 256;
+    return launch_op("permute_activations_kernel", twm::tc::permute_activations_kernel, dim3(perm_blocks + sum_blocks), dim3(256), 0,
+                     flags & TWM_FLAG_PDL, stream, xp, a8, a, lda, rows, K / 8, perm_blocks, group, nb_pad);
+}
 }  // namespace
 
 extern "C" {
@@ -409,13 +462,15 @@ twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int split
     const int nkb = K / 32;
     int kernel = kernel_override;
     if (kernel == TWM_KERNEL_AUTO) kernel = auto_kernel(M, N, K, group_size, true, false, splits_override);
-    if (kernel != TWM_KERNEL_SIMT && kernel != TWM_KERNEL_TC && kernel != TWM_KERNEL_MMA) return TWM_EINVAL;
+    if (kernel != TWM_KERNEL_SIMT && kernel != TWM_KERNEL_TC && kernel != TWM_KERNEL_MMA && kernel != TWM_KERNEL_TCW) return TWM_EINVAL;
+    if (kernel == TWM_KERNEL_TCW && (group_size != 128 || N < 128)) return TWM_EINVAL;
     // rows one launch carries; more rows are served by further launches
-    const int rows = std::min(M, kernel == TWM_KERNEL_TC ? kTcRows : 8);
+    const int rows = std::min(M, kernel == TWM_KERNEL_TC ? kTcRows : (kernel == TWM_KERNEL_TCW ? kTcwRows : 8));
     const int n_tiles = (N + twm::simt::NT - 1) / twm::simt::NT;
-    const int slots = sm_count * ((kernel != TWM_KERNEL_SIMT || mmax_for(rows) <= 4) ? 2 : 1);
+    const int slots = kernel == TWM_KERNEL_TCW ? sm_count
+                                               : sm_count * ((kernel != TWM_KERNEL_SIMT || mmax_for(rows) <= 4) ? 2 : 1);
     const int max_bps = nkb;
-    const int align = (kernel == TWM_KERNEL_MMA || kernel == TWM_KERNEL_TC) ? group_size / 32 : 1;   // whole scale groups per slice
+    const int align = (kernel == TWM_KERNEL_MMA || kernel == TWM_KERNEL_TC || kernel == TWM_KERNEL_TCW) ? group_size / 32 : 1;   // whole scale groups per slice
     // up to two rows on the streaming MMA kernel: K slices add up inside a cluster (at most 16 slices)
     const bool can_cluster = (kernel == TWM_KERNEL_MMA) && rows <= twm::mma::CLUSTER_ROWS;
     int splits, bps;
@@ -439,8 +494,10 @@ twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int split
     out->workspace_bytes = (splits > 1 && !cluster) ? kCounterBytes + (size_t)splits * rows * N * sizeof(float) : 0;
     if (kernel == TWM_KERNEL_TC)    // + the launch's activations in the MMA's K order and their per-group sums, behind the split-K part
         out->workspace_bytes = kCounterBytes + (splits > 1 ? (size_t)splits * rows * N * sizeof(float) : 0) +
-                               256 + (size_t)rows * K * 2 + 256 + (size_t)(K / group_size) * kTcRows * sizeof(float) +
-                               256 + (size_t)kTcRows * sizeof(float);
+                               256 + (size_t)rows * K * 2 + 256 + (size_t)(K / group_size) * kTcRows * sizeof(float);
+    if (kernel == TWM_KERNEL_TCW)   // the same two pre-pass outputs, sized for 128 rows per launch
+        out->workspace_bytes = kCounterBytes + (splits > 1 ? (size_t)splits * rows * N * sizeof(float) : 0) +
+                               256 + (size_t)rows * K * 2 + 256 + (size_t)(K / group_size) * kTcwRows * sizeof(float);
     out->cluster_reduce = cluster ? 1 : 0;
     return TWM_OK;
 }
@@ -451,6 +508,7 @@ size_t twm_workspace_bytes(int M, int N, int K, int group_size)
     twm_plan_t tc, simt;
     size_t need = 0;
     if (twm_plan(M, N, K, group_size, kDefaultSms, 0, TWM_KERNEL_TC, &tc) == TWM_OK) need = tc.workspace_bytes;
+    if (twm_plan(M, N, K, group_size, kDefaultSms, 0, TWM_KERNEL_TCW, &tc) == TWM_OK) need = std::max(need, tc.workspace_bytes);
     if (twm_plan(M, N, K, group_size, kDefaultSms, 0, TWM_KERNEL_SIMT, &simt) == TWM_OK)
         need = std::max(need, simt.workspace_bytes);
     if (twm_plan(M, N, K, group_size, kDefaultSms, 0, TWM_KERNEL_MMA, &simt) == TWM_OK)
@@ -508,11 +566,12 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
     cudaStream_t stream = (cudaStream_t)stream_;
     const size_t a_elt = a->a_dtype == TWM_F16 ? 2 : 4;
     const size_t c_elt = a->c_dtype == TWM_F16 ? 2 : 4;
-    const int row_step = kernel == TWM_KERNEL_TC ? kTcRows : 8;
+    if (kernel == TWM_KERNEL_TCW && (a->packed_offsets != nullptr || a->comm)) return TWM_EINVAL;
+    const int row_step = kernel == TWM_KERNEL_TC ? kTcRows : (kernel == TWM_KERNEL_TCW ? kTcwRows : 8);
     CUtensorMap packed_map;
     int map_rows = 0;
     if (a->packed_offsets == nullptr && a->N >= 128 && kernel != TWM_KERNEL_SIMT) {
-        const int want = kernel == TWM_KERNEL_MMA ? twm::mma::SB : twm::tc::WSTAGE_BLOCKS;
+        const int want = kernel == TWM_KERNEL_MMA ? twm::mma::SB : twm::tc::WSTAGE_BLOCKS;      // (the wide kernel's stage is four blocks too)
         if (make_packed_map(&packed_map, a->packed, a->N, a->K / 32, want)) map_rows = want;
     }
     for (int m0 = 0; m0 < a->M; m0 += row_step) {
@@ -541,7 +600,24 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
         p.map_rows = map_rows;
         if (map_rows) p.packed_map = packed_map;
         const bool pdl = (a->flags & TWM_FLAG_PDL) != 0;
-        if (kernel == TWM_KERNEL_TC) {
+        if (kernel == TWM_KERNEL_TCW) {
+            if (!map_rows) {
+                snprintf(t_last_error, sizeof(t_last_error), "cuTensorMapEncodeTiled failed for the packed map of the wide tcgen05 kernel");
+                return TWM_ELAUNCH;
+            }
+            const size_t part_bytes = pl.splits > 1 ? (size_t)pl.splits * std::min(a->M, kTcwRows) * a->N * sizeof(float) : 0;
+            char* xp = (char*)a->workspace + kCounterBytes + ((part_bytes + 255) / 256) * 256;
+            if (!make_act_map_wide(&p.act_map, xp, rows, a->K)) {
+                snprintf(t_last_error, sizeof(t_last_error), "cuTensorMapEncodeTiled failed for the activation map");
+                return TWM_ELAUNCH;
+            }
+            char* a8 = xp + (((size_t)rows * a->K * 2 + 255) / 256) * 256;
+            p.tc_a8 = (const float*)a8;
+            st = launch_prepass((__half*)xp, (float*)a8, (const __half*)p.a, p.lda, rows, a->K, a->group_size, kTcwRows, a->flags, stream_);
+            if (st != TWM_OK) return st;
+            st = launch_tcw(p, dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
+        }
+        else if (kernel == TWM_KERNEL_TC) {
             // pre-pass: this launch's rows in [K/8][rows][8] order, then the GEMM loads them by TMA
             const size_t part_bytes = pl.splits > 1 ? (size_t)pl.splits * std::min(a->M, kTcRows) * a->N * sizeof(float) : 0;
             char* xp = (char*)a->workspace + kCounterBytes + ((part_bytes + 255) / 256) * 256;
@@ -551,12 +627,8 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
                 return TWM_ELAUNCH;
             }
             char* a8 = xp + (((size_t)rows * a->K * 2 + 255) / 256) * 256;
-            char* rs = a8 + (((size_t)(a->K / a->group_size) * kTcRows * sizeof(float) + 255) / 256) * 256;
             p.tc_a8 = (const float*)a8;
-            p.tc_rowscale = (const float*)rs;
-            st = launch_op("permute_activations_kernel", twm::tc::permute_activations_kernel, dim3(nb_rows),
-                           dim3(256), 0, a->flags & TWM_FLAG_PDL, stream_, (__half*)xp, (float*)a8, (float*)rs,
-                           (const __half*)p.a, p.lda, rows, a->K / 8, a->group_size, nb_rows);
+            st = launch_prepass((__half*)xp, (float*)a8, (const __half*)p.a, p.lda, rows, a->K, a->group_size, nb_rows, a->flags, stream_);
             if (st != TWM_OK) return st;
             st = launch_tc(p, rows, dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
         }
@@ -1289,14 +1361,6 @@ const char* twm_status_string(twm_status s)
     }
     return "unknown status";
 }
-
-#ifdef TWM_CHAIN_TL
-int twm_chain_timeline_read(unsigned long long* out, int n)
-{
-    cudaDeviceSynchronize();
-    return cudaMemcpyFromSymbol(out, twm::chain::g_chain_tl, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 const char* twm_last_error(void) { return t_last_error; }
 

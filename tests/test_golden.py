@@ -63,3 +63,35 @@ def test_decode_order_equals_reference_f16_dequant_and_tile_gemm():
     assert np.array_equal(oracle.f32_to_f16_bits(dense), GOLD["tile_dequant_f16_bits"])
     c = oracle.gemm_f32(a, dense, a.shape[0], n, k)
     assert np.max(np.abs(c - GOLD["tile_c"])) < 1e-4 * float(np.sqrt(np.mean(c.astype(np.float64) ** 2)))
+
+
+def test_reorder_restatement_on_the_reference_quantisers_blocks():
+    """reorder_to_tw_marlin (quantize.rs:912-956) restated: on column-major Q4_0 blocks written by the
+    reference's own quantise kernel it gives the oracle quantiser's packed bytes and the FP16 rounding
+    of the blocks' FP32 scales; and back again."""
+    w = GOLD["tile_w"]
+    k, n = w.shape
+    packed, scales = oracle.reorder_to_tw_marlin(GOLD["tile_blocks"], k, n)
+    p_ref, s_ref = oracle.quantize_pack(w, k, n, 32)
+    assert np.array_equal(packed, p_ref) and np.array_equal(scales, s_ref)
+    blocks = GOLD["tile_blocks"].reshape(n, k // 32, 20)
+    scale32 = blocks[:, :, :4].copy().view(np.float32).reshape(n, k // 32).T
+    assert np.array_equal(oracle.f32_to_f16_bits(scale32), scales)
+    again = oracle.reorder_to_tw_marlin(oracle.tw_marlin_to_q4_0_blocks(packed, scales, k, n), k, n)
+    assert np.array_equal(again[0], packed) and np.array_equal(again[1], scales)
+
+
+def test_moe_restatement_equals_reference_batched_kernels():
+    """batched_marlin_gate_up / split_geglu / down_axpy (moe_batched_marlin.rs:21-152): the gate+up kernel
+    bit for bit, GEGLU to the last place of tanhf, the atomicAdd-ed weighted sum to FP32 summation order."""
+    hidden, moe_dim, n_experts, top_k, gu_pb, gu_sb, dn_pb, dn_sb = (int(v) for v in GOLD["moe_dims"])
+    x, ids, wts = GOLD["moe_x"], GOLD["moe_ids"], GOLD["moe_wts"]
+    gu = oracle.moe_gate_up(x, GOLD["moe_gu_packed"], GOLD["moe_gu_scales"], ids, gu_pb, gu_sb, hidden, 2 * moe_dim, 32)
+    assert np.array_equal(gu.view(np.uint32), GOLD["moe_gate_up"].view(np.uint32))
+    act = oracle.moe_split_geglu(gu, moe_dim)
+    assert np.max(np.abs(act - GOLD["moe_act"])) <= 1e-6 * max(1.0, float(np.abs(act).max()))
+    acc, acc64 = oracle.moe_down_axpy(GOLD["moe_act"], GOLD["moe_dn_packed"], GOLD["moe_dn_scales"], ids, wts, dn_pb, dn_sb,
+                                      moe_dim, hidden, 32)
+    rms = float(np.sqrt(np.mean(acc64 ** 2)))
+    assert np.max(np.abs(GOLD["moe_acc"] - acc64)) < 1e-5 * rms
+    assert np.max(np.abs(acc - acc64)) < 1e-5 * rms
