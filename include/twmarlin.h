@@ -92,6 +92,16 @@ typedef struct twm_comm {
  * and gemm_tw_marlin_m1_indirect (quantize_indirect.rs:228-253; fill the
  * *_offsets fields), and is the M > 1 TW-Marlin GEMM the reference lacks
  * (its stand-in is gemm_q4_0, quantize.rs:1825-1858). */
+/* What the activation rows of a GEMM hold (twm_gemm_args.a_prologue, twm_moe_args.a_prologue). */
+enum {
+    TWM_A_PLAIN = 0,     /* a is f16 (or f32) [M][lda] */
+    TWM_A_SILU_MUL = 1,  /* a is f16 [M][lda] holding [gate | up] (up at column K): the GEMM reads
+                            silu(gate) * up, rounded to f16 as twm_silu_mul would have stored it
+                            (fused_silu_mul, crates/kernels/src/ops.rs:966-977) */
+    TWM_A_GEGLU = 2      /* the same with tanh-gelu(gate) * up (batched_marlin_split_geglu,
+                            crates/kernels/src/moe_batched_marlin.rs:138-152); not in GEMM chains */
+};
+
 typedef struct twm_gemm_args {
     int M, N, K;
     int group_size;          /* 32 or 128; K % group_size == 0 */
@@ -124,6 +134,12 @@ typedef struct twm_gemm_args {
      * taken by twm_allreduce_add_rmsnorm on each rank.  M <= 2 (the plan must be one K slice per tile or
      * a cluster reduce), FP16 activations, streaming MMA kernel. */
     const twm_comm* comm;
+    /* What the activation rows hold: TWM_A_PLAIN (0) the activations; TWM_A_SILU_MUL / TWM_A_GEGLU: the
+     * fused [gate | up] output of the preceding GEMM (2K f16 per row, up at column K, lda >= 2K), and the
+     * GEMM multiplies act(gate) * up, computed in FP32 and rounded to f16 exactly as twm_silu_mul would
+     * have stored it, so the separate pass and its buffer go away.  M == 1, FP16 activations, streaming
+     * MMA kernel only (TWM_EINVAL otherwise). */
+    int a_prologue;
 } twm_gemm_args;
 
 /* What the heuristic decided for a shape; pure host arithmetic. */
@@ -187,21 +203,12 @@ twm_status twm_ipc_close(void* ptr);
  * twm_chain_create is a set-up call: it allocates the chain's device memory (GEMM table, split
  * partials, counters; twm_chain_info reports the size) and synchronises.  twm_chain_launch only
  * enqueues and is legal during stream capture.  One chain runs on one stream at a time. */
-enum {
-    TWM_A_PLAIN = 0,     /* a is f16 [M][lda] */
-    TWM_A_SILU_MUL = 1,  /* a is f16 [M][lda] holding [gate | up] (up at column K): the GEMM reads
-                            silu(gate) * up, rounded to f16 as twm_silu_mul would have stored it
-                            (fused_silu_mul, crates/kernels/src/ops.rs:966-977) */
-    TWM_A_GEGLU = 2      /* the same with tanh-gelu(gate) * up (batched_marlin_split_geglu,
-                            crates/kernels/src/moe_batched_marlin.rs:138-152); expert GEMVs only */
-};
-
 typedef struct twm_chain_op {
-    twm_gemm_args gemm;  /* workspace, *_override, *_offsets and comm must be zero; flags: TWM_FLAG_ACCUMULATE,
-                            and TWM_FLAG_INDEPENDENT = this GEMM reads nothing an earlier GEMM of the chain
+    twm_gemm_args gemm;  /* workspace, *_override, *_offsets and comm must be zero; a_prologue TWM_A_PLAIN or
+                            TWM_A_SILU_MUL (here with M up to 8); flags: TWM_FLAG_ACCUMULATE, and
+                            TWM_FLAG_INDEPENDENT = this GEMM reads nothing an earlier GEMM of the chain
                             writes (it does not wait; a later dependent GEMM still waits for it and for
                             everything before it) */
-    int a_prologue;      /* TWM_A_* */
 } twm_chain_op;
 
 typedef struct twm_chain twm_chain;      /* opaque */

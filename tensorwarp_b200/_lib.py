@@ -31,6 +31,7 @@ class GemmArgs(C.Structure):
         ("splits_override", C.c_int), ("kernel_override", C.c_int), ("flags", C.c_int),
         ("packed_offsets", C.c_void_p), ("scales_offsets", C.c_void_p), ("expert_idx", C.c_int),
         ("comm", C.c_void_p),
+        ("a_prologue", C.c_int),
     ]
 
 
@@ -54,7 +55,7 @@ class MoeArgs(C.Structure):
 
 class ChainOp(C.Structure):
     """``twm_chain_op``."""
-    _fields_ = [("gemm", GemmArgs), ("a_prologue", C.c_int)]
+    _fields_ = [("gemm", GemmArgs)]
 
 
 class ChainInfo(C.Structure):

@@ -524,6 +524,8 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
     if ((a->a_dtype != TWM_F32 && a->a_dtype != TWM_F16) || (a->c_dtype != TWM_F32 && a->c_dtype != TWM_F16))
         return TWM_EINVAL;
     if (a->lda < a->K || a->ldc < a->N) return TWM_EINVAL;
+    if (a->a_prologue < TWM_A_PLAIN || a->a_prologue > TWM_A_GEGLU) return TWM_EINVAL;
+    if (a->a_prologue != TWM_A_PLAIN && (a->M != 1 || a->a_dtype != TWM_F16 || a->lda < 2L * a->K)) return TWM_EINVAL;
     if ((a->packed_offsets == nullptr) != (a->scales_offsets == nullptr)) return TWM_EINVAL;
     if (a->packed_offsets && a->expert_idx < 0) return TWM_EINVAL;
     if (reinterpret_cast<uintptr_t>(a->packed) & 15) return TWM_EALIGN;
@@ -539,6 +541,7 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
     // reference's own signature) run on the FP32 streaming kernel.
     const int kernel = resolve_kernel(a);
     if (kernel != TWM_KERNEL_SIMT && a->a_dtype != TWM_F16) return TWM_EINVAL;
+    if (a->a_prologue != TWM_A_PLAIN && kernel != TWM_KERNEL_MMA) return TWM_EINVAL;
     twm_plan_t pl;
     st = twm_plan(a->M, a->N, a->K, a->group_size, sm_count, a->splits_override, kernel, &pl);
     if (st != TWM_OK) return st;
@@ -592,6 +595,7 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
         p.no_wait = ((a->flags & TWM_FLAG_INDEPENDENT) && (a->flags & TWM_FLAG_PDL) && kernel == TWM_KERNEL_MMA &&
                      pl.workspace_bytes == 0 && !p.accumulate && a->packed_offsets == nullptr && !a->comm) ? 1 : 0;
         p.packed_offsets = a->packed_offsets; p.scales_offsets = a->scales_offsets; p.expert_idx = a->expert_idx;
+        p.a_kind = a->a_prologue;
         if (a->comm) {
             p.n_peers = a->comm->n_ranks; p.peer_rank = a->comm->rank; p.peer_slot_elems = a->comm->slot_elems;
             for (int r = 0; r < a->comm->n_ranks; ++r) { p.peer_data[r] = a->comm->data[r]; p.peer_flags[r] = a->comm->flags[r]; }
@@ -843,8 +847,8 @@ twm_status twm_chain_create(const twm_chain_op* ops, int count, twm_chain** out)
         if (!shape_ok(a.M, a.N, a.K, a.group_size) || a.M > 8) return TWM_EINVAL;
         if (!a.a || !a.packed || !a.scales || !a.c) return TWM_EINVAL;
         if (a.a_dtype != TWM_F16 || (a.c_dtype != TWM_F32 && a.c_dtype != TWM_F16)) return TWM_EINVAL;
-        if (ops[i].a_prologue != TWM_A_PLAIN && ops[i].a_prologue != TWM_A_SILU_MUL) return TWM_EINVAL;
-        if (a.lda < (ops[i].a_prologue == TWM_A_SILU_MUL ? 2L * a.K : (long)a.K) || a.ldc < a.N) return TWM_EINVAL;
+        if (a.a_prologue != TWM_A_PLAIN && a.a_prologue != TWM_A_SILU_MUL) return TWM_EINVAL;
+        if (a.lda < (a.a_prologue == TWM_A_SILU_MUL ? 2L * a.K : (long)a.K) || a.ldc < a.N) return TWM_EINVAL;
         if (a.packed_offsets || a.scales_offsets || a.comm || a.splits_override || a.kernel_override) return TWM_EINVAL;
         if (reinterpret_cast<uintptr_t>(a.packed) & 15) return TWM_EALIGN;
         if ((reinterpret_cast<uintptr_t>(a.scales) & 1) || (reinterpret_cast<uintptr_t>(a.a) & 1)) return TWM_EALIGN;
@@ -887,7 +891,7 @@ twm_status twm_chain_create(const twm_chain_op* ops, int count, twm_chain** out)
         op.total_units = (int)total;
         op.ranks = (int)std::min<long long>(ch->grid, total);
         op.rot = (int)(((long long)i * 97) % ch->grid);
-        op.a_kind = ops[i].a_prologue == TWM_A_SILU_MUL ? twm::chain::A_SILU_MUL : twm::chain::A_F16;
+        op.a_kind = a.a_prologue == TWM_A_SILU_MUL ? twm::chain::A_SILU_MUL : twm::chain::A_F16;
         op.c_is_f16 = a.c_dtype == TWM_F16;
         op.accumulate = (a.flags & TWM_FLAG_ACCUMULATE) ? 1 : 0;
         if (a.flags & TWM_FLAG_INDEPENDENT) {

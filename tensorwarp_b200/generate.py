@@ -120,7 +120,6 @@ class Q4DecodeBuffers:
         self.q = torch.zeros(cfg.q_dim, dtype=f16, device=dev)
         self.attn = torch.zeros(cfg.q_dim, dtype=f16, device=dev)
         self.gate_up = torch.zeros(2 * cfg.ffn, dtype=f16, device=dev)
-        self.act = torch.zeros(cfg.ffn, dtype=f16, device=dev)
         self.logits = torch.zeros(cfg.vocab, dtype=f32, device=dev)
         self.token = torch.zeros(1, dtype=i32, device=dev)
         self.pos = torch.zeros(1, dtype=i32, device=dev)                          # pos_buf (generate.rs:1413)
@@ -184,13 +183,14 @@ class QuantizedGenerationEngine:
         lib, cfg, b, fl = _lib.lib(), self.cfg, self.buf, self.flags
         ops = []
 
-        def gemm(a, w, c, n_out, k_in, accumulate=False):
+        def gemm(a, w, c, n_out, k_in, accumulate=False, silu_mul=False):
             args = _lib.GemmArgs(M=1, N=n_out, K=k_in, group_size=cfg.group_size, a_dtype=_lib.TWM_F16,
                                  c_dtype=_lib.TWM_F32 if c.dtype == torch.float32 else _lib.TWM_F16,
-                                 a=a.data_ptr(), lda=k_in, packed=w[0].data_ptr(), scales=w[1].data_ptr(),
-                                 c=c.data_ptr(), ldc=n_out, workspace=b.workspace.ptr,
+                                 a=a.data_ptr(), lda=2 * k_in if silu_mul else k_in, packed=w[0].data_ptr(),
+                                 scales=w[1].data_ptr(), c=c.data_ptr(), ldc=n_out, workspace=b.workspace.ptr,
                                  workspace_bytes=b.workspace.nbytes,
-                                 flags=fl | (_lib.TWM_FLAG_ACCUMULATE if accumulate else 0))
+                                 flags=fl | (_lib.TWM_FLAG_ACCUMULATE if accumulate else 0),
+                                 a_prologue=_lib.TWM_A_SILU_MUL if silu_mul else _lib.TWM_A_PLAIN)
             return lambda: check(lib.twm_gemm_w4a16(C.byref(args), stream_ptr), "twm_gemm_w4a16")
 
         ops.append(("embedding", 1, lambda: check(lib.twm_embed(b.x.data_ptr(), self.model.embed.data_ptr(), b.token.data_ptr(),
@@ -211,9 +211,9 @@ class QuantizedGenerationEngine:
             ops.append(("ffn_rmsnorm", 1, lambda lw=lw: check(lib.twm_rmsnorm(
                 b.normed.data_ptr(), b.x.data_ptr(), lw.ffn_norm.data_ptr(), 1, cfg.hidden, cfg.eps, fl, stream_ptr), "twm_rmsnorm")))
             ops.append(("gate_up_gemm", 1, gemm(b.normed, lw.wgu, b.gate_up, 2 * cfg.ffn, cfg.hidden)))
-            ops.append(("silu_mul", 1, lambda: check(lib.twm_silu_mul(b.act.data_ptr(), b.gate_up.data_ptr(), 1, cfg.ffn, fl,
-                                                                       stream_ptr), "twm_silu_mul")))
-            ops.append(("down_gemm", 1, gemm(b.act, lw.w_down, b.x, cfg.hidden, cfg.ffn, accumulate=True)))         # x += down(act)
+            # x += down(silu(gate) * up): the gated activation (fused_silu_mul, ops.rs:966-977) is taken on the fly by
+            # the down GEMM's activation reader, bit for bit what the separate pass stored
+            ops.append(("down_gemm", 1, gemm(b.gate_up, lw.w_down, b.x, cfg.hidden, cfg.ffn, accumulate=True, silu_mul=True)))
         ops.append(("final_rmsnorm", 1, lambda: check(lib.twm_rmsnorm(b.normed.data_ptr(), b.x.data_ptr(),
                                                                       self.model.final_norm.data_ptr(), 1, cfg.hidden, cfg.eps,
                                                                       fl, stream_ptr), "twm_rmsnorm")))
@@ -266,7 +266,7 @@ class QuantizedGenerationEngine:
         per_step = {k: v / steps for k, v in acc.items()}
         total = sum(per_step.values())
         layered = {"attn_rmsnorm", "qkv_gemm", "rope_kv_append", "attention", "out_gemm", "ffn_rmsnorm", "gate_up_gemm",
-                   "silu_mul", "down_gemm"}
+                   "down_gemm"}
         nl = max(len(self.model.layers), 1)
         table = {k: {"us": round(v, 1), "us_per_layer": round(v / nl, 2) if k in layered else None,
                      "pct": round(100.0 * v / total, 1)} for k, v in per_step.items()}

@@ -78,21 +78,25 @@ def gemm_tw_marlin(a: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, 
                    workspace: Optional[Workspace] = None, stream: Optional[torch.cuda.Stream] = None,
                    flags: int = 0, splits_override: int = 0, kernel_override: int = 0,
                    packed_offsets: Optional[torch.Tensor] = None,
-                   scales_offsets: Optional[torch.Tensor] = None, expert_idx: int = 0) -> None:
+                   scales_offsets: Optional[torch.Tensor] = None, expert_idx: int = 0,
+                   a_prologue: int = _lib.TWM_A_PLAIN) -> None:
     """C[m,n] = A[m,k] x dequant(packed, scales); A and C are f32 or f16, row-major.
 
-    The M > 1 form of ``gemm_tw_marlin_m1``; enqueue only, like the reference."""
+    The M > 1 form of ``gemm_tw_marlin_m1``; enqueue only, like the reference.  With
+    ``a_prologue=TWM_A_SILU_MUL`` (m = 1, f16) ``a`` is the [gate | up] output of the preceding GEMM
+    (2k values) and the GEMM reads silu(gate) * up: fused_silu_mul (ops.rs:966-977) without its pass."""
     _require_cuda(a, packed, scales, c)
     if a.dtype not in _DTYPES or c.dtype not in _DTYPES:
         raise TwmError(_lib.TWM_EINVAL, "gemm_tw_marlin: A and C must be float32 or float16")
     if packed.dtype != torch.uint8 or scales.dtype not in (torch.float16, torch.uint16, torch.int16):
         raise TwmError(_lib.TWM_EINVAL, "gemm_tw_marlin: packed must be uint8 and scales float16")
-    if a.numel() < m * k or c.numel() < m * n:
+    a_cols = k if a_prologue == _lib.TWM_A_PLAIN else 2 * k
+    if a.numel() < m * a_cols or c.numel() < m * n:
         raise TwmError(_lib.TWM_EINVAL, "gemm_tw_marlin: A or C smaller than the stated shape")
     if packed_offsets is None:
         if packed.numel() < (k // 32) * n * 16 or scales.numel() < (k // group_size) * n:
             raise TwmError(_lib.TWM_EINVAL, "gemm_tw_marlin: packed or scales smaller than the stated shape")
-    lda = a.stride(0) if a.dim() == 2 else k
+    lda = a.stride(0) if a.dim() == 2 else a_cols
     ldc = c.stride(0) if c.dim() == 2 else n
     args = GemmArgs(
         M=m, N=n, K=k, group_size=group_size,
@@ -104,7 +108,7 @@ def gemm_tw_marlin(a: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, 
         splits_override=splits_override, kernel_override=kernel_override, flags=flags,
         packed_offsets=packed_offsets.data_ptr() if packed_offsets is not None else None,
         scales_offsets=scales_offsets.data_ptr() if scales_offsets is not None else None,
-        expert_idx=expert_idx,
+        expert_idx=expert_idx, a_prologue=a_prologue,
     )
     check(_lib.lib().twm_gemm_w4a16(C.byref(args), _stream_ptr(stream)), "twm_gemm_w4a16")
 
@@ -314,7 +318,7 @@ class GemmChain:
         op.gemm = GemmArgs(M=m, N=n, K=k, group_size=group_size, a_dtype=_lib.TWM_F16, c_dtype=_DTYPES[c.dtype],
                            a=a.data_ptr(), lda=lda, packed=packed.data_ptr(), scales=scales.data_ptr(),
                            c=c.data_ptr(), ldc=ldc, flags=flags)
-        op.a_prologue = _lib.TWM_A_SILU_MUL if silu_mul else _lib.TWM_A_PLAIN
+        op.gemm.a_prologue = _lib.TWM_A_SILU_MUL if silu_mul else _lib.TWM_A_PLAIN
         self._ops.append(op)
         self._keep.append((a, packed, scales, c))
         return self

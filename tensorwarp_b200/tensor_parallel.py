@@ -240,13 +240,14 @@ class TPDecodeStack:
         self.pos.fill_(length)
         self.cache_len.fill_(length + 1)
 
-    def _gemm(self, a, w, c, n_out, k_in, stream_ptr, push=False):
+    def _gemm(self, a, w, c, n_out, k_in, stream_ptr, push=False, silu_mul=False):
         args = _lib.GemmArgs(M=self.rows, N=n_out, K=k_in, group_size=self.cfg.group_size, a_dtype=_lib.TWM_F16,
                              c_dtype=_lib.TWM_F32 if c.dtype == torch.float32 else _lib.TWM_F16,
-                             a=a.data_ptr(), lda=k_in, packed=w[0].data_ptr(), scales=w[1].data_ptr(),
-                             c=c.data_ptr(), ldc=n_out, workspace=self.workspace.ptr,
+                             a=a.data_ptr(), lda=2 * k_in if silu_mul else k_in, packed=w[0].data_ptr(),
+                             scales=w[1].data_ptr(), c=c.data_ptr(), ldc=n_out, workspace=self.workspace.ptr,
                              workspace_bytes=self.workspace.nbytes, flags=self.flags,
-                             comm=self.comm.ptr if (push and self.comm is not None) else None)
+                             comm=self.comm.ptr if (push and self.comm is not None) else None,
+                             a_prologue=_lib.TWM_A_SILU_MUL if silu_mul else _lib.TWM_A_PLAIN)
         check(_lib.lib().twm_gemm_w4a16(C.byref(args), stream_ptr), "twm_gemm_w4a16")
         self.launches += 1
 
@@ -287,6 +288,10 @@ class TPDecodeStack:
         lib, cfg, fl, m, lw = _lib.lib(), self.cfg, self.flags, self.rows, self.layers[li]
         self._join_and_norm(self.normed.data_ptr(), lw.ffn_norm.data_ptr(), stream_ptr)
         self._gemm(self.normed, lw.wgu, self.gate_up, self.spec.n_gu, cfg.hidden, stream_ptr)            # column-parallel
+        if m == 1:      # one row: the down GEMM's activation reader takes silu(gate) * up on the fly (the same bits)
+            self.launches += 1
+            self._gemm(self.gate_up, lw.w_down, self.part, cfg.hidden, self.spec.n_gu // 2, stream_ptr, push=True, silu_mul=True)
+            return
         check(lib.twm_silu_mul(self.act.data_ptr(), self.gate_up.data_ptr(), m, self.spec.n_gu // 2, fl, stream_ptr),
               "twm_silu_mul")
         self.launches += 2

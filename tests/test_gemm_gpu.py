@@ -224,6 +224,51 @@ def test_wide_tensor_core_kernel(m, k, n, splits):
     assert q.plan(m, n, k, group).kernel == (kern if m >= 65 else _lib.TWM_KERNEL_TC)       # the heuristic's choice
 
 
+@pytest.mark.parametrize("kind", ["silu", "geglu"])
+@pytest.mark.parametrize("group", [32, 128])
+@pytest.mark.parametrize("k,n,splits", [(2816, 1024, 0), (18944, 3584, 0), (512, 300, 1), (1024, 128, 3)])
+def test_gated_activation_prologue(k, n, splits, group, kind):
+    """twm_gemm_args.a_prologue: the GEMM reads act(gate) * up from the preceding GEMM's [gate | up] row.
+    Bit for bit the result of the separate pass (fused_silu_mul, ops.rs:966-977; split_geglu,
+    moe_batched_marlin.rs:138-152, restated in the oracle) followed by the plain GEMM."""
+    _, packed, scales = _quantised(k, n, group, 57)
+    gu = (seeded_activations(1, 2 * k, 6) * 1.5).astype(np.float16).astype(np.float32)
+    if kind == "silu":
+        g, u = gu[:, :k].astype(np.float32), gu[:, k:].astype(np.float32)
+        act_dev = torch.zeros((1, k), dtype=torch.float16, device=DEV)
+        _lib.check(_lib.lib().twm_silu_mul(act_dev.data_ptr(), _to_dev(gu, torch.float16).data_ptr(), 1, k, 0,
+                                           torch.cuda.current_stream().cuda_stream), "twm_silu_mul")
+        act = act_dev.float().cpu().numpy()
+        ref_act = (g / (1.0 + np.exp(-g)) * u).astype(np.float16).astype(np.float32)
+        assert np.max(np.abs(act - ref_act)) <= 2.0 ** -9 * max(1.0, float(np.abs(ref_act).max()))       # expf's last place
+        prologue = _lib.TWM_A_SILU_MUL
+    else:
+        act = oracle.moe_split_geglu(gu.reshape(1, 2 * k), k).astype(np.float16).astype(np.float32)
+        prologue = _lib.TWM_A_GEGLU
+    plain = _run_gemm(act, packed, scales, 1, n, k, group, torch.float16, torch.float32, splits_override=splits)
+    fused = _run_gemm(gu, packed, scales, 1, n, k, group, torch.float16, torch.float32, splits_override=splits,
+                      a_prologue=prologue, flags=_lib.TWM_FLAG_PDL)
+    if kind == "silu":
+        assert np.array_equal(fused, plain)
+    else:       # tanhf on the device against the oracle's: one f16 place of the activation at most
+        ref = oracle.w4a16_f64(act, packed, scales, 1, n, k, group)
+        assert _abs_err_over_rms(fused, ref) < 2e-3
+    ref = oracle.w4a16_f64(act, packed, scales, 1, n, k, group)
+    assert rel_err_floored(plain, ref) < TOL_F16 and _abs_err_over_rms(plain, ref) < TC_ABS_F32
+
+
+def test_gated_activation_prologue_refusals():
+    k, n = 256, 256
+    _, packed, scales = _quantised(k, n, 32, 58)
+    gu2 = seeded_activations(2, 2 * k)
+    for kw in (dict(m=2, a=gu2, dt=torch.float16), dict(m=1, a=gu2[:1], dt=torch.float32),
+               dict(m=1, a=gu2[:1], dt=torch.float16, kernel_override=_lib.TWM_KERNEL_SIMT)):
+        with pytest.raises(_lib.TwmError) as e:
+            extra = {x: kw[x] for x in kw if x not in ("m", "a", "dt")}
+            _run_gemm(kw["a"], packed, scales, kw["m"], n, k, 32, kw["dt"], torch.float32, a_prologue=_lib.TWM_A_SILU_MUL, **extra)
+        assert e.value.status == _lib.TWM_EINVAL
+
+
 def test_wide_tensor_core_kernel_refuses_what_it_cannot_do():
     k, n = 256, 256
     _, packed, scales = _quantised(k, n, 32, 46)
