@@ -151,15 +151,19 @@ def run_ours(args):
     stream = torch.cuda.Stream(device)
     flags = _lib.TWM_FLAG_PDL        # weights are constants: let each GEMM prefetch them early
 
-    def enqueue_all(extra_flags=0):
+    gemm_list = [(weights[layer][pid], k, n) for layer in range(LAYERS) for pid, (_, k, n) in enumerate(LAYER_GEMMS)]
+
+    def enqueue_all(extra_flags=0, hint=True):
+        # every GEMM names its successor (the step's first GEMM follows its last one in the next replay),
+        # so the successor's first weights are on their way into L2 while this GEMM's grid drains
         ao = co = 0
-        for layer in range(LAYERS):
-            for pid, (_, k, n) in enumerate(LAYER_GEMMS):
-                p, s = weights[layer][pid]
-                q.gemm_tw_marlin_m1(dev_a[ao:ao + k], p, s, dev_c[co:co + n], n, k, group_size=GROUP,
-                                    workspace=ws, flags=flags | extra_flags)
-                ao += k
-                co += n
+        for i, ((p, s), k, n) in enumerate(gemm_list):
+            (np_, ns_), nk, nn = gemm_list[(i + 1) % len(gemm_list)]
+            q.gemm_tw_marlin_m1(dev_a[ao:ao + k], p, s, dev_c[co:co + n], n, k, group_size=GROUP,
+                                workspace=ws, flags=flags | extra_flags,
+                                next_gemm=(np_, ns_, m, nn, nk, GROUP) if hint else None)
+            ao += k
+            co += n
 
     with torch.cuda.stream(stream):
         enqueue_all()                                   # eager once: initialises per-device state
@@ -233,6 +237,24 @@ def run_ours(args):
             ind_ms = g0.elapsed_time(g1) / args.steps
         independent = {"ms_per_step": round(ind_ms, 4), "same_bits_as_dependent_run": same}
         del graph_i
+        # Diagnostic: the headline's launches without the hint that names each GEMM's successor
+        with torch.cuda.stream(stream):
+            dev_c.zero_()
+            graph_n = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph_n, stream=stream):
+                enqueue_all(hint=False)
+            for _ in range(args.warmup):
+                graph_n.replay()
+            torch.cuda.synchronize()
+            same_n = bool(torch.equal(dev_c, ref_c))
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g0.record(stream)
+            for _ in range(args.steps):
+                graph_n.replay()
+            g1.record(stream)
+            torch.cuda.synchronize()
+            independent["without_next_hint"] = {"ms_per_step": round(g0.elapsed_time(g1) / args.steps, 4), "same_bits": same_n}
+        del graph_n
     err = q.device_error(stream)
     if err:
         raise RuntimeError(f"device error word {err:#x}")
@@ -290,6 +312,7 @@ def run_ours(args):
         ind_gbs = step_bytes / (independent["ms_per_step"] * 1e-3) / 1e9
         independent.update({"gbs": round(ind_gbs, 1), "hbm_frac": round(ind_gbs / peak, 4),
                             "note": "same GEMM set without the wait for the preceding launch (TWM_FLAG_INDEPENDENT); diagnostic"})
+        line["without_next_hint"] = independent.pop("without_next_hint")
         line["independent_launches"] = independent
     if decode is not None:
         line["decode"] = decode

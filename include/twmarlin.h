@@ -140,6 +140,12 @@ typedef struct twm_gemm_args {
      * have stored it, so the separate pass and its buffer go away.  M == 1, FP16 activations, streaming
      * MMA kernel only (TWM_EINVAL otherwise). */
     int a_prologue;
+    /* Optional: the GEMM that will be enqueued after this one (on this stream, other kernels may come
+     * between).  Read during this call only.  While this GEMM's grid drains, its CTAs ask the memory
+     * system to pull the first K blocks of that GEMM's weights (up to 16 MB, the part its CTAs start
+     * with under its own plan) into L2, so HBM keeps streaming across the launch boundary and the next
+     * GEMM starts from L2.  A hint: results never depend on it.  Streaming MMA kernel only. */
+    const struct twm_gemm_args* next;
 } twm_gemm_args;
 
 /* What the heuristic decided for a shape; pure host arithmetic. */

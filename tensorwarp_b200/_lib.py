@@ -32,6 +32,7 @@ class GemmArgs(C.Structure):
         ("packed_offsets", C.c_void_p), ("scales_offsets", C.c_void_p), ("expert_idx", C.c_int),
         ("comm", C.c_void_p),
         ("a_prologue", C.c_int),
+        ("next", C.c_void_p),
     ]
 
 

@@ -84,6 +84,39 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, u
         : "memory");
 }
 
+// Ask the memory system to bring [src, src + bytes) into L2 (bytes a multiple of 16, src 16-byte aligned).
+// Nothing waits for it and nothing depends on it.
+__device__ __forceinline__ void l2_prefetch_bulk(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
+// The weights the NEXT GEMM on the stream starts with (twm_gemm_args.next): `regions` runs of `bytes`
+// bytes, `stride` apart, of its packed array and of its scale rows.  The CTAs of this launch share them
+// out in 4 KB pieces; the producer warp asks for its pieces once its own last load is on its way.
+struct NextHead {
+    const uint8_t* packed;       // null = none
+    const uint16_t* scales;
+    unsigned long long packed_stride, scales_stride;   // bytes
+    unsigned int packed_bytes, scales_bytes;           // per region, multiples of 16
+    unsigned int regions;
+};
+
+__device__ __forceinline__ void prefetch_next_head(const NextHead& nh, unsigned cta, unsigned n_ctas, int lane) {
+    if (nh.packed == nullptr) return;
+    constexpr unsigned PIECE = 4096;
+    auto run = [&](const uint8_t* base, unsigned long long stride, unsigned bytes) {
+        const unsigned per = (bytes + PIECE - 1) / PIECE;
+        const unsigned total = per * nh.regions;
+        for (unsigned i = cta + (unsigned)lane * n_ctas; i < total; i += 32u * n_ctas) {
+            const unsigned r = i / per, o = (i - r * per) * PIECE;
+            l2_prefetch_bulk(base + (size_t)r * stride + o, min(PIECE, bytes - o));
+        }
+    };
+    run(nh.packed, nh.packed_stride, nh.packed_bytes);
+    if (nh.scales != nullptr && nh.scales_bytes != 0)
+        run(reinterpret_cast<const uint8_t*>(nh.scales), nh.scales_stride, nh.scales_bytes);
+}
+
 // 2-D tiled TMA load (tensor map in kernel-parameter space), completion counted on `bar`.
 // x is the innermost coordinate in elements of the map's data type; x * element size must
 // be a multiple of 16 bytes.  No multicast.
@@ -200,6 +233,7 @@ struct GemmParams {
     int n_experts;
     int reduce_slices;           // K slices x slots that add up into one output tile (1 = none)
     int a_kind;                  // 0: a is f16; 1: SwiGLU, 2: tanh-GEGLU of a row [gate | up] (up at column K)
+    NextHead next;               // what to pull into L2 for the GEMM after this one
     const float* expert_ids;
     const float* expert_weights;
     size_t packed_expert_stride; // bytes

@@ -243,6 +243,10 @@ gemv_kernel(const __grid_constant__ GemmParams p)
             }
             __syncwarp();
         }
+        // every load of this CTA is on its way: now the head of the next GEMM's weights, so that memory
+        // stays busy while this grid drains and the next one starts up, and the next one starts from L2
+        prefetch_next_head(p.next, blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z),
+                           gridDim.x * gridDim.y * gridDim.z, lane);
         // A launch that does not wait for its predecessor must still not END before it: the kernel
         // after this one waits for this one only.  This warp has nothing left to do.
         if (p.no_wait) pdl_wait_prior_grids();

@@ -439,6 +439,41 @@ twm_status launch_op(const char* name, void (*kernel)(KArgs...), dim3 grid, dim3
     return TWM_OK;
 }
 
+// twm_gemm_args.next: which bytes the GEMM after this one starts with, under its own plan.
+twm::NextHead next_head_for(const twm_gemm_args* nx, int sm_count)
+{
+    twm::NextHead h;
+    memset(&h, 0, sizeof(h));
+    if (!nx || !nx->packed || !nx->scales || nx->packed_offsets) return h;
+    if (!shape_ok(nx->M, nx->N, nx->K, nx->group_size) || (reinterpret_cast<uintptr_t>(nx->packed) & 15)) return h;
+    const int kernel = resolve_kernel(nx);
+    twm_plan_t pl;
+    if (twm_plan(nx->M, nx->N, nx->K, nx->group_size, sm_count, nx->splits_override, kernel, &pl) != TWM_OK) return h;
+    if (pl.workspace_bytes > 0 && (!nx->workspace || nx->workspace_bytes < pl.workspace_bytes) && kernel != TWM_KERNEL_TC &&
+        kernel != TWM_KERNEL_TCW && nx->splits_override == 0 &&
+        twm_plan(nx->M, nx->N, nx->K, nx->group_size, sm_count, 1, kernel, &pl) != TWM_OK)
+        return h;
+    const long row_bytes = (long)nx->N * twm::kBlockBytes;           // one 32-block of K over all columns
+    const int gblocks = nx->group_size / 32;
+    const int nkb = nx->K / 32;
+    const int last = nkb - (pl.splits - 1) * pl.blocks_per_split;    // blocks of the last (shortest) K slice
+    long hb = (16L << 20) / ((long)pl.splits * row_bytes);
+    hb = std::min<long>(hb, std::min(pl.blocks_per_split, last));
+    hb = hb / gblocks * gblocks;
+    if (hb < gblocks) hb = std::min(gblocks, std::min(pl.blocks_per_split, last));
+    if (hb < 1) return h;
+    h.packed = nx->packed;
+    h.regions = (unsigned)pl.splits;
+    h.packed_stride = (unsigned long long)pl.blocks_per_split * row_bytes;
+    h.packed_bytes = (unsigned)(hb * row_bytes);
+    if ((nx->N & 7) == 0 && (reinterpret_cast<uintptr_t>(nx->scales) & 15) == 0 && pl.blocks_per_split % gblocks == 0) {
+        h.scales = nx->scales;
+        h.scales_stride = (unsigned long long)(pl.blocks_per_split / gblocks) * nx->N * 2;
+        h.scales_bytes = (unsigned)(((hb + gblocks - 1) / gblocks) * nx->N * 2);
+    }
+    return h;
+}
+
 // The pre-pass of the tcgen05 kernels: the launch's rows in [K/8][rows][8] order and the -8 * sum table.
 twm_status launch_prepass(__half* xp, float* a8, const __half* a, long lda, int rows, int K, int group, int nb_pad,
                           unsigned flags, void* stream)
@@ -596,6 +631,7 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
                      pl.workspace_bytes == 0 && !p.accumulate && a->packed_offsets == nullptr && !a->comm) ? 1 : 0;
         p.packed_offsets = a->packed_offsets; p.scales_offsets = a->scales_offsets; p.expert_idx = a->expert_idx;
         p.a_kind = a->a_prologue;
+        if (kernel == TWM_KERNEL_MMA && m0 + row_step >= a->M) p.next = next_head_for(a->next, sm_count);
         if (a->comm) {
             p.n_peers = a->comm->n_ranks; p.peer_rank = a->comm->rank; p.peer_slot_elems = a->comm->slot_elems;
             for (int r = 0; r < a->comm->n_ranks; ++r) { p.peer_data[r] = a->comm->data[r]; p.peer_flags[r] = a->comm->flags[r]; }

@@ -183,6 +183,8 @@ class QuantizedGenerationEngine:
         lib, cfg, b, fl = _lib.lib(), self.cfg, self.buf, self.flags
         ops = []
 
+        pending = []         # the Q4 GEMMs' arguments in launch order: each one names its successor
+
         def gemm(a, w, c, n_out, k_in, accumulate=False, silu_mul=False):
             args = _lib.GemmArgs(M=1, N=n_out, K=k_in, group_size=cfg.group_size, a_dtype=_lib.TWM_F16,
                                  c_dtype=_lib.TWM_F32 if c.dtype == torch.float32 else _lib.TWM_F16,
@@ -191,6 +193,9 @@ class QuantizedGenerationEngine:
                                  workspace_bytes=b.workspace.nbytes,
                                  flags=fl | (_lib.TWM_FLAG_ACCUMULATE if accumulate else 0),
                                  a_prologue=_lib.TWM_A_SILU_MUL if silu_mul else _lib.TWM_A_PLAIN)
+            if pending:      # the GEMM before this one pulls the head of these weights into L2 while it drains
+                pending[-1].next = C.addressof(args)
+            pending.append(args)
             return lambda: check(lib.twm_gemm_w4a16(C.byref(args), stream_ptr), "twm_gemm_w4a16")
 
         ops.append(("embedding", 1, lambda: check(lib.twm_embed(b.x.data_ptr(), self.model.embed.data_ptr(), b.token.data_ptr(),
@@ -227,6 +232,8 @@ class QuantizedGenerationEngine:
             b.token.data_ptr(), b.history.data_ptr(), b.history.numel(), b.pos.data_ptr(), b.cache_len.data_ptr(),
             b.step.data_ptr(), b.logits.data_ptr(), cfg.vocab, b.argmax_scratch.data_ptr(), b.argmax_scratch.numel(), fl,
             stream_ptr), "twm_argmax_advance")))
+        if len(pending) > 1:
+            pending[-1].next = C.addressof(pending[0])       # the next token's first GEMM
         return ops
 
     def forward_decode_tw_marlin_graph(self, stream_ptr: int) -> int:

@@ -79,12 +79,14 @@ def gemm_tw_marlin(a: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, 
                    flags: int = 0, splits_override: int = 0, kernel_override: int = 0,
                    packed_offsets: Optional[torch.Tensor] = None,
                    scales_offsets: Optional[torch.Tensor] = None, expert_idx: int = 0,
-                   a_prologue: int = _lib.TWM_A_PLAIN) -> None:
+                   a_prologue: int = _lib.TWM_A_PLAIN, next_gemm: Optional[tuple] = None) -> None:
     """C[m,n] = A[m,k] x dequant(packed, scales); A and C are f32 or f16, row-major.
 
     The M > 1 form of ``gemm_tw_marlin_m1``; enqueue only, like the reference.  With
     ``a_prologue=TWM_A_SILU_MUL`` (m = 1, f16) ``a`` is the [gate | up] output of the preceding GEMM
-    (2k values) and the GEMM reads silu(gate) * up: fused_silu_mul (ops.rs:966-977) without its pass."""
+    (2k values) and the GEMM reads silu(gate) * up: fused_silu_mul (ops.rs:966-977) without its pass.
+    ``next_gemm=(packed, scales, m, n, k, group_size)`` names the GEMM that follows on the stream (same
+    dtypes and workspace): while this one drains, the head of that one's weights is pulled into L2."""
     _require_cuda(a, packed, scales, c)
     if a.dtype not in _DTYPES or c.dtype not in _DTYPES:
         raise TwmError(_lib.TWM_EINVAL, "gemm_tw_marlin: A and C must be float32 or float16")
@@ -110,6 +112,12 @@ def gemm_tw_marlin(a: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, 
         scales_offsets=scales_offsets.data_ptr() if scales_offsets is not None else None,
         expert_idx=expert_idx, a_prologue=a_prologue,
     )
+    if next_gemm is not None:
+        np_, ns_, nm, nn, nk, ng = next_gemm
+        nxt = GemmArgs(M=nm, N=nn, K=nk, group_size=ng, a_dtype=args.a_dtype, c_dtype=args.c_dtype,
+                       packed=np_.data_ptr(), scales=ns_.data_ptr(), workspace=args.workspace,
+                       workspace_bytes=args.workspace_bytes)
+        args.next = C.addressof(nxt)          # read during the call below only
     check(_lib.lib().twm_gemm_w4a16(C.byref(args), _stream_ptr(stream)), "twm_gemm_w4a16")
 
 

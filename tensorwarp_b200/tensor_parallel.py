@@ -240,14 +240,22 @@ class TPDecodeStack:
         self.pos.fill_(length)
         self.cache_len.fill_(length + 1)
 
-    def _gemm(self, a, w, c, n_out, k_in, stream_ptr, push=False, silu_mul=False):
+    def _gemm(self, a, w, c, n_out, k_in, stream_ptr, push=False, silu_mul=False, then=None):
+        """`then` = (weights, n_out, k_in) of the GEMM that follows: its first weights are pulled into L2
+        while this one drains (twm_gemm_args.next)."""
+        nxt = None
+        if then is not None:
+            nxt = _lib.GemmArgs(M=self.rows, N=then[1], K=then[2], group_size=self.cfg.group_size, a_dtype=_lib.TWM_F16,
+                                c_dtype=_lib.TWM_F32, packed=then[0][0].data_ptr(), scales=then[0][1].data_ptr(),
+                                workspace=self.workspace.ptr, workspace_bytes=self.workspace.nbytes)
         args = _lib.GemmArgs(M=self.rows, N=n_out, K=k_in, group_size=self.cfg.group_size, a_dtype=_lib.TWM_F16,
                              c_dtype=_lib.TWM_F32 if c.dtype == torch.float32 else _lib.TWM_F16,
                              a=a.data_ptr(), lda=2 * k_in if silu_mul else k_in, packed=w[0].data_ptr(),
                              scales=w[1].data_ptr(), c=c.data_ptr(), ldc=n_out, workspace=self.workspace.ptr,
                              workspace_bytes=self.workspace.nbytes, flags=self.flags,
                              comm=self.comm.ptr if (push and self.comm is not None) else None,
-                             a_prologue=_lib.TWM_A_SILU_MUL if silu_mul else _lib.TWM_A_PLAIN)
+                             a_prologue=_lib.TWM_A_SILU_MUL if silu_mul else _lib.TWM_A_PLAIN,
+                             next=C.addressof(nxt) if nxt is not None else None)
         check(_lib.lib().twm_gemm_w4a16(C.byref(args), stream_ptr), "twm_gemm_w4a16")
         self.launches += 1
 
@@ -270,7 +278,8 @@ class TPDecodeStack:
                                   cfg.eps, fl, stream_ptr), "twm_rmsnorm")
         else:           # the previous layer's summed down output joins the residual stream here
             self._join_and_norm(self.normed.data_ptr(), lw.attn_norm.data_ptr(), stream_ptr)
-        self._gemm(self.normed, lw.wqkv, self.qkv, self.spec.n_qkv, cfg.hidden, stream_ptr)            # column-parallel
+        self._gemm(self.normed, lw.wqkv, self.qkv, self.spec.n_qkv, cfg.hidden, stream_ptr,            # column-parallel
+                   then=(lw.wo, cfg.hidden, self.hq * hd))
         check(lib.twm_rope_append(self.q.data_ptr(), self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(),
                                   self.qkv.data_ptr(), lw.bqkv.data_ptr() if lw.bqkv is not None else None, m,
                                   self.hq, self.hk, hd, self.pos.data_ptr(), cfg.max_seq, cfg.rope_theta, fl,
@@ -280,22 +289,28 @@ class TPDecodeStack:
                                   cfg.max_seq, self.attn_scratch.data_ptr(), self.attn_scratch.numel(), fl,
                                   stream_ptr), "twm_attn_decode")
         self.launches += 4
-        self._gemm(self.attn, lw.wo, self.part, cfg.hidden, self.hq * hd, stream_ptr, push=True)        # row-parallel
+        self._gemm(self.attn, lw.wo, self.part, cfg.hidden, self.hq * hd, stream_ptr, push=True,        # row-parallel
+                   then=(lw.wgu, self.spec.n_gu, cfg.hidden))
 
     def ffn_phase(self, li: int, stream_ptr: int) -> None:
         """Add the all-reduced o output, norm, column-parallel gate+up, SwiGLU, row-parallel down:
         leaves this rank's partial down output in `part`."""
         lib, cfg, fl, m, lw = _lib.lib(), self.cfg, self.flags, self.rows, self.layers[li]
         self._join_and_norm(self.normed.data_ptr(), lw.ffn_norm.data_ptr(), stream_ptr)
-        self._gemm(self.normed, lw.wgu, self.gate_up, self.spec.n_gu, cfg.hidden, stream_ptr)            # column-parallel
+        nl = self.layers[(li + 1) % len(self.layers)]
+        after_down = (nl.wqkv, self.spec.n_qkv, cfg.hidden)
+        self._gemm(self.normed, lw.wgu, self.gate_up, self.spec.n_gu, cfg.hidden, stream_ptr,            # column-parallel
+                   then=(lw.w_down, cfg.hidden, self.spec.n_gu // 2))
         if m == 1:      # one row: the down GEMM's activation reader takes silu(gate) * up on the fly (the same bits)
             self.launches += 1
-            self._gemm(self.gate_up, lw.w_down, self.part, cfg.hidden, self.spec.n_gu // 2, stream_ptr, push=True, silu_mul=True)
+            self._gemm(self.gate_up, lw.w_down, self.part, cfg.hidden, self.spec.n_gu // 2, stream_ptr, push=True, silu_mul=True,
+                       then=after_down)
             return
         check(lib.twm_silu_mul(self.act.data_ptr(), self.gate_up.data_ptr(), m, self.spec.n_gu // 2, fl, stream_ptr),
               "twm_silu_mul")
         self.launches += 2
-        self._gemm(self.act, lw.w_down, self.part, cfg.hidden, self.spec.n_gu // 2, stream_ptr, push=True)   # row-parallel
+        self._gemm(self.act, lw.w_down, self.part, cfg.hidden, self.spec.n_gu // 2, stream_ptr, push=True,   # row-parallel
+                   then=after_down)
 
     def finish(self, stream_ptr: int) -> None:
         """The last layer's summed down output joins the residual stream."""
