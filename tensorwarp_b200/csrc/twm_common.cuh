@@ -254,8 +254,6 @@ struct GemmParams {
     // ring stage (box = 256 u64 x map_rows rows = 128 columns x map_rows 32-blocks).
     int map_rows;                // 0 = no map (1-D bulk copies per row instead)
     alignas(64) CUtensorMap packed_map;
-    // tcgen05 kernel: -8 * sum of a scale group's activations per row, FP32 [K/G][NB] (written by the pre-pass)
-    const float* tc_a8;
     // tcgen05 kernel: tensor map over the launch's permuted activations, f16 [K/8][rows][8]
     alignas(64) CUtensorMap act_map;
 };

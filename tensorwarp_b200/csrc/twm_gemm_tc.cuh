@@ -13,13 +13,12 @@
 // The weight operand is never converted.  A nibble left in place in its 16-bit
 // half IS an FP16 subnormal: `v & 0x000F000F` = (q0, q4) * 2^-24, `v & 0x00F000F0`
 // = (q1, q5) * 2^-20, the same on `v >> 8` for (q2, q6), (q3, q7): five integer
-// instructions per eight nibbles; one FP16 multiply by 2^-4 brings each odd pair
-// down to 2^-24 as well (a subnormal times a power of two: exact), and the sixteen
-// registers of a 32-block go into tensor memory with one tcgen05.st as the MMA's A
-// operand.  The activations enter as they are (the pre-pass only reorders them), so
-// every product is exact whatever their magnitude; the "-8" becomes -8 * sum of the
-// group's activations (FP32 table from the pre-pass); the scale meets the
-// accumulator when a group's sum is read back.
+// instructions per eight nibbles; one FP16 add (or fused multiply-add by 2^-4) per
+// pair then makes them the signed weights (q - 8) * 2^-24, exactly (signed_low /
+// signed_high below), and the sixteen registers of a 32-block go into tensor memory
+// with one tcgen05.st as the MMA's A operand.  The activations enter as they are (the pre-pass only reorders them), so
+// every product is exact whatever their magnitude; the scale meets the accumulator
+// when a group's sum is read back.
 //
 // Data path per CTA (128 columns x a K slice of whole scale groups):
 //   warp 12      streams packed rows (one tiled TMA load per stage of four
@@ -54,12 +53,23 @@ constexpr int DEQ_SETS = 2;           // unpack warp sets, alternate blocks
 constexpr int DEQ_THREADS = DEQ_SETS * 128;
 constexpr int WARP_READ0 = 8;         // first read-back warp
 constexpr int B_STAGE_KCORES = WSTAGE_BLOCKS * 4;     // 8-wide K cores per activation stage
-constexpr int A8_SMEM_FLOATS = 8192;  // the K slice's -8*sum table is copied into shared memory when it fits (32 KB)
 
-// (n << 4) * 2^-24 as two FP16 subnormals -> n * 2^-24: exact, and on the FP16 pipe, which the unpack leaves idle
-__device__ __forceinline__ uint32_t sixteenth(uint32_t pair)
+// Two nibbles left in place in their 16-bit halves are the FP16 subnormals n * 2^-24 (bits 0-3) or
+// (n << 4) * 2^-24 (bits 4-7).  One FP16 instruction turns either pair into the signed weights
+// (n - 8) * 2^-24: every value involved is a multiple of 2^-24 below 2^-14, so the results are exact
+// (no flush to zero: the intrinsics compile to add/fma without .ftz), and the FP16 pipe is otherwise idle
+// in the unpack warps.  With the "-8" inside the operand nothing has to be added to an accumulator later.
+__device__ __forceinline__ uint32_t signed_low(uint32_t pair)
 {
-    const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&pair), __float2half2_rn(0.0625f));
+    const uint32_t minus8 = 0x80088008u;                 // two times -8 * 2^-24 = -2^-21 as FP16 subnormals
+    const __half2 r = __hadd2(*reinterpret_cast<const __half2*>(&pair), *reinterpret_cast<const __half2*>(&minus8));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t signed_high(uint32_t pair)
+{
+    const uint32_t minus8 = 0x80088008u;
+    const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&pair), __float2half2_rn(0.0625f),
+                              *reinterpret_cast<const __half2*>(&minus8));
     return *reinterpret_cast<const uint32_t*>(&r);
 }
 
@@ -87,7 +97,6 @@ template <int NB>
 struct Smem {
     alignas(128) uint8_t packed[WSTAGES][WSTAGE_BLOCKS * NT * kBlockBytes];
     alignas(128) uint8_t b[Cfg<NB>::ASLOTS][Cfg<NB>::B_STAGE_BYTES];          // [K core][row][8 K]
-    alignas(16) float a8[A8_SMEM_FLOATS];                                     // [group of the slice][NB]
     alignas(8) uint64_t w_full[WSTAGES];
     alignas(8) uint64_t w_empty[WSTAGES];
     alignas(8) uint64_t a_full[Cfg<NB>::ASLOTS];     // unpack -> MMA: a stage's A operands are in tensor memory
@@ -401,10 +410,10 @@ gemm_kernel(const __grid_constant__ GemmParams p)
                     for (int w = 0; w < 4; ++w) {
                         const uint32_t x = words[w];
                         const uint32_t x8 = x >> 8;
-                        regs[4 * w + 0] = x & 0x000F000Fu;         // (k0, k4) * 2^-24
-                        regs[4 * w + 1] = sixteenth(x & 0x00F000F0u);         // (k1, k5) * 2^-20, times 2^-4
-                        regs[4 * w + 2] = x8 & 0x000F000Fu;        // (k2, k6) * 2^-24
-                        regs[4 * w + 3] = sixteenth(x8 & 0x00F000F0u);        // (k3, k7) * 2^-20, times 2^-4
+                        regs[4 * w + 0] = signed_low(x & 0x000F000Fu);          // (k0, k4): (n - 8) * 2^-24
+                        regs[4 * w + 1] = signed_high(x & 0x00F000F0u);         // (k1, k5)
+                        regs[4 * w + 2] = signed_low(x8 & 0x000F000Fu);         // (k2, k6)
+                        regs[4 * w + 3] = signed_high(x8 & 0x00F000F0u);        // (k3, k7)
                     }
                     tmem_st16(lane_tmem + aslot * C::A_SLOT_COLS + r * 16, regs);
                 }
@@ -427,7 +436,7 @@ gemm_kernel(const __grid_constant__ GemmParams p)
         const bool owner = n < p.N;
         const uint32_t lane_tmem = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const uint16_t* scales = p.scales;
-        pdl_wait_prior_grids();          // the -8*sum table comes from the pre-pass; C may be read by the kernel before
+        pdl_wait_prior_grids();          // C may be read by the kernel before
         if (p.scales_offsets != nullptr) scales += p.scales_offsets[p.expert_idx];
         float acc[RC];
 #pragma unroll
@@ -439,21 +448,11 @@ gemm_kernel(const __grid_constant__ GemmParams p)
             return (owner && gq < n_groups) ? __ldg(scales + (size_t)(grow0 + gq) * p.N + n) : (uint16_t)0;
         };
         uint16_t s_next = load_scale(0);
-        // the slice's rows of the -8*sum table: into shared memory when they fit, else read from global
-        const bool a8_local = n_groups * NB <= A8_SMEM_FLOATS;
-        if (a8_local) {
-            const float4* src = reinterpret_cast<const float4*>(p.tc_a8 + (size_t)grow0 * NB);
-            float4* dst = reinterpret_cast<float4*>(sm.a8);
-            for (int i = tid - WARP_READ0 * 32; i < n_groups * NB / 4; i += EPI_THREADS) dst[i] = __ldcg(src + i);       // not through L1: see twm_gemm_tcw.cuh
-        }
-        named_bar_sync(2, EPI_THREADS);
         for (int gq = 0; gq < n_groups; ++gq) {
-            // accumulator of scale group gq: acc += s * (2^24 D - 8 sum(a))
+            // accumulator of scale group gq: acc += (s * 2^24) * D
             const int db = gq & 1;
-            const float sg = f16_bits_to_f32(s_next);
+            const float sg = f16_bits_to_f32(s_next) * 16777216.0f;
             s_next = load_scale(gq + 1);
-            const float4* a8p = a8_local ? reinterpret_cast<const float4*>(sm.a8 + gq * NB)
-                                         : reinterpret_cast<const float4*>(p.tc_a8 + (size_t)(grow0 + gq) * NB);
             {
                 uint64_t* bar = lean ? &sm.done[gq & 3] : &sm.d_full[db];
                 const uint32_t par = lean ? ((gq >> 2) & 1) : ((gq >> 1) & 1);
@@ -465,13 +464,9 @@ gemm_kernel(const __grid_constant__ GemmParams p)
                 if (row0 + c0 < p.M) {                                 // warp-uniform
                     uint32_t d[8];
                     tmem_ld<8>(lane_tmem + C::D_COL0 + db * NB + row0 + c0, d);
-                    const float4 q0 = a8_local ? a8p[(row0 + c0) / 4] : __ldcg(a8p + (row0 + c0) / 4);
-                    const float4 q1 = a8_local ? a8p[(row0 + c0) / 4 + 1] : __ldcg(a8p + (row0 + c0) / 4 + 1);
-                    const float a8[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
                     tmem_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        acc[c0 + j] = fmaf(sg, fmaf(__uint_as_float(d[j]), 16777216.0f, a8[j]), acc[c0 + j]);
+                    for (int j = 0; j < 8; ++j) acc[c0 + j] = fmaf(sg, __uint_as_float(d[j]), acc[c0 + j]);
                 }
             }
             tc_fence_before();
@@ -535,48 +530,16 @@ gemm_kernel(const __grid_constant__ GemmParams p)
     }
 }
 
-// Pre-pass of the tcgen05 kernels, one launch per GEMM launch.
-// Blocks [0, perm_blocks): rows [0, rows) of the activations, f16 [rows][lda], rewritten as
-// [K/8][rows][8] with the eight K of a core in the order k0,k4,k1,k5,k2,k6,k3,k7 (the order in
-// which the unpack lays nibbles into the operand); the values themselves are not touched, so any
-// FP16 activation, subnormals included, enters the products exactly.  One thread per (K core, row).
-// Remaining blocks: the table a8[g][m] = -8 * sum of row m's activations over scale group g, FP32,
-// [K/G][nb_pad] (rows past `rows` zero), summed in a fixed order by group/8 lanes per (g, m).
+// Pre-pass of the tcgen05 kernels, one launch per GEMM launch: rows [0, rows) of the activations,
+// f16 [rows][lda], rewritten as [K/8][rows][8] with the eight K of a core in the order
+// k0,k4,k1,k5,k2,k6,k3,k7 (the order in which the unpack lays nibbles into the operand).  The values
+// themselves are not touched, so any FP16 activation, subnormals included, enters the products
+// exactly.  One thread per (K core, row).
 __global__ void __launch_bounds__(256)
-permute_activations_kernel(__half* __restrict__ out, float* __restrict__ a8, const __half* __restrict__ a, long lda,
-                           int rows, int kcores, int perm_blocks, int group, int nb_pad)
+permute_activations_kernel(__half* __restrict__ out, const __half* __restrict__ a, long lda, int rows, int kcores)
 {
     pdl_launch_dependents();
     pdl_wait_prior_grids();
-    if ((int)blockIdx.x >= perm_blocks) {
-        // group/8 consecutive lanes share one (g, m): each adds 8 values, then a fixed shuffle tree
-        const int lpg = group >> 3;                                     // 4 or 16 lanes
-        const int idx = ((int)blockIdx.x - perm_blocks) * blockDim.x + threadIdx.x;
-        const int ngroups = kcores * 8 / group;
-        const int item = idx / lpg, part = idx - item * lpg;
-        const bool live = item < ngroups * nb_pad;
-        const int g = live ? item / nb_pad : 0, m = live ? item - g * nb_pad : 0;
-        float s = 0.0f;
-        if (live && m < rows) {
-            const __half* src = a + (size_t)m * lda + (size_t)g * group + part * 8;
-            uint4 x;
-            if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-                x = *reinterpret_cast<const uint4*>(src);
-            } else {
-                const uint16_t* s16 = reinterpret_cast<const uint16_t*>(src);
-                x.x = s16[0] | ((uint32_t)s16[1] << 16); x.y = s16[2] | ((uint32_t)s16[3] << 16);
-                x.z = s16[4] | ((uint32_t)s16[5] << 16); x.w = s16[6] | ((uint32_t)s16[7] << 16);
-            }
-            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&x.x));
-            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&x.y));
-            const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&x.z));
-            const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&x.w));
-            s = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
-        }
-        for (int d = 1; d < lpg; d <<= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
-        if (live && part == 0) a8[item] = -8.0f * s;
-        return;
-    }
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= rows * kcores) return;
     const int kc = idx / rows, m = idx - kc * rows;

@@ -11,11 +11,12 @@
 //
 // Same result definition as every other kernel of the library: w = f32(scale) * (nibble - 8),
 // exact products, FP32 accumulation, the scale applied in FP32 per 128-group.  The weight operand
-// is never converted: `v & 0x000F000F` etc. leave each nibble as an FP16 subnormal (five integer
-// instructions and two exact FP16 multiplies by 2^-4 per eight nibbles); the unpack warps write those bit patterns into shared memory as
+// is never converted: `v & 0x000F000F` etc. leave each nibble as an FP16 subnormal, one FP16 add or
+// fused multiply-add per pair makes it the signed weight (q - 8) * 2^-24, exactly (nine instructions
+// per eight nibbles); the unpack warps write those bit patterns into shared memory as
 // the MMA's B operand (K-major 8x16-byte core matrices, no swizzle).  The activations come from
-// the same pre-pass as in twm_gemm_tc.cuh (K order k0,k4,k1,k5,..., and the table -8 * sum(a) per
-// group and row) and are the A operand, loaded by tiled TMA.  Every scale group accumulates into a fresh accumulator (two, used in turn); the
+// the same pre-pass as in twm_gemm_tc.cuh (K order k0,k4,k1,k5,...) and are the A operand, loaded
+// by tiled TMA.  Every scale group accumulates into a fresh accumulator (two, used in turn); the
 // read-back warps take a finished group out of tensor memory, multiply by their column's FP32
 // scale and add into registers: thread = one activation row, 128 column sums.
 //
@@ -206,10 +207,10 @@ gemm_kernel(const __grid_constant__ GemmParams p)
                     const uint32_t x = words[w];
                     const uint32_t x8 = x >> 8;
                     uint4 o;
-                    o.x = x & 0x000F000Fu;          // (k0, k4) * 2^-24
-                    o.y = tc::sixteenth(x & 0x00F000F0u);          // (k1, k5) * 2^-20, times 2^-4
-                    o.z = x8 & 0x000F000Fu;         // (k2, k6) * 2^-24
-                    o.w = tc::sixteenth(x8 & 0x00F000F0u);         // (k3, k7) * 2^-20, times 2^-4
+                    o.x = tc::signed_low(x & 0x000F000Fu);           // (k0, k4): (n - 8) * 2^-24
+                    o.y = tc::signed_high(x & 0x00F000F0u);          // (k1, k5)
+                    o.z = tc::signed_low(x8 & 0x000F000Fu);          // (k2, k6)
+                    o.w = tc::signed_high(x8 & 0x00F000F0u);         // (k3, k7)
                     *reinterpret_cast<uint4*>(dst + w * (NT * 16)) = o;
                 }
             }
@@ -224,20 +225,14 @@ gemm_kernel(const __grid_constant__ GemmParams p)
         const int m = quarter * 32 + lane;                   // this thread's activation row = its TMEM lane
         const int cbase = half * EPI_COLS;                   // its first column inside the tile
         const uint32_t lane_tmem = tmem_base + ((uint32_t)(quarter * 32) << 16) + cbase;
-        // The tables come from the pre-pass; C may be read by the kernel before.  They are read with
-        // ld.global.cg: under programmatic launch this CTA can start while the launch before still runs
-        // on this SM and fills L1 with the PREVIOUS pre-pass's lines of the same addresses.
-        pdl_wait_prior_grids();
+        pdl_wait_prior_grids();                              // C may be read by the kernel before
         float acc[EPI_COLS];
 #pragma unroll
         for (int j = 0; j < EPI_COLS; ++j) acc[j] = 0.0f;
         const int grow0 = b0 / GROUP_BLOCKS;
         bool ok = true;
-        float a8_next = n_stages > 0 ? __ldcg(p.tc_a8 + (size_t)grow0 * MB + m) : 0.0f;
         for (int st = 0; st < n_stages; ++st) {
             const int db = st % ACCS, sb = st & 1;
-            const float a8 = a8_next;                                  // -8 * sum of this row's activations over the group
-            if (st + 1 < n_stages) a8_next = __ldcg(p.tc_a8 + (size_t)(grow0 + st + 1) * MB + m);
             if (!tc::wait_uniform(&sm.d_full[db], (st / ACCS) & 1, abort_flag)) { ok = false; break; }
             tc::tc_fence_after();
             // Every thread needs its columns' scales as FP32: thread j < 128 converts scale j once (the
@@ -248,7 +243,7 @@ gemm_kernel(const __grid_constant__ GemmParams p)
                 uint16_t h = 0;
                 if (scale_bulk) h = sm.sc[st % SSTAGES][tid];
                 else if (n < p.N) h = __ldg(p.scales + (size_t)(grow0 + st) * p.N + n);
-                sm.scf[sb][tid] = f16_bits_to_f32(h);
+                sm.scf[sb][tid] = f16_bits_to_f32(h) * 16777216.0f;      // the operand's 2^-24 comes out here
             }
             named_bar_sync(2, EPI_THREADS);
             const float* scf = &sm.scf[sb][cbase];
@@ -265,7 +260,7 @@ gemm_kernel(const __grid_constant__ GemmParams p)
                 tc::tmem_wait_ld();
 #pragma unroll
                 for (int j = 0; j < 16; ++j)
-                    acc[c0 + j] = fmaf(sc[j], fmaf(__uint_as_float(d[j]), 16777216.0f, a8), acc[c0 + j]);
+                    acc[c0 + j] = fmaf(sc[j], __uint_as_float(d[j]), acc[c0 + j]);
             }
             tc::tc_fence_before();
             __syncwarp();

@@ -474,15 +474,12 @@ twm::NextHead next_head_for(const twm_gemm_args* nx, int sm_count)
     return h;
 }
 
-// The pre-pass of the tcgen05 kernels: the launch's rows in [K/8][rows][8] order and the -8 * sum table.
-twm_status launch_prepass(__half* xp, float* a8, const __half* a, long lda, int rows, int K, int group, int nb_pad,
-                          unsigned flags, void* stream)
+// The pre-pass of the tcgen05 kernels: the launch's rows in [K/8][rows][8] order.
+twm_status launch_prepass(__half* xp, const __half* a, long lda, int rows, int K, unsigned flags, void* stream)
 {
     const int items = rows * (K / 8);
-    const int perm_blocks = (items + 255) / 256;
-    const int sum_blocks = ((K / group) * nb_pad * (group / 8) + 255) / 256;
-    return launch_op("permute_activations_kernel", twm::tc::permute_activations_kernel, dim3(perm_blocks + sum_blocks), dim3(256), 0,
-                     flags & TWM_FLAG_PDL, stream, xp, a8, a, lda, rows, K / 8, perm_blocks, group, nb_pad);
+    return launch_op("permute_activations_kernel", twm::tc::permute_activations_kernel, dim3((items + 255) / 256), dim3(256), 0,
+                     flags & TWM_FLAG_PDL, stream, xp, a, lda, rows, K / 8);
 }
 }  // namespace
 
@@ -527,12 +524,8 @@ twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int split
     out->grid_x = n_tiles;
     out->grid_y = splits;
     out->workspace_bytes = (splits > 1 && !cluster) ? kCounterBytes + (size_t)splits * rows * N * sizeof(float) : 0;
-    if (kernel == TWM_KERNEL_TC)    // + the launch's activations in the MMA's K order and their per-group sums, behind the split-K part
-        out->workspace_bytes = kCounterBytes + (splits > 1 ? (size_t)splits * rows * N * sizeof(float) : 0) +
-                               256 + (size_t)rows * K * 2 + 256 + (size_t)(K / group_size) * kTcRows * sizeof(float);
-    if (kernel == TWM_KERNEL_TCW)   // the same two pre-pass outputs, sized for 128 rows per launch
-        out->workspace_bytes = kCounterBytes + (splits > 1 ? (size_t)splits * rows * N * sizeof(float) : 0) +
-                               256 + (size_t)rows * K * 2 + 256 + (size_t)(K / group_size) * kTcwRows * sizeof(float);
+    if (kernel == TWM_KERNEL_TC || kernel == TWM_KERNEL_TCW)    // + the launch's activations in the MMA's K order, behind the split-K part
+        out->workspace_bytes = kCounterBytes + (splits > 1 ? (size_t)splits * rows * N * sizeof(float) : 0) + 256 + (size_t)rows * K * 2;
     out->cluster_reduce = cluster ? 1 : 0;
     return TWM_OK;
 }
@@ -651,9 +644,7 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
                 snprintf(t_last_error, sizeof(t_last_error), "cuTensorMapEncodeTiled failed for the activation map");
                 return TWM_ELAUNCH;
             }
-            char* a8 = xp + (((size_t)rows * a->K * 2 + 255) / 256) * 256;
-            p.tc_a8 = (const float*)a8;
-            st = launch_prepass((__half*)xp, (float*)a8, (const __half*)p.a, p.lda, rows, a->K, a->group_size, kTcwRows, a->flags, stream_);
+            st = launch_prepass((__half*)xp, (const __half*)p.a, p.lda, rows, a->K, a->flags, stream_);
             if (st != TWM_OK) return st;
             st = launch_tcw(p, dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
         }
@@ -666,9 +657,7 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
                 snprintf(t_last_error, sizeof(t_last_error), "cuTensorMapEncodeTiled failed for the activation map");
                 return TWM_ELAUNCH;
             }
-            char* a8 = xp + (((size_t)rows * a->K * 2 + 255) / 256) * 256;
-            p.tc_a8 = (const float*)a8;
-            st = launch_prepass((__half*)xp, (float*)a8, (const __half*)p.a, p.lda, rows, a->K, a->group_size, nb_rows, a->flags, stream_);
+            st = launch_prepass((__half*)xp, (const __half*)p.a, p.lda, rows, a->K, a->flags, stream_);
             if (st != TWM_OK) return st;
             st = launch_tc(p, rows, dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
         }
