@@ -891,9 +891,10 @@ def _tp_line(args, world, state, failed):
     return line
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch, averaged over one layer's four kernels,
-# from the ncu capture summarised in profiles/bench_config1_launch_list.md
-TRAFFIC_PER_LAUNCH = 30116928
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, averaged over one layer's four kernels
+# (8 588 032 + 6 695 424 + 70 571 264 + 35 111 936 bytes for qkv, o, gate+up, down; one ncu capture per
+# shape, summarised in profiles/bench_config1_launch_list.md)
+TRAFFIC_PER_LAUNCH = 30241664
 
 
 # ------------------------------------------------------- CPU baseline arm --

@@ -487,16 +487,19 @@ gemv_kernel(const __grid_constant__ GemmParams p)
     // After a CTA's stores (if any): make them visible system-wide and count the CTA; the last CTA
     // of the grid tells every peer that this rank's partial for operation comm_seq is complete.
     // Called by ONE thread of each storing CTA after a CTA-wide barrier: the barrier orders the
-    // CTA's stores before this thread, its system-scope fence is cumulative over them, and the
-    // release stores of the last CTA carry every counted CTA's stores with them.  (A fence by
-    // every thread would cost a link round trip each.)
+    // CTA's stores before this thread and its system-scope fence is cumulative over them (a fence by
+    // every thread would cost a link round trip each).  The CTAs hand their stores to the last CTA
+    // at GPU scope (fence + relaxed atomic on this GPU's counter; relaxed atomic + fence on the
+    // other side); the last CTA's fence, at system scope, is also the release for its flag
+    // stores, which then go out back to back: a st.release per peer would wait for the previous
+    // flag's acknowledgement each time, one link round trip per peer.
     auto comm_cta_done = [&](unsigned int total) {
-        __threadfence_system();
+        fence_acq_rel_gpu();
         if (atomicAdd(&p.comm_state[1], 1u) == total - 1) {
-            __threadfence_system();          // acquire side: the other CTAs' counted stores come before the flags below
+            fence_acq_rel_sys();
             atomicExch(&p.comm_state[1], 0u);
             for (int s = 0; s < p.n_peers; ++s)
-                st_release_sys_u32(p.peer_flags[s] + ((comm_seq & 1u) * p.n_peers + p.peer_rank) * 8, comm_seq + 1u);
+                st_relaxed_sys_u32(p.peer_flags[s] + ((comm_seq & 1u) * p.n_peers + p.peer_rank) * 8, comm_seq + 1u);
         }
     };
 
