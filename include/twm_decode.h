@@ -50,6 +50,18 @@ twm_status twm_attn_decode(void* out_f16, const void* q_f16, const void* k_cache
                            int rows, int num_heads, int num_kv_heads, int head_dim, const int* len_buf, int max_seq,
                            void* scratch, size_t scratch_bytes, int flags, void* stream);
 
+/* The two passes above as one: the attention kernel takes the fused QKV GEMM output [rows][q | k | v]
+ * itself, rotates q on the way in, and the CTA whose chunk holds position pos_buf[0] rotates and
+ * appends the new k row and the new v row (bias added) before using them.  Same bits as
+ * twm_rope_append followed by twm_attn_decode, one launch less per layer.  rope_table = cos
+ * [head_dim/2] then sin [head_dim/2] of pos_buf[0], written once per decode step by twm_rope_table
+ * (the freq/theta formulas of ops.rs:2601-2650); it must be the table of the same position. */
+twm_status twm_rope_table(float* table, const int* pos_buf, int head_dim, float rope_base, int flags, void* stream);
+twm_status twm_attn_decode_rope(void* out_f16, const void* qkv_f16, const float* bias, const float* rope_table,
+                                void* k_cache_f16, void* v_cache_f16, int rows, int num_heads, int num_kv_heads,
+                                int head_dim, const int* pos_buf, const int* len_buf, int max_seq, void* scratch,
+                                size_t scratch_bytes, int flags, void* stream);
+
 /* act (f16 [rows][ffn]) = silu(gate) * up on the fused gate+up GEMM output [rows][gate | up];
  * replaces split_gate_up + fused_silu_mul (ops.rs:2255-2298, 966-977). */
 twm_status twm_silu_mul(void* act_f16, const void* gate_up_f16, int rows, int ffn, int flags, void* stream);

@@ -294,6 +294,34 @@ allreduce_add_rmsnorm_kernel(__half* __restrict__ y, float* __restrict__ x, cons
     }
 }
 
+// cos and sin of the rotation of pair `pair` at position `pos` (freq = 1/powf(base, 2*pair/head_dim),
+// theta = pos*freq: crates/kernels/src/ops.rs:2601-2650), and the rotated value of one element of
+// the pair (x0 = first half, x1 = second half).  Written without contraction so that every kernel
+// that rotates gives the same bits.
+__device__ __forceinline__ void rope_cos_sin(int pos, int pair, int head_dim, float rope_base, float* c, float* s)
+{
+    const float freq = 1.0f / powf(rope_base, 2.0f * (float)pair / (float)head_dim);
+    const float theta = __fmul_rn((float)pos, freq);
+    *c = cosf(theta);
+    *s = sinf(theta);
+}
+__device__ __forceinline__ float rope_rotate(float x0, float x1, float c, float s, bool first_half)
+{
+    return first_half ? __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)) : __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+}
+
+// The table of one position: cos [head_dim/2] then sin [head_dim/2], once per decode step, for the
+// attention kernel that rotates q and k itself (attn_chunk_kernel<.., true>).
+__global__ void __launch_bounds__(256)
+rope_table_kernel(float* __restrict__ table, const int* __restrict__ pos_buf, int head_dim, float rope_base)
+{
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    const int half_d = head_dim / 2;
+    const int pair = blockIdx.x * blockDim.x + threadIdx.x;
+    if (pair < half_d) rope_cos_sin(pos_buf[0], pair, head_dim, rope_base, &table[pair], &table[half_d + pair]);
+}
+
 // q/k bias + rotate-half RoPE, v bias, append k and v at position pos_buf[0].  Reference:
 // warp_fused_bias_rope_append_dp, crates/kernels/src/ops.rs:2601-2650 (same formulas: freq =
 // 1/powf(base, 2*pair/head_dim), theta = pos*freq).  qkv is the fused GEMM output
@@ -324,13 +352,12 @@ rope_append_kernel(__half* __restrict__ q_out, __half* __restrict__ k_cache, __h
         const int head = local / head_dim;
         const int d = local - head * head_dim;
         const int pair = d % half_d;
-        const float freq = 1.0f / powf(rope_base, 2.0f * (float)pair / (float)head_dim);
-        const float theta = (float)pos * freq;
-        const float cos_t = cosf(theta), sin_t = sinf(theta);
+        float cos_t, sin_t;
+        rope_cos_sin(pos, pair, head_dim, rope_base, &cos_t, &sin_t);
         const int src0 = (is_q ? 0 : q_total) + head * head_dim + pair;
         float x0 = __half2float(qkv[src0]), x1 = __half2float(qkv[src0 + half_d]);
         if (bias) { x0 += bias[src0]; x1 += bias[src0 + half_d]; }
-        const float r = (d < half_d) ? x0 * cos_t - x1 * sin_t : x0 * sin_t + x1 * cos_t;
+        const float r = rope_rotate(x0, x1, cos_t, sin_t, d < half_d);
         if (is_q) q_out[local] = __float2half_rn(r);
         else if (pos < max_seq) k_cache[(size_t)pos * kv_dim + local] = __float2half_rn(r);
     }
@@ -359,11 +386,19 @@ rope_append_kernel(__half* __restrict__ q_out, __half* __restrict__ k_cache, __h
 constexpr int ATT_CHUNK = 32;       // tokens per CTA = lanes of a warp
 constexpr int ATT_MAX_GROUP = 8;      // q heads per kv head, at most
 
-template <int HEAD_DIM>
+//
+// ROPE = true: the kernel takes the fused QKV GEMM output instead of a rotated q.  Every warp
+// rotates its own q head on the way in (bias, rotate-half with the step's cos/sin table, rounding
+// to f16 as rope_append_kernel stores q), and the one CTA per kv head whose chunk holds position
+// pos_buf[0] rotates the new k row, adds the bias to the new v row, appends both to the caches
+// (it is their only writer) and uses them from shared memory: the separate RoPE/append pass
+// (fused_bias_rope_append_device_pos, ops.rs:2601-2680) disappears, same bits.
+template <int HEAD_DIM, bool ROPE>
 __global__ void __launch_bounds__(ATT_MAX_GROUP * 32)
 attn_chunk_kernel(float* __restrict__ part /* [heads][chunks][HEAD_DIM + 2] */, const __half* __restrict__ q,
-                  const __half* __restrict__ k_cache, const __half* __restrict__ v_cache, int num_heads,
-                  int num_kv_heads, const int* __restrict__ len_buf, int max_chunks, int max_seq)
+                  __half* k_cache, __half* v_cache, int num_heads, int num_kv_heads, const int* __restrict__ len_buf,
+                  int max_chunks, int max_seq, const float* __restrict__ bias, const float* __restrict__ rope,
+                  const int* __restrict__ pos_buf)
 {
     static_assert(HEAD_DIM == 128, "lane owns 4 of 128 dims");
     constexpr int ROW_BYTES = HEAD_DIM * 2;                 // one token's K (or V) row of this kv head
@@ -373,9 +408,9 @@ attn_chunk_kernel(float* __restrict__ part /* [heads][chunks][HEAD_DIM + 2] */, 
     pdl_launch_dependents();
     pdl_wait_prior_grids();
     const int chunk = blockIdx.x, kvh = blockIdx.y;
-    {   // one sequence per grid z: its own q, cache and partials
+    {   // one sequence per grid z: its own q (or fused q|k|v row), cache and partials
         const size_t row = blockIdx.z;
-        q += row * (size_t)num_heads * HEAD_DIM;
+        q += row * (size_t)(ROPE ? (num_heads + 2 * num_kv_heads) : num_heads) * HEAD_DIM;
         k_cache += row * (size_t)max_seq * num_kv_heads * HEAD_DIM;
         v_cache += row * (size_t)max_seq * num_kv_heads * HEAD_DIM;
         part += row * (size_t)num_heads * max_chunks * (HEAD_DIM + 2);
@@ -386,6 +421,42 @@ attn_chunk_kernel(float* __restrict__ part /* [heads][chunks][HEAD_DIM + 2] */, 
     const int kv_dim = num_kv_heads * HEAD_DIM;
     const int h = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* dst = part + ((size_t)(kvh * group + h) * max_chunks + chunk) * (HEAD_DIM + 2);
+    // four dims of one head, rotated: lane l holds dims 4l .. 4l+3, its partner lane l ^ 16 the other half of the pairs
+    auto rope4 = [&](int elem0, bool rotate) -> uint2 {
+        const uint2 raw = *reinterpret_cast<const uint2*>(q + elem0 + lane * 4);
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+        float f[4] = {a.x, a.y, b.x, b.y};
+        if (bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) f[j] += bias[elem0 + lane * 4 + j];
+        }
+        float r[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float other = __shfl_xor_sync(0xffffffffu, f[j], 16);
+            const int pair = (lane & 15) * 4 + j;
+            const bool first = lane < 16;
+            r[j] = rotate ? rope_rotate(first ? f[j] : other, first ? other : f[j], rope[pair], rope[HEAD_DIM / 2 + pair], first)
+                          : f[j];
+        }
+        const __half2 h0 = __floats2half2_rn(r[0], r[1]), h1 = __floats2half2_rn(r[2], r[3]);
+        uint2 o;
+        o.x = *reinterpret_cast<const uint32_t*>(&h0);
+        o.y = *reinterpret_cast<const uint32_t*>(&h1);
+        return o;
+    };
+    const int q_total = num_heads * HEAD_DIM;
+    const int pos = ROPE ? pos_buf[0] : -1;
+    const int new_tok = pos - t0;                        // row of the new token inside this chunk, if it is in it
+    const bool has_new = ROPE && new_tok >= 0 && new_tok < ATT_CHUNK && pos < max_seq;      // CTA-uniform
+    uint2 k_new = make_uint2(0, 0), v_new = make_uint2(0, 0);
+    if (has_new && h == 0) {                             // the new k and v rows of this kv head: into the caches
+        k_new = rope4(q_total + kvh * HEAD_DIM, true);
+        v_new = rope4(q_total + kv_dim + kvh * HEAD_DIM, false);
+        *reinterpret_cast<uint2*>(k_cache + (size_t)pos * kv_dim + kvh * HEAD_DIM + lane * 4) = k_new;
+        *reinterpret_cast<uint2*>(v_cache + (size_t)pos * kv_dim + kvh * HEAD_DIM + lane * 4) = v_new;
+    }
     if (t0 >= len) {
         // empty chunk: mark as such so the merge ignores it
         if (lane == 0) { dst[HEAD_DIM] = -INFINITY; dst[HEAD_DIM + 1] = 0.0f; }
@@ -395,7 +466,8 @@ attn_chunk_kernel(float* __restrict__ part /* [heads][chunks][HEAD_DIM + 2] */, 
     __shared__ __align__(16) unsigned char k_s[ATT_CHUNK * KROW];
     __shared__ __align__(16) unsigned char v_s[ATT_CHUNK * ROW_BYTES];
     __shared__ __align__(16) float q_s[ATT_MAX_GROUP][HEAD_DIM];
-    const uint2 qr = *reinterpret_cast<const uint2*>(q + (size_t)(kvh * group + h) * HEAD_DIM + lane * 4);
+    const uint2 qr = ROPE ? rope4((kvh * group + h) * HEAD_DIM, true)
+                          : *reinterpret_cast<const uint2*>(q + (size_t)(kvh * group + h) * HEAD_DIM + lane * 4);
     {
         // K and V of the chunk: piece i is bytes [16 i, 16 i + 16) of the chunk's rows laid end to end;
         // rows past the sequence end are zero-filled (their probability is 0, and 0 x garbage could be NaN)
@@ -409,7 +481,7 @@ attn_chunk_kernel(float* __restrict__ part /* [heads][chunks][HEAD_DIM + 2] */, 
             for (int b = 0; b < BATCH; ++b) {
                 const int i = i0 + b * blockDim.x;
                 const int tok = i / PER_ROW, piece = i % PER_ROW;
-                const bool in = (i < PIECES) && (tok < nt);
+                const bool in = (i < PIECES) && (tok < nt) && !(has_new && tok == new_tok);     // the new row is not in the cache yet
                 kk[b] = in ? *reinterpret_cast<const uint4*>(kg + tok * row_stride + piece * 16) : make_uint4(0, 0, 0, 0);
                 vv[b] = in ? *reinterpret_cast<const uint4*>(vg + tok * row_stride + piece * 16) : make_uint4(0, 0, 0, 0);
             }
@@ -418,11 +490,16 @@ attn_chunk_kernel(float* __restrict__ part /* [heads][chunks][HEAD_DIM + 2] */, 
                 const int i = i0 + b * blockDim.x;
                 if (i < PIECES) {
                     const int tok = i / PER_ROW, piece = i % PER_ROW;
+                    if (has_new && tok == new_tok) continue;           // written below by warp 0
                     *reinterpret_cast<uint4*>(k_s + tok * KROW + piece * 16) = kk[b];
                     *reinterpret_cast<uint4*>(v_s + i * 16) = vv[b];
                 }
             }
         }
+    }
+    if (has_new && h == 0) {
+        *reinterpret_cast<uint2*>(k_s + new_tok * KROW + lane * 8) = k_new;
+        *reinterpret_cast<uint2*>(v_s + new_tok * ROW_BYTES + lane * 8) = v_new;
     }
     {
         const float scale = rsqrtf((float)HEAD_DIM);

@@ -1212,24 +1212,60 @@ size_t twm_attn_scratch_bytes(int rows, int num_heads, int head_dim, int max_seq
     return (size_t)rows * num_heads * chunks * (head_dim + 2) * sizeof(float);
 }
 
-twm_status twm_attn_decode(void* out, const void* q, const void* k_cache, const void* v_cache, int rows, int num_heads,
-                           int num_kv_heads, int head_dim, const int* len_buf, int max_seq, void* scratch,
-                           size_t scratch_bytes, int flags, void* stream)
+namespace {
+twm_status attn_decode_common(void* out, const void* q_or_qkv, void* k_cache, void* v_cache, int rows, int num_heads,
+                              int num_kv_heads, int head_dim, const int* len_buf, int max_seq, void* scratch,
+                              size_t scratch_bytes, const float* bias, const float* rope_table, const int* pos_buf,
+                              int flags, void* stream)
 {
-    if (!out || !q || !k_cache || !v_cache || !len_buf || !scratch || rows < 1 || rows > 65535) return TWM_EINVAL;
+    if (!out || !q_or_qkv || !k_cache || !v_cache || !len_buf || !scratch || rows < 1 || rows > 65535) return TWM_EINVAL;
     if (head_dim != 128 || num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads) return TWM_EINVAL;
     if (num_heads / num_kv_heads > twm::ops::ATT_MAX_GROUP) return TWM_EINVAL;
     if (scratch_bytes < twm_attn_scratch_bytes(rows, num_heads, head_dim, max_seq)) return TWM_EWORKSPACE;
+    if (reinterpret_cast<uintptr_t>(q_or_qkv) & 7) return TWM_EALIGN;
     twm_status st = ensure_device(nullptr);
     if (st != TWM_OK) return st;
     const int chunks = (max_seq + twm::ops::ATT_CHUNK - 1) / twm::ops::ATT_CHUNK;
     if (chunks > 1024) return TWM_EINVAL;          // the merge pass keeps one weight per chunk in shared memory
-    st = launch_op("twm_attn_decode(chunks)", twm::ops::attn_chunk_kernel<128>, dim3(chunks, num_kv_heads, rows),
-                   dim3(32 * (num_heads / num_kv_heads)), 0, flags, stream, (float*)scratch, (const __half*)q, (const __half*)k_cache,
-                   (const __half*)v_cache, num_heads, num_kv_heads, len_buf, chunks, max_seq);
+    const dim3 grid(chunks, num_kv_heads, rows), block(32 * (num_heads / num_kv_heads));
+    if (rope_table)
+        st = launch_op("twm_attn_decode_rope(chunks)", twm::ops::attn_chunk_kernel<128, true>, grid, block, 0, flags, stream,
+                       (float*)scratch, (const __half*)q_or_qkv, (__half*)k_cache, (__half*)v_cache, num_heads, num_kv_heads,
+                       len_buf, chunks, max_seq, bias, rope_table, pos_buf);
+    else
+        st = launch_op("twm_attn_decode(chunks)", twm::ops::attn_chunk_kernel<128, false>, grid, block, 0, flags, stream,
+                       (float*)scratch, (const __half*)q_or_qkv, (__half*)k_cache, (__half*)v_cache, num_heads, num_kv_heads,
+                       len_buf, chunks, max_seq, (const float*)nullptr, (const float*)nullptr, (const int*)nullptr);
     if (st != TWM_OK) return st;
     return launch_op("twm_attn_decode(merge)", twm::ops::attn_merge_kernel<128>, dim3(num_heads, rows), dim3(128 * twm::ops::ATT_MERGE_PARTS), 0, flags,
                      stream, (__half*)out, (const float*)scratch, len_buf, chunks);
+}
+}  // namespace
+
+twm_status twm_attn_decode(void* out, const void* q, const void* k_cache, const void* v_cache, int rows, int num_heads,
+                           int num_kv_heads, int head_dim, const int* len_buf, int max_seq, void* scratch,
+                           size_t scratch_bytes, int flags, void* stream)
+{
+    return attn_decode_common(out, q, const_cast<void*>(k_cache), const_cast<void*>(v_cache), rows, num_heads, num_kv_heads,
+                              head_dim, len_buf, max_seq, scratch, scratch_bytes, nullptr, nullptr, nullptr, flags, stream);
+}
+
+twm_status twm_rope_table(float* table, const int* pos_buf, int head_dim, float rope_base, int flags, void* stream)
+{
+    if (!table || !pos_buf || head_dim < 2 || (head_dim & 1)) return TWM_EINVAL;
+    twm_status st = ensure_device(nullptr);
+    if (st != TWM_OK) return st;
+    return launch_op("twm_rope_table", twm::ops::rope_table_kernel, dim3((head_dim / 2 + 255) / 256), dim3(256), 0, flags, stream,
+                     table, pos_buf, head_dim, rope_base);
+}
+
+twm_status twm_attn_decode_rope(void* out, const void* qkv, const float* bias, const float* rope_table, void* k_cache,
+                                void* v_cache, int rows, int num_heads, int num_kv_heads, int head_dim, const int* pos_buf,
+                                const int* len_buf, int max_seq, void* scratch, size_t scratch_bytes, int flags, void* stream)
+{
+    if (!rope_table || !pos_buf) return TWM_EINVAL;
+    return attn_decode_common(out, qkv, k_cache, v_cache, rows, num_heads, num_kv_heads, head_dim, len_buf, max_seq, scratch,
+                              scratch_bytes, bias, rope_table, pos_buf, flags, stream);
 }
 
 twm_status twm_silu_mul(void* act, const void* gate_up, int rows, int ffn, int flags, void* stream)

@@ -117,7 +117,7 @@ class Q4DecodeBuffers:
         self.x = torch.zeros(cfg.hidden, dtype=f32, device=dev)                  # residual stream
         self.normed = torch.zeros(cfg.hidden, dtype=f16, device=dev)
         self.qkv = torch.zeros(cfg.q_dim + 2 * cfg.kv_dim, dtype=f16, device=dev)
-        self.q = torch.zeros(cfg.q_dim, dtype=f16, device=dev)
+        self.rope_table = torch.zeros(cfg.head_dim, dtype=torch.float32, device=dev)      # cos | sin of the step's position
         self.attn = torch.zeros(cfg.q_dim, dtype=f16, device=dev)
         self.gate_up = torch.zeros(2 * cfg.ffn, dtype=f16, device=dev)
         self.logits = torch.zeros(cfg.vocab, dtype=f32, device=dev)
@@ -198,20 +198,22 @@ class QuantizedGenerationEngine:
             pending.append(args)
             return lambda: check(lib.twm_gemm_w4a16(C.byref(args), stream_ptr), "twm_gemm_w4a16")
 
+        # cos/sin of this step's position, once for all layers
+        ops.append(("rope_table", 1, lambda: check(lib.twm_rope_table(b.rope_table.data_ptr(), b.pos.data_ptr(), cfg.head_dim,
+                                                                      cfg.rope_theta, fl, stream_ptr), "twm_rope_table")))
         ops.append(("embedding", 1, lambda: check(lib.twm_embed(b.x.data_ptr(), self.model.embed.data_ptr(), b.token.data_ptr(),
                                                                  1, cfg.hidden, fl, stream_ptr), "twm_embed")))
         for li, lw in enumerate(self.model.layers):
             ops.append(("attn_rmsnorm", 1, lambda lw=lw: check(lib.twm_rmsnorm(
                 b.normed.data_ptr(), b.x.data_ptr(), lw.attn_norm.data_ptr(), 1, cfg.hidden, cfg.eps, fl, stream_ptr), "twm_rmsnorm")))
             ops.append(("qkv_gemm", 1, gemm(b.normed, lw.wqkv, b.qkv, cfg.q_dim + 2 * cfg.kv_dim, cfg.hidden)))
-            ops.append(("rope_kv_append", 1, lambda li=li, lw=lw: check(lib.twm_rope_append(
-                b.q.data_ptr(), b.k_cache[li].data_ptr(), b.v_cache[li].data_ptr(), b.qkv.data_ptr(),
-                lw.bqkv.data_ptr() if lw.bqkv is not None else None, 1, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim,
-                b.pos.data_ptr(), cfg.max_seq, cfg.rope_theta, fl, stream_ptr), "twm_rope_append")))
-            ops.append(("attention", 2, lambda li=li: check(lib.twm_attn_decode(
-                b.attn.data_ptr(), b.q.data_ptr(), b.k_cache[li].data_ptr(), b.v_cache[li].data_ptr(), 1, cfg.num_heads,
-                cfg.num_kv_heads, cfg.head_dim, b.cache_len.data_ptr(), cfg.max_seq, b.attn_scratch.data_ptr(),
-                b.attn_scratch.numel(), fl, stream_ptr), "twm_attn_decode")))
+            # bias + RoPE on q and k, the KV append and the attention itself: the attention kernel takes the fused
+            # QKV output (fused_bias_rope_append_device_pos + decode_attention_flash_device_len, generate.rs:2164-2178)
+            ops.append(("attention", 2, lambda li=li, lw=lw: check(lib.twm_attn_decode_rope(
+                b.attn.data_ptr(), b.qkv.data_ptr(), lw.bqkv.data_ptr() if lw.bqkv is not None else None,
+                b.rope_table.data_ptr(), b.k_cache[li].data_ptr(), b.v_cache[li].data_ptr(), 1, cfg.num_heads,
+                cfg.num_kv_heads, cfg.head_dim, b.pos.data_ptr(), b.cache_len.data_ptr(), cfg.max_seq,
+                b.attn_scratch.data_ptr(), b.attn_scratch.numel(), fl, stream_ptr), "twm_attn_decode_rope")))
             ops.append(("out_gemm", 1, gemm(b.attn, lw.wo, b.x, cfg.hidden, cfg.q_dim, accumulate=True)))          # x += o(attn)
             ops.append(("ffn_rmsnorm", 1, lambda lw=lw: check(lib.twm_rmsnorm(
                 b.normed.data_ptr(), b.x.data_ptr(), lw.ffn_norm.data_ptr(), 1, cfg.hidden, cfg.eps, fl, stream_ptr), "twm_rmsnorm")))
@@ -272,8 +274,7 @@ class QuantizedGenerationEngine:
             torch.cuda.synchronize()
         per_step = {k: v / steps for k, v in acc.items()}
         total = sum(per_step.values())
-        layered = {"attn_rmsnorm", "qkv_gemm", "rope_kv_append", "attention", "out_gemm", "ffn_rmsnorm", "gate_up_gemm",
-                   "down_gemm"}
+        layered = {"attn_rmsnorm", "qkv_gemm", "attention", "out_gemm", "ffn_rmsnorm", "gate_up_gemm", "down_gemm"}
         nl = max(len(self.model.layers), 1)
         table = {k: {"us": round(v, 1), "us_per_layer": round(v / nl, 2) if k in layered else None,
                      "pct": round(100.0 * v / total, 1)} for k, v in per_step.items()}

@@ -216,7 +216,7 @@ class TPDecodeStack:
         self.part = torch.zeros((m, h), dtype=f32, device=dev)          # row-parallel partial, all-reduced in place
         self.normed = torch.zeros((m, h), dtype=f16, device=dev)
         self.qkv = torch.zeros((m, spec.n_qkv), dtype=f16, device=dev)
-        self.q = torch.zeros((m, hq * hd), dtype=f16, device=dev)
+        self.rope_table = torch.zeros(hd, dtype=torch.float32, device=dev)       # cos | sin of the step's position
         self.attn = torch.zeros((m, hq * hd), dtype=f16, device=dev)
         self.gate_up = torch.zeros((m, spec.n_gu), dtype=f16, device=dev)
         self.act = torch.zeros((m, spec.n_gu // 2), dtype=f16, device=dev)
@@ -280,15 +280,17 @@ class TPDecodeStack:
             self._join_and_norm(self.normed.data_ptr(), lw.attn_norm.data_ptr(), stream_ptr)
         self._gemm(self.normed, lw.wqkv, self.qkv, self.spec.n_qkv, cfg.hidden, stream_ptr,            # column-parallel
                    then=(lw.wo, cfg.hidden, self.hq * hd))
-        check(lib.twm_rope_append(self.q.data_ptr(), self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(),
-                                  self.qkv.data_ptr(), lw.bqkv.data_ptr() if lw.bqkv is not None else None, m,
-                                  self.hq, self.hk, hd, self.pos.data_ptr(), cfg.max_seq, cfg.rope_theta, fl,
-                                  stream_ptr), "twm_rope_append")
-        check(lib.twm_attn_decode(self.attn.data_ptr(), self.q.data_ptr(), self.k_cache[li].data_ptr(),
-                                  self.v_cache[li].data_ptr(), m, self.hq, self.hk, hd, self.cache_len.data_ptr(),
-                                  cfg.max_seq, self.attn_scratch.data_ptr(), self.attn_scratch.numel(), fl,
-                                  stream_ptr), "twm_attn_decode")
-        self.launches += 4
+        if li == 0:      # cos/sin of the step's position, once for all layers
+            check(lib.twm_rope_table(self.rope_table.data_ptr(), self.pos.data_ptr(), hd, cfg.rope_theta, fl, stream_ptr),
+                  "twm_rope_table")
+            self.launches += 1
+        check(lib.twm_attn_decode_rope(self.attn.data_ptr(), self.qkv.data_ptr(),
+                                       lw.bqkv.data_ptr() if lw.bqkv is not None else None, self.rope_table.data_ptr(),
+                                       self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(), m, self.hq, self.hk, hd,
+                                       self.pos.data_ptr(), self.cache_len.data_ptr(), cfg.max_seq,
+                                       self.attn_scratch.data_ptr(), self.attn_scratch.numel(), fl, stream_ptr),
+              "twm_attn_decode_rope")
+        self.launches += 3
         self._gemm(self.attn, lw.wo, self.part, cfg.hidden, self.hq * hd, stream_ptr, push=True,        # row-parallel
                    then=(lw.wgu, self.spec.n_gu, cfg.hidden))
 

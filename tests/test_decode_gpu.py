@@ -253,6 +253,53 @@ def test_attention_against_float64(length, heads, kv_heads, rows):
     assert q.device_error() == 0
 
 
+@pytest.mark.parametrize("pos", [0, 31, 32, 100, 511])
+@pytest.mark.parametrize("heads,kv_heads,rows,with_bias", [(28, 4, 1, True), (8, 8, 2, False), (16, 2, 3, True)])
+def test_attention_with_fused_rope_equals_the_two_passes(pos, heads, kv_heads, rows, with_bias):
+    """twm_rope_table + twm_attn_decode_rope against twm_rope_append + twm_attn_decode on the same
+    fused QKV rows: the attention output and both caches bit for bit (position at the start, at the
+    end and in the middle of a 32-token chunk, at the end of the cache, with the length covering the
+    new token and one token short of it)."""
+    lib = _lib.lib()
+    hd, max_seq, base = 128, 512, 1e6
+    kv_dim = kv_heads * hd
+    g = torch.Generator(device="cuda").manual_seed(pos * 7 + heads)
+    qkv = torch.randn((rows, (heads + 2 * kv_heads) * hd), generator=g, device="cuda").half()
+    bias = torch.randn((heads + 2 * kv_heads) * hd, generator=g, device="cuda") if with_bias else None
+    k0 = torch.randn((rows, max_seq, kv_dim), generator=g, device="cuda").half()
+    v0 = torch.randn((rows, max_seq, kv_dim), generator=g, device="cuda").half()
+    pos_buf = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    sp = torch.cuda.current_stream().cuda_stream
+    bias_ptr = bias.data_ptr() if bias is not None else None
+    for length in (pos + 1, pos):
+        if length < 1:
+            continue
+        len_buf = torch.tensor([length], dtype=torch.int32, device="cuda")
+        scratch = torch.zeros(lib.twm_attn_scratch_bytes(rows, heads, hd, max_seq), dtype=torch.uint8, device="cuda")
+        # two passes
+        ka, va = k0.clone(), v0.clone()
+        qa = torch.zeros((rows, heads * hd), dtype=torch.float16, device="cuda")
+        out_a = torch.full((rows, heads * hd), float("nan"), dtype=torch.float16, device="cuda")
+        _lib.check(lib.twm_rope_append(qa.data_ptr(), ka.data_ptr(), va.data_ptr(), qkv.data_ptr(), bias_ptr, rows, heads,
+                                       kv_heads, hd, pos_buf.data_ptr(), max_seq, base, 0, sp), "twm_rope_append")
+        _lib.check(lib.twm_attn_decode(out_a.data_ptr(), qa.data_ptr(), ka.data_ptr(), va.data_ptr(), rows, heads, kv_heads, hd,
+                                       len_buf.data_ptr(), max_seq, scratch.data_ptr(), scratch.numel(), 0, sp), "twm_attn_decode")
+        # one pass
+        kb, vb = k0.clone(), v0.clone()
+        table = torch.zeros(hd, dtype=torch.float32, device="cuda")
+        out_b = torch.full((rows, heads * hd), float("nan"), dtype=torch.float16, device="cuda")
+        _lib.check(lib.twm_rope_table(table.data_ptr(), pos_buf.data_ptr(), hd, base, _lib.TWM_FLAG_PDL, sp), "twm_rope_table")
+        _lib.check(lib.twm_attn_decode_rope(out_b.data_ptr(), qkv.data_ptr(), bias_ptr, table.data_ptr(), kb.data_ptr(),
+                                            vb.data_ptr(), rows, heads, kv_heads, hd, pos_buf.data_ptr(), len_buf.data_ptr(),
+                                            max_seq, scratch.data_ptr(), scratch.numel(), _lib.TWM_FLAG_PDL, sp),
+                   "twm_attn_decode_rope")
+        torch.cuda.synchronize()
+        assert torch.equal(ka, kb) and torch.equal(va, vb)
+        assert torch.equal(out_a.view(torch.int16), out_b.view(torch.int16))
+        assert not torch.equal(ka, k0)                       # the row was appended
+    assert q.device_error() == 0
+
+
 def test_q4_lm_head_option():
     """The LM head as a TW-Marlin GEMM inside the step (forward_lm_head_tw_marlin,
     generate.rs:1750-1761): logits equal the oracle's W4A16 product of the step's final normed
