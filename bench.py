@@ -723,7 +723,7 @@ def _tp_body(args, torch, dist, world, rank, local_rank, device, state):
 
     # generous limit for the consumer's wait on the peers (the ranks are aligned on the device before
     # every phase; the limit only matters if a rank dies)
-    comm = tp.PeerComm.distributed(2 * cfg.hidden, wait_ms=10000.0)
+    comm = tp.PeerComm.distributed(32 * cfg.hidden, wait_ms=10000.0)
 
     # ---- exactness of the fused all-reduce: x after the first exchange against the rank-order sum of
     # the gathered partials, bit for bit (the order twm_allreduce_add_rmsnorm adds in)
@@ -763,7 +763,7 @@ def _tp_body(args, torch, dist, world, rank, local_rank, device, state):
     # (rows, collective): "fused" = the row-parallel GEMM epilogues store their FP32 partials into every
     # rank's receive buffer over NVLink and the add+RMSNorm kernel sums them (no collective launch);
     # "nccl" = ncclAllReduce between the GEMM and the add+RMSNorm kernel.
-    for rows, coll in ((1, "fused"), (1, "nccl"), (32, "nccl")):
+    for rows, coll in ((1, "fused"), (1, "nccl"), (32, "fused"), (32, "nccl")):
         key = f"m{rows}_{coll}"
         state["phase"] = f"{key}: set-up"
         stack = tp.TPDecodeStack(cfg, spec, layers, rows, device, all_reduce=lambda t: dist.all_reduce(t),

@@ -130,9 +130,10 @@ typedef struct twm_gemm_args {
     int expert_idx;
     /* Tensor-parallel row shard: when comm != NULL the FP32 result is not stored to `c` but pushed
      * into every rank's receive buffer (plain stores over NVLink into the peer's own memory, tile
-     * by tile as the tiles finish), and the grid's last CTA raises the arrival flags.  The sum is
-     * taken by twm_allreduce_add_rmsnorm on each rank.  M <= 2 (the plan must be one K slice per tile or
-     * a cluster reduce), FP16 activations, streaming MMA kernel. */
+     * by tile as the tiles finish), and the grid's last storing CTA raises the arrival flags.  The
+     * sum is taken by twm_allreduce_add_rmsnorm on each rank.  FP16 activations, M <= 64: one or two
+     * rows run on the streaming MMA kernel (one K slice per tile or a cluster reduce), more rows on
+     * the narrow tcgen05 kernel (workspace required). */
     const twm_comm* comm;
     /* What the activation rows hold: TWM_A_PLAIN (0) the activations; TWM_A_SILU_MUL / TWM_A_GEGLU: the
      * fused [gate | up] output of the preceding GEMM (2K f16 per row, up at column K, lda >= 2K), and the

@@ -263,4 +263,32 @@ struct GemmParams {
     alignas(64) CUtensorMap act_map;
 };
 
+// ---- row-parallel output pushed to the tensor-parallel peers (GemmParams::n_peers != 0) ----
+// One value of the FP32 result, element `off` of the [M, ldc] output: a plain store into every
+// peer's receive slot for operation `seq` (each peer's own memory; this rank's own slot included).
+__device__ __forceinline__ void comm_store(const GemmParams& p, unsigned int seq, size_t off, float v)
+{
+    const size_t slot = ((size_t)(seq & 1u) * p.n_peers + p.peer_rank) * p.peer_slot_elems + off;
+    for (int s = 0; s < p.n_peers; ++s) p.peer_data[s][slot] = v;
+}
+
+// After a CTA's stores (if any): hand them to the grid's last storing CTA and, there, tell every
+// peer that this rank's partial for operation `seq` is complete.  Called by ONE thread of each
+// storing CTA after a CTA-wide barrier: the barrier orders the CTA's stores before this thread and
+// its fence is cumulative over them (a fence by every thread would cost a link round trip each).
+// The CTAs hand over at GPU scope (fence + relaxed atomic on this GPU's counter; relaxed atomic +
+// fence on the other side); the last CTA's fence, at system scope, is also the release for its
+// flag stores, which then go out back to back: a st.release per peer would wait for the previous
+// flag's acknowledgement each time, one link round trip per peer.
+__device__ __forceinline__ void comm_cta_done(const GemmParams& p, unsigned int seq, unsigned int total)
+{
+    fence_acq_rel_gpu();
+    if (atomicAdd(&p.comm_state[1], 1u) == total - 1) {
+        fence_acq_rel_sys();
+        atomicExch(&p.comm_state[1], 0u);
+        for (int s = 0; s < p.n_peers; ++s)
+            st_relaxed_sys_u32(p.peer_flags[s] + ((seq & 1u) * p.n_peers + p.peer_rank) * 8, seq + 1u);
+    }
+}
+
 }  // namespace twm

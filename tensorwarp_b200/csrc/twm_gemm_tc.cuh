@@ -475,8 +475,11 @@ gemm_kernel(const __grid_constant__ GemmParams p)
         }
         ok = ok && (*abort_flag == 0);
 
+        // tensor-parallel row shard: the FP32 result goes to every peer's receive slot instead of C
+        const unsigned int comm_seq = p.n_peers ? ld_volatile_u32(p.comm_state) : 0u;
         auto store_c = [&](int m, float vv) {
             const size_t off = (size_t)m * p.ldc + n;
+            if (p.n_peers) { comm_store(p, comm_seq, off, vv); return; }
             if (p.c_is_f16) {
                 __half* cp = reinterpret_cast<__half*>(p.c);
                 if (p.accumulate) vv += __half2float(cp[off]);
@@ -518,6 +521,13 @@ gemm_kernel(const __grid_constant__ GemmParams p)
                 }
                 if (tid == WARP_READ0 * 32) atomicExch(&p.ws_counters[blockIdx.x], 0u);
             }
+        }
+        // the CTAs that stored a tile (every CTA without K slices, the last arriver of each tile with them)
+        // count themselves; the last of them raises the peers' flags (also after an expired wait, so that
+        // the peers' consumers do not wait for this rank in vain: the error word says the step is void)
+        if (p.n_peers && (p.splits == 1 || sm.is_last)) {
+            named_bar_sync(3, EPI_THREADS);
+            if (tid == WARP_READ0 * 32) comm_cta_done(p, comm_seq, gridDim.x);
         }
     }
 

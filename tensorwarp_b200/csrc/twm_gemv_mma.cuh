@@ -468,9 +468,7 @@ gemv_kernel(const __grid_constant__ GemmParams p)
         if (m >= p.M || n >= p.N) return;
         const size_t off = (size_t)m * p.ldc + n + c_slot_off;
         if (p.n_peers) {
-            // plain stores into every peer's receive slot (its own GPU's memory), this rank's own included
-            const size_t slot = ((size_t)(comm_seq & 1u) * p.n_peers + p.peer_rank) * p.peer_slot_elems + off;
-            for (int s = 0; s < p.n_peers; ++s) p.peer_data[s][slot] = v;
+            comm_store(p, comm_seq, off, v);
             return;
         }
         if (p.c_is_f16) {
@@ -481,25 +479,6 @@ gemv_kernel(const __grid_constant__ GemmParams p)
             float* cp = reinterpret_cast<float*>(p.c);
             if (p.accumulate) v += cp[off];
             cp[off] = v;
-        }
-    };
-
-    // After a CTA's stores (if any): make them visible system-wide and count the CTA; the last CTA
-    // of the grid tells every peer that this rank's partial for operation comm_seq is complete.
-    // Called by ONE thread of each storing CTA after a CTA-wide barrier: the barrier orders the
-    // CTA's stores before this thread and its system-scope fence is cumulative over them (a fence by
-    // every thread would cost a link round trip each).  The CTAs hand their stores to the last CTA
-    // at GPU scope (fence + relaxed atomic on this GPU's counter; relaxed atomic + fence on the
-    // other side); the last CTA's fence, at system scope, is also the release for its flag
-    // stores, which then go out back to back: a st.release per peer would wait for the previous
-    // flag's acknowledgement each time, one link round trip per peer.
-    auto comm_cta_done = [&](unsigned int total) {
-        fence_acq_rel_gpu();
-        if (atomicAdd(&p.comm_state[1], 1u) == total - 1) {
-            fence_acq_rel_sys();
-            atomicExch(&p.comm_state[1], 0u);
-            for (int s = 0; s < p.n_peers; ++s)
-                st_relaxed_sys_u32(p.peer_flags[s] + ((comm_seq & 1u) * p.n_peers + p.peer_rank) * 8, comm_seq + 1u);
         }
     };
 
@@ -529,7 +508,7 @@ gemv_kernel(const __grid_constant__ GemmParams p)
         }
         if (p.n_peers && rank == 0) {       // only the cluster leaders store
             __syncthreads();
-            if (tid == 0) comm_cta_done(gridDim.x);
+            if (tid == 0) comm_cta_done(p, comm_seq, gridDim.x);
         }
         return;
     }
@@ -543,7 +522,7 @@ gemv_kernel(const __grid_constant__ GemmParams p)
         }
         if (p.n_peers) {
             named_bar_sync(1, CONSUMERS);
-            if (tid == 0) comm_cta_done(gridDim.x * gridDim.y);
+            if (tid == 0) comm_cta_done(p, comm_seq, gridDim.x * gridDim.y);
         }
         return;
     }

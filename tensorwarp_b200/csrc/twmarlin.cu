@@ -259,7 +259,9 @@ int resolve_kernel(const twm_gemm_args* a)
                              a->splits_override);
     // five to eight rows: the tcgen05 kernel when the caller's workspace holds its pre-pass
     // output, else the streaming kernel (which needs less or none)
-    if (kernel == TWM_KERNEL_TC && a->M <= 8 && a->comm) kernel = TWM_KERNEL_MMA;    // the peer push lives in the streaming kernels
+    // pushing to tensor-parallel peers: the streaming kernel's cluster leaders push one or two rows, the
+    // narrow tcgen05 kernel's read-back warps up to 64
+    if (a->comm && a->a_dtype == TWM_F16) return a->M <= twm::mma::CLUSTER_ROWS ? TWM_KERNEL_MMA : TWM_KERNEL_TC;
     if (kernel == TWM_KERNEL_TC && a->M <= 8) {
         twm_plan_t pl;
         if (twm_plan(a->M, a->N, a->K, a->group_size, kDefaultSms, a->splits_override, TWM_KERNEL_TC, &pl) != TWM_OK ||
@@ -590,7 +592,8 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
         // pushing the result to tensor-parallel peers: streaming MMA kernel, no workspace-based split
         const twm_comm* cm = a->comm;
         const bool mma_ok = kernel == TWM_KERNEL_MMA && a->M <= twm::mma::CLUSTER_ROWS && (pl.splits == 1 || pl.cluster_reduce);
-        if (!mma_ok) return TWM_EINVAL;
+        const bool tc_ok = kernel == TWM_KERNEL_TC && a->M <= 64;           // one launch: one operation of the flag protocol
+        if (!mma_ok && !tc_ok) return TWM_EINVAL;
         if (cm->n_ranks < 1 || cm->n_ranks > 8 || cm->rank < 0 || cm->rank >= cm->n_ranks || !cm->state) return TWM_EINVAL;
         if (cm->slot_elems < (long)a->M * a->ldc) return TWM_EINVAL;
     }

@@ -200,10 +200,10 @@ class TPDecodeStack:
         self.cfg, self.spec, self.layers, self.rows = cfg, spec, layers, rows
         self.device = torch.device(device)
         self.all_reduce = all_reduce
-        # With `comm` (and at most two rows) the row-parallel GEMMs push their FP32 result straight
-        # into every rank's receive buffer and the following add + RMSNorm kernel takes the sum:
-        # no collective call, no extra launch.  Otherwise `all_reduce` (NCCL) runs on `part`.
-        self.comm = comm if (comm is not None and rows <= 2) else None
+        # With `comm` (and at most 64 rows, one GEMM launch) the row-parallel GEMMs push their FP32 result
+        # straight into every rank's receive buffer and the following add + RMSNorm kernel takes the
+        # sum: no collective call, no extra launch.  Otherwise `all_reduce` (NCCL) runs on `part`.
+        self.comm = comm if (comm is not None and rows <= 64) else None
         if self.comm is not None and self.comm.slot_elems < rows * cfg.hidden:
             raise ValueError("comm slots are smaller than rows * hidden")
         self.flags = _lib.TWM_FLAG_PDL if use_pdl else 0

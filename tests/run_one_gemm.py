@@ -5,8 +5,8 @@
 Seeded random weights (quantised on the device) and FP16 N(0,1) activations; every launch goes
 through tensorwarp_b200.quantize.gemm_tw_marlin with programmatic dependent launch, as in the
 benchmarks.  Prints the mean device time per GEMM (CUDA events) and the library's error word.
-`--tp-layers L --tp N` instead runs L layers of the tensor-parallel decode stack at degree N with
-every rank emulated on this one GPU (ranks enqueued one after another, so the producers of an
+`--tp-layers L --tp N` instead runs L layers of the tensor-parallel decode stack at degree N
+(`--m` rows = sequences decoding in lock step) with every rank emulated on this one GPU (ranks enqueued one after another, so the producers of an
 all-reduce have finished before its consumer starts)."""
 import argparse
 import os
@@ -54,14 +54,14 @@ def tp_layers(args) -> None:
     base = tp.LLAMA3_70B
     cfg = type(base)(**{**base.__dict__, "max_seq": args.kv + 8, "layers": args.tp_layers})
     dev = "cuda"
-    comms = tp.PeerComm.local_group(args.tp, cfg.hidden)
+    comms = tp.PeerComm.local_group(args.tp, args.m * cfg.hidden)
     stacks = []
     for r in range(args.tp):
         spec = tp.shard_spec(cfg, args.tp, r)
         layers = [tp.random_shard_layer(cfg, spec, li, dev, args.seed) for li in range(cfg.layers)]
-        st = tp.TPDecodeStack(cfg, spec, layers, 1, dev, all_reduce=lambda t: None, comm=comms[r])
+        st = tp.TPDecodeStack(cfg, spec, layers, args.m, dev, all_reduce=lambda t: None, comm=comms[r])
         st.prefill_random_kv(args.kv)
-        st.x.copy_(torch.randn((1, cfg.hidden), generator=torch.Generator().manual_seed(args.seed)).to(dev))
+        st.x.copy_(torch.randn((args.m, cfg.hidden), generator=torch.Generator().manual_seed(args.seed)).to(dev))
         stacks.append(st)
     sp = torch.cuda.current_stream().cuda_stream
     for _ in range(2):                       # two passes: the second one is warm
@@ -74,7 +74,7 @@ def tp_layers(args) -> None:
             st.finish(sp)
         torch.cuda.synchronize()
     finite = all(bool(torch.isfinite(st.x).all()) for st in stacks)
-    print(f"tp={args.tp}, {cfg.layers} layers, KV {args.kv}: two passes over all ranks on one GPU, "
+    print(f"tp={args.tp}, {cfg.layers} layers, {args.m} row(s), KV {args.kv}: two passes over all ranks on one GPU, "
           f"finite={finite}, error word {q.device_error():#x}")
     for c in comms:
         c.close()

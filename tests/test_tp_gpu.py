@@ -80,7 +80,7 @@ def _run(cfg, full, degree, rows, x0, kv_len, fused=False):
     return out
 
 
-@pytest.mark.parametrize("rows", [1, 2, 3])
+@pytest.mark.parametrize("rows", [1, 2, 3, 9])
 def test_sharded_stack_equals_unsharded(rows):
     cfg = CFG
     full = _full_layers(cfg, 21)
@@ -93,19 +93,20 @@ def test_sharded_stack_equals_unsharded(rows):
             assert np.array_equal(o, outs[0])                 # every rank ends with the same activations
         err = float(np.max(np.abs(outs[0] - ref))) / rms
         assert err < 2e-3, (degree, err)                      # FP32 partials, different summation order only
-        if rows <= 2:
-            # the fused path: GEMM epilogues push into the peers' buffers, add+RMSNorm takes the sum
-            fused = _run(cfg, full, degree, rows, x0, 100, fused=True)
-            for o in fused[1:]:
-                assert np.array_equal(o, fused[0])
-            assert float(np.max(np.abs(fused[0] - ref))) / rms < 2e-3, degree
+        # the fused path: GEMM epilogues push into the peers' buffers, add+RMSNorm takes the sum
+        fused = _run(cfg, full, degree, rows, x0, 100, fused=True)
+        for o in fused[1:]:
+            assert np.array_equal(o, fused[0])
+        assert float(np.max(np.abs(fused[0] - ref))) / rms < 2e-3, degree
 
 
-@pytest.mark.parametrize("kernel,rows,n", [(3, 1, 3072), (3, 2, 3072), (3, 1, 8192), (3, 2, 16384), (3, 1, 512)])
-def test_row_parallel_push_and_sum(kernel, rows, n):
-    """The row-parallel GEMM with `comm` on the streaming MMA kernel, then the consumer: every rank's
-    x + sum over ranks equals x + the unsharded GEMM, and all ranks hold the same bits.  Run twice
-    in a row: the sequence number alternates between the two buffer sets."""
+@pytest.mark.parametrize("kernel,rows,n,splits", [(3, 1, 3072, 0), (3, 2, 3072, 0), (3, 1, 8192, 0), (3, 2, 16384, 0), (3, 1, 512, 0),
+                                                  (2, 5, 3072, 0), (2, 32, 8192, 0), (2, 64, 512, 0), (2, 32, 3072, 3)])
+def test_row_parallel_push_and_sum(kernel, rows, n, splits):
+    """The row-parallel GEMM with `comm` on the streaming MMA kernel (one or two rows) and on the narrow
+    tcgen05 kernel (up to 64, also with K slices through the workspace), then the consumer: every
+    rank's x + sum over ranks equals x + the unsharded GEMM, and all ranks hold the same bits.  Run
+    twice in a row: the sequence number alternates between the two buffer sets."""
     import ctypes as C
     from tensorwarp_b200 import _lib
     lib = _lib.lib()
@@ -115,7 +116,8 @@ def test_row_parallel_push_and_sum(kernel, rows, n):
     packed, scales = q.quantize_f32_to_tw_marlin(w, k, n, group)
     a = torch.randn((rows, k), generator=gen, device="cuda").half()
     full = torch.zeros((rows, n), device="cuda")
-    q.gemm_tw_marlin(a, packed, scales, full, rows, n, k, group_size=group, workspace=q.Workspace(1 << 22))
+    ws = q.Workspace(64 << 20)
+    q.gemm_tw_marlin(a, packed, scales, full, rows, n, k, group_size=group, workspace=ws)
     comms = tp.PeerComm.local_group(degree, rows * n)
     gamma = torch.ones(n, device="cuda")
     stream = torch.cuda.current_stream().cuda_stream
@@ -130,7 +132,8 @@ def test_row_parallel_push_and_sum(kernel, rows, n):
     for r in range(degree):
         p_r, s_r, a_r = shards[r]
         part = torch.zeros((rows, n), device="cuda")
-        q.gemm_tw_marlin(a_r, p_r, s_r, part, rows, n, kb, group_size=group, kernel_override=kernel)
+        q.gemm_tw_marlin(a_r, p_r, s_r, part, rows, n, kb, group_size=group, kernel_override=kernel, workspace=ws,
+                         splits_override=splits)
         parts.append(part)
     for step in range(2):
         xs = [torch.full((rows, n), 0.5 * (step + 1), device="cuda") for _ in range(degree)]
@@ -139,7 +142,8 @@ def test_row_parallel_push_and_sum(kernel, rows, n):
             p_r, s_r, a_r = shards[r]
             args = _lib.GemmArgs(M=rows, N=n, K=kb, group_size=group, a_dtype=_lib.TWM_F16, c_dtype=_lib.TWM_F32,
                                  a=a_r.data_ptr(), lda=kb, packed=p_r.data_ptr(), scales=s_r.data_ptr(),
-                                 c=dummy.data_ptr(), ldc=n, kernel_override=kernel, comm=comms[r].ptr)
+                                 c=dummy.data_ptr(), ldc=n, kernel_override=kernel, comm=comms[r].ptr,
+                                 workspace=ws.ptr, workspace_bytes=ws.nbytes, splits_override=splits)
             _lib.check(lib.twm_gemm_w4a16(C.byref(args), stream), "twm_gemm_w4a16")
         ys = [torch.zeros((rows, n), device="cuda", dtype=torch.float16) for _ in range(degree)]
         for r in range(degree):                         # ... then every rank's consumer
