@@ -381,7 +381,11 @@ rope_append_kernel(__half* __restrict__ q_out, __half* __restrict__ k_cache, __h
 // About 28 warp instructions per (token, head), staging included (1.64 M per call at 2049 tokens x
 // 28 heads); the earlier one-token-per-warp loop with a shuffle reduction per score needed 87
 // (5.0 M) and 123 registers.  Writes (max, sum, unnormalised o[128]) per (q head, chunk).  The
-// sequence length is read from the device (len_buf[0]), the grid covers max_seq.  Reference:
+// sequence length is read from the device (len_buf[0]), the grid covers max_seq.  With many
+// sequences in lock step the grid would be tens of waves of these small CTAs; the host then gives
+// each CTA `span` consecutive chunks, which it walks with a running (max, sum, o) and with the next
+// chunk's loads in flight during the arithmetic, and writes one partial per span (span = 1 gives
+// the single-chunk result bit for bit).  Reference:
 // warp_flash_decode_chunk_dl, crates/kernels/src/kv_cache.rs:951-1076.
 constexpr int ATT_CHUNK = 32;       // tokens per CTA = lanes of a warp
 constexpr int ATT_MAX_GROUP = 8;      // q heads per kv head, at most
@@ -395,9 +399,9 @@ constexpr int ATT_MAX_GROUP = 8;      // q heads per kv head, at most
 // (fused_bias_rope_append_device_pos, ops.rs:2601-2680) disappears, same bits.
 template <int HEAD_DIM, bool ROPE>
 __global__ void __launch_bounds__(ATT_MAX_GROUP * 32)
-attn_chunk_kernel(float* __restrict__ part /* [heads][chunks][HEAD_DIM + 2] */, const __half* __restrict__ q,
+attn_chunk_kernel(float* __restrict__ part /* [heads][parts][HEAD_DIM + 2] */, const __half* __restrict__ q,
                   __half* k_cache, __half* v_cache, int num_heads, int num_kv_heads, const int* __restrict__ len_buf,
-                  int max_chunks, int max_seq, const float* __restrict__ bias, const float* __restrict__ rope,
+                  int max_parts, int span, int max_seq, const float* __restrict__ bias, const float* __restrict__ rope,
                   const int* __restrict__ pos_buf)
 {
     static_assert(HEAD_DIM == 128, "lane owns 4 of 128 dims");
@@ -407,20 +411,20 @@ attn_chunk_kernel(float* __restrict__ part /* [heads][chunks][HEAD_DIM + 2] */, 
     constexpr int PER_ROW = ROW_BYTES / 16;                 // 16
     pdl_launch_dependents();
     pdl_wait_prior_grids();
-    const int chunk = blockIdx.x, kvh = blockIdx.y;
+    const int kvh = blockIdx.y;
     {   // one sequence per grid z: its own q (or fused q|k|v row), cache and partials
         const size_t row = blockIdx.z;
         q += row * (size_t)(ROPE ? (num_heads + 2 * num_kv_heads) : num_heads) * HEAD_DIM;
         k_cache += row * (size_t)max_seq * num_kv_heads * HEAD_DIM;
         v_cache += row * (size_t)max_seq * num_kv_heads * HEAD_DIM;
-        part += row * (size_t)num_heads * max_chunks * (HEAD_DIM + 2);
+        part += row * (size_t)num_heads * max_parts * (HEAD_DIM + 2);
     }
     const int len = min(len_buf[0], max_seq);            // never past the cache
-    const int t0 = chunk * ATT_CHUNK;
+    const int chunk0 = blockIdx.x * span;                // this CTA's chunks: chunk0 .. chunk0 + span - 1
     const int group = num_heads / num_kv_heads;          // = warps of this CTA (the host launches group x 32 threads)
     const int kv_dim = num_kv_heads * HEAD_DIM;
     const int h = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float* dst = part + ((size_t)(kvh * group + h) * max_chunks + chunk) * (HEAD_DIM + 2);
+    float* dst = part + ((size_t)(kvh * group + h) * max_parts + blockIdx.x) * (HEAD_DIM + 2);
     // four dims of one head, rotated: lane l holds dims 4l .. 4l+3, its partner lane l ^ 16 the other half of the pairs
     auto rope4 = [&](int elem0, bool rotate) -> uint2 {
         const uint2 raw = *reinterpret_cast<const uint2*>(q + elem0 + lane * 4);
@@ -448,8 +452,8 @@ attn_chunk_kernel(float* __restrict__ part /* [heads][chunks][HEAD_DIM + 2] */, 
     };
     const int q_total = num_heads * HEAD_DIM;
     const int pos = ROPE ? pos_buf[0] : -1;
-    const int new_tok = pos - t0;                        // row of the new token inside this chunk, if it is in it
-    const bool has_new = ROPE && new_tok >= 0 && new_tok < ATT_CHUNK && pos < max_seq;      // CTA-uniform
+    // the new token's row, if one of this CTA's chunks holds it (CTA-uniform)
+    const bool has_new = ROPE && pos >= chunk0 * ATT_CHUNK && pos < (chunk0 + span) * ATT_CHUNK && pos < max_seq;
     uint2 k_new = make_uint2(0, 0), v_new = make_uint2(0, 0);
     if (has_new && h == 0) {                             // the new k and v rows of this kv head: into the caches
         k_new = rope4(q_total + kvh * HEAD_DIM, true);
@@ -457,95 +461,125 @@ attn_chunk_kernel(float* __restrict__ part /* [heads][chunks][HEAD_DIM + 2] */, 
         *reinterpret_cast<uint2*>(k_cache + (size_t)pos * kv_dim + kvh * HEAD_DIM + lane * 4) = k_new;
         *reinterpret_cast<uint2*>(v_cache + (size_t)pos * kv_dim + kvh * HEAD_DIM + lane * 4) = v_new;
     }
-    if (t0 >= len) {
-        // empty chunk: mark as such so the merge ignores it
+    if (chunk0 * ATT_CHUNK >= len) {
+        // nothing to attend to: mark the partial as empty so the merge ignores it
         if (lane == 0) { dst[HEAD_DIM] = -INFINITY; dst[HEAD_DIM + 1] = 0.0f; }
         return;
     }
-    const int nt = min(ATT_CHUNK, len - t0);             // tokens of this chunk (CTA-uniform)
     __shared__ __align__(16) unsigned char k_s[ATT_CHUNK * KROW];
     __shared__ __align__(16) unsigned char v_s[ATT_CHUNK * ROW_BYTES];
     __shared__ __align__(16) float q_s[ATT_MAX_GROUP][HEAD_DIM];
-    const uint2 qr = ROPE ? rope4((kvh * group + h) * HEAD_DIM, true)
-                          : *reinterpret_cast<const uint2*>(q + (size_t)(kvh * group + h) * HEAD_DIM + lane * 4);
     {
-        // K and V of the chunk: piece i is bytes [16 i, 16 i + 16) of the chunk's rows laid end to end;
-        // rows past the sequence end are zero-filled (their probability is 0, and 0 x garbage could be NaN)
-        const unsigned char* kg = reinterpret_cast<const unsigned char*>(k_cache + (size_t)t0 * kv_dim + kvh * HEAD_DIM);
-        const unsigned char* vg = reinterpret_cast<const unsigned char*>(v_cache + (size_t)t0 * kv_dim + kvh * HEAD_DIM);
-        const size_t row_stride = (size_t)kv_dim * 2;
-        constexpr int BATCH = 3;                         // 3 x 224 threads cover the 512 pieces of a 7-head group at once
-        for (int i0 = threadIdx.x; i0 < PIECES; i0 += BATCH * blockDim.x) {
-            uint4 kk[BATCH], vv[BATCH];
-#pragma unroll
-            for (int b = 0; b < BATCH; ++b) {
-                const int i = i0 + b * blockDim.x;
-                const int tok = i / PER_ROW, piece = i % PER_ROW;
-                const bool in = (i < PIECES) && (tok < nt) && !(has_new && tok == new_tok);     // the new row is not in the cache yet
-                kk[b] = in ? *reinterpret_cast<const uint4*>(kg + tok * row_stride + piece * 16) : make_uint4(0, 0, 0, 0);
-                vv[b] = in ? *reinterpret_cast<const uint4*>(vg + tok * row_stride + piece * 16) : make_uint4(0, 0, 0, 0);
-            }
-#pragma unroll
-            for (int b = 0; b < BATCH; ++b) {
-                const int i = i0 + b * blockDim.x;
-                if (i < PIECES) {
-                    const int tok = i / PER_ROW, piece = i % PER_ROW;
-                    if (has_new && tok == new_tok) continue;           // written below by warp 0
-                    *reinterpret_cast<uint4*>(k_s + tok * KROW + piece * 16) = kk[b];
-                    *reinterpret_cast<uint4*>(v_s + i * 16) = vv[b];
-                }
-            }
-        }
-    }
-    if (has_new && h == 0) {
-        *reinterpret_cast<uint2*>(k_s + new_tok * KROW + lane * 8) = k_new;
-        *reinterpret_cast<uint2*>(v_s + new_tok * ROW_BYTES + lane * 8) = v_new;
-    }
-    {
+        const uint2 qr = ROPE ? rope4((kvh * group + h) * HEAD_DIM, true)
+                              : *reinterpret_cast<const uint2*>(q + (size_t)(kvh * group + h) * HEAD_DIM + lane * 4);
         const float scale = rsqrtf((float)HEAD_DIM);
         const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&qr.x));
         const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&qr.y));
         *reinterpret_cast<float4*>(&q_s[h][lane * 4]) = make_float4(a.x * scale, a.y * scale, b.x * scale, b.y * scale);
     }
-    __syncthreads();
-    // ---- score of this lane's token ----
-    const bool valid = lane < nt;
-    float sc = 0.0f;
-    {
-        const uint4* krow = reinterpret_cast<const uint4*>(k_s + lane * KROW);
+    const size_t row_stride = (size_t)kv_dim * 2;
+    constexpr int BATCH = 3;                             // 3 x 224 threads cover the 512 pieces of a 7-head group at once
+    // With at least 171 threads one round of loads holds a whole chunk in registers: the next chunk's
+    // loads are then issued before this chunk's arithmetic (CTAs that walk several chunks).
+    const bool one_round = BATCH * (int)blockDim.x >= PIECES;
+    uint4 kk[BATCH], vv[BATCH];
+    // K and V of chunk c: piece i is bytes [16 i, 16 i + 16) of the chunk's rows laid end to end; rows past
+    // the sequence end are zero (their probability is 0, and 0 x garbage could be NaN); the new token's
+    // row is not in the cache yet
+    auto load_round = [&](int c, int i0) {
+        const int t0 = c * ATT_CHUNK;
+        const int nt = min(ATT_CHUNK, len - t0);
+        const unsigned char* kg = reinterpret_cast<const unsigned char*>(k_cache + (size_t)t0 * kv_dim + kvh * HEAD_DIM);
+        const unsigned char* vg = reinterpret_cast<const unsigned char*>(v_cache + (size_t)t0 * kv_dim + kvh * HEAD_DIM);
 #pragma unroll
-        for (int dc = 0; dc < HEAD_DIM / 8; ++dc) {
-            const uint4 kr = krow[dc];
-            const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kr.x));
-            const float2 k1 = __half22float2(*reinterpret_cast<const __half2*>(&kr.y));
-            const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&kr.z));
-            const float2 k3 = __half22float2(*reinterpret_cast<const __half2*>(&kr.w));
-            const float4 qa = *reinterpret_cast<const float4*>(&q_s[h][dc * 8]);
-            const float4 qb = *reinterpret_cast<const float4*>(&q_s[h][dc * 8 + 4]);
-            sc = fmaf(k0.x, qa.x, fmaf(k0.y, qa.y, fmaf(k1.x, qa.z, fmaf(k1.y, qa.w,
-                 fmaf(k2.x, qb.x, fmaf(k2.y, qb.y, fmaf(k3.x, qb.z, fmaf(k3.y, qb.w, sc))))))));
+        for (int b = 0; b < BATCH; ++b) {
+            const int i = i0 + b * blockDim.x;
+            const int tok = i / PER_ROW, piece = i % PER_ROW;
+            const bool in = (i < PIECES) && (tok < nt) && !(has_new && t0 + tok == pos);
+            kk[b] = in ? *reinterpret_cast<const uint4*>(kg + tok * row_stride + piece * 16) : make_uint4(0, 0, 0, 0);
+            vv[b] = in ? *reinterpret_cast<const uint4*>(vg + tok * row_stride + piece * 16) : make_uint4(0, 0, 0, 0);
         }
-    }
-    // ---- soft-max statistics of the chunk ----
-    const float sv = valid ? sc : -INFINITY;
-    const float mw = warp_max(sv);
-    const float pr = valid ? __expf(sv - mw) : 0.0f;
-    const float lw = warp_sum(pr);
-    // ---- o[dims of this lane] = sum_t p[t] * v_t ----
-    float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
-    const uint2* vcol = reinterpret_cast<const uint2*>(v_s) + lane;
+    };
+    auto store_round = [&](int c, int i0) {
+        const int t0 = c * ATT_CHUNK;
 #pragma unroll
-    for (int j = 0; j < ATT_CHUNK; ++j) {
-        const float pt = __shfl_sync(0xffffffffu, pr, j);              // 0 for tokens past the end
-        const uint2 vr = vcol[j * (ROW_BYTES / 8)];
-        const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&vr.x));
-        const float2 v1 = __half22float2(*reinterpret_cast<const __half2*>(&vr.y));
-        o0 = fmaf(pt, v0.x, o0); o1 = fmaf(pt, v0.y, o1); o2 = fmaf(pt, v1.x, o2); o3 = fmaf(pt, v1.y, o3);
+        for (int b = 0; b < BATCH; ++b) {
+            const int i = i0 + b * blockDim.x;
+            if (i < PIECES) {
+                const int tok = i / PER_ROW, piece = i % PER_ROW;
+                if (has_new && t0 + tok == pos) continue;               // written by warp 0
+                *reinterpret_cast<uint4*>(k_s + tok * KROW + piece * 16) = kk[b];
+                *reinterpret_cast<uint4*>(v_s + i * 16) = vv[b];
+            }
+        }
+    };
+    float m_run = -INFINITY, l_run = 0.0f, o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
+    if (one_round) load_round(chunk0, threadIdx.x);
+    for (int sc = 0; sc < span; ++sc) {
+        const int c = chunk0 + sc;
+        const int t0 = c * ATT_CHUNK;
+        if (t0 >= len) break;                              // CTA-uniform
+        const int nt = min(ATT_CHUNK, len - t0);           // tokens of this chunk
+        if (one_round) {
+            store_round(c, threadIdx.x);
+        } else {
+            for (int i0 = threadIdx.x; i0 < PIECES; i0 += BATCH * blockDim.x) { load_round(c, i0); store_round(c, i0); }
+        }
+        if (has_new && h == 0 && pos >= t0 && pos < t0 + ATT_CHUNK) {
+            *reinterpret_cast<uint2*>(k_s + (pos - t0) * KROW + lane * 8) = k_new;
+            *reinterpret_cast<uint2*>(v_s + (pos - t0) * ROW_BYTES + lane * 8) = v_new;
+        }
+        __syncthreads();
+        if (one_round && sc + 1 < span && (c + 1) * ATT_CHUNK < len) load_round(c + 1, threadIdx.x);
+        // ---- score of this lane's token ----
+        const bool valid = lane < nt;
+        float s_tok = 0.0f;
+        {
+            const uint4* krow = reinterpret_cast<const uint4*>(k_s + lane * KROW);
+#pragma unroll
+            for (int dc = 0; dc < HEAD_DIM / 8; ++dc) {
+                const uint4 kr = krow[dc];
+                const float2 k0 = __half22float2(*reinterpret_cast<const __half2*>(&kr.x));
+                const float2 k1 = __half22float2(*reinterpret_cast<const __half2*>(&kr.y));
+                const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&kr.z));
+                const float2 k3 = __half22float2(*reinterpret_cast<const __half2*>(&kr.w));
+                const float4 qa = *reinterpret_cast<const float4*>(&q_s[h][dc * 8]);
+                const float4 qb = *reinterpret_cast<const float4*>(&q_s[h][dc * 8 + 4]);
+                s_tok = fmaf(k0.x, qa.x, fmaf(k0.y, qa.y, fmaf(k1.x, qa.z, fmaf(k1.y, qa.w,
+                        fmaf(k2.x, qb.x, fmaf(k2.y, qb.y, fmaf(k3.x, qb.z, fmaf(k3.y, qb.w, s_tok))))))));
+            }
+        }
+        // ---- soft-max statistics of the chunk ----
+        const float sv = valid ? s_tok : -INFINITY;
+        const float mw = warp_max(sv);
+        const float pr = valid ? __expf(sv - mw) : 0.0f;
+        const float lw = warp_sum(pr);
+        // ---- o[dims of this lane] = sum_t p[t] * v_t ----
+        float c0 = 0.0f, c1 = 0.0f, c2 = 0.0f, c3 = 0.0f;
+        const uint2* vcol = reinterpret_cast<const uint2*>(v_s) + lane;
+#pragma unroll
+        for (int j = 0; j < ATT_CHUNK; ++j) {
+            const float pt = __shfl_sync(0xffffffffu, pr, j);              // 0 for tokens past the end
+            const uint2 vr = vcol[j * (ROW_BYTES / 8)];
+            const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&vr.x));
+            const float2 v1 = __half22float2(*reinterpret_cast<const __half2*>(&vr.y));
+            c0 = fmaf(pt, v0.x, c0); c1 = fmaf(pt, v0.y, c1); c2 = fmaf(pt, v1.x, c2); c3 = fmaf(pt, v1.y, c3);
+        }
+        if (sc == 0) {
+            m_run = mw; l_run = lw; o0 = c0; o1 = c1; o2 = c2; o3 = c3;
+        } else {                                           // fold this chunk into the running (max, sum, o)
+            const float m_new = fmaxf(m_run, mw);
+            const float wa = __expf(m_run - m_new), wb = __expf(mw - m_new);
+            l_run = fmaf(l_run, wa, lw * wb);
+            o0 = fmaf(o0, wa, c0 * wb); o1 = fmaf(o1, wa, c1 * wb); o2 = fmaf(o2, wa, c2 * wb); o3 = fmaf(o3, wa, c3 * wb);
+            m_run = m_new;
+        }
+        if (sc + 1 < span) __syncthreads();                // the next chunk overwrites the staged rows
     }
     // a partial is HEAD_DIM + 2 floats long, so its start is 8-byte aligned only: two float2 stores
     *reinterpret_cast<float2*>(dst + lane * 4) = make_float2(o0, o1);
     *reinterpret_cast<float2*>(dst + lane * 4 + 2) = make_float2(o2, o3);
-    if (lane == 0) { dst[HEAD_DIM] = mw; dst[HEAD_DIM + 1] = lw; }
+    if (lane == 0) { dst[HEAD_DIM] = m_run; dst[HEAD_DIM + 1] = l_run; }
 }
 
 // Pass 2: merge the chunks of one q head (log-sum-exp weights), write f16.  CTA = q head, 4 x 128
@@ -555,7 +589,7 @@ constexpr int ATT_MERGE_PARTS = 4;
 template <int HEAD_DIM>
 __global__ void __launch_bounds__(HEAD_DIM * ATT_MERGE_PARTS)
 attn_merge_kernel(__half* __restrict__ out, const float* __restrict__ part, const int* __restrict__ len_buf,
-                  int max_chunks)
+                  int max_chunks /* partials per head */, int span /* chunks per partial */)
 {
     pdl_launch_dependents();
     pdl_wait_prior_grids();
@@ -568,7 +602,7 @@ attn_merge_kernel(__half* __restrict__ out, const float* __restrict__ part, cons
     const int head = blockIdx.x, tid = threadIdx.x, d = tid % HEAD_DIM, prt = tid / HEAD_DIM;
     out += (size_t)blockIdx.y * gridDim.x * HEAD_DIM;
     part += (size_t)blockIdx.y * gridDim.x * max_chunks * STRIDE;
-    const int chunks = min(min(max_chunks, MAXC), (len_buf[0] + ATT_CHUNK - 1) / ATT_CHUNK);
+    const int chunks = min(min(max_chunks, MAXC), ((len_buf[0] + ATT_CHUNK - 1) / ATT_CHUNK + span - 1) / span);
     const float* base = part + (size_t)head * max_chunks * STRIDE;
     // every chunk's (max, sum) in one round of loads, one chunk per thread
     float mloc = -INFINITY;

@@ -1230,18 +1230,26 @@ twm_status attn_decode_common(void* out, const void* q_or_qkv, void* k_cache, vo
     if (st != TWM_OK) return st;
     const int chunks = (max_seq + twm::ops::ATT_CHUNK - 1) / twm::ops::ATT_CHUNK;
     if (chunks > 1024) return TWM_EINVAL;          // the merge pass keeps one weight per chunk in shared memory
-    const dim3 grid(chunks, num_kv_heads, rows), block(32 * (num_heads / num_kv_heads));
+    // one 32-token chunk per CTA while that is at most two waves of CTAs (four fit an SM); beyond that
+    // (many sequences in lock step) each CTA walks 2, 4 or 8 chunks
+    int sms = kDefaultSms;
+    st = ensure_device(&sms);
+    if (st != TWM_OK) return st;
+    int span = 1;
+    while (span < 8 && (long)((chunks + span - 1) / span) * num_kv_heads * rows > 2L * 4 * sms) span *= 2;
+    const int parts = (chunks + span - 1) / span;
+    const dim3 grid(parts, num_kv_heads, rows), block(32 * (num_heads / num_kv_heads));
     if (rope_table)
         st = launch_op("twm_attn_decode_rope(chunks)", twm::ops::attn_chunk_kernel<128, true>, grid, block, 0, flags, stream,
                        (float*)scratch, (const __half*)q_or_qkv, (__half*)k_cache, (__half*)v_cache, num_heads, num_kv_heads,
-                       len_buf, chunks, max_seq, bias, rope_table, pos_buf);
+                       len_buf, parts, span, max_seq, bias, rope_table, pos_buf);
     else
         st = launch_op("twm_attn_decode(chunks)", twm::ops::attn_chunk_kernel<128, false>, grid, block, 0, flags, stream,
                        (float*)scratch, (const __half*)q_or_qkv, (__half*)k_cache, (__half*)v_cache, num_heads, num_kv_heads,
-                       len_buf, chunks, max_seq, (const float*)nullptr, (const float*)nullptr, (const int*)nullptr);
+                       len_buf, parts, span, max_seq, (const float*)nullptr, (const float*)nullptr, (const int*)nullptr);
     if (st != TWM_OK) return st;
     return launch_op("twm_attn_decode(merge)", twm::ops::attn_merge_kernel<128>, dim3(num_heads, rows), dim3(128 * twm::ops::ATT_MERGE_PARTS), 0, flags,
-                     stream, (__half*)out, (const float*)scratch, len_buf, chunks);
+                     stream, (__half*)out, (const float*)scratch, len_buf, parts, span);
 }
 }  // namespace
 

@@ -253,15 +253,15 @@ def test_attention_against_float64(length, heads, kv_heads, rows):
     assert q.device_error() == 0
 
 
-@pytest.mark.parametrize("pos", [0, 31, 32, 100, 511])
+@pytest.mark.parametrize("pos,max_seq", [(0, 512), (31, 512), (32, 512), (100, 512), (511, 512), (4000, 9000), (4031, 9000)])
 @pytest.mark.parametrize("heads,kv_heads,rows,with_bias", [(28, 4, 1, True), (8, 8, 2, False), (16, 2, 3, True)])
-def test_attention_with_fused_rope_equals_the_two_passes(pos, heads, kv_heads, rows, with_bias):
+def test_attention_with_fused_rope_equals_the_two_passes(pos, max_seq, heads, kv_heads, rows, with_bias):
     """twm_rope_table + twm_attn_decode_rope against twm_rope_append + twm_attn_decode on the same
     fused QKV rows: the attention output and both caches bit for bit (position at the start, at the
     end and in the middle of a 32-token chunk, at the end of the cache, with the length covering the
-    new token and one token short of it)."""
+    new token and one token short of it; the large cache makes each CTA walk several chunks)."""
     lib = _lib.lib()
-    hd, max_seq, base = 128, 512, 1e6
+    hd, base = 128, 1e6
     kv_dim = kv_heads * hd
     g = torch.Generator(device="cuda").manual_seed(pos * 7 + heads)
     qkv = torch.randn((rows, (heads + 2 * kv_heads) * hd), generator=g, device="cuda").half()
