@@ -258,6 +258,24 @@ def test_gated_activation_prologue(k, n, splits, group, kind):
     assert _abs_err_over_rms(plain, ref) < TC_ABS_F32 * max(1.0, k / 3584)
 
 
+def test_next_gemm_hint_changes_nothing_but_timing():
+    """twm_gemm_args.next: the producer warps ask for the head of the following GEMM's weights; the
+    result is the same bits with and without it, whatever the successor looks like (another shape, a
+    plan with K slices, a successor the library cannot plan: the hint is then dropped)."""
+    k, n, group = 3584, 4608, 128
+    _, packed, scales = _quantised(k, n, group, 61)
+    _, p2, s2 = _quantised(18944, 3584, group, 62)
+    a = seeded_activations(1, k, 8)
+    plain = _run_gemm(a, packed, scales, 1, n, k, group, torch.float16, torch.float32, flags=_lib.TWM_FLAG_PDL)
+    p2d, s2d = _to_dev(p2), _to_dev(s2.view(np.float16))
+    pd, sd = _to_dev(packed), _to_dev(scales.view(np.float16))
+    for nxt in ((p2d, s2d, 1, 3584, 18944, group), (pd, sd, 1, n, k, group), (p2d, s2d, 64, 3584, 18944, group),
+                (p2d, s2d, 1, 3584, 18944 + 32, group)):          # the last one is not a valid shape (K % 128 != 0)
+        hinted = _run_gemm(a, packed, scales, 1, n, k, group, torch.float16, torch.float32, flags=_lib.TWM_FLAG_PDL,
+                           next_gemm=nxt)
+        assert np.array_equal(hinted, plain)
+
+
 def test_gated_activation_prologue_refusals():
     k, n = 256, 256
     _, packed, scales = _quantised(k, n, 32, 58)
