@@ -582,6 +582,252 @@ attn_chunk_kernel(float* __restrict__ part /* [heads][parts][HEAD_DIM + 2] */, c
     if (lane == 0) { dst[HEAD_DIM] = m_run; dst[HEAD_DIM + 1] = l_run; }
 }
 
+// ---- the same pass on the tensor cores, for launches whose CTAs walk several chunks ----
+// With many sequences in lock step the lane-per-token kernel above is bound by instruction issue
+// (28 warp instructions per token and q head).  Here the q heads of a kv head are the M dimension of
+// warp-level MMAs (up to 8 heads, padded to 16 rows): per 32-token chunk each of the CTA's four warps
+// takes 8 tokens, S = Q K^T as 8 x m16n8k16 (K rows are the B fragments as they lie in shared
+// memory), an online soft-max of its own (the warp keeps its own running max, sum and O over "its"
+// tokens of every chunk, so the warps never synchronise inside a chunk), and O += P V as 16 x m16n8k8
+// with P rounded to f16 and V fragments fetched with ldmatrix.trans.  At the end the four warps'
+// (max, sum, O) are merged through shared memory into one partial per q head, in the format of
+// the kernel above.  About 130 warp instructions per warp and chunk instead of 896.
+__device__ __forceinline__ void att_mma_16816(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1)
+{
+    // rows 8..15 of A (a1, a3) are padding: zero
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void att_mma_1688(float& d0, float& d1, uint32_t a0, uint32_t b0)
+{
+    float z2 = 0.0f, z3 = 0.0f;                  // rows 8..15: padding, results dropped
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                 : "+f"(d0), "+f"(d1), "+f"(z2), "+f"(z3)
+                 : "r"(a0), "r"(0u), "r"(b0));
+}
+__device__ __forceinline__ void att_ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t smem_addr)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr));
+}
+
+constexpr int ATT_MMA_WARPS = 4;
+template <int HEAD_DIM, bool ROPE>
+__global__ void __launch_bounds__(ATT_MMA_WARPS * 32)
+attn_span_mma_kernel(float* __restrict__ part /* [heads][parts][HEAD_DIM + 2] */, const __half* __restrict__ q,
+                     __half* k_cache, __half* v_cache, int num_heads, int num_kv_heads, const int* __restrict__ len_buf,
+                     int max_parts, int span, int max_seq, const float* __restrict__ bias, const float* __restrict__ rope,
+                     const int* __restrict__ pos_buf)
+{
+    static_assert(HEAD_DIM == 128, "lane owns 4 of 128 dims when staging");
+    constexpr int ROW_BYTES = HEAD_DIM * 2;
+    constexpr int KROW = ROW_BYTES + 16;                    // padded K and V rows: conflict-free fragment loads
+    constexpr int PIECES = ATT_CHUNK * ROW_BYTES / 16;      // 512 16-byte pieces of a chunk's K (or V)
+    constexpr int PER_ROW = ROW_BYTES / 16;
+    constexpr int THREADS = ATT_MMA_WARPS * 32;
+    constexpr int BATCH = PIECES / THREADS;                 // 4: one round of loads holds a whole chunk
+    constexpr int STRIDE = HEAD_DIM + 2;
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    const int kvh = blockIdx.y;
+    {
+        const size_t row = blockIdx.z;
+        q += row * (size_t)(ROPE ? (num_heads + 2 * num_kv_heads) : num_heads) * HEAD_DIM;
+        k_cache += row * (size_t)max_seq * num_kv_heads * HEAD_DIM;
+        v_cache += row * (size_t)max_seq * num_kv_heads * HEAD_DIM;
+        part += row * (size_t)num_heads * max_parts * STRIDE;
+    }
+    const int len = min(len_buf[0], max_seq);
+    const int chunk0 = blockIdx.x * span;
+    const int group = num_heads / num_kv_heads;          // q heads of this kv head, at most 8
+    const int kv_dim = num_kv_heads * HEAD_DIM;
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    float* dst0 = part + ((size_t)(kvh * group) * max_parts + blockIdx.x) * STRIDE;      // head h: + h * max_parts * STRIDE
+    // four dims of one head (the whole warp: one head), biased and rotated, as f16
+    auto rope4 = [&](int elem0, bool rotate) -> uint2 {
+        const uint2 raw = *reinterpret_cast<const uint2*>(q + elem0 + lane * 4);
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+        float f[4] = {a.x, a.y, b.x, b.y};
+        if (bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) f[j] += bias[elem0 + lane * 4 + j];
+        }
+        float r[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float other = __shfl_xor_sync(0xffffffffu, f[j], 16);
+            const int pair = (lane & 15) * 4 + j;
+            const bool first = lane < 16;
+            r[j] = rotate ? rope_rotate(first ? f[j] : other, first ? other : f[j], rope[pair], rope[HEAD_DIM / 2 + pair], first)
+                          : f[j];
+        }
+        const __half2 h0 = __floats2half2_rn(r[0], r[1]), h1 = __floats2half2_rn(r[2], r[3]);
+        uint2 o;
+        o.x = *reinterpret_cast<const uint32_t*>(&h0);
+        o.y = *reinterpret_cast<const uint32_t*>(&h1);
+        return o;
+    };
+    const int q_total = num_heads * HEAD_DIM;
+    const int pos = ROPE ? pos_buf[0] : -1;
+    const bool has_new = ROPE && pos >= chunk0 * ATT_CHUNK && pos < (chunk0 + span) * ATT_CHUNK && pos < max_seq;
+    uint2 k_new = make_uint2(0, 0), v_new = make_uint2(0, 0);
+    if (has_new && w == 0) {
+        k_new = rope4(q_total + kvh * HEAD_DIM, true);
+        v_new = rope4(q_total + kv_dim + kvh * HEAD_DIM, false);
+        *reinterpret_cast<uint2*>(k_cache + (size_t)pos * kv_dim + kvh * HEAD_DIM + lane * 4) = k_new;
+        *reinterpret_cast<uint2*>(v_cache + (size_t)pos * kv_dim + kvh * HEAD_DIM + lane * 4) = v_new;
+    }
+    if (chunk0 * ATT_CHUNK >= len) {
+        for (int h = threadIdx.x; h < group; h += THREADS) {
+            float* d = dst0 + (size_t)h * max_parts * STRIDE;
+            d[HEAD_DIM] = -INFINITY; d[HEAD_DIM + 1] = 0.0f;
+        }
+        return;
+    }
+    // K and V of the chunk; after the last chunk the same bytes hold the four warps' results
+    __shared__ __align__(16) unsigned char kv_s[2 * ATT_CHUNK * KROW];
+    __shared__ __align__(16) __half q_s[ATT_MAX_GROUP][HEAD_DIM];
+    unsigned char* k_s = kv_s;
+    unsigned char* v_s = kv_s + ATT_CHUNK * KROW;
+    static_assert(2 * ATT_CHUNK * KROW >= ATT_MMA_WARPS * ATT_MAX_GROUP * STRIDE * 4, "merge buffer fits the staging bytes");
+    for (int hh = w; hh < ATT_MAX_GROUP; hh += ATT_MMA_WARPS) {
+        uint2 qr = make_uint2(0, 0);                     // heads past the group: zero rows
+        if (hh < group)
+            qr = ROPE ? rope4((kvh * group + hh) * HEAD_DIM, true)
+                      : *reinterpret_cast<const uint2*>(q + (size_t)(kvh * group + hh) * HEAD_DIM + lane * 4);
+        *reinterpret_cast<uint2*>(&q_s[hh][lane * 4]) = qr;
+    }
+    __syncthreads();
+    uint32_t qa0[HEAD_DIM / 16], qa2[HEAD_DIM / 16];     // A fragments of Q, row g (rows 8..15 are zero)
+#pragma unroll
+    for (int ks = 0; ks < HEAD_DIM / 16; ++ks) {
+        qa0[ks] = *reinterpret_cast<const uint32_t*>(&q_s[g][ks * 16 + 2 * t]);
+        qa2[ks] = *reinterpret_cast<const uint32_t*>(&q_s[g][ks * 16 + 8 + 2 * t]);
+    }
+    const size_t row_stride = (size_t)kv_dim * 2;
+    uint4 kk[BATCH], vv[BATCH];
+    auto load_round = [&](int c) {
+        const int t0 = c * ATT_CHUNK;
+        const int nt = min(ATT_CHUNK, len - t0);
+        const unsigned char* kg = reinterpret_cast<const unsigned char*>(k_cache + (size_t)t0 * kv_dim + kvh * HEAD_DIM);
+        const unsigned char* vg = reinterpret_cast<const unsigned char*>(v_cache + (size_t)t0 * kv_dim + kvh * HEAD_DIM);
+#pragma unroll
+        for (int b = 0; b < BATCH; ++b) {
+            const int i = threadIdx.x + b * THREADS;
+            const int tok = i / PER_ROW, piece = i % PER_ROW;
+            const bool in = (tok < nt) && !(has_new && t0 + tok == pos);      // rows past the end are zero; the new row is not in the cache yet
+            kk[b] = in ? *reinterpret_cast<const uint4*>(kg + tok * row_stride + piece * 16) : make_uint4(0, 0, 0, 0);
+            vv[b] = in ? *reinterpret_cast<const uint4*>(vg + tok * row_stride + piece * 16) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    auto store_round = [&](int c) {
+        const int t0 = c * ATT_CHUNK;
+#pragma unroll
+        for (int b = 0; b < BATCH; ++b) {
+            const int i = threadIdx.x + b * THREADS;
+            const int tok = i / PER_ROW, piece = i % PER_ROW;
+            if (has_new && t0 + tok == pos) continue;                          // written by warp 0
+            *reinterpret_cast<uint4*>(k_s + tok * KROW + piece * 16) = kk[b];
+            *reinterpret_cast<uint4*>(v_s + tok * KROW + piece * 16) = vv[b];
+        }
+    };
+    const float scale = rsqrtf((float)HEAD_DIM);
+    float m_run = -INFINITY, l_run = 0.0f;
+    float o[HEAD_DIM / 8][2];                            // head g: dims 8 j + 2 t, + 1
+#pragma unroll
+    for (int j = 0; j < HEAD_DIM / 8; ++j) { o[j][0] = 0.0f; o[j][1] = 0.0f; }
+    load_round(chunk0);
+    for (int sc = 0; sc < span; ++sc) {
+        const int c = chunk0 + sc;
+        const int t0 = c * ATT_CHUNK;
+        if (t0 >= len) break;                              // CTA-uniform
+        const int nt = min(ATT_CHUNK, len - t0);
+        store_round(c);
+        if (has_new && w == 0 && pos >= t0 && pos < t0 + ATT_CHUNK) {
+            *reinterpret_cast<uint2*>(k_s + (pos - t0) * KROW + lane * 8) = k_new;
+            *reinterpret_cast<uint2*>(v_s + (pos - t0) * KROW + lane * 8) = v_new;
+        }
+        __syncthreads();
+        if (sc + 1 < span && (c + 1) * ATT_CHUNK < len) load_round(c + 1);      // in flight during the arithmetic
+        // ---- S[head g][tokens 8 w + 2 t, + 1] ----
+        float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        {
+            const unsigned char* krow = k_s + (8 * w + g) * KROW + 4 * t;
+#pragma unroll
+            for (int ks = 0; ks < HEAD_DIM / 16; ++ks) {
+                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + ks * 32);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + ks * 32 + 16);
+                att_mma_16816(s4, qa0[ks], qa2[ks], b0, b1);
+            }
+        }
+        // ---- this warp's online soft-max over its 8 tokens ----
+        const int tk = 8 * w + 2 * t;
+        const float s0 = (tk < nt) ? s4[0] * scale : -INFINITY;
+        const float s1 = (tk + 1 < nt) ? s4[1] * scale : -INFINITY;
+        float mx = fmaxf(s0, s1);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);
+        const bool any = m_new != -INFINITY;               // the same for the four lanes of a head
+        const float corr = (m_run == -INFINITY) ? 0.0f : __expf(m_run - m_new);
+        const float p0 = (any && tk < nt) ? __expf(s0 - m_new) : 0.0f;
+        const float p1 = (any && tk + 1 < nt) ? __expf(s1 - m_new) : 0.0f;
+        float ps = p0 + p1;
+        ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+        ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+        l_run = fmaf(l_run, corr, ps);
+        m_run = m_new;
+        const __half2 ph = __floats2half2_rn(p0, p1);
+        const uint32_t pa = *reinterpret_cast<const uint32_t*>(&ph);
+        // ---- O[head g][:] = O * corr + P V over the warp's 8 tokens ----
+        const uint32_t v_base = smem_u32(v_s + (8 * w + (lane & 7)) * KROW + (lane >> 3) * 16);
+#pragma unroll
+        for (int j4 = 0; j4 < HEAD_DIM / 32; ++j4) {
+            uint32_t vb[4];
+            att_ldmatrix_x4_trans(vb, v_base + j4 * 64);     // dims 32 j4 .. 32 j4 + 31: four 8-dim tiles
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+                float& d0 = o[j4 * 4 + jj][0];
+                float& d1 = o[j4 * 4 + jj][1];
+                d0 *= corr; d1 *= corr;
+                att_mma_1688(d0, d1, pa, vb[jj]);
+            }
+        }
+        if (sc + 1 < span) __syncthreads();                // the next chunk overwrites the staged rows
+    }
+    // ---- merge the four warps' results per q head ----
+    __syncthreads();                                       // everybody is done with the staged rows
+    float* mb = reinterpret_cast<float*>(kv_s);            // [warp][head][STRIDE]
+    if (g < group) {
+        float* mine = mb + ((size_t)w * ATT_MAX_GROUP + g) * STRIDE;
+#pragma unroll
+        for (int j = 0; j < HEAD_DIM / 8; ++j) *reinterpret_cast<float2*>(mine + 8 * j + 2 * t) = make_float2(o[j][0], o[j][1]);
+        if (t == 0) { mine[HEAD_DIM] = m_run; mine[HEAD_DIM + 1] = l_run; }
+    }
+    __syncthreads();
+    const int d = threadIdx.x;                             // 128 threads = 128 dims
+    for (int h = 0; h < group; ++h) {
+        float mw[ATT_MMA_WARPS], mm = -INFINITY;
+#pragma unroll
+        for (int ww = 0; ww < ATT_MMA_WARPS; ++ww) {
+            mw[ww] = mb[((size_t)ww * ATT_MAX_GROUP + h) * STRIDE + HEAD_DIM];
+            mm = fmaxf(mm, mw[ww]);
+        }
+        float ov = 0.0f, lv = 0.0f;
+#pragma unroll
+        for (int ww = 0; ww < ATT_MMA_WARPS; ++ww) {
+            const float wgt = (mw[ww] == -INFINITY) ? 0.0f : __expf(mw[ww] - mm);
+            ov = fmaf(mb[((size_t)ww * ATT_MAX_GROUP + h) * STRIDE + d], wgt, ov);
+            lv = fmaf(mb[((size_t)ww * ATT_MAX_GROUP + h) * STRIDE + HEAD_DIM + 1], wgt, lv);
+        }
+        float* dsth = dst0 + (size_t)h * max_parts * STRIDE;
+        dsth[d] = ov;
+        if (d == 0) { dsth[HEAD_DIM] = mm; dsth[HEAD_DIM + 1] = lv; }
+    }
+}
+
 // Pass 2: merge the chunks of one q head (log-sum-exp weights), write f16.  CTA = q head, 4 x 128
 // threads: thread (part, d) sums dimension d over every fourth chunk, eight loads in flight.
 // Reference: warp_flash_decode_reduce, crates/kernels/src/kv_cache.rs:790-841.

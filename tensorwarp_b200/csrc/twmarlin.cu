@@ -1238,15 +1238,25 @@ twm_status attn_decode_common(void* out, const void* q_or_qkv, void* k_cache, vo
     int span = 1;
     while (span < 8 && (long)((chunks + span - 1) / span) * num_kv_heads * rows > 2L * 4 * sms) span *= 2;
     const int parts = (chunks + span - 1) / span;
-    const dim3 grid(parts, num_kv_heads, rows), block(32 * (num_heads / num_kv_heads));
-    if (rope_table)
+    // CTAs that walk several chunks run the tensor-core form of the pass (four warps, 8 tokens of a chunk each)
+    const dim3 grid(parts, num_kv_heads, rows), block(span > 1 ? 32 * twm::ops::ATT_MMA_WARPS : 32 * (num_heads / num_kv_heads));
+    float* sp = (float*)scratch;
+    const __half* qp = (const __half*)q_or_qkv;
+    __half *kp = (__half*)k_cache, *vp = (__half*)v_cache;
+    const float* nof = nullptr;
+    const int* noi = nullptr;
+    if (rope_table && span > 1)
+        st = launch_op("twm_attn_decode_rope(spans)", twm::ops::attn_span_mma_kernel<128, true>, grid, block, 0, flags, stream,
+                       sp, qp, kp, vp, num_heads, num_kv_heads, len_buf, parts, span, max_seq, bias, rope_table, pos_buf);
+    else if (rope_table)
         st = launch_op("twm_attn_decode_rope(chunks)", twm::ops::attn_chunk_kernel<128, true>, grid, block, 0, flags, stream,
-                       (float*)scratch, (const __half*)q_or_qkv, (__half*)k_cache, (__half*)v_cache, num_heads, num_kv_heads,
-                       len_buf, parts, span, max_seq, bias, rope_table, pos_buf);
+                       sp, qp, kp, vp, num_heads, num_kv_heads, len_buf, parts, span, max_seq, bias, rope_table, pos_buf);
+    else if (span > 1)
+        st = launch_op("twm_attn_decode(spans)", twm::ops::attn_span_mma_kernel<128, false>, grid, block, 0, flags, stream,
+                       sp, qp, kp, vp, num_heads, num_kv_heads, len_buf, parts, span, max_seq, nof, nof, noi);
     else
         st = launch_op("twm_attn_decode(chunks)", twm::ops::attn_chunk_kernel<128, false>, grid, block, 0, flags, stream,
-                       (float*)scratch, (const __half*)q_or_qkv, (__half*)k_cache, (__half*)v_cache, num_heads, num_kv_heads,
-                       len_buf, parts, span, max_seq, (const float*)nullptr, (const float*)nullptr, (const int*)nullptr);
+                       sp, qp, kp, vp, num_heads, num_kv_heads, len_buf, parts, span, max_seq, nof, nof, noi);
     if (st != TWM_OK) return st;
     return launch_op("twm_attn_decode(merge)", twm::ops::attn_merge_kernel<128>, dim3(num_heads, rows), dim3(128 * twm::ops::ATT_MERGE_PARTS), 0, flags,
                      stream, (__half*)out, (const float*)scratch, len_buf, parts, span);

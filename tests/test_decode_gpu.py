@@ -210,11 +210,12 @@ def test_without_programmatic_launch_same_tokens():
 
 
 @pytest.mark.parametrize("length", [1, 31, 500, 2049])
-@pytest.mark.parametrize("heads,kv_heads,rows", [(28, 4, 1), (8, 8, 2), (16, 2, 3)])
+@pytest.mark.parametrize("heads,kv_heads,rows", [(28, 4, 1), (8, 8, 2), (16, 2, 3), (28, 4, 3)])
 def test_attention_against_float64(length, heads, kv_heads, rows):
     """twm_attn_decode (split-KV chunk kernel + merge kernel) with two cache capacities (the grid
     covers the capacity, the length comes from the device) against a float64 soft-max attention
-    on the same cache contents."""
+    on the same cache contents.  The large capacity with several sequences makes the CTAs walk
+    several chunks, which runs the tensor-core form of the pass (groups of 1, 7 and 8 q heads)."""
     lib = _lib.lib()
     hd = 128
     g = torch.Generator(device="cuda").manual_seed(length * 31 + heads)
@@ -254,7 +255,7 @@ def test_attention_against_float64(length, heads, kv_heads, rows):
 
 
 @pytest.mark.parametrize("pos,max_seq", [(0, 512), (31, 512), (32, 512), (100, 512), (511, 512), (4000, 9000), (4031, 9000)])
-@pytest.mark.parametrize("heads,kv_heads,rows,with_bias", [(28, 4, 1, True), (8, 8, 2, False), (16, 2, 3, True)])
+@pytest.mark.parametrize("heads,kv_heads,rows,with_bias", [(28, 4, 1, True), (8, 8, 2, False), (16, 2, 3, True), (28, 4, 3, False)])
 def test_attention_with_fused_rope_equals_the_two_passes(pos, max_seq, heads, kv_heads, rows, with_bias):
     """twm_rope_table + twm_attn_decode_rope against twm_rope_append + twm_attn_decode on the same
     fused QKV rows: the attention output and both caches bit for bit (position at the start, at the
