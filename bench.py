@@ -591,7 +591,7 @@ def m_sweep(torch, q, device):
     tensor fractions of the measured peaks."""
     from tensorwarp_b200 import _lib
     k, n, copies = 3584, 37888, 8
-    names = {_lib.TWM_KERNEL_SIMT: "simt", _lib.TWM_KERNEL_TC: "tcgen05", _lib.TWM_KERNEL_MMA: "mma", _lib.TWM_KERNEL_TCW: "tcgen05-wide"}
+    names = {_lib.TWM_KERNEL_SIMT: "simt", _lib.TWM_KERNEL_TC: "tcgen05", _lib.TWM_KERNEL_MMA: "mma", _lib.TWM_KERNEL_TCW: "tcgen05-wide", _lib.TWM_KERNEL_TCR: "tcgen05-256col-f16w"}
     peak, _ = measured_peak_gbs()
     tf_peak = 1629.9
     try:

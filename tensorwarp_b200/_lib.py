@@ -13,7 +13,7 @@ LIB_PATH = os.environ.get("TWMARLIN_LIB", os.path.join(PKG, "libtwmarlin.so"))
 
 TWM_OK, TWM_EINVAL, TWM_EALIGN, TWM_EWORKSPACE, TWM_ELAUNCH, TWM_EARCH, TWM_ETIMEOUT = 0, -1, -2, -3, -4, -5, -6
 TWM_F32, TWM_F16 = 0, 1
-TWM_KERNEL_AUTO, TWM_KERNEL_SIMT, TWM_KERNEL_TC, TWM_KERNEL_MMA, TWM_KERNEL_TCW = 0, 1, 2, 3, 4
+TWM_KERNEL_AUTO, TWM_KERNEL_SIMT, TWM_KERNEL_TC, TWM_KERNEL_MMA, TWM_KERNEL_TCW, TWM_KERNEL_TCR = 0, 1, 2, 3, 4, 5
 TWM_FLAG_PDL, TWM_FLAG_ACCUMULATE, TWM_FLAG_INDEPENDENT = 1, 2, 4
 TWM_A_PLAIN, TWM_A_SILU_MUL, TWM_A_GEGLU = 0, 1, 2
 

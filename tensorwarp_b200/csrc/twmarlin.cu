@@ -19,6 +19,7 @@
 #include "twm_gemv_simt.cuh"
 #include "twm_gemm_tc.cuh"
 #include "twm_gemm_tcw.cuh"
+#include "twm_gemm_tcr.cuh"
 #include "twm_gemv_mma.cuh"
 #include "twm_chain.cuh"
 #include "twm_layout.cuh"
@@ -92,6 +93,7 @@ twm_status ensure_device(int* sm_count_out)
             raise_tc((const void*)twm::tc::gemm_kernel<32>, tc_smem_bytes(32));
             raise_tc((const void*)twm::tc::gemm_kernel<64>, tc_smem_bytes(64));
             raise_tc((const void*)twm::tcw::gemm_kernel, sizeof(twm::tcw::Smem));
+            raise_tc((const void*)twm::tcr::gemm_kernel, sizeof(twm::tcr::Smem));
             auto raise_mma = [&](const void* fn) {
                 if (r == cudaSuccess)
                     r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(twm::mma::Smem));
@@ -177,13 +179,13 @@ bool make_act_map(CUtensorMap* map, const void* xp, int rows, int K, int nb_rows
 // Tensor map over the permuted activations of one wide tcgen05 launch, f16 [K/8][rows][8], seen as
 // 64-bit words [K/8][rows * 2]: a box of 256 words x 16 K cores is one scale group of 128 K for
 // 128 rows, landing as [K core][row][16 bytes]; rows past `rows` read as zero.
-bool make_act_map_wide(CUtensorMap* map, const void* xp, int rows, int K)
+bool make_act_map_wide(CUtensorMap* map, const void* xp, int rows, int K, int kcores = twm::tcw::A_KCORES)
 {
     EncodeTiledFn enc = get_encode_tiled();
     if (!enc) return false;
     const cuuint64_t gdim[2] = {(cuuint64_t)rows * 2, (cuuint64_t)K / 8};
     const cuuint64_t gstride[1] = {(cuuint64_t)rows * 16};
-    const cuuint32_t box[2] = {(cuuint32_t)twm::tcw::MB * 2, (cuuint32_t)twm::tcw::A_KCORES};
+    const cuuint32_t box[2] = {(cuuint32_t)twm::tcw::MB * 2, (cuuint32_t)kcores};
     const cuuint32_t estride[2] = {1, 1};
     return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(xp), gdim, gstride, box, estride,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -246,9 +248,14 @@ constexpr int kTcwFromRows = 65;
 int auto_kernel(int M, int N, int K, int G, bool a_is_f16, bool indirect, int splits_override)
 {
     if (!a_is_f16) return TWM_KERNEL_SIMT;
-    (void)K; (void)splits_override;
-    // many rows: the wide tcgen05 kernel (rows on the MMA's M dimension); it wants group 128 and full 128-column tiles
-    if (M >= kTcwFromRows && G == 128 && N >= 128 && !indirect) return TWM_KERNEL_TCW;
+    (void)K;
+    // many rows: rows on the MMA's M dimension; group 128 and full 128-column tiles.  Wide matrices (at least half
+    // a wave of 256-column tiles, no K slices asked for) take the 256-column kernel, whose weights enter the tensor
+    // core rounded to FP16 as in the reference's batched route; the others the exact-weight kernel, which can split K.
+    if (M >= kTcwFromRows && G == 128 && N >= 128 && !indirect) {
+        const bool wide = (N + twm::tcr::NT - 1) / twm::tcr::NT >= kDefaultSms / 2 && splits_override <= 1;
+        return wide ? TWM_KERNEL_TCR : TWM_KERNEL_TCW;
+    }
     return M >= kTcFromRows ? TWM_KERNEL_TC : TWM_KERNEL_MMA;
 }
 
@@ -289,6 +296,24 @@ twm_status launch_tcw(const twm::GemmParams& p, dim3 grid, bool pdl, cudaStream_
     cfg.numAttrs = pdl ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, twm::tcw::gemm_kernel, p);
     if (e != cudaSuccess) { set_error("launch tcw::gemm_kernel", e); return TWM_ELAUNCH; }
+    return TWM_OK;
+}
+
+twm_status launch_tcr(const twm::GemmParams& p, dim3 grid, bool pdl, cudaStream_t stream)
+{
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(twm::tcr::THREADS, 1, 1);
+    cfg.dynamicSmemBytes = sizeof(twm::tcr::Smem);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, twm::tcr::gemm_kernel, p);
+    if (e != cudaSuccess) { set_error("launch tcr::gemm_kernel", e); return TWM_ELAUNCH; }
     return TWM_OK;
 }
 
@@ -496,8 +521,23 @@ twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int split
     const int nkb = K / 32;
     int kernel = kernel_override;
     if (kernel == TWM_KERNEL_AUTO) kernel = auto_kernel(M, N, K, group_size, true, false, splits_override);
-    if (kernel != TWM_KERNEL_SIMT && kernel != TWM_KERNEL_TC && kernel != TWM_KERNEL_MMA && kernel != TWM_KERNEL_TCW) return TWM_EINVAL;
-    if (kernel == TWM_KERNEL_TCW && (group_size != 128 || N < 128)) return TWM_EINVAL;
+    if (kernel != TWM_KERNEL_SIMT && kernel != TWM_KERNEL_TC && kernel != TWM_KERNEL_MMA && kernel != TWM_KERNEL_TCW &&
+        kernel != TWM_KERNEL_TCR)
+        return TWM_EINVAL;
+    if ((kernel == TWM_KERNEL_TCW || kernel == TWM_KERNEL_TCR) && (group_size != 128 || N < 128)) return TWM_EINVAL;
+    if (kernel == TWM_KERNEL_TCR) {          // 256-column tiles over the whole K: no slices, no scratch but the reordered activations
+        if (splits_override > 1) return TWM_EINVAL;
+        const int rows_r = std::min(M, kTcwRows);
+        out->kernel = kernel;
+        out->n_tile = twm::tcr::NT;
+        out->splits = 1;
+        out->blocks_per_split = K / 32;
+        out->grid_x = (N + twm::tcr::NT - 1) / twm::tcr::NT;
+        out->grid_y = 1;
+        out->workspace_bytes = kCounterBytes + 256 + (size_t)rows_r * K * 2;
+        out->cluster_reduce = 0;
+        return TWM_OK;
+    }
     // rows one launch carries; more rows are served by further launches
     const int rows = std::min(M, kernel == TWM_KERNEL_TC ? kTcRows : (kernel == TWM_KERNEL_TCW ? kTcwRows : 8));
     const int n_tiles = (N + twm::simt::NT - 1) / twm::simt::NT;
@@ -539,6 +579,7 @@ size_t twm_workspace_bytes(int M, int N, int K, int group_size)
     size_t need = 0;
     if (twm_plan(M, N, K, group_size, kDefaultSms, 0, TWM_KERNEL_TC, &tc) == TWM_OK) need = tc.workspace_bytes;
     if (twm_plan(M, N, K, group_size, kDefaultSms, 0, TWM_KERNEL_TCW, &tc) == TWM_OK) need = std::max(need, tc.workspace_bytes);
+    if (twm_plan(M, N, K, group_size, kDefaultSms, 0, TWM_KERNEL_TCR, &tc) == TWM_OK) need = std::max(need, tc.workspace_bytes);
     if (twm_plan(M, N, K, group_size, kDefaultSms, 0, TWM_KERNEL_SIMT, &simt) == TWM_OK)
         need = std::max(need, simt.workspace_bytes);
     if (twm_plan(M, N, K, group_size, kDefaultSms, 0, TWM_KERNEL_MMA, &simt) == TWM_OK)
@@ -600,12 +641,12 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
     cudaStream_t stream = (cudaStream_t)stream_;
     const size_t a_elt = a->a_dtype == TWM_F16 ? 2 : 4;
     const size_t c_elt = a->c_dtype == TWM_F16 ? 2 : 4;
-    if (kernel == TWM_KERNEL_TCW && (a->packed_offsets != nullptr || a->comm)) return TWM_EINVAL;
-    const int row_step = kernel == TWM_KERNEL_TC ? kTcRows : (kernel == TWM_KERNEL_TCW ? kTcwRows : 8);
+    if ((kernel == TWM_KERNEL_TCW || kernel == TWM_KERNEL_TCR) && (a->packed_offsets != nullptr || a->comm)) return TWM_EINVAL;
+    const int row_step = kernel == TWM_KERNEL_TC ? kTcRows : ((kernel == TWM_KERNEL_TCW || kernel == TWM_KERNEL_TCR) ? kTcwRows : 8);
     CUtensorMap packed_map;
     int map_rows = 0;
     if (a->packed_offsets == nullptr && a->N >= 128 && kernel != TWM_KERNEL_SIMT) {
-        const int want = kernel == TWM_KERNEL_MMA ? twm::mma::SB : twm::tc::WSTAGE_BLOCKS;      // (the wide kernel's stage is four blocks too)
+        const int want = kernel == TWM_KERNEL_MMA ? twm::mma::SB : (kernel == TWM_KERNEL_TCR ? twm::tcr::SB : twm::tc::WSTAGE_BLOCKS);      // (the wide kernel's stage is four blocks too)
         if (make_packed_map(&packed_map, a->packed, a->N, a->K / 32, want)) map_rows = want;
     }
     for (int m0 = 0; m0 < a->M; m0 += row_step) {
@@ -636,7 +677,21 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
         p.map_rows = map_rows;
         if (map_rows) p.packed_map = packed_map;
         const bool pdl = (a->flags & TWM_FLAG_PDL) != 0;
-        if (kernel == TWM_KERNEL_TCW) {
+        if (kernel == TWM_KERNEL_TCR) {
+            if (!map_rows) {
+                snprintf(t_last_error, sizeof(t_last_error), "cuTensorMapEncodeTiled failed for the packed map of the 256-column tcgen05 kernel");
+                return TWM_ELAUNCH;
+            }
+            char* xp = (char*)a->workspace + kCounterBytes;
+            if (!make_act_map_wide(&p.act_map, xp, rows, a->K, twm::tcr::KCORES)) {
+                snprintf(t_last_error, sizeof(t_last_error), "cuTensorMapEncodeTiled failed for the activation map");
+                return TWM_ELAUNCH;
+            }
+            st = launch_prepass((__half*)xp, (const __half*)p.a, p.lda, rows, a->K, a->flags, stream_);
+            if (st != TWM_OK) return st;
+            st = launch_tcr(p, dim3(pl.grid_x, 1, 1), pdl, stream);
+        }
+        else if (kernel == TWM_KERNEL_TCW) {
             if (!map_rows) {
                 snprintf(t_last_error, sizeof(t_last_error), "cuTensorMapEncodeTiled failed for the packed map of the wide tcgen05 kernel");
                 return TWM_ELAUNCH;

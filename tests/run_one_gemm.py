@@ -20,7 +20,7 @@ from tensorwarp_b200 import _lib  # noqa: E402
 from tensorwarp_b200 import quantize as q  # noqa: E402
 
 KERNELS = {"auto": 0, "simt": _lib.TWM_KERNEL_SIMT, "tc": _lib.TWM_KERNEL_TC, "mma": _lib.TWM_KERNEL_MMA,
-           "tcw": _lib.TWM_KERNEL_TCW}
+           "tcw": _lib.TWM_KERNEL_TCW, "tcr": _lib.TWM_KERNEL_TCR}
 
 
 def one_gemm(args) -> None:

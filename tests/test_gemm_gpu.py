@@ -30,8 +30,10 @@ TC_ABS_F32 = 2e-5
 
 
 def _tc_ref(a, packed, scales, m, n, k, group, kernel):
-    """The adjudicating oracle for a kernel family."""
-    return oracle.w4a16_f64(a, packed, scales, m, n, k, group)
+    """The adjudicating oracle for a kernel family: exact weights f32(scale) * (q - 8), except for the
+    256-column tcgen05 kernel, whose weights enter the tensor core as f16_rn(scale * (q - 8)), the
+    rounding of the reference's own batched route (dequant_q4_to_f16, quantize.rs:534-571)."""
+    return oracle.w4a16_f64(a, packed, scales, m, n, k, group, weights_f16=(kernel == _lib.TWM_KERNEL_TCR))
 
 
 def _abs_err_over_rms(y, ref64):
@@ -288,6 +290,30 @@ def test_gated_activation_prologue_refusals():
         assert e.value.status == _lib.TWM_EINVAL
 
 
+@pytest.mark.parametrize("m", [65, 100, 128, 129, 256])
+@pytest.mark.parametrize("k,n", [(256, 256), (512, 300), (1024, 1000), (3584, 768)])
+def test_256_column_tensor_core_kernel(m, k, n):
+    """The 256-column tcgen05 kernel (TWM_KERNEL_TCR): weights rounded to FP16 as the reference's batched
+    route rounds them, one accumulator over the whole K.  Against the FP16-weight oracle to accumulation
+    error, against the exact-weight oracle to the weight rounding; ragged N (a last tile of one half, of
+    a partial half), a partial last row block, more rows than one launch carries; FP32 and FP16 outputs."""
+    group, kern = 128, _lib.TWM_KERNEL_TCR
+    _, packed, scales = _quantised(k, n, group, 53)
+    a = seeded_activations(m, k, 4)
+    ref16 = oracle.w4a16_f64(a, packed, scales, m, n, k, group, weights_f16=True)
+    y32 = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float32, kernel_override=kern)
+    # one accumulator over the whole K: the tensor core's truncation adds up over K / 16 chained MMAs
+    # (2.4e-5 of the output RMS seen at K = 3584) instead of over the eight of a scale group
+    assert _abs_err_over_rms(y32, ref16) < 4 * TC_ABS_F32 * max(1.0, k / 3584) and rel_err_floored(y32, ref16) < TOL_F16
+    assert _abs_err_over_rms(y32, oracle.w4a16_f64(a, packed, scales, m, n, k, group)) < TC_ABS_VS_EXACT
+    y16 = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float16, kernel_override=kern, flags=_lib.TWM_FLAG_PDL)
+    assert np.array_equal(y32.astype(np.float16).astype(np.float32), y16)          # one rounding of the sums, at the end
+    again = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float32, kernel_override=kern)
+    assert np.array_equal(again, y32)
+    with pytest.raises(_lib.TwmError):                                             # it does not split K
+        _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float32, kernel_override=kern, splits_override=2)
+
+
 def test_wide_tensor_core_kernel_refuses_what_it_cannot_do():
     k, n = 256, 256
     _, packed, scales = _quantised(k, n, 32, 46)
@@ -340,8 +366,12 @@ def test_config2_shapes_beyond_eight_rows(m):
     cols = slice(12800, 12800 + 384)
     packed = p.cpu().numpy()[:, cols].copy()
     scales = s.cpu().numpy().view(np.uint16)[:, cols].copy()
-    ref = oracle.w4a16_f64(a, packed, scales, m, 384, k, group)
+    chosen = q.plan(m, n, k, group).kernel
+    assert chosen == (_lib.TWM_KERNEL_TCR if m >= 65 else _lib.TWM_KERNEL_TC)
+    ref = _tc_ref(a, packed, scales, m, 384, k, group, chosen)
     assert rel_err_floored(c[:, cols].float().cpu().numpy(), ref) < TOL_F16
+    # whichever weights the kernel multiplies, the result is within 2e-3 of the output RMS of the exact-weight product
+    assert _abs_err_over_rms(c[:, cols].float().cpu().numpy(), oracle.w4a16_f64(a, packed, scales, m, 384, k, group)) < TC_ABS_VS_EXACT
     # and size-independent properties on the whole output: every element written, linear in the activations
     assert not torch.isnan(c).any()
     c2 = torch.empty_like(c)
@@ -442,7 +472,7 @@ def test_deterministic_and_split_invariant():
     k, n, group = 3584, 4608, 128
     _, packed, scales = _quantised(k, n, group, 53)
     a = seeded_activations(1, k, 0)
-    for kernel in (_lib.TWM_KERNEL_SIMT, _lib.TWM_KERNEL_TC, _lib.TWM_KERNEL_MMA, _lib.TWM_KERNEL_TCW):
+    for kernel in (_lib.TWM_KERNEL_SIMT, _lib.TWM_KERNEL_TC, _lib.TWM_KERNEL_MMA, _lib.TWM_KERNEL_TCW, _lib.TWM_KERNEL_TCR):
         runs = [_run_gemm(a, packed, scales, 1, n, k, group, torch.float16, torch.float32, kernel_override=kernel)
                 for _ in range(3)]
         assert np.array_equal(runs[0], runs[1]) and np.array_equal(runs[0], runs[2])
