@@ -30,43 +30,55 @@ namespace twm {
 namespace tcr {
 
 constexpr int NT = 256;                 // weight columns per CTA = MMA N
-constexpr int MB = 128;                 // activation rows per launch = MMA M (rows past M are zero)
+constexpr int MB = 128;                 // activation rows per MMA (rows past M are zero)
 constexpr int SB = 2;                   // 32-blocks per stage: 64 K
-constexpr int PSTAGES = 6;              // packed ring: 6 x 8 KB
-constexpr int ASTAGES = 4;              // activation stages: 4 x 16 KB
-constexpr int BSTAGES = 3;              // unpacked FP16 weights: 3 x 32 KB
 constexpr int SSTAGES = 4;              // scale rows of the tile (one per 128-group, 512 B)
 constexpr int KCORES = SB * 4;          // 8-wide K cores per stage
-constexpr int A_STAGE_BYTES = KCORES * MB * 16;        // [K core][row][16 bytes]
+constexpr int A_BLOCK_BYTES = KCORES * MB * 16;        // one block of 128 rows: [K core][row][16 bytes]
 constexpr int B_STAGE_BYTES = KCORES * NT * 16;        // [K core][column][16 bytes]
 constexpr int P_HALF_BYTES = SB * 128 * kBlockBytes;   // one tensor-map box: [block][128 columns][16 bytes]
 constexpr int P_STAGE_BYTES = 2 * P_HALF_BYTES;
-constexpr int UNPACK_WARPS = 16;         // two sets of eight: set s unpacks block s of every stage
+constexpr int UNPACK_WARPS = 16;        // two sets of eight: set s unpacks block s of every stage
 constexpr int WARP_TMA = UNPACK_WARPS, WARP_MMA = WARP_TMA + 1;
 constexpr int THREADS = (WARP_MMA + 1) * 32;
-constexpr int TMEM_COLS = NT;
 
+// RB = blocks of 128 activation rows per launch (1: up to 128 rows, 2: up to 256).  With two blocks
+// every unpacked stage feeds two MMAs per K step (one per row block, one accumulator each), so
+// the unpack and the weight traffic are paid once for 256 rows.
+template <int RB>
+struct Cfg {
+    static constexpr int PSTAGES = RB == 1 ? 6 : 5;            // packed ring, 8 KB stages
+    static constexpr int ASTAGES = RB == 1 ? 4 : 3;            // activation stages of RB x 16 KB
+    static constexpr int BSTAGES = RB == 1 ? 3 : 2;            // unpacked FP16 weights, 32 KB stages
+    static constexpr int A_STAGE_BYTES = RB * A_BLOCK_BYTES;
+    static constexpr int TMEM_COLS = RB * NT;                  // one accumulator of 256 columns per row block
+};
+
+template <int RB>
 struct Smem {
-    alignas(128) uint8_t packed[PSTAGES][P_STAGE_BYTES];     // [half of the tile][block][column of the half][16 bytes]
-    alignas(128) uint8_t bw[BSTAGES][B_STAGE_BYTES];
-    alignas(128) uint8_t a[ASTAGES][A_STAGE_BYTES];
+    alignas(128) uint8_t packed[Cfg<RB>::PSTAGES][P_STAGE_BYTES];     // [half of the tile][block][column of the half][16 bytes]
+    alignas(128) uint8_t bw[Cfg<RB>::BSTAGES][B_STAGE_BYTES];
+    alignas(128) uint8_t a[Cfg<RB>::ASTAGES][Cfg<RB>::A_STAGE_BYTES]; // [row block][K core][row][16 bytes]
     alignas(16) uint16_t sc[SSTAGES][NT];
-    alignas(8) uint64_t p_full[PSTAGES];
-    alignas(8) uint64_t p_empty[PSTAGES];        // unpack warps
-    alignas(8) uint64_t b_full[BSTAGES];         // unpack warps
-    alignas(8) uint64_t b_empty[BSTAGES];        // MMA commit
-    alignas(8) uint64_t a_full[ASTAGES];
-    alignas(8) uint64_t a_empty[ASTAGES];        // MMA commit
-    alignas(8) uint64_t d_full;                  // MMA commit: the tile's accumulator is complete
+    alignas(8) uint64_t p_full[Cfg<RB>::PSTAGES];
+    alignas(8) uint64_t p_empty[Cfg<RB>::PSTAGES];       // unpack warps
+    alignas(8) uint64_t b_full[Cfg<RB>::BSTAGES];        // unpack warps
+    alignas(8) uint64_t b_empty[Cfg<RB>::BSTAGES];       // MMA commit
+    alignas(8) uint64_t a_full[Cfg<RB>::ASTAGES];
+    alignas(8) uint64_t a_empty[Cfg<RB>::ASTAGES];       // MMA commit
+    alignas(8) uint64_t d_full;                          // MMA commit: the tile's accumulators are complete
     uint32_t tmem_base;
     int abort_flag;
 };
 
+template <int RB>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_kernel(const __grid_constant__ GemmParams p)
 {
+    using C = Cfg<RB>;
+    constexpr int PSTAGES = C::PSTAGES, ASTAGES = C::ASTAGES, BSTAGES = C::BSTAGES, TMEM_COLS = C::TMEM_COLS;
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
+    Smem<RB>& sm = *reinterpret_cast<Smem<RB>*>(smem_raw);
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -122,8 +134,10 @@ gemm_kernel(const __grid_constant__ GemmParams p)
                 if (ast < n_stages) {
                     const int as = ast % ASTAGES;
                     if (ast < ASTAGES || mbar_try_wait(&sm.a_empty[as], ((ast / ASTAGES) - 1) & 1)) {
-                        mbar_arrive_expect_tx(&sm.a_full[as], (uint32_t)A_STAGE_BYTES);
-                        tma_load_2d(&sm.a[as][0], &p.act_map, 0, ast * KCORES, &sm.a_full[as]);
+                        mbar_arrive_expect_tx(&sm.a_full[as], (uint32_t)C::A_STAGE_BYTES);
+#pragma unroll
+                        for (int rb = 0; rb < RB; ++rb)         // rows 128 rb ...: 256 64-bit words further along a K core's row run
+                            tma_load_2d(&sm.a[as][rb * A_BLOCK_BYTES], &p.act_map, rb * MB * 2, ast * KCORES, &sm.a_full[as]);
                         ++ast; progress = true;
                     }
                 }
@@ -151,14 +165,17 @@ gemm_kernel(const __grid_constant__ GemmParams p)
                 tc::tc_fence_after();
                 // A: [K core][row][16 B]: next K core MB*16 bytes on, next 8 rows 128 bytes on.
                 // B: [K core][column][16 B]: next K core NT*16 bytes on, next 8 columns 128 bytes on.
-                uint64_t ad = tc::make_b_desc(smem_u32(&sm.a[as][0]), MB * 16, 128);
-                uint64_t bd = tc::make_b_desc(smem_u32(&sm.bw[bs][0]), NT * 16, 128);
                 constexpr uint64_t a_step = (uint64_t)((2 * MB * 16) >> 4), b_step = (uint64_t)((2 * NT * 16) >> 4);   // two K cores, in descriptor units
 #pragma unroll
-                for (int h = 0; h < 2 * SB; ++h) {                          // four MMAs of K = 16
-                    tcw::mma_ss(tmem_base, ad, bd, idesc, (st == 0 && h == 0) ? 0u : 1u);
-                    ad += a_step;
-                    bd += b_step;
+                for (int rb = 0; rb < RB; ++rb) {                           // one accumulator per block of 128 rows
+                    uint64_t ad = tc::make_b_desc(smem_u32(&sm.a[as][rb * A_BLOCK_BYTES]), MB * 16, 128);
+                    uint64_t bd = tc::make_b_desc(smem_u32(&sm.bw[bs][0]), NT * 16, 128);
+#pragma unroll
+                    for (int h = 0; h < 2 * SB; ++h) {                      // four MMAs of K = 16
+                        tcw::mma_ss(tmem_base + rb * NT, ad, bd, idesc, (st == 0 && h == 0) ? 0u : 1u);
+                        ad += a_step;
+                        bd += b_step;
+                    }
                 }
                 tc::tc_commit(&sm.b_empty[bs]);
                 tc::tc_commit(&sm.a_empty[as]);
@@ -223,15 +240,16 @@ gemm_kernel(const __grid_constant__ GemmParams p)
         // thread = activation row (its TMEM lane); warp w takes lanes 32 (w & 3) ... and columns 64 (w >> 2) ...
         constexpr int RCOLS = NT / (UNPACK_WARPS / 4);
         const int quarter = warp & 3, cpart = warp >> 2;
-        const int m = quarter * 32 + lane;
-        const uint32_t lane_tmem = tmem_base + ((uint32_t)(quarter * 32) << 16) + cpart * RCOLS;
         ok = ok && tc::wait_uniform(&sm.d_full, 0, abort_flag);
         tc::tc_fence_after();
         ok = ok && (*abort_flag == 0);
-        const bool row_ok = m < p.M;
         const int nb = n0 + cpart * RCOLS;
-        const size_t row_off = (size_t)m * p.ldc + nb;
-        if (ok) {
+#pragma unroll 1
+        for (int rb = 0; rb < RB && ok; ++rb) {
+            const int m = rb * MB + quarter * 32 + lane;
+            const uint32_t lane_tmem = tmem_base + ((uint32_t)(quarter * 32) << 16) + rb * NT + cpart * RCOLS;
+            const bool row_ok = m < p.M;
+            const size_t row_off = (size_t)m * p.ldc + nb;
 #pragma unroll 1
             for (int c0 = 0; c0 < RCOLS; c0 += 16) {
                 uint32_t d[16];

@@ -93,7 +93,8 @@ twm_status ensure_device(int* sm_count_out)
             raise_tc((const void*)twm::tc::gemm_kernel<32>, tc_smem_bytes(32));
             raise_tc((const void*)twm::tc::gemm_kernel<64>, tc_smem_bytes(64));
             raise_tc((const void*)twm::tcw::gemm_kernel, sizeof(twm::tcw::Smem));
-            raise_tc((const void*)twm::tcr::gemm_kernel, sizeof(twm::tcr::Smem));
+            raise_tc((const void*)twm::tcr::gemm_kernel<1>, sizeof(twm::tcr::Smem<1>));
+            raise_tc((const void*)twm::tcr::gemm_kernel<2>, sizeof(twm::tcr::Smem<2>));
             auto raise_mma = [&](const void* fn) {
                 if (r == cudaSuccess)
                     r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(twm::mma::Smem));
@@ -280,6 +281,7 @@ int resolve_kernel(const twm_gemm_args* a)
 
 constexpr int kTcRows = 64;      // activation rows one tcgen05 launch carries
 constexpr int kTcwRows = twm::tcw::MB;   // ... and one wide tcgen05 launch
+constexpr int kTcrRows = 2 * twm::tcr::MB;   // ... and one 256-column tcgen05 launch (two blocks of 128 rows)
 
 twm_status launch_tcw(const twm::GemmParams& p, dim3 grid, bool pdl, cudaStream_t stream)
 {
@@ -299,20 +301,21 @@ twm_status launch_tcw(const twm::GemmParams& p, dim3 grid, bool pdl, cudaStream_
     return TWM_OK;
 }
 
-twm_status launch_tcr(const twm::GemmParams& p, dim3 grid, bool pdl, cudaStream_t stream)
+twm_status launch_tcr(const twm::GemmParams& p, int rows, dim3 grid, bool pdl, cudaStream_t stream)
 {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = grid;
     cfg.blockDim = dim3(twm::tcr::THREADS, 1, 1);
-    cfg.dynamicSmemBytes = sizeof(twm::tcr::Smem);
+    cfg.dynamicSmemBytes = rows > twm::tcr::MB ? sizeof(twm::tcr::Smem<2>) : sizeof(twm::tcr::Smem<1>);
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, twm::tcr::gemm_kernel, p);
+    cudaError_t e = rows > twm::tcr::MB ? cudaLaunchKernelEx(&cfg, twm::tcr::gemm_kernel<2>, p)
+                                        : cudaLaunchKernelEx(&cfg, twm::tcr::gemm_kernel<1>, p);
     if (e != cudaSuccess) { set_error("launch tcr::gemm_kernel", e); return TWM_ELAUNCH; }
     return TWM_OK;
 }
@@ -527,7 +530,7 @@ twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int split
     if ((kernel == TWM_KERNEL_TCW || kernel == TWM_KERNEL_TCR) && (group_size != 128 || N < 128)) return TWM_EINVAL;
     if (kernel == TWM_KERNEL_TCR) {          // 256-column tiles over the whole K: no slices, no scratch but the reordered activations
         if (splits_override > 1) return TWM_EINVAL;
-        const int rows_r = std::min(M, kTcwRows);
+        const int rows_r = std::min(M, kTcrRows);
         out->kernel = kernel;
         out->n_tile = twm::tcr::NT;
         out->splits = 1;
@@ -642,7 +645,7 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
     const size_t a_elt = a->a_dtype == TWM_F16 ? 2 : 4;
     const size_t c_elt = a->c_dtype == TWM_F16 ? 2 : 4;
     if ((kernel == TWM_KERNEL_TCW || kernel == TWM_KERNEL_TCR) && (a->packed_offsets != nullptr || a->comm)) return TWM_EINVAL;
-    const int row_step = kernel == TWM_KERNEL_TC ? kTcRows : ((kernel == TWM_KERNEL_TCW || kernel == TWM_KERNEL_TCR) ? kTcwRows : 8);
+    const int row_step = kernel == TWM_KERNEL_TC ? kTcRows : (kernel == TWM_KERNEL_TCW ? kTcwRows : (kernel == TWM_KERNEL_TCR ? kTcrRows : 8));
     CUtensorMap packed_map;
     int map_rows = 0;
     if (a->packed_offsets == nullptr && a->N >= 128 && kernel != TWM_KERNEL_SIMT) {
@@ -689,7 +692,7 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
             }
             st = launch_prepass((__half*)xp, (const __half*)p.a, p.lda, rows, a->K, a->flags, stream_);
             if (st != TWM_OK) return st;
-            st = launch_tcr(p, dim3(pl.grid_x, 1, 1), pdl, stream);
+            st = launch_tcr(p, rows, dim3(pl.grid_x, 1, 1), pdl, stream);
         }
         else if (kernel == TWM_KERNEL_TCW) {
             if (!map_rows) {
