@@ -48,10 +48,12 @@ enum {
     TWM_KERNEL_TC = 2,   /* tcgen05 kernel: weights dequantised into tensor memory, FP32 accumulate in TMEM */
     TWM_KERNEL_TCW = 4,  /* tcgen05 kernel for many rows (65 .. 128 per launch, group 128, N >= 128): the activation rows
                             are the MMA's M dimension, the unpacked weights its N = 128 */
-    TWM_KERNEL_TCR = 5,  /* tcgen05 kernel for many rows and wide matrices (65 .. 128 rows per launch, group 128, no K
-                            slices): 256-column tiles, the weights enter the tensor core as f16_rn(scale * (q - 8)), the
-                            rounding of the reference's own batched route (dequant_q4_to_f16, quantize.rs:534-571),
-                            and one FP32 accumulator runs over the whole K.  The other kernels multiply exact weights. */
+    TWM_KERNEL_TCR = 5,  /* tcgen05 kernel for many rows and wide matrices (65 .. 256 rows per launch, group 128, no K
+                            slices; chosen when N holds at least half a wave of 256-column tiles): the weights enter
+                            the tensor core as f16_rn(scale * (q - 8)), the rounding of the reference's own batched
+                            route (dequant_q4_to_f16, quantize.rs:534-571), and one FP32 accumulator per 128 rows runs
+                            over the whole K.  Every other kernel multiplies exact weights; ask for TWM_KERNEL_TCW to
+                            keep them exact at these shapes too. */
     TWM_KERNEL_MMA = 3   /* streaming kernel for M <= 8, FP16 activations, warp-level MMA on unpacked registers,
                             128-column tiles with split-K (inside a thread-block cluster for M <= 2) */
 };
