@@ -314,10 +314,17 @@ gemm_kernel(const __grid_constant__ GemmParams p)
                     }
                 }
             } else {
+                // (N is a multiple of 4 whenever a tile is full, and the partials start 16-byte aligned)
                 float* part = p.ws_partials + ((size_t)blockIdx.y * p.M + m) * p.N + nb;
+                if (full && (p.N & 3) == 0) {
 #pragma unroll
-                for (int j = 0; j < EPI_COLS; ++j)
-                    if (nb + j < p.N) part[j] = acc[j];
+                    for (int j = 0; j < EPI_COLS; j += 4)
+                        *reinterpret_cast<float4*>(part + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < EPI_COLS; ++j)
+                        if (nb + j < p.N) part[j] = acc[j];
+                }
             }
         }
         if (p.splits > 1) {
@@ -330,21 +337,39 @@ gemm_kernel(const __grid_constant__ GemmParams p)
             named_bar_sync(3, EPI_THREADS);
             if (sm.is_last) {
                 __threadfence();
-                if (row_ok && *abort_flag == 0) {
-                    for (int j = 0; j < EPI_COLS; ++j) {
-                        if (nb + j >= p.N) break;
-                        float s = 0.0f;
-                        for (int sp = 0; sp < p.splits; ++sp)
-                            s += ld_cg_f32(&p.ws_partials[((size_t)sp * p.M + m) * p.N + nb + j]);
-                        const size_t off = row_off + j;
-                        if (p.c_is_f16) {
-                            __half* cp = reinterpret_cast<__half*>(p.c);
-                            if (p.accumulate) s += __half2float(cp[off]);
-                            cp[off] = __float2half_rn(s);
+                // the last arriver adds the slices in slice order.  The tile is walked four columns per thread,
+                // a warp along a row (coalesced), the slices' loads issued together
+                if (*abort_flag == 0) {
+                    const bool vec = (p.N & 3) == 0;
+                    for (int idx = tid; idx < MB * (NT / 4); idx += EPI_THREADS) {
+                        const int r = idx / (NT / 4), c = n0 + (idx % (NT / 4)) * 4;
+                        if (r >= p.M || c >= p.N) continue;
+                        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                        if (vec) {
+#pragma unroll 4
+                            for (int sp = 0; sp < p.splits; ++sp) {
+                                const float4 t4 = __ldcg(reinterpret_cast<const float4*>(&p.ws_partials[((size_t)sp * p.M + r) * p.N + c]));
+                                v[0] += t4.x; v[1] += t4.y; v[2] += t4.z; v[3] += t4.w;
+                            }
                         } else {
-                            float* cp = reinterpret_cast<float*>(p.c);
-                            if (p.accumulate) s += cp[off];
-                            cp[off] = s;
+                            for (int sp = 0; sp < p.splits; ++sp)
+                                for (int j = 0; j < 4; ++j)
+                                    if (c + j < p.N) v[j] += ld_cg_f32(&p.ws_partials[((size_t)sp * p.M + r) * p.N + c + j]);
+                        }
+                        const size_t off = (size_t)r * p.ldc + c;
+                        for (int j = 0; j < 4; ++j) {
+                            if (c + j >= p.N) break;
+                            if (p.c_is_f16) {
+                                __half* cp = reinterpret_cast<__half*>(p.c);
+                                float sv = v[j];
+                                if (p.accumulate) sv += __half2float(cp[off + j]);
+                                cp[off + j] = __float2half_rn(sv);
+                            } else {
+                                float* cp = reinterpret_cast<float*>(p.c);
+                                float sv = v[j];
+                                if (p.accumulate) sv += cp[off + j];
+                                cp[off + j] = sv;
+                            }
                         }
                     }
                 }

@@ -254,7 +254,13 @@ int auto_kernel(int M, int N, int K, int G, bool a_is_f16, bool indirect, int sp
     // a wave of 256-column tiles, no K slices asked for) take the 256-column kernel, whose weights enter the tensor
     // core rounded to FP16 as in the reference's batched route; the others the exact-weight kernel, which can split K.
     if (M >= kTcwFromRows && G == 128 && N >= 128 && !indirect) {
-        const bool wide = (N + twm::tcr::NT - 1) / twm::tcr::NT >= kDefaultSms / 2 && splits_override <= 1;
+        // Measured on K=3584 (us, 128 / 256 rows): N=37888: tcr 43 / 60, tcw 56 / 111; N=28416: 44 / 60 against 56 / 112;
+        // N=18944: 44 / 59 against 32 / 60; N=9472: 42 / 56 against 30 / 60; N=4608: 41 / 55 against 29 / 59.  And K=18944,
+        // N=3584: tcr 182 (14 tiles, no K slices), tcw 64 in five slices.  So: more than one wave of 128-column
+        // tiles, or more than 128 rows, goes to the 256-column kernel unless K is long and the tiles are few.
+        const int tiles_w = (N + twm::tcw::NT - 1) / twm::tcw::NT, tiles_r = (N + twm::tcr::NT - 1) / twm::tcr::NT;
+        const bool long_k_few_tiles = K >= 8192 && 4 * tiles_r <= kDefaultSms;
+        const bool wide = (tiles_w > kDefaultSms || M > twm::tcw::MB) && !long_k_few_tiles && splits_override <= 1;
         return wide ? TWM_KERNEL_TCR : TWM_KERNEL_TCW;
     }
     return M >= kTcFromRows ? TWM_KERNEL_TC : TWM_KERNEL_MMA;
@@ -555,6 +561,15 @@ twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int split
         bps = (nkb + splits_override - 1) / splits_override;
         bps = (bps + align - 1) / align * align;
         if (bps > max_bps) return TWM_EINVAL;
+        splits = (nkb + bps - 1) / bps;
+    } else if (kernel == TWM_KERNEL_TCW) {
+        // Measured (128 rows): a 128-K stage costs about 0.8 us, a K slice about 7 us of its own (partials out, count,
+        // the last arriver's sum).  Slices pay only with few tiles and a long K: N=3584, K=18944: 124 us unsplit,
+        // 64 us in five slices; N=3584, K=3584: 29 us unsplit, 36 us in two.
+        const int stages = nkb / align;
+        int want = 1;
+        if (stages >= 64 && 2 * n_tiles <= slots) want = std::min(std::min(slots / n_tiles, stages / 28), kMaxSplits);
+        bps = (stages + want - 1) / want * align;
         splits = (nkb + bps - 1) / bps;
     } else {
         choose_splits(n_tiles, nkb, slots, sm_count, max_bps, align, can_cluster ? twm::mma::MAX_CLUSTER / rows : kMaxSplits,

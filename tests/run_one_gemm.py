@@ -33,7 +33,7 @@ def one_gemm(args) -> None:
     a = torch.randn((args.m, args.k), generator=gen, device=dev).to(a_dtype)
     c = torch.empty((args.m, args.n), dtype=a_dtype, device=dev)
     kern = KERNELS[args.kernel]
-    ws = q.Workspace(max(q.plan(args.m, args.n, args.k, args.group, kernel_override=kern).workspace_bytes, 16), dev)
+    ws = q.Workspace(max(q.plan(args.m, args.n, args.k, args.group, kernel_override=kern, splits_override=args.splits).workspace_bytes, 16), dev)
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -41,11 +41,12 @@ def one_gemm(args) -> None:
             if i == 1:
                 e0.record(stream)
             q.gemm_tw_marlin(a, packed, scales, c, args.m, args.n, args.k, group_size=args.group, workspace=ws,
-                             flags=_lib.TWM_FLAG_PDL, kernel_override=kern)
+                             flags=_lib.TWM_FLAG_PDL, kernel_override=kern, splits_override=args.splits)
         e1.record(stream)
         torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / max(args.launches, 1)
-    print(f"m={args.m} k={args.k} n={args.n} group={args.group} kernel={args.kernel}: {us:.2f} us per GEMM "
+    pl = q.plan(args.m, args.n, args.k, args.group, kernel_override=kern, splits_override=args.splits)
+    print(f"m={args.m} k={args.k} n={args.n} group={args.group} kernel={args.kernel} (plan: kernel {pl.kernel}, {pl.grid_x} tiles x {pl.splits} K slices): {us:.2f} us per GEMM "
           f"(eager launches, cold start included), error word {q.device_error():#x}")
 
 
@@ -88,6 +89,7 @@ def main() -> None:
     ap.add_argument("--group", type=int, default=128)
     ap.add_argument("--kernel", default="auto", choices=sorted(KERNELS))
     ap.add_argument("--launches", type=int, default=4)
+    ap.add_argument("--splits", type=int, default=0, help="K slices (0 = the plan's choice)")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--tp", type=int, default=0)
     ap.add_argument("--tp-layers", type=int, default=3)

@@ -223,7 +223,8 @@ def test_wide_tensor_core_kernel(m, k, n, splits):
     assert np.array_equal(y32.astype(np.float16).astype(np.float32), y16)          # one rounding, at the end
     again = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float32, kernel_override=kern, splits_override=splits)
     assert np.array_equal(again, y32)                                              # fixed summation order
-    assert q.plan(m, n, k, group).kernel == (kern if m >= 65 else _lib.TWM_KERNEL_TC)       # the heuristic's choice
+    # the heuristic's choice at these narrow shapes: this kernel for 65 ... 128 rows, the 256-column kernel beyond
+    assert q.plan(m, n, k, group).kernel == (_lib.TWM_KERNEL_TCR if m > 128 else (kern if m >= 65 else _lib.TWM_KERNEL_TC))
 
 
 @pytest.mark.parametrize("kind", ["silu", "geglu"])
@@ -341,7 +342,8 @@ def test_m_beyond_eight(m, group):
     _, packed, scales = _quantised(k, n, group, 47)
     a = seeded_activations(m, k, 0)
     y = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float16)
-    assert rel_err_floored(y, oracle.w4a16_f64(a, packed, scales, m, n, k, group)) < TOL_F16
+    # (130 rows at group 128 run on the 256-column kernel: adjudicated by the FP16-weight oracle)
+    assert rel_err_floored(y, _tc_ref(a, packed, scales, m, n, k, group, q.plan(m, n, k, group).kernel)) < TOL_F16
     assert _abs_err_over_rms(y, oracle.w4a16_f64(a, packed, scales, m, n, k, group)) < TC_ABS_VS_EXACT
     # FP32 rows from the FP32-FMA kernel agree too (m > 8 there is served by several launches)
     y32 = _run_gemm(a, packed, scales, m, n, k, group, torch.float32, torch.float32)
@@ -398,9 +400,12 @@ def test_tensor_core_kernel_with_tiny_activation_rows(m):
     a = a.astype(np.float16).astype(np.float32)
     y = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float32)
     ref = oracle.w4a16_f64(a, packed, scales, m, n, k, group)
+    # (200 rows run on the 256-column kernel, whose weights are rounded to FP16: the same relative bound
+    #  for every row, tiny or not, only a larger one)
+    bound = 2e-3 if q.plan(m, n, k, group).kernel == _lib.TWM_KERNEL_TCR else 1e-4
     for row in (0, 1, m - 1):
         rms = float(np.sqrt(np.mean(ref[row] ** 2)))
-        assert float(np.max(np.abs(y[row] - ref[row]))) < 1e-4 * rms, row
+        assert float(np.max(np.abs(y[row] - ref[row]))) < bound * rms, row
 
 
 def test_config0_shape_vs_literal_cpu_path():
