@@ -21,7 +21,8 @@ TOL_F32 = 1e-3
 # fewer guard bits than an IEEE fused multiply-add chain (about 1e-6 of the output RMS observed);
 # still two orders below the FP16 rounding of the final store
 TOL_TC_F32 = 5e-3
-# Every kernel multiplies exact weights f32(scale) * (nibble - 8) by the activations as they are.
+# Every kernel but the 256-column tcgen05 one multiplies exact weights f32(scale) * (nibble - 8) by the
+# activations as they are (that one rounds the weights to FP16: see _tc_ref).
 # Absolute bounds in units of the output RMS, on top of the relative test: FP16 output (its own
 # rounding), and FP32 output of the tensor-core kernels (the accumulator's truncation adds up
 # along K: 6.4e-6 seen at K = 3584 over 200 000 outputs).
