@@ -292,7 +292,7 @@ def test_gated_activation_prologue_refusals():
         assert e.value.status == _lib.TWM_EINVAL
 
 
-@pytest.mark.parametrize("m", [65, 100, 128, 129, 256])
+@pytest.mark.parametrize("m", [65, 100, 128, 129, 256, 300])
 @pytest.mark.parametrize("k,n", [(256, 256), (512, 300), (1024, 1000), (3584, 768)])
 def test_256_column_tensor_core_kernel(m, k, n):
     """The 256-column tcgen05 kernel (TWM_KERNEL_TCR): weights rounded to FP16 as the reference's batched
