@@ -242,6 +242,7 @@ gemm_kernel(const __grid_constant__ GemmParams p)
         const int quarter = warp & 3, cpart = warp >> 2;
         ok = ok && tc::wait_uniform(&sm.d_full, 0, abort_flag);
         tc::tc_fence_after();
+        pdl_wait_prior_grids();                                // C may be read (or, with the accumulate flag, was written) by a kernel before
         ok = ok && (*abort_flag == 0);
         const int nb = n0 + cpart * RCOLS;
 #pragma unroll 1
