@@ -261,6 +261,9 @@ struct GemmParams {
     alignas(64) CUtensorMap packed_map;
     // tcgen05 kernel: tensor map over the launch's permuted activations, f16 [K/8][rows][8]
     alignas(64) CUtensorMap act_map;
+    // streaming kernel from nine rows on: the pre-pass's B fragments [K/32][rows16][4][16 B] and group sums [K/group][rows16]
+    const uint8_t* rows_b;
+    const float* rows_asum;
 };
 
 // ---- row-parallel output pushed to the tensor-parallel peers (GemmParams::n_peers != 0) ----

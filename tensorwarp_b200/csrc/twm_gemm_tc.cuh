@@ -512,11 +512,28 @@ gemm_kernel(const __grid_constant__ GemmParams p)
             if (sm.is_last) {
                 __threadfence();
                 if (owner && *abort_flag == 0) {
-                    for (int m = row0; m < min(p.M, row0 + RC); ++m) {
-                        float s = 0.0f;
-                        for (int sp = 0; sp < p.splits; ++sp)
-                            s += ld_cg_f32(&p.ws_partials[((size_t)sp * p.M + m) * p.N + n]);
-                        store_c(m, s);
+                    // slices in slice order; four rows x four slices of loads in flight together (one load at
+                    // a time is a round trip to L2 per row and slice: 45 us of a 49 us launch at 32 rows, 7 slices)
+                    const int mend = min(p.M, row0 + RC);
+                    for (int m0 = row0; m0 < mend; m0 += 4) {
+                        float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                        for (int sp0 = 0; sp0 < p.splits; sp0 += 4) {
+                            float v[4][4];
+#pragma unroll
+                            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                                for (int e = 0; e < 4; ++e)
+                                    v[u][e] = (sp0 + u < p.splits && m0 + e < mend)
+                                                  ? ld_cg_f32(&p.ws_partials[((size_t)(sp0 + u) * p.M + m0 + e) * p.N + n]) : 0.0f;
+#pragma unroll
+                            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                                for (int e = 0; e < 4; ++e)
+                                    if (sp0 + u < p.splits) s[e] += v[u][e];
+                        }
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (m0 + e < mend) store_c(m0 + e, s[e]);
                     }
                 }
                 if (tid == WARP_READ0 * 32) atomicExch(&p.ws_counters[blockIdx.x], 0u);

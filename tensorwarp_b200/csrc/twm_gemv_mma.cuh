@@ -48,7 +48,19 @@ constexpr int SB = TWM_MMA_SB;            // 32-blocks per ring stage
 constexpr int STAGES = TWM_MMA_STAGES;
 constexpr int CONSUMER_WARPS = 8;
 constexpr int CONSUMERS = CONSUMER_WARPS * 32;
-constexpr int THREADS = CONSUMERS + 64;      // + producer warp + stager warp
+// + producer warp + stager warps: one stager keeps up with one or two activation rows, four rows take three and
+// eight take four (a stager's round is a global load, a permute and a group sum per lane, and every CTA stages
+// all rows of its K range).  Measured on K=3584, N=37888: four rows 20.7 us with one stager, 17.0 with two, 16.3
+// with three; eight rows 34.5 / 22.4 (three) / 19.0 (four), no gain from six or seven.
+#ifndef TWM_MMA_SW4
+#define TWM_MMA_SW4 3
+#endif
+#ifndef TWM_MMA_SW8
+#define TWM_MMA_SW8 4
+#endif
+__host__ __device__ constexpr int stager_warps(int mp) { return mp >= 8 ? TWM_MMA_SW8 : (mp >= 4 ? TWM_MMA_SW4 : 1); }
+__host__ __device__ constexpr int threads_for(int mp) { return CONSUMERS + 32 + 32 * stager_warps(mp); }
+constexpr int THREADS = threads_for(1);
 constexpr int B_BUF_BYTES = 4096;            // staged activations per chunk buffer
 constexpr int ASUM_GROUPS = 64;              // scale groups per chunk, at most
 #ifndef TWM_MMA_MAX_CLUSTER
@@ -143,7 +155,7 @@ __device__ __forceinline__ uint4 load_act8(const __half* p8, int up_offset, int 
 // MP = activation rows staged (power of two >= M, <= 8); GSHIFT = log2(32-blocks per scale group);
 // AKIND = what the activation rows hold (0: f16 values; 1 / 2: [gate | up], see load_act8)
 template <int MP, int GSHIFT, int AKIND = 0>
-__global__ void __launch_bounds__(THREADS, TWM_MMA_MIN_CTAS)
+__global__ void __launch_bounds__(threads_for(MP), TWM_MMA_MIN_CTAS)
 gemv_kernel(const __grid_constant__ GemmParams p)
 {
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -168,7 +180,8 @@ gemv_kernel(const __grid_constant__ GemmParams p)
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], CONSUMER_WARPS); }
-        for (int s = 0; s < 2; ++s) { mbar_init(&sm.b_full[s], 1); mbar_init(&sm.b_empty[s], CONSUMER_WARPS); }
+        // a chunk of activations is full once every stager warp has arrived
+        for (int s = 0; s < 2; ++s) { mbar_init(&sm.b_full[s], stager_warps(MP)); mbar_init(&sm.b_empty[s], CONSUMER_WARPS); }
         sm.abort_flag = 0;
         sm.is_last = 0;
         mbar_fence_init();
@@ -250,8 +263,8 @@ gemv_kernel(const __grid_constant__ GemmParams p)
         // A launch that does not wait for its predecessor must still not END before it: the kernel
         // after this one waits for this one only.  This warp has nothing left to do.
         if (p.no_wait) pdl_wait_prior_grids();
-    } else if (warp == CONSUMER_WARPS + 1) {
-        // ------------------------------------------------ activation stager --
+    } else if (warp > CONSUMER_WARPS) {
+        // ----------------------------------------------- activation stagers --
         // One item = 8 consecutive K of one row, stored as the 16 bytes
         // {k0,k4 | k2,k6 | k1,k5 | k3,k7}: the B fragments of the block's two MMAs.
         // Items are numbered so that the 4 << gshift lanes that hold one (scale
@@ -262,7 +275,9 @@ gemv_kernel(const __grid_constant__ GemmParams p)
         const __half* A = A_base;
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(A) & 15) == 0) && ((p.lda & 7) == 0) &&
                             ((p.a_expert_stride & 7) == 0);
-        constexpr int PF = 8;
+        constexpr int SW = stager_warps(MP);
+        constexpr int PF = 8 / SW + (8 % SW ? 1 : 0);        // rounds of 32 items a warp has in flight; a chunk has eight
+        const int sw = warp - CONSUMER_WARPS - 1;            // stager warp sw takes rounds sw, sw + SW, ...
         for (int chunk = 1; chunk < n_chunks; ++chunk) {     // chunk 0 is staged by the consumer warps (below)
             const int buf = chunk & 1;
             const int use = chunk >> 1;
@@ -270,12 +285,12 @@ gemv_kernel(const __grid_constant__ GemmParams p)
             const int cb = min(CHUNK_BLOCKS, total_blocks - cb0);
             const int items = cb * MP * 4;                    // item = (((gi * MP) + m) << gshift | bj) * 4 + t
             bool waited = false, ok = true;
-            for (int base = 0; base < items && ok; base += 32 * PF) {
-                const int live = min(PF, (items - base + 31) >> 5);     // rounds of 32 items that hold anything (warp-uniform)
+            for (int base = sw * 32; base < items && ok; base += 32 * SW * PF) {
+                const int live = min(PF, (items - base + 32 * SW - 1) / (32 * SW));     // rounds of 32 items that hold anything (warp-uniform)
                 uint4 x[PF];
 #pragma unroll
                 for (int u = 0; u < PF; ++u) {
-                    const int it = base + u * 32 + lane;
+                    const int it = base + u * 32 * SW + lane;
                     x[u] = make_uint4(0, 0, 0, 0);
                     if (u < live && it < items) {
                         const int tt = it & 3;
@@ -299,7 +314,7 @@ gemv_kernel(const __grid_constant__ GemmParams p)
 #pragma unroll
                 for (int u = 0; u < PF; ++u) {
                     if (u >= live) break;                            // nothing in the later rounds: skip their shuffles too
-                    const int it = base + u * 32 + lane;
+                    const int it = base + u * 32 * SW + lane;
                     const int tt = it & 3;
                     const int bj = (it >> 2) & gmask;
                     const int rest = it >> (2 + gshift);
@@ -326,6 +341,12 @@ gemv_kernel(const __grid_constant__ GemmParams p)
                     }
                     if (it < items && (it & ((4 << gshift) - 1)) == 0) sm.asum8[buf][gi][m] = -8.0f * s;
                 }
+            }
+            if (ok && !waited && use > 0) {
+                // a warp with no item in a ragged last chunk still waits for the buffer's turn: its arrival
+                // must not be counted into the phase of the chunk that used the buffer before
+                const bool got = mbar_wait_bounded(&sm.b_empty[buf], (use - 1) & 1, abort_flag);
+                if (!__all_sync(0xffffffffu, got)) ok = false;
             }
             if (!ok) break;
             __syncwarp();
@@ -378,7 +399,8 @@ gemv_kernel(const __grid_constant__ GemmParams p)
         }
         if (it < items && (it & ((4 << gshift) - 1)) == 0) sm.asum8[0][gi][m] = -8.0f * s;
         named_bar_sync(1, CONSUMERS);
-        if (tid == 0) mbar_arrive(&sm.b_full[0]);
+        if (tid == 0)
+            for (int i = 0; i < stager_warps(MP); ++i) mbar_arrive(&sm.b_full[0]);      // the consumers stand in for every stager warp
     }
     const float zero4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     const uint32_t w_base = smem_u32(&sm.packed[0][0]) + wcol * kBlockBytes + lane * 4;
@@ -541,13 +563,332 @@ gemv_kernel(const __grid_constant__ GemmParams p)
     named_bar_sync(1, CONSUMERS);
     if (!sm.is_last) return;
     __threadfence();
-    auto finish = [&](int m, int n) {
+    // The last arriver adds the slices in slice order, four slices' loads of all four outputs in flight together
+    // (one load per slice in turn costs a round trip to L2 per slice and output).
+    const int ms[4] = {mA, mB, mA, mB}, ns[4] = {nA, nA, nB, nB};
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int sp0 = 0; sp0 < p.reduce_slices; sp0 += 4) {
+        float v[4][4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                v[u][e] = (sp0 + u < p.reduce_slices && ms[e] < p.M && ns[e] < p.N) ? ld_cg_f32(ws_at(sp0 + u, ms[e], ns[e])) : 0.0f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (sp0 + u < p.reduce_slices) acc[e] += v[u][e];
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) store_c(ms[e], ns[e], acc[e]);
+    if (tid == 0) atomicExch(&p.ws_counters[blockIdx.x], 0u);
+}
+
+
+// ------------------------------------------------------------ 9 to 32 rows --
+// The same multiply with two or four MMA N-tiles of eight rows per block.  Here every CTA staging every
+// row itself would cost more than the multiply (16 rows of K = 3584 are 114 KB per CTA), so a pre-pass
+// (stage_rows_kernel) writes the B fragments and the group sums once, in the stagers' layout, to the
+// workspace, and one lane per CTA copies a ring stage's share of them with bulk copies, next to the
+// producer warp's weights.  Arithmetic and summation order are those of gemv_kernel.
+
+constexpr int rows_stages(int mp) { return mp <= 8 ? 5 : (mp <= 16 ? 4 : 3); }    // ring depth that leaves two CTAs per SM
+
+template <int MP>
+struct RowsSmem {
+    static constexpr int ST = rows_stages(MP);
+    alignas(128) uint8_t packed[ST][SB * NT * kBlockBytes];
+    alignas(128) uint16_t scales[ST][SB][NT];
+    alignas(128) uint8_t b[ST][SB * MP * 64];            // [block in stage][row m < MP][t] x 16 bytes
+    alignas(16) float asum8[ST][SB * MP];                // [group in stage][row]: -8 * sum of the group's activations
+    alignas(8) uint64_t full[ST];
+    alignas(8) uint64_t empty[ST];
+    alignas(8) uint64_t b_full[ST];
+    int abort_flag;
+    int is_last;
+};
+
+// One thread per item (8 consecutive K of one row), numbered as the stager warps number them, so that the
+// lanes of one (scale group, row) are consecutive and the group sum is the same fixed-order shuffle tree.
+// bq: [K/32][MP][4][16 B]; asum: [K/group][MP].  Rows M..MP-1 are written as zeros.
+template <int GSHIFT, int AKIND>
+__global__ void __launch_bounds__(256)
+stage_rows_kernel(uint8_t* __restrict__ bq, float* __restrict__ asum, const __half* __restrict__ A, long lda, int M, int MP,
+                  int K, int nkb)
+{
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    constexpr int gshift = GSHIFT;
+    constexpr int gmask = (1 << gshift) - 1;
+    const int it = blockIdx.x * blockDim.x + threadIdx.x;
+    const int items = nkb * MP * 4;                          // a multiple of 32: whole warps are in or out
+    if (it >= items) return;
+    const int tt = it & 3;
+    const int bj = (it >> 2) & gmask;
+    const int rest = it >> (2 + gshift);
+    const int m = rest % MP;
+    const int gi = rest / MP;
+    const int bi = (gi << gshift) + bj;
+    const bool vec_ok = ((reinterpret_cast<uintptr_t>(A) & 15) == 0) && ((lda & 7) == 0);
+    uint4 x = make_uint4(0, 0, 0, 0);
+    if (m < M) x = load_act8(A + (size_t)m * lda + (size_t)bi * kBlockK + tt * 8, K, AKIND, vec_ok);
+    uint4 o;
+    o.x = __byte_perm(x.x, x.z, 0x5410); o.y = __byte_perm(x.y, x.w, 0x5410);
+    o.z = __byte_perm(x.x, x.z, 0x7632); o.w = __byte_perm(x.y, x.w, 0x7632);
+    *reinterpret_cast<uint4*>(bq + ((size_t)(bi * MP + m) * 4 + tt) * 16) = o;
+    const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&x.x));
+    const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&x.y));
+    const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&x.z));
+    const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&x.w));
+    float s = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    if (gshift != 0) {
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        s += __shfl_xor_sync(0xffffffffu, s, 8);
+    }
+    if ((it & ((4 << gshift) - 1)) == 0) asum[(size_t)gi * MP + m] = -8.0f * s;
+}
+
+// MP = 16 or 32 rows staged; GSHIFT as above.  p.rows_b / p.rows_asum: the pre-pass's output.
+template <int MP, int GSHIFT>
+__global__ void __launch_bounds__(THREADS, TWM_MMA_MIN_CTAS)
+gemm_rows_kernel(const __grid_constant__ GemmParams p)
+{
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    using Sm = RowsSmem<MP>;
+    Sm& sm = *reinterpret_cast<Sm*>(smem_raw);
+    constexpr int ST = Sm::ST;
+    constexpr int NTL = MP / 8;                              // MMA N-tiles of eight rows
+    constexpr int GB = 1 << GSHIFT;
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int n0 = blockIdx.x * NT;
+    const int cols = min(NT, p.N - n0);
+    const int b0 = blockIdx.y * p.blocks_per_split;
+    const int b1 = min(p.nkb, b0 + p.blocks_per_split);
+    const int total_blocks = b1 - b0;
+    const int n_stages = (total_blocks + SB - 1) / SB;
+
+    if (tid == 0) {
+        for (int s = 0; s < ST; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], CONSUMER_WARPS); mbar_init(&sm.b_full[s], 1); }
+        sm.abort_flag = 0;
+        sm.is_last = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+    volatile int* abort_flag = &sm.abort_flag;
+
+    float tot[NTL][4];
+#pragma unroll
+    for (int nt = 0; nt < NTL; ++nt) { tot[nt][0] = tot[nt][1] = tot[nt][2] = tot[nt][3] = 0.0f; }
+    const int g = lane >> 2;
+    const int t = lane & 3;
+    const int wcol = warp * 16;
+    if (warp == CONSUMER_WARPS) {
+        // -------------------------- producer: packed + scales (weights are constants: no wait) --
+        const uint8_t* packed = p.packed;
+        const uint16_t* scales = p.scales;
+        const bool scale_bulk_ok = ((cols & 7) == 0) && ((p.N & 7) == 0) &&
+                                   ((reinterpret_cast<uintptr_t>(scales + n0) & 15) == 0);
+        for (int it = 0; it < n_stages; ++it) {
+            const int slot = it % ST;
+            const int use = it / ST;
+            if (use > 0) {
+                const bool got = mbar_wait_bounded(&sm.empty[slot], (use - 1) & 1, abort_flag);
+                if (!__all_sync(0xffffffffu, got)) break;
+            }
+            const int bstart = b0 + it * SB;
+            const int nb = min(SB, b1 - bstart);
+            const int srow_first = bstart >> GSHIFT;
+            const int nrows = ((bstart + nb - 1) >> GSHIFT) - srow_first + 1;
+            uint32_t tx = (uint32_t)nb * cols * kBlockBytes;
+            if (scale_bulk_ok) {
+                tx += (uint32_t)nrows * cols * 2;
+            } else {
+                for (int r = 0; r < nrows; ++r) {
+                    const uint16_t* src = scales + (size_t)(srow_first + r) * p.N + n0;
+                    for (int cidx = lane; cidx < cols; cidx += 32) sm.scales[slot][r][cidx] = src[cidx];
+                }
+                __syncwarp();
+            }
+            const bool tiled = (p.map_rows == SB) && (nb == SB);
+            if (tiled) tx = (uint32_t)SB * NT * kBlockBytes + (scale_bulk_ok ? (uint32_t)nrows * cols * 2 : 0u);
+            if (lane == 0) {
+                mbar_arrive_expect_tx(&sm.full[slot], tx);
+                if (tiled) tma_load_2d(&sm.packed[slot][0], &p.packed_map, n0 * 2, bstart, &sm.full[slot]);
+            }
+            __syncwarp();
+            if (!tiled && lane < nb) {
+                bulk_g2s(&sm.packed[slot][lane * NT * kBlockBytes],
+                         packed + ((size_t)(bstart + lane) * p.N + n0) * kBlockBytes,
+                         (uint32_t)cols * kBlockBytes, &sm.full[slot]);
+            } else if (scale_bulk_ok && lane >= 16 && lane - 16 < nrows) {
+                const int r = lane - 16;
+                bulk_g2s(&sm.scales[slot][r][0], scales + (size_t)(srow_first + r) * p.N + n0,
+                         (uint32_t)cols * 2, &sm.full[slot]);
+            }
+            __syncwarp();
+        }
+        prefetch_next_head(p.next, blockIdx.x + gridDim.x * blockIdx.y, gridDim.x * gridDim.y, lane);
+    } else if (warp == CONSUMER_WARPS + 1) {
+        // ------------- staged activations: one lane, two bulk copies per ring stage, after the pre-pass --
+        pdl_wait_prior_grids();
+        if (lane == 0) {
+            for (int it = 0; it < n_stages; ++it) {
+                const int slot = it % ST;
+                const int use = it / ST;
+                if (use > 0 && !mbar_wait_bounded(&sm.empty[slot], (use - 1) & 1, abort_flag)) break;
+                const int bstart = b0 + it * SB;
+                const int nb = min(SB, b1 - bstart);
+                const int ngroups = (nb + GB - 1) >> GSHIFT;
+                const uint32_t b_bytes = (uint32_t)nb * MP * 64, s_bytes = (uint32_t)ngroups * MP * 4;
+                mbar_arrive_expect_tx(&sm.b_full[slot], b_bytes + s_bytes);
+                bulk_g2s(&sm.b[slot][0], p.rows_b + (size_t)bstart * MP * 64, b_bytes, &sm.b_full[slot]);
+                bulk_g2s(&sm.asum8[slot][0], p.rows_asum + (size_t)(bstart >> GSHIFT) * MP, s_bytes, &sm.b_full[slot]);
+            }
+        }
+    } else {
+    // ---------------------------------------------------------- consumers --
+    pdl_wait_prior_grids();          // their stores and workspace traffic come after the launch before
+    const float zero4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const uint32_t w_base = smem_u32(&sm.packed[0][0]) + wcol * kBlockBytes + lane * 4;
+    const uint32_t s_base = smem_u32(&sm.scales[0][0][0]) + (wcol + g) * 2;
+    const uint32_t b_base = smem_u32(&sm.b[0][0]) + (g * 4 + t) * 16;
+    const uint32_t a8_base = smem_u32(&sm.asum8[0][0]) + t * 8;
+    bool ok = true;
+    for (int it = 0; it < n_stages; ++it) {
+        const int slot = it % ST;
+        const int nb = min(SB, b1 - (b0 + it * SB));
+        if (ok) {
+            const bool got = mbar_wait_bounded(&sm.b_full[slot], (it / ST) & 1, abort_flag);
+            if (!__all_sync(0xffffffffu, got)) ok = false;
+        }
+        if (ok) {
+            const bool got = mbar_wait_bounded(&sm.full[slot], (it / ST) & 1, abort_flag);
+            if (!__all_sync(0xffffffffu, got)) ok = false;
+        }
+        if (ok) {
+            const uint32_t w_st = w_base + slot * (SB * NT * kBlockBytes);
+            const uint32_t s_st = s_base + slot * (SB * NT * 2);
+            const uint32_t b_st = b_base + slot * (SB * MP * 64);
+            const uint32_t a8_st = a8_base + slot * (SB * MP * 4);
+#pragma unroll
+            for (int r0 = 0; r0 < SB; r0 += GB) {
+                if (r0 < nb) {
+                    float lo[NTL][4], hi[NTL][4];
+#pragma unroll
+                    for (int j = 0; j < GB; ++j) {
+                        const int r = r0 + j;
+                        const uint32_t v0 = lds32_at(w_st + r * (NT * kBlockBytes));          // column g, word t
+                        const uint32_t v1 = lds32_at(w_st + r * (NT * kBlockBytes) + 128);    // column g + 8, word t
+                        const uint32_t v0s = v0 >> 8, v1s = v1 >> 8;
+                        const uint32_t l0 = v0 & 0x000F000Fu, l1 = v1 & 0x000F000Fu, l2 = v0s & 0x000F000Fu, l3 = v1s & 0x000F000Fu;
+                        const uint32_t h0 = v0 & 0x00F000F0u, h1 = v1 & 0x00F000F0u, h2 = v0s & 0x00F000F0u, h3 = v1s & 0x00F000F0u;
+#pragma unroll
+                        for (int nt = 0; nt < NTL; ++nt) {
+                            const uint4 xb = lds128_at(b_st + r * (MP * 64) + nt * 512);      // rows 8 nt + g
+                            if (j == 0) {
+                                mma_m16n8k16(lo[nt], l0, l1, l2, l3, xb.x, xb.y, zero4);
+                                mma_m16n8k16(hi[nt], h0, h1, h2, h3, xb.z, xb.w, zero4);
+                            } else {
+                                mma_m16n8k16(lo[nt], l0, l1, l2, l3, xb.x, xb.y, lo[nt]);
+                                mma_m16n8k16(hi[nt], h0, h1, h2, h3, xb.z, xb.w, hi[nt]);
+                            }
+                        }
+                    }
+                    // group done: value = 2^24*lo + 2^20*hi - 8*sum(a), times the FP32 scale
+                    const float s0 = f16_bits_to_f32(lds16_at(s_st + (r0 >> GSHIFT) * (NT * 2)));
+                    const float s1 = f16_bits_to_f32(lds16_at(s_st + (r0 >> GSHIFT) * (NT * 2) + 16));
+                    const float k20 = 1048576.0f;                     // 2^20
+#pragma unroll
+                    for (int nt = 0; nt < NTL; ++nt) {
+                        const float2 a8 = lds64f_at(a8_st + (r0 >> GSHIFT) * (MP * 4) + nt * 32);
+                        tot[nt][0] = fmaf(s0, fmaf(fmaf(lo[nt][0], 16.0f, hi[nt][0]), k20, a8.x), tot[nt][0]);
+                        tot[nt][1] = fmaf(s0, fmaf(fmaf(lo[nt][1], 16.0f, hi[nt][1]), k20, a8.y), tot[nt][1]);
+                        tot[nt][2] = fmaf(s1, fmaf(fmaf(lo[nt][2], 16.0f, hi[nt][2]), k20, a8.x), tot[nt][2]);
+                        tot[nt][3] = fmaf(s1, fmaf(fmaf(lo[nt][3], 16.0f, hi[nt][3]), k20, a8.y), tot[nt][3]);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0 && ok) mbar_arrive(&sm.empty[slot]);
+    }
+    }   // consumers
+
+    // ----------------------------------------------------- store / split-K --
+    // lane (g, t): C[m = 8 nt + 2t, + 1][n = n0 + wcol + g] and the same rows for column + 8
+    if (warp >= CONSUMER_WARPS) return;
+    const int nA = n0 + wcol + g, nB = nA + 8;
+    auto store_c = [&](int m, int n, float v) {
         if (m >= p.M || n >= p.N) return;
-        float s = 0.0f;
-        for (int sp = 0; sp < p.reduce_slices; ++sp) s += ld_cg_f32(ws_at(sp, m, n));
-        store_c(m, n, s);
+        const size_t off = (size_t)m * p.ldc + n;
+        if (p.c_is_f16) {
+            __half* cp = reinterpret_cast<__half*>(p.c);
+            if (p.accumulate) v += __half2float(cp[off]);
+            cp[off] = __float2half_rn(v);
+        } else {
+            float* cp = reinterpret_cast<float*>(p.c);
+            if (p.accumulate) v += cp[off];
+            cp[off] = v;
+        }
     };
-    finish(mA, nA); finish(mB, nA); finish(mA, nB); finish(mB, nB);
+    named_bar_sync(1, CONSUMERS);
+    if (*abort_flag) return;          // a wait expired: leave C untouched, the error word is set
+    if (p.reduce_slices == 1) {
+#pragma unroll
+        for (int nt = 0; nt < NTL; ++nt) {
+            const int mA = nt * 8 + 2 * t, mB = mA + 1;
+            store_c(mA, nA, tot[nt][0]); store_c(mB, nA, tot[nt][1]); store_c(mA, nB, tot[nt][2]); store_c(mB, nB, tot[nt][3]);
+        }
+        return;
+    }
+    auto ws_at = [&](int sp, int m, int n) -> float* { return &p.ws_partials[((size_t)sp * p.M + m) * p.N + n]; };
+    const int my_slice = blockIdx.y;
+#pragma unroll
+    for (int nt = 0; nt < NTL; ++nt) {
+        const int mA = nt * 8 + 2 * t, mB = mA + 1;
+        if (mA < p.M && nA < p.N) *ws_at(my_slice, mA, nA) = tot[nt][0];
+        if (mB < p.M && nA < p.N) *ws_at(my_slice, mB, nA) = tot[nt][1];
+        if (mA < p.M && nB < p.N) *ws_at(my_slice, mA, nB) = tot[nt][2];
+        if (mB < p.M && nB < p.N) *ws_at(my_slice, mB, nB) = tot[nt][3];
+    }
+    __threadfence();
+    named_bar_sync(1, CONSUMERS);
+    if (tid == 0) {
+        const unsigned prev = atomicAdd(&p.ws_counters[blockIdx.x], 1u);
+        sm.is_last = (prev == (unsigned)(p.reduce_slices - 1));
+    }
+    named_bar_sync(1, CONSUMERS);
+    if (!sm.is_last) return;
+    __threadfence();
+    // the last arriver adds the slices in slice order, one N-tile's four outputs over four slices in flight together
+#pragma unroll
+    for (int nt = 0; nt < NTL; ++nt) {
+        const int mA = nt * 8 + 2 * t, mB = mA + 1;
+        const int ms[4] = {mA, mB, mA, mB}, ns[4] = {nA, nA, nB, nB};
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int sp0 = 0; sp0 < p.reduce_slices; sp0 += 4) {
+            float v[4][4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    v[u][e] = (sp0 + u < p.reduce_slices && ms[e] < p.M && ns[e] < p.N) ? ld_cg_f32(ws_at(sp0 + u, ms[e], ns[e])) : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (sp0 + u < p.reduce_slices) acc[e] += v[u][e];
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) store_c(ms[e], ns[e], acc[e]);
+    }
     if (tid == 0) atomicExch(&p.ws_counters[blockIdx.x], 0u);
 }
 

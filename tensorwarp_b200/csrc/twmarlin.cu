@@ -113,6 +113,15 @@ twm_status ensure_device(int* sm_count_out)
             raise_mma((const void*)twm::mma::gemv_kernel<1, 0, 2>);
             raise_mma((const void*)twm::mma::gemv_kernel<1, 2, 1>);
             raise_mma((const void*)twm::mma::gemv_kernel<1, 2, 2>);
+            auto raise_rows = [&](const void* fn, size_t bytes) {
+                if (r == cudaSuccess) r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+            };
+            raise_rows((const void*)twm::mma::gemm_rows_kernel<8, 0>, sizeof(twm::mma::RowsSmem<8>));
+            raise_rows((const void*)twm::mma::gemm_rows_kernel<8, 2>, sizeof(twm::mma::RowsSmem<8>));
+            raise_rows((const void*)twm::mma::gemm_rows_kernel<16, 0>, sizeof(twm::mma::RowsSmem<16>));
+            raise_rows((const void*)twm::mma::gemm_rows_kernel<16, 2>, sizeof(twm::mma::RowsSmem<16>));
+            raise_rows((const void*)twm::mma::gemm_rows_kernel<32, 0>, sizeof(twm::mma::RowsSmem<32>));
+            raise_rows((const void*)twm::mma::gemm_rows_kernel<32, 2>, sizeof(twm::mma::RowsSmem<32>));
             auto raise_chain = [&](const void* fn) {
                 if (r == cudaSuccess)
                     r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(twm::chain::Smem));
@@ -239,10 +248,22 @@ void choose_splits(int n_tiles, int nkb, int slots, int sm_count, int max_bps, i
 }
 
 int mmax_for(int M) { return M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : 8)); }
+// activation rows one launch of the streaming MMA kernel carries: up to eight staged by the CTAs themselves,
+// sixteen or thirty-two through the staging pre-pass
+int mma_rows_for(int M) { return M <= 8 ? 8 : (M <= 16 ? 16 : 32); }
+// Whether a launch of `rows` rows goes through the staging pre-pass.  From nine rows it must (the CTAs' own stager
+// warps stop at eight).  For three to eight rows both work: measured (us per GEMM, pre-pass / stager warps) on
+// K=3584 N=37888: 15.0 / 16.2 at 3 rows, 15.3 / 19.6 at 8; K=18944 N=3584: 15.3 / 15.4 and 15.8 / 17.0; but
+// K=3584 N=4608: 9.1 / 8.5 and 9.7 / 8.9 (the extra launch costs 0.6-0.8 us), hence the size threshold.
+bool mma_prepass(int rows, long K, long N) { return rows >= 9 || (rows >= 3 && K * N >= (1L << 26)); }
+// bytes of the staging pre-pass's output for `rows` rows: B fragments, then group sums
+size_t mma_rows_b_bytes(int rows, int K) { return (size_t)(K / 32) * mma_rows_for(rows) * 64; }
+size_t mma_rows_stage_bytes(int rows, int K, int group) { return mma_rows_b_bytes(rows, K) + (size_t)(K / group) * mma_rows_for(rows) * 4; }
 
-// Measured on the 7B gate+up shape (us per launch in a dependent chain): the streaming MMA kernel
-// 15.7 / 16.2 / 20.3 / 30.7 at M = 1 / 2 / 4 / 8, the tcgen05 kernel 26-27 for any M up to 16.
-constexpr int kTcFromRows = 5;
+// Measured (us per launch in a dependent chain, streaming MMA kernel / narrow tcgen05 kernel): 7B gate+up shape
+// 15.3 / 24.5 at 8 rows, 19.2 / 25.5 at 16, 30.7 / 31.2 at 32; K=3584 N=4608: 8.9 / 18.2, 13.3 / 27.5 and
+// 18.0 / 48.7 (the latter before its K-slice sum was pipelined); K=18944 N=3584: 17.0 / 27.2, 20.4 / 37.9, 31.9 / 62.6.
+constexpr int kTcFromRows = 33;
 // Measured on the 7B gate+up shape: 64 rows 51.6 us on the weight-stationary kernel against 58.0 on the wide one,
 // 96 rows 76 against 59, 128 rows 79 (as two launches of 64; one launch with a 128-row accumulator was no faster) against 60.
 constexpr int kTcwFromRows = 65;
@@ -263,7 +284,8 @@ int auto_kernel(int M, int N, int K, int G, bool a_is_f16, bool indirect, int sp
         const bool wide = (tiles_w > kDefaultSms || M > twm::tcw::MB) && !long_k_few_tiles && splits_override <= 1;
         return wide ? TWM_KERNEL_TCR : TWM_KERNEL_TCW;
     }
-    return M >= kTcFromRows ? TWM_KERNEL_TC : TWM_KERNEL_MMA;
+    // the streaming kernel reads per-expert offset tables only with its own stager warps (up to eight rows)
+    return (M >= kTcFromRows || (M > 8 && indirect)) ? TWM_KERNEL_TC : TWM_KERNEL_MMA;
 }
 
 int resolve_kernel(const twm_gemm_args* a)
@@ -271,17 +293,9 @@ int resolve_kernel(const twm_gemm_args* a)
     if (a->kernel_override != TWM_KERNEL_AUTO) return a->kernel_override;
     int kernel = auto_kernel(a->M, a->N, a->K, a->group_size, a->a_dtype == TWM_F16, a->packed_offsets != nullptr,
                              a->splits_override);
-    // five to eight rows: the tcgen05 kernel when the caller's workspace holds its pre-pass
-    // output, else the streaming kernel (which needs less or none)
     // pushing to tensor-parallel peers: the streaming kernel's cluster leaders push one or two rows, the
     // narrow tcgen05 kernel's read-back warps up to 64
     if (a->comm && a->a_dtype == TWM_F16) return a->M <= twm::mma::CLUSTER_ROWS ? TWM_KERNEL_MMA : TWM_KERNEL_TC;
-    if (kernel == TWM_KERNEL_TC && a->M <= 8) {
-        twm_plan_t pl;
-        if (twm_plan(a->M, a->N, a->K, a->group_size, kDefaultSms, a->splits_override, TWM_KERNEL_TC, &pl) != TWM_OK ||
-            !a->workspace || a->workspace_bytes < pl.workspace_bytes)
-            kernel = TWM_KERNEL_MMA;
-    }
     return kernel;
 }
 
@@ -352,7 +366,7 @@ twm_status launch_mma(const twm::GemmParams& p, int mp, dim3 grid, bool pdl, cud
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = grid;
-    cfg.blockDim = dim3(twm::mma::THREADS, 1, 1);
+    cfg.blockDim = dim3(twm::mma::threads_for(mp), 1, 1);       // more stager warps from four rows on
     cfg.dynamicSmemBytes = sizeof(twm::mma::Smem);
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
@@ -517,12 +531,42 @@ twm_status launch_prepass(__half* xp, const __half* a, long lda, int rows, int K
     return launch_op("permute_activations_kernel", twm::tc::permute_activations_kernel, dim3((items + 255) / 256), dim3(256), 0,
                      flags & TWM_FLAG_PDL, stream, xp, a, lda, rows, K / 8);
 }
+
+// 9..32 rows on the streaming MMA kernel: the pre-pass that stages the rows as B fragments, then the GEMM
+twm_status launch_mma_rows(twm::GemmParams& p, char* stage, dim3 grid, unsigned flags, cudaStream_t stream)
+{
+    const int mp = mma_rows_for(p.M);
+    p.rows_b = (const uint8_t*)stage;
+    p.rows_asum = (const float*)(stage + mma_rows_b_bytes(p.M, p.K));
+    const int items = p.nkb * mp * 4;
+    twm_status st;
+    if (p.group == 128)
+        st = launch_op("stage_rows_kernel", twm::mma::stage_rows_kernel<2, 0>, dim3((items + 255) / 256), dim3(256), 0,
+                       flags & TWM_FLAG_PDL, stream, (uint8_t*)stage, (float*)p.rows_asum, (const __half*)p.a, p.lda, p.M, mp, p.K, p.nkb);
+    else
+        st = launch_op("stage_rows_kernel", twm::mma::stage_rows_kernel<0, 0>, dim3((items + 255) / 256), dim3(256), 0,
+                       flags & TWM_FLAG_PDL, stream, (uint8_t*)stage, (float*)p.rows_asum, (const __half*)p.a, p.lda, p.M, mp, p.K, p.nkb);
+    if (st != TWM_OK) return st;
+    const size_t smem = mp == 8 ? sizeof(twm::mma::RowsSmem<8>) : (mp == 16 ? sizeof(twm::mma::RowsSmem<16>) : sizeof(twm::mma::RowsSmem<32>));
+    if (mp == 8)
+        return p.group == 128 ? launch_op("mma::gemm_rows_kernel", twm::mma::gemm_rows_kernel<8, 2>, grid, dim3(twm::mma::THREADS), smem, flags & TWM_FLAG_PDL, stream, p)
+                              : launch_op("mma::gemm_rows_kernel", twm::mma::gemm_rows_kernel<8, 0>, grid, dim3(twm::mma::THREADS), smem, flags & TWM_FLAG_PDL, stream, p);
+    if (mp == 16)
+        return p.group == 128 ? launch_op("mma::gemm_rows_kernel", twm::mma::gemm_rows_kernel<16, 2>, grid, dim3(twm::mma::THREADS), smem, flags & TWM_FLAG_PDL, stream, p)
+                              : launch_op("mma::gemm_rows_kernel", twm::mma::gemm_rows_kernel<16, 0>, grid, dim3(twm::mma::THREADS), smem, flags & TWM_FLAG_PDL, stream, p);
+    return p.group == 128 ? launch_op("mma::gemm_rows_kernel", twm::mma::gemm_rows_kernel<32, 2>, grid, dim3(twm::mma::THREADS), smem, flags & TWM_FLAG_PDL, stream, p)
+                          : launch_op("mma::gemm_rows_kernel", twm::mma::gemm_rows_kernel<32, 0>, grid, dim3(twm::mma::THREADS), smem, flags & TWM_FLAG_PDL, stream, p);
+}
 }  // namespace
 
 extern "C" {
 
-twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int splits_override,
-                    int kernel_override, twm_plan_t* out)
+}  // extern "C"
+
+namespace {
+// twm_plan; allow_prepass = false: the streaming MMA kernel without its staging pre-pass (up to eight rows)
+twm_status plan_impl(int M, int N, int K, int group_size, int sm_count, int splits_override,
+                     int kernel_override, bool allow_prepass, twm_plan_t* out)
 {
     if (!out || !shape_ok(M, N, K, group_size)) return TWM_EINVAL;
     if (splits_override < 0 || splits_override > kMaxSplits) return TWM_EINVAL;
@@ -548,7 +592,7 @@ twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int split
         return TWM_OK;
     }
     // rows one launch carries; more rows are served by further launches
-    const int rows = std::min(M, kernel == TWM_KERNEL_TC ? kTcRows : (kernel == TWM_KERNEL_TCW ? kTcwRows : 8));
+    const int rows = std::min(M, kernel == TWM_KERNEL_TC ? kTcRows : (kernel == TWM_KERNEL_TCW ? kTcwRows : (kernel == TWM_KERNEL_MMA ? mma_rows_for(M) : 8)));
     const int n_tiles = (N + twm::simt::NT - 1) / twm::simt::NT;
     const int slots = kernel == TWM_KERNEL_TCW ? sm_count
                                                : sm_count * ((kernel != TWM_KERNEL_SIMT || mmax_for(rows) <= 4) ? 2 : 1);
@@ -586,8 +630,23 @@ twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int split
     out->workspace_bytes = (splits > 1 && !cluster) ? kCounterBytes + (size_t)splits * rows * N * sizeof(float) : 0;
     if (kernel == TWM_KERNEL_TC || kernel == TWM_KERNEL_TCW)    // + the launch's activations in the MMA's K order, behind the split-K part
         out->workspace_bytes = kCounterBytes + (splits > 1 ? (size_t)splits * rows * N * sizeof(float) : 0) + 256 + (size_t)rows * K * 2;
+    if (kernel == TWM_KERNEL_MMA && mma_prepass(rows, K, N)) {      // + the rows staged as B fragments with their group sums
+        if (allow_prepass)
+            out->workspace_bytes = kCounterBytes + (splits > 1 ? (size_t)splits * rows * N * sizeof(float) : 0) + 256 + mma_rows_stage_bytes(rows, K, group_size);
+        else if (rows > 8)
+            return TWM_EINVAL;
+    }
     out->cluster_reduce = cluster ? 1 : 0;
     return TWM_OK;
+}
+}  // namespace
+
+extern "C" {
+
+twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int splits_override,
+                    int kernel_override, twm_plan_t* out)
+{
+    return plan_impl(M, N, K, group_size, sm_count, splits_override, kernel_override, true, out);
 }
 
 size_t twm_workspace_bytes(int M, int N, int K, int group_size)
@@ -631,15 +690,26 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
     const int kernel = resolve_kernel(a);
     if (kernel != TWM_KERNEL_SIMT && a->a_dtype != TWM_F16) return TWM_EINVAL;
     if (a->a_prologue != TWM_A_PLAIN && kernel != TWM_KERNEL_MMA) return TWM_EINVAL;
+    // streaming MMA kernel: three rows or more on a large matrix, and nine or more on any, are staged by a pre-pass
+    bool prepass = kernel == TWM_KERNEL_MMA && mma_prepass(std::min(a->M, mma_rows_for(a->M)), a->K, a->N);
+    if (prepass && (a->packed_offsets != nullptr || a->comm || a->a_prologue != TWM_A_PLAIN)) {
+        if (a->M > 8) return TWM_EINVAL;
+        prepass = false;                         // the CTAs' own stager warps
+    }
     twm_plan_t pl;
-    st = twm_plan(a->M, a->N, a->K, a->group_size, sm_count, a->splits_override, kernel, &pl);
+    st = plan_impl(a->M, a->N, a->K, a->group_size, sm_count, a->splits_override, kernel, prepass, &pl);
     if (st != TWM_OK) return st;
+    if (prepass && a->M <= 8 && (!a->workspace || a->workspace_bytes < pl.workspace_bytes)) {
+        prepass = false;                         // no room for the staged rows: the stager warps need none
+        st = plan_impl(a->M, a->N, a->K, a->group_size, sm_count, a->splits_override, kernel, false, &pl);
+        if (st != TWM_OK) return st;
+    }
     if (pl.workspace_bytes > 0 && (!a->workspace || a->workspace_bytes < pl.workspace_bytes) &&
         kernel != TWM_KERNEL_TC && a->splits_override == 0) {
         // The reference's call has no scratch argument (its split-K adds into C with atomics,
         // quantize.rs:1337-1357).  A caller that passes none still gets its GEMM: one K slice per
         // tile, nothing to add up, at the price of fewer CTAs on small N.
-        st = twm_plan(a->M, a->N, a->K, a->group_size, sm_count, 1, kernel, &pl);
+        st = plan_impl(a->M, a->N, a->K, a->group_size, sm_count, 1, kernel, prepass, &pl);
         if (st != TWM_OK) return st;
     }
     if (pl.workspace_bytes > 0) {
@@ -660,7 +730,7 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
     const size_t a_elt = a->a_dtype == TWM_F16 ? 2 : 4;
     const size_t c_elt = a->c_dtype == TWM_F16 ? 2 : 4;
     if ((kernel == TWM_KERNEL_TCW || kernel == TWM_KERNEL_TCR) && (a->packed_offsets != nullptr || a->comm)) return TWM_EINVAL;
-    const int row_step = kernel == TWM_KERNEL_TC ? kTcRows : (kernel == TWM_KERNEL_TCW ? kTcwRows : (kernel == TWM_KERNEL_TCR ? kTcrRows : 8));
+    const int row_step = kernel == TWM_KERNEL_TC ? kTcRows : (kernel == TWM_KERNEL_TCW ? kTcwRows : (kernel == TWM_KERNEL_TCR ? kTcrRows : (kernel == TWM_KERNEL_MMA ? mma_rows_for(a->M) : 8)));
     CUtensorMap packed_map;
     int map_rows = 0;
     if (a->packed_offsets == nullptr && a->N >= 128 && kernel != TWM_KERNEL_SIMT) {
@@ -737,6 +807,11 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
             if (st != TWM_OK) return st;
             st = launch_tc(p, rows, dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
         }
+        else if (kernel == TWM_KERNEL_MMA && prepass && rows >= 3) {
+            const size_t part_bytes = pl.splits > 1 ? (size_t)pl.splits * std::min(a->M, row_step) * a->N * sizeof(float) : 0;
+            char* stage = (char*)a->workspace + kCounterBytes + ((part_bytes + 255) / 256) * 256;
+            st = launch_mma_rows(p, stage, dim3(pl.grid_x, pl.grid_y, 1), a->flags, stream);
+        }
         else if (kernel == TWM_KERNEL_MMA)
             st = launch_mma(p, mmax_for(rows), dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
         else
@@ -769,8 +844,8 @@ twm_status twm_gemm_w4a16_static_ws(const twm_gemm_args* a, void* stream_)
     st = static_ws_address(&ws);
     if (st != TWM_OK) return st;
     // The call that will run: the caller's arguments with the built-in array as its workspace.  The
-    // kernel choice and the plan are made for THAT call (a workspace of this size can change the
-    // choice for five to eight rows), so the capacity check and the clearing below match what runs.
+    // kernel choice and the plan are made for THAT call (a workspace of this size decides
+    // whether three to eight rows are staged by a pre-pass), so the capacity check and the clearing below match what runs.
     twm_gemm_args b = *a;
     b.workspace = ws;
     b.workspace_bytes = kStaticWsBytes;
@@ -779,6 +854,11 @@ twm_status twm_gemm_w4a16_static_ws(const twm_gemm_args* a, void* stream_)
     twm_plan_t pl;
     st = twm_plan(a->M, a->N, a->K, a->group_size, sm_count, a->splits_override, kernel, &pl);
     if (st != TWM_OK) return st;
+    if (pl.workspace_bytes > kStaticWsBytes && kernel == TWM_KERNEL_MMA && a->M <= 8) {
+        // as twm_gemm_w4a16 will: up to eight rows can do without the staging pre-pass
+        st = plan_impl(a->M, a->N, a->K, a->group_size, sm_count, a->splits_override, kernel, false, &pl);
+        if (st != TWM_OK) return st;
+    }
     if (pl.workspace_bytes > kStaticWsBytes) {
         snprintf(t_last_error, sizeof(t_last_error),
                  "twm_gemm_w4a16_static_ws: this shape needs %zu bytes of split-K scratch, the built-in array holds %zu; "

@@ -336,6 +336,74 @@ def test_tc_kernel_rejects_f32_activations():
 
 
 @pytest.mark.parametrize("group", [32, 128])
+@pytest.mark.parametrize("splits", [0, 1, 3])
+@pytest.mark.parametrize("m", [9, 12, 16, 17, 31, 32, 40, 67])
+@pytest.mark.parametrize("k,n", [(256, 128), (512, 200), (2048, 1000), (3584, 136)])
+def test_streaming_kernel_nine_to_32_rows(m, k, n, splits, group):
+    """The warp-level-MMA kernel with its staging pre-pass (16- and 32-row launches, and what is left of
+    more rows): ragged N, ragged last ring stage, K slices through the workspace, both outputs."""
+    kern = _lib.TWM_KERNEL_MMA
+    _, packed, scales = _quantised(k, n, group, 51)
+    a = seeded_activations(m, k, 3)
+    ref = oracle.w4a16_f64(a, packed, scales, m, n, k, group)
+    y32 = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float32, kernel_override=kern, splits_override=splits)
+    assert rel_err_floored(y32, ref) < TOL_TC_F32 and _abs_err_over_rms(y32, ref) < TC_ABS_F32
+    y16 = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float16, kernel_override=kern, splits_override=splits,
+                    flags=_lib.TWM_FLAG_PDL)
+    assert np.array_equal(y32.astype(np.float16).astype(np.float32), y16)          # one rounding, at the end
+    # every row is computed as in a launch of up to eight rows: same products, same summation order
+    rows8 = np.concatenate([_run_gemm(a[m0:m0 + 8], packed, scales, min(8, m - m0), n, k, group, torch.float16, torch.float32,
+                                      kernel_override=kern, splits_override=splits)
+                            for m0 in range(0, m, 8)])
+    if splits != 0:                                                                # (the automatic slice count depends on the rows)
+        assert np.array_equal(rows8, y32)
+    # the heuristic's choice up to 32 rows
+    assert q.plan(min(m, 32), n, k, group).kernel == kern
+
+
+def test_streaming_kernel_staged_rows_on_a_large_matrix():
+    """Three to eight rows on a matrix of 2^26 weights or more go through the pre-pass as well; without room
+    for the staged rows in the workspace the CTAs' own stager warps do the same work: same bits."""
+    k, n, group = 3584, 18944, 128
+    _, packed, scales = _quantised(k, n, group, 52)
+    for m in (3, 5, 8):
+        a = seeded_activations(m, k, 4)
+        assert q.plan(m, n, k, group).workspace_bytes >= m * k * 2
+        staged = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float32, splits_override=1)
+        small = q.Workspace(16384 + 64)                                             # counters only: no room for the rows
+        own = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float32, ws=small, splits_override=1)
+        assert np.array_equal(staged, own)
+        ref = oracle.w4a16_f64(a, packed, scales, m, n, k, group)
+        assert rel_err_floored(staged, ref) < TOL_TC_F32 and _abs_err_over_rms(staged, ref) < TC_ABS_F32
+    # accumulate into C, and a second call gives the same bits
+    a = seeded_activations(12, k, 5)
+    base = _run_gemm(a, packed, scales, 12, n, k, group, torch.float16, torch.float32)
+    c = torch.ones((12, n), dtype=torch.float32, device=DEV)
+    ws = q.Workspace(q.workspace_bytes(12, n, k, group))
+    q.gemm_tw_marlin(_to_dev(a, torch.float16), _to_dev(packed), _to_dev(scales.view(np.float16)), c, 12, n, k, group_size=group,
+                     workspace=ws, flags=_lib.TWM_FLAG_ACCUMULATE)
+    torch.cuda.synchronize()
+    assert np.array_equal(c.cpu().numpy(), base + 1.0)
+    assert np.array_equal(_run_gemm(a, packed, scales, 12, n, k, group, torch.float16, torch.float32), base)
+
+
+def test_streaming_kernel_refuses_what_needs_its_own_stagers_beyond_eight_rows():
+    k, n, group, m = 512, 256, 128, 12
+    _, packed, scales = _quantised(k, n, group, 53)
+    a = _to_dev(seeded_activations(m, k, 0), torch.float16)
+    c = torch.empty((m, n), dtype=torch.float16, device=DEV)
+    p, s = _to_dev(packed), _to_dev(scales.view(np.float16))
+    with pytest.raises(_lib.TwmError):                                            # no workspace: nowhere to stage the rows
+        q.gemm_tw_marlin(a, p, s, c, m, n, k, group_size=group, kernel_override=_lib.TWM_KERNEL_MMA)
+    offs = torch.zeros(1, dtype=torch.int32, device=DEV)
+    # per-expert offset tables: the kernel's own stager warps only, so not beyond eight rows
+    args_ws = q.Workspace(q.workspace_bytes(m, n, k, group))
+    with pytest.raises(_lib.TwmError):
+        q.gemm_tw_marlin(a, p, s, c, m, n, k, group_size=group, workspace=args_ws, kernel_override=_lib.TWM_KERNEL_MMA,
+                         packed_offsets=offs, scales_offsets=offs, expert_idx=0)
+
+
+@pytest.mark.parametrize("group", [32, 128])
 @pytest.mark.parametrize("m", [9, 16, 19, 32, 33, 64, 70, 130])
 def test_m_beyond_eight(m, group):
     """The tcgen05 kernel's two accumulator widths (16, 32 rows) and more rows than one launch carries."""
@@ -370,7 +438,7 @@ def test_config2_shapes_beyond_eight_rows(m):
     packed = p.cpu().numpy()[:, cols].copy()
     scales = s.cpu().numpy().view(np.uint16)[:, cols].copy()
     chosen = q.plan(m, n, k, group).kernel
-    assert chosen == (_lib.TWM_KERNEL_TCR if m >= 65 else _lib.TWM_KERNEL_TC)
+    assert chosen == (_lib.TWM_KERNEL_TCR if m >= 65 else (_lib.TWM_KERNEL_TC if m >= 33 else _lib.TWM_KERNEL_MMA))
     ref = _tc_ref(a, packed, scales, m, 384, k, group, chosen)
     assert rel_err_floored(c[:, cols].float().cpu().numpy(), ref) < TOL_F16
     # whichever weights the kernel multiplies, the result is within 2e-3 of the output RMS of the exact-weight product

@@ -75,4 +75,7 @@ def test_static_scratch_rejects_oversized_plans():
     st = lib.twm_gemm_w4a16_static_ws(C.byref(args), torch.cuda.current_stream().cuda_stream)
     assert st == _lib.TWM_EWORKSPACE
     msg = lib.twm_last_error().decode()
-    assert str(cap) in msg and str(need) in msg
+    # (the size named is that of the plan the call would run: up to eight rows fall back from the staging
+    #  pre-pass to the kernel's own stager warps before giving up, which needs the split-K part only)
+    named = int(msg.split("needs ")[1].split(" bytes")[0])
+    assert str(cap) in msg and cap < named <= need
