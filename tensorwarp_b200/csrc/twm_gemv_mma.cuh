@@ -825,9 +825,12 @@ gemm_rows_kernel(const __grid_constant__ GemmParams p)
     // lane (g, t): C[m = 8 nt + 2t, + 1][n = n0 + wcol + g] and the same rows for column + 8
     if (warp >= CONSUMER_WARPS) return;
     const int nA = n0 + wcol + g, nB = nA + 8;
+    // tensor-parallel push: this launch's sequence number and buffer set (only the consumer kernel advances it)
+    const unsigned int comm_seq = p.n_peers ? ld_volatile_u32(p.comm_state) : 0u;
     auto store_c = [&](int m, int n, float v) {
         if (m >= p.M || n >= p.N) return;
         const size_t off = (size_t)m * p.ldc + n;
+        if (p.n_peers) { comm_store(p, comm_seq, off, v); return; }
         if (p.c_is_f16) {
             __half* cp = reinterpret_cast<__half*>(p.c);
             if (p.accumulate) v += __half2float(cp[off]);
@@ -839,12 +842,20 @@ gemm_rows_kernel(const __grid_constant__ GemmParams p)
         }
     };
     named_bar_sync(1, CONSUMERS);
-    if (*abort_flag) return;          // a wait expired: leave C untouched, the error word is set
+    // a wait expired: leave C untouched, the error word is set; with peers the CTA still counts itself, so that
+    // their consumers do not wait for this rank in vain
+    if (*abort_flag && !p.n_peers) return;
     if (p.reduce_slices == 1) {
+        if (*abort_flag == 0) {
 #pragma unroll
-        for (int nt = 0; nt < NTL; ++nt) {
-            const int mA = nt * 8 + 2 * t, mB = mA + 1;
-            store_c(mA, nA, tot[nt][0]); store_c(mB, nA, tot[nt][1]); store_c(mA, nB, tot[nt][2]); store_c(mB, nB, tot[nt][3]);
+            for (int nt = 0; nt < NTL; ++nt) {
+                const int mA = nt * 8 + 2 * t, mB = mA + 1;
+                store_c(mA, nA, tot[nt][0]); store_c(mB, nA, tot[nt][1]); store_c(mA, nB, tot[nt][2]); store_c(mB, nB, tot[nt][3]);
+            }
+        }
+        if (p.n_peers) {
+            named_bar_sync(1, CONSUMERS);
+            if (tid == 0) comm_cta_done(p, comm_seq, gridDim.x * gridDim.y);
         }
         return;
     }
@@ -890,6 +901,10 @@ gemm_rows_kernel(const __grid_constant__ GemmParams p)
         for (int e = 0; e < 4; ++e) store_c(ms[e], ns[e], acc[e]);
     }
     if (tid == 0) atomicExch(&p.ws_counters[blockIdx.x], 0u);
+    if (p.n_peers) {                   // one storing CTA per tile
+        named_bar_sync(1, CONSUMERS);
+        if (tid == 0) comm_cta_done(p, comm_seq, gridDim.x);
+    }
 }
 
 }  // namespace mma

@@ -293,9 +293,9 @@ int resolve_kernel(const twm_gemm_args* a)
     if (a->kernel_override != TWM_KERNEL_AUTO) return a->kernel_override;
     int kernel = auto_kernel(a->M, a->N, a->K, a->group_size, a->a_dtype == TWM_F16, a->packed_offsets != nullptr,
                              a->splits_override);
-    // pushing to tensor-parallel peers: the streaming kernel's cluster leaders push one or two rows, the
-    // narrow tcgen05 kernel's read-back warps up to 64
-    if (a->comm && a->a_dtype == TWM_F16) return a->M <= twm::mma::CLUSTER_ROWS ? TWM_KERNEL_MMA : TWM_KERNEL_TC;
+    // pushing to tensor-parallel peers: the streaming kernel's cluster leaders push one or two rows, its
+    // pre-pass form three to 32, the narrow tcgen05 kernel's read-back warps up to 64
+    if (a->comm && a->a_dtype == TWM_F16) return a->M < kTcFromRows ? TWM_KERNEL_MMA : TWM_KERNEL_TC;
     return kernel;
 }
 
@@ -564,9 +564,10 @@ extern "C" {
 }  // extern "C"
 
 namespace {
-// twm_plan; allow_prepass = false: the streaming MMA kernel without its staging pre-pass (up to eight rows)
+// twm_plan; prepass (streaming MMA kernel's staging pre-pass) 0: not used (up to eight rows), 1: by the size rule,
+// 2: from three rows on whatever the size
 twm_status plan_impl(int M, int N, int K, int group_size, int sm_count, int splits_override,
-                     int kernel_override, bool allow_prepass, twm_plan_t* out)
+                     int kernel_override, int prepass, twm_plan_t* out)
 {
     if (!out || !shape_ok(M, N, K, group_size)) return TWM_EINVAL;
     if (splits_override < 0 || splits_override > kMaxSplits) return TWM_EINVAL;
@@ -630,8 +631,8 @@ twm_status plan_impl(int M, int N, int K, int group_size, int sm_count, int spli
     out->workspace_bytes = (splits > 1 && !cluster) ? kCounterBytes + (size_t)splits * rows * N * sizeof(float) : 0;
     if (kernel == TWM_KERNEL_TC || kernel == TWM_KERNEL_TCW)    // + the launch's activations in the MMA's K order, behind the split-K part
         out->workspace_bytes = kCounterBytes + (splits > 1 ? (size_t)splits * rows * N * sizeof(float) : 0) + 256 + (size_t)rows * K * 2;
-    if (kernel == TWM_KERNEL_MMA && mma_prepass(rows, K, N)) {      // + the rows staged as B fragments with their group sums
-        if (allow_prepass)
+    if (kernel == TWM_KERNEL_MMA && (mma_prepass(rows, K, N) || (prepass == 2 && rows >= 3))) {      // + the rows staged as B fragments with their group sums
+        if (prepass)
             out->workspace_bytes = kCounterBytes + (splits > 1 ? (size_t)splits * rows * N * sizeof(float) : 0) + 256 + mma_rows_stage_bytes(rows, K, group_size);
         else if (rows > 8)
             return TWM_EINVAL;
@@ -646,7 +647,7 @@ extern "C" {
 twm_status twm_plan(int M, int N, int K, int group_size, int sm_count, int splits_override,
                     int kernel_override, twm_plan_t* out)
 {
-    return plan_impl(M, N, K, group_size, sm_count, splits_override, kernel_override, true, out);
+    return plan_impl(M, N, K, group_size, sm_count, splits_override, kernel_override, 1, out);
 }
 
 size_t twm_workspace_bytes(int M, int N, int K, int group_size)
@@ -659,7 +660,8 @@ size_t twm_workspace_bytes(int M, int N, int K, int group_size)
     if (twm_plan(M, N, K, group_size, kDefaultSms, 0, TWM_KERNEL_TCR, &tc) == TWM_OK) need = std::max(need, tc.workspace_bytes);
     if (twm_plan(M, N, K, group_size, kDefaultSms, 0, TWM_KERNEL_SIMT, &simt) == TWM_OK)
         need = std::max(need, simt.workspace_bytes);
-    if (twm_plan(M, N, K, group_size, kDefaultSms, 0, TWM_KERNEL_MMA, &simt) == TWM_OK)
+    // (the streaming MMA kernel with its staging pre-pass whatever the size: a push to peers asks for it)
+    if (plan_impl(M, N, K, group_size, kDefaultSms, 0, TWM_KERNEL_MMA, 2, &simt) == TWM_OK)
         need = std::max(need, simt.workspace_bytes);
     return need;
 }
@@ -691,17 +693,22 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
     if (kernel != TWM_KERNEL_SIMT && a->a_dtype != TWM_F16) return TWM_EINVAL;
     if (a->a_prologue != TWM_A_PLAIN && kernel != TWM_KERNEL_MMA) return TWM_EINVAL;
     // streaming MMA kernel: three rows or more on a large matrix, and nine or more on any, are staged by a pre-pass
-    bool prepass = kernel == TWM_KERNEL_MMA && mma_prepass(std::min(a->M, mma_rows_for(a->M)), a->K, a->N);
-    if (prepass && (a->packed_offsets != nullptr || a->comm || a->a_prologue != TWM_A_PLAIN)) {
-        if (a->M > 8) return TWM_EINVAL;
-        prepass = false;                         // the CTAs' own stager warps
+    // (a push to tensor-parallel peers of three rows or more always is: the pre-pass kernel carries the push)
+    int prepass = 0;
+    if (kernel == TWM_KERNEL_MMA) {
+        if (a->comm && a->M >= 3) prepass = 2;
+        else if (mma_prepass(std::min(a->M, mma_rows_for(a->M)), a->K, a->N)) prepass = 1;
+    }
+    if (prepass && (a->packed_offsets != nullptr || a->a_prologue != TWM_A_PLAIN)) {
+        if (a->M > 8 || a->comm) return TWM_EINVAL;
+        prepass = 0;                             // the CTAs' own stager warps
     }
     twm_plan_t pl;
     st = plan_impl(a->M, a->N, a->K, a->group_size, sm_count, a->splits_override, kernel, prepass, &pl);
     if (st != TWM_OK) return st;
-    if (prepass && a->M <= 8 && (!a->workspace || a->workspace_bytes < pl.workspace_bytes)) {
-        prepass = false;                         // no room for the staged rows: the stager warps need none
-        st = plan_impl(a->M, a->N, a->K, a->group_size, sm_count, a->splits_override, kernel, false, &pl);
+    if (prepass == 1 && a->M <= 8 && (!a->workspace || a->workspace_bytes < pl.workspace_bytes)) {
+        prepass = 0;                             // no room for the staged rows: the stager warps need none
+        st = plan_impl(a->M, a->N, a->K, a->group_size, sm_count, a->splits_override, kernel, 0, &pl);
         if (st != TWM_OK) return st;
     }
     if (pl.workspace_bytes > 0 && (!a->workspace || a->workspace_bytes < pl.workspace_bytes) &&
@@ -720,7 +727,8 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
     if (a->comm) {
         // pushing the result to tensor-parallel peers: streaming MMA kernel, no workspace-based split
         const twm_comm* cm = a->comm;
-        const bool mma_ok = kernel == TWM_KERNEL_MMA && a->M <= twm::mma::CLUSTER_ROWS && (pl.splits == 1 || pl.cluster_reduce);
+        const bool mma_ok = kernel == TWM_KERNEL_MMA &&
+                            ((a->M <= twm::mma::CLUSTER_ROWS && (pl.splits == 1 || pl.cluster_reduce)) || (prepass && a->M <= 32));
         const bool tc_ok = kernel == TWM_KERNEL_TC && a->M <= 64;           // one launch: one operation of the flag protocol
         if (!mma_ok && !tc_ok) return TWM_EINVAL;
         if (cm->n_ranks < 1 || cm->n_ranks > 8 || cm->rank < 0 || cm->rank >= cm->n_ranks || !cm->state) return TWM_EINVAL;
@@ -856,7 +864,7 @@ twm_status twm_gemm_w4a16_static_ws(const twm_gemm_args* a, void* stream_)
     if (st != TWM_OK) return st;
     if (pl.workspace_bytes > kStaticWsBytes && kernel == TWM_KERNEL_MMA && a->M <= 8) {
         // as twm_gemm_w4a16 will: up to eight rows can do without the staging pre-pass
-        st = plan_impl(a->M, a->N, a->K, a->group_size, sm_count, a->splits_override, kernel, false, &pl);
+        st = plan_impl(a->M, a->N, a->K, a->group_size, sm_count, a->splits_override, kernel, 0, &pl);
         if (st != TWM_OK) return st;
     }
     if (pl.workspace_bytes > kStaticWsBytes) {

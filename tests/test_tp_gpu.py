@@ -101,10 +101,13 @@ def test_sharded_stack_equals_unsharded(rows):
 
 
 @pytest.mark.parametrize("kernel,rows,n,splits", [(3, 1, 3072, 0), (3, 2, 3072, 0), (3, 1, 8192, 0), (3, 2, 16384, 0), (3, 1, 512, 0),
-                                                  (2, 5, 3072, 0), (2, 32, 8192, 0), (2, 64, 512, 0), (2, 32, 3072, 3)])
+                                                  (2, 5, 3072, 0), (2, 32, 8192, 0), (2, 64, 512, 0), (2, 32, 3072, 3),
+                                                  (3, 3, 3072, 0), (3, 8, 3072, 2), (3, 9, 8192, 0), (3, 16, 3072, 3), (3, 32, 512, 0),
+                                                  (3, 17, 3072, 0), (0, 12, 3072, 0), (0, 40, 3072, 0)])
 def test_row_parallel_push_and_sum(kernel, rows, n, splits):
-    """The row-parallel GEMM with `comm` on the streaming MMA kernel (one or two rows) and on the narrow
-    tcgen05 kernel (up to 64, also with K slices through the workspace), then the consumer: every
+    """The row-parallel GEMM with `comm` on the streaming MMA kernel (one or two rows from its cluster leaders,
+    three to 32 in its staged-rows form, also with K slices through the workspace), on the narrow tcgen05
+    kernel (up to 64), and with the kernel left to the library, then the consumer: every
     rank's x + sum over ranks equals x + the unsharded GEMM, and all ranks hold the same bits.  Run
     twice in a row: the sequence number alternates between the two buffer sets."""
     import ctypes as C
