@@ -651,7 +651,7 @@ stage_rows_kernel(uint8_t* __restrict__ bq, float* __restrict__ asum, const __ha
     if ((it & ((4 << gshift) - 1)) == 0) asum[(size_t)gi * MP + m] = -8.0f * s;
 }
 
-// MP = 16 or 32 rows staged; GSHIFT as above.  p.rows_b / p.rows_asum: the pre-pass's output.
+// MP = 8, 16, 24 or 32 rows staged (whole MMA N-tiles of eight); GSHIFT as above.  p.rows_b / p.rows_asum: the pre-pass's output.
 template <int MP, int GSHIFT>
 __global__ void __launch_bounds__(THREADS, TWM_MMA_MIN_CTAS)
 gemm_rows_kernel(const __grid_constant__ GemmParams p)

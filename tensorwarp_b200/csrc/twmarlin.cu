@@ -120,6 +120,8 @@ twm_status ensure_device(int* sm_count_out)
             raise_rows((const void*)twm::mma::gemm_rows_kernel<8, 2>, sizeof(twm::mma::RowsSmem<8>));
             raise_rows((const void*)twm::mma::gemm_rows_kernel<16, 0>, sizeof(twm::mma::RowsSmem<16>));
             raise_rows((const void*)twm::mma::gemm_rows_kernel<16, 2>, sizeof(twm::mma::RowsSmem<16>));
+            raise_rows((const void*)twm::mma::gemm_rows_kernel<24, 0>, sizeof(twm::mma::RowsSmem<24>));
+            raise_rows((const void*)twm::mma::gemm_rows_kernel<24, 2>, sizeof(twm::mma::RowsSmem<24>));
             raise_rows((const void*)twm::mma::gemm_rows_kernel<32, 0>, sizeof(twm::mma::RowsSmem<32>));
             raise_rows((const void*)twm::mma::gemm_rows_kernel<32, 2>, sizeof(twm::mma::RowsSmem<32>));
             auto raise_chain = [&](const void* fn) {
@@ -249,8 +251,8 @@ void choose_splits(int n_tiles, int nkb, int slots, int sm_count, int max_bps, i
 
 int mmax_for(int M) { return M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : 8)); }
 // activation rows one launch of the streaming MMA kernel carries: up to eight staged by the CTAs themselves,
-// sixteen or thirty-two through the staging pre-pass
-int mma_rows_for(int M) { return M <= 8 ? 8 : (M <= 16 ? 16 : 32); }
+// 16, 24 or 32 through the staging pre-pass
+int mma_rows_for(int M) { return M <= 8 ? 8 : (M <= 16 ? 16 : (M <= 24 ? 24 : 32)); }
 // Whether a launch of `rows` rows goes through the staging pre-pass.  From nine rows it must (the CTAs' own stager
 // warps stop at eight).  For three to eight rows both work: measured (us per GEMM, pre-pass / stager warps) on
 // K=3584 N=37888: 15.0 / 16.2 at 3 rows, 15.3 / 19.6 at 8; K=18944 N=3584: 15.3 / 15.4 and 15.8 / 17.0; but
@@ -547,23 +549,16 @@ twm_status launch_mma_rows(twm::GemmParams& p, char* stage, dim3 grid, unsigned 
         st = launch_op("stage_rows_kernel", twm::mma::stage_rows_kernel<0, 0>, dim3((items + 255) / 256), dim3(256), 0,
                        flags & TWM_FLAG_PDL, stream, (uint8_t*)stage, (float*)p.rows_asum, (const __half*)p.a, p.lda, p.M, mp, p.K, p.nkb);
     if (st != TWM_OK) return st;
-    const size_t smem = mp == 8 ? sizeof(twm::mma::RowsSmem<8>) : (mp == 16 ? sizeof(twm::mma::RowsSmem<16>) : sizeof(twm::mma::RowsSmem<32>));
-    if (mp == 8)
-        return p.group == 128 ? launch_op("mma::gemm_rows_kernel", twm::mma::gemm_rows_kernel<8, 2>, grid, dim3(twm::mma::THREADS), smem, flags & TWM_FLAG_PDL, stream, p)
-                              : launch_op("mma::gemm_rows_kernel", twm::mma::gemm_rows_kernel<8, 0>, grid, dim3(twm::mma::THREADS), smem, flags & TWM_FLAG_PDL, stream, p);
-    if (mp == 16)
-        return p.group == 128 ? launch_op("mma::gemm_rows_kernel", twm::mma::gemm_rows_kernel<16, 2>, grid, dim3(twm::mma::THREADS), smem, flags & TWM_FLAG_PDL, stream, p)
-                              : launch_op("mma::gemm_rows_kernel", twm::mma::gemm_rows_kernel<16, 0>, grid, dim3(twm::mma::THREADS), smem, flags & TWM_FLAG_PDL, stream, p);
-    return p.group == 128 ? launch_op("mma::gemm_rows_kernel", twm::mma::gemm_rows_kernel<32, 2>, grid, dim3(twm::mma::THREADS), smem, flags & TWM_FLAG_PDL, stream, p)
-                          : launch_op("mma::gemm_rows_kernel", twm::mma::gemm_rows_kernel<32, 0>, grid, dim3(twm::mma::THREADS), smem, flags & TWM_FLAG_PDL, stream, p);
+    auto go = [&](auto k128, auto k32, size_t smem) {
+        return p.group == 128 ? launch_op("mma::gemm_rows_kernel", k128, grid, dim3(twm::mma::THREADS), smem, flags & TWM_FLAG_PDL, stream, p)
+                              : launch_op("mma::gemm_rows_kernel", k32, grid, dim3(twm::mma::THREADS), smem, flags & TWM_FLAG_PDL, stream, p);
+    };
+    if (mp == 8) return go(twm::mma::gemm_rows_kernel<8, 2>, twm::mma::gemm_rows_kernel<8, 0>, sizeof(twm::mma::RowsSmem<8>));
+    if (mp == 16) return go(twm::mma::gemm_rows_kernel<16, 2>, twm::mma::gemm_rows_kernel<16, 0>, sizeof(twm::mma::RowsSmem<16>));
+    if (mp == 24) return go(twm::mma::gemm_rows_kernel<24, 2>, twm::mma::gemm_rows_kernel<24, 0>, sizeof(twm::mma::RowsSmem<24>));
+    return go(twm::mma::gemm_rows_kernel<32, 2>, twm::mma::gemm_rows_kernel<32, 0>, sizeof(twm::mma::RowsSmem<32>));
 }
-}  // namespace
 
-extern "C" {
-
-}  // extern "C"
-
-namespace {
 // twm_plan; prepass (streaming MMA kernel's staging pre-pass) 0: not used (up to eight rows), 1: by the size rule,
 // 2: from three rows on whatever the size
 twm_status plan_impl(int M, int N, int K, int group_size, int sm_count, int splits_override,

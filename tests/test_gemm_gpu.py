@@ -337,7 +337,7 @@ def test_tc_kernel_rejects_f32_activations():
 
 @pytest.mark.parametrize("group", [32, 128])
 @pytest.mark.parametrize("splits", [0, 1, 3])
-@pytest.mark.parametrize("m", [9, 12, 16, 17, 31, 32, 40, 67])
+@pytest.mark.parametrize("m", [9, 12, 16, 17, 24, 31, 32, 40, 67])
 @pytest.mark.parametrize("k,n", [(256, 128), (512, 200), (2048, 1000), (3584, 136)])
 def test_streaming_kernel_nine_to_32_rows(m, k, n, splits, group):
     """The warp-level-MMA kernel with its staging pre-pass (16- and 32-row launches, and what is left of
