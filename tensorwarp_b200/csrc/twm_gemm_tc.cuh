@@ -477,8 +477,8 @@ gemm_kernel(const __grid_constant__ GemmParams p)
 
         // tensor-parallel row shard: the FP32 result goes to every peer's receive slot instead of C
         const unsigned int comm_seq = p.n_peers ? ld_volatile_u32(p.comm_state) : 0u;
-        auto store_c = [&](int m, float vv) {
-            const size_t off = (size_t)m * p.ldc + n;
+        auto store_at = [&](int m, int nn, float vv) {
+            const size_t off = (size_t)m * p.ldc + nn;
             if (p.n_peers) { comm_store(p, comm_seq, off, vv); return; }
             if (p.c_is_f16) {
                 __half* cp = reinterpret_cast<__half*>(p.c);
@@ -490,6 +490,7 @@ gemm_kernel(const __grid_constant__ GemmParams p)
                 cp[off] = vv;
             }
         };
+        auto store_c = [&](int m, float vv) { store_at(m, n, vv); };
         if (ok && owner) {
 #pragma unroll
             for (int j = 0; j < RC; ++j) {
@@ -511,29 +512,30 @@ gemm_kernel(const __grid_constant__ GemmParams p)
             named_bar_sync(3, EPI_THREADS);
             if (sm.is_last) {
                 __threadfence();
-                if (owner && *abort_flag == 0) {
-                    // slices in slice order; four rows x four slices of loads in flight together (one load at
-                    // a time is a round trip to L2 per row and slice: 45 us of a 49 us launch at 32 rows, 7 slices)
-                    const int mend = min(p.M, row0 + RC);
-                    for (int m0 = row0; m0 < mend; m0 += 4) {
-                        float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                        for (int sp0 = 0; sp0 < p.splits; sp0 += 4) {
-                            float v[4][4];
-#pragma unroll
-                            for (int u = 0; u < 4; ++u)
-#pragma unroll
-                                for (int e = 0; e < 4; ++e)
-                                    v[u][e] = (sp0 + u < p.splits && m0 + e < mend)
-                                                  ? ld_cg_f32(&p.ws_partials[((size_t)(sp0 + u) * p.M + m0 + e) * p.N + n]) : 0.0f;
-#pragma unroll
-                            for (int u = 0; u < 4; ++u)
-#pragma unroll
-                                for (int e = 0; e < 4; ++e)
-                                    if (sp0 + u < p.splits) s[e] += v[u][e];
+                if (*abort_flag == 0) {
+                    // Slices in slice order.  The tile is walked four columns per thread, a warp along a row
+                    // (coalesced), by all read-back threads, the slices' loads issued together: a thread that
+                    // summed its own column row by row waited a round trip to L2 per row and slice (45 us of a
+                    // 49 us launch at 32 rows in 7 slices).
+                    const bool vec = (p.N & 3) == 0;
+                    const int e = tid - WARP_READ0 * 32;
+                    for (int idx = e; idx < p.M * 32; idx += EPI_THREADS) {
+                        const int m = idx >> 5, c = n0 + (idx & 31) * 4;
+                        if (c >= p.N) continue;
+                        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                        if (vec) {
+#pragma unroll 4
+                            for (int sp = 0; sp < p.splits; ++sp) {
+                                const float4 t4 = __ldcg(reinterpret_cast<const float4*>(&p.ws_partials[((size_t)sp * p.M + m) * p.N + c]));
+                                v[0] += t4.x; v[1] += t4.y; v[2] += t4.z; v[3] += t4.w;
+                            }
+                        } else {
+                            for (int sp = 0; sp < p.splits; ++sp)
+                                for (int j = 0; j < 4; ++j)
+                                    if (c + j < p.N) v[j] += ld_cg_f32(&p.ws_partials[((size_t)sp * p.M + m) * p.N + c + j]);
                         }
-#pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            if (m0 + e < mend) store_c(m0 + e, s[e]);
+                        for (int j = 0; j < 4; ++j)
+                            if (c + j < p.N) store_at(m, c + j, v[j]);
                     }
                 }
                 if (tid == WARP_READ0 * 32) atomicExch(&p.ws_counters[blockIdx.x], 0u);
