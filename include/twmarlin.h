@@ -54,8 +54,11 @@ enum {
                             route (dequant_q4_to_f16, quantize.rs:534-571), and one FP32 accumulator per 128 rows runs
                             over the whole K.  Every other kernel multiplies exact weights; ask for TWM_KERNEL_TCW to
                             keep them exact at these shapes too. */
-    TWM_KERNEL_MMA = 3   /* streaming kernel for M <= 8, FP16 activations, warp-level MMA on unpacked registers,
-                            128-column tiles with split-K (inside a thread-block cluster for M <= 2) */
+    TWM_KERNEL_MMA = 3   /* streaming kernel for up to 32 rows per launch, FP16 activations, warp-level MMA on unpacked
+                            registers, 128-column tiles with split-K (inside a thread-block cluster for M <= 2).  Up to
+                            eight rows its CTAs stage the activations themselves; from nine rows (and from three on
+                            matrices of 2^26 weights or more when the workspace has room) a pre-pass stages them once
+                            in the workspace (twm_plan's workspace_bytes says how much) */
 };
 
 /* Flags of twm_gemm_args.flags. */
@@ -138,8 +141,8 @@ typedef struct twm_gemm_args {
      * into every rank's receive buffer (plain stores over NVLink into the peer's own memory, tile
      * by tile as the tiles finish), and the grid's last storing CTA raises the arrival flags.  The
      * sum is taken by twm_allreduce_add_rmsnorm on each rank.  FP16 activations, M <= 64: one or two
-     * rows run on the streaming MMA kernel (one K slice per tile or a cluster reduce), more rows on
-     * the narrow tcgen05 kernel (workspace required). */
+     * rows run on the streaming MMA kernel (one K slice per tile or a cluster reduce), three to 32
+     * on its staged-rows form and more rows on the narrow tcgen05 kernel (workspace required for both). */
     const twm_comm* comm;
     /* What the activation rows hold: TWM_A_PLAIN (0) the activations; TWM_A_SILU_MUL / TWM_A_GEGLU: the
      * fused [gate | up] output of the preceding GEMM (2K f16 per row, up at column K, lda >= 2K), and the
