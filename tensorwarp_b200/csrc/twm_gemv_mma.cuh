@@ -1,4 +1,6 @@
-// twm_gemv_mma.cuh — the memory-bound W4A16 kernel for M <= 8, FP16 activations.
+// twm_gemv_mma.cuh — the streaming W4A16 kernels on warp-level MMA, FP16 activations: gemv_kernel for up to
+// eight rows (the decode kernel, memory-bound), gemm_rows_kernel + stage_rows_kernel for up to 32 (second half of
+// the file).
 //
 // Replaces warp_gemm_tw_marlin_m1 / _m1_direct
 // (crates/kernels/src/quantize.rs:1186-1298) and the launcher's split-K
@@ -10,9 +12,9 @@
 // Shape of the work.  A CTA owns 128 columns and a contiguous range of
 // 32-blocks of K.  One producer warp streams packed rows (2 KB contiguous per
 // block) and scale rows into a five-deep shared-memory ring with 1-D bulk
-// copies (TMA unit, mbarrier completion, no multicast).  One stager warp puts
-// the slice's activations into shared memory in the order the tensor-core
-// fragments want them, with the per-group sums that fold the "-8".  Eight
+// copies (TMA unit, mbarrier completion, no multicast).  One to four stager
+// warps put the slice's activations into shared memory in the order the
+// tensor-core fragments want them, with the per-group sums that fold the "-8".  Eight
 // consumer warps own 16 columns each for the whole K range, so there is no
 // cross-warp reduction.
 //
