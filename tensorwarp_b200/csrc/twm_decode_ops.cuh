@@ -613,6 +613,15 @@ __device__ __forceinline__ void att_ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t
 }
 
 constexpr int ATT_MMA_WARPS = 4;
+constexpr int ATT_MMA_STAGES = 3;                             // chunks of K and V in shared memory: one in use, two on their way
+constexpr int ATT_MMA_STAGE_BYTES = 2 * ATT_CHUNK * (128 * 2 + 16);
+constexpr int ATT_MMA_SMEM_BYTES = ATT_MMA_STAGES * ATT_MMA_STAGE_BYTES;   // dynamic shared memory of attn_span_mma_kernel<128, .>
+// 16 bytes global -> shared without passing through registers; src_bytes = 0 writes zeros and reads nothing
+__device__ __forceinline__ void att_cp_async16(uint32_t smem_dst, const void* gsrc, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void att_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void att_cp_async_wait_all_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 template <int HEAD_DIM, bool ROPE>
 __global__ void __launch_bounds__(ATT_MMA_WARPS * 32)
 attn_span_mma_kernel(float* __restrict__ part /* [heads][parts][HEAD_DIM + 2] */, const __half* __restrict__ q,
@@ -686,12 +695,14 @@ attn_span_mma_kernel(float* __restrict__ part /* [heads][parts][HEAD_DIM + 2] */
         }
         return;
     }
-    // K and V of the chunk; after the last chunk the same bytes hold the four warps' results
-    __shared__ __align__(16) unsigned char kv_s[2 * ATT_CHUNK * KROW];
+    // K and V of three chunks in turn (asynchronous copies, two chunks ahead of the arithmetic: with one chunk
+    // ahead and the copy staged through registers the pass reached 54 % of the HBM rate at 32 sequences x 4096
+    // tokens); after the last chunk the same bytes hold the four warps' results
+    extern __shared__ __align__(16) unsigned char kv_s[];
     __shared__ __align__(16) __half q_s[ATT_MAX_GROUP][HEAD_DIM];
-    unsigned char* k_s = kv_s;
-    unsigned char* v_s = kv_s + ATT_CHUNK * KROW;
-    static_assert(2 * ATT_CHUNK * KROW >= ATT_MMA_WARPS * ATT_MAX_GROUP * STRIDE * 4, "merge buffer fits the staging bytes");
+    constexpr int STAGE_BYTES = 2 * ATT_CHUNK * KROW;
+    static_assert(STAGE_BYTES == ATT_MMA_STAGE_BYTES, "host and device agree on the stage size");
+    static_assert(STAGE_BYTES >= ATT_MMA_WARPS * ATT_MAX_GROUP * STRIDE * 4, "merge buffer fits the staging bytes");
     for (int hh = w; hh < ATT_MAX_GROUP; hh += ATT_MMA_WARPS) {
         uint2 qr = make_uint2(0, 0);                     // heads past the group: zero rows
         if (hh < group)
@@ -707,50 +718,52 @@ attn_span_mma_kernel(float* __restrict__ part /* [heads][parts][HEAD_DIM + 2] */
         qa2[ks] = *reinterpret_cast<const uint32_t*>(&q_s[g][ks * 16 + 8 + 2 * t]);
     }
     const size_t row_stride = (size_t)kv_dim * 2;
-    uint4 kk[BATCH], vv[BATCH];
-    auto load_round = [&](int c) {
+    const uint32_t kv_base = smem_u32(kv_s);
+    // chunk c into ring stage st: every thread copies four 16-byte pieces of K and of V; rows past the end
+    // are zero-filled, the new row (not in the cache yet) is left to warp 0.  Always one commit, also for
+    // a chunk that does not exist, so that "all but the latest group" means the same in every iteration.
+    auto issue_chunk = [&](int c, int st) {
         const int t0 = c * ATT_CHUNK;
-        const int nt = min(ATT_CHUNK, len - t0);
-        const unsigned char* kg = reinterpret_cast<const unsigned char*>(k_cache + (size_t)t0 * kv_dim + kvh * HEAD_DIM);
-        const unsigned char* vg = reinterpret_cast<const unsigned char*>(v_cache + (size_t)t0 * kv_dim + kvh * HEAD_DIM);
+        if (t0 < len && c < chunk0 + span) {
+            const int nt = min(ATT_CHUNK, len - t0);
+            const unsigned char* kg = reinterpret_cast<const unsigned char*>(k_cache + (size_t)t0 * kv_dim + kvh * HEAD_DIM);
+            const unsigned char* vg = reinterpret_cast<const unsigned char*>(v_cache + (size_t)t0 * kv_dim + kvh * HEAD_DIM);
+            const uint32_t ks = kv_base + st * STAGE_BYTES, vs = ks + ATT_CHUNK * KROW;
 #pragma unroll
-        for (int b = 0; b < BATCH; ++b) {
-            const int i = threadIdx.x + b * THREADS;
-            const int tok = i / PER_ROW, piece = i % PER_ROW;
-            const bool in = (tok < nt) && !(has_new && t0 + tok == pos);      // rows past the end are zero; the new row is not in the cache yet
-            kk[b] = in ? *reinterpret_cast<const uint4*>(kg + tok * row_stride + piece * 16) : make_uint4(0, 0, 0, 0);
-            vv[b] = in ? *reinterpret_cast<const uint4*>(vg + tok * row_stride + piece * 16) : make_uint4(0, 0, 0, 0);
+            for (int b = 0; b < BATCH; ++b) {
+                const int i = threadIdx.x + b * THREADS;
+                const int tok = i / PER_ROW, piece = i % PER_ROW;
+                if (has_new && t0 + tok == pos) continue;                      // written by warp 0
+                const int bytes = (tok < nt) ? 16 : 0;
+                const size_t goff = (tok < nt) ? (size_t)tok * row_stride + piece * 16 : 0;
+                att_cp_async16(ks + tok * KROW + piece * 16, kg + goff, bytes);
+                att_cp_async16(vs + tok * KROW + piece * 16, vg + goff, bytes);
+            }
         }
-    };
-    auto store_round = [&](int c) {
-        const int t0 = c * ATT_CHUNK;
-#pragma unroll
-        for (int b = 0; b < BATCH; ++b) {
-            const int i = threadIdx.x + b * THREADS;
-            const int tok = i / PER_ROW, piece = i % PER_ROW;
-            if (has_new && t0 + tok == pos) continue;                          // written by warp 0
-            *reinterpret_cast<uint4*>(k_s + tok * KROW + piece * 16) = kk[b];
-            *reinterpret_cast<uint4*>(v_s + tok * KROW + piece * 16) = vv[b];
-        }
+        att_cp_async_commit();
     };
     const float scale = rsqrtf((float)HEAD_DIM);
     float m_run = -INFINITY, l_run = 0.0f;
     float o[HEAD_DIM / 8][2];                            // head g: dims 8 j + 2 t, + 1
 #pragma unroll
     for (int j = 0; j < HEAD_DIM / 8; ++j) { o[j][0] = 0.0f; o[j][1] = 0.0f; }
-    load_round(chunk0);
+    issue_chunk(chunk0, 0);
+    issue_chunk(chunk0 + 1, 1);
     for (int sc = 0; sc < span; ++sc) {
         const int c = chunk0 + sc;
         const int t0 = c * ATT_CHUNK;
         if (t0 >= len) break;                              // CTA-uniform
         const int nt = min(ATT_CHUNK, len - t0);
-        store_round(c);
+        const int st = sc % ATT_MMA_STAGES;
+        unsigned char* k_s = kv_s + st * STAGE_BYTES;
+        unsigned char* v_s = k_s + ATT_CHUNK * KROW;
+        att_cp_async_wait_all_but_one();                   // this thread's pieces of chunk c have landed
         if (has_new && w == 0 && pos >= t0 && pos < t0 + ATT_CHUNK) {
             *reinterpret_cast<uint2*>(k_s + (pos - t0) * KROW + lane * 8) = k_new;
             *reinterpret_cast<uint2*>(v_s + (pos - t0) * KROW + lane * 8) = v_new;
         }
-        __syncthreads();
-        if (sc + 1 < span && (c + 1) * ATT_CHUNK < len) load_round(c + 1);      // in flight during the arithmetic
+        __syncthreads();                                   // everybody's pieces; and everybody is done with chunk c - 1,
+        issue_chunk(c + 2, (sc + 2) % ATT_MMA_STAGES);     // whose stage the chunk after next now takes
         // ---- S[head g][tokens 8 w + 2 t, + 1] ----
         float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         {
@@ -795,9 +808,9 @@ attn_span_mma_kernel(float* __restrict__ part /* [heads][parts][HEAD_DIM + 2] */
                 att_mma_1688(d0, d1, pa, vb[jj]);
             }
         }
-        if (sc + 1 < span) __syncthreads();                // the next chunk overwrites the staged rows
     }
     // ---- merge the four warps' results per q head ----
+    asm volatile("cp.async.wait_all;" ::: "memory");       // (only empty groups can be left)
     __syncthreads();                                       // everybody is done with the staged rows
     float* mb = reinterpret_cast<float*>(kv_s);            // [warp][head][STRIDE]
     if (g < group) {

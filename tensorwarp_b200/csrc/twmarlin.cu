@@ -124,6 +124,8 @@ twm_status ensure_device(int* sm_count_out)
             raise_rows((const void*)twm::mma::gemm_rows_kernel<24, 2>, sizeof(twm::mma::RowsSmem<24>));
             raise_rows((const void*)twm::mma::gemm_rows_kernel<32, 0>, sizeof(twm::mma::RowsSmem<32>));
             raise_rows((const void*)twm::mma::gemm_rows_kernel<32, 2>, sizeof(twm::mma::RowsSmem<32>));
+            raise_rows((const void*)twm::ops::attn_span_mma_kernel<128, true>, twm::ops::ATT_MMA_SMEM_BYTES);
+            raise_rows((const void*)twm::ops::attn_span_mma_kernel<128, false>, twm::ops::ATT_MMA_SMEM_BYTES);
             auto raise_chain = [&](const void* fn) {
                 if (r == cudaSuccess)
                     r = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(twm::chain::Smem));
@@ -1402,13 +1404,13 @@ twm_status attn_decode_common(void* out, const void* q_or_qkv, void* k_cache, vo
     const float* nof = nullptr;
     const int* noi = nullptr;
     if (rope_table && span > 1)
-        st = launch_op("twm_attn_decode_rope(spans)", twm::ops::attn_span_mma_kernel<128, true>, grid, block, 0, flags, stream,
+        st = launch_op("twm_attn_decode_rope(spans)", twm::ops::attn_span_mma_kernel<128, true>, grid, block, twm::ops::ATT_MMA_SMEM_BYTES, flags, stream,
                        sp, qp, kp, vp, num_heads, num_kv_heads, len_buf, parts, span, max_seq, bias, rope_table, pos_buf);
     else if (rope_table)
         st = launch_op("twm_attn_decode_rope(chunks)", twm::ops::attn_chunk_kernel<128, true>, grid, block, 0, flags, stream,
                        sp, qp, kp, vp, num_heads, num_kv_heads, len_buf, parts, span, max_seq, bias, rope_table, pos_buf);
     else if (span > 1)
-        st = launch_op("twm_attn_decode(spans)", twm::ops::attn_span_mma_kernel<128, false>, grid, block, 0, flags, stream,
+        st = launch_op("twm_attn_decode(spans)", twm::ops::attn_span_mma_kernel<128, false>, grid, block, twm::ops::ATT_MMA_SMEM_BYTES, flags, stream,
                        sp, qp, kp, vp, num_heads, num_kv_heads, len_buf, parts, span, max_seq, nof, nof, noi);
     else
         st = launch_op("twm_attn_decode(chunks)", twm::ops::attn_chunk_kernel<128, false>, grid, block, 0, flags, stream,
