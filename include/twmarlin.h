@@ -147,8 +147,9 @@ typedef struct twm_gemm_args {
     /* What the activation rows hold: TWM_A_PLAIN (0) the activations; TWM_A_SILU_MUL / TWM_A_GEGLU: the
      * fused [gate | up] output of the preceding GEMM (2K f16 per row, up at column K, lda >= 2K), and the
      * GEMM multiplies act(gate) * up, computed in FP32 and rounded to f16 exactly as twm_silu_mul would
-     * have stored it, so the separate pass and its buffer go away.  M == 1, FP16 activations, streaming
-     * MMA kernel only (TWM_EINVAL otherwise). */
+     * have stored it, so the separate pass and its buffer go away.  M <= 32, FP16 activations, streaming
+     * MMA kernel only (TWM_EINVAL otherwise); from two rows on the prologue is applied by that kernel's
+     * staging pre-pass, so the workspace must hold the staged rows (twm_workspace_bytes covers it). */
     int a_prologue;
     /* Optional: the GEMM that will be enqueued after this one (on this stream, other kernels may come
      * between).  Read during this call only.  While this GEMM's grid drains, its CTAs ask the memory

@@ -537,19 +537,22 @@ twm_status launch_prepass(__half* xp, const __half* a, long lda, int rows, int K
 }
 
 // 9..32 rows on the streaming MMA kernel: the pre-pass that stages the rows as B fragments, then the GEMM
-twm_status launch_mma_rows(twm::GemmParams& p, char* stage, dim3 grid, unsigned flags, cudaStream_t stream)
+twm_status launch_mma_rows(twm::GemmParams& p, char* stage_buf, dim3 grid, unsigned flags, cudaStream_t stream)
 {
     const int mp = mma_rows_for(p.M);
-    p.rows_b = (const uint8_t*)stage;
-    p.rows_asum = (const float*)(stage + mma_rows_b_bytes(p.M, p.K));
+    p.rows_b = (const uint8_t*)stage_buf;
+    p.rows_asum = (const float*)(stage_buf + mma_rows_b_bytes(p.M, p.K));
     const int items = p.nkb * mp * 4;
     twm_status st;
+    auto stage = [&](auto kern) {
+        return launch_op("stage_rows_kernel", kern, dim3((items + 255) / 256), dim3(256), 0, flags & TWM_FLAG_PDL, stream,
+                         (uint8_t*)stage_buf, (float*)p.rows_asum, (const __half*)p.a, p.lda, p.M, mp, p.K, p.nkb);
+    };
+    // (a gated-activation prologue is applied here, once, while the rows are staged)
     if (p.group == 128)
-        st = launch_op("stage_rows_kernel", twm::mma::stage_rows_kernel<2, 0>, dim3((items + 255) / 256), dim3(256), 0,
-                       flags & TWM_FLAG_PDL, stream, (uint8_t*)stage, (float*)p.rows_asum, (const __half*)p.a, p.lda, p.M, mp, p.K, p.nkb);
+        st = p.a_kind == 0 ? stage(twm::mma::stage_rows_kernel<2, 0>) : (p.a_kind == 1 ? stage(twm::mma::stage_rows_kernel<2, 1>) : stage(twm::mma::stage_rows_kernel<2, 2>));
     else
-        st = launch_op("stage_rows_kernel", twm::mma::stage_rows_kernel<0, 0>, dim3((items + 255) / 256), dim3(256), 0,
-                       flags & TWM_FLAG_PDL, stream, (uint8_t*)stage, (float*)p.rows_asum, (const __half*)p.a, p.lda, p.M, mp, p.K, p.nkb);
+        st = p.a_kind == 0 ? stage(twm::mma::stage_rows_kernel<0, 0>) : (p.a_kind == 1 ? stage(twm::mma::stage_rows_kernel<0, 1>) : stage(twm::mma::stage_rows_kernel<0, 2>));
     if (st != TWM_OK) return st;
     auto go = [&](auto k128, auto k32, size_t smem) {
         return p.group == 128 ? launch_op("mma::gemm_rows_kernel", k128, grid, dim3(twm::mma::THREADS), smem, flags & TWM_FLAG_PDL, stream, p)
@@ -562,7 +565,7 @@ twm_status launch_mma_rows(twm::GemmParams& p, char* stage, dim3 grid, unsigned 
 }
 
 // twm_plan; prepass (streaming MMA kernel's staging pre-pass) 0: not used (up to eight rows), 1: by the size rule,
-// 2: from three rows on whatever the size
+// 2: from two rows on whatever the size
 twm_status plan_impl(int M, int N, int K, int group_size, int sm_count, int splits_override,
                      int kernel_override, int prepass, twm_plan_t* out)
 {
@@ -628,7 +631,7 @@ twm_status plan_impl(int M, int N, int K, int group_size, int sm_count, int spli
     out->workspace_bytes = (splits > 1 && !cluster) ? kCounterBytes + (size_t)splits * rows * N * sizeof(float) : 0;
     if (kernel == TWM_KERNEL_TC || kernel == TWM_KERNEL_TCW)    // + the launch's activations in the MMA's K order, behind the split-K part
         out->workspace_bytes = kCounterBytes + (splits > 1 ? (size_t)splits * rows * N * sizeof(float) : 0) + 256 + (size_t)rows * K * 2;
-    if (kernel == TWM_KERNEL_MMA && (mma_prepass(rows, K, N) || (prepass == 2 && rows >= 3))) {      // + the rows staged as B fragments with their group sums
+    if (kernel == TWM_KERNEL_MMA && (mma_prepass(rows, K, N) || (prepass == 2 && rows >= 2))) {      // + the rows staged as B fragments with their group sums
         if (prepass)
             out->workspace_bytes = kCounterBytes + (splits > 1 ? (size_t)splits * rows * N * sizeof(float) : 0) + 256 + mma_rows_stage_bytes(rows, K, group_size);
         else if (rows > 8)
@@ -672,7 +675,7 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
         return TWM_EINVAL;
     if (a->lda < a->K || a->ldc < a->N) return TWM_EINVAL;
     if (a->a_prologue < TWM_A_PLAIN || a->a_prologue > TWM_A_GEGLU) return TWM_EINVAL;
-    if (a->a_prologue != TWM_A_PLAIN && (a->M != 1 || a->a_dtype != TWM_F16 || a->lda < 2L * a->K)) return TWM_EINVAL;
+    if (a->a_prologue != TWM_A_PLAIN && (a->M > 32 || a->a_dtype != TWM_F16 || a->lda < 2L * a->K)) return TWM_EINVAL;
     if ((a->packed_offsets == nullptr) != (a->scales_offsets == nullptr)) return TWM_EINVAL;
     if (a->packed_offsets && a->expert_idx < 0) return TWM_EINVAL;
     if (reinterpret_cast<uintptr_t>(a->packed) & 15) return TWM_EALIGN;
@@ -690,14 +693,15 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
     if (kernel != TWM_KERNEL_SIMT && a->a_dtype != TWM_F16) return TWM_EINVAL;
     if (a->a_prologue != TWM_A_PLAIN && kernel != TWM_KERNEL_MMA) return TWM_EINVAL;
     // streaming MMA kernel: three rows or more on a large matrix, and nine or more on any, are staged by a pre-pass
-    // (a push to tensor-parallel peers of three rows or more always is: the pre-pass kernel carries the push)
+    // (a push to tensor-parallel peers of three rows or more always is: the pre-pass form carries the push; and so is
+    //  a gated-activation prologue on two rows or more: the pre-pass applies it)
     int prepass = 0;
     if (kernel == TWM_KERNEL_MMA) {
-        if (a->comm && a->M >= 3) prepass = 2;
+        if ((a->comm && a->M >= 3) || (a->a_prologue != TWM_A_PLAIN && a->M >= 2)) prepass = 2;
         else if (mma_prepass(std::min(a->M, mma_rows_for(a->M)), a->K, a->N)) prepass = 1;
     }
-    if (prepass && (a->packed_offsets != nullptr || a->a_prologue != TWM_A_PLAIN)) {
-        if (a->M > 8 || a->comm) return TWM_EINVAL;
+    if (prepass && a->packed_offsets != nullptr) {
+        if (a->M > 8 || prepass == 2) return TWM_EINVAL;
         prepass = 0;                             // the CTAs' own stager warps
     }
     twm_plan_t pl;
@@ -812,7 +816,7 @@ twm_status twm_gemm_w4a16(const twm_gemm_args* a, void* stream_)
             if (st != TWM_OK) return st;
             st = launch_tc(p, rows, dim3(pl.grid_x, pl.grid_y, 1), pdl, stream);
         }
-        else if (kernel == TWM_KERNEL_MMA && prepass && rows >= 3) {
+        else if (kernel == TWM_KERNEL_MMA && prepass && rows >= (prepass == 2 ? 2 : 3)) {
             const size_t part_bytes = pl.splits > 1 ? (size_t)pl.splits * std::min(a->M, row_step) * a->N * sizeof(float) : 0;
             char* stage = (char*)a->workspace + kCounterBytes + ((part_bytes + 255) / 256) * 256;
             st = launch_mma_rows(p, stage, dim3(pl.grid_x, pl.grid_y, 1), a->flags, stream);

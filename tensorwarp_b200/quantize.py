@@ -83,7 +83,7 @@ def gemm_tw_marlin(a: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, 
     """C[m,n] = A[m,k] x dequant(packed, scales); A and C are f32 or f16, row-major.
 
     The M > 1 form of ``gemm_tw_marlin_m1``; enqueue only, like the reference.  With
-    ``a_prologue=TWM_A_SILU_MUL`` (m = 1, f16) ``a`` is the [gate | up] output of the preceding GEMM
+    ``a_prologue=TWM_A_SILU_MUL`` (m <= 32, f16) ``a`` is the [gate | up] output of the preceding GEMM
     (2k values) and the GEMM reads silu(gate) * up: fused_silu_mul (ops.rs:966-977) without its pass.
     ``next_gemm=(packed, scales, m, n, k, group_size)`` names the GEMM that follows on the stream (same
     dtypes and workspace): while this one drains, the head of that one's weights is pulled into L2."""

@@ -303,7 +303,8 @@ class TPDecodeStack:
         after_down = (nl.wqkv, self.spec.n_qkv, cfg.hidden)
         self._gemm(self.normed, lw.wgu, self.gate_up, self.spec.n_gu, cfg.hidden, stream_ptr,            # column-parallel
                    then=(lw.w_down, cfg.hidden, self.spec.n_gu // 2))
-        if m == 1:      # one row: the down GEMM's activation reader takes silu(gate) * up on the fly (the same bits)
+        if m <= 32:     # the down GEMM's activation reader (one row) or its staging pre-pass (up to 32) takes
+                        # silu(gate) * up on the fly: the same bits as the separate pass
             self.launches += 1
             self._gemm(self.gate_up, lw.w_down, self.part, cfg.hidden, self.spec.n_gu // 2, stream_ptr, push=True, silu_mul=True,
                        then=after_down)

@@ -262,6 +262,36 @@ def test_gated_activation_prologue(k, n, splits, group, kind):
     assert _abs_err_over_rms(plain, ref) < TC_ABS_F32 * max(1.0, k / 3584)
 
 
+@pytest.mark.parametrize("kind", ["silu", "geglu"])
+@pytest.mark.parametrize("m", [2, 5, 16, 24, 32])
+@pytest.mark.parametrize("k,n,group", [(512, 300, 32), (2816, 1024, 128)])
+def test_gated_activation_prologue_on_several_rows(m, k, n, group, kind):
+    """Two to 32 rows: the streaming kernel's staging pre-pass applies the prologue while it stages the rows.
+    With one K slice the result is, bit for bit, that of the separate pass followed by the plain GEMM."""
+    _, packed, scales = _quantised(k, n, group, 59)
+    gu = (seeded_activations(m, 2 * k, 7) * 1.5).astype(np.float16).astype(np.float32)
+    if kind == "silu":
+        act_dev = torch.zeros((m, k), dtype=torch.float16, device=DEV)
+        _lib.check(_lib.lib().twm_silu_mul(act_dev.data_ptr(), _to_dev(gu, torch.float16).data_ptr(), m, k, 0,
+                                           torch.cuda.current_stream().cuda_stream), "twm_silu_mul")
+        act = act_dev.float().cpu().numpy()
+        prologue = _lib.TWM_A_SILU_MUL
+    else:
+        act = oracle.moe_split_geglu(gu, k).astype(np.float16).astype(np.float32)
+        prologue = _lib.TWM_A_GEGLU
+    ref = oracle.w4a16_f64(act, packed, scales, m, n, k, group)
+    for splits in (1, 0):
+        plain = _run_gemm(act, packed, scales, m, n, k, group, torch.float16, torch.float32, splits_override=splits)
+        fused = _run_gemm(gu, packed, scales, m, n, k, group, torch.float16, torch.float32, splits_override=splits,
+                          a_prologue=prologue, flags=_lib.TWM_FLAG_PDL)
+        if kind == "silu" and splits == 1:
+            assert np.array_equal(fused, plain)
+        # (gated activations are far from N(0,1): a few large products per output, so twice the usual bound
+        #  on the accumulator's truncation, still two orders below an FP16 step of the output)
+        assert _abs_err_over_rms(fused, ref) < (2e-3 if kind == "geglu" else 2 * TC_ABS_F32)
+        assert _abs_err_over_rms(plain, ref) < 2 * TC_ABS_F32
+
+
 def test_next_gemm_hint_changes_nothing_but_timing():
     """twm_gemm_args.next: the producer warps ask for the head of the following GEMM's weights; the
     result is the same bits with and without it, whatever the successor looks like (another shape, a
@@ -284,7 +314,9 @@ def test_gated_activation_prologue_refusals():
     k, n = 256, 256
     _, packed, scales = _quantised(k, n, 32, 58)
     gu2 = seeded_activations(2, 2 * k)
-    for kw in (dict(m=2, a=gu2, dt=torch.float16), dict(m=1, a=gu2[:1], dt=torch.float32),
+    gu33 = seeded_activations(33, 2 * k)
+    for kw in (dict(m=33, a=gu33, dt=torch.float16), dict(m=1, a=gu2[:1], dt=torch.float32),
+               dict(m=2, a=gu2, dt=torch.float16, kernel_override=_lib.TWM_KERNEL_TC),
                dict(m=1, a=gu2[:1], dt=torch.float16, kernel_override=_lib.TWM_KERNEL_SIMT)):
         with pytest.raises(_lib.TwmError) as e:
             extra = {x: kw[x] for x in kw if x not in ("m", "a", "dt")}
