@@ -257,7 +257,11 @@ class TPDecodeStack:
                              a_prologue=_lib.TWM_A_SILU_MUL if silu_mul else _lib.TWM_A_PLAIN,
                              next=C.addressof(nxt) if nxt is not None else None)
         check(_lib.lib().twm_gemm_w4a16(C.byref(args), stream_ptr), "twm_gemm_w4a16")
-        self.launches += 1
+        # kernels this call enqueued: the GEMM, and its activation pre-pass where the library uses one (from 9
+        # rows always; from 3 rows with a push or on a matrix of 2^26 weights; from 2 rows with the prologue)
+        m = self.rows
+        staged = m >= 9 or (m >= 3 and ((push and self.comm is not None) or k_in * n_out >= 1 << 26)) or (silu_mul and m >= 2)
+        self.launches += 2 if staged else 1
 
     def _join_and_norm(self, y_ptr, gamma_ptr, stream_ptr) -> None:
         """The summed output of the last row-parallel GEMM joins the residual stream, then RMSNorm."""
