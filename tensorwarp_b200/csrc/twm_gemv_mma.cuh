@@ -278,7 +278,10 @@ gemv_kernel(const __grid_constant__ GemmParams p)
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(A) & 15) == 0) && ((p.lda & 7) == 0) &&
                             ((p.a_expert_stride & 7) == 0);
         constexpr int SW = stager_warps(MP);
-        constexpr int PF = 8 / SW + (8 % SW ? 1 : 0);        // rounds of 32 items a warp has in flight; a chunk has eight
+        // rounds of 32 items a warp has in flight; a chunk has eight.  (Four with one stager warp: the eight
+        // 16-byte loads of a full chunk in flight made this kernel's 77 registers; with four it takes 64 and
+        // each of the four decode GEMMs got 0.1-0.3 us faster.)
+        constexpr int PF = SW == 1 ? 4 : 8 / SW + (8 % SW ? 1 : 0);
         const int sw = warp - CONSUMER_WARPS - 1;            // stager warp sw takes rounds sw, sw + SW, ...
         for (int chunk = 1; chunk < n_chunks; ++chunk) {     // chunk 0 is staged by the consumer warps (below)
             const int buf = chunk & 1;
