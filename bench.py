@@ -586,7 +586,8 @@ def config0_gemv(torch, q, device):
 
 def m_sweep(torch, q, device):
     """configs[2]: the 7B gate+up shape (K=3584, N=37888, G=128, FP16) at M = 1..256, eight distinct
-    weight sets per graph (568 MB, larger than L2), programmatic dependent launch; microseconds per
+    weight sets per graph (568 MB, larger than L2), programmatic dependent launch, every GEMM naming the
+    next one (`next_gemm`, as the decode engines do); microseconds per
     GEMM (for M above one launch's rows: all its launches), the kernel the heuristic chose, HBM and
     tensor fractions of the measured peaks."""
     from tensorwarp_b200 import _lib
@@ -612,8 +613,10 @@ def m_sweep(torch, q, device):
         stream = torch.cuda.Stream(device)
 
         def enqueue():
-            for p_, s_ in ws:
-                q.gemm_tw_marlin(a, p_, s_, c, m, n, k, group_size=GROUP, workspace=wsb, flags=_lib.TWM_FLAG_PDL)
+            for i, (p_, s_) in enumerate(ws):
+                nxt = ws[(i + 1) % copies]               # as a decode step does: each GEMM names its successor (L2 hint)
+                q.gemm_tw_marlin(a, p_, s_, c, m, n, k, group_size=GROUP, workspace=wsb, flags=_lib.TWM_FLAG_PDL,
+                                 next_gemm=(nxt[0], nxt[1], m, n, k, GROUP))
 
         with torch.cuda.stream(stream):
             enqueue()
