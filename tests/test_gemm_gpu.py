@@ -393,6 +393,19 @@ def test_streaming_kernel_nine_to_32_rows(m, k, n, splits, group):
     assert q.plan(min(m, 32), n, k, group).kernel == kern
 
 
+@pytest.mark.parametrize("m,k,n,group", [(12, 96, 40, 32), (20, 256, 72, 128), (32, 160, 8, 32), (9, 128, 1, 128)])
+def test_streaming_kernel_staged_rows_narrower_than_a_tile(m, k, n, group):
+    """Fewer columns than one 128-column tile (no tensor map: row-by-row bulk copies, scale rows copied by
+    the lanes when they are not 16-byte multiples), K shorter than a ring stage."""
+    _, packed, scales = _quantised(k, n, group, 54)
+    a = seeded_activations(m, k, 6)
+    ref = oracle.w4a16_f64(a, packed, scales, m, n, k, group)
+    for splits in (0, 1):
+        y = _run_gemm(a, packed, scales, m, n, k, group, torch.float16, torch.float32, kernel_override=_lib.TWM_KERNEL_MMA,
+                      splits_override=splits)
+        assert rel_err_floored(y, ref) < TOL_TC_F32 and _abs_err_over_rms(y, ref) < 2 * TC_ABS_F32
+
+
 def test_streaming_kernel_staged_rows_on_a_large_matrix():
     """Three to eight rows on a matrix of 2^26 weights or more go through the pre-pass as well; without room
     for the staged rows in the workspace the CTAs' own stager warps do the same work: same bits."""
