@@ -243,7 +243,10 @@ void choose_splits(int n_tiles, int nkb, int slots, int sm_count, int max_bps, i
             if (resident_clusters == 0) continue;
             waves = std::max(waves, ((long)n_tiles + resident_clusters - 1) / resident_clusters);
         }
-        double cost = (double)waves * (b + 16.0);
+        // Every wave after the first starts from empty rings on SMs that have just been vacated (no weights
+        // streamed in ahead of it): measured, about 40 blocks' worth.  K=28672 N=8192, one row: 9 slices (two
+        // waves of clusters) 33.3 us, 4 slices (one wave) 27.5; K=8192 N=57344: 3 slices 59.3 us, none 57.6.
+        double cost = (double)waves * (b + 16.0) + (double)(waves - 1) * 40.0;
         if (s_eff > 1) cost += 10.0 + 0.25 * s_eff;
         if (cost < best - 1e-9) { best = cost; best_s = s_eff; best_bps = b; }
     }
