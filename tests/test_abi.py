@@ -68,6 +68,33 @@ def test_plan_benchmark_shapes(twm_lib):
     assert (a.splits, a.blocks_per_split, a.grid_x) == (b.splits, b.blocks_per_split, b.grid_x)
 
 
+def test_plan_rows_and_staged_activations(twm_lib):
+    """Which kernel the heuristic names by row count, and the workspace a plan asks for: the streaming MMA kernel up
+    to 32 rows, with room for the staged rows ([K/32][rows16][64 B] + [K/G][rows16] f32 behind counters and K-slice
+    partials) from nine rows on any matrix and from three rows on matrices of 2^26 weights."""
+    k, n, g = 3584, 37888, 128
+    kinds = [_plan(twm_lib, m, n, k, g, 148, 0, 0)[1].kernel for m in (1, 8, 9, 16, 32, 33, 64, 65, 256)]
+    assert kinds == [_lib.TWM_KERNEL_MMA] * 5 + [_lib.TWM_KERNEL_TC] * 2 + [_lib.TWM_KERNEL_TCR] * 2
+    for m, rows in ((9, 16), (16, 16), (17, 24), (24, 24), (25, 32), (32, 32)):
+        p = _plan(twm_lib, m, n, k, g, 148, 0, _lib.TWM_KERNEL_MMA)[1]
+        assert p.splits == 1 and p.cluster_reduce == 0
+        assert p.workspace_bytes == 16384 + 256 + (k // 32) * rows * 64 + (k // g) * rows * 4, m
+        assert twm_lib.twm_workspace_bytes(m, n, k, g) >= p.workspace_bytes
+    # three to eight rows: staged on the large matrix, the CTAs' own stager warps on the small one
+    assert _plan(twm_lib, 3, n, k, g, 148, 0, _lib.TWM_KERNEL_MMA)[1].workspace_bytes == 16384 + 256 + (k // 32) * 8 * 64 + (k // g) * 8 * 4
+    assert _plan(twm_lib, 2, n, k, g, 148, 0, _lib.TWM_KERNEL_MMA)[1].workspace_bytes == 0
+    small = _plan(twm_lib, 4, 4608, k, g, 148, 0, _lib.TWM_KERNEL_MMA)[1]
+    assert small.splits > 1 and small.workspace_bytes == 16384 + small.splits * 4 * 4608 * 4
+    # ... but a caller may need the staged form there too (a push to tensor-parallel peers): covered by the size query
+    assert twm_lib.twm_workspace_bytes(4, 4608, k, g) >= small.workspace_bytes + 256 + (k // 32) * 8 * 64 + (k // g) * 8 * 4
+    # more rows than one launch carries: planned for the first launch's 32
+    p40 = _plan(twm_lib, 40, 4608, k, g, 148, 0, _lib.TWM_KERNEL_MMA)[1]
+    assert p40.workspace_bytes == 16384 + p40.splits * 32 * 4608 * 4 + 256 + (k // 32) * 32 * 64 + (k // g) * 32 * 4
+    # a K slice count that needs a second wave of CTAs is not chosen over one wave (70B-sized down projection)
+    p = _plan(twm_lib, 1, 8192, 28672, g, 148, 0, 0)[1]
+    assert p.grid_x * p.grid_y <= 2 * 148 and p.splits == 4
+
+
 def test_plan_rejects_bad_shapes(twm_lib):
     assert _plan(twm_lib, 1, 128, 100, 32, 148, 0, 0)[0] == _lib.TWM_EINVAL     # K % 32
     assert _plan(twm_lib, 1, 128, 96, 128, 148, 0, 0)[0] == _lib.TWM_EINVAL     # K % G
